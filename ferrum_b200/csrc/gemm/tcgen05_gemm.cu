@@ -1,0 +1,454 @@
+// bf16 x bf16 -> fp32-accumulate GEMM for sm_100a on the 5th-generation
+// tensor cores: TMA (cp.async.bulk.tensor, 128-byte swizzle) stages operand
+// tiles in shared memory, one elected thread issues tcgen05.mma with the
+// accumulator in tensor memory (TMEM), and four epilogue warps read the
+// accumulator back with tcgen05.ld and apply bias / activation / dtype
+// conversion while the next tile's main loop already runs (the 512 TMEM
+// columns hold two 128 x 256 fp32 accumulators).
+//
+// Replaces the reference's scalar i-j-p loop (ferrum-core/src/tensor.rs:2487-2558)
+// and the tiled / rayon / BLAS variants (ferrum-ops/src/matmul.rs:27-173).
+//
+// Computes   D[M,N] = act(A[M,K] * B[N,K]^T + bias[N])   (optionally += D)
+// where each operand may be stored K-major (reduction dimension contiguous)
+// or MN-major (M resp. N contiguous), which covers the three products of a
+// linear layer without a transpose copy:
+//   forward  y  = x  W^T : A K-major,  B K-major
+//   dgrad    dx = dy W   : A K-major,  B MN-major
+//   wgrad    dW = dy^T x : A MN-major, B MN-major
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one elected lane)
+//   warps 2..5  epilogue (TMEM lane quarter = warp_id % 4)
+// No cluster launch and no multicast TMA: every CTA loads its own tiles, so
+// the same binary is safe in multi-GPU jobs.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "../common/ptx.cuh"
+#include "../common/status.h"
+#include "../include/ferrum_kernels.h"
+
+namespace fb {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;      // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;   // K extent of one tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;  // m-blocks per rasterisation group (L2 reuse)
+
+template <int BN>
+struct Cfg {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+};
+
+struct GemmArgs {
+  void* out;
+  const float* bias;
+  int M, N, K;
+  long long ldc;
+  int a_mn_major, b_mn_major;
+  int out_bf16;
+  int act;
+  int beta;
+  int32_t* status;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case FB_ACT_RELU:
+      return fmaxf(x, 0.f);
+    case FB_ACT_GELU: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+      return 0.5f * x * (1.f + t);
+    }
+    case FB_ACT_SILU:
+      return x / (1.f + __expf(-x));
+    case FB_ACT_TANH: {
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+      return t;
+    }
+    case FB_ACT_SIGMOID:
+      return 1.f / (1.f + __expf(-x));
+    default:
+      return x;
+  }
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int per_group = kGroupM * num_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int gsize = min(num_m - first_m, kGroupM);
+  const int r = t - g * per_group;
+  m_blk = first_m + (r % gsize);
+  n_blk = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmArgs p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + C::kStages * C::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* tmem_full = empty_bar + C::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (p.M + kBM - 1) / kBM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&tmem_full[a], 1);
+      ptx::mbar_init(&tmem_empty[a], 4);
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tma_a);
+    ptx::prefetch_tensormap(&tma_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * kBM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
+            report_status(p.status, kStatusGemmTimeout, 1, blockIdx.x, stage);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+          const int k0 = kb * kBK;
+          if (p.a_mn_major) {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              ptx::tma_load_2d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0);
+          } else {
+            ptx::tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
+          }
+          if (p.b_mn_major) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              ptx::tma_load_2d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0);
+          } else {
+            ptx::tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+          }
+          ++issued;
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Drain: wait (bounded) for the copies this thread already issued so
+        // that no bulk copy is still writing shared memory when the CTA exits.
+        for (int s = 0; s < C::kStages; ++s) {
+          if (issued > s) {
+            const long long last = ((issued - 1 - s) / C::kStages) * C::kStages + s;
+            const uint32_t par = static_cast<uint32_t>((last / C::kStages) & 1);
+            const uint64_t t0 = ptx::globaltimer();
+            while (!ptx::mbar_try_wait(&full_bar[s], par)) {
+              if (ptx::globaltimer() - t0 > p.timeout_ns) break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc(1u, kBM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? kBK * 128 : 16;
+      const uint32_t b_lbo = p.b_mn_major ? kBK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
+          report_status(p.status, kStatusGemmTimeout, 2, blockIdx.x, acc);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
+            report_status(p.status, kStatusGemmTimeout, 3, blockIdx.x, stage);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[stage]);  // frees the smem slot when the MMAs retire
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(&tmem_full[acc]);  // accumulator complete -> epilogue
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int row = m_blk * kBM + quarter * 32 + lane;
+      const int n0 = n_blk * BN;
+      // The vote keeps the warp converged for the .sync.aligned TMEM loads below.
+      const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) report_status(p.status, kStatusGemmTimeout, 4, blockIdx.x, acc);
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int j = 0; j < BN / 32; ++j) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(taddr + j * 32, r);
+        ptx::tmem_wait_ld();
+        const int col0 = n0 + j * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+          }
+          if (p.act != FB_ACT_NONE) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
+          }
+          const bool full = (col0 + 32 <= p.N) && vec_ok;
+          if (p.out_bf16) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+              uint4* o4 = reinterpret_cast<uint4*>(o);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
+                  w[h] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+            }
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+              float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 x = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                if (p.beta) {
+                  const float4 old = o4[q];
+                  x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                }
+                o4[q] = x;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows,
+// row pitch `ld` elements, box = 64 x box_outer, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int num_tiles = ((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN);
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (num_tiles < grid) grid = num_tiles;
+  gemm_bf16_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace fb
+
+extern "C" int fb_gemm_bf16_supported(const void* a, const void* b, long long lda, long long ldb) {
+  return ((reinterpret_cast<uintptr_t>(a) & 15) == 0) && ((reinterpret_cast<uintptr_t>(b) & 15) == 0) &&
+         ((lda * 2) % 16 == 0) && ((ldb * 2) % 16 == 0);
+}
+
+extern "C" int fb_gemm_bf16(const void* a, const void* b, void* out, const float* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                            int out_bf16, int act, int beta, int max_ctas, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const bool small_n = N <= 128;
+  const int bn = small_n ? 128 : 256;
+  CUtensorMap ma, mb;
+  bool ok;
+  if (a_mn_major)
+    ok = make_map(&ma, a, M, K, lda, 64);
+  else
+    ok = make_map(&ma, a, K, M, lda, kBM);
+  if (!ok) return -2;
+  if (b_mn_major)
+    ok = make_map(&mb, b, N, K, ldb, 64);
+  else
+    ok = make_map(&mb, b, K, N, ldb, bn);
+  if (!ok) return -2;
+  GemmArgs args;
+  args.out = out;
+  args.bias = bias;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = out_bf16;
+  args.act = act;
+  args.beta = beta;
+  args.status = status;
+  args.timeout_ns = 2000000000ull;
+  return small_n ? launch<128>(ma, mb, args, max_ctas, stream) : launch<256>(ma, mb, args, max_ctas, stream);
+}

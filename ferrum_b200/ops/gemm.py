@@ -1,0 +1,110 @@
+"""Raw (non-autograd) GEMM launchers.
+
+``gemm_bf16``  — the tcgen05/TMEM kernel (``csrc/gemm/tcgen05_gemm.cu``).
+``gemm_f32``   — the fp32 SIMT kernel with arbitrary strides (``csrc/gemm/simt_gemm.cu``).
+
+Both compute ``out = act(A @ B^T + bias)`` in the "NT" convention used by
+``Linear`` (reference forward: ferrum-nn/src/linear.rs:78-89), where operand
+layouts are described by flags instead of transposed copies.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..utils import runtime as _rt
+
+ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "silu": 3, "tanh": 4, "sigmoid": 5}
+
+_max_ctas = 0  # 0 = all SMs; the DDP engine lowers this to leave SMs for the comm kernel
+
+
+def set_gemm_cta_limit(n: int) -> None:
+    """Cap the persistent GEMM grid (0 = one CTA per SM)."""
+    global _max_ctas
+    _max_ctas = int(n)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def bf16_operand_ok(t: torch.Tensor) -> bool:
+    """True when a 2-D bf16 tensor can be described by a TMA map (either major)."""
+    if t.dtype != torch.bfloat16 or t.dim() != 2:
+        return False
+    if t.data_ptr() % 16:
+        return False
+    s0, s1 = t.stride()
+    if s1 == 1:
+        return (s0 * 2) % 16 == 0 and s0 >= t.shape[1]
+    if s0 == 1:
+        return (s1 * 2) % 16 == 0 and s1 >= t.shape[0]
+    return False
+
+
+def _major(t: torch.Tensor):
+    """(mn_major flag, row pitch in elements) of an operand given as an [MN, K] view."""
+    s0, s1 = t.stride()
+    if s1 == 1:
+        return 0, s0  # stored [MN][K]: K-major
+    if s0 == 1:
+        return 1, s1  # stored [K][MN]: MN-major
+    raise ValueError("GEMM operand needs one unit stride")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+              out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+              accumulate: bool = False) -> torch.Tensor:
+    """``out[M,N] = act(a[M,K] @ b[N,K]^T + bias)`` on the tcgen05 tensor cores.
+
+    ``a`` and ``b`` are bf16 2-D tensors with one unit stride (any of the two);
+    a transposed view (``x.t()``) is consumed as an MN-major operand without a copy.
+    """
+    assert a.is_cuda and b.is_cuda and a.dim() == 2 and b.dim() == 2
+    M, K = a.shape
+    N, Kb = b.shape
+    assert K == Kb, f"inner dimensions differ: {a.shape} x {b.shape}^T"
+    a_mn, lda = _major(a)
+    b_mn, ldb = _major(b)
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    if accumulate:
+        assert out.dtype == torch.float32, "accumulate needs an fp32 output"
+    lib = _lib.cuda()
+    rc = lib.fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+                          M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
+                          ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
+    _lib.check(rc, "fb_gemm_bf16")
+    return out
+
+
+def gemm_f32(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+             out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """fp32 ``out = act(a @ b^T + bias)`` with arbitrary strides; ``a``/``b`` may be 2-D or batched 3-D."""
+    assert a.is_cuda and a.dtype == torch.float32 and b.dtype == torch.float32
+    batched = a.dim() == 3
+    if batched:
+        Bt, M, K = a.shape
+        _, N, _ = b.shape
+        sam, sak = a.stride(1), a.stride(2)
+        sbn, sbk = b.stride(1), b.stride(2)
+        bsa, bsb = a.stride(0), b.stride(0)
+    else:
+        Bt = 1
+        M, K = a.shape
+        N, _ = b.shape
+        sam, sak = a.stride()
+        sbn, sbk = b.stride()
+        bsa = bsb = 0
+    if out is None:
+        out = torch.empty((Bt, M, N) if batched else (M, N), device=a.device, dtype=torch.float32)
+    ldc = out.stride(-2)
+    bsc = out.stride(0) if batched else 0
+    lib = _lib.cuda()
+    rc = lib.fb_gemm_f32_simt(a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                              bias.data_ptr() if bias is not None else None, M, N, K, sam, sak, sbk, sbn, ldc,
+                              ACT[act], 1 if accumulate else 0, Bt, bsa, bsb, bsc, _stream())
+    _lib.check(rc, "fb_gemm_f32_simt")
+    return out

@@ -1,0 +1,99 @@
+"""tcgen05 GEMM and SIMT GEMM against a plain fp32 PyTorch reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, bias, act):
+    y = a.float() @ b.float().t()
+    if bias is not None:
+        y = y + bias
+    if act == "relu":
+        y = torch.relu(y)
+    elif act == "gelu":
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = torch.nn.functional.silu(y)
+    return y
+
+
+def _mk(rows, cols, mn_major, scale=1.0):
+    """bf16 [rows(MN), cols(K)] view, stored K-major or MN-major."""
+    if mn_major:
+        return (torch.randn(cols, rows, device="cuda") * scale).to(torch.bfloat16).t()
+    return (torch.randn(rows, cols, device="cuda") * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (384, 200, 328), (136, 72, 1000),
+                                   (1024, 1000, 4096)])
+def test_gemm_bf16_layouts(a_mn, b_mn, M, N, K):
+    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(M * 7 + N * 3 + K + a_mn * 2 + b_mn)
+    a = _mk(M, K, a_mn, 0.5)
+    b = _mk(N, K, b_mn, 0.5)
+    out = gemm_bf16(a, b, out_dtype=torch.float32)
+    check_status()
+    ref = _ref(a, b, None, None)
+    err = (out - ref).abs().max().item()
+    tol = 2e-3 * (K ** 0.5) * 0.25 + 1e-3
+    assert err < tol, f"max err {err} (tol {tol}) for {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}"
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu", "silu"])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_bf16_epilogue(act, out_dtype):
+    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(1)
+    M, N, K = 300, 520, 192
+    a = _mk(M, K, 0, 0.3)
+    b = _mk(N, K, 0, 0.3)
+    bias = torch.randn(N, device="cuda")
+    out = gemm_bf16(a, b, bias=bias, act=act, out_dtype=out_dtype)
+    check_status()
+    ref = _ref(a, b, bias, act)
+    tol = 3e-2 if out_dtype == torch.bfloat16 else 5e-3
+    assert (out.float() - ref).abs().max().item() < tol * max(1.0, ref.abs().max().item())
+
+
+def test_gemm_bf16_accumulate():
+    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(2)
+    a = _mk(256, 128, 1, 0.3)
+    b = _mk(264, 128, 1, 0.3)
+    out = torch.randn(256, 264, device="cuda")
+    ref = out + _ref(a, b, None, None)
+    gemm_bf16(a, b, out=out, accumulate=True)
+    check_status()
+    assert (out - ref).abs().max().item() < 5e-3
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_gemm_f32_simt(ta, tb):
+    from ferrum_b200.ops.gemm import gemm_f32
+
+    torch.manual_seed(3)
+    M, N, K = 70, 45, 33
+    a = torch.randn(K, M, device="cuda").t() if ta else torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda").t() if tb else torch.randn(N, K, device="cuda")
+    bias = torch.randn(N, device="cuda")
+    out = gemm_f32(a, b, bias=bias, act="relu")
+    ref = torch.relu(a @ b.t() + bias)
+    assert torch.allclose(out, ref, atol=1e-4, rtol=1e-4)
+
+
+def test_gemm_f32_batched():
+    from ferrum_b200.ops.gemm import gemm_f32
+
+    torch.manual_seed(4)
+    a = torch.randn(3, 17, 29, device="cuda")
+    b = torch.randn(3, 11, 29, device="cuda")
+    out = gemm_f32(a, b)
+    assert torch.allclose(out, a @ b.transpose(1, 2), atol=1e-4, rtol=1e-4)
