@@ -1,0 +1,258 @@
+"""Headline benchmark: training throughput of the 8-block, 4096-wide MLP (125.8 M parameters).
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference|torch]
+
+Model / config: 8 x [Linear(., 4096) - GELU - LayerNorm(4096)], input 1024 features ~ N(0,1), 1000-way head,
+uniform labels, cross-entropy, Adam lr 3e-4, per-GPU batch 8192, fp32 master weights, bf16 tensor-core GEMMs,
+25 MB gradient buckets; weak scaling (per-GPU batch fixed).  Synthetic data, random-init weights.
+
+One rank per GPU.  For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N
+--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...``.  W untimed warm-up steps, then exactly K steps
+timed with CUDA events between barrier + synchronize pairs; the reported time is the max over ranks.  Rank 0
+prints one JSON line.
+
+``--impl torch`` runs the stock torch DDP (NCCL + cuBLAS, bf16 autocast, fused Adam) build of the same model:
+the comparison baseline.  ``--impl reference`` is the arm for the unmodified reference; it is a Rust workspace
+with no Python package and no toolchain to build it in this image, so that arm reports itself unavailable.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+MODEL = dict(in_features=1024, width=4096, depth=8, num_classes=1000)
+PER_GPU_BATCH = 8192
+LR = 3e-4
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
+    ap.add_argument("--batch", type=int, default=PER_GPU_BATCH, help="per-GPU batch")
+    ap.add_argument("--depth", type=int, default=MODEL["depth"])
+    ap.add_argument("--width", type=int, default=MODEL["width"])
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    return rank, world, local
+
+
+def timed_steps(step_fn, steps, world, barrier):
+    import torch
+
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def run_ours(args):
+    import torch
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    import ferrum_b200 as fb
+    from ferrum_b200 import _lib, nn, optim
+    from ferrum_b200.models import wide_mlp
+
+    dev = fb.Device.Cuda(local)
+    if world > 1:
+        fb.distributed.init_process_group_from_env(backend="nvlink")
+    torch.manual_seed(1234)
+    model = wide_mlp(MODEL["in_features"], args.width, args.depth, MODEL["num_classes"], device=dev)
+    opt = optim.Adam(model.parameters(), optim.AdamConfig(lr=LR))
+    engine = None
+    if world > 1:
+        engine = fb.distributed.DistributedDataParallel(model, fb.distributed.get_world()).bucket_size_mb(25)
+        engine.fuse_optimizer(opt)
+        net = engine
+    else:
+        net = model
+    B = args.batch
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x_dev = torch.randn(B, MODEL["in_features"], device="cuda", generator=g)
+    y_dev = torch.randint(0, MODEL["num_classes"], (B,), device="cuda", generator=g)
+    x_pin = x_dev.cpu().pin_memory()
+    y_pin = y_dev.cpu().pin_memory()
+
+    def train_step(x, y):
+        opt.zero_grad()
+        with fb.autocast():
+            logits = net(x)
+            loss = nn.cross_entropy(logits, y)
+        loss.backward()
+        opt.step()
+        return loss
+
+    def step_device():
+        train_step(x_dev, y_dev)
+
+    losses = []
+
+    def step_e2e():
+        x = x_pin.to("cuda", non_blocking=True)
+        y = y_pin.to("cuda", non_blocking=True)
+        loss = train_step(x, y)
+        losses.append(float(loss.item()))  # device -> host read of the step result
+
+    if world > 1:
+        import torch.distributed as dist
+
+        barrier = dist.barrier
+    else:
+        def barrier():
+            return None
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    ms = timed_steps(step_device, args.steps, world, barrier)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            step_e2e()
+        ms_e2e = timed_steps(step_e2e, args.steps, world, barrier)
+        e2e = {"value": args.steps * B * world / (ms_e2e / 1e3), "unit": "samples/s",
+               "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": (x_pin.numel() * x_pin.element_size() + y_pin.numel() * y_pin.element_size()),
+               "d2h_bytes_per_step": 4, "final_loss": losses[-1] if losses else None}
+    fb.utils.runtime.check_status()
+    if engine is not None:
+        engine.shutdown()
+    return ms, launches, clocks, e2e, "nvlink-fused-ddp" if world > 1 else "single"
+
+
+def run_torch(args):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import torch_ddp_mlp
+
+    return torch_ddp_mlp.run(args, MODEL, LR, dist_env, timed_steps, ClockSampler)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "reference is a Rust workspace (no Python package; pip install of "
+                                         "/root/reference fails: no setup.py/pyproject.toml) and cargo/rustc are not "
+                                         "in this image, so it cannot be built or run here"}))
+        return 0
+    rank, world, _ = dist_env()
+    if world != args.gpus and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    if args.impl == "ours":
+        ms, launches, clocks, e2e, par = run_ours(args)
+    else:
+        ms, launches, clocks, e2e, par = run_torch(args)
+    if rank != 0:
+        return 0
+    steps = args.steps
+    value = steps * args.batch * world / (ms / 1e3)
+    out = {
+        "metric": "MLP-4096x8 DDP train samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+        "config": {"model": f"MLP {args.depth}x[Linear({args.width})-GELU-LayerNorm] + 1000-way head, 1024 inputs",
+                   "global_batch": args.batch * world, "per_gpu_batch": args.batch, "seq_len": 1,
+                   "parallelism": f"dp{world}" if world > 1 else "single-gpu", "engine": par,
+                   "optimizer": "Adam lr 3e-4 (fp32 master weights)", "loss": "cross_entropy",
+                   "l2": "working set per step (>700 MB of weights, activations, optimizer state) exceeds the "
+                         "126 MB L2, no explicit flush"},
+        "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -105,7 +105,8 @@ _CUDA_SIGS = {
     "fb_cast": (I, [P, P, LL, I, I, P]),
     "fb_transpose_2d": (I, [P, P, I, I, I, P]),
     # reductions
-    "fb_reduce": (I, [P, P, LL, LL, LL, I, P]),
+    "fb_reduce_scratch_elems": (LL, [LL, LL, LL]),
+    "fb_reduce": (I, [P, P, LL, LL, LL, I, P, LL, P]),
     "fb_arg_reduce": (I, [P, P, P, LL, LL, LL, I, P]),
     "fb_colsum": (I, [P, P, LL, LL, I, I, P]),
     # norms
@@ -152,6 +153,43 @@ def _bind(lib, sigs, strict: bool = False):
     return lib
 
 
+_launches = 0
+
+
+class _CountingLib:
+    """Forwards attribute access to the CDLL and counts calls of kernel launchers.
+
+    Every entry point that is not part of the runtime layer (``fb_rt_*``) or a pure
+    query enqueues at least one of this package's kernels, so the count is a lower
+    bound on kernel launches; ``launch_count()`` reads it.
+    """
+
+    _NO_COUNT = ("fb_rt_", "fb_reduce_scratch_elems", "fb_layernorm_bwd_blocks", "fb_gemm_bf16_supported",
+                 "fb_dist_query_")
+
+    def __init__(self, lib):
+        self._lib = lib
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name.startswith(self._NO_COUNT):
+            setattr(self, name, fn)
+            return fn
+
+        def counted(*args, _fn=fn):
+            global _launches
+            _launches += 1
+            return _fn(*args)
+
+        setattr(self, name, counted)
+        return counted
+
+
+def launch_count() -> int:
+    """Number of kernel-launcher calls made through this module so far."""
+    return _launches
+
+
 def cuda():
     """The sm_100a kernel library (``lib/libferrum_b200_cuda.so``)."""
     global _cuda
@@ -163,7 +201,7 @@ def cuda():
                 _bind(lib, _CUDA_SIGS)
                 from . import _lib_dist  # signatures of the inter-GPU entry points
                 _bind(lib, _lib_dist.SIGS)
-                _cuda = lib
+                _cuda = _CountingLib(lib)
     return _cuda
 
 

@@ -68,8 +68,11 @@ int fb_cast(const void* src, void* dst, long long n, int src_dtype, int dst_dtyp
 int fb_transpose_2d(const void* src, void* dst, int rows, int cols, int elem_size, cudaStream_t stream);
 
 // ---- reductions: input viewed as [outer, R, inner] --------------------------
-int fb_reduce(const float* x, float* out, long long outer, long long R, long long inner, int op,
-              cudaStream_t stream);
+// `scratch` (may be NULL) lets the kernel split R over several blocks when there are
+// few outputs; fb_reduce_scratch_elems() says how many floats that takes (0 = none).
+long long fb_reduce_scratch_elems(long long outer, long long R, long long inner);
+int fb_reduce(const float* x, float* out, long long outer, long long R, long long inner, int op, float* scratch,
+              long long scratch_elems, cudaStream_t stream);
 int fb_arg_reduce(const float* x, long long* idx, float* val, long long outer, long long R, long long inner,
                   int is_max, cudaStream_t stream);
 // Column sums of a [rows, cols] matrix (fp32 or bf16 in, fp32 out): bias gradients.

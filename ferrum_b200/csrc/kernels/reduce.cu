@@ -1,0 +1,297 @@
+// Reductions over a tensor viewed as [outer, R, inner]: sum / mean / max / min /
+// prod, argmax / argmin, and the column-sum used for bias gradients.
+//
+// Reference: ferrum-cuda/src/kernels.rs:264-369 (reduce_op, outer x reduce x inner
+// loops) and ferrum-core/src/tensor.rs:1611-2243 (sum, mean, sum_dim, mean_dim,
+// argmax, argmin, max_dim, min_dim).
+//
+// inner == 1  : one block per row (vector loads, warp-shuffle + smem tree).
+// inner  > 1  : one thread per output column, coalesced across `inner`.
+// When there are too few outputs to fill the GPU, R is split across blockIdx.y
+// and the partials go through a caller-provided scratch buffer (two launches,
+// deterministic order).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+
+#include "../include/ferrum_kernels.h"
+
+namespace fb {
+namespace {
+
+__device__ __forceinline__ float red_identity(int op) {
+  switch (op) {
+    case FB_RED_MAX: return -FLT_MAX;
+    case FB_RED_MIN: return FLT_MAX;
+    case FB_RED_PROD: return 1.f;
+    default: return 0.f;
+  }
+}
+__device__ __forceinline__ float red_combine(float a, float b, int op) {
+  switch (op) {
+    case FB_RED_MAX: return fmaxf(a, b);
+    case FB_RED_MIN: return fminf(a, b);
+    case FB_RED_PROD: return a * b;
+    default: return a + b;
+  }
+}
+
+__device__ __forceinline__ float block_reduce(float v, int op, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = red_combine(v, __shfl_xor_sync(0xffffffffu, v, o), op);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  v = (threadIdx.x < nw) ? smem[threadIdx.x] : red_identity(op);
+  if (warp == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = red_combine(v, __shfl_xor_sync(0xffffffffu, v, o), op);
+  }
+  return v;  // valid in thread 0
+}
+
+// x: [outer, R]; block (row = blockIdx.x, split = blockIdx.y) reduces its segment.
+__global__ void reduce_rows_kernel(const float* __restrict__ x, float* __restrict__ out, long long R, int op,
+                                   float scale, int splits) {
+  __shared__ float smem[32];
+  const long long row = blockIdx.x;
+  const long long seg = (R + splits - 1) / splits;
+  const long long lo = blockIdx.y * seg;
+  const long long hi = min(R, lo + seg);
+  const float* p = x + row * R;
+  const int cop = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
+  float acc = red_identity(cop);
+  // vector body when the segment start is 16-byte aligned
+  long long i = lo + threadIdx.x;
+  if (((reinterpret_cast<uintptr_t>(p + lo) & 15) == 0) && hi - lo >= 4) {
+    const long long n4 = (hi - lo) >> 2;
+    const float4* p4 = reinterpret_cast<const float4*>(p + lo);
+    for (long long k = threadIdx.x; k < n4; k += blockDim.x) {
+      const float4 v = p4[k];
+      acc = red_combine(acc, red_combine(red_combine(v.x, v.y, cop), red_combine(v.z, v.w, cop), cop), cop);
+    }
+    i = lo + (n4 << 2) + threadIdx.x;
+  }
+  for (; i < hi; i += blockDim.x) acc = red_combine(acc, p[i], cop);
+  acc = block_reduce(acc, cop, smem);
+  if (threadIdx.x == 0) out[row * splits + blockIdx.y] = acc * scale;
+}
+
+// x: [outer, R, inner]; thread per (outer, inner), optional split of R over blockIdx.y.
+__global__ void reduce_cols_kernel(const float* __restrict__ x, float* __restrict__ out, long long outer,
+                                   long long R, long long inner, int op, float scale, int splits) {
+  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (col >= outer * inner) return;
+  const long long o = col / inner, in = col % inner;
+  const long long seg = (R + splits - 1) / splits;
+  const long long lo = blockIdx.y * seg;
+  const long long hi = min(R, lo + seg);
+  const int cop = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
+  float acc = red_identity(cop);
+  const float* p = x + o * R * inner + in;
+  for (long long r = lo; r < hi; ++r) acc = red_combine(acc, p[r * inner], cop);
+  // partial layout: [splits, outer*inner]
+  out[static_cast<long long>(blockIdx.y) * outer * inner + col] = acc * scale;
+}
+
+__global__ void arg_rows_kernel(const float* __restrict__ x, long long* __restrict__ idx, float* __restrict__ val,
+                                long long R, int is_max) {
+  __shared__ float sv[128];
+  __shared__ long long si[128];
+  const long long row = blockIdx.x;
+  const float* p = x + row * R;
+  float best = is_max ? -FLT_MAX : FLT_MAX;
+  long long bi = 0x7fffffffffffffffLL;
+  for (long long i = threadIdx.x; i < R; i += blockDim.x) {
+    const float v = p[i];
+    if (is_max ? (v > best) : (v < best)) {
+      best = v;
+      bi = i;
+    }
+  }
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = sv[threadIdx.x + s];
+      const long long oi = si[threadIdx.x + s];
+      const float mv = sv[threadIdx.x];
+      const long long mi = si[threadIdx.x];
+      const bool better = is_max ? (ov > mv) : (ov < mv);
+      if (better || (ov == mv && oi < mi)) {
+        sv[threadIdx.x] = ov;
+        si[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    idx[row] = si[0] == 0x7fffffffffffffffLL ? 0 : si[0];
+    if (val) val[row] = sv[0];
+  }
+}
+
+__global__ void arg_cols_kernel(const float* __restrict__ x, long long* __restrict__ idx, float* __restrict__ val,
+                                long long outer, long long R, long long inner, int is_max) {
+  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (col >= outer * inner) return;
+  const long long o = col / inner, in = col % inner;
+  const float* p = x + o * R * inner + in;
+  float best = p[0];
+  long long bi = 0;
+  for (long long r = 1; r < R; ++r) {
+    const float v = p[r * inner];
+    if (is_max ? (v > best) : (v < best)) {
+      best = v;
+      bi = r;
+    }
+  }
+  idx[col] = bi;
+  if (val) val[col] = best;
+}
+
+// Column sums of [rows, cols]: block = 128 columns x a chunk of rows, 8 warps
+// walk the rows, lanes own 4 adjacent columns; partials meet in shared memory
+// and leave with one atomicAdd per column per block.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, long long cols,
+              long long rows_per_block) {
+  __shared__ float sm[8][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long c0 = static_cast<long long>(blockIdx.x) * 128 + lane * 4;
+  const long long r_lo = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r_hi = min(rows, r_lo + rows_per_block);
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  const bool vec = (cols % 4 == 0) && (c0 + 3 < cols) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  for (long long r = r_lo + warp; r < r_hi; r += 8) {
+    const T* p = x + r * cols + c0;
+    if (vec) {
+      if constexpr (sizeof(T) == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        a0 += f0.x; a1 += f0.y; a2 += f1.x; a3 += f1.y;
+      }
+    } else {
+      if (c0 < cols) a0 += static_cast<float>(p[0]);
+      if (c0 + 1 < cols) a1 += static_cast<float>(p[1]);
+      if (c0 + 2 < cols) a2 += static_cast<float>(p[2]);
+      if (c0 + 3 < cols) a3 += static_cast<float>(p[3]);
+    }
+  }
+  sm[warp][lane * 4 + 0] = a0;
+  sm[warp][lane * 4 + 1] = a1;
+  sm[warp][lane * 4 + 2] = a2;
+  sm[warp][lane * 4 + 3] = a3;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += sm[w][threadIdx.x];
+    const long long c = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
+    if (c < cols) atomicAdd(out + c, s);
+  }
+}
+
+int sm_count() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+// Number of scratch floats fb_reduce wants for this problem (0 = single pass).
+extern "C" long long fb_reduce_scratch_elems(long long outer, long long R, long long inner) {
+  const long long outs = outer * inner;
+  if (outs >= 1024 || R < 4096) return 0;
+  long long splits = (static_cast<long long>(sm_count()) * 4 + outs - 1) / outs;
+  const long long max_splits = (R + 1023) / 1024;
+  if (splits > max_splits) splits = max_splits;
+  if (splits <= 1) return 0;
+  return splits * outs;
+}
+
+extern "C" int fb_reduce(const float* x, float* out, long long outer, long long R, long long inner, int op,
+                         float* scratch, long long scratch_elems, cudaStream_t stream) {
+  if (outer <= 0 || inner <= 0) return 0;
+  if (R <= 0) return -1;
+  const long long outs = outer * inner;
+  const float final_scale = (op == FB_RED_MEAN) ? 1.f / static_cast<float>(R) : 1.f;
+  int splits = 1;
+  if (scratch != nullptr && scratch_elems >= 2 * outs) {
+    const long long want = fb_reduce_scratch_elems(outer, R, inner);
+    if (want > 0 && want <= scratch_elems) splits = static_cast<int>(want / outs);
+  }
+  const int stage_op = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
+  if (inner == 1) {
+    if (outer > 2147483647LL) return -1;
+    if (splits == 1) {
+      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), 1), 256, 0, stream>>>(x, out, R, op, final_scale, 1);
+    } else {
+      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), splits), 256, 0, stream>>>(x, scratch, R, stage_op,
+                                                                                           1.f, splits);
+      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), 1), 256, 0, stream>>>(scratch, out, splits, stage_op,
+                                                                                      final_scale, 1);
+    }
+  } else {
+    const unsigned gx = static_cast<unsigned>((outs + 255) / 256);
+    if (splits == 1) {
+      reduce_cols_kernel<<<dim3(gx, 1), 256, 0, stream>>>(x, out, outer, R, inner, op, final_scale, 1);
+    } else {
+      reduce_cols_kernel<<<dim3(gx, splits), 256, 0, stream>>>(x, scratch, outer, R, inner, stage_op, 1.f, splits);
+      reduce_cols_kernel<<<dim3(gx, 1), 256, 0, stream>>>(scratch, out, 1, splits, outs, stage_op, final_scale, 1);
+    }
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_arg_reduce(const float* x, long long* idx, float* val, long long outer, long long R,
+                             long long inner, int is_max, cudaStream_t stream) {
+  if (outer <= 0 || inner <= 0) return 0;
+  if (R <= 0) return -1;
+  if (inner == 1) {
+    arg_rows_kernel<<<static_cast<unsigned>(outer), 128, 0, stream>>>(x, idx, val, R, is_max);
+  } else {
+    const long long outs = outer * inner;
+    arg_cols_kernel<<<static_cast<unsigned>((outs + 255) / 256), 256, 0, stream>>>(x, idx, val, outer, R, inner,
+                                                                                  is_max);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_colsum(const void* x, float* out, long long rows, long long cols, int dtype, int accumulate,
+                         cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (!accumulate) {
+    cudaError_t e = cudaMemsetAsync(out, 0, cols * sizeof(float), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const long long col_blocks = (cols + 127) / 128;
+  long long row_blocks = (static_cast<long long>(sm_count()) * 4 + col_blocks - 1) / col_blocks;
+  const long long max_rb = (rows + 63) / 64;
+  if (row_blocks > max_rb) row_blocks = max_rb;
+  if (row_blocks < 1) row_blocks = 1;
+  if (row_blocks > 65535) row_blocks = 65535;
+  const long long rpb = (rows + row_blocks - 1) / row_blocks;
+  dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks));
+  if (dtype == FB_DT_F32) {
+    colsum_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), out, rows, cols, rpb);
+  } else if (dtype == FB_DT_BF16) {
+    colsum_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols,
+                                                           rpb);
+  } else {
+    return -1;
+  }
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,4 @@
+"""Model zoo (ferrum-nn/src/models.rs) and the benchmark networks."""
+from .mlp import MLP, EmbeddingClassifier, mnist_classifier, wide_mlp
+
+__all__ = ["MLP", "wide_mlp", "mnist_classifier", "EmbeddingClassifier"]

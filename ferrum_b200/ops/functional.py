@@ -1,0 +1,1030 @@
+"""Differentiable ops on ``torch.Tensor`` values.
+
+Every function here takes and returns plain torch tensors.  For CUDA tensors
+(fp32 / bf16) the forward and the backward both run this package's sm_100a
+kernels through ``torch.autograd.Function`` subclasses; for CPU tensors the
+same mathematics is expressed with torch CPU ops so that the torch autograd
+engine differentiates it.  There is no second GPU implementation: if the
+native library is missing on a GPU machine the launchers raise.
+
+Formulas follow the reference where it is sound (GELU tanh constants of
+ferrum-nn/src/activation.rs:254-262, BCE epsilon of ferrum-nn/src/loss.rs:51-71,
+mean over B*C in cross_entropy_loss, loss.rs:119-123) and are mathematically
+correct where the reference's tape is not (per-row softmax / LayerNorm,
+gradients through scalar ops, embedding backward).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch.autograd import Function
+
+from .. import _lib, config
+from ..utils import runtime as _rt
+from . import gemm as _gemm
+
+F32, BF16 = 0, 3
+
+UNARY = {
+    "none": 0, "relu": 1, "gelu": 2, "silu": 3, "tanh": 4, "sigmoid": 5, "leaky_relu": 6, "elu": 7, "neg": 8,
+    "exp": 9, "log": 10, "sqrt": 11, "abs": 12, "sin": 13, "cos": 14, "pow": 15, "add_scalar": 16,
+    "mul_scalar": 17, "rsub_scalar": 18, "rdiv_scalar": 19, "affine": 20, "clamp": 21,
+}
+_SAVES_OUTPUT = {"tanh", "sigmoid", "exp", "sqrt"}
+_SAVES_NOTHING = {"neg", "add_scalar", "mul_scalar", "rsub_scalar", "affine", "none"}
+BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4, "max": 5, "min": 6}
+REDUCE = {"sum": 0, "mean": 1, "max": 2, "min": 3, "prod": 4}
+LOSS = {"mse": 0, "bce": 1, "l1": 2, "smooth_l1": 3}
+
+GELU_C = 0.7978845608028654
+GELU_A = 0.044715
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"kernel supports fp32 / bf16, got {t.dtype}")
+
+
+def _native(t: torch.Tensor) -> bool:
+    """True when `t` is handled by this package's CUDA kernels."""
+    return t.is_cuda and t.dtype in (torch.float32, torch.bfloat16)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+# =============================================================================== raw launchers
+def raw_cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    if x.is_cuda and {x.dtype, dtype} == {torch.float32, torch.bfloat16}:
+        x = x.contiguous()
+        out = torch.empty_like(x, dtype=dtype)
+        _lib.check(_lib.cuda().fb_cast(x.data_ptr(), out.data_ptr(), x.numel(), _dt(x), _dt(out), _stream()),
+                   "fb_cast")
+        return out
+    return x.to(dtype)
+
+
+def raw_unary(x: torch.Tensor, op: str, alpha: float = 0.0, beta: float = 0.0) -> torch.Tensor:
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    _lib.check(_lib.cuda().fb_unary_fwd(x.data_ptr(), y.data_ptr(), x.numel(), UNARY[op], alpha, beta, _dt(x),
+                                        _stream()), "fb_unary_fwd")
+    return y
+
+
+def raw_unary_bwd(dy: torch.Tensor, saved, op: str, alpha: float = 0.0, beta: float = 0.0) -> torch.Tensor:
+    dy = dy.contiguous()
+    if saved is not None:
+        saved = saved.contiguous()
+        if saved.dtype != dy.dtype:
+            saved = raw_cast(saved, dy.dtype)
+    dx = torch.empty_like(dy)
+    _lib.check(_lib.cuda().fb_unary_bwd(dy.data_ptr(), _ptr(saved), dx.data_ptr(), dy.numel(), UNARY[op], alpha,
+                                        beta, _dt(dy), _stream()), "fb_unary_bwd")
+    return dx
+
+
+def raw_binary(a: torch.Tensor, b: torch.Tensor, op: str) -> torch.Tensor:
+    """Broadcasting fp32 binary op; operands may be strided / expanded views."""
+    import ctypes
+
+    shape = torch.broadcast_shapes(a.shape, b.shape)
+    if len(shape) > 6:
+        a, b = a.expand(shape).reshape(-1), b.expand(shape).reshape(-1)
+        shape = a.shape
+    ae, be = a.expand(shape), b.expand(shape)
+    out = torch.empty(shape, device=a.device, dtype=torch.float32)
+    n = len(shape)
+    LL = ctypes.c_longlong * max(n, 1)
+    _lib.check(_lib.cuda().fb_binary_fwd(ae.data_ptr(), be.data_ptr(), out.data_ptr(), BINARY[op], n,
+                                         LL(*shape) if n else LL(1), LL(*ae.stride()) if n else LL(0),
+                                         LL(*be.stride()) if n else LL(0), _stream()), "fb_binary_fwd")
+    return out
+
+
+_scratch_cache: dict = {}
+
+
+def _scratch(device, nfloats: int) -> torch.Tensor:
+    """A per-device fp32 workspace reused by reductions (grown on demand)."""
+    key = (device.type, device.index)
+    buf = _scratch_cache.get(key)
+    if buf is None or buf.numel() < nfloats:
+        buf = torch.empty(max(nfloats, 1 << 16), device=device, dtype=torch.float32)
+        _scratch_cache[key] = buf
+    return buf
+
+
+def raw_reduce(x: torch.Tensor, op: str, dim: int | None, keepdim: bool = False) -> torch.Tensor:
+    x = x.contiguous()
+    if dim is None:
+        outer, R, inner = 1, x.numel(), 1
+        oshape = [1] * x.dim() if keepdim else []
+    else:
+        shp = list(x.shape)
+        outer = math.prod(shp[:dim])
+        R = shp[dim]
+        inner = math.prod(shp[dim + 1:])
+        oshape = shp[:dim] + ([1] if keepdim else []) + shp[dim + 1:]
+    out = torch.empty(oshape, device=x.device, dtype=torch.float32)
+    if out.numel() == 0:
+        return out
+    lib = _lib.cuda()
+    want = lib.fb_reduce_scratch_elems(outer, R, inner)
+    scr = _scratch(x.device, want) if want > 0 else None
+    _lib.check(lib.fb_reduce(x.data_ptr(), out.data_ptr(), outer, R, inner, REDUCE[op], _ptr(scr),
+                             scr.numel() if scr is not None else 0, _stream()), "fb_reduce")
+    return out
+
+
+def raw_colsum(x2d: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    x2d = x2d.contiguous()
+    rows, cols = x2d.shape
+    if out is None:
+        out = torch.empty(cols, device=x2d.device, dtype=torch.float32)
+        accumulate = False
+    _lib.check(_lib.cuda().fb_colsum(x2d.data_ptr(), out.data_ptr(), rows, cols, _dt(x2d), 1 if accumulate else 0,
+                                     _stream()), "fb_colsum")
+    return out
+
+
+def _f32(x: torch.Tensor) -> torch.Tensor:
+    return raw_cast(x, torch.float32) if x.is_cuda else x.float()
+
+
+def reduce_to_shape(g: torch.Tensor, shape) -> torch.Tensor:
+    """Sum a broadcast gradient back to the operand's shape (autograd_ops.rs:589-640)."""
+    shape = tuple(shape)
+    if tuple(g.shape) == shape:
+        return g
+    if not g.is_cuda:
+        return g.sum_to_size(shape) if shape else g.sum()
+    out = _f32(g)
+    while out.dim() > len(shape):
+        out = raw_reduce(out, "sum", 0)
+    for i, s in enumerate(shape):
+        if s == 1 and out.shape[i] != 1:
+            out = raw_reduce(out, "sum", i, keepdim=True)
+    return out
+
+
+# =============================================================================== elementwise
+def _unary_cpu(x, op, a, b):
+    if op == "relu":
+        return torch.relu(x)
+    if op == "gelu":
+        return 0.5 * x * (1.0 + torch.tanh(GELU_C * (x + GELU_A * x * x * x)))
+    if op == "silu":
+        return x * torch.sigmoid(x)
+    if op == "tanh":
+        return torch.tanh(x)
+    if op == "sigmoid":
+        return torch.sigmoid(x)
+    if op == "leaky_relu":
+        return torch.where(x > 0, x, x * a)
+    if op == "elu":
+        return torch.where(x > 0, x, a * (torch.exp(x) - 1.0))
+    if op == "neg":
+        return -x
+    if op == "exp":
+        return torch.exp(x)
+    if op == "log":
+        return torch.log(x)
+    if op == "sqrt":
+        return torch.sqrt(x)
+    if op == "abs":
+        return torch.abs(x)
+    if op == "sin":
+        return torch.sin(x)
+    if op == "cos":
+        return torch.cos(x)
+    if op == "pow":
+        return torch.pow(x, a)
+    if op == "add_scalar":
+        return x + a
+    if op == "mul_scalar":
+        return x * a
+    if op == "rsub_scalar":
+        return a - x
+    if op == "rdiv_scalar":
+        return a / x
+    if op == "affine":
+        return x * a + b
+    if op == "clamp":
+        return torch.clamp(x, a, b)
+    if op == "none":
+        return x
+    raise ValueError(op)
+
+
+class _UnaryFn(Function):
+    @staticmethod
+    def forward(ctx, x, op, alpha, beta):
+        y = raw_unary(x, op, alpha, beta)
+        ctx.op, ctx.alpha, ctx.beta = op, alpha, beta
+        if op in _SAVES_NOTHING:
+            ctx.save_for_backward()
+        elif op in _SAVES_OUTPUT:
+            ctx.save_for_backward(y)
+        else:
+            ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        saved = ctx.saved_tensors[0] if ctx.saved_tensors else None
+        return raw_unary_bwd(g, saved, ctx.op, ctx.alpha, ctx.beta), None, None, None
+
+
+def unary(x: torch.Tensor, op: str, alpha: float = 0.0, beta: float = 0.0) -> torch.Tensor:
+    if _native(x):
+        return _UnaryFn.apply(x, op, float(alpha), float(beta))
+    return _unary_cpu(x, op, alpha, beta)
+
+
+_SCALAR_TO_UNARY = {"add": "add_scalar", "mul": "mul_scalar", "rsub": "rsub_scalar", "rdiv": "rdiv_scalar"}
+
+
+def scalar_op(x: torch.Tensor, op: str, s: float) -> torch.Tensor:
+    """x (op) s for op in add / sub / mul / div / pow / rsub / rdiv — differentiable (unlike tensor.rs:1551-1591)."""
+    if op == "sub":
+        op, s = "add", -s
+    elif op == "div":
+        op, s = "mul", 1.0 / s
+    if op == "pow":
+        return unary(x, "pow", s)
+    if op in ("max", "min"):
+        return unary(x, "clamp", s if op == "max" else -3.0e38, 3.0e38 if op == "max" else s)
+    return unary(x, _SCALAR_TO_UNARY[op], s)
+
+
+class _BinaryFn(Function):
+    @staticmethod
+    def forward(ctx, a, b, op):
+        af, bf = _f32(a), _f32(b)
+        out = raw_binary(af, bf, op)
+        ctx.op = op
+        ctx.dtypes = (a.dtype, b.dtype)
+        ctx.shapes = (a.shape, b.shape)
+        if op in ("add", "sub"):
+            ctx.save_for_backward()
+        elif op in ("pow",):
+            ctx.save_for_backward(af, bf, out)
+        else:
+            ctx.save_for_backward(af, bf)
+        rd = torch.promote_types(a.dtype, b.dtype)
+        return raw_cast(out, rd)
+
+    @staticmethod
+    def backward(ctx, g):
+        op = ctx.op
+        g = _f32(g.contiguous())
+        need_a, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        ga = gb = None
+        if op in ("add", "sub"):
+            if need_a:
+                ga = g
+            if need_b:
+                gb = g if op == "add" else raw_unary(g, "neg")
+        else:
+            a, b = ctx.saved_tensors[0], ctx.saved_tensors[1]
+            if op == "mul":
+                ga = raw_binary(g, b, "mul") if need_a else None
+                gb = raw_binary(g, a, "mul") if need_b else None
+            elif op == "div":
+                ga = raw_binary(g, b, "div") if need_a else None
+                if need_b:
+                    q = raw_binary(raw_binary(g, a, "mul"), raw_binary(b, b, "mul"), "div")
+                    gb = raw_unary(q, "neg")
+            elif op == "pow":
+                out = ctx.saved_tensors[2]
+                if need_a:  # b * a^(b-1) = b * out / a
+                    ga = raw_binary(g, raw_binary(raw_binary(b, out, "mul"), a, "div"), "mul")
+                if need_b:
+                    gb = raw_binary(g, raw_binary(out, raw_unary(a, "log"), "mul"), "mul")
+            else:  # max / min: gradient goes to the selected operand (ties -> a)
+                sel = (a >= b) if op == "max" else (a <= b)
+                self_mask = sel.to(torch.float32)
+                if need_a:
+                    ga = raw_binary(g, self_mask, "mul")
+                if need_b:
+                    gb = raw_binary(g, raw_unary(self_mask, "rsub_scalar", 1.0), "mul")
+        if ga is not None:
+            ga = raw_cast(reduce_to_shape(ga, ctx.shapes[0]), ctx.dtypes[0])
+        if gb is not None:
+            gb = raw_cast(reduce_to_shape(gb, ctx.shapes[1]), ctx.dtypes[1])
+        return ga, gb, None
+
+
+def _binary_cpu(a, b, op):
+    if op == "add":
+        return a + b
+    if op == "sub":
+        return a - b
+    if op == "mul":
+        return a * b
+    if op == "div":
+        return a / b
+    if op == "pow":
+        return torch.pow(a, b)
+    if op == "max":
+        return torch.maximum(a, b)
+    if op == "min":
+        return torch.minimum(a, b)
+    raise ValueError(op)
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, op: str) -> torch.Tensor:
+    if _native(a) and _native(b):
+        return _BinaryFn.apply(a, b, op)
+    return _binary_cpu(a, b, op)
+
+
+class _CastFn(Function):
+    @staticmethod
+    def forward(ctx, x, dtype):
+        ctx.src = x.dtype
+        return raw_cast(x, dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return raw_cast(g, ctx.src), None
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    if x.is_cuda and {x.dtype, dtype} == {torch.float32, torch.bfloat16}:
+        return _CastFn.apply(x, dtype)
+    return x.to(dtype)
+
+
+def cat(tensors, dim: int = 0) -> torch.Tensor:
+    """Concatenation is pure data movement (async device copies); torch provides the CatBackward split."""
+    return torch.cat(list(tensors), dim)
+
+
+# =============================================================================== reductions
+class _ReduceFn(Function):
+    @staticmethod
+    def forward(ctx, x, op, dim, keepdim):
+        xf = _f32(x)
+        y = raw_reduce(xf, op, dim, True)
+        ctx.op, ctx.dim, ctx.keepdim, ctx.src_dtype = op, dim, keepdim, x.dtype
+        ctx.xshape = x.shape
+        if op in ("max", "min", "prod"):
+            ctx.save_for_backward(xf, y)
+        else:
+            ctx.save_for_backward()
+        out = y if keepdim else (y.reshape(()) if dim is None else y.squeeze(dim))
+        return raw_cast(out, x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        op, dim = ctx.op, ctx.dim
+        g = _f32(g)
+        kshape = [1] * len(ctx.xshape) if dim is None else [
+            1 if i == dim else s for i, s in enumerate(ctx.xshape)]
+        gk = g.reshape(kshape)
+        if op == "sum":
+            gx = gk.expand(ctx.xshape)
+        elif op == "mean":
+            R = math.prod(ctx.xshape) if dim is None else ctx.xshape[dim]
+            gx = raw_unary(gk, "mul_scalar", 1.0 / max(R, 1)).expand(ctx.xshape)
+        elif op in ("max", "min"):
+            x, y = ctx.saved_tensors
+            mask = (x == y).to(torch.float32)
+            gx = raw_binary(gk, mask, "mul")
+        else:  # prod: d/dx_i = prod / x_i
+            x, y = ctx.saved_tensors
+            gx = raw_binary(raw_binary(gk, y, "mul"), x, "div")
+        if gx.dtype != ctx.src_dtype:
+            gx = raw_cast(gx.contiguous(), ctx.src_dtype)
+        return gx, None, None, None
+
+
+def reduce(x: torch.Tensor, op: str, dim: int | None = None, keepdim: bool = False) -> torch.Tensor:
+    if _native(x) and x.numel() > 0:
+        return _ReduceFn.apply(x, op, dim, keepdim)
+    if dim is None:
+        fn = {"sum": torch.sum, "mean": torch.mean, "max": torch.max, "min": torch.min, "prod": torch.prod}[op]
+        out = fn(x)
+        return out.reshape([1] * x.dim()) if keepdim else out
+    if op in ("max", "min"):
+        return getattr(torch, op)(x, dim=dim, keepdim=keepdim).values
+    return getattr(torch, op)(x, dim=dim, keepdim=keepdim)
+
+
+def arg_reduce(x: torch.Tensor, is_max: bool, dim: int | None = None, keepdim: bool = False) -> torch.Tensor:
+    """Index of the first maximum / minimum (tensor.rs:1838-2036)."""
+    if _native(x) and x.numel() > 0:
+        xf = _f32(x).contiguous()
+        if dim is None:
+            outer, R, inner, oshape = 1, xf.numel(), 1, []
+        else:
+            shp = list(xf.shape)
+            outer, R, inner = math.prod(shp[:dim]), shp[dim], math.prod(shp[dim + 1:])
+            oshape = shp[:dim] + ([1] if keepdim else []) + shp[dim + 1:]
+        idx = torch.empty(oshape, device=x.device, dtype=torch.int64)
+        _lib.check(_lib.cuda().fb_arg_reduce(xf.data_ptr(), idx.data_ptr(), None, outer, R, inner,
+                                             1 if is_max else 0, _stream()), "fb_arg_reduce")
+        return idx
+    fn = torch.argmax if is_max else torch.argmin
+    return fn(x) if dim is None else fn(x, dim=dim, keepdim=keepdim)
+
+
+# =============================================================================== GEMM-shaped ops
+def _gemm_nt(a: torch.Tensor, b_nt: torch.Tensor, bias=None, act=None, low: bool = False, out=None,
+             out_dtype=None, accumulate=False) -> torch.Tensor:
+    """out = act(a @ b_nt^T + bias) with a [M,K], b_nt [N,K] (any strides)."""
+    if low:
+        ab = a if a.dtype == torch.bfloat16 else raw_cast(a.contiguous(), torch.bfloat16)
+        bb = b_nt if b_nt.dtype == torch.bfloat16 else raw_cast(b_nt.contiguous(), torch.bfloat16)
+        if not _gemm.bf16_operand_ok(ab):
+            ab = ab.contiguous()
+        if not _gemm.bf16_operand_ok(bb):
+            bb = bb.contiguous()
+        if _gemm.bf16_operand_ok(ab) and _gemm.bf16_operand_ok(bb):
+            return _gemm.gemm_bf16(ab, bb, bias=bias, act=act, out=out,
+                                   out_dtype=out_dtype or torch.bfloat16, accumulate=accumulate)
+        # row pitch not a multiple of 16 bytes: exact SIMT kernel on fp32 copies
+        res = _gemm.gemm_f32(_f32(ab), _f32(bb), bias=bias, act=act, out=out if out is not None and
+                             out.dtype == torch.float32 else None, accumulate=accumulate and out is not None)
+        if out is not None and out.dtype != torch.float32:
+            out.copy_(res)
+            return out
+        return raw_cast(res, out_dtype or torch.bfloat16)
+    res = _gemm.gemm_f32(_f32(a), _f32(b_nt), bias=bias, act=act, out=out, accumulate=accumulate)
+    return res
+
+
+class _MatmulFn(Function):
+    @staticmethod
+    def forward(ctx, a, b, low):
+        ctx.low = low
+        ctx.dtypes = (a.dtype, b.dtype)
+        if low:
+            a = raw_cast(a.contiguous(), torch.bfloat16)
+            b = raw_cast(b.contiguous(), torch.bfloat16)
+        ctx.save_for_backward(a, b)
+        out = _gemm_nt(a, b.t(), low=low)
+        return out if low else raw_cast(out, torch.promote_types(*ctx.dtypes))
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        low = ctx.low
+        g = g.contiguous()
+        if low and g.dtype != torch.bfloat16:
+            g = raw_cast(g, torch.bfloat16)
+        ga = gb = None
+        if ctx.needs_input_grad[0]:
+            ga = raw_cast(_gemm_nt(g, b, low=low), ctx.dtypes[0])
+        if ctx.needs_input_grad[1]:
+            gb = raw_cast(_gemm_nt(a.t(), g.t(), low=low, out_dtype=torch.float32), ctx.dtypes[1])
+        return ga, gb, None
+
+
+class _BmmFn(Function):
+    """Batched fp32 matmul on the SIMT kernel (grid.z = batch)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return _gemm.gemm_f32(a, b.transpose(1, 2))
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        g = g.contiguous()
+        ga = _gemm.gemm_f32(g, b) if ctx.needs_input_grad[0] else None
+        gb = _gemm.gemm_f32(a.transpose(1, 2), g.transpose(1, 2)) if ctx.needs_input_grad[1] else None
+        return ga, gb
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """2D@2D, 2D@1D, 1D@2D (tensor.rs:2433-2485) and batched ND@ND / ND@2D."""
+    if not (_native(a) and _native(b)):
+        return torch.matmul(a, b)
+    low = config.low_precision_active()
+    if a.dim() == 1 and b.dim() == 1:
+        return reduce(binary(a, b, "mul"), "sum")
+    if a.dim() == 1:
+        return matmul(a.unsqueeze(0), b).squeeze(-2)
+    if b.dim() == 1:
+        return matmul(a, b.unsqueeze(1)).squeeze(-1)
+    if a.dim() == 2 and b.dim() == 2:
+        return _MatmulFn.apply(a, b, low)
+    if b.dim() == 2:  # [..., M, K] @ [K, N]
+        lead = a.shape[:-1]
+        return _MatmulFn.apply(a.reshape(-1, a.shape[-1]), b, low).reshape(*lead, b.shape[1])
+    # batched: broadcast batch dims, run the fp32 batched kernel
+    bs = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    a3 = _f32(a.expand(*bs, *a.shape[-2:]).reshape(-1, *a.shape[-2:]).contiguous())
+    b3 = _f32(b.expand(*bs, *b.shape[-2:]).reshape(-1, *b.shape[-2:]).contiguous())
+    out = _BmmFn.apply(a3, b3)
+    return raw_cast(out.reshape(*bs, a.shape[-2], b.shape[-1]), torch.promote_types(a.dtype, b.dtype))
+
+
+class GradSink:
+    """Where a Linear's weight gradient is written.
+
+    ``acquire(param)`` returns ``(buffer, accumulate)``: an fp32 tensor shaped like
+    the parameter and whether the wgrad GEMM must add to its contents; ``ready(param)``
+    is called once the gradient is enqueued on the current stream.  The DDP engine
+    implements this to have wgrad written straight into its flat gradient arena.
+    """
+
+    def acquire(self, param):  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def ready(self, param):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class _LinearFn(Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, act, low, w_low, sink):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.low, ctx.act, ctx.sink = low, act, sink
+        ctx.x_dtype, ctx.lead = x.dtype, lead
+        ctx.has_bias = bias is not None
+        ctx.weight_ref = weight
+        if low:
+            xb = x2 if x2.dtype == torch.bfloat16 else raw_cast(x2.contiguous(), torch.bfloat16)
+            wb = w_low if w_low is not None else raw_cast(weight.detach().contiguous(), torch.bfloat16)
+            y = _gemm_nt(xb, wb, bias=bias, act=act, low=True)
+            saved_x, saved_w = xb, wb
+        else:
+            xf = _f32(x2)
+            y = _gemm_nt(xf, weight.detach(), bias=bias, act=act, low=False)
+            saved_x, saved_w = xf, weight.detach()
+        if act is None:
+            ctx.save_for_backward(saved_x, saved_w)
+        else:
+            ctx.save_for_backward(saved_x, saved_w, y)
+        return y.reshape(*lead, weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, g):
+        low, act = ctx.low, ctx.act
+        saved = ctx.saved_tensors
+        x2, w = saved[0], saved[1]
+        g2 = g.reshape(-1, g.shape[-1]).contiguous()
+        if low and g2.dtype != torch.bfloat16:
+            g2 = raw_cast(g2, torch.bfloat16)
+        if not low:
+            g2 = _f32(g2)
+        if act is not None:
+            # only activations whose derivative is a function of the output are fused here
+            g2 = raw_unary_bwd(g2, saved[2], act)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:  # dgrad first: the weight may be overwritten once its bucket is reduced
+            gx = _gemm_nt(g2, w.t(), low=low)
+            gx = raw_cast(gx, ctx.x_dtype).reshape(*ctx.lead, w.shape[1])
+        if ctx.needs_input_grad[1]:
+            sink = ctx.sink
+            if sink is not None:
+                buf, acc = sink.acquire(ctx.weight_ref)
+                _gemm_nt(g2.t(), x2.t(), low=low, out=buf, out_dtype=torch.float32, accumulate=acc)
+            else:
+                gw = _gemm_nt(g2.t(), x2.t(), low=low, out_dtype=torch.float32)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = raw_colsum(g2)
+        if ctx.needs_input_grad[1] and ctx.sink is not None:
+            ctx.sink.ready(ctx.weight_ref)
+        return gx, gw, gb, None, None, None, None
+
+
+_FUSABLE_ACT = {"relu", "tanh", "sigmoid"}  # derivative expressible from the output
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+           w_low: torch.Tensor | None = None, sink: GradSink | None = None) -> torch.Tensor:
+    """``act(x @ weight^T + bias)`` with weight ``[out, in]`` (ferrum-nn/src/linear.rs:78-89).
+
+    On CUDA the bias (and relu/tanh/sigmoid) run in the GEMM epilogue.  ``w_low`` is an
+    up-to-date bf16 copy of ``weight`` (kept by the optimizer) used under bf16 precision.
+    """
+    if not _native(x):
+        y = torch.nn.functional.linear(x, weight, bias)
+        return _unary_cpu(y, act, 0.0, 0.0) if act else y
+    low = config.low_precision_active()
+    needs_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+    if act is not None and act not in _FUSABLE_ACT and needs_grad:
+        y = _LinearFn.apply(x, weight, bias, None, low, w_low, sink)
+        return unary(y, act)
+    return _LinearFn.apply(x, weight, bias, act, low, w_low, sink)
+
+
+# =============================================================================== normalisation
+class _LayerNormFn(Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, pre_act, want_colsum):
+        cols = x.shape[-1]
+        x2 = x.reshape(-1, cols).contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        g = gamma.detach().contiguous() if gamma is not None else None
+        b = beta.detach().contiguous() if beta is not None else None
+        _lib.check(_lib.cuda().fb_layernorm_fwd(x2.data_ptr(), _ptr(g), _ptr(b), y.data_ptr(), mean.data_ptr(),
+                                                rstd.data_ptr(), rows, cols, eps, UNARY[pre_act or "none"],
+                                                _dt(x2), _stream()), "fb_layernorm_fwd")
+        ctx.save_for_backward(x2, g, mean, rstd)
+        ctx.pre_act, ctx.shape, ctx.want_colsum = pre_act, x.shape, want_colsum
+        ctx.has_gamma, ctx.has_beta = gamma is not None, beta is not None
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, g, mean, rstd = ctx.saved_tensors
+        rows, cols = x2.shape
+        gy2 = gy.reshape(rows, cols).contiguous()
+        if gy2.dtype != x2.dtype:
+            gy2 = raw_cast(gy2, x2.dtype)
+        lib = _lib.cuda()
+        dx = torch.empty_like(x2)
+        nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
+        partial = torch.empty((max(nblk, 1), 3, cols), device=x2.device, dtype=torch.float32)
+        dgamma = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.has_gamma else None
+        dbeta = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.has_beta else None
+        dcol = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.want_colsum else None
+        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), x2.data_ptr(), _ptr(g), mean.data_ptr(), rstd.data_ptr(),
+                                        dx.data_ptr(), partial.data_ptr(), _ptr(dgamma), _ptr(dbeta), _ptr(dcol),
+                                        rows, cols, UNARY[ctx.pre_act or "none"], _dt(x2), nblk, _stream()),
+                   "fb_layernorm_bwd")
+        ctx.colsum = dcol
+        return dx.reshape(ctx.shape), dgamma, dbeta, None, None, None
+
+
+def layer_norm(x: torch.Tensor, gamma=None, beta=None, eps: float = 1e-5, pre_act: str | None = None,
+               n_norm_dims: int = 1) -> torch.Tensor:
+    """Normalise over the last ``n_norm_dims`` dimensions; optional fused GELU before the statistics."""
+    if n_norm_dims != 1:
+        lead = x.shape[:-n_norm_dims]
+        flat = x.reshape(*lead, -1)
+        g = gamma.reshape(-1) if gamma is not None else None
+        b = beta.reshape(-1) if beta is not None else None
+        return layer_norm(flat, g, b, eps, pre_act, 1).reshape(x.shape)
+    if _native(x):
+        return _LayerNormFn.apply(x, gamma, beta, float(eps), pre_act, False)
+    a = _unary_cpu(x, pre_act, 0.0, 0.0) if pre_act else x
+    mu = a.mean(-1, keepdim=True)
+    var = ((a - mu) ** 2).mean(-1, keepdim=True)
+    y = (a - mu) / torch.sqrt(var + eps)
+    if gamma is not None:
+        y = y * gamma
+    if beta is not None:
+        y = y + beta
+    return y
+
+
+class _BatchNormFn(Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, running_mean, running_var, eps, momentum, training):
+        x2 = _f32(x).contiguous()
+        rows, cols = x2.shape
+        y = torch.empty_like(x2)
+        sm = torch.empty(cols, device=x.device, dtype=torch.float32)
+        sr = torch.empty(cols, device=x.device, dtype=torch.float32)
+        g = gamma.detach().contiguous() if gamma is not None else None
+        b = beta.detach().contiguous() if beta is not None else None
+        _lib.check(_lib.cuda().fb_batchnorm_fwd(x2.data_ptr(), _ptr(g), _ptr(b), y.data_ptr(), sm.data_ptr(),
+                                                sr.data_ptr(), _ptr(running_mean), _ptr(running_var), rows, cols,
+                                                eps, momentum, 1 if training else 0, _stream()),
+                   "fb_batchnorm_fwd")
+        if not training:
+            sm = running_mean.detach().clone()
+            sr = torch.rsqrt(running_var.detach() + eps)
+        ctx.save_for_backward(x2, g, sm, sr)
+        ctx.training = training
+        ctx.flags = (gamma is not None, beta is not None)
+        ctx.src_dtype = x.dtype
+        return raw_cast(y, x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, g, sm, sr = ctx.saved_tensors
+        rows, cols = x2.shape
+        gy2 = _f32(gy).contiguous()
+        if ctx.training:
+            dx = torch.empty_like(x2)
+            dgamma = torch.empty(cols, device=x2.device, dtype=torch.float32)
+            dbeta = torch.empty(cols, device=x2.device, dtype=torch.float32)
+            _lib.check(_lib.cuda().fb_batchnorm_bwd(gy2.data_ptr(), x2.data_ptr(), _ptr(g), sm.data_ptr(),
+                                                    sr.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
+                                                    dbeta.data_ptr(), rows, cols, _stream()), "fb_batchnorm_bwd")
+        else:  # statistics are constants in eval mode
+            scale = sr if g is None else raw_binary(sr, g, "mul")
+            dx = raw_binary(gy2, scale, "mul")
+            xhat = raw_binary(raw_binary(x2, sm, "sub"), sr, "mul")
+            dgamma = raw_reduce(raw_binary(gy2, xhat, "mul"), "sum", 0)
+            dbeta = raw_reduce(gy2, "sum", 0)
+        return (raw_cast(dx, ctx.src_dtype), dgamma if ctx.flags[0] else None, dbeta if ctx.flags[1] else None,
+                None, None, None, None, None)
+
+
+def batch_norm(x: torch.Tensor, gamma, beta, running_mean, running_var, training: bool, momentum: float = 0.1,
+               eps: float = 1e-5) -> torch.Tensor:
+    """Per-feature batch normalisation of ``[B, F]`` input with running-stat update."""
+    if x.dim() != 2:
+        raise ValueError("batch_norm expects [batch, features]")
+    if _native(x):
+        return _BatchNormFn.apply(x, gamma, beta, running_mean, running_var, float(eps), float(momentum),
+                                  bool(training))
+    if training:
+        mu = x.mean(0)
+        var = ((x - mu) ** 2).mean(0)
+        if running_mean is not None:
+            with torch.no_grad():
+                n = x.shape[0]
+                running_mean.mul_(1 - momentum).add_(momentum * mu.detach())
+                running_var.mul_(1 - momentum).add_(momentum * var.detach() * (n / (n - 1) if n > 1 else 1.0))
+    else:
+        mu, var = running_mean, running_var
+    y = (x - mu) / torch.sqrt(var + eps)
+    if gamma is not None:
+        y = y * gamma
+    if beta is not None:
+        y = y + beta
+    return y
+
+
+# =============================================================================== softmax / losses
+class _SoftmaxFn(Function):
+    @staticmethod
+    def forward(ctx, x, log_mode):
+        cols = x.shape[-1]
+        x2 = x.reshape(-1, cols).contiguous()
+        y = torch.empty_like(x2)
+        _lib.check(_lib.cuda().fb_softmax_fwd(x2.data_ptr(), y.data_ptr(), x2.shape[0], cols, 1 if log_mode else 0,
+                                              _dt(x2), _stream()), "fb_softmax_fwd")
+        ctx.save_for_backward(y)
+        ctx.log_mode, ctx.shape = log_mode, x.shape
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        rows, cols = y.shape
+        g2 = g.reshape(rows, cols).contiguous()
+        if g2.dtype != y.dtype:
+            g2 = raw_cast(g2, y.dtype)
+        dx = torch.empty_like(y)
+        _lib.check(_lib.cuda().fb_softmax_bwd(g2.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols,
+                                              1 if ctx.log_mode else 0, _dt(y), _stream()), "fb_softmax_bwd")
+        return dx.reshape(ctx.shape), None
+
+
+def _softmax_any_dim(x, dim, log_mode):
+    nd = x.dim()
+    if nd == 0:
+        x = x.reshape(1)
+        nd, dim = 1, 0
+    d = dim + nd if dim < 0 else dim
+    if _native(x):
+        if d != nd - 1:
+            return _SoftmaxFn.apply(x.transpose(d, -1), log_mode).transpose(d, -1)
+        return _SoftmaxFn.apply(x, log_mode)
+    return torch.log_softmax(x, d) if log_mode else torch.softmax(x, d)
+
+
+def softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """Numerically stable softmax along ``dim`` (per-row spec of ferrum-cuda/src/kernels.rs:501-560)."""
+    return _softmax_any_dim(x, dim, False)
+
+
+def log_softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    return _softmax_any_dim(x, dim, True)
+
+
+class _CEFn(Function):
+    """Fused log-softmax + NLL over integer labels: one kernel yields loss rows and the logit gradient."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, scale):
+        rows, cols = logits.shape
+        lg = logits.contiguous()
+        row_loss = torch.empty(rows, device=lg.device, dtype=torch.float32)
+        need_grad = ctx.needs_input_grad[0]
+        dl = torch.empty_like(lg) if need_grad else None
+        _lib.check(_lib.cuda().fb_ce_fwd_bwd(lg.data_ptr(), labels.data_ptr(), row_loss.data_ptr(), _ptr(dl), rows,
+                                             cols, scale, _dt(lg), _dt(lg), _stream()), "fb_ce_fwd_bwd")
+        if need_grad:
+            ctx.save_for_backward(dl)
+        loss = raw_reduce(row_loss, "sum", None)
+        return raw_unary(loss, "mul_scalar", scale)
+
+    @staticmethod
+    def backward(ctx, g):
+        (dl,) = ctx.saved_tensors
+        # dl already carries the 1/rows factor; scale by the incoming scalar gradient
+        gf = _f32(g).reshape(1)
+        if dl.dtype == torch.float32:
+            out = raw_binary(dl, gf, "mul")
+        else:
+            out = raw_cast(raw_binary(_f32(dl), gf, "mul"), dl.dtype)
+        return out, None, None
+
+
+def cross_entropy_logits(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Mean over the batch of ``-log softmax(logits)[label]`` for integer ``labels`` (fused kernel on CUDA)."""
+    if logits.dim() != 2:
+        logits = logits.reshape(-1, logits.shape[-1])
+        labels = labels.reshape(-1)
+    labels = labels.to(torch.int64)
+    if _native(logits):
+        x = logits
+        if not torch.is_grad_enabled():
+            x = logits.detach()
+        return _CEFn.apply(x, labels.contiguous(), 1.0 / logits.shape[0])
+    lp = torch.log_softmax(logits.float(), -1)
+    return -lp.gather(1, labels.unsqueeze(1)).mean()
+
+
+class _ElemLossFn(Function):
+    @staticmethod
+    def forward(ctx, pred, target, kind):
+        p, t = _f32(pred).contiguous(), _f32(target).contiguous()
+        out = torch.zeros((), device=p.device, dtype=torch.float32)
+        n = p.numel()
+        _lib.check(_lib.cuda().fb_loss_fwd(p.data_ptr(), t.data_ptr(), out.data_ptr(), n, LOSS[kind], 1.0 / n,
+                                           _stream()), "fb_loss_fwd")
+        ctx.save_for_backward(p, t)
+        ctx.kind, ctx.shape, ctx.dtype = kind, pred.shape, pred.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        p, t = ctx.saved_tensors
+        gf = _f32(g).contiguous()
+        dp = torch.empty_like(p)
+        n = p.numel()
+        _lib.check(_lib.cuda().fb_loss_bwd(p.data_ptr(), t.data_ptr(), gf.data_ptr(), dp.data_ptr(), n,
+                                           LOSS[ctx.kind], 1.0 / n, _stream()), "fb_loss_bwd")
+        return raw_cast(dp.reshape(ctx.shape), ctx.dtype), None, None
+
+
+def elementwise_loss(pred: torch.Tensor, target: torch.Tensor, kind: str) -> torch.Tensor:
+    """mse / bce / l1 / smooth_l1, mean over all elements (ferrum-nn/src/loss.rs:24-105)."""
+    if tuple(pred.shape) != tuple(target.shape):
+        target = target.expand_as(pred)
+    if _native(pred) and pred.numel() > 0:
+        return _ElemLossFn.apply(pred, target.detach(), kind)
+    d = pred - target
+    if kind == "mse":
+        return (d * d).mean()
+    if kind == "bce":
+        eps = 1e-7
+        pc = pred + eps
+        q = (1.0 + eps) - pc
+        return -(target * torch.log(pc) + (1.0 - target) * torch.log(q)).mean()
+    if kind == "l1":
+        return d.abs().mean()
+    a = d.abs()
+    return torch.where(a < 1.0, 0.5 * d * d, a - 0.5).mean()
+
+
+# =============================================================================== dropout / embedding / gather
+_dropout_offset = 0
+
+
+class _DropoutFn(Function):
+    @staticmethod
+    def forward(ctx, x, p, seed, offset):
+        x2 = x.contiguous()
+        y = torch.empty_like(x2)
+        mask = torch.empty(x2.shape, device=x.device, dtype=torch.uint8)
+        _lib.check(_lib.cuda().fb_dropout_fwd(x2.data_ptr(), y.data_ptr(), mask.data_ptr(), x2.numel(), p, seed,
+                                              offset, _dt(x2), _stream()), "fb_dropout_fwd")
+        ctx.save_for_backward(mask)
+        ctx.p = p
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (mask,) = ctx.saved_tensors
+        g2 = g.contiguous()
+        dx = torch.empty_like(g2)
+        _lib.check(_lib.cuda().fb_dropout_bwd(g2.data_ptr(), mask.data_ptr(), dx.data_ptr(), g2.numel(), ctx.p,
+                                              _dt(g2), _stream()), "fb_dropout_bwd")
+        return dx, None, None, None
+
+
+def dropout(x: torch.Tensor, p: float, training: bool, seed: int | None = None) -> torch.Tensor:
+    """Inverted dropout: keep with probability 1-p and scale by 1/(1-p) while training; identity otherwise."""
+    global _dropout_offset
+    if not training or p <= 0.0:
+        return x
+    if p >= 1.0:
+        return x * 0.0
+    if _native(x):
+        if seed is None:
+            seed = torch.initial_seed()
+        _dropout_offset += 1
+        return _DropoutFn.apply(x, float(p), int(seed) & 0xFFFFFFFFFFFFFFFF, _dropout_offset)
+    return torch.nn.functional.dropout(x, p, True)
+
+
+def _sorted_indices(idx_flat: torch.Tensor):
+    """(sorted indices, original positions): a radix sort of the looked-up ids."""
+    return torch.sort(idx_flat, stable=True)
+
+
+class _EmbeddingFn(Function):
+    @staticmethod
+    def forward(ctx, weight, idx, padding_idx, out_dtype, pool):
+        w = weight.detach().contiguous()
+        V, D = w.shape
+        idx_c = idx.contiguous()
+        lib = _lib.cuda()
+        if pool:
+            B, S = idx_c.shape
+            out = torch.empty((B, D), device=w.device, dtype=out_dtype)
+            _lib.check(lib.fb_embedding_meanpool_fwd(w.data_ptr(), idx_c.data_ptr(), out.data_ptr(), B, S, D, V,
+                                                     F32 if out_dtype == torch.float32 else BF16, _stream()),
+                       "fb_embedding_meanpool_fwd")
+            ctx.group = S
+        else:
+            out = torch.empty((*idx_c.shape, D), device=w.device, dtype=out_dtype)
+            _lib.check(lib.fb_embedding_fwd(w.data_ptr(), idx_c.data_ptr(), out.data_ptr(), idx_c.numel(), D, V,
+                                            -1 if padding_idx is None else padding_idx,
+                                            F32 if out_dtype == torch.float32 else BF16, _rt.status_ptr(),
+                                            _stream()), "fb_embedding_fwd")
+            ctx.group = 1
+        ctx.save_for_backward(idx_c)
+        ctx.wshape, ctx.padding_idx, ctx.pool = (V, D), padding_idx, pool
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        V, D = ctx.wshape
+        g2 = g.reshape(-1, D).contiguous()
+        flat = idx.reshape(-1)
+        sidx, perm = _sorted_indices(flat)
+        dw = torch.zeros((V, D), device=g.device, dtype=torch.float32)
+        scale = 1.0 / ctx.group if ctx.pool else 1.0
+        _lib.check(_lib.cuda().fb_embedding_bwd_sorted(g2.data_ptr(), sidx.data_ptr(), perm.data_ptr(),
+                                                       dw.data_ptr(), flat.numel(), D, ctx.group, scale,
+                                                       -1 if ctx.padding_idx is None else ctx.padding_idx,
+                                                       _dt(g2), _stream()), "fb_embedding_bwd_sorted")
+        return dw, None, None, None, None
+
+
+def embedding(weight: torch.Tensor, idx: torch.Tensor, padding_idx: int | None = None,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Row gather ``weight[idx]`` -> ``[*idx.shape, D]``; rows at ``padding_idx`` are zero (embedding.rs:122-208)."""
+    idx = idx.to(torch.int64)
+    if weight.is_cuda and weight.dtype == torch.float32:
+        return _EmbeddingFn.apply(weight, idx, padding_idx, out_dtype or torch.float32, False)
+    out = torch.nn.functional.embedding(idx, weight)
+    if padding_idx is not None:
+        out = out * (idx != padding_idx).unsqueeze(-1).to(out.dtype)
+    return out
+
+
+def embedding_mean_pool(weight: torch.Tensor, idx: torch.Tensor, out_dtype: torch.dtype | None = None):
+    """``mean_s weight[idx[b, s]]`` for ``idx [B, S]`` without materialising ``[B, S, D]``."""
+    idx = idx.to(torch.int64)
+    if weight.is_cuda and weight.dtype == torch.float32 and idx.dim() == 2 and idx.shape[1] * 8 <= 48 * 1024:
+        return _EmbeddingFn.apply(weight, idx, None, out_dtype or torch.float32, True)
+    return torch.nn.functional.embedding(idx, weight).mean(1)
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """``src[idx]`` along dim 0 for a contiguous device-resident tensor (DataLoader collate)."""
+    if not src.is_cuda:
+        return src.index_select(0, idx.to(torch.int64))
+    src = src.contiguous()
+    idx = idx.to(device=src.device, dtype=torch.int64).contiguous()
+    out = torch.empty((idx.numel(), *src.shape[1:]), device=src.device, dtype=src.dtype)
+    row_bytes = src[0].numel() * src.element_size() if src.shape[0] else 0
+    _lib.check(_lib.cuda().fb_gather_rows(src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), row_bytes,
+                                          _stream()), "fb_gather_rows")
+    return out
+
+
+def transpose_2d(x: torch.Tensor) -> torch.Tensor:
+    """Materialised transpose of a 2-D tensor (ferrum-cuda/src/kernels.rs:442-494)."""
+    if not (x.is_cuda and x.element_size() in (2, 4)):
+        return x.t().contiguous()
+    x = x.contiguous()
+    out = torch.empty((x.shape[1], x.shape[0]), device=x.device, dtype=x.dtype)
+    _lib.check(_lib.cuda().fb_transpose_2d(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], x.element_size(),
+                                           _stream()), "fb_transpose_2d")
+    return out
