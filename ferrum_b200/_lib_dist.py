@@ -1,4 +1,47 @@
 """ctypes signatures of the inter-GPU entry points (csrc/dist)."""
-from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p, POINTER
+import ctypes
+from ctypes import POINTER, c_float, c_int, c_int32, c_longlong, c_uint, c_ulonglong, c_void_p
 
-SIGS = {}
+MAX_RANKS = 8
+
+
+class DistCtx(ctypes.Structure):
+    """Mirror of ``fb_dist_ctx`` (csrc/dist/dist_ctx.h)."""
+
+    _fields_ = [("rank", c_int), ("world", c_int), ("arena", c_void_p * MAX_RANKS), ("mc_arena", c_void_p),
+                ("status", c_void_p), ("timeout_ns", c_ulonglong)]
+
+
+def _sigs():
+    from ._lib import AdamH, SgdH
+
+    P, LL, I, F, U = c_void_p, c_longlong, c_int, c_float, c_uint
+    return {
+        "fb_symm_alloc": (P, [c_ulonglong]),
+        "fb_symm_free": (I, [P]),
+        "fb_symm_handle_bytes": (I, []),
+        "fb_symm_export": (I, [P, P]),
+        "fb_symm_import": (P, [P, POINTER(c_int)]),
+        "fb_symm_close": (I, [P]),
+        "fb_symm_enable_peer": (I, [I]),
+        "fb_dist_query_flag_bytes": (I, []),
+        "fb_dist_query_max_blocks": (I, []),
+        "fb_dist_query_channels": (I, []),
+        "fb_dist_allreduce": (I, [POINTER(DistCtx), I, I, I, U, LL, LL, LL, LL, I, F, POINTER(AdamH), POINTER(SgdH),
+                                  P, P, I, I, P]),
+        "fb_dist_allreduce_emulated": (I, [POINTER(DistCtx), I, I, I, U, LL, LL, LL, LL, I, F, POINTER(AdamH),
+                                           POINTER(SgdH), POINTER(c_void_p), POINTER(c_void_p), I, I, P]),
+        "fb_dist_collective": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, LL, I, F, I, P]),
+        "fb_dist_collective_emulated": (I, [POINTER(DistCtx), I, I, I, U, I, LL, LL, LL, I, F, I, P]),
+        "fb_dist_barrier": (I, [POINTER(DistCtx), I, U, P]),
+    }
+
+
+class _Lazy(dict):
+    def items(self):
+        if not self:
+            self.update(_sigs())
+        return super().items()
+
+
+SIGS = _Lazy()

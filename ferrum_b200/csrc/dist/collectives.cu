@@ -1,0 +1,445 @@
+// Inter-GPU kernels over NVLink 5 / NVSwitch.  Every rank owns a "symmetric
+// arena" (same layout on every GPU, mapped into every peer's address space) and
+// the kernels move data with plain peer loads / stores issued from inside the
+// kernel, or with multimem.ld_reduce / multimem.st through the NVSwitch multicast
+// alias when one is set up.  No library collective is called and no TMA multicast
+// is used anywhere.
+//
+//   fused all-reduce (+ 1/world scale) (+ SGD-momentum | Adam update + parameter
+//   publish)              -> fb_dist_allreduce          (gradient buckets of DDP)
+//   broadcast / all-gather / gather / scatter / reduce-scatter / reduce
+//                          -> fb_dist_collective
+//   barrier                -> fb_dist_barrier
+//
+// The reference declares these operations and implements them as no-ops
+// (ferrum-distributed/src/collectives.rs:74-129; ddp.rs:96-111 loops over them).
+//
+// Algorithm of the fused all-reduce (two-shot, shard-owner update): rank r owns the
+// r-th shard of the bucket.  After an entry handshake it sums that shard over all
+// ranks (reads of the peers' gradient arenas), applies the scale and the optimizer
+// rule to its fp32 master copy and the moments it alone keeps for the shard, and
+// stores the new fp32 parameters and their bf16 copy into EVERY rank's arena.  An
+// exit handshake tells each rank that all shards have arrived and that nobody still
+// reads its gradients.  Per element the link carries one gradient read and one
+// parameter write per peer — the cost of an all-reduce — and the separate optimizer
+// pass over memory disappears.
+//
+// Handshakes are per (channel, block): block b of every rank writes an epoch into
+// slot [channel][b][its rank] of every peer's flag region and waits until its own
+// region shows that epoch from every peer.  Waits are bounded by ctx.timeout_ns;
+// on expiry the block records {peer, epoch} in the status block, the kernel skips
+// the rest of its work and returns.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../common/ptx.cuh"
+#include "../common/status.h"
+#include "../include/ferrum_kernels.h"
+#include "dist_ctx.h"
+
+namespace fb {
+namespace {
+
+__device__ __forceinline__ uint32_t* flag_slot(unsigned char* arena, int channel, int block, int src) {
+  return reinterpret_cast<uint32_t*>(arena) + ((channel * FB_FLAG_BLOCKS + block) * FB_MAX_RANKS + src);
+}
+
+// Called by every thread of the block.  Returns false (for the whole block) if a wait gave up.
+__device__ bool block_handshake(const fb_dist_ctx& c, int channel, int vblock, uint32_t epoch, int* s_fail,
+                                int site) {
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    ptx::st_release_sys(flag_slot(c.arena[peer], channel, vblock, c.rank), epoch);
+    const uint32_t* mine = flag_slot(c.arena[c.rank], channel, vblock, peer);
+    const uint64_t t0 = ptx::globaltimer();
+    uint32_t it = 0;
+    while (static_cast<int32_t>(ptx::ld_acquire_sys(mine) - epoch) < 0) {
+      if (((++it) & 31u) == 0u) {
+        if (*reinterpret_cast<volatile int*>(s_fail)) break;
+        if (ptx::globaltimer() - t0 > c.timeout_ns) {
+          report_status(c.status, kStatusPeerTimeout, site, peer, static_cast<int32_t>(epoch));
+          *reinterpret_cast<volatile int*>(s_fail) = 1;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return *reinterpret_cast<volatile int*>(s_fail) == 0;
+}
+
+struct ArArgs {
+  int channel;
+  uint32_t epoch;
+  long long grad_off;    // byte offsets into the arena
+  long long param_off;   // fp32 master parameters (fused modes)
+  long long shadow_off;  // bf16 copy of the parameters (fused modes; <0 = none)
+  long long n;           // bucket length in elements (multiple of 4)
+  int op;
+  float scale;
+  fb_adam_hparams adam;
+  fb_sgd_hparams sgd;
+  float* m;  // this rank's moment / velocity storage for ITS shard (index 0 = first element of the shard)
+  float* v;
+};
+
+__device__ __forceinline__ float4 combine4(float4 a, float4 b, int op) {
+  switch (op) {
+    case FB_OP_PROD: return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+    case FB_OP_MIN: return make_float4(fminf(a.x, b.x), fminf(a.y, b.y), fminf(a.z, b.z), fminf(a.w, b.w));
+    case FB_OP_MAX: return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w));
+    default: return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+  }
+}
+
+__device__ __forceinline__ void adam1(float& p, float g, float& m, float& v, const fb_adam_hparams& h) {
+  g *= h.grad_scale;
+  if (h.weight_decay != 0.f) p -= h.lr * h.weight_decay * p;
+  m = h.beta1 * m + (1.f - h.beta1) * g;
+  v = h.beta2 * v + (1.f - h.beta2) * g * g;
+  p -= h.lr * (m / h.bias_corr1) / (sqrtf(v / h.bias_corr2) + h.eps);
+}
+__device__ __forceinline__ void sgd1(float& p, float g, float& vel, const fb_sgd_hparams& h) {
+  g *= h.grad_scale;
+  if (h.weight_decay != 0.f) g += h.weight_decay * p;
+  float upd = g;
+  if (h.momentum != 0.f) {
+    vel = h.first_step ? g : h.momentum * vel + g;
+    upd = h.nesterov ? g + h.momentum * vel : vel;
+  }
+  p -= h.lr * upd;
+}
+
+// Reduce the shard of rank c.rank over all ranks, (optionally) update, publish to all ranks.
+template <int FUSE, bool MC>
+__device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, const ArArgs& a, int* s_fail) {
+  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 100)) return;
+
+  long long per = (a.n + c.world - 1) / c.world;
+  per = (per + 3) & ~3LL;
+  const long long lo = min(a.n, per * c.rank);
+  const long long hi = min(a.n, lo + per);
+  const long long n4 = (hi - lo) >> 2;
+  const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
+
+  for (long long i4 = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+    const long long e = lo + (i4 << 2);  // element index inside the bucket
+    float4 g;
+    if (MC) {
+      g = ptx::multimem_ld_reduce_add_f4(reinterpret_cast<const float4*>(c.mc_arena + a.grad_off) + (e >> 2));
+    } else {
+      float4 part[FB_MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < FB_MAX_RANKS; ++r)
+        if (r < c.world)
+          part[r] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + (e >> 2));
+      g = part[0];
+#pragma unroll
+      for (int r = 1; r < FB_MAX_RANKS; ++r)
+        if (r < c.world) g = combine4(g, part[r], a.op);
+    }
+    if (FUSE == FB_FUSE_NONE) {
+      g.x *= a.scale; g.y *= a.scale; g.z *= a.scale; g.w *= a.scale;
+      if (MC) {
+        ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.grad_off) + (e >> 2), g);
+      } else {
+#pragma unroll
+        for (int r = 0; r < FB_MAX_RANKS; ++r)
+          if (r < c.world) ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.grad_off) + (e >> 2), g);
+      }
+    } else {
+      float4 p = *(reinterpret_cast<const float4*>(c.arena[c.rank] + a.param_off) + (e >> 2));
+      if (FUSE == FB_FUSE_ADAM) {
+        float4 m = reinterpret_cast<float4*>(a.m)[i4];
+        float4 v = reinterpret_cast<float4*>(a.v)[i4];
+        adam1(p.x, g.x, m.x, v.x, a.adam);
+        adam1(p.y, g.y, m.y, v.y, a.adam);
+        adam1(p.z, g.z, m.z, v.z, a.adam);
+        adam1(p.w, g.w, m.w, v.w, a.adam);
+        reinterpret_cast<float4*>(a.m)[i4] = m;
+        reinterpret_cast<float4*>(a.v)[i4] = v;
+      } else {
+        float4 vel = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.m != nullptr) vel = reinterpret_cast<float4*>(a.m)[i4];
+        sgd1(p.x, g.x, vel.x, a.sgd);
+        sgd1(p.y, g.y, vel.y, a.sgd);
+        sgd1(p.z, g.z, vel.z, a.sgd);
+        sgd1(p.w, g.w, vel.w, a.sgd);
+        if (a.m != nullptr) reinterpret_cast<float4*>(a.m)[i4] = vel;
+      }
+      uint2 sh;
+      *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p.x, p.y);
+      *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p.z, p.w);
+      if (MC) {
+        ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + (e >> 2), p);
+        if (a.shadow_off >= 0)
+          ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + (e >> 2),
+                              make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
+      } else {
+#pragma unroll
+        for (int r = 0; r < FB_MAX_RANKS; ++r)
+          if (r < c.world) {
+            ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + (e >> 2), p);
+            if (a.shadow_off >= 0)
+              ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + (e >> 2), sh);
+          }
+      }
+    }
+  }
+  block_handshake(c, a.channel, vblock, a.epoch + 1, s_fail, 101);
+}
+
+template <int FUSE, bool MC>
+__global__ void __launch_bounds__(1024)
+allreduce_kernel(const fb_dist_ctx c, const ArArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  allreduce_body<FUSE, MC>(c, blockIdx.x, gridDim.x, a, &s_fail);
+}
+
+// All ranks of a job emulated by ONE cooperative launch on one GPU: virtual rank =
+// blockIdx.x / blocks_per_rank.  Used to exercise the multi-rank protocol where only a
+// single GPU is available (separate launches that wait on each other must never share a GPU).
+struct EmuPack {
+  fb_dist_ctx c[FB_MAX_RANKS];
+  float* m[FB_MAX_RANKS];
+  float* v[FB_MAX_RANKS];
+  int blocks_per_rank;
+};
+
+template <int FUSE>
+__global__ void __launch_bounds__(1024)
+allreduce_emulated_kernel(const EmuPack pk, ArArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const int vr = blockIdx.x / pk.blocks_per_rank;
+  const int vb = blockIdx.x % pk.blocks_per_rank;
+  a.m = pk.m[vr];
+  a.v = pk.v[vr];
+  allreduce_body<FUSE, false>(pk.c[vr], vb, pk.blocks_per_rank, a, &s_fail);
+}
+
+// ------------------------------------------------------------- pull collectives
+struct CollArgs {
+  int mode;
+  int channel;
+  uint32_t epoch;
+  int root;
+  long long in_off, out_off;  // byte offsets into the arena
+  long long n_bytes;          // bytes per chunk
+  int op;
+  float scale;
+};
+
+__device__ __forceinline__ void copy_bytes(const unsigned char* src, unsigned char* dst, long long nbytes,
+                                           long long tid, long long stride) {
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    const long long nv = nbytes >> 4;
+    for (long long i = tid; i < nv; i += stride) {
+      const float4 v = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + i);
+      reinterpret_cast<float4*>(dst)[i] = v;
+    }
+    for (long long i = (nv << 4) + tid; i < nbytes; i += stride) dst[i] = src[i];
+  } else {
+    for (long long i = tid; i < nbytes; i += stride) dst[i] = src[i];
+  }
+}
+
+__device__ void reduce_floats(const fb_dist_ctx& c, long long src_off, unsigned char* dst, long long nfloats,
+                              int op, float scale, long long tid, long long stride) {
+  for (long long i = tid; i < nfloats; i += stride) {
+    float acc = 0.f;
+    for (int r = 0; r < c.world; ++r) {
+      const float x = *reinterpret_cast<const volatile float*>(c.arena[r] + src_off + i * 4);
+      if (r == 0) acc = x;
+      else if (op == FB_OP_PROD) acc *= x;
+      else if (op == FB_OP_MIN) acc = fminf(acc, x);
+      else if (op == FB_OP_MAX) acc = fmaxf(acc, x);
+      else acc += x;
+    }
+    reinterpret_cast<float*>(dst)[i] = acc * scale;
+  }
+}
+
+__device__ void collective_body(const fb_dist_ctx& c, int vblock, int nvblocks, const CollArgs& a, int* s_fail) {
+  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 200)) return;
+  const long long tid = static_cast<long long>(vblock) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
+  unsigned char* self = c.arena[c.rank];
+  switch (a.mode) {
+    case FB_COLL_BROADCAST:
+      if (c.rank != a.root) copy_bytes(c.arena[a.root] + a.in_off, self + a.in_off, a.n_bytes, tid, stride);
+      break;
+    case FB_COLL_GATHER:
+      if (c.rank != a.root) break;
+      // fallthrough
+    case FB_COLL_ALL_GATHER:
+      for (int p = 0; p < c.world; ++p)
+        copy_bytes(c.arena[p] + a.in_off, self + a.out_off + p * a.n_bytes, a.n_bytes, tid, stride);
+      break;
+    case FB_COLL_SCATTER:
+      copy_bytes(c.arena[a.root] + a.in_off + c.rank * a.n_bytes, self + a.out_off, a.n_bytes, tid, stride);
+      break;
+    case FB_COLL_REDUCE_SCATTER:
+      reduce_floats(c, a.in_off + c.rank * a.n_bytes, self + a.out_off, a.n_bytes >> 2, a.op, a.scale, tid, stride);
+      break;
+    case FB_COLL_REDUCE:
+      if (c.rank == a.root) reduce_floats(c, a.in_off, self + a.out_off, a.n_bytes >> 2, a.op, a.scale, tid, stride);
+      break;
+    default:
+      break;
+  }
+  block_handshake(c, a.channel, vblock, a.epoch + 1, s_fail, 201);
+}
+
+__global__ void __launch_bounds__(512)
+collective_kernel(const fb_dist_ctx c, const CollArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  collective_body(c, blockIdx.x, gridDim.x, a, &s_fail);
+}
+
+struct EmuCtxPack {
+  fb_dist_ctx c[FB_MAX_RANKS];
+  int blocks_per_rank;
+};
+__global__ void __launch_bounds__(512)
+collective_emulated_kernel(const EmuCtxPack pk, const CollArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  collective_body(pk.c[blockIdx.x / pk.blocks_per_rank], blockIdx.x % pk.blocks_per_rank, pk.blocks_per_rank, a,
+                  &s_fail);
+}
+
+__global__ void barrier_kernel(const fb_dist_ctx c, int channel, uint32_t epoch) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  block_handshake(c, channel, 0, epoch, &s_fail, 300);
+}
+
+bool ctx_ok(const fb_dist_ctx* c) {
+  return c != nullptr && c->world >= 1 && c->world <= FB_MAX_RANKS && c->rank >= 0 && c->rank < c->world;
+}
+
+template <int FUSE>
+int launch_ar(const fb_dist_ctx& c, const ArArgs& a, int use_mc, int nblocks, int nthreads, cudaStream_t st) {
+  if (use_mc)
+    allreduce_kernel<FUSE, true><<<nblocks, nthreads, 0, st>>>(c, a);
+  else
+    allreduce_kernel<FUSE, false><<<nblocks, nthreads, 0, st>>>(c, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_dist_query_flag_bytes() { return FB_FLAG_BYTES; }
+extern "C" int fb_dist_query_max_blocks() { return FB_FLAG_BLOCKS; }
+extern "C" int fb_dist_query_channels() { return FB_FLAG_CHANNELS; }
+
+// Fused all-reduce of one gradient bucket.  `epoch` and `epoch + 1` are consumed on `channel`.
+// fuse: FB_FUSE_NONE (in-place all-reduce of the region at grad_off), FB_FUSE_SGD, FB_FUSE_ADAM.
+extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
+                                 long long grad_off, long long param_off, long long shadow_off, long long n,
+                                 int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
+                                 float* m, float* v, int nblocks, int nthreads, cudaStream_t stream) {
+  if (!ctx_ok(ctx) || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || nthreads < 32 ||
+      nthreads > 1024 || channel < 0 || channel >= FB_FLAG_CHANNELS)
+    return -1;
+  if (use_mc && (ctx->mc_arena == nullptr || (op != FB_OP_SUM && op != FB_OP_AVG))) return -2;
+  ArArgs a{};
+  a.channel = channel;
+  a.epoch = epoch;
+  a.grad_off = grad_off;
+  a.param_off = param_off;
+  a.shadow_off = shadow_off;
+  a.n = n;
+  a.op = op;
+  a.scale = scale;
+  if (adam) a.adam = *adam;
+  if (sgd) a.sgd = *sgd;
+  a.m = m;
+  a.v = v;
+  switch (fuse) {
+    case FB_FUSE_NONE: return launch_ar<FB_FUSE_NONE>(*ctx, a, use_mc, nblocks, nthreads, stream);
+    case FB_FUSE_SGD: return launch_ar<FB_FUSE_SGD>(*ctx, a, use_mc, nblocks, nthreads, stream);
+    case FB_FUSE_ADAM:
+      if (m == nullptr || v == nullptr) return -3;
+      return launch_ar<FB_FUSE_ADAM>(*ctx, a, use_mc, nblocks, nthreads, stream);
+    default: return -1;
+  }
+}
+
+// Same computation with all `world` ranks emulated on the current GPU in one cooperative launch.
+extern "C" int fb_dist_allreduce_emulated(const fb_dist_ctx* ctxs, int world, int fuse, int channel,
+                                          unsigned epoch, long long grad_off, long long param_off,
+                                          long long shadow_off, long long n, int op, float scale,
+                                          const fb_adam_hparams* adam, const fb_sgd_hparams* sgd, float* const* m,
+                                          float* const* v, int nblocks, int nthreads, cudaStream_t stream) {
+  if (world < 1 || world > FB_MAX_RANKS || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS) return -1;
+  EmuPack pk{};
+  for (int r = 0; r < world; ++r) {
+    if (!ctx_ok(&ctxs[r]) || ctxs[r].world != world || ctxs[r].rank != r) return -1;
+    pk.c[r] = ctxs[r];
+    pk.m[r] = m ? m[r] : nullptr;
+    pk.v[r] = v ? v[r] : nullptr;
+  }
+  pk.blocks_per_rank = nblocks;
+  ArArgs a{};
+  a.channel = channel;
+  a.epoch = epoch;
+  a.grad_off = grad_off;
+  a.param_off = param_off;
+  a.shadow_off = shadow_off;
+  a.n = n;
+  a.op = op;
+  a.scale = scale;
+  if (adam) a.adam = *adam;
+  if (sgd) a.sgd = *sgd;
+  void* args[] = {&pk, &a};
+  const dim3 grid(world * nblocks), block(nthreads);
+  const void* fn = fuse == FB_FUSE_ADAM  ? reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_ADAM>)
+                   : fuse == FB_FUSE_SGD ? reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_SGD>)
+                                         : reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_NONE>);
+  return static_cast<int>(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
+}
+
+extern "C" int fb_dist_collective(const fb_dist_ctx* ctx, int mode, int channel, unsigned epoch, int root,
+                                  long long in_off, long long out_off, long long n_bytes, int op, float scale,
+                                  int nblocks, cudaStream_t stream) {
+  if (!ctx_ok(ctx) || n_bytes < 0 || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || channel < 0 ||
+      channel >= FB_FLAG_CHANNELS || root < 0 || root >= ctx->world)
+    return -1;
+  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale};
+  collective_kernel<<<nblocks, 512, 0, stream>>>(*ctx, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_dist_collective_emulated(const fb_dist_ctx* ctxs, int world, int mode, int channel,
+                                           unsigned epoch, int root, long long in_off, long long out_off,
+                                           long long n_bytes, int op, float scale, int nblocks,
+                                           cudaStream_t stream) {
+  if (world < 1 || world > FB_MAX_RANKS || nblocks < 1 || nblocks > FB_FLAG_BLOCKS) return -1;
+  EmuCtxPack pk{};
+  for (int r = 0; r < world; ++r) pk.c[r] = ctxs[r];
+  pk.blocks_per_rank = nblocks;
+  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale};
+  void* args[] = {&pk, &a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(collective_emulated_kernel),
+                                                      dim3(world * nblocks), dim3(512), args, 0, stream));
+}
+
+extern "C" int fb_dist_barrier(const fb_dist_ctx* ctx, int channel, unsigned epoch, cudaStream_t stream) {
+  if (!ctx_ok(ctx) || channel < 0 || channel >= FB_FLAG_CHANNELS) return -1;
+  barrier_kernel<<<1, 32, 0, stream>>>(*ctx, channel, epoch);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,163 @@
+"""``DataLoader`` (ferrum-data/src/dataloader.rs:13-190).
+
+Builder-style configuration as in the reference (``batch_size`` / ``shuffle`` / ``drop_last`` /
+``num_workers``).  A batch is, by default, the pair of stacked tensors the reference's README shows;
+``collate(False)`` yields the reference's actual ``Vec<Sample>`` (a list).  For a dataset built from
+stacked tensors the batch is fetched with one row-gather kernel on the device that holds the data;
+``num_workers > 0`` fetches samples of map-style datasets on a thread pool.  ``pin_memory(True)``
+together with ``to(device)`` stages batches in pinned host memory and copies them asynchronously.
+"""
+from __future__ import annotations
+
+from concurrent.futures import ThreadPoolExecutor
+
+import torch
+
+from ..core import Tensor, _as_device, _unwrap
+from .dataset import Dataset, TensorDataset
+from .sampler import BatchSampler, RandomSampler, Sampler, SequentialSampler
+
+
+def default_collate(samples):
+    """Stack a list of samples field by field."""
+    first = samples[0]
+    if isinstance(first, (tuple, list)):
+        return tuple(default_collate([s[i] for s in samples]) for i in range(len(first)))
+    if isinstance(first, (Tensor, torch.Tensor)):
+        return Tensor(torch.stack([_unwrap(s) for s in samples], 0))
+    return Tensor(torch.as_tensor(samples))
+
+
+class DataLoader:
+    def __init__(self, dataset: Dataset, batch_size: int = 1, shuffle: bool = False, drop_last: bool = False,
+                 num_workers: int = 0, sampler: Sampler | None = None, seed: int | None = None):
+        self._dataset = dataset
+        self._batch_size, self._shuffle, self._drop_last = int(batch_size), bool(shuffle), bool(drop_last)
+        self._num_workers, self._sampler, self._seed = int(num_workers), sampler, seed
+        self._collate = default_collate
+        self._pin, self._device = False, None
+        self._epoch = 0
+        self._pool = None
+
+    @classmethod
+    def new(cls, dataset):
+        return cls(dataset)
+
+    # builder methods (each returns self)
+    def batch_size(self, n: int) -> "DataLoader":
+        self._batch_size = int(n)
+        return self
+
+    def shuffle(self, flag: bool) -> "DataLoader":
+        self._shuffle = bool(flag)
+        return self
+
+    def drop_last(self, flag: bool) -> "DataLoader":
+        self._drop_last = bool(flag)
+        return self
+
+    def num_workers(self, n: int) -> "DataLoader":
+        self._num_workers = int(n)
+        return self
+
+    def sampler(self, s: Sampler) -> "DataLoader":
+        self._sampler = s
+        return self
+
+    def seed(self, s: int) -> "DataLoader":
+        self._seed = int(s)
+        return self
+
+    def collate(self, fn) -> "DataLoader":
+        """``False``/``None`` = list of samples (the reference's behaviour); a callable = custom collation."""
+        self._collate = fn if fn else None
+        return self
+
+    def pin_memory(self, flag: bool = True) -> "DataLoader":
+        self._pin = bool(flag)
+        return self
+
+    def to(self, device) -> "DataLoader":
+        self._device = _as_device(device).to_torch()
+        return self
+
+    def dataset(self) -> Dataset:
+        return self._dataset
+
+    def len(self) -> int:
+        n = self._sampler.len() if self._sampler is not None else self._dataset.len()
+        return n // self._batch_size if self._drop_last else -(-n // self._batch_size)
+
+    __len__ = len
+
+    def is_empty(self) -> bool:
+        return self.len() == 0
+
+    def _make_sampler(self) -> Sampler:
+        if self._sampler is not None:
+            self._sampler.reset()
+            return self._sampler
+        n = self._dataset.len()
+        if self._shuffle:
+            s = RandomSampler(n, None if self._seed is None else self._seed + self._epoch)
+        else:
+            s = SequentialSampler(n)
+        return s
+
+    def _move(self, t):
+        if isinstance(t, tuple):
+            return tuple(self._move(x) for x in t)
+        if isinstance(t, Tensor) and self._device is not None and t._t.device != self._device:
+            src = t._t
+            if self._pin and not src.is_cuda and not src.is_pinned():
+                src = src.pin_memory()
+            return Tensor(src.to(self._device, non_blocking=True))
+        return t
+
+    def iter(self):
+        bs = BatchSampler(self._make_sampler(), self._batch_size, self._drop_last)
+        self._epoch += 1
+        ds = self._dataset
+        fast = isinstance(ds, TensorDataset) and ds.stacked and self._collate is default_collate
+        while True:
+            idx = bs.next_batch()
+            if idx is None:
+                return
+            if fast:
+                batch = ds.get_batch(idx)
+            else:
+                if self._num_workers > 0:
+                    if self._pool is None:
+                        self._pool = ThreadPoolExecutor(self._num_workers)
+                    samples = list(self._pool.map(ds.get, idx.tolist()))
+                else:
+                    samples = [ds.get(int(i)) for i in idx]
+                batch = self._collate(samples) if self._collate is not None else samples
+            yield self._move(batch) if self._collate is not None else batch
+
+    __iter__ = iter
+
+
+class CollatedDataLoader:
+    """Wraps a loader that yields sample lists with a collate function (dataloader.rs:169-190)."""
+
+    def __init__(self, loader: DataLoader, collate_fn):
+        self.loader, self.collate_fn = loader, collate_fn
+
+    @classmethod
+    def new(cls, loader, collate_fn):
+        return cls(loader, collate_fn)
+
+    def iter(self):
+        prev = self.loader._collate
+        self.loader._collate = None
+        try:
+            for samples in self.loader.iter():
+                yield self.collate_fn(samples)
+        finally:
+            self.loader._collate = prev
+
+    __iter__ = iter
+
+    def len(self):
+        return self.loader.len()

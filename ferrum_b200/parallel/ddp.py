@@ -1,0 +1,481 @@
+"""``DistributedDataParallel`` (ferrum-distributed/src/ddp.rs:35-237), for real.
+
+The reference wraps a module and offers ``sync_gradients`` / ``broadcast_parameters`` that loop over no-op
+collectives; its 25 MB ``bucket_size_mb`` and ``GradientBucket`` are never used.  Here:
+
+* parameters, gradients and the bf16 weight copies live in ONE peer-mapped symmetric arena per rank, laid out
+  by the native bucket planner (reverse registration order, ``bucket_size_mb`` buckets);
+* during ``backward`` each Linear's weight-gradient GEMM writes straight into its arena slot; when the last
+  gradient of a bucket is enqueued, the bucket's reduction kernel is launched on a separate high-priority
+  stream, so the reduction of layer *l* overlaps the backward GEMMs of layer *l-1*;
+* with ``fuse_optimizer(opt)`` that kernel is the fused all-reduce + 1/world + SGD-momentum / Adam update +
+  parameter publish (``fb_dist_allreduce``): ``opt.step()`` then only joins the streams.  Optimizer moments are
+  kept only by the rank that owns a shard (1/world of the state per GPU);
+* without a fused optimizer the same kernel averages the gradients in place and ``opt.step()`` runs the usual
+  multi-tensor update;
+* ``broadcast_parameters`` copies rank 0's arena to every rank with the pull-broadcast kernel.
+
+With ``Backend.Nccl`` / ``Backend.Gloo`` (baseline and CPU tests) gradients are averaged per bucket with the
+library's all-reduce on flat buffers and the optimizer runs unfused.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .. import _lib, config
+from ..core import Tensor, _unwrap
+from ..nn.modules import Linear, Module, tensor_io
+from ..ops import gemm as _gemm
+from ..ops.functional import GradSink
+from ..utils import runtime as _rt
+from .backend import Backend, CommunicationError, ReduceOp, Timeout
+from .process_group import ProcessGroup, get_world
+from .symm import SymmetricArena
+
+
+class GradientBucket:
+    """A contiguous run of gradient slots reduced together (ddp.rs:126-180)."""
+
+    def __init__(self, index: int = 0, start: int = 0, length: int = 0):
+        self.index, self.start, self.length = index, start, length
+        self.param_indices: list[int] = []
+        self.sizes: list[int] = []
+        self.buffer: list[float] = []  # host-side staging used only by add_gradient()
+        self.ready = False
+        self._pending = 0
+
+    @classmethod
+    def new(cls):
+        return cls()
+
+    def add_gradient(self, param_idx: int, grad) -> None:
+        vals = list(_unwrap(grad).reshape(-1).tolist()) if isinstance(_unwrap(grad), torch.Tensor) else list(grad)
+        self.param_indices.append(param_idx)
+        self.sizes.append(len(vals))
+        self.buffer.extend(vals)
+
+    def mark_ready(self) -> None:
+        self.ready = True
+
+    def is_ready(self) -> bool:
+        return self.ready
+
+    def size_bytes(self) -> int:
+        return (self.length or len(self.buffer)) * 4
+
+    def __repr__(self):
+        return f"GradientBucket(index={self.index}, params={self.param_indices}, bytes={self.size_bytes()})"
+
+
+class GradientHook:
+    """Bucket bookkeeping handle (ddp.rs:182-198)."""
+
+    def __init__(self, process_group, num_buckets: int):
+        self.process_group = process_group
+        self.buckets = [GradientBucket(i) for i in range(num_buckets)]
+
+    @classmethod
+    def new(cls, process_group, num_buckets):
+        return cls(process_group, num_buckets)
+
+    def all_ready(self) -> bool:
+        return all(b.is_ready() for b in self.buckets)
+
+
+def _plan(sizes, cap_elems: int, align: int, param_align: int):
+    n = len(sizes)
+    LL, I = ctypes.c_longlong, ctypes.c_int
+    szs = (LL * n)(*sizes)
+    offs, bof = (LL * n)(), (I * n)()
+    bstart, blen = (LL * max(n, 1))(), (LL * max(n, 1))()
+    nb = I(0)
+    total = _lib.host().fb_plan_buckets(n, szs, cap_elems, align, param_align, offs, bof, bstart, blen,
+                                        ctypes.byref(nb))
+    if total < 0:
+        raise ValueError("bucket planning failed")
+    return total, list(offs), list(bof), list(bstart)[:nb.value], list(blen)[:nb.value]
+
+
+class DistributedDataParallel(Module, GradSink):
+    def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, optimizer=None):
+        super().__init__()
+        self.inner = module
+        self._pg = process_group or get_world() or ProcessGroup(Backend.Gloo, 0, 1)
+        self._bucket_mb = 25.0
+        self._broadcast_buffers = True
+        self._find_unused = False
+        self._built = False
+        self._opt = None
+        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "24"))
+        self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "512"))
+        if optimizer is not None:
+            self.fuse_optimizer(optimizer)
+
+    # ------------------------------------------------------------------ reference API
+    @classmethod
+    def new(cls, module, process_group):
+        return cls(module, process_group)
+
+    def bucket_size_mb(self, size: float) -> "DistributedDataParallel":
+        self._bucket_mb = float(size)
+        return self
+
+    def broadcast_buffers(self, flag: bool) -> "DistributedDataParallel":
+        self._broadcast_buffers = bool(flag)
+        return self
+
+    def find_unused_parameters(self, flag: bool) -> "DistributedDataParallel":
+        self._find_unused = bool(flag)
+        return self
+
+    def module(self):
+        return self.inner
+
+    module_mut = module
+
+    def process_group(self) -> ProcessGroup:
+        return self._pg
+
+    def into_inner(self):
+        self.shutdown()
+        return self.inner
+
+    def fuse_optimizer(self, optimizer) -> "DistributedDataParallel":
+        """Apply ``optimizer``'s update inside the bucket reduction kernels (SGD or Adam)."""
+        self._opt = optimizer
+        optimizer._engine = self
+        return self
+
+    # ------------------------------------------------------------------ build
+    def _native(self) -> bool:
+        return (self._pg.backend() is Backend.Nvlink and self._pg.world_size() > 1 and
+                all(p.is_cuda for p in torch.nn.Module.parameters(self.inner)))
+
+    def _build(self) -> None:
+        if self._built:
+            return
+        self._built = True
+        self._params = [p for p in torch.nn.Module.parameters(self.inner) if p.requires_grad]
+        if any(p.dtype != torch.float32 for p in self._params):
+            raise CommunicationError("DistributedDataParallel expects fp32 master parameters")
+        world, rank = self._pg.world_size(), self._pg.rank()
+        cap = max(1, int(self._bucket_mb * (1 << 20)) // 4)
+        sizes = [p.numel() for p in self._params]
+        total, offs, bof, bstart, blen = _plan(sizes, cap, 4 * world, 32)
+        self._total, self._offs, self._bucket_of = total, offs, bof
+        self.buckets = [GradientBucket(i, bstart[i], blen[i]) for i in range(len(bstart))]
+        for i, b in enumerate(bof):
+            self.buckets[b].param_indices.append(i)
+            self.buckets[b].sizes.append(sizes[i])
+        self._index = {id(p): i for i, p in enumerate(self._params)}
+        self._written = [False] * len(self._params)
+        self._launched = [False] * len(self.buckets)
+        self._use_native = self._native()
+        dev = self._params[0].device if self._params else torch.device("cpu")
+        if self._use_native:
+            self._build_native(total, dev)
+        else:
+            self._flat_grads = torch.zeros(total, device=dev, dtype=torch.float32)
+            for i, p in enumerate(self._params):
+                p.grad = self._flat_grads[offs[i]:offs[i] + sizes[i]].view(p.shape)
+        # sinks and hooks
+        self._small_runs = []  # (start, length) runs of non-GEMM gradients, zeroed every step
+        sink_ids = set()
+        for mod in self.inner.modules():
+            if type(mod) is Linear and id(mod.weight) in self._index and self._use_native:
+                mod.grad_sink = self
+                sink_ids.add(id(mod.weight))
+        run = None
+        order = sorted(range(len(self._params)), key=lambda i: offs[i])
+        for i in order:
+            p = self._params[i]
+            if id(p) in sink_ids:
+                if run:
+                    self._small_runs.append(tuple(run))
+                    run = None
+                continue
+            if run and run[0] + run[1] <= offs[i] <= run[0] + run[1] + 64:
+                run[1] = offs[i] + sizes[i] - run[0]
+            else:
+                if run:
+                    self._small_runs.append(tuple(run))
+                run = [offs[i], sizes[i]]
+            p.register_post_accumulate_grad_hook(self._make_hook(i))
+        if run:
+            self._small_runs.append(tuple(run))
+        self._sink_ids = sink_ids
+        self.broadcast_parameters()
+        self._reset_step_state()
+
+    def _build_native(self, total: int, dev) -> None:
+        world, rank = self._pg.world_size(), self._pg.rank()
+        lib = _lib.cuda()
+        fb = lib.fb_dist_query_flag_bytes()
+        self._off_param = fb
+        self._off_grad = fb + total * 4
+        self._off_shadow = fb + total * 8
+        self._arena = SymmetricArena.create(total * 10, rank, world, self._pg.exchange,
+                                            self._pg.config().device_wait_ns())
+        a = self._arena
+        self._flat_params = a.view(self._off_param, (total,), torch.float32)
+        self._flat_grads = a.view(self._off_grad, (total,), torch.float32)
+        self._flat_shadow = a.view(self._off_shadow, (total,), torch.bfloat16)
+        for i, p in enumerate(self._params):
+            o, n = self._offs[i], p.numel()
+            slot = self._flat_params[o:o + n].view(p.shape)
+            slot.copy_(p.detach())
+            p.data = slot
+            p.grad = self._flat_grads[o:o + n].view(p.shape)
+            p.__dict__["_fb_shadow"] = self._flat_shadow[o:o + n].view(p.shape)
+            p.__dict__["_fb_shadow_key"] = None
+        # per-shard optimizer state (owner only) — allocated lazily in _launch_bucket
+        self._state_m = None
+        self._state_v = None
+        self._comm_stream = torch.cuda.Stream(device=dev, priority=-1)
+        self._ready_event = torch.cuda.Event()
+        self._done_event = torch.cuda.Event()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self._gemm_limit = max(sms - self._comm_blocks, sms // 2)
+
+    def _refresh_shadow(self) -> None:
+        """Recompute every bf16 weight copy from the fp32 arena with one cast kernel."""
+        lib = _lib.cuda()
+        _lib.check(lib.fb_cast(self._flat_params.data_ptr(), self._flat_shadow.data_ptr(), self._total, 0, 3,
+                               torch.cuda.current_stream().cuda_stream), "fb_cast")
+        for p in self._params:
+            p.__dict__["_fb_shadow_key"] = (p._version, p.data_ptr())
+
+    # ------------------------------------------------------------------ GradSink (called from Linear backward)
+    def acquire(self, param):
+        i = self._index[id(param)]
+        o, n = self._offs[i], param.numel()
+        acc = self._written[i]
+        self._written[i] = True
+        return self._flat_grads[o:o + n].view(param.shape), acc
+
+    def ready(self, param) -> None:
+        self._mark_ready(self._index[id(param)])
+
+    def _make_hook(self, i: int):
+        def hook(p):
+            self._mark_ready(i)
+
+        return hook
+
+    def _mark_ready(self, i: int) -> None:
+        if not self._sync_enabled:
+            return
+        b = self._bucket_of[i]
+        bk = self.buckets[b]
+        if i in self._pending[b]:
+            self._pending[b].discard(i)
+            if not self._pending[b] and not self._launched[b]:
+                self._launch_bucket(b)
+
+    def _reset_step_state(self) -> None:
+        self._pending = [set(b.param_indices) for b in self.buckets]
+        self._launched = [False] * len(self.buckets)
+        self._written = [False] * len(self._params)
+        self._sync_enabled = True
+        for b in self.buckets:
+            b.ready = False
+
+    # ------------------------------------------------------------------ bucket reduction
+    def _launch_bucket(self, b: int) -> None:
+        self._launched[b] = True
+        bk = self.buckets[b]
+        bk.ready = True
+        world = self._pg.world_size()
+        if not self._use_native:
+            if world > 1:
+                seg = self._flat_grads[bk.start:bk.start + bk.length]
+                self._pg.all_reduce(seg, ReduceOp.Average)
+            return
+        lib = _lib.cuda()
+        a = self._arena
+        cur = torch.cuda.current_stream()
+        self._ready_event.record(cur)
+        self._comm_stream.wait_event(self._ready_event)
+        opt = self._opt
+        fuse, adam_h, sgd_h, m_ptr, v_ptr = 0, None, None, None, None
+        per = ((bk.length + world - 1) // world + 3) // 4 * 4
+        lo = min(bk.length, per * self._pg.rank())
+        if opt is not None:
+            from ..optim.optimizers import SGD, Adam
+
+            if self._state_m is None:
+                dev = self._flat_params.device
+                shard_total = sum(((x.length + world - 1) // world + 3) // 4 * 4 for x in self.buckets)
+                self._state_m = torch.zeros(shard_total, device=dev, dtype=torch.float32)
+                self._state_v = torch.zeros(shard_total, device=dev, dtype=torch.float32) if isinstance(
+                    opt, Adam) else None
+                acc, self._state_off = 0, []
+                for x in self.buckets:
+                    self._state_off.append(acc)
+                    acc += ((x.length + world - 1) // world + 3) // 4 * 4
+            so = self._state_off[b]
+            if isinstance(opt, Adam):
+                fuse = 2
+                adam_h = ctypes.pointer(opt.hparams(opt.step_count + 1, 1.0 / world))
+                m_ptr = self._state_m.data_ptr() + so * 4
+                v_ptr = self._state_v.data_ptr() + so * 4
+            elif isinstance(opt, SGD):
+                fuse = 1
+                sgd_h = ctypes.pointer(opt.hparams(1.0 / world))
+                if opt.config.momentum != 0.0:
+                    m_ptr = self._state_m.data_ptr() + so * 4
+            else:
+                raise CommunicationError(f"cannot fuse optimizer of type {type(opt).__name__}")
+        e = a.next_epoch(2)
+        use_mc = 1 if a.has_multicast() else 0
+        rc = lib.fb_dist_allreduce(a.ctx, fuse, use_mc, 2, e, self._off_grad + bk.start * 4,
+                                   self._off_param + bk.start * 4, self._off_shadow + bk.start * 2, bk.length,
+                                   4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr, self._comm_blocks,
+                                   self._comm_threads, self._comm_stream.cuda_stream)
+        _lib.check(rc, "fb_dist_allreduce")
+
+    def _flush(self) -> None:
+        """Launch every bucket that has not been reduced in this step (unused parameters, explicit sync)."""
+        for b in range(len(self.buckets)):
+            if not self._launched[b]:
+                self._launch_bucket(b)
+        if self._use_native:
+            self._done_event.record(self._comm_stream)
+            torch.cuda.current_stream().wait_event(self._done_event)
+
+    # ------------------------------------------------------------------ step protocol
+    def zero_grad(self) -> None:
+        self._build()
+        for start, length in self._small_runs:
+            self._flat_grads[start:start + length].zero_()
+        if not self._use_native:
+            self._flat_grads.zero_()
+        self._reset_step_state()
+
+    def finish_step(self, optimizer) -> None:
+        """Called by ``optimizer.step()`` when the update is fused into the reduction."""
+        self._build()
+        self._flush()
+        if self._use_native and self._opt is optimizer:
+            optimizer.step_count += 1
+            for p in self._params:  # the kernels refreshed the bf16 copies together with the fp32 weights
+                p.__dict__["_fb_shadow_key"] = (p._version, p.data_ptr())
+        else:
+            optimizer._step_local()
+        self._check_status()
+        self._reset_step_state()
+
+    def sync_gradients(self, gradients=None) -> None:
+        """Average gradients over the group.  With arena-backed gradients this flushes the pending buckets;
+        explicit ``gradients`` (the reference's calling convention) are all-reduced one by one."""
+        if gradients is not None:
+            for g in gradients:
+                self._pg.all_reduce(g, ReduceOp.Average)
+            return
+        self._build()
+        self._flush()
+        self._check_status()
+
+    def broadcast_parameters(self, parameters=None) -> None:
+        """Make every rank's parameters (and buffers) equal to rank 0's."""
+        if parameters is not None:
+            for p in parameters:
+                self._pg.broadcast(p, 0)
+            return
+        self._build()
+        world = self._pg.world_size()
+        if self._use_native:
+            a = self._arena
+            torch.cuda.current_stream().synchronize()
+            e = a.next_epoch(2)
+            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 0, 2, e, 0, self._off_param, self._off_param,
+                                                      self._total * 4, 0, 1.0, 32,
+                                                      torch.cuda.current_stream().cuda_stream), "fb_dist_collective")
+            self._refresh_shadow()
+            torch.cuda.current_stream().synchronize()
+            self._check_status()
+        elif world > 1:
+            with torch.no_grad():
+                for p in self._params:
+                    self._pg.broadcast(p.data, 0)
+        if self._broadcast_buffers and world > 1:
+            with torch.no_grad():
+                for buf in self.inner.buffers():
+                    self._pg.broadcast(buf, 0)
+
+    def no_sync(self):
+        """Context manager: accumulate gradients locally without reducing (gradient accumulation)."""
+        engine = self
+
+        class _NoSync:
+            def __enter__(self):
+                engine._build()
+                engine._sync_enabled = False
+
+            def __exit__(self, *exc):
+                engine._sync_enabled = True
+
+        return _NoSync()
+
+    def _check_status(self) -> None:
+        if not self._use_native:
+            return
+        code, where, i0, i1 = _rt.read_status(clear=False)
+        if code == 0:
+            return
+        _rt.read_status(clear=True)
+        if code == 2:
+            raise Timeout(f"gradient reduction (rank {self._pg.rank()} waited for rank {i0}, epoch {i1})")
+        raise CommunicationError(f"device status {code} at site {where} ({i0}, {i1})")
+
+    # ------------------------------------------------------------------ forward
+    @tensor_io
+    def forward(self, *args, **kw):
+        self._build()
+        if self._use_native:
+            _gemm.set_gemm_cta_limit(self._gemm_limit)
+        return self.inner(*args, **kw)
+
+    def gather_optimizer_state(self) -> dict:
+        """Full-length optimizer moments assembled from the shard owners (for checkpoints)."""
+        if not (self._use_native and self._state_m is not None):
+            return {}
+        world = self._pg.world_size()
+        out = {}
+        for name, st in (("m", self._state_m), ("v", self._state_v)):
+            if st is None:
+                continue
+            parts = [torch.empty_like(st) for _ in range(world)]
+            self._pg.all_gather(parts, st)
+            full = torch.zeros(self._total, device=st.device, dtype=torch.float32)
+            for b, bk in enumerate(self.buckets):
+                per = ((bk.length + world - 1) // world + 3) // 4 * 4
+                for r in range(world):
+                    lo = min(bk.length, per * r)
+                    hi = min(bk.length, lo + per)
+                    if hi > lo:
+                        full[bk.start + lo:bk.start + hi] = parts[r][self._state_off[b]:self._state_off[b] + hi - lo]
+            out[name] = full
+        return out
+
+    def shutdown(self) -> None:
+        """Release the arena (collective: every rank should call it after its last step)."""
+        if getattr(self, "_use_native", False) and getattr(self, "_arena", None) is not None:
+            torch.cuda.synchronize()
+            _gemm.set_gemm_cta_limit(0)
+            try:
+                self._pg.barrier()
+            except Exception:
+                pass
+            for p in self._params:  # detach parameters from the arena before it is unmapped
+                p.data = p.data.clone()
+                p.grad = None
+                p.__dict__.pop("_fb_shadow", None)
+                p.__dict__.pop("_fb_shadow_key", None)
+            self._flat_params = self._flat_grads = self._flat_shadow = None
+            self._arena.close()
+            self._arena = None
+            self._use_native = False

@@ -1,0 +1,466 @@
+"""Process groups and collectives (ferrum-distributed/src/{lib,process_group,collectives}.rs).
+
+One process per GPU.  ``torch.distributed`` provides the rendezvous (TCP store at ``MASTER_ADDR:MASTER_PORT``)
+and the CPU / NCCL baselines; with ``Backend.Nvlink`` every collective on CUDA tensors is one of this package's
+kernels (``csrc/dist/collectives.cu``) acting on peer-mapped symmetric arenas: the tensor is staged into the
+arena, the kernel handshakes with the peers through flags in the arenas, moves / reduces the data over NVLink,
+and the result is copied back out.  A group of world size 1 needs no rendezvous and its collectives are
+identities — the behaviour of the reference's ``SimulatedCollectives`` for any world size.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+import threading
+
+import torch
+
+from .. import _lib
+from ..core import Tensor, _unwrap
+from ..utils import runtime as _rt
+from .backend import (AlreadyInitialized, Backend, BackendConfig, CommunicationError, InvalidConfiguration,
+                      InvalidRank, NotInitialized, ReduceOp, TensorError, Timeout, UnsupportedBackend)
+from .symm import SymmetricArena
+
+_lock = threading.Lock()
+_default_group: "ProcessGroup | None" = None
+
+_OP_CODE = {ReduceOp.Sum: 0, ReduceOp.Product: 1, ReduceOp.Min: 2, ReduceOp.Max: 3, ReduceOp.Average: 4}
+
+
+def _torch_op(op: ReduceOp):
+    import torch.distributed as dist
+
+    return {ReduceOp.Sum: dist.ReduceOp.SUM, ReduceOp.Product: dist.ReduceOp.PRODUCT, ReduceOp.Min: dist.ReduceOp.MIN,
+            ReduceOp.Max: dist.ReduceOp.MAX, ReduceOp.Average: dist.ReduceOp.SUM}[op]
+
+
+class ProcessGroup:
+    def __init__(self, backend: Backend, rank: int, world_size: int, config: BackendConfig | None = None,
+                 _torch_group=None, _ranks=None):
+        if world_size < 1 or not 0 <= rank < world_size:
+            raise InvalidRank(rank, world_size)
+        if not backend.is_available() and world_size > 1:
+            raise UnsupportedBackend(backend.value)
+        self._backend, self._rank, self._world = backend, rank, world_size
+        self._config = config or BackendConfig.from_env()
+        self._tg = _torch_group
+        self._ranks = list(_ranks) if _ranks is not None else list(range(world_size))
+        self._arena: SymmetricArena | None = None
+        self._sync_arena: SymmetricArena | None = None
+        self._chunk = int(float(os.environ.get("FERRUM_COMM_CHUNK_MB", "32")) * (1 << 20))
+        self._seq = 0  # collective sequence number, identical on all ranks of a correct program
+
+    # ------------------------------------------------------------------ accessors
+    @classmethod
+    def new(cls, backend, rank, world_size):
+        return cls(backend, rank, world_size)
+
+    @classmethod
+    def with_config(cls, backend, rank, world_size, config):
+        return cls(backend, rank, world_size, config)
+
+    def backend(self) -> Backend:
+        return self._backend
+
+    def rank(self) -> int:
+        return self._rank
+
+    def world_size(self) -> int:
+        return self._world
+
+    def is_main(self) -> bool:
+        return self._rank == 0
+
+    def config(self) -> BackendConfig:
+        return self._config
+
+    def torch_group(self):
+        return self._tg
+
+    # ------------------------------------------------------------------ plumbing
+    def exchange(self, obj) -> list:
+        """Gather one picklable object from every rank (host side, rank order)."""
+        if self._world == 1:
+            return [obj]
+        import torch.distributed as dist
+
+        out = [None] * self._world
+        dist.all_gather_object(out, obj, group=self._tg)
+        return out
+
+    def _native(self, t: torch.Tensor) -> bool:
+        return self._backend is Backend.Nvlink and self._world > 1 and t.is_cuda
+
+    def comm_arena(self) -> SymmetricArena:
+        """The staging arena of this group (allocated collectively on first use)."""
+        if self._arena is None:
+            need = self._chunk * (1 + self._world)
+            self._arena = SymmetricArena.create(need, self._rank, self._world, self.exchange,
+                                                self._config.device_wait_ns())
+        return self._arena
+
+    def _check_device_status(self, what: str) -> None:
+        code, where, i0, i1 = _rt.read_status(clear=True)
+        if code == 2:
+            raise Timeout(f"{what} (rank {self._rank} waited for rank {i0}, epoch {i1}, site {where})")
+        if code != 0:
+            raise CommunicationError(f"{what}: device status {code} at site {where} ({i0}, {i1})")
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def _blocks(self, nbytes: int) -> int:
+        return max(1, min(32, nbytes // (256 * 1024) + 1))
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, tensor, op: ReduceOp = ReduceOp.Sum):
+        """In-place reduction over all ranks; ``Average`` divides by the world size."""
+        t = _unwrap(tensor)
+        self._seq += 1
+        if self._world == 1:
+            return tensor
+        if self._native(t):
+            self._native_allreduce(t, op)
+            return tensor
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=_torch_op(op), group=self._tg)
+        if op is ReduceOp.Average:
+            t.div_(self._world)
+        return tensor
+
+    def _native_allreduce(self, t: torch.Tensor, op: ReduceOp) -> None:
+        from ..ops import functional as F
+
+        if not t.is_floating_point():
+            raise TensorError("native all_reduce supports floating-point tensors")
+        arena = self.comm_arena()
+        lib = _lib.cuda()
+        flat = t.contiguous().view(-1)
+        work = flat if flat.dtype == torch.float32 else F.raw_cast(flat, torch.float32) if flat.dtype == torch.bfloat16 \
+            else flat.float()
+        n = work.numel()
+        per = self._chunk // 4
+        off = arena.data_offset()
+        scale = 1.0 / self._world if op is ReduceOp.Average else 1.0
+        use_mc = 1 if (arena.has_multicast() and op in (ReduceOp.Sum, ReduceOp.Average)) else 0
+        for lo in range(0, n, per):
+            cnt = min(per, n - lo)
+            padded = (cnt + 4 * self._world - 1) // (4 * self._world) * (4 * self._world)
+            stage = arena.view(off, (padded,), torch.float32)
+            stage[:cnt].copy_(work[lo:lo + cnt])
+            if padded > cnt:
+                stage[cnt:].zero_()  # the padding is reduced too but never copied back
+            e = arena.next_epoch(0)
+            _lib.check(lib.fb_dist_allreduce(arena.ctx, 0, use_mc, 0, e, off, 0, -1, padded, _OP_CODE[op], scale,
+                                             None, None, None, None, self._blocks(padded * 4), 512, self._stream()),
+                       "fb_dist_allreduce")
+            work[lo:lo + cnt].copy_(stage[:cnt])
+        if work.data_ptr() != flat.data_ptr():
+            flat.copy_(work)
+        if flat.data_ptr() != t.data_ptr():
+            t.copy_(flat.view(t.shape))
+
+    def _native_pull(self, mode: int, root: int, src: torch.Tensor | None, nbytes_chunk: int, op: ReduceOp,
+                     out_chunks: int) -> torch.Tensor:
+        """Stage ``src`` at the arena's input region, run the pull kernel, return a view of the output region."""
+        arena = self.comm_arena()
+        in_off = arena.data_offset()
+        out_off = in_off + self._chunk
+        if src is not None:
+            sb = src.contiguous().view(-1).view(torch.uint8)
+            arena.view(in_off, (sb.numel(),), torch.uint8).copy_(sb)
+        e = arena.next_epoch(0)
+        scale = 1.0 / self._world if op is ReduceOp.Average else 1.0
+        _lib.check(_lib.cuda().fb_dist_collective(arena.ctx, mode, 0, e, root, in_off, out_off, nbytes_chunk,
+                                                  _OP_CODE[op], scale, self._blocks(nbytes_chunk), self._stream()),
+                   "fb_dist_collective")
+        return arena.view(out_off, (nbytes_chunk * max(out_chunks, 1),), torch.uint8)
+
+    def broadcast(self, tensor, root: int = 0):
+        t = _unwrap(tensor)
+        self._seq += 1
+        if not 0 <= root < self._world:
+            raise InvalidRank(root, self._world)
+        if self._world == 1:
+            return tensor
+        if self._native(t):
+            arena = self.comm_arena()
+            flat = t.contiguous().view(-1).view(torch.uint8)
+            off = arena.data_offset()
+            for lo in range(0, flat.numel(), self._chunk):
+                cnt = min(self._chunk, flat.numel() - lo)
+                stage = arena.view(off, (cnt,), torch.uint8)
+                if self._rank == root:
+                    stage.copy_(flat[lo:lo + cnt])
+                e = arena.next_epoch(0)
+                _lib.check(_lib.cuda().fb_dist_collective(arena.ctx, 0, 0, e, root, off, off, cnt, 0, 1.0,
+                                                          self._blocks(cnt), self._stream()), "fb_dist_collective")
+                if self._rank != root:
+                    flat[lo:lo + cnt].copy_(stage)
+            if flat.data_ptr() != t.data_ptr():
+                t.copy_(flat.view(t.dtype).view(t.shape))
+            return tensor
+        import torch.distributed as dist
+
+        dist.broadcast(t, src=self._ranks[root], group=self._tg)
+        return tensor
+
+    def reduce(self, tensor, dst: int = 0, op: ReduceOp = ReduceOp.Sum):
+        t = _unwrap(tensor)
+        self._seq += 1
+        if not 0 <= dst < self._world:
+            raise InvalidRank(dst, self._world)
+        if self._world == 1:
+            return tensor
+        if self._native(t) and t.dtype == torch.float32 and t.numel() * 4 <= self._chunk:
+            out = self._native_pull(5, dst, t, t.numel() * 4, op, 1)
+            if self._rank == dst:
+                t.copy_(out.view(torch.float32).view(t.shape))
+            return tensor
+        import torch.distributed as dist
+
+        dist.reduce(t, dst=self._ranks[dst], op=_torch_op(op), group=self._tg)
+        if op is ReduceOp.Average and self._rank == dst:
+            t.div_(self._world)
+        return tensor
+
+    def all_gather(self, output, input):
+        """``output[r]`` receives rank ``r``'s ``input``."""
+        x = _unwrap(input)
+        outs = [_unwrap(o) for o in output]
+        self._seq += 1
+        if len(outs) != self._world:
+            raise InvalidConfiguration(f"all_gather needs {self._world} output tensors, got {len(outs)}")
+        if self._world == 1:
+            outs[0].copy_(x)
+            return output
+        nbytes = x.numel() * x.element_size()
+        if self._native(x) and nbytes <= self._chunk:
+            res = self._native_pull(1, 0, x, nbytes, ReduceOp.Sum, self._world)
+            for r, o in enumerate(outs):
+                o.copy_(res[r * nbytes:(r + 1) * nbytes].view(x.dtype).view(o.shape))
+            return output
+        import torch.distributed as dist
+
+        dist.all_gather(outs, x, group=self._tg)
+        return output
+
+    def gather(self, output, input, dst: int = 0):
+        x = _unwrap(input)
+        self._seq += 1
+        if not 0 <= dst < self._world:
+            raise InvalidRank(dst, self._world)
+        outs = [_unwrap(o) for o in output] if output is not None else None
+        if self._rank == dst and (outs is None or len(outs) != self._world):
+            raise InvalidConfiguration("gather needs one output tensor per rank on the destination")
+        if self._world == 1:
+            outs[0].copy_(x)
+            return output
+        nbytes = x.numel() * x.element_size()
+        if self._native(x) and nbytes <= self._chunk:
+            res = self._native_pull(2, dst, x, nbytes, ReduceOp.Sum, self._world)
+            if self._rank == dst:
+                for r, o in enumerate(outs):
+                    o.copy_(res[r * nbytes:(r + 1) * nbytes].view(x.dtype).view(o.shape))
+            return output
+        import torch.distributed as dist
+
+        dist.gather(x, outs if self._rank == dst else None, dst=self._ranks[dst], group=self._tg)
+        return output
+
+    def scatter(self, output, input, src: int = 0):
+        o = _unwrap(output)
+        self._seq += 1
+        if not 0 <= src < self._world:
+            raise InvalidRank(src, self._world)
+        ins = [_unwrap(i) for i in input] if input is not None else None
+        if self._rank == src and (ins is None or len(ins) != self._world):
+            raise InvalidConfiguration("scatter needs one input tensor per rank on the source")
+        if self._world == 1:
+            o.copy_(ins[0])
+            return output
+        nbytes = o.numel() * o.element_size()
+        if self._native(o) and nbytes * self._world <= self._chunk:
+            stacked = torch.cat([i.contiguous().view(-1) for i in ins]) if self._rank == src else None
+            res = self._native_pull(3, src, stacked, nbytes, ReduceOp.Sum, 1)
+            o.copy_(res.view(o.dtype).view(o.shape))
+            return output
+        import torch.distributed as dist
+
+        dist.scatter(o, ins if self._rank == src else None, src=self._ranks[src], group=self._tg)
+        return output
+
+    def reduce_scatter(self, output, input, op: ReduceOp = ReduceOp.Sum):
+        """``output`` receives the reduction over ranks of ``input[rank]``."""
+        o = _unwrap(output)
+        ins = [_unwrap(i) for i in input]
+        self._seq += 1
+        if len(ins) != self._world:
+            raise InvalidConfiguration(f"reduce_scatter needs {self._world} input tensors, got {len(ins)}")
+        if self._world == 1:
+            o.copy_(ins[0])
+            return output
+        nbytes = o.numel() * 4
+        if self._native(o) and o.dtype == torch.float32 and nbytes * self._world <= self._chunk:
+            stacked = torch.cat([i.contiguous().view(-1) for i in ins])
+            res = self._native_pull(4, 0, stacked, nbytes, op, 1)
+            o.copy_(res.view(torch.float32).view(o.shape))
+            return output
+        import torch.distributed as dist
+
+        dist.reduce_scatter(o, ins, op=_torch_op(op), group=self._tg)
+        if op is ReduceOp.Average:
+            o.div_(self._world)
+        return output
+
+    def barrier(self) -> None:
+        self._seq += 1
+        if self._world == 1:
+            return
+        if self._backend is Backend.Nvlink and torch.cuda.is_available():
+            if self._sync_arena is None:  # a flags-only arena: the barrier moves no data
+                self._sync_arena = SymmetricArena.create(4096, self._rank, self._world, self.exchange,
+                                                         self._config.device_wait_ns())
+            arena = self._sync_arena
+            e = arena.next_epoch(1)
+            _lib.check(_lib.cuda().fb_dist_barrier(arena.ctx, 1, e, self._stream()), "fb_dist_barrier")
+            torch.cuda.current_stream().synchronize()
+            self._check_device_status("barrier")
+            return
+        import torch.distributed as dist
+
+        try:
+            dist.barrier(group=self._tg)
+        except RuntimeError as exc:
+            raise Timeout(f"barrier ({exc})") from None
+
+    def sequence_number(self) -> int:
+        """How many collectives this rank has issued on the group (for mismatch detection on the host)."""
+        return self._seq
+
+    def verify_in_step(self) -> None:
+        """Host-side check that all ranks issued the same number of collectives; raises on mismatch."""
+        seqs = self.exchange(self._seq)
+        if len(set(seqs)) != 1:
+            raise CommunicationError(f"ranks disagree on the collective sequence number: {seqs}")
+
+    def close(self) -> None:
+        for name in ("_arena", "_sync_arena"):
+            a = getattr(self, name)
+            if a is not None:
+                a.close()
+                setattr(self, name, None)
+
+
+# ---------------------------------------------------------------------- module-level API (lib.rs:46-130)
+def _init_torch(backend: Backend, rank: int, world: int, cfg: BackendConfig) -> None:
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        return
+    tb = "gloo" if backend is Backend.Gloo else "cpu:gloo,cuda:nccl"
+    if backend is Backend.Mpi:
+        raise UnsupportedBackend("mpi")
+    os.environ.setdefault("MASTER_ADDR", cfg.master_addr)
+    os.environ.setdefault("MASTER_PORT", str(cfg.master_port))
+    try:
+        dist.init_process_group(tb, init_method=f"tcp://{cfg.master_addr}:{cfg.master_port}", rank=rank,
+                                world_size=world, timeout=datetime.timedelta(seconds=cfg.timeout_seconds))
+    except Exception as exc:  # rendezvous failed: a rank never joined, wrong address, ...
+        msg = str(exc)
+        if "imeout" in msg or "timed out" in msg:
+            raise Timeout(f"rendezvous at {cfg.master_addr}:{cfg.master_port} ({msg})") from None
+        raise CommunicationError(msg) from None
+
+
+def init_process_group(backend=Backend.Nvlink, rank: int = 0, world_size: int = 1,
+                       config: BackendConfig | None = None) -> ProcessGroup:
+    global _default_group
+    if isinstance(backend, str):
+        backend = Backend.from_str(backend)
+    with _lock:
+        if _default_group is not None:
+            raise AlreadyInitialized()
+        if world_size < 1 or not 0 <= rank < world_size:
+            raise InvalidRank(rank, world_size)
+        cfg = config or BackendConfig.from_env()
+        if world_size > 1:
+            if not backend.is_available():
+                raise UnsupportedBackend(backend.value)
+            _init_torch(backend, rank, world_size, cfg)
+        _default_group = ProcessGroup(backend, rank, world_size, cfg)
+        return _default_group
+
+
+def init_process_group_from_env(backend=None) -> ProcessGroup:
+    """``RANK`` (0), ``WORLD_SIZE`` (1), ``DIST_BACKEND`` (gloo), plus ``LOCAL_RANK`` to pick the GPU."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if backend is None:
+        backend = os.environ.get("DIST_BACKEND", "gloo")
+    if isinstance(backend, str):
+        backend = Backend.from_str(backend)
+    if backend in (Backend.Nvlink, Backend.Nccl) and torch.cuda.is_available():
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", str(rank))) % max(torch.cuda.device_count(), 1))
+    return init_process_group(backend, rank, world)
+
+
+def get_world():
+    return _default_group
+
+
+def is_initialized() -> bool:
+    return _default_group is not None
+
+
+def destroy_process_group() -> None:
+    global _default_group
+    with _lock:
+        g, _default_group = _default_group, None
+    if g is not None:
+        g.close()
+        import torch.distributed as dist
+
+        if g.world_size() > 1 and dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def get_rank() -> int:
+    return _default_group.rank() if _default_group is not None else 0
+
+
+def get_world_size() -> int:
+    return _default_group.world_size() if _default_group is not None else 1
+
+
+def is_main_process() -> bool:
+    return get_rank() == 0
+
+
+def barrier() -> None:
+    if _default_group is not None:
+        _default_group.barrier()
+
+
+def new_group(ranks) -> ProcessGroup:
+    """A sub-group of the default group containing ``ranks`` (collective over the default group)."""
+    if _default_group is None:
+        raise NotInitialized()
+    ranks = sorted(int(r) for r in ranks)
+    world = _default_group.world_size()
+    if not ranks or any(r < 0 or r >= world for r in ranks):
+        raise InvalidRank(ranks[0] if ranks else -1, world)
+    me = _default_group.rank()
+    tg = None
+    if world > 1:
+        import torch.distributed as dist
+
+        tg = dist.new_group(ranks)
+    backend = _default_group.backend()
+    if backend is Backend.Nvlink and len(ranks) != world:
+        backend = Backend.Nccl  # arenas are mapped for the full world; sub-groups use the library transport
+    if me not in ranks:
+        return ProcessGroup(backend, 0, 1, _default_group.config())
+    return ProcessGroup(backend, ranks.index(me), len(ranks), _default_group.config(), _torch_group=tg, _ranks=ranks)

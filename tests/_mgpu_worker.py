@@ -1,0 +1,130 @@
+"""One rank of the multi-GPU test job (launched by torch.distributed.run): native NVLink collectives and the
+fused DDP engine against locally computed expectations.  Writes "PASS" / a failure list per rank."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import ferrum_b200 as fb  # noqa: E402
+from ferrum_b200 import distributed as d  # noqa: E402
+
+
+def main(out_dir):
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    pg = d.init_process_group_from_env("nvlink")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fails = []
+
+    def check(name, cond):
+        if not bool(cond):
+            fails.append(name)
+
+    # ---- collectives on CUDA tensors (this package's kernels)
+    for n in (3, 1000, 1 << 20, (1 << 23) + 5):
+        t = torch.full((n,), float(rank + 1), device=dev)
+        pg.all_reduce(t, d.ReduceOp.Sum)
+        check(f"all_reduce sum {n}", torch.allclose(t, torch.full_like(t, world * (world + 1) / 2)))
+    g = torch.Generator(device=dev).manual_seed(11)
+    base = torch.randn(world, 4099, device=dev, generator=g)
+    t = base[rank].clone()
+    pg.all_reduce(t, d.ReduceOp.Average)
+    check("all_reduce avg", torch.allclose(t, base.mean(0), atol=1e-5))
+    t = base[rank].clone()
+    pg.all_reduce(t, d.ReduceOp.Max)
+    check("all_reduce max", torch.equal(t, base.max(0).values))
+    tb = base[rank].to(torch.bfloat16)
+    pg.all_reduce(tb, d.ReduceOp.Sum)
+    check("all_reduce bf16", torch.allclose(tb.float(), base.to(torch.bfloat16).float().sum(0), atol=5e-2, rtol=2e-2))
+    b = base[1].clone() if rank == 1 else torch.zeros(4099, device=dev)
+    pg.broadcast(b, 1)
+    check("broadcast", torch.equal(b, base[1]))
+    outs = [torch.empty(4099, device=dev) for _ in range(world)]
+    pg.all_gather(outs, base[rank].clone())
+    check("all_gather", all(torch.equal(o, base[r]) for r, o in enumerate(outs)))
+    go = [torch.empty(17, device=dev) for _ in range(world)] if rank == 0 else None
+    pg.gather(go, base[rank, :17].clone(), 0)
+    if rank == 0:
+        check("gather", all(torch.equal(o, base[r, :17]) for r, o in enumerate(go)))
+    o = torch.empty(33, device=dev)
+    pg.scatter(o, [base[r, :33].clone() for r in range(world)] if rank == 0 else None, 0)
+    check("scatter", torch.equal(o, base[rank, :33]))
+    o = torch.empty(64, device=dev)
+    pg.reduce_scatter(o, [base[rank, r * 64:(r + 1) * 64].clone() for r in range(world)], d.ReduceOp.Sum)
+    check("reduce_scatter", torch.allclose(o, base[:, rank * 64:(rank + 1) * 64].sum(0), atol=1e-5))
+    r_ = base[rank, :100].clone()
+    pg.reduce(r_, 0, d.ReduceOp.Sum)
+    if rank == 0:
+        check("reduce", torch.allclose(r_, base[:, :100].sum(0), atol=1e-5))
+    pg.barrier()
+
+    # ---- fused DDP (fp32 GEMMs): world ranks x batch 16 == one process x batch world*16
+    def make_model(seed=5):
+        torch.manual_seed(seed)
+        return fb.nn.Sequential(fb.nn.Linear(24, 64), fb.nn.GELU(), fb.nn.LayerNorm([64]), fb.nn.Linear(64, 64),
+                                fb.nn.ReLU(), fb.nn.Linear(64, 8)).to_device(fb.Device.Cuda(dev.index))
+
+    gen = torch.Generator().manual_seed(9)
+    X = torch.randn(world * 16, 24, generator=gen).to(dev)
+    Y = torch.randint(0, 8, (world * 16,), generator=gen).to(dev)
+    ref = make_model()
+    ropt = fb.optim.Adam(ref.parameters(), fb.optim.AdamConfig(lr=1e-2, weight_decay=0.01))
+    for _ in range(5):
+        ropt.zero_grad()
+        fb.nn.cross_entropy(ref(X), Y).backward()
+        ropt.step()
+    model = make_model()
+    if rank != 0:
+        with torch.no_grad():
+            for p in model.torch_parameters():
+                p.add_(0.5)
+    opt = fb.optim.Adam(model.parameters(), fb.optim.AdamConfig(lr=1e-2, weight_decay=0.01))
+    ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.005)
+    ddp.fuse_optimizer(opt)
+    xs, ys = X[rank * 16:(rank + 1) * 16], Y[rank * 16:(rank + 1) * 16]
+    for _ in range(5):
+        opt.zero_grad()
+        fb.nn.cross_entropy(ddp(xs), ys).backward()
+        opt.step()
+    torch.cuda.synchronize()
+    check("ddp buckets > 1", len(ddp.buckets) > 1)
+    for i, (p, q) in enumerate(zip(model.torch_parameters(), ref.torch_parameters())):
+        check(f"ddp fused adam param {i} (max err {(p - q).abs().max().item():.2e})",
+              torch.allclose(p, q, atol=5e-5, rtol=1e-3))
+    flat = torch.cat([p.detach().reshape(-1) for p in model.torch_parameters()])
+    allp = [torch.empty_like(flat) for _ in range(world)]
+    pg.all_gather(allp, flat)
+    check("ddp replicas identical", all(torch.equal(allp[0], a) for a in allp))
+    state = ddp.gather_optimizer_state()
+    check("optimizer state gathered", "m" in state and state["m"].abs().sum().item() > 0)
+    ddp.shutdown()
+
+    # ---- fused DDP under bf16 autocast with SGD momentum: replicas stay identical, loss goes down
+    model = make_model(6)
+    opt = fb.optim.SGD(model.parameters(), fb.optim.SGDConfig(lr=0.05, momentum=0.9))
+    ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.005).fuse_optimizer(opt)
+    losses = []
+    for _ in range(8):
+        opt.zero_grad()
+        with fb.autocast():
+            loss = fb.nn.cross_entropy(ddp(xs), ys)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    check(f"bf16 ddp loss decreases {losses[0]:.3f}->{losses[-1]:.3f}", losses[-1] < losses[0])
+    flat = torch.cat([p.detach().reshape(-1) for p in model.torch_parameters()])
+    allp = [torch.empty_like(flat) for _ in range(world)]
+    pg.all_gather(allp, flat)
+    check("bf16 ddp replicas identical", all(torch.equal(allp[0], a) for a in allp))
+    ddp.shutdown()
+    fb.utils.runtime.check_status()
+    d.destroy_process_group()
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write("PASS" if not fails else "FAIL: " + "; ".join(fails))
+    print(f"rank {rank}:", "PASS" if not fails else fails)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

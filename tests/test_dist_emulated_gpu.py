@@ -1,0 +1,205 @@
+"""Inter-GPU kernels with all ranks emulated on ONE GPU as a single cooperative launch.
+
+The same device code runs in the multi-process path; here the "peers" are further arenas on the same device,
+so the handshake protocol, the shard arithmetic and the fused optimizer update are checked without a second GPU.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(world, nfloats_total):
+    from ferrum_b200 import _lib
+    from ferrum_b200._lib_dist import DistCtx
+    from ferrum_b200.parallel.symm import SymmetricArena
+
+    arenas = SymmetricArena.emulated(nfloats_total * 4, world)
+    ctxs = (DistCtx * world)(*[a.ctx for a in arenas])
+    return _lib.cuda(), arenas, ctxs
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("n", [8 * 4, 8 * 4 * 333, 1 << 20])
+def test_allreduce_average_emulated(world, n):
+    from ferrum_b200.utils.runtime import check_status
+
+    lib, arenas, ctxs = _setup(world, n)
+    off = arenas[0].data_offset()
+    torch.manual_seed(world * 31 + n)
+    data = [torch.randn(n, device="cuda") for _ in range(world)]
+    for a, d in zip(arenas, data):
+        a.view(off, (n,), torch.float32).copy_(d)
+    rc = lib.fb_dist_allreduce_emulated(ctxs, world, 0, 0, 1, off, 0, -1, n, 4, 1.0 / world, None, None, None, None,
+                                        4, 256, _stream())
+    assert rc == 0
+    check_status()
+    ref = torch.stack(data).sum(0) / world
+    for a in arenas:
+        assert torch.allclose(a.view(off, (n,), torch.float32), ref, atol=1e-5, rtol=1e-5)
+    for a in arenas:
+        a.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_allreduce_adam_emulated(world):
+    from ferrum_b200 import _lib as L
+    from ferrum_b200.utils.runtime import check_status
+
+    n = 4 * world * 1000
+    lib, arenas, ctxs = _setup(world, n * 3)
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + n * 4, base + n * 8
+    torch.manual_seed(5)
+    p0 = torch.randn(n, device="cuda")
+    grads = [torch.randn(n, device="cuda") for _ in range(world)]
+    for a, g in zip(arenas, grads):
+        a.view(off_p, (n,), torch.float32).copy_(p0)
+        a.view(off_g, (n,), torch.float32).copy_(g)
+    per = n // world
+    ms = [torch.zeros(per, device="cuda") for _ in range(world)]
+    vs = [torch.zeros(per, device="cuda") for _ in range(world)]
+    mp = (ctypes.c_void_p * world)(*[m.data_ptr() for m in ms])
+    vp = (ctypes.c_void_p * world)(*[v.data_ptr() for v in vs])
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.999, 1e-8, 0.05
+    ref_p, ref_m, ref_v = p0.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    epoch = 1
+    for t in (1, 2, 3):
+        h = L.AdamH(lr, b1, b2, eps, wd, 1 - b1 ** t, 1 - b2 ** t, 1.0 / world)
+        rc = lib.fb_dist_allreduce_emulated(ctxs, world, 2, 0, epoch, off_g, off_p, off_s, n, 0, 1.0,
+                                            ctypes.byref(h), None, mp, vp, 3, 256, _stream())
+        assert rc == 0
+        epoch += 2
+        g = torch.stack(grads).sum(0) / world
+        ref_p = ref_p - lr * wd * ref_p
+        ref_m = b1 * ref_m + (1 - b1) * g
+        ref_v = b2 * ref_v + (1 - b2) * g * g
+        ref_p = ref_p - lr * (ref_m / (1 - b1 ** t)) / ((ref_v / (1 - b2 ** t)).sqrt() + eps)
+    check_status()
+    for a in arenas:
+        assert torch.allclose(a.view(off_p, (n,), torch.float32), ref_p, atol=1e-5, rtol=1e-5)
+        assert torch.equal(a.view(off_s, (n,), torch.bfloat16), ref_p_bf16(a, off_p, n))
+    assert torch.allclose(torch.cat(ms), ref_m, atol=1e-6)
+    for a in arenas:
+        a.close()
+
+
+def ref_p_bf16(arena, off_p, n):
+    return arena.view(off_p, (n,), torch.float32).to(torch.bfloat16)
+
+
+def test_fused_allreduce_sgd_momentum_emulated():
+    from ferrum_b200 import _lib as L
+    from ferrum_b200.utils.runtime import check_status
+
+    world, n = 4, 16 * 257
+    lib, arenas, ctxs = _setup(world, n * 3)
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + n * 4, base + n * 8
+    p0 = torch.randn(n, device="cuda")
+    grads = [torch.randn(n, device="cuda") for _ in range(world)]
+    for a, g in zip(arenas, grads):
+        a.view(off_p, (n,), torch.float32).copy_(p0)
+        a.view(off_g, (n,), torch.float32).copy_(g)
+    per = ((n + world - 1) // world + 3) // 4 * 4
+    vel = [torch.zeros(per, device="cuda") for _ in range(world)]
+    mp = (ctypes.c_void_p * world)(*[v.data_ptr() for v in vel])
+    ref_p, ref_v = p0.clone(), None
+    epoch = 1
+    for step in range(3):
+        h = L.SgdH(0.1, 0.9, 1e-4, 1.0 / world, 0, 1 if step == 0 else 0)
+        rc = lib.fb_dist_allreduce_emulated(ctxs, world, 1, 0, epoch, off_g, off_p, off_s, n, 0, 1.0, None,
+                                            ctypes.byref(h), mp, None, 2, 128, _stream())
+        assert rc == 0
+        epoch += 2
+        g = torch.stack(grads).sum(0) / world + 1e-4 * ref_p
+        ref_v = g.clone() if ref_v is None else 0.9 * ref_v + g
+        ref_p = ref_p - 0.1 * ref_v
+    check_status()
+    for a in arenas:
+        assert torch.allclose(a.view(off_p, (n,), torch.float32), ref_p, atol=1e-5, rtol=1e-5)
+    for a in arenas:
+        a.close()
+
+
+def test_pull_collectives_emulated():
+    from ferrum_b200.utils.runtime import check_status
+
+    world, n = 4, 1000
+    lib, arenas, ctxs = _setup(world, n * (2 + 2 * world))
+    base = arenas[0].data_offset()
+    in_off, out_off = base, base + n * world * 4
+    data = [torch.randn(n * world, device="cuda") for _ in range(world)]
+
+    def load():
+        for a, d in zip(arenas, data):
+            a.view(in_off, (n * world,), torch.float32).copy_(d)
+
+    epoch = 1
+    # broadcast from rank 2 (in place)
+    load()
+    assert lib.fb_dist_collective_emulated(ctxs, world, 0, 0, epoch, 2, in_off, in_off, n * 4, 0, 1.0, 2, _stream()) == 0
+    epoch += 2
+    for a in arenas:
+        assert torch.equal(a.view(in_off, (n,), torch.float32), data[2][:n])
+    # all-gather of the first n floats of every rank
+    load()
+    assert lib.fb_dist_collective_emulated(ctxs, world, 1, 0, epoch, 0, in_off, out_off, n * 4, 0, 1.0, 2, _stream()) == 0
+    epoch += 2
+    want = torch.cat([d[:n] for d in data])
+    for a in arenas:
+        assert torch.equal(a.view(out_off, (n * world,), torch.float32), want)
+    # scatter from rank 1
+    load()
+    assert lib.fb_dist_collective_emulated(ctxs, world, 3, 0, epoch, 1, in_off, out_off, n * 4, 0, 1.0, 2, _stream()) == 0
+    epoch += 2
+    for r, a in enumerate(arenas):
+        assert torch.equal(a.view(out_off, (n,), torch.float32), data[1][r * n:(r + 1) * n])
+    # reduce-scatter (sum)
+    load()
+    assert lib.fb_dist_collective_emulated(ctxs, world, 4, 0, epoch, 0, in_off, out_off, n * 4, 0, 1.0, 2, _stream()) == 0
+    epoch += 2
+    tot = torch.stack(data).sum(0)
+    for r, a in enumerate(arenas):
+        assert torch.allclose(a.view(out_off, (n,), torch.float32), tot[r * n:(r + 1) * n], atol=1e-5)
+    # reduce (max) to rank 3
+    load()
+    assert lib.fb_dist_collective_emulated(ctxs, world, 5, 0, epoch, 3, in_off, out_off, n * 4, 3, 1.0, 2, _stream()) == 0
+    epoch += 2
+    assert torch.equal(arenas[3].view(out_off, (n,), torch.float32), torch.stack(data).max(0).values[:n])
+    check_status()
+    for a in arenas:
+        a.close()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A handshake whose peer never signals gives up after the configured bound and reports it."""
+    from ferrum_b200 import _lib
+    from ferrum_b200._lib_dist import DistCtx
+    from ferrum_b200.parallel.symm import SymmetricArena
+    from ferrum_b200.utils import runtime as rt
+
+    arena = SymmetricArena.emulated(4096, 1, wait_ns=50_000_000)[0]
+    ctx = DistCtx()
+    ctx.rank, ctx.world = 0, 2
+    ctx.arena[0] = arena.local_ptr
+    ctx.arena[1] = arena.local_ptr  # "rank 1" never writes its slot: nothing else is launched
+    ctx.status = rt.status_ptr()
+    ctx.timeout_ns = 50_000_000
+    rt.read_status(clear=True)
+    assert _lib.cuda().fb_dist_barrier(ctx, 3, 7, _stream()) == 0
+    torch.cuda.synchronize()
+    code, where, peer, epoch = rt.read_status(clear=True)
+    assert code == 2 and peer == 1 and epoch == 7
+    with pytest.raises(rt.DeviceStatusError):
+        _lib.cuda().fb_dist_barrier(ctx, 3, 9, _stream())
+        rt.check_status()
+    x = torch.ones(1024, device="cuda")
+    assert float((x * 2).sum()) == 2048.0  # the context is still usable
+    arena.close()
