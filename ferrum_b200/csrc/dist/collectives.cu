@@ -113,7 +113,9 @@ __device__ __forceinline__ void sgd1(float& p, float g, float& vel, const fb_sgd
 }
 
 // Reduce the shard of rank c.rank over all ranks, (optionally) update, publish to all ranks.
-template <int FUSE, bool MC>
+// Each thread keeps U independent float4 positions in flight: a peer load costs a round trip over
+// NVLink (microseconds), so throughput is set by the bytes outstanding per SM, not by the thread count.
+template <int FUSE, bool MC, int U, int W>
 __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, const ArArgs& a, int* s_fail) {
   if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 100)) return;
 
@@ -123,81 +125,117 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
   const long long hi = min(a.n, lo + per);
   const long long n4 = (hi - lo) >> 2;
   const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
+  const long long lo4 = lo >> 2;
 
-  for (long long i4 = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
-    const long long e = lo + (i4 << 2);  // element index inside the bucket
-    float4 g;
+  for (long long base = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; base < n4; base += stride * U) {
+    float4 g[U];
     if (MC) {
-      g = ptx::multimem_ld_reduce_add_f4(reinterpret_cast<const float4*>(c.mc_arena + a.grad_off) + (e >> 2));
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * stride;
+        if (i4 < n4)
+          g[u] = ptx::multimem_ld_reduce_add_f4(reinterpret_cast<const float4*>(c.mc_arena + a.grad_off) + lo4 + i4);
+      }
     } else {
-      float4 part[FB_MAX_RANKS];
+      float4 part[U][W];  // W = compile-time bound on the world size, so the table stays in registers
 #pragma unroll
-      for (int r = 0; r < FB_MAX_RANKS; ++r)
-        if (r < c.world)
-          part[r] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + (e >> 2));
-      g = part[0];
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * stride;
+        if (i4 < n4) {
 #pragma unroll
-      for (int r = 1; r < FB_MAX_RANKS; ++r)
-        if (r < c.world) g = combine4(g, part[r], a.op);
+          for (int r = 0; r < W; ++r)
+            if (r < c.world)
+              part[u][r] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + lo4 + i4);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (base + u * stride < n4) {
+          g[u] = part[u][0];
+#pragma unroll
+          for (int r = 1; r < W; ++r)
+            if (r < c.world) g[u] = combine4(g[u], part[u][r], a.op);
+        }
+      }
     }
     if (FUSE == FB_FUSE_NONE) {
-      g.x *= a.scale; g.y *= a.scale; g.z *= a.scale; g.w *= a.scale;
-      if (MC) {
-        ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.grad_off) + (e >> 2), g);
-      } else {
 #pragma unroll
-        for (int r = 0; r < FB_MAX_RANKS; ++r)
-          if (r < c.world) ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.grad_off) + (e >> 2), g);
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * stride;
+        if (i4 >= n4) continue;
+        float4 x = g[u];
+        x.x *= a.scale; x.y *= a.scale; x.z *= a.scale; x.w *= a.scale;
+        if (MC) {
+          ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.grad_off) + lo4 + i4, x);
+        } else {
+#pragma unroll
+          for (int r = 0; r < W; ++r)
+            if (r < c.world) ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.grad_off) + lo4 + i4, x);
+        }
       }
     } else {
-      float4 p = *(reinterpret_cast<const float4*>(c.arena[c.rank] + a.param_off) + (e >> 2));
-      if (FUSE == FB_FUSE_ADAM) {
-        float4 m = reinterpret_cast<float4*>(a.m)[i4];
-        float4 v = reinterpret_cast<float4*>(a.v)[i4];
-        adam1(p.x, g.x, m.x, v.x, a.adam);
-        adam1(p.y, g.y, m.y, v.y, a.adam);
-        adam1(p.z, g.z, m.z, v.z, a.adam);
-        adam1(p.w, g.w, m.w, v.w, a.adam);
-        reinterpret_cast<float4*>(a.m)[i4] = m;
-        reinterpret_cast<float4*>(a.v)[i4] = v;
-      } else {
-        float4 vel = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a.m != nullptr) vel = reinterpret_cast<float4*>(a.m)[i4];
-        sgd1(p.x, g.x, vel.x, a.sgd);
-        sgd1(p.y, g.y, vel.y, a.sgd);
-        sgd1(p.z, g.z, vel.z, a.sgd);
-        sgd1(p.w, g.w, vel.w, a.sgd);
-        if (a.m != nullptr) reinterpret_cast<float4*>(a.m)[i4] = vel;
-      }
-      uint2 sh;
-      *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p.x, p.y);
-      *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p.z, p.w);
-      if (MC) {
-        ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + (e >> 2), p);
-        if (a.shadow_off >= 0)
-          ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + (e >> 2),
-                              make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
-      } else {
+      float4 p[U], m[U], v[U];
 #pragma unroll
-        for (int r = 0; r < FB_MAX_RANKS; ++r)
-          if (r < c.world) {
-            ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + (e >> 2), p);
-            if (a.shadow_off >= 0)
-              ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + (e >> 2), sh);
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * stride;
+        if (i4 < n4) {
+          p[u] = *(reinterpret_cast<const float4*>(c.arena[c.rank] + a.param_off) + lo4 + i4);
+          if (FUSE == FB_FUSE_ADAM) {
+            m[u] = reinterpret_cast<const float4*>(a.m)[i4];
+            v[u] = reinterpret_cast<const float4*>(a.v)[i4];
+          } else {
+            m[u] = a.m != nullptr ? reinterpret_cast<const float4*>(a.m)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
           }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i4 = base + u * stride;
+        if (i4 >= n4) continue;
+        if (FUSE == FB_FUSE_ADAM) {
+          adam1(p[u].x, g[u].x, m[u].x, v[u].x, a.adam);
+          adam1(p[u].y, g[u].y, m[u].y, v[u].y, a.adam);
+          adam1(p[u].z, g[u].z, m[u].z, v[u].z, a.adam);
+          adam1(p[u].w, g[u].w, m[u].w, v[u].w, a.adam);
+          reinterpret_cast<float4*>(a.m)[i4] = m[u];
+          reinterpret_cast<float4*>(a.v)[i4] = v[u];
+        } else {
+          sgd1(p[u].x, g[u].x, m[u].x, a.sgd);
+          sgd1(p[u].y, g[u].y, m[u].y, a.sgd);
+          sgd1(p[u].z, g[u].z, m[u].z, a.sgd);
+          sgd1(p[u].w, g[u].w, m[u].w, a.sgd);
+          if (a.m != nullptr) reinterpret_cast<float4*>(a.m)[i4] = m[u];
+        }
+        uint2 sh;
+        *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p[u].x, p[u].y);
+        *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p[u].z, p[u].w);
+        if (MC) {
+          ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + lo4 + i4, p[u]);
+          if (a.shadow_off >= 0)
+            ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + lo4 + i4,
+                                make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
+        } else {
+#pragma unroll
+          for (int r = 0; r < W; ++r)
+            if (r < c.world) {
+              ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + lo4 + i4, p[u]);
+              if (a.shadow_off >= 0)
+                ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + lo4 + i4, sh);
+            }
+        }
       }
     }
   }
   block_handshake(c, a.channel, vblock, a.epoch + 1, s_fail, 101);
 }
 
-template <int FUSE, bool MC>
-__global__ void __launch_bounds__(1024)
+template <int FUSE, bool MC, int U, int W>
+__global__ void __launch_bounds__(256)
 allreduce_kernel(const fb_dist_ctx c, const ArArgs a) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
-  allreduce_body<FUSE, MC>(c, blockIdx.x, gridDim.x, a, &s_fail);
+  allreduce_body<FUSE, MC, U, W>(c, blockIdx.x, gridDim.x, a, &s_fail);
 }
 
 // All ranks of a job emulated by ONE cooperative launch on one GPU: virtual rank =
@@ -211,7 +249,7 @@ struct EmuPack {
 };
 
 template <int FUSE>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 allreduce_emulated_kernel(const EmuPack pk, ArArgs a) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
@@ -220,7 +258,7 @@ allreduce_emulated_kernel(const EmuPack pk, ArArgs a) {
   const int vb = blockIdx.x % pk.blocks_per_rank;
   a.m = pk.m[vr];
   a.v = pk.v[vr];
-  allreduce_body<FUSE, false>(pk.c[vr], vb, pk.blocks_per_rank, a, &s_fail);
+  allreduce_body<FUSE, false, 1, FB_MAX_RANKS>(pk.c[vr], vb, pk.blocks_per_rank, a, &s_fail);
 }
 
 // ------------------------------------------------------------- pull collectives
@@ -330,10 +368,15 @@ bool ctx_ok(const fb_dist_ctx* c) {
 
 template <int FUSE>
 int launch_ar(const fb_dist_ctx& c, const ArArgs& a, int use_mc, int nblocks, int nthreads, cudaStream_t st) {
+  // bytes in flight per thread = U * world * 16 (peer loads) = 128: deeper unrolling for small worlds
   if (use_mc)
-    allreduce_kernel<FUSE, true><<<nblocks, nthreads, 0, st>>>(c, a);
+    allreduce_kernel<FUSE, true, 4, FB_MAX_RANKS><<<nblocks, nthreads, 0, st>>>(c, a);
+  else if (c.world <= 2)
+    allreduce_kernel<FUSE, false, 4, 2><<<nblocks, nthreads, 0, st>>>(c, a);
+  else if (c.world <= 4)
+    allreduce_kernel<FUSE, false, 2, 4><<<nblocks, nthreads, 0, st>>>(c, a);
   else
-    allreduce_kernel<FUSE, false><<<nblocks, nthreads, 0, st>>>(c, a);
+    allreduce_kernel<FUSE, false, 1, FB_MAX_RANKS><<<nblocks, nthreads, 0, st>>>(c, a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -353,7 +396,7 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
                                  int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
                                  float* m, float* v, int nblocks, int nthreads, cudaStream_t stream) {
   if (!ctx_ok(ctx) || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || nthreads < 32 ||
-      nthreads > 1024 || channel < 0 || channel >= FB_FLAG_CHANNELS)
+      nthreads > 256 || channel < 0 || channel >= FB_FLAG_CHANNELS)
     return -1;
   if (use_mc && (ctx->mc_arena == nullptr || (op != FB_OP_SUM && op != FB_OP_AVG))) return -2;
   ArArgs a{};

@@ -2,6 +2,9 @@
 from . import init
 from .loss import (bce_loss, cross_entropy, cross_entropy_loss, l1_loss, log_softmax, mse_loss, nll_loss,
                    smooth_l1_loss, softmax)
+from .conv import AdaptiveAvgPool2d, AvgPool2d, Conv1d, Conv2d, MaxPool2d
+from .rnn import GRU, LSTM, RNN, GRUCell, LSTMCell, Nonlinearity, RNNCell
+from .transformer import MultiHeadAttention, PositionalEncoding, TransformerEncoderLayer
 from .modules import (ELU, GELU, BatchNorm1d, Dropout, Embedding, LayerNorm, LeakyReLU, Linear, LogSoftmax,
                       MeanPoolEmbedding, Module, ReLU, Sequential, Sigmoid, SiLU, Softmax, Tanh, tensor_io)
 
@@ -9,5 +12,7 @@ __all__ = [
     "Module", "Linear", "Sequential", "ReLU", "Sigmoid", "Tanh", "GELU", "SiLU", "LeakyReLU", "ELU", "Softmax",
     "LogSoftmax", "LayerNorm", "BatchNorm1d", "Dropout", "Embedding", "MeanPoolEmbedding", "mse_loss", "bce_loss",
     "l1_loss", "smooth_l1_loss", "cross_entropy_loss", "nll_loss", "cross_entropy", "softmax", "log_softmax",
-    "init", "tensor_io",
+    "init", "tensor_io", "Conv1d", "Conv2d", "MaxPool2d", "AvgPool2d", "AdaptiveAvgPool2d", "RNNCell", "LSTMCell",
+    "GRUCell", "RNN", "LSTM", "GRU", "Nonlinearity", "MultiHeadAttention", "TransformerEncoderLayer",
+    "PositionalEncoding",
 ]

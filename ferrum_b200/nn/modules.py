@@ -428,7 +428,14 @@ class Sequential(Module):
         while i < n:
             l = layers[i]
             nxt = layers[i + 1] if i + 1 < n else None
-            if fuse and type(l) is Linear and type(nxt) in _EPILOGUE_ACTS:
+            nxt2 = layers[i + 2] if i + 2 < n else None
+            if (fuse and type(l) is Linear and type(nxt) is GELU and type(nxt2) is LayerNorm
+                    and len(nxt2.normalized_shape) == 1 and nxt2.weight is not None
+                    and nxt2.normalized_shape[0] == l._out):
+                x = F.linear_act_layernorm(x, l.weight, l.bias, nxt2.weight, nxt2.bias, nxt2.eps, "gelu",
+                                           low_precision_weight(l.weight), l.grad_sink)
+                i += 3
+            elif fuse and type(l) is Linear and type(nxt) in _EPILOGUE_ACTS:
                 x = l._forward_act(x, _EPILOGUE_ACTS[type(nxt)])
                 i += 2
             elif fuse and type(l) is GELU and type(nxt) is LayerNorm and len(nxt.normalized_shape) == 1:

@@ -693,6 +693,78 @@ def layer_norm(x: torch.Tensor, gamma=None, beta=None, eps: float = 1e-5, pre_ac
     return y
 
 
+class _LinearActNormFn(Function):
+    """One autograd node for the block ``LayerNorm(act(x W^T + b))``.
+
+    Forward: GEMM with bias epilogue writes the pre-activation z once; the fused activation+LayerNorm kernel
+    reads z and writes y.  Backward: one kernel turns dy into dz and also yields d_gamma, d_beta and the column
+    sum of dz (= the bias gradient), then the dgrad and wgrad GEMMs run on dz.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, gamma, beta, eps, act, low, w_low, sink):
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if low:
+            xs = x2 if x2.dtype == torch.bfloat16 else raw_cast(x2.contiguous(), torch.bfloat16)
+            ws = w_low if w_low is not None else raw_cast(weight.detach().contiguous(), torch.bfloat16)
+        else:
+            xs, ws = _f32(x2), weight.detach()
+        z = _gemm_nt(xs, ws, bias=bias, act=None, low=low)
+        rows, cols = z.shape
+        y = torch.empty_like(z)
+        mean = torch.empty(rows, device=z.device, dtype=torch.float32)
+        rstd = torch.empty(rows, device=z.device, dtype=torch.float32)
+        g = gamma.detach().contiguous()
+        b = beta.detach().contiguous()
+        _lib.check(_lib.cuda().fb_layernorm_fwd(z.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
+                                                mean.data_ptr(), rstd.data_ptr(), rows, cols, eps, UNARY[act], _dt(z),
+                                                _stream()), "fb_layernorm_fwd")
+        ctx.save_for_backward(xs, ws, z, g, mean, rstd)
+        ctx.low, ctx.act, ctx.sink, ctx.weight_ref = low, act, sink, weight
+        ctx.x_dtype, ctx.lead, ctx.has_bias = x.dtype, lead, bias is not None
+        return y.reshape(*lead, cols)
+
+    @staticmethod
+    def backward(ctx, gy):
+        xs, ws, z, g, mean, rstd = ctx.saved_tensors
+        rows, cols = z.shape
+        low = ctx.low
+        gy2 = gy.reshape(rows, cols).contiguous()
+        if gy2.dtype != z.dtype:
+            gy2 = raw_cast(gy2, z.dtype)
+        lib = _lib.cuda()
+        dz = torch.empty_like(z)
+        nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
+        partial = torch.empty((max(nblk, 1), 3, cols), device=z.device, dtype=torch.float32)
+        stats = torch.zeros((3, cols), device=z.device, dtype=torch.float32)  # d_gamma, d_beta, colsum(dz)
+        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), z.data_ptr(), g.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                        dz.data_ptr(), partial.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
+                                        stats[2].data_ptr(), rows, cols, UNARY[ctx.act], _dt(z), nblk, _stream()),
+                   "fb_layernorm_bwd")
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = raw_cast(_gemm_nt(dz, ws.t(), low=low), ctx.x_dtype).reshape(*ctx.lead, ws.shape[1])
+        if ctx.needs_input_grad[1]:
+            if ctx.sink is not None:
+                buf, acc = ctx.sink.acquire(ctx.weight_ref)
+                _gemm_nt(dz.t(), xs.t(), low=low, out=buf, out_dtype=torch.float32, accumulate=acc)
+                ctx.sink.ready(ctx.weight_ref)
+            else:
+                gw = _gemm_nt(dz.t(), xs.t(), low=low, out_dtype=torch.float32)
+        gb = stats[2] if ctx.has_bias else None
+        return gx, gw, gb, stats[0], stats[1], None, None, None, None, None
+
+
+def linear_act_layernorm(x, weight, bias, gamma, beta, eps: float = 1e-5, act: str = "gelu", w_low=None,
+                         sink: GradSink | None = None):
+    """``LayerNorm(act(x @ weight^T + bias)) * gamma + beta`` as one fused block (CUDA); composed ops on CPU."""
+    if _native(x) and gamma is not None and beta is not None:
+        return _LinearActNormFn.apply(x, weight, bias, gamma, beta, float(eps), act, config.low_precision_active(),
+                                      w_low, sink)
+    return layer_norm(linear(x, weight, bias, None, w_low, sink), gamma, beta, eps, act)
+
+
 class _BatchNormFn(Function):
     @staticmethod
     def forward(ctx, x, gamma, beta, running_mean, running_var, eps, momentum, training):

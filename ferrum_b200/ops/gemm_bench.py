@@ -1,0 +1,78 @@
+"""Time the tcgen05 GEMM on one shape (also the small case used for kernel profiles).
+
+    python -m ferrum_b200.ops.gemm_bench --m 8192 --n 4096 --k 4096 --layout nt --iters 20 [--cublas]
+
+``--layout``: ``nt`` forward (A, B K-major), ``nn`` dgrad (B MN-major), ``tn`` wgrad (both MN-major, fp32 out).
+Prints one JSON line: median CUDA-event time after warm-up with an L2 flush between iterations, TFLOP/s, and the
+fraction of the measured cuBLAS bf16 peak when ``MEASURED_PEAKS.json`` is present at the repository root.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--act", default=None)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
+    a = ap.parse_args()
+
+    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.utils.runtime import check_status
+
+    M, N, K = a.m, a.n, a.k
+    a_mn = a.layout == "tn"
+    b_mn = a.layout in ("nn", "tn")
+    A = torch.randn(K, M, device="cuda").to(torch.bfloat16).t() if a_mn else torch.randn(M, K, device="cuda").to(
+        torch.bfloat16)
+    B = torch.randn(K, N, device="cuda").to(torch.bfloat16).t() if b_mn else torch.randn(N, K, device="cuda").to(
+        torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.layout == "tn" else torch.bfloat16)
+    bias = torch.randn(N, device="cuda") if a.bias else None
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timeit(fn):
+        for _ in range(a.warmup):
+            fn()
+        ts = []
+        for _ in range(a.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out))
+    check_status()
+    flops = 2.0 * M * N * K
+    res = {"kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+           "tflops": flops / ms / 1e9}
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                         "MEASURED_PEAKS.json")
+    if os.path.exists(peaks):
+        pk = json.load(open(peaks))
+        res["frac_of_measured_bf16_burst"] = res["tflops"] / pk["bf16_tflops"]
+    if a.cublas:
+        Ac, Bc = A.contiguous(), B.contiguous()
+        cms = timeit(lambda: torch.matmul(Ac, Bc.t()))
+        res["cublas_ms"], res["cublas_tflops"] = cms, flops / cms / 1e9
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

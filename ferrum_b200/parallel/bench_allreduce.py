@@ -21,8 +21,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=float, default=1024.0)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--blocks", type=int, default=32)
-    ap.add_argument("--threads", type=int, default=512)
+    ap.add_argument("--blocks", type=int, default=64)
+    ap.add_argument("--threads", type=int, default=256)
     ap.add_argument("--out", default="")
     args = ap.parse_args()
 

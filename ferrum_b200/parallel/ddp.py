@@ -109,8 +109,8 @@ class DistributedDataParallel(Module, GradSink):
         self._find_unused = False
         self._built = False
         self._opt = None
-        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "24"))
-        self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "512"))
+        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "48"))
+        self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
         if optimizer is not None:
             self.fuse_optimizer(optimizer)
 
@@ -237,8 +237,9 @@ class DistributedDataParallel(Module, GradSink):
         self._comm_stream = torch.cuda.Stream(device=dev, priority=-1)
         self._ready_event = torch.cuda.Event()
         self._done_event = torch.cuda.Event()
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        self._gemm_limit = max(sms - self._comm_blocks, sms // 2)
+        # A reduction block (256 threads, no shared memory) fits on an SM beside a persistent GEMM CTA, so the
+        # GEMM grid is not shrunk by default; FERRUM_GEMM_CTA_LIMIT reserves SMs for experiments.
+        self._gemm_limit = int(os.environ.get("FERRUM_GEMM_CTA_LIMIT", "0"))
 
     def _refresh_shadow(self) -> None:
         """Recompute every bf16 weight copy from the fp32 arena with one cast kernel."""

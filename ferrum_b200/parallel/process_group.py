@@ -111,7 +111,7 @@ class ProcessGroup:
         return torch.cuda.current_stream().cuda_stream
 
     def _blocks(self, nbytes: int) -> int:
-        return max(1, min(32, nbytes // (256 * 1024) + 1))
+        return max(1, min(64, nbytes // (128 * 1024) + 1))
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, tensor, op: ReduceOp = ReduceOp.Sum):
@@ -154,7 +154,7 @@ class ProcessGroup:
                 stage[cnt:].zero_()  # the padding is reduced too but never copied back
             e = arena.next_epoch(0)
             _lib.check(lib.fb_dist_allreduce(arena.ctx, 0, use_mc, 0, e, off, 0, -1, padded, _OP_CODE[op], scale,
-                                             None, None, None, None, self._blocks(padded * 4), 512, self._stream()),
+                                             None, None, None, None, self._blocks(padded * 4), 256, self._stream()),
                        "fb_dist_allreduce")
             work[lo:lo + cnt].copy_(stage[:cnt])
         if work.data_ptr() != flat.data_ptr():

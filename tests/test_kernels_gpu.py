@@ -380,3 +380,36 @@ def test_linear_fwd_bwd(low):
     assert torch.allclose(x1.grad, x2.grad, atol=tol * 2, rtol=tol)
     assert torch.allclose(w1.grad, w2.grad, atol=tol * 8, rtol=tol)
     assert torch.allclose(b1.grad, b2.grad, atol=tol * 8, rtol=tol)
+
+
+@pytest.mark.parametrize("low", [False, True])
+def test_fused_linear_gelu_layernorm_block(low):
+    """Sequential's fused Linear-GELU-LayerNorm node equals the composition of the three layers."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    torch.manual_seed(11)
+    dev = fb.Device.Cuda(0)
+    blk = nn.Sequential(nn.Linear(136, 264, device=dev), nn.GELU(), nn.LayerNorm([264], device=dev))
+    with torch.no_grad():
+        blk[2].weight.uniform_(0.5, 1.5)
+        blk[2].bias.normal_()
+    x = torch.randn(200, 136, device="cuda")
+    x1 = x.clone().requires_grad_(True)
+    with fb.autocast(enabled=low):
+        y = blk(x1)
+    x2 = x.clone().requires_grad_(True)
+    ref = torch.nn.functional.layer_norm(
+        torch.nn.functional.gelu(torch.nn.functional.linear(x2, blk[0].weight, blk[0].bias), approximate="tanh"),
+        (264,), blk[2].weight, blk[2].bias, 1e-5)
+    tol = 6e-2 if low else 2e-4
+    assert torch.allclose(y.float(), ref, atol=tol, rtol=tol)
+    g = torch.randn_like(ref)
+    y.backward(g.to(y.dtype))
+    mine = [x1.grad] + [p.grad.clone() for p in blk.torch_parameters()]
+    blk.zero_grad()
+    ref.backward(g)
+    theirs = [x2.grad] + [p.grad for p in blk.torch_parameters()]
+    for a, b in zip(mine, theirs):
+        scale = max(1.0, b.abs().max().item())
+        assert (a.float() - b).abs().max().item() < (0.15 if low else 2e-3) * scale
