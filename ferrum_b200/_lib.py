@@ -97,6 +97,8 @@ _CUDA_SIGS = {
     # gemm
     "fb_gemm_bf16_supported": (I, [P, P, LL, LL]),
     "fb_gemm_bf16": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
+    "fb_gemm_bf16_2cta": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
+    "fb_gemm_bf16_2cta_pairs": (I, []),
     "fb_gemm_f32_simt": (I, [P, P, P, P, I, I, I, LL, LL, LL, LL, LL, I, I, I, LL, LL, LL, P]),
     # elementwise
     "fb_unary_fwd": (I, [P, P, LL, I, F, F, I, P]),
@@ -111,7 +113,7 @@ _CUDA_SIGS = {
     "fb_colsum": (I, [P, P, LL, LL, I, I, P]),
     # norms
     "fb_layernorm_fwd": (I, [P, P, P, P, P, P, LL, I, F, I, I, P]),
-    "fb_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, I, P]),
+    "fb_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, LL, I, I, I, I, I, P]),
     "fb_layernorm_bwd_blocks": (I, [LL, I]),
     "fb_batchnorm_fwd": (I, [P, P, P, P, P, P, P, P, LL, I, F, F, I, P]),
     "fb_batchnorm_bwd": (I, [P, P, P, P, P, P, P, P, LL, I, P]),
@@ -164,7 +166,7 @@ class _CountingLib:
     bound on kernel launches; ``launch_count()`` reads it.
     """
 
-    _NO_COUNT = ("fb_rt_", "fb_reduce_scratch_elems", "fb_layernorm_bwd_blocks", "fb_gemm_bf16_supported",
+    _NO_COUNT = ("fb_rt_", "fb_reduce_scratch_elems", "fb_layernorm_bwd_blocks", "fb_gemm_bf16_supported", "fb_gemm_bf16_2cta_pairs",
                  "fb_dist_query_")
 
     def __init__(self, lib):

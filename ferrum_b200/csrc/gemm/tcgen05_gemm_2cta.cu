@@ -1,0 +1,437 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2 computes a 256 x 256 output tile
+// per cluster of two CTAs (two SMs).  Each CTA stages only ITS half of the operands
+// — 128 rows of A and 128 rows of B per 64-deep k-block, 32 KB — so a stage costs a
+// third less L2 -> shared-memory traffic per SM than the single-CTA kernel's
+// 128 x 256 tile and six stages fit where that kernel has four; both matter because
+// the single-CTA kernel is limited by operand-fetch latency, not by the tensor pipe.
+// The accumulator of a CTA (its 128 rows x 256 columns, fp32) lives in that CTA's
+// tensor memory, double-buffered (2 x 256 of the 512 columns).
+//
+// Same contract and operand layouts as fb_gemm_bf16 (tcgen05_gemm.cu); the reference
+// loops it replaces are ferrum-core/src/tensor.rs:2487-2558.
+//
+// Roles (192 threads per CTA):
+//   warp 0      TMA producer of this CTA's halves; the byte counts of BOTH CTAs land
+//               on the leader's "full" mbarrier (plain cta_group::2 loads, no multicast)
+//   warp 1      TMEM allocation (both CTAs); in the leader (cluster rank 0) one lane
+//               issues every MMA and commits to the mbarriers of both CTAs
+//   warps 2..5  epilogue of this CTA's 128 rows; "accumulator drained" is signalled
+//               to the leader's mbarrier from both CTAs
+// Every wait is bounded; the two cluster barriers (after set-up, before exit) are
+// reached on every path, including the abort path.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../common/ptx.cuh"
+#include "../common/status.h"
+#include "../include/ferrum_kernels.h"
+
+namespace fb {
+namespace {
+
+constexpr int kBM = 128;       // rows per CTA; the pair covers 256
+constexpr int kBN = 256;       // columns per pair; each CTA stages 128 of them
+constexpr int kBK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kStages = 6;
+constexpr int kGroupM = 8;     // pair-tiles (256 rows) per rasterisation group
+constexpr int kABytes = kBM * kBK * 2;          // 16 KB
+constexpr int kBBytes = (kBN / 2) * kBK * 2;    // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;  // 32 KB per CTA
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kTmemCols = 512;
+
+struct Args2 {
+  void* out;
+  const float* bias;
+  int M, N, K;
+  long long ldc;
+  int a_mn_major, b_mn_major;
+  int out_bf16;
+  int act;
+  int beta;
+  int32_t* status;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ float apply_act2(float x, int act) {
+  switch (act) {
+    case FB_ACT_RELU:
+      return fmaxf(x, 0.f);
+    case FB_ACT_GELU: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+      return 0.5f * x * (1.f + t);
+    }
+    case FB_ACT_SILU:
+      return x / (1.f + __expf(-x));
+    case FB_ACT_TANH: {
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+      return t;
+    }
+    case FB_ACT_SIGMOID:
+      return 1.f / (1.f + __expf(-x));
+    default:
+      return x;
+  }
+}
+
+__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int per_group = kGroupM * num_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int gsize = min(num_m - first_m, kGroupM);
+  const int r = t - g * per_group;
+  m_blk = first_m + (r % gsize);
+  n_blk = r / gsize;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const Args2 p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + kStages * kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader only
+  uint64_t* empty_bar = full_bar + kStages;                     // one set per CTA
+  uint64_t* tmem_full = empty_bar + kStages;                    // one set per CTA
+  uint64_t* tmem_empty = tmem_full + 2;                         // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int num_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+  const int num_n = (p.N + kBN - 1) / kBN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx; bytes of both CTAs are counted on it
+      ptx::mbar_init(&empty_bar[s], 1);  // one commit arrival per CTA
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&tmem_full[a], 1);
+      ptx::mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each of the two CTAs
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tma_a);
+    ptx::prefetch_tensormap(&tma_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_2cta(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_2cta();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // the peer's mbarriers must exist before anything arrives on them remotely
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords2(t, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * 2 * kBM + static_cast<int>(rank) * kBM;        // this CTA's 128 rows of A
+        const int n0 = n_blk * kBN + static_cast<int>(rank) * (kBN / 2);      // this CTA's 128 rows of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
+            report_status(p.status, kStatusGemmTimeout, 11, blockIdx.x, stage);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+          const uint32_t bar = ptx::smem_u32(&full_bar[stage]) & ptx::kPeerBitMask;  // the leader's barrier
+          const int k0 = kb * kBK;
+          if (p.a_mn_major) {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d_2cta(sa + c * (kBK * 128), &tma_a, bar, m0 + c * 64, k0);
+          } else {
+            ptx::tma_load_2d_2cta(sa, &tma_a, bar, k0, m0);
+          }
+          if (p.b_mn_major) {
+#pragma unroll
+            for (int c = 0; c < (kBN / 2) / 64; ++c)
+              ptx::tma_load_2d_2cta(sb + c * (kBK * 128), &tma_b, bar, n0 + c * 64, k0);
+          } else {
+            ptx::tma_load_2d_2cta(sb, &tma_b, bar, k0, n0);
+          }
+          ++issued;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before shared memory is released
+        const uint64_t t0 = ptx::globaltimer();
+        while (issued > 0 && ptx::globaltimer() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      const uint32_t idesc = ptx::make_idesc(1u, 2 * kBM, kBN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? kBK * 128 : 16;
+      const uint32_t b_lbo = p.b_mn_major ? kBK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
+          report_status(p.status, kStatusGemmTimeout, 12, blockIdx.x, acc);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
+            report_status(p.status, kStatusGemmTimeout, 13, blockIdx.x, stage);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit_2cta(&empty_bar[stage], 0x3);  // frees the slot in both CTAs
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit_2cta(&tmem_full[acc], 0x3);  // accumulator complete -> both epilogues
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int m_blk, n_blk;
+      tile_coords2(t, num_m, num_n, m_blk, n_blk);
+      const int row = m_blk * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+      const int n0 = n_blk * kBN;
+      const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) report_status(p.status, kStatusGemmTimeout, 14, blockIdx.x, acc);
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int j = 0; j < kBN / 32; ++j) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(taddr + j * 32, r);
+        ptx::tmem_wait_ld();
+        const int col0 = n0 + j * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+          }
+          if (p.act != FB_ACT_NONE) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = apply_act2(v[i], p.act);
+          }
+          const bool full = (col0 + 32 <= p.N) && vec_ok;
+          if (p.out_bf16) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+              uint4* o4 = reinterpret_cast<uint4*>(o);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
+                  w[h] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
+            }
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+              float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 x = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                if (p.beta) {
+                  const float4 old = o4[q];
+                  x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                }
+                o4[q] = x;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      // "drained" goes to the leader's barrier from both CTAs
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::smem_u32(&tmem_empty[acc]) & ptx::kPeerBitMask);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // Teardown: nobody leaves while the peer may still read this CTA's shared memory (the leader's MMAs
+  // read both) or arrive on its mbarriers.
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_2cta(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn2 encode_fn2() {
+  static EncodeTiledFn2 fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn2>(sym);
+  }
+  return fn;
+}
+
+bool make_map2(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+  EncodeTiledFn2 enc = encode_fn2();
+  if (enc == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Number of CTA pairs that can be resident at once (0 if cluster launch is unavailable).
+int max_pairs() {
+  static int n = -1;
+  if (n < 0) {
+    n = 0;
+    if (cudaFuncSetAttribute(gemm_bf16_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return n;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_2cta_kernel, &cfg) == cudaSuccess) n = clusters;
+    else cudaGetLastError();
+  }
+  return n;
+}
+
+}  // namespace
+}  // namespace fb
+
+extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs(); }
+
+// Same arguments as fb_gemm_bf16.  Returns -3 when CTA pairs cannot be launched on this device.
+extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, const float* bias, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                 int out_bf16, int act, int beta, int max_ctas, int32_t* status,
+                                 cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int pairs_avail = max_pairs();
+  if (pairs_avail <= 0) return -3;
+  CUtensorMap ma, mb;
+  bool ok = a_mn_major ? make_map2(&ma, a, M, K, lda, 64) : make_map2(&ma, a, K, M, lda, kBM);
+  if (!ok) return -2;
+  ok = b_mn_major ? make_map2(&mb, b, N, K, ldb, 64) : make_map2(&mb, b, K, N, ldb, kBN / 2);
+  if (!ok) return -2;
+  Args2 args;
+  args.out = out;
+  args.bias = bias;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = out_bf16;
+  args.act = act;
+  args.beta = beta;
+  args.status = status;
+  args.timeout_ns = 2000000000ull;
+  const int num_tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
+  int pairs = pairs_avail;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (num_tiles < pairs) pairs = num_tiles;
+  gemm_bf16_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(ma, mb, args);
+  return static_cast<int>(cudaGetLastError());
+}

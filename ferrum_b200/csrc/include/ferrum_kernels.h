@@ -83,10 +83,10 @@ int fb_colsum(const void* x, float* out, long long rows, long long cols, int dty
 // pre_act: FB_ACT_NONE or FB_ACT_GELU applied to x before normalising (fused block).
 int fb_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
                      long long rows, int cols, float eps, int pre_act, int dtype, cudaStream_t stream);
-// dgamma/dbeta/dbias_pre are accumulated from a zeroed [cols] buffer via partial[nblk, 3, cols].
+// stats = [3][cols]: d_gamma, d_beta, column sum of dx (accumulated into); partial = [nblk][3][cols] workspace.
 int fb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
-                     void* dx, float* partial, float* dgamma, float* dbeta, float* dcolsum, long long rows,
-                     int cols, int pre_act, int dtype, int nblk, cudaStream_t stream);
+                     void* dx, float* partial, float* stats, long long rows, int cols, int pre_act, int dtype,
+                     int nblk, int want_colsum, cudaStream_t stream);
 int fb_layernorm_bwd_blocks(long long rows, int cols);
 int fb_batchnorm_fwd(const float* x, const float* gamma, const float* beta, float* y, float* save_mean,
                      float* save_rstd, float* running_mean, float* running_var, long long rows, int cols,

@@ -660,13 +660,14 @@ class _LayerNormFn(Function):
         dx = torch.empty_like(x2)
         nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
         partial = torch.empty((max(nblk, 1), 3, cols), device=x2.device, dtype=torch.float32)
-        dgamma = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.has_gamma else None
-        dbeta = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.has_beta else None
-        dcol = torch.zeros(cols, device=x2.device, dtype=torch.float32) if ctx.want_colsum else None
+        stats = torch.zeros((3, cols), device=x2.device, dtype=torch.float32)
         _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), x2.data_ptr(), _ptr(g), mean.data_ptr(), rstd.data_ptr(),
-                                        dx.data_ptr(), partial.data_ptr(), _ptr(dgamma), _ptr(dbeta), _ptr(dcol),
-                                        rows, cols, UNARY[ctx.pre_act or "none"], _dt(x2), nblk, _stream()),
-                   "fb_layernorm_bwd")
+                                        dx.data_ptr(), partial.data_ptr(), stats.data_ptr(), rows, cols,
+                                        UNARY[ctx.pre_act or "none"], _dt(x2), nblk, 1 if ctx.want_colsum else 0,
+                                        _stream()), "fb_layernorm_bwd")
+        dgamma = stats[0] if ctx.has_gamma else None
+        dbeta = stats[1] if ctx.has_beta else None
+        dcol = stats[2] if ctx.want_colsum else None
         ctx.colsum = dcol
         return dx.reshape(ctx.shape), dgamma, dbeta, None, None, None
 
@@ -739,9 +740,8 @@ class _LinearActNormFn(Function):
         partial = torch.empty((max(nblk, 1), 3, cols), device=z.device, dtype=torch.float32)
         stats = torch.zeros((3, cols), device=z.device, dtype=torch.float32)  # d_gamma, d_beta, colsum(dz)
         _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), z.data_ptr(), g.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
-                                        dz.data_ptr(), partial.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
-                                        stats[2].data_ptr(), rows, cols, UNARY[ctx.act], _dt(z), nblk, _stream()),
-                   "fb_layernorm_bwd")
+                                        dz.data_ptr(), partial.data_ptr(), stats.data_ptr(), rows, cols,
+                                        UNARY[ctx.act], _dt(z), nblk, 1, _stream()), "fb_layernorm_bwd")
         gx = gw = None
         if ctx.needs_input_grad[0]:
             gx = raw_cast(_gemm_nt(dz, ws.t(), low=low), ctx.x_dtype).reshape(*ctx.lead, ws.shape[1])

@@ -9,6 +9,8 @@ layouts are described by flags instead of transposed copies.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _lib
@@ -17,6 +19,15 @@ from ..utils import runtime as _rt
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "silu": 3, "tanh": 4, "sigmoid": 5}
 
 _max_ctas = 0  # 0 = all SMs; the DDP engine lowers this to leave SMs for the comm kernel
+# CTA-pair kernel (tcgen05 cta_group::2, 256x256 tile per two SMs) for large problems; "0" selects the
+# single-CTA kernel everywhere.
+_use_2cta = os.environ.get("FERRUM_GEMM_2CTA", "0") == "1"
+
+
+def set_gemm_2cta(flag: bool) -> None:
+    """Choose between the CTA-pair kernel (large shapes) and the single-CTA kernel."""
+    global _use_2cta
+    _use_2cta = bool(flag)
 
 
 def set_gemm_cta_limit(n: int) -> None:
@@ -73,9 +84,14 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     if accumulate:
         assert out.dtype == torch.float32, "accumulate needs an fp32 output"
     lib = _lib.cuda()
-    rc = lib.fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
-                          M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
-                          ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
+    fn = lib.fb_gemm_bf16_2cta if (_use_2cta and M >= 512 and N >= 256) else lib.fb_gemm_bf16
+    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+            M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
+            ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
+    if rc == -3:  # CTA pairs cannot be scheduled on this device
+        rc = lib.fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+                              M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
+                              ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
     _lib.check(rc, "fb_gemm_bf16")
     return out
 

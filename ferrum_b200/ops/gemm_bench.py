@@ -25,10 +25,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--act", default=None)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--two-cta", action="store_true", help="use the CTA-pair (cta_group::2) kernel")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
     a = ap.parse_args()
 
+    from ferrum_b200.ops import gemm as _g
     from ferrum_b200.ops.gemm import gemm_bf16
+
+    _g.set_gemm_2cta(a.two_cta)
     from ferrum_b200.utils.runtime import check_status
 
     M, N, K = a.m, a.n, a.k
@@ -60,8 +64,13 @@ def main():
     ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out))
     check_status()
     flops = 2.0 * M * N * K
-    res = {"kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+    if a.two_cta:
+        ref = (A[:256].float() @ B.float().t())
+        res_err = (out[:256].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+    res = {"kernel": "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
            "tflops": flops / ms / 1e9}
+    if a.two_cta:
+        res["rel_err_first_rows"] = res_err
     peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                          "MEASURED_PEAKS.json")
     if os.path.exists(peaks):

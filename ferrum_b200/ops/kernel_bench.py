@@ -1,0 +1,168 @@
+"""Time the memory-bound kernels on benchmark-sized inputs and report achieved bandwidth against the roofline.
+
+    python -m ferrum_b200.ops.kernel_bench [--only NAME[,NAME...]] [--iters 20] [--small] [--out FILE]
+
+Each case launches one kernel entry point on inputs larger than the L2 (so DRAM figures mean something), is
+timed with CUDA events after warm-up (median), and reports ``GB/s = algorithmic bytes / time`` and the fraction of
+the measured HBM copy bandwidth (``MEASURED_PEAKS.json`` at the repository root; 6450 GB/s otherwise).
+``--small`` shrinks every case to a few hundred MB for profiler captures.  One JSON line per case.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def _cases(small: bool):
+    from ferrum_b200 import _lib, optim
+    from ferrum_b200.ops import functional as F
+
+    R = 4096 if small else 8192
+    C = 4096
+    dev = "cuda"
+    bf = torch.bfloat16
+    x32 = torch.randn(R, C, device=dev)
+    xb = x32.to(bf)
+    gb = torch.randn(R, C, device=dev).to(bf)
+    gamma = torch.rand(C, device=dev) + 0.5
+    beta = torch.randn(C, device=dev)
+    cases = {}
+
+    def case(name, fn, nbytes, note=""):
+        cases[name] = (fn, nbytes, note)
+
+    n = R * C
+    case("unary_gelu_fwd_bf16", lambda: F.raw_unary(xb, "gelu"), n * 4, "K2")
+    case("unary_gelu_bwd_bf16", lambda: F.raw_unary_bwd(gb, xb, "gelu"), n * 6, "K2 bwd")
+    case("unary_relu_fwd_f32", lambda: F.raw_unary(x32, "relu"), n * 8, "K2")
+    case("scalar_affine_f32", lambda: F.raw_unary(x32, "affine", 2.0, 1.0), n * 8, "K3 / Normalize")
+    y32 = torch.randn(R, C, device=dev)
+    case("binary_add_f32", lambda: F.raw_binary(x32, y32, "add"), n * 12, "K1")
+    case("binary_bcast_row_f32", lambda: F.raw_binary(x32, beta, "add"), n * 8, "K1 [B,F]+[F]")
+    case("cast_f32_to_bf16", lambda: F.raw_cast(x32, bf), n * 6, "cast")
+    case("transpose_bf16", lambda: F.transpose_2d(xb), n * 4, "K5t")
+    case("reduce_sum_all_f32", lambda: F.raw_reduce(x32, "sum", None), n * 4, "K4 full")
+    case("reduce_sum_rows_f32", lambda: F.raw_reduce(x32, "sum", 1), n * 4, "K4 row")
+    case("reduce_sum_cols_f32", lambda: F.raw_reduce(x32, "sum", 0), n * 4, "K4 column")
+    case("argmax_rows_f32", lambda: F.arg_reduce(x32, True, 1), n * 4, "K4 arg")
+    case("colsum_bf16", lambda: F.raw_colsum(xb), n * 2, "bias gradient")
+
+    lib = _lib.cuda()
+    st = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    yb = torch.empty_like(xb)
+    mean = torch.empty(R, device=dev)
+    rstd = torch.empty(R, device=dev)
+
+    def ln_fwd():
+        lib.fb_layernorm_fwd(xb.data_ptr(), gamma.data_ptr(), beta.data_ptr(), yb.data_ptr(), mean.data_ptr(),
+                             rstd.data_ptr(), R, C, 1e-5, 2, 3, st())
+
+    ln_fwd()
+    nblk = lib.fb_layernorm_bwd_blocks(R, C)
+    partial = torch.empty(max(nblk, 1), 3, C, device=dev)
+    stats = torch.zeros(3, C, device=dev)
+    dxb = torch.empty_like(xb)
+
+    def ln_bwd():
+        lib.fb_layernorm_bwd(gb.data_ptr(), xb.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                             dxb.data_ptr(), partial.data_ptr(), stats.data_ptr(), R, C, 2, 3, nblk, 1, st())
+
+    case("layernorm_gelu_fwd_bf16", ln_fwd, n * 4, "K7 fused GELU+LN")
+    case("layernorm_gelu_bwd_bf16", ln_bwd, n * 6, "K7 bwd + dgamma/dbeta/colsum")
+
+    Cs = 1000
+    lg = torch.randn(R, Cs, device=dev).to(bf)
+    labels = torch.randint(0, Cs, (R,), device=dev)
+    rl = torch.empty(R, device=dev)
+    dl = torch.empty_like(lg)
+    case("softmax_fwd_bf16_1000", lambda: F.softmax(lg, -1), R * Cs * 4, "K6")
+    case("cross_entropy_fused_bf16_1000",
+         lambda: lib.fb_ce_fwd_bwd(lg.data_ptr(), labels.data_ptr(), rl.data_ptr(), dl.data_ptr(), R, Cs, 1.0 / R, 3, 3,
+                                   st()), R * Cs * 4, "K6b loss + dlogits")
+    p32 = torch.rand(R, C, device=dev) * 0.9 + 0.05
+    t32 = torch.rand(R, C, device=dev)
+    case("mse_loss_fwd_f32", lambda: F.elementwise_loss(p32, t32, "mse"), n * 8, "K11")
+    bx = torch.randn(R, 1024, device=dev)
+    bg_, bb_ = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
+    rm, rv = torch.zeros(1024, device=dev), torch.ones(1024, device=dev)
+    case("batchnorm_fwd_f32", lambda: F.batch_norm(bx, bg_, bb_, rm, rv, True), R * 1024 * 4 * 4, "K8 (3 reads + 1 write)")
+    case("dropout_fwd_bf16", lambda: F.dropout(xb, 0.1, True, seed=1), n * 5, "K9 (+1 B mask)")
+
+    V, D, S, Bt = 50000, 1024, 256, 128 if small else 512
+    w = torch.randn(V, D, device=dev)
+    from ferrum_b200.data import zipf_indices
+
+    idx = torch.from_numpy(zipf_indices(V, 1.1, Bt * S, seed=0)).to(dev).reshape(Bt, S)
+    case("embedding_meanpool_fwd", lambda: F.embedding_mean_pool(w, idx, bf), Bt * S * D * 4, "K10 gather+pool")
+    gout = torch.randn(Bt, D, device=dev).to(bf)
+    sidx, perm = torch.sort(idx.reshape(-1), stable=True)
+    dw = torch.zeros(V, D, device=dev)
+    case("embedding_scatter_add_bwd",
+         lambda: lib.fb_embedding_bwd_sorted(gout.data_ptr(), sidx.data_ptr(), perm.data_ptr(), dw.data_ptr(),
+                                             Bt * S, D, S, 1.0 / S, -1, 3, st()), Bt * S * D * 2, "K10 bwd")
+    gi = torch.randint(0, R, (R,), device=dev)
+    case("gather_rows_f32", lambda: F.gather_rows(x32, gi), n * 8, "K18 collate")
+
+    P = (32 << 20) if small else (125 << 20)
+    pp = torch.randn(P, device=dev, requires_grad=True)
+    pp.grad = torch.randn(P, device=dev) * 1e-2
+    adam = optim.Adam([pp], optim.AdamConfig(lr=3e-4))
+    adam.step()
+    case("adam_multi_tensor", adam.step, P * 28, "K12 (g,p,m,v read; p,m,v write)")
+    sgd = optim.SGD([pp], optim.SGDConfig(lr=0.1, momentum=0.9))
+    sgd.step()
+    case("sgd_momentum_multi_tensor", sgd.step, P * 20, "K12")
+    gsc = optim.GradScaler.with_scale(2.0)
+    case("amp_unscale_check", lambda: gsc.unscale_gradients([pp]), P * 8, "K17")
+    case("amp_clip_grad_norm", lambda: optim.clip_grad_norm([pp], 1e9), P * 4, "K17 (sum of squares pass)")
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--out", default="")
+    a = ap.parse_args()
+    from ferrum_b200.utils.profiler import measured_peaks
+    from ferrum_b200.utils.runtime import check_status
+
+    pk = measured_peaks()
+    hbm = pk["hbm_gbs"] if pk else 6450.0
+    cases = _cases(a.small)
+    only = [s for s in a.only.split(",") if s]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    results = []
+    for name, (fn, nbytes, note) in cases.items():
+        if only and name not in only:
+            continue
+        for _ in range(a.warmup):
+            fn()
+        ts = []
+        for _ in range(a.iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        ms = ts[len(ts) // 2]
+        res = {"kernel": name, "row": note, "us": 1e3 * ms, "algorithmic_MB": nbytes / 1e6,
+               "GBps": nbytes / ms / 1e6, "frac_of_measured_hbm" if pk else "frac_of_fallback_hbm":
+               nbytes / ms / 1e6 / hbm}
+        results.append(res)
+        print(json.dumps(res), flush=True)
+    check_status()
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump(results, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,1 +1,5 @@
-"""Runtime helpers, profiler, logging."""
+"""Runtime helpers, profiler, metrics."""
+from . import profiler, runtime
+from .profiler import StepTimer, profile
+
+__all__ = ["runtime", "profiler", "profile", "StepTimer"]

@@ -97,3 +97,32 @@ def test_gemm_f32_batched():
     b = torch.randn(3, 11, 29, device="cuda")
     out = gemm_f32(a, b)
     assert torch.allclose(out, a @ b.transpose(1, 2), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 512, 256), (1024, 1000, 520), (776, 264, 1000),
+                                   (2048, 4096, 1024)])
+def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn, M, N, K):
+    """cta_group::2 kernel (256x256 tile per CTA pair) against the fp32 reference, all operand layouts."""
+    from ferrum_b200.ops import gemm as g
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(M + N + K + a_mn * 2 + b_mn)
+    a = _mk(M, K, a_mn, 0.5)
+    b = _mk(N, K, b_mn, 0.5)
+    bias = torch.randn(N, device="cuda")
+    g.set_gemm_2cta(True)
+    try:
+        out = g.gemm_bf16(a, b, bias=bias, out_dtype=torch.float32)
+        acc = torch.ones(M, N, device="cuda")
+        g.gemm_bf16(a, b, out=acc, accumulate=True)
+        outb = g.gemm_bf16(a, b, act="relu")
+        check_status()
+    finally:
+        g.set_gemm_2cta(False)
+    ref = _ref(a, b, bias, None)
+    tol = 2e-3 * (K ** 0.5) * 0.25 + 1e-3
+    assert (out - ref).abs().max().item() < tol
+    assert (acc - (1.0 + _ref(a, b, None, None))).abs().max().item() < tol
+    refb = torch.relu(_ref(a, b, None, None))
+    assert (outb.float() - refb).abs().max().item() < 3e-2 * max(1.0, refb.abs().max().item())
