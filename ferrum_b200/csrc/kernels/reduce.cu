@@ -214,8 +214,12 @@ using namespace fb;
 // Number of scratch floats fb_reduce wants for this problem (0 = single pass).
 extern "C" long long fb_reduce_scratch_elems(long long outer, long long R, long long inner) {
   const long long outs = outer * inner;
-  if (outs >= 1024 || R < 4096) return 0;
-  long long splits = (static_cast<long long>(sm_count()) * 4 + outs - 1) / outs;
+  if (R < 4096 || outs <= 0) return 0;
+  // blocks a single pass would launch: one per row (inner == 1) or one per 256 columns
+  const long long blocks = inner == 1 ? outs : (outs + 255) / 256;
+  const long long target = static_cast<long long>(sm_count()) * 4;
+  if (blocks >= target / 2) return 0;
+  long long splits = (target + blocks - 1) / blocks;
   const long long max_splits = (R + 1023) / 1024;
   if (splits > max_splits) splits = max_splits;
   if (splits <= 1) return 0;
@@ -294,4 +298,71 @@ extern "C" int fb_colsum(const void* x, float* out, long long rows, long long co
     return -1;
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+// ----------------------------------------------------------------------------
+// Allocation-free variant (declared in reduce_noalloc.h).
+#include <cstdio>
+#include <mutex>
+
+#include "reduce_noalloc.h"
+
+namespace {
+
+// Workspace of fb_reduce_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the device address it yields is what kernels receive.
+static __device__ __align__(256) float g_reduce_noalloc_scratch[FB_REDUCE_NOALLOC_MAX_FLOATS];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+void noalloc_err(char* err, int err_len, const char* msg) {
+  if (err != nullptr && err_len > 0) std::snprintf(err, static_cast<size_t>(err_len), "%s", msg);
+}
+
+}  // namespace
+
+extern "C" int fb_reduce_noalloc(const float* x, float* out, long long outer, long long R, long long inner,
+                                 int op, cudaStream_t stream, char* err, int err_len) {
+  if (err != nullptr && err_len > 0) err[0] = '\0';
+  if (outer <= 0 || inner <= 0) return 0;
+  if (R <= 0) {
+    noalloc_err(err, err_len, "fb_reduce_noalloc: reduced extent R must be positive");
+    return -1;
+  }
+  const long long want = fb_reduce_scratch_elems(outer, R, inner);
+  if (want > FB_REDUCE_NOALLOC_MAX_FLOATS) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg),
+                  "fb_reduce_noalloc: this shape needs %lld partial sums, the built-in workspace holds %d; "
+                  "use fb_reduce with a caller-provided workspace",
+                  want, FB_REDUCE_NOALLOC_MAX_FLOATS);
+    noalloc_err(err, err_len, msg);
+    return FB_REDUCE_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    noalloc_err(err, err_len, "fb_reduce_noalloc: device ordinal out of range");
+    return -1;
+  }
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      // once per device, with that device current
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_reduce_noalloc_scratch);
+      if (e != cudaSuccess) {
+        noalloc_err(err, err_len, "fb_reduce_noalloc: cudaGetSymbolAddress failed");
+        return static_cast<int>(e);
+      }
+      g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  return fb_reduce(x, out, outer, R, inner, op, want > 0 ? scratch : nullptr,
+                   want > 0 ? FB_REDUCE_NOALLOC_MAX_FLOATS : 0, stream);
 }
