@@ -1,0 +1,165 @@
+"""Secondary benchmark configurations (the headline one is bench.py).
+
+    python bench_configs.py --config mnist|embedding [--impl ours|torch] [--steps K] [--warmup W]
+    python -m torch.distributed.run --nproc-per-node N bench_configs.py --config embedding ...
+
+mnist      60000 synthetic samples of 784 features ~ U[0,1), labels uniform in 0..9; Linear(784,256)-ReLU-
+           LayerNorm(256)-Linear(256,10)-LogSoftmax, nll_loss, Adam lr 1e-3, DataLoader batch 128 shuffled
+           (device-resident dataset, one row-gather kernel per batch).
+embedding  vocab 50000, dim 1024, 256 token ids ~ Zipf(1.1) per sample, mean-pooled Embedding ->
+           Linear(1024,4096)-SiLU-Dropout(0.1)-Linear(4096,512), cross_entropy, SGD momentum 0.9 wd 1e-4 with a
+           cosine LR schedule, per-GPU batch 512.
+
+Prints one JSON line (rank 0): samples/s over K timed steps (CUDA events, max over ranks), synthetic seeded data.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=["mnist", "embedding"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--bf16", action="store_true", help="bf16 tensor-core GEMMs (default for embedding)")
+    a = ap.parse_args()
+
+    import torch
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import ferrum_b200 as fb
+    from ferrum_b200 import data, nn, optim
+    from ferrum_b200.models import EmbeddingClassifier, mnist_classifier
+
+    if world > 1:
+        if a.impl == "ours":
+            fb.distributed.init_process_group_from_env("nvlink")
+        else:
+            torch.distributed.init_process_group("nccl", device_id=dev)
+    low = a.bf16 or a.config == "embedding"
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(1 + rank)
+
+    if a.config == "mnist":
+        batch = 128
+        n = 60000
+        x = torch.rand(n, 784, generator=g).to(dev)
+        y = torch.randint(0, 10, (n,), generator=g).to(dev)
+        if a.impl == "ours":
+            model = mnist_classifier(device=fb.Device.Cuda(local))
+            opt = optim.Adam(model.parameters(), optim.AdamConfig(lr=1e-3))
+            loss_fn = nn.nll_loss
+        else:
+            model = torch.nn.Sequential(torch.nn.Linear(784, 256), torch.nn.ReLU(), torch.nn.LayerNorm(256),
+                                        torch.nn.Linear(256, 10), torch.nn.LogSoftmax(-1)).to(dev)
+            opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True)
+            loss_fn = torch.nn.functional.nll_loss
+        sched = None
+    else:
+        batch = 512
+        n = batch * 8
+        ids = data.zipf_indices(50000, 1.1, n * 256, seed=7 + rank)
+        x = torch.from_numpy(ids).reshape(n, 256).to(dev)
+        y = torch.randint(0, 512, (n,), generator=g).to(dev)
+        if a.impl == "ours":
+            model = EmbeddingClassifier(device=fb.Device.Cuda(local))
+            opt = optim.SGD(model.parameters(), optim.SGDConfig(lr=0.1, momentum=0.9, weight_decay=1e-4))
+            loss_fn = nn.cross_entropy
+            sched = optim.CosineAnnealingLR(0.1, a.steps + a.warmup, 0.0)
+        else:
+            class Net(torch.nn.Module):
+                def __init__(self):
+                    super().__init__()
+                    self.emb = torch.nn.EmbeddingBag(50000, 1024, mode="mean")
+                    self.head = torch.nn.Sequential(torch.nn.Linear(1024, 4096), torch.nn.SiLU(), torch.nn.Dropout(0.1),
+                                                    torch.nn.Linear(4096, 512))
+
+                def forward(self, idx):
+                    return self.head(self.emb(idx))
+
+            model = Net().to(dev)
+            opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+            loss_fn = torch.nn.functional.cross_entropy
+            sched = torch.optim.lr_scheduler.CosineAnnealingLR(opt, a.steps + a.warmup)
+
+    net = model
+    engine = None
+    if world > 1:
+        if a.impl == "ours":
+            engine = fb.distributed.DistributedDataParallel(model, fb.distributed.get_world()).fuse_optimizer(opt)
+            net = engine
+        else:
+            net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local])
+
+    ds = data.TensorDataset.from_tensors(x, y)
+    loader = data.DataLoader(ds, batch_size=batch, shuffle=True, seed=3, drop_last=True)
+
+    def batches():
+        while True:
+            for xb, yb in loader:
+                yield xb.torch(), yb.torch()
+
+    it = batches()
+
+    def step():
+        xb, yb = next(it)
+        if a.impl == "ours":
+            if sched is not None:
+                opt.set_learning_rate(sched.get_lr())
+            opt.zero_grad()
+            with fb.autocast(enabled=low):
+                loss = loss_fn(net(xb), yb)
+            loss.backward()
+            opt.step()
+            if sched is not None:
+                sched.step()
+        else:
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=low):
+                loss = loss_fn(net(xb), yb)
+            loss.backward()
+            opt.step()
+            if sched is not None:
+                sched.step()
+        return loss
+
+    for _ in range(a.warmup):
+        step()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    if a.impl == "ours":
+        fb.utils.runtime.check_status()
+    if rank == 0:
+        print(json.dumps({"config": a.config, "impl": a.impl, "n_gpus": world, "steps": a.steps,
+                          "ms_per_step": ms / a.steps, "samples_per_s": a.steps * batch * world / (ms / 1e3),
+                          "dtype": "bf16" if low else "fp32", "final_loss": float(loss), "data": "synthetic"}))
+    if engine is not None:
+        engine.shutdown()
+    if world > 1 and a.impl == "ours":
+        fb.distributed.destroy_process_group()
+    elif world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    sys.exit(main())

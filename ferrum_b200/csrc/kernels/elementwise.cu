@@ -19,6 +19,16 @@ namespace {
 constexpr float kGeluC = 0.7978845608028654f;
 constexpr float kGeluA = 0.044715f;
 
+__device__ __forceinline__ float tanh_fast(float u) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return t;
+}
+// bf16 storage rounds at 2^-9; the hardware tanh (2^-11) and __expf are accurate enough there and keep the
+// kernel memory-bound.
+__device__ __forceinline__ float unary_f_fast(float x, int op, float alpha, float beta);
+__device__ __forceinline__ float unary_grad_fast(float dy, float s, int op, float alpha, float beta);
+
 __device__ __forceinline__ float unary_f(float x, int op, float alpha, float beta) {
   switch (op) {
     case FB_ACT_NONE: return x;
@@ -82,6 +92,30 @@ __device__ __forceinline__ float unary_grad(float dy, float s, int op, float alp
     case FB_UNARY_AFFINE: return dy * alpha;
     case FB_UNARY_CLAMP: return (s >= alpha && s <= beta) ? dy : 0.f;
     default: return dy;
+  }
+}
+
+__device__ __forceinline__ float unary_f_fast(float x, int op, float alpha, float beta) {
+  switch (op) {
+    case FB_ACT_GELU: return 0.5f * x * (1.f + tanh_fast(kGeluC * (x + kGeluA * x * x * x)));
+    case FB_ACT_SILU: return x / (1.f + __expf(-x));
+    case FB_ACT_TANH: return tanh_fast(x);
+    case FB_ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+    default: return unary_f(x, op, alpha, beta);
+  }
+}
+__device__ __forceinline__ float unary_grad_fast(float dy, float s, int op, float alpha, float beta) {
+  switch (op) {
+    case FB_ACT_GELU: {
+      const float t = tanh_fast(kGeluC * (s + kGeluA * s * s * s));
+      const float du = kGeluC * (1.f + 3.f * kGeluA * s * s);
+      return dy * (0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * du);
+    }
+    case FB_ACT_SILU: {
+      const float sg = 1.f / (1.f + __expf(-s));
+      return dy * (sg * (1.f + s * (1.f - sg)));
+    }
+    default: return unary_grad(dy, s, op, alpha, beta);
   }
 }
 
@@ -160,13 +194,13 @@ __global__ void unary_fwd_bf16(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
       float f[8];
       bf16x8_to_f32(reinterpret_cast<const uint4*>(x)[i], f);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] = unary_f(f[k], op, a, b);
+      for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], op, a, b);
       reinterpret_cast<uint4*>(y)[i] = f32_to_bf16x8(f);
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
-      y[i] = __float2bfloat16_rn(unary_f(__bfloat162float(x[i]), op, a, b));
+      y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), op, a, b));
   } else {
-    for (long long i = tid; i < n; i += stride) y[i] = __float2bfloat16_rn(unary_f(__bfloat162float(x[i]), op, a, b));
+    for (long long i = tid; i < n; i += stride) y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), op, a, b));
   }
 }
 
@@ -185,14 +219,14 @@ __global__ void unary_bwd_bf16(const __nv_bfloat16* __restrict__ dy, const __nv_
       bf16x8_to_f32(reinterpret_cast<const uint4*>(dy)[i], g);
       bf16x8_to_f32(reinterpret_cast<const uint4*>(sp)[i], v);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = unary_grad(g[k], v[k], op, a, b);
+      for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], op, a, b);
       reinterpret_cast<uint4*>(dx)[i] = f32_to_bf16x8(g);
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
-      dx[i] = __float2bfloat16_rn(unary_grad(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
+      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
   } else {
     for (long long i = tid; i < n; i += stride)
-      dx[i] = __float2bfloat16_rn(unary_grad(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
+      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
   }
 }
 
@@ -238,6 +272,27 @@ __global__ void binary_contig(const float* __restrict__ a, const float* __restri
     for (long long i = (n4 << 2) + tid; i < n; i += stride) o[i] = binary_f(a[i], b[i], op);
   } else {
     for (long long i = tid; i < n; i += stride) o[i] = binary_f(a[i], b[i], op);
+  }
+}
+
+// [rows, cols] (op) [cols]: the second operand is broadcast along rows (bias add, per-feature scaling).
+// swap = the broadcast operand is the FIRST argument of the op.
+__global__ void binary_rowbcast(const float* __restrict__ full, const float* __restrict__ vec, float* __restrict__ o,
+                                long long n, long long cols, int op, int swap) {
+  const long long n4 = n >> 2;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 x = reinterpret_cast<const float4*>(full)[i];
+    const float4 y = *reinterpret_cast<const float4*>(vec + (i << 2) % cols);
+    float4 r;
+    if (swap) {
+      r.x = binary_f(y.x, x.x, op); r.y = binary_f(y.y, x.y, op);
+      r.z = binary_f(y.z, x.z, op); r.w = binary_f(y.w, x.w, op);
+    } else {
+      r.x = binary_f(x.x, y.x, op); r.y = binary_f(x.y, y.y, op);
+      r.z = binary_f(x.z, y.z, op); r.w = binary_f(x.w, y.w, op);
+    }
+    reinterpret_cast<float4*>(o)[i] = r;
   }
 }
 
@@ -379,8 +434,30 @@ extern "C" int fb_binary_fwd(const float* a, const float* b, float* out, int op,
     if (shape[i] != 1 && (stride_a[i] != expect || stride_b[i] != expect)) contig = false;
     expect *= shape[i];
   }
+  // row-broadcast fast path: one operand contiguous over the full shape, the other only along the last dim
+  auto is_full = [&](const long long* st) {
+    long long e = 1;
+    for (int i = ndim - 1; i >= 0; --i) {
+      if (shape[i] != 1 && st[i] != e) return false;
+      e *= shape[i];
+    }
+    return true;
+  };
+  auto is_row = [&](const long long* st) {
+    if (ndim < 2 || st[ndim - 1] != 1) return false;
+    for (int i = 0; i < ndim - 1; ++i)
+      if (shape[i] != 1 && st[i] != 0) return false;
+    return true;
+  };
+  const long long cols = ndim > 0 ? shape[ndim - 1] : 1;
+  const bool al = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                    reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   if (contig) {
     binary_contig<<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(a, b, out, n, op);
+  } else if (al && cols % 4 == 0 && is_full(stride_a) && is_row(stride_b)) {
+    binary_rowbcast<<<grid_for(n / 4, 256), 256, 0, stream>>>(a, b, out, n, cols, op, 0);
+  } else if (al && cols % 4 == 0 && is_full(stride_b) && is_row(stride_a)) {
+    binary_rowbcast<<<grid_for(n / 4, 256), 256, 0, stream>>>(b, a, out, n, cols, op, 1);
   } else {
     BcastDesc d;
     d.ndim = ndim;

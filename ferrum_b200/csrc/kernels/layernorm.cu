@@ -137,15 +137,26 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
   const int t = threadIdx.x % TPR;
   const int nvec = cols >> 3;
   const float inv_n = 1.f / static_cast<float>(cols);
-  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows;
-       row0 += static_cast<long long>(gridDim.x) * kRowsPerBlock) {
-    const long long row = row0 + sub;
-    const bool live = row < rows;
-    typename V8<T>::Raw raw[K];
+  const long long row_stride = static_cast<long long>(gridDim.x) * kRowsPerBlock;
+  typename V8<T>::Raw raw[K], nxt[K];
+  {
+    const long long r0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock + sub;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int vi = t + k * TPR;
-      if (live && vi < nvec) raw[k] = V8<T>::ld(x + row * cols + vi * 8);
+      if (r0 < rows && vi < nvec) raw[k] = V8<T>::ld(x + r0 * cols + vi * 8);
+    }
+  }
+  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows; row0 += row_stride) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    {  // the next row's loads are in flight while this row is reduced and written
+      const long long rn = row + row_stride;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int vi = t + k * TPR;
+        if (rn < rows && vi < nvec) nxt[k] = V8<T>::ld(x + rn * cols + vi * 8);
+      }
     }
     float v[K][8];
     float s = 0.f;
@@ -196,6 +207,8 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
         V8<T>::st(y + row * cols + vi * 8, o);
       }
     }
+#pragma unroll
+    for (int k = 0; k < K; ++k) raw[k] = nxt[k];
   }
 }
 
@@ -203,7 +216,7 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
 // three column partials (dy*xhat, dy, dx) accumulate in registers over all rows the block visits and are
 // written once to partial[blockIdx][3][cols].
 template <typename T, int TPR, int K>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
               const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
               float* __restrict__ partial, long long rows, int cols, int pre_act, int want_colsum) {
@@ -220,17 +233,31 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc_g[k][i] = acc_b[k][i] = acc_c[k][i] = 0.f;
 
-  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows;
-       row0 += static_cast<long long>(gridDim.x) * kRowsPerBlock) {
-    const long long row = row0 + sub;
-    const bool live = row < rows;
-    typename V8<T>::Raw xr[K], gr[K];
+  const long long row_stride = static_cast<long long>(gridDim.x) * kRowsPerBlock;
+  typename V8<T>::Raw xr[K], gr[K], xn[K], gn[K];
+  {
+    const long long r0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock + sub;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int vi = t + k * TPR;
-      if (live && vi < nvec) {
-        xr[k] = V8<T>::ld(x + row * cols + vi * 8);
-        gr[k] = V8<T>::ld(dy + row * cols + vi * 8);
+      if (r0 < rows && vi < nvec) {
+        xr[k] = V8<T>::ld(x + r0 * cols + vi * 8);
+        gr[k] = V8<T>::ld(dy + r0 * cols + vi * 8);
+      }
+    }
+  }
+  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows; row0 += row_stride) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    {  // prefetch the next row while this one is processed
+      const long long rn = row + row_stride;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int vi = t + k * TPR;
+        if (rn < rows && vi < nvec) {
+          xn[k] = V8<T>::ld(x + rn * cols + vi * 8);
+          gn[k] = V8<T>::ld(dy + rn * cols + vi * 8);
+        }
       }
     }
     const float mu = live ? mean[row] : 0.f;
@@ -277,6 +304,11 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
         }
         V8<T>::st(dx + row * cols + vi * 8, o);
       }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      xr[k] = xn[k];
+      gr[k] = gn[k];
     }
   }
 

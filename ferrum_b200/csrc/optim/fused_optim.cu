@@ -86,7 +86,34 @@ __device__ __forceinline__ void adam_range(float* __restrict__ p, const float* _
 __device__ __forceinline__ void sgd_range(float* __restrict__ p, const float* __restrict__ g,
                                           float* __restrict__ buf, __nv_bfloat16* __restrict__ sh, long long n,
                                           const fb_sgd_hparams& h, long long tid, long long stride) {
-  for (long long i = tid; i < n; i += stride) {
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                         reinterpret_cast<uintptr_t>(buf)) & 15) == 0 &&
+                       (sh == nullptr || (reinterpret_cast<uintptr_t>(sh) & 7) == 0);
+  long long done = 0;
+  if (aligned) {
+    const long long n4 = n >> 2;
+    const bool mom = h.momentum != 0.f && buf != nullptr;
+    for (long long i = tid; i < n4; i += stride) {
+      float4 pp = reinterpret_cast<float4*>(p)[i];
+      const float4 gg = reinterpret_cast<const float4*>(g)[i];
+      float4 vv = mom ? reinterpret_cast<float4*>(buf)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      float* pv = reinterpret_cast<float*>(&pp);
+      const float* gv = reinterpret_cast<const float*>(&gg);
+      float* bv = reinterpret_cast<float*>(&vv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) sgd_one(pv[k], gv[k], mom ? bv : nullptr, k, h);
+      reinterpret_cast<float4*>(p)[i] = pp;
+      if (mom) reinterpret_cast<float4*>(buf)[i] = vv;
+      if (sh != nullptr) {
+        uint2 u;
+        *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(pp.x, pp.y);
+        *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(pp.z, pp.w);
+        reinterpret_cast<uint2*>(sh)[i] = u;
+      }
+    }
+    done = n4 << 2;
+  }
+  for (long long i = done + tid; i < n; i += stride) {
     float pp = p[i];
     sgd_one(pp, g[i], buf, i, h);
     p[i] = pp;

@@ -325,6 +325,7 @@ class Embedding(Module):
             if padding_idx is not None:
                 _weight[padding_idx].zero_()
         self.weight = _param(_weight, requires_grad=not freeze)
+        self.grad_sink = None  # set by the DDP engine
 
     @classmethod
     def new(cls, num_embeddings, embedding_dim):
@@ -360,7 +361,7 @@ class Embedding(Module):
     @tensor_io
     def forward(self, idx):
         self._check(idx)
-        return F.embedding(self.weight, idx, self.padding_idx)
+        return F.embedding(self.weight, idx, self.padding_idx, sink=self.grad_sink)
 
     forward_indices = forward
 
@@ -369,7 +370,7 @@ class Embedding(Module):
         """Mean-pooled lookup ``[B, S] -> [B, D]`` in one kernel."""
         self._check(idx)
         out_dtype = torch.bfloat16 if config.low_precision_active() and self.weight.is_cuda else None
-        return F.embedding_mean_pool(self.weight, idx, out_dtype)
+        return F.embedding_mean_pool(self.weight, idx, out_dtype, self.grad_sink)
 
 
 class MeanPoolEmbedding(Embedding):
@@ -379,7 +380,7 @@ class MeanPoolEmbedding(Embedding):
     def forward(self, idx):
         self._check(idx)
         out_dtype = torch.bfloat16 if config.low_precision_active() and self.weight.is_cuda else None
-        return F.embedding_mean_pool(self.weight, idx, out_dtype)
+        return F.embedding_mean_pool(self.weight, idx, out_dtype, self.grad_sink)
 
 
 # ------------------------------------------------------------------ container

@@ -1019,7 +1019,8 @@ def _sorted_indices(idx_flat: torch.Tensor):
 
 class _EmbeddingFn(Function):
     @staticmethod
-    def forward(ctx, weight, idx, padding_idx, out_dtype, pool):
+    def forward(ctx, weight, idx, padding_idx, out_dtype, pool, sink=None):
+        ctx.sink, ctx.weight_ref = sink, weight
         w = weight.detach().contiguous()
         V, D = w.shape
         idx_c = idx.contiguous()
@@ -1049,32 +1050,41 @@ class _EmbeddingFn(Function):
         g2 = g.reshape(-1, D).contiguous()
         flat = idx.reshape(-1)
         sidx, perm = _sorted_indices(flat)
-        dw = torch.zeros((V, D), device=g.device, dtype=torch.float32)
+        if ctx.sink is not None:  # accumulate straight into the data-parallel gradient arena
+            dw, acc = ctx.sink.acquire(ctx.weight_ref)
+            if not acc:
+                dw.zero_()
+        else:
+            dw = torch.zeros((V, D), device=g.device, dtype=torch.float32)
         scale = 1.0 / ctx.group if ctx.pool else 1.0
         _lib.check(_lib.cuda().fb_embedding_bwd_sorted(g2.data_ptr(), sidx.data_ptr(), perm.data_ptr(),
                                                        dw.data_ptr(), flat.numel(), D, ctx.group, scale,
                                                        -1 if ctx.padding_idx is None else ctx.padding_idx,
                                                        _dt(g2), _stream()), "fb_embedding_bwd_sorted")
-        return dw, None, None, None, None
+        if ctx.sink is not None:
+            ctx.sink.ready(ctx.weight_ref)
+            return None, None, None, None, None, None
+        return dw, None, None, None, None, None
 
 
 def embedding(weight: torch.Tensor, idx: torch.Tensor, padding_idx: int | None = None,
-              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+              out_dtype: torch.dtype | None = None, sink: GradSink | None = None) -> torch.Tensor:
     """Row gather ``weight[idx]`` -> ``[*idx.shape, D]``; rows at ``padding_idx`` are zero (embedding.rs:122-208)."""
     idx = idx.to(torch.int64)
     if weight.is_cuda and weight.dtype == torch.float32:
-        return _EmbeddingFn.apply(weight, idx, padding_idx, out_dtype or torch.float32, False)
+        return _EmbeddingFn.apply(weight, idx, padding_idx, out_dtype or torch.float32, False, sink)
     out = torch.nn.functional.embedding(idx, weight)
     if padding_idx is not None:
         out = out * (idx != padding_idx).unsqueeze(-1).to(out.dtype)
     return out
 
 
-def embedding_mean_pool(weight: torch.Tensor, idx: torch.Tensor, out_dtype: torch.dtype | None = None):
+def embedding_mean_pool(weight: torch.Tensor, idx: torch.Tensor, out_dtype: torch.dtype | None = None,
+                        sink: GradSink | None = None):
     """``mean_s weight[idx[b, s]]`` for ``idx [B, S]`` without materialising ``[B, S, D]``."""
     idx = idx.to(torch.int64)
     if weight.is_cuda and weight.dtype == torch.float32 and idx.dim() == 2 and idx.shape[1] * 8 <= 48 * 1024:
-        return _EmbeddingFn.apply(weight, idx, None, out_dtype or torch.float32, True)
+        return _EmbeddingFn.apply(weight, idx, None, out_dtype or torch.float32, True, sink)
     return torch.nn.functional.embedding(idx, weight).mean(1)
 
 

@@ -19,9 +19,9 @@ from ..utils import runtime as _rt
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "silu": 3, "tanh": 4, "sigmoid": 5}
 
 _max_ctas = 0  # 0 = all SMs; the DDP engine lowers this to leave SMs for the comm kernel
-# CTA-pair kernel (tcgen05 cta_group::2, 256x256 tile per two SMs) for large problems; "0" selects the
-# single-CTA kernel everywhere.
-_use_2cta = os.environ.get("FERRUM_GEMM_2CTA", "0") == "1"
+# CTA-pair kernel (tcgen05 cta_group::2, 256x256 tile per two SMs) for large problems (default);
+# FERRUM_GEMM_2CTA=0 selects the single-CTA kernel everywhere.
+_use_2cta = os.environ.get("FERRUM_GEMM_2CTA", "1") == "1"
 
 
 def set_gemm_2cta(flag: bool) -> None:

@@ -27,7 +27,7 @@ import torch
 
 from .. import _lib, config
 from ..core import Tensor, _unwrap
-from ..nn.modules import Linear, Module, tensor_io
+from ..nn.modules import Embedding, Linear, Module, tensor_io
 from ..ops import gemm as _gemm
 from ..ops.functional import GradSink
 from ..utils import runtime as _rt
@@ -185,7 +185,8 @@ class DistributedDataParallel(Module, GradSink):
         self._small_runs = []  # (start, length) runs of non-GEMM gradients, zeroed every step
         sink_ids = set()
         for mod in self.inner.modules():
-            if type(mod) is Linear and id(mod.weight) in self._index and self._use_native:
+            if ((type(mod) is Linear or isinstance(mod, Embedding)) and id(mod.weight) in self._index
+                    and self._use_native):
                 mod.grad_sink = self
                 sink_ids.add(id(mod.weight))
         run = None
