@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--depth", type=int, default=MODEL["depth"])
     ap.add_argument("--width", type=int, default=MODEL["width"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shard-master", action="store_true",
+                    help="DDP: publish only bf16 weights to peers, fp32 master weights stay with the shard owner")
     return ap.parse_args()
 
 
@@ -149,6 +151,8 @@ def run_ours(args):
     if world > 1:
         engine = fb.distributed.DistributedDataParallel(model, fb.distributed.get_world()).bucket_size_mb(25)
         engine.fuse_optimizer(opt)
+        if args.shard_master:
+            engine.shard_master_weights(True)
         net = engine
     else:
         net = model
@@ -209,7 +213,7 @@ def run_ours(args):
     fb.utils.runtime.check_status()
     if engine is not None:
         engine.shutdown()
-    return ms, launches, clocks, e2e, "nvlink-fused-ddp" if world > 1 else "single"
+    return ms, launches, clocks, e2e, ("nvlink-fused-ddp" + ("-sharded-master" if args.shard_master else "")) if world > 1 else "single"
 
 
 def run_torch(args):

@@ -28,9 +28,9 @@ def _sigs():
         "fb_dist_query_max_blocks": (I, []),
         "fb_dist_query_channels": (I, []),
         "fb_dist_allreduce": (I, [POINTER(DistCtx), I, I, I, U, LL, LL, LL, LL, I, F, POINTER(AdamH), POINTER(SgdH),
-                                  P, P, I, I, P]),
+                                  P, P, I, I, I, P]),
         "fb_dist_allreduce_emulated": (I, [POINTER(DistCtx), I, I, I, U, LL, LL, LL, LL, I, F, POINTER(AdamH),
-                                           POINTER(SgdH), POINTER(c_void_p), POINTER(c_void_p), I, I, P]),
+                                           POINTER(SgdH), POINTER(c_void_p), POINTER(c_void_p), I, I, I, P]),
         "fb_dist_collective": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, LL, I, F, I, P]),
         "fb_dist_collective_emulated": (I, [POINTER(DistCtx), I, I, I, U, I, LL, LL, LL, I, F, I, P]),
         "fb_dist_barrier": (I, [POINTER(DistCtx), I, U, P]),

@@ -83,6 +83,7 @@ struct ArArgs {
   fb_sgd_hparams sgd;
   float* m;  // this rank's moment / velocity storage for ITS shard (index 0 = first element of the shard)
   float* v;
+  int publish_master;  // 1: new fp32 parameters go to every rank; 0: only the bf16 copy does (owner keeps fp32)
 };
 
 __device__ __forceinline__ float4 combine4(float4 a, float4 b, int op) {
@@ -209,8 +210,11 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
         uint2 sh;
         *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p[u].x, p[u].y);
         *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p[u].z, p[u].w);
+        if (!a.publish_master)
+          *(reinterpret_cast<float4*>(c.arena[c.rank] + a.param_off) + lo4 + i4) = p[u];
         if (MC) {
-          ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + lo4 + i4, p[u]);
+          if (a.publish_master)
+            ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + lo4 + i4, p[u]);
           if (a.shadow_off >= 0)
             ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + lo4 + i4,
                                 make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
@@ -218,7 +222,8 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
 #pragma unroll
           for (int r = 0; r < W; ++r)
             if (r < c.world) {
-              ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + lo4 + i4, p[u]);
+              if (a.publish_master)
+                ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + lo4 + i4, p[u]);
               if (a.shadow_off >= 0)
                 ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + lo4 + i4, sh);
             }
@@ -319,6 +324,11 @@ __device__ void collective_body(const fb_dist_ctx& c, int vblock, int nvblocks, 
       for (int p = 0; p < c.world; ++p)
         copy_bytes(c.arena[p] + a.in_off, self + a.out_off + p * a.n_bytes, a.n_bytes, tid, stride);
       break;
+    case FB_COLL_ALL_GATHER_INPLACE:
+      for (int p = 0; p < c.world; ++p)
+        if (p != c.rank)
+          copy_bytes(c.arena[p] + a.in_off + p * a.n_bytes, self + a.in_off + p * a.n_bytes, a.n_bytes, tid, stride);
+      break;
     case FB_COLL_SCATTER:
       copy_bytes(c.arena[a.root] + a.in_off + c.rank * a.n_bytes, self + a.out_off, a.n_bytes, tid, stride);
       break;
@@ -394,7 +404,8 @@ extern "C" int fb_dist_query_channels() { return FB_FLAG_CHANNELS; }
 extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
                                  long long grad_off, long long param_off, long long shadow_off, long long n,
                                  int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
-                                 float* m, float* v, int nblocks, int nthreads, cudaStream_t stream) {
+                                 float* m, float* v, int publish_master, int nblocks, int nthreads,
+                                 cudaStream_t stream) {
   if (!ctx_ok(ctx) || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || nthreads < 32 ||
       nthreads > 256 || channel < 0 || channel >= FB_FLAG_CHANNELS)
     return -1;
@@ -412,6 +423,7 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
   if (sgd) a.sgd = *sgd;
   a.m = m;
   a.v = v;
+  a.publish_master = publish_master;
   switch (fuse) {
     case FB_FUSE_NONE: return launch_ar<FB_FUSE_NONE>(*ctx, a, use_mc, nblocks, nthreads, stream);
     case FB_FUSE_SGD: return launch_ar<FB_FUSE_SGD>(*ctx, a, use_mc, nblocks, nthreads, stream);
@@ -427,7 +439,8 @@ extern "C" int fb_dist_allreduce_emulated(const fb_dist_ctx* ctxs, int world, in
                                           unsigned epoch, long long grad_off, long long param_off,
                                           long long shadow_off, long long n, int op, float scale,
                                           const fb_adam_hparams* adam, const fb_sgd_hparams* sgd, float* const* m,
-                                          float* const* v, int nblocks, int nthreads, cudaStream_t stream) {
+                                          float* const* v, int publish_master, int nblocks, int nthreads,
+                                          cudaStream_t stream) {
   if (world < 1 || world > FB_MAX_RANKS || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS) return -1;
   EmuPack pk{};
   for (int r = 0; r < world; ++r) {
@@ -448,6 +461,7 @@ extern "C" int fb_dist_allreduce_emulated(const fb_dist_ctx* ctxs, int world, in
   a.scale = scale;
   if (adam) a.adam = *adam;
   if (sgd) a.sgd = *sgd;
+  a.publish_master = publish_master;
   void* args[] = {&pk, &a};
   const dim3 grid(world * nblocks), block(nthreads);
   const void* fn = fuse == FB_FUSE_ADAM  ? reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_ADAM>)

@@ -6,7 +6,7 @@
 
 #define FB_MAX_RANKS 8
 #define FB_FLAG_CHANNELS 8
-#define FB_FLAG_BLOCKS 64
+#define FB_FLAG_BLOCKS 128
 // flags[channel][block][source rank], one 32-bit epoch each
 #define FB_FLAG_WORDS (FB_FLAG_CHANNELS * FB_FLAG_BLOCKS * FB_MAX_RANKS)
 #define FB_FLAG_BYTES 65536  // flag words, rounded up so the data region stays 64 KiB aligned
@@ -29,6 +29,7 @@ enum {
   FB_COLL_SCATTER = 3,
   FB_COLL_REDUCE_SCATTER = 4,
   FB_COLL_REDUCE = 5,
+  FB_COLL_ALL_GATHER_INPLACE = 6,  // rank p's chunk already sits at in_off + p * n_bytes on rank p
 };
 enum { FB_OP_SUM = 0, FB_OP_PROD = 1, FB_OP_MIN = 2, FB_OP_MAX = 3, FB_OP_AVG = 4 };
 enum { FB_FUSE_NONE = 0, FB_FUSE_SGD = 1, FB_FUSE_ADAM = 2 };

@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--blocks", type=int, default=64)
     ap.add_argument("--threads", type=int, default=256)
+    ap.add_argument("--shard-master", action="store_true", help="publish only the bf16 copy to peers")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
 
@@ -88,7 +89,8 @@ def main():
             h = _lib.AdamH(3e-4, 0.9, 0.999, 1e-8, 0.0, 1 - 0.9 ** t, 1 - 0.999 ** t, 1.0 / world)
             e = arena.next_epoch(0)
             rc = lib.fb_dist_allreduce(arena.ctx, 2, use_mc, 0, e, off_g, off_p, off_s, n, 0, 1.0, ctypes.byref(h),
-                                       None, m.data_ptr(), v.data_ptr(), min(args.blocks, max(1, n // 4096)),
+                                       None, m.data_ptr(), v.data_ptr(), 0 if args.shard_master else 1,
+                                       min(args.blocks, max(1, n // 4096)),
                                        args.threads, stream.cuda_stream)
             assert rc == 0, rc
 
@@ -108,7 +110,8 @@ def main():
         bus = 2 * (world - 1) / world * n * 4 / 1e9
         res = {"bytes": n * 4, "world": world, "fused_ms": t_ours, "nccl_plus_adam_ms": t_base,
                "fused_bus_gbs": bus / (t_ours / 1e3), "baseline_bus_gbs": bus / (t_base / 1e3),
-               "speedup": t_base / t_ours, "multicast": bool(use_mc)}
+               "speedup": t_base / t_ours, "multicast": bool(use_mc), "blocks": args.blocks,
+               "shard_master": bool(args.shard_master)}
         results.append(res)
         if rank == 0:
             print(json.dumps(res), flush=True)

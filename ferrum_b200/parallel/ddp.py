@@ -109,6 +109,8 @@ class DistributedDataParallel(Module, GradSink):
         self._find_unused = False
         self._built = False
         self._opt = None
+        self._shard_master = os.environ.get("FERRUM_SHARD_MASTER", "0") == "1"
+        self._master_stale = False
         self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "48"))
         self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
         if optimizer is not None:
@@ -142,6 +144,33 @@ class DistributedDataParallel(Module, GradSink):
     def into_inner(self):
         self.shutdown()
         return self.inner
+
+    def shard_master_weights(self, flag: bool = True) -> "DistributedDataParallel":
+        """Keep the fp32 master copy of a parameter current only on the rank that owns its shard.
+
+        The fused reduction then publishes just the bf16 copies (2 instead of 6 bytes per parameter per peer),
+        which is all that bf16 forward / backward passes read.  The fp32 tensors of the other ranks are brought
+        up to date by ``sync_master_weights()`` (called automatically by ``shutdown`` and ``state_dict``-style
+        accessors of this wrapper); use it only together with ``autocast``.
+        """
+        self._shard_master = bool(flag)
+        return self
+
+    def sync_master_weights(self) -> None:
+        """All-gather the fp32 parameter shards so that every rank holds the full, current master weights."""
+        if not (getattr(self, "_use_native", False) and self._master_stale):
+            return
+        a = self._arena
+        world = self._pg.world_size()
+        self._done_event.record(self._comm_stream)
+        torch.cuda.current_stream().wait_event(self._done_event)
+        st = torch.cuda.current_stream().cuda_stream
+        for bk in self.buckets:
+            per = bk.length // world
+            e = a.next_epoch(2)
+            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 6, 2, e, 0, self._off_param + bk.start * 4, 0,
+                                                      per * 4, 0, 1.0, 32, st), "fb_dist_collective")
+        self._master_stale = False
 
     def fuse_optimizer(self, optimizer) -> "DistributedDataParallel":
         """Apply ``optimizer``'s update inside the bucket reduction kernels (SGD or Adam)."""
@@ -335,8 +364,11 @@ class DistributedDataParallel(Module, GradSink):
         use_mc = 1 if a.has_multicast() else 0
         rc = lib.fb_dist_allreduce(a.ctx, fuse, use_mc, 2, e, self._off_grad + bk.start * 4,
                                    self._off_param + bk.start * 4, self._off_shadow + bk.start * 2, bk.length,
-                                   4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr, self._comm_blocks,
+                                   4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr,
+                                   0 if (self._shard_master and fuse) else 1, self._comm_blocks,
                                    self._comm_threads, self._comm_stream.cuda_stream)
+        if self._shard_master and fuse:
+            self._master_stale = True
         _lib.check(rc, "fb_dist_allreduce")
 
     def _flush(self) -> None:
@@ -466,6 +498,7 @@ class DistributedDataParallel(Module, GradSink):
     def shutdown(self) -> None:
         """Release the arena (collective: every rank should call it after its last step)."""
         if getattr(self, "_use_native", False) and getattr(self, "_arena", None) is not None:
+            self.sync_master_weights()
             torch.cuda.synchronize()
             _gemm.set_gemm_cta_limit(0)
             try:

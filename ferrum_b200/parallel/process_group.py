@@ -154,7 +154,7 @@ class ProcessGroup:
                 stage[cnt:].zero_()  # the padding is reduced too but never copied back
             e = arena.next_epoch(0)
             _lib.check(lib.fb_dist_allreduce(arena.ctx, 0, use_mc, 0, e, off, 0, -1, padded, _OP_CODE[op], scale,
-                                             None, None, None, None, self._blocks(padded * 4), 256, self._stream()),
+                                             None, None, None, None, 1, self._blocks(padded * 4), 256, self._stream()),
                        "fb_dist_allreduce")
             work[lo:lo + cnt].copy_(stage[:cnt])
         if work.data_ptr() != flat.data_ptr():

@@ -37,7 +37,7 @@ def test_allreduce_average_emulated(world, n):
     for a, d in zip(arenas, data):
         a.view(off, (n,), torch.float32).copy_(d)
     rc = lib.fb_dist_allreduce_emulated(ctxs, world, 0, 0, 1, off, 0, -1, n, 4, 1.0 / world, None, None, None, None,
-                                        4, 256, _stream())
+                                        1, 4, 256, _stream())
     assert rc == 0
     check_status()
     ref = torch.stack(data).sum(0) / world
@@ -73,7 +73,7 @@ def test_fused_allreduce_adam_emulated(world):
     for t in (1, 2, 3):
         h = L.AdamH(lr, b1, b2, eps, wd, 1 - b1 ** t, 1 - b2 ** t, 1.0 / world)
         rc = lib.fb_dist_allreduce_emulated(ctxs, world, 2, 0, epoch, off_g, off_p, off_s, n, 0, 1.0,
-                                            ctypes.byref(h), None, mp, vp, 3, 256, _stream())
+                                            ctypes.byref(h), None, mp, vp, 1, 3, 256, _stream())
         assert rc == 0
         epoch += 2
         g = torch.stack(grads).sum(0) / world
@@ -115,7 +115,7 @@ def test_fused_allreduce_sgd_momentum_emulated():
     for step in range(3):
         h = L.SgdH(0.1, 0.9, 1e-4, 1.0 / world, 0, 1 if step == 0 else 0)
         rc = lib.fb_dist_allreduce_emulated(ctxs, world, 1, 0, epoch, off_g, off_p, off_s, n, 0, 1.0, None,
-                                            ctypes.byref(h), mp, None, 2, 128, _stream())
+                                            ctypes.byref(h), mp, None, 1, 2, 128, _stream())
         assert rc == 0
         epoch += 2
         g = torch.stack(grads).sum(0) / world + 1e-4 * ref_p
@@ -203,3 +203,38 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     x = torch.ones(1024, device="cuda")
     assert float((x * 2).sum()) == 2048.0  # the context is still usable
     arena.close()
+
+
+def test_sharded_master_weights_and_inplace_all_gather_emulated():
+    """publish_master = 0: peers receive only the bf16 copy; the in-place all-gather then restores fp32 everywhere."""
+    from ferrum_b200 import _lib as L
+    from ferrum_b200.utils.runtime import check_status
+
+    world = 4
+    n = 4 * world * 500
+    lib, arenas, ctxs = _setup(world, n * 3)
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + n * 4, base + n * 8
+    p0 = torch.randn(n, device="cuda")
+    grads = [torch.randn(n, device="cuda") for _ in range(world)]
+    for a, g in zip(arenas, grads):
+        a.view(off_p, (n,), torch.float32).copy_(p0)
+        a.view(off_g, (n,), torch.float32).copy_(g)
+    per = n // world
+    vel = [torch.zeros(per, device="cuda") for _ in range(world)]
+    mp = (ctypes.c_void_p * world)(*[v.data_ptr() for v in vel])
+    h = L.SgdH(0.1, 0.0, 0.0, 1.0 / world, 0, 1)
+    assert lib.fb_dist_allreduce_emulated(ctxs, world, 1, 0, 1, off_g, off_p, off_s, n, 0, 1.0, None, ctypes.byref(h),
+                                          mp, None, 0, 2, 128, _stream()) == 0
+    ref = p0 - 0.1 * torch.stack(grads).sum(0) / world
+    for r, a in enumerate(arenas):
+        mine = a.view(off_p, (n,), torch.float32)
+        assert torch.allclose(mine[r * per:(r + 1) * per], ref[r * per:(r + 1) * per], atol=1e-6)
+        other = (r + 1) % world
+        assert torch.equal(mine[other * per:(other + 1) * per], p0[other * per:(other + 1) * per])  # still stale
+        assert torch.allclose(a.view(off_s, (n,), torch.bfloat16).float(), ref, atol=2e-2, rtol=1e-2)  # bf16 current
+    assert lib.fb_dist_collective_emulated(ctxs, world, 6, 0, 3, 0, off_p, 0, per * 4, 0, 1.0, 2, _stream()) == 0
+    check_status()
+    for a in arenas:
+        assert torch.allclose(a.view(off_p, (n,), torch.float32), ref, atol=1e-6)
+        a.close()
