@@ -25,6 +25,9 @@ from . import autograd  # noqa: E402
 from . import data  # noqa: E402
 from . import serialize  # noqa: E402
 from . import cuda  # noqa: E402
+from . import kernels  # noqa: E402
+from . import autograd_functions  # noqa: E402
+from .storage import CpuAllocator, CudaAllocator, DeviceAllocator, Storage  # noqa: E402
 from . import parallel  # noqa: E402
 from . import parallel as distributed  # noqa: E402
 from .autograd import GradientTape, NoGradGuard, backward, is_grad_enabled, no_grad  # noqa: E402

@@ -1,0 +1,108 @@
+"""Storage / allocators, the named backward formulas (ferrum-autograd/tests/integration_test.rs calls them
+directly), the functional op namespace, the prelude, secondary layers, profiler plumbing."""
+import pytest
+import torch
+
+import ferrum_b200 as fb
+from ferrum_b200 import DType, Storage, Tensor, nn, ops
+from ferrum_b200 import autograd_functions as AF
+
+
+def test_storage_sharing_and_copy_on_write():
+    s = Storage.zeros(16)
+    assert s.size() == 16 and s.read_as(DType.F32) == [0.0] * 4 and s.device() == fb.Device.Cpu
+    s = Storage.from_slice([1.0, 2.0, 3.0])
+    assert s.is_unique() and s.ref_count() == 1
+    s2 = s.share()
+    assert not s.is_unique() and s2.ref_count() == 2 and s2.as_ptr() == s.as_ptr()
+    s2.make_unique()
+    s2.write_as([9.0], DType.F32)
+    assert s.read_as(DType.F32) == [1.0, 2.0, 3.0] and s2.read_as(DType.F32) == [9.0, 2.0, 3.0]
+    assert s.is_unique() and Storage.uninit(0).size() == 0
+    assert Storage.from_bytes(b"\x00\x00\x80\x3f").read_as(DType.F32) == [1.0]
+    assert s.as_tensor(DType.F32, [3]).to_vec() == [1.0, 2.0, 3.0]
+    buf = fb.CpuAllocator().alloc(100)
+    assert buf.data_ptr() % 64 == 0 and buf.numel() == 100
+
+
+def test_named_backward_functions():
+    a, b = Tensor.from_slice([1.0, 2.0, 3.0]), Tensor.from_slice([4.0, 5.0, 6.0])
+    g = Tensor.ones([3])
+    assert [t.to_vec() for t in AF.AddBackward(a, b).backward(g)] == [[1, 1, 1], [1, 1, 1]]
+    assert AF.SubBackward(a, b).backward(g)[1].to_vec() == [-1, -1, -1]
+    assert [t.to_vec() for t in AF.MulBackward(a, b).backward(g)] == [[4, 5, 6], [1, 2, 3]]
+    ga, gb = AF.DivBackward(Tensor.from_slice([2.0, 4.0]), Tensor.from_slice([1.0, 2.0])).backward(Tensor.ones([2]))
+    assert ga.to_vec() == [1, 0.5] and gb.to_vec() == [-2, -1]
+    ga, gb = AF.MatMulBackward(Tensor.from_slice([[1.0, 2.0], [3.0, 4.0]]),
+                               Tensor.from_slice([[5.0, 6.0], [7.0, 8.0]])).backward(Tensor.ones([2, 2]))
+    assert ga.to_vec() == [11, 15, 11, 15] and gb.to_vec() == [4, 4, 6, 6]
+    assert AF.ReLUBackward(Tensor.from_slice([-1.0, 2.0])).backward(Tensor.ones([2]))[0].to_vec() == [0, 1]
+    assert AF.SigmoidBackward(Tensor.from_slice([0.5])).backward(Tensor.ones([1]))[0].item() == 0.25
+    assert AF.TanhBackward(Tensor.from_slice([0.0])).backward(Tensor.ones([1]))[0].item() == 1.0
+    assert AF.ExpBackward(Tensor.from_slice([2.0])).backward(Tensor.from_slice([3.0]))[0].item() == 6.0
+    assert AF.LogBackward(Tensor.from_slice([4.0])).backward(Tensor.ones([1]))[0].item() == 0.25
+    assert AF.PowBackward(Tensor.from_slice([3.0]), 2.0).backward(Tensor.ones([1]))[0].item() == 6.0
+    assert AF.SqrtBackward(Tensor.from_slice([2.0])).backward(Tensor.ones([1]))[0].item() == 0.25
+    assert AF.NegBackward().backward(Tensor.ones([2]))[0].to_vec() == [-1, -1]
+    assert AF.SumBackward([2, 2]).backward(Tensor.from_slice(2.0))[0].to_vec() == [2, 2, 2, 2]
+    assert AF.MeanBackward([2, 2]).backward(Tensor.from_slice(1.0))[0].to_vec() == [0.25] * 4
+    assert AF.SumDimBackward([2, 3], 0).backward(Tensor.ones([3]))[0].shape == (2, 3)
+    parts = AF.CatBackward([2, 1], 0).backward(Tensor.from_slice([1.0, 2.0, 3.0]))
+    assert parts[0].to_vec() == [1, 2] and parts[1].to_vec() == [3]
+    assert AF.AddBackward(Tensor.ones([2, 3]), Tensor.ones([3])).backward(Tensor.ones([2, 3]))[1].to_vec() == [2, 2, 2]
+    assert AF.MulBackward(a, b).name() == "MulBackward"
+    assert AF.reduce_gradient(Tensor.ones([4, 3]), [1, 3]).to_vec() == [4, 4, 4]
+
+
+def test_ops_namespace_and_prelude():
+    a, b = Tensor.from_slice([[1.0, 2.0], [3.0, 4.0]]), Tensor.ones([2, 2])
+    assert ops.add(a, b).to_vec() == [2, 3, 4, 5] and ops.matmul(a, b).to_vec() == [3, 3, 7, 7]
+    assert ops.matmul_tiled(a, b).to_vec() == ops.matmul_blas(a, b).to_vec() == ops.matmul_parallel(a, b).to_vec()
+    assert ops.sum_dim(a, 0).to_vec() == [4, 6] and ops.argmax(a, 1).to_vec() == [1, 1]
+    assert ops.bmm(Tensor.ones([2, 2, 3]), Tensor.ones([2, 3, 2])).shape == (2, 2, 2)
+    assert ops.stack([a, b]).shape == (2, 2, 2) and ops.neg(a).to_vec()[0] == -1
+    ns = {}
+    exec("from ferrum_b200.prelude import *", ns)
+    for name in ("Tensor", "DType", "Device", "Linear", "Sequential", "GELU", "LayerNorm", "Adam", "AdamConfig",
+                 "SGD", "StepLR", "OneCycleLR", "DataLoader", "DistributedSampler", "save", "load", "GradientTape",
+                 "no_grad", "DistributedDataParallel", "ReduceOp", "mse_loss", "nll_loss", "init_process_group"):
+        assert name in ns, name
+
+
+def test_conv_pool_rnn_transformer_shapes_and_values():
+    x = Tensor.randn([2, 3, 8, 8])
+    c = nn.Conv2d.new(3, 4, 3).padding(1)
+    assert torch.allclose(c(x).torch(), torch.nn.functional.conv2d(x.torch(), c.weight, c.bias, padding=1), atol=1e-5)
+    assert nn.MaxPool2d.new(2)(x).shape == (2, 3, 4, 4) and nn.AvgPool2d.new(2)(x).shape == (2, 3, 4, 4)
+    assert nn.AdaptiveAvgPool2d.square(1)(x).shape == (2, 3, 1, 1)
+    assert nn.Conv1d.new(3, 5, 3)(Tensor.randn([2, 3, 10])).shape == (2, 5, 8)
+    out, h = nn.RNN.new(4, 6, 2).forward_seq(Tensor.randn([5, 3, 4]))
+    assert out.shape == (5, 3, 6) and h.shape == (2, 3, 6)
+    out, (h, cc) = nn.LSTM.new(4, 6, 1).forward_seq(Tensor.randn([5, 3, 4]))
+    assert out.shape == (5, 3, 6) and cc.shape == (1, 3, 6)
+    assert nn.GRUCell.new(4, 6)(Tensor.randn([3, 4]), Tensor.zeros([3, 6])).shape == (3, 6)
+    loss = nn.GRU.new(4, 6, 1)(Tensor.randn([5, 3, 4])).sum()
+    loss.backward()  # recurrent layers are differentiable (host-only math without autograd in the reference)
+    xs = Tensor.randn([2, 5, 16])
+    assert nn.MultiHeadAttention.new(16, 4)(xs).shape == (2, 5, 16)
+    assert nn.TransformerEncoderLayer.new(16, 4, 32)(xs).shape == (2, 5, 16)
+    pe = nn.PositionalEncoding.new(16, 10)
+    assert torch.allclose(pe(Tensor.zeros([1, 3, 16])).torch()[0, 0, 1::2], torch.ones(8))
+    from ferrum_b200.models import MLP, BasicBlock
+
+    assert MLP.new([4, 8, 2])(Tensor.randn([3, 4])).shape == (3, 2) and len(MLP([4, 8, 8, 2])) == 5
+    assert BasicBlock.new(4, 8, 2)(Tensor.randn([1, 4, 8, 8])).shape == (1, 8, 4, 4)
+
+
+def test_step_timer_and_peaks_file():
+    from ferrum_b200.utils import StepTimer
+    from ferrum_b200.utils.profiler import measured_peaks
+
+    lines = []
+    t = StepTimer(every=2, flops_per_sample=1e6, sink=lines.append)
+    for _ in range(4):
+        with t.step(8):
+            pass
+    assert len(lines) == 2 and "samples_per_s" in lines[0] and len(t.history) == 2
+    pk = measured_peaks()
+    assert pk is None or "hbm_gbs" in pk
