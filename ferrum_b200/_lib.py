@@ -96,12 +96,23 @@ _CUDA_SIGS = {
     "fb_rt_error_string": (c_char_p, [I]),
     # gemm
     "fb_gemm_bf16_supported": (I, [P, P, LL, LL]),
-    "fb_gemm_bf16": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
-    "fb_gemm_bf16_2cta": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
+    "fb_gemm_bf16": (I, [P, P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
+    "fb_gemm_bf16_2cta": (I, [P, P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
     "fb_gemm_bf16_2cta_pairs": (I, []),
+    "fb_gemm_bf16_batched": (I, [P, P, P, I, I, I, LL, LL, LL, I, I, LL, LL, LL, LL, LL, LL, I, I, I, I, F, P, P]),
     "fb_gemm_f32_simt": (I, [P, P, P, P, I, I, I, LL, LL, LL, LL, LL, I, I, I, LL, LL, LL, P]),
+    # secondary layers
+    "fb_lstm_gates_fwd": (I, [P, P, P, P, P, P, LL, I, P]),
+    "fb_lstm_gates_bwd": (I, [P, P, P, P, P, P, P, LL, I, P]),
+    "fb_gru_gates_fwd": (I, [P, P, P, P, P, LL, I, P]),
+    "fb_gru_gates_bwd": (I, [P, P, P, P, P, P, LL, I, P]),
+    "fb_im2col": (I, [P, P] + [I] * 14 + [LL, I, P]),
+    "fb_col2im": (I, [P, P] + [I] * 14 + [LL, P]),
+    "fb_pool2d_fwd": (I, [P, P, P] + [I] * 10 + [I, P]),
+    "fb_pool2d_bwd": (I, [P, P, P] + [I] * 10 + [I, P]),
     # elementwise
     "fb_unary_fwd": (I, [P, P, LL, I, F, F, I, P]),
+    "fb_scale_by_device_scalar": (I, [P, P, P, LL, I, P]),
     "fb_unary_bwd": (I, [P, P, P, LL, I, F, F, I, P]),
     "fb_binary_fwd": (I, [P, P, P, I, I, POINTER(LL), POINTER(LL), POINTER(LL), P]),
     "fb_cast": (I, [P, P, LL, I, I, P]),
@@ -113,7 +124,7 @@ _CUDA_SIGS = {
     "fb_colsum": (I, [P, P, LL, LL, I, I, P]),
     # norms
     "fb_layernorm_fwd": (I, [P, P, P, P, P, P, LL, I, F, I, I, P]),
-    "fb_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, LL, I, I, I, I, I, P]),
+    "fb_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, LL, I, I, I, I, I, P]),
     "fb_layernorm_bwd_blocks": (I, [LL, I]),
     "fb_batchnorm_fwd": (I, [P, P, P, P, P, P, P, P, LL, I, F, F, I, P]),
     "fb_batchnorm_bwd": (I, [P, P, P, P, P, P, P, P, LL, I, P]),

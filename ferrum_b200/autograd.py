@@ -32,6 +32,58 @@ def set_grad_enabled(flag: bool) -> None:
     torch.set_grad_enabled(flag)
 
 
+# Names of the core hook layer (autograd_ops.rs:95-183).  The reference wires its tensor type to the tape through a
+# thread-local pair of callbacks; with torch's engine underneath there is nothing to wire, so registration only
+# keeps the callables (they are invoked by ``record_operation`` / ``execute_backward`` for code that drives the
+# hooks by hand) and the enable switch maps onto torch's grad mode.
+is_autograd_enabled = is_grad_enabled
+set_autograd_enabled = set_grad_enabled
+_id_lock = threading.Lock()
+_next_tensor_id = [1]
+
+
+def new_tensor_id() -> int:
+    """Process-wide monotonically increasing tensor id (autograd_ops.rs:133-138)."""
+    with _id_lock:
+        v = _next_tensor_id[0]
+        _next_tensor_id[0] += 1
+        return v
+
+
+class NodeId(int):
+    """Identifier of a graph node (graph.rs:18-30); allocated from a global counter."""
+
+    _counter = [0]
+
+    @classmethod
+    def new(cls) -> "NodeId":
+        with _id_lock:
+            cls._counter[0] += 1
+            return cls(cls._counter[0])
+
+
+def register_autograd_callbacks(record_fn, backward_fn) -> None:
+    _tls.callbacks = (record_fn, backward_fn)
+
+
+def unregister_autograd_callbacks() -> None:
+    _tls.callbacks = None
+
+
+def record_operation(*args, **kwargs):
+    """Forward to the registered record callback, if any (autograd_ops.rs:140-161)."""
+    cb = getattr(_tls, "callbacks", None)
+    return cb[0](*args, **kwargs) if cb and cb[0] is not None and torch.is_grad_enabled() else None
+
+
+def execute_backward(output):
+    """Run the registered backward callback, or the engine's backward (autograd_ops.rs:163-183)."""
+    cb = getattr(_tls, "callbacks", None)
+    if cb and cb[1] is not None:
+        return cb[1](output)
+    return backward(output)
+
+
 class NoGradGuard:
     """RAII-style guard: gradients are not recorded while it is alive (autograd_ops.rs:189-212)."""
 

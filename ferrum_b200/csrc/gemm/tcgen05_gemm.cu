@@ -33,6 +33,7 @@
 #include "../common/ptx.cuh"
 #include "../common/status.h"
 #include "../include/ferrum_kernels.h"
+#include "epilogue.cuh"
 
 namespace fb {
 namespace {
@@ -56,6 +57,7 @@ struct Cfg {
 
 struct GemmArgs {
   void* out;
+  void* out2;  // optional: act'(z) in the layout and dtype of out (bf16 outputs only)
   const float* bias;
   int M, N, K;
   long long ldc;
@@ -65,6 +67,11 @@ struct GemmArgs {
   int beta;
   int32_t* status;
   unsigned long long timeout_ns;
+  // Batched form only: batch = batch_outer x batch_inner slices; the operands' slice strides live in
+  // the 4-D tensor maps, the output's here (elements).  alpha scales the accumulator before bias / act.
+  int batch_inner, batch_total;
+  long long sc_outer, sc_inner;
+  float alpha;
 };
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -101,7 +108,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gsize;
 }
 
-template <int BN>
+template <int BN, bool kBatched>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmArgs p) {
@@ -122,7 +129,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   const int num_m = (p.M + kBM - 1) / kBM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int tiles_per_slice = num_m * num_n;
+  const int num_tiles = kBatched ? tiles_per_slice * p.batch_total : tiles_per_slice;
   const int num_kb = (p.K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
@@ -157,8 +165,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int slice = kBatched ? t / tiles_per_slice : 0;
+        tile_coords(kBatched ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
         const int m0 = m_blk * kBM, n0 = n_blk * BN;
+        const int bz = kBatched ? slice % p.batch_inner : 0, bw = kBatched ? slice / p.batch_inner : 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 1, blockIdx.x, stage);
@@ -169,19 +179,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sb = sa + C::kABytes;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const int k0 = kb * kBK;
-          if (p.a_mn_major) {
+          if constexpr (kBatched) {
+            if (p.a_mn_major) {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c)
-              ptx::tma_load_2d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0);
-          } else {
-            ptx::tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
-          }
-          if (p.b_mn_major) {
+              for (int c = 0; c < kBM / 64; ++c)
+                ptx::tma_load_4d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0, bz, bw);
+            } else {
+              ptx::tma_load_4d(sa, &tma_a, &full_bar[stage], k0, m0, bz, bw);
+            }
+            if (p.b_mn_major) {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              ptx::tma_load_2d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0);
+              for (int c = 0; c < BN / 64; ++c)
+                ptx::tma_load_4d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0, bz, bw);
+            } else {
+              ptx::tma_load_4d(sb, &tma_b, &full_bar[stage], k0, n0, bz, bw);
+            }
           } else {
-            ptx::tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+            if (p.a_mn_major) {
+#pragma unroll
+              for (int c = 0; c < kBM / 64; ++c)
+                ptx::tma_load_2d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0);
+            } else {
+              ptx::tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
+            }
+            if (p.b_mn_major) {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                ptx::tma_load_2d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0);
+            } else {
+              ptx::tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
+            }
           }
           ++issued;
           if (++stage == C::kStages) {
@@ -257,13 +284,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    const int esz = p.out_bf16 ? 2 : 4;
+    const bool vec_ok = ((p.ldc * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        (!kBatched || ((p.sc_outer * esz) % 16 == 0 && (p.sc_inner * esz) % 16 == 0));
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int slice = kBatched ? t / tiles_per_slice : 0;
+      tile_coords(kBatched ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
       const int row = m_blk * kBM + quarter * 32 + lane;
       const int n0 = n_blk * BN;
+      const long long slice_off =
+          kBatched ? (slice / p.batch_inner) * p.sc_outer + (slice % p.batch_inner) * p.sc_inner : 0;
       // The vote keeps the warp converged for the .sync.aligned TMEM loads below.
       const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
       if (!__all_sync(0xffffffffu, ready)) {
@@ -282,18 +313,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if constexpr (kBatched) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+          }
           if (p.bias != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
           }
+          const bool full = (col0 + 32 <= p.N) && vec_ok;
+          if (p.out2 != nullptr) {
+            // value and derivative of the activation, both stored as bf16
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + slice_off + static_cast<long long>(row) * p.ldc + col0;
+            __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + slice_off + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t wv[4], wd[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                float a0, d0, a1, d1;
+                act_both(v[q * 8 + h * 2], p.act, a0, d0);
+                act_both(v[q * 8 + h * 2 + 1], p.act, a1, d1);
+                __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pd = __floats2bfloat162_rn(d0, d1);
+                wv[h] = *reinterpret_cast<uint32_t*>(&pa);
+                wd[h] = *reinterpret_cast<uint32_t*>(&pd);
+              }
+              if (full) {
+                reinterpret_cast<uint4*>(o)[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                reinterpret_cast<uint4*>(o2)[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+              } else {
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  const int c = q * 8 + h * 2;
+                  const __nv_bfloat162 pa = *reinterpret_cast<__nv_bfloat162*>(&wv[h]);
+                  const __nv_bfloat162 pd = *reinterpret_cast<__nv_bfloat162*>(&wd[h]);
+                  if (col0 + c < p.N) { o[c] = pa.x; o2[c] = pd.x; }
+                  if (col0 + c + 1 < p.N) { o[c + 1] = pa.y; o2[c + 1] = pd.y; }
+                }
+              }
+            }
+          } else {
           if (p.act != FB_ACT_NONE) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
           }
-          const bool full = (col0 + 32 <= p.N) && vec_ok;
           if (p.out_bf16) {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            __nv_bfloat16* o =
+                reinterpret_cast<__nv_bfloat16*>(p.out) + slice_off + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
               uint4* o4 = reinterpret_cast<uint4*>(o);
 #pragma unroll
@@ -311,7 +378,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
             }
           } else {
-            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            float* o = reinterpret_cast<float*>(p.out) + slice_off + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
               float4* o4 = reinterpret_cast<float4*>(o);
 #pragma unroll
@@ -328,6 +395,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
             }
           }
+          }  // out2 == nullptr
         }
       }
       ptx::tc_fence_before();
@@ -381,6 +449,31 @@ bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long oute
   return r == CUDA_SUCCESS;
 }
 
+// 4-D form of the same map for batched operands: dims {inner, outer, batch_inner, batch_outer} with the two slice
+// strides in elements; box = 64 x box_outer x 1 x 1, so a tile never crosses a slice and rows past the slice's
+// extent read zeros.
+bool make_map_batched(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld,
+                      int box_outer, int batch_inner, int batch_outer, long long s_inner, long long s_outer) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  if (batch_inner > 1 && (s_inner <= 0 || (s_inner * 2) % 16 != 0)) return false;
+  if (batch_outer > 1 && (s_outer <= 0 || (s_outer * 2) % 16 != 0)) return false;
+  // A dimension of extent 1 still needs a legal (non-zero, 16-byte multiple) stride.
+  const long long si = batch_inner > 1 ? s_inner : ld * outer + ((8 - (ld * outer) % 8) % 8);
+  const long long so = batch_outer > 1 ? s_outer : si * batch_inner;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer),
+                        static_cast<cuuint64_t>(batch_inner), static_cast<cuuint64_t>(batch_outer)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(si) * 2,
+                           static_cast<cuuint64_t>(so) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_outer), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -391,21 +484,23 @@ int sm_count() {
   return n;
 }
 
-template <int BN>
+template <int BN, bool kBatched>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kBatched>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int num_tiles = ((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN);
+  const long long tiles = static_cast<long long>((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) *
+                          (kBatched ? args.batch_total : 1);
+  if (tiles > 0x7fffffffll) return -1;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (num_tiles < grid) grid = num_tiles;
-  gemm_bf16_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  gemm_bf16_kernel<BN, kBatched><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -417,11 +512,12 @@ extern "C" int fb_gemm_bf16_supported(const void* a, const void* b, long long ld
          ((lda * 2) % 16 == 0) && ((ldb * 2) % 16 == 0);
 }
 
-extern "C" int fb_gemm_bf16(const void* a, const void* b, void* out, const float* bias, int M, int N, int K,
+extern "C" int fb_gemm_bf16(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
                             long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
                             int out_bf16, int act, int beta, int max_ctas, int32_t* status, cudaStream_t stream) {
   using namespace fb;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if (out2 != nullptr && (!out_bf16 || beta)) return -1;
   const bool small_n = N <= 128;
   const int bn = small_n ? 128 : 256;
   CUtensorMap ma, mb;
@@ -438,6 +534,7 @@ extern "C" int fb_gemm_bf16(const void* a, const void* b, void* out, const float
   if (!ok) return -2;
   GemmArgs args;
   args.out = out;
+  args.out2 = out2;
   args.bias = bias;
   args.M = M;
   args.N = N;
@@ -450,5 +547,57 @@ extern "C" int fb_gemm_bf16(const void* a, const void* b, void* out, const float
   args.beta = beta;
   args.status = status;
   args.timeout_ns = 2000000000ull;
-  return small_n ? launch<128>(ma, mb, args, max_ctas, stream) : launch<256>(ma, mb, args, max_ctas, stream);
+  args.batch_inner = 1;
+  args.batch_total = 1;
+  args.sc_outer = args.sc_inner = 0;
+  args.alpha = 1.f;
+  return small_n ? launch<128, false>(ma, mb, args, max_ctas, stream)
+                 : launch<256, false>(ma, mb, args, max_ctas, stream);
+}
+
+// Batched product over batch_outer x batch_inner slices:  D[s] = alpha * A[s] * B[s]^T  (optionally += D[s]).
+// Every operand has its own pair of slice strides (elements), so [B, S, H, D] activations are used in place
+// (slice (b, h) at b * S*H*D + h * D with row pitch H*D) as well as plain [batch, rows, cols] arrays.
+extern "C" int fb_gemm_bf16_batched(const void* a, const void* b, void* out, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldc, int batch_outer, int batch_inner,
+                                    long long sa_outer, long long sa_inner, long long sb_outer, long long sb_inner,
+                                    long long sc_outer, long long sc_inner, int a_mn_major, int b_mn_major,
+                                    int out_bf16, int beta, float alpha, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0 || batch_outer <= 0 || batch_inner <= 0) return -1;
+  const bool small_n = N <= 128;
+  const int bn = small_n ? 128 : 256;
+  CUtensorMap ma, mb;
+  bool ok;
+  if (a_mn_major)
+    ok = make_map_batched(&ma, a, M, K, lda, 64, batch_inner, batch_outer, sa_inner, sa_outer);
+  else
+    ok = make_map_batched(&ma, a, K, M, lda, kBM, batch_inner, batch_outer, sa_inner, sa_outer);
+  if (!ok) return -2;
+  if (b_mn_major)
+    ok = make_map_batched(&mb, b, N, K, ldb, 64, batch_inner, batch_outer, sb_inner, sb_outer);
+  else
+    ok = make_map_batched(&mb, b, K, N, ldb, bn, batch_inner, batch_outer, sb_inner, sb_outer);
+  if (!ok) return -2;
+  GemmArgs args;
+  args.out = out;
+  args.out2 = nullptr;
+  args.bias = nullptr;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = out_bf16;
+  args.act = FB_ACT_NONE;
+  args.beta = beta;
+  args.status = status;
+  args.timeout_ns = 2000000000ull;
+  args.batch_inner = batch_inner;
+  args.batch_total = batch_inner * batch_outer;
+  args.sc_outer = sc_outer;
+  args.sc_inner = sc_inner;
+  args.alpha = alpha;
+  return small_n ? launch<128, true>(ma, mb, args, 0, stream) : launch<256, true>(ma, mb, args, 0, stream);
 }

@@ -28,25 +28,33 @@
 #include "../common/ptx.cuh"
 #include "../common/status.h"
 #include "../include/ferrum_kernels.h"
+#include "epilogue.cuh"
 
 namespace fb {
 namespace {
 
 constexpr int kBM = 128;       // rows per CTA; the pair covers 256
-constexpr int kBN = 256;       // columns per pair; each CTA stages 128 of them
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
-constexpr int kStages = 6;
 constexpr int kGroupM = 8;     // pair-tiles (256 rows) per rasterisation group
 constexpr int kABytes = kBM * kBK * 2;          // 16 KB
-constexpr int kBBytes = (kBN / 2) * kBK * 2;    // 16 KB
-constexpr int kStageBytes = kABytes + kBBytes;  // 32 KB per CTA
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-constexpr int kTmemCols = 512;
+
+// BN = columns per pair (each CTA stages half of them).  256 is the high-intensity shape; 128 halves the
+// tile so that outputs whose 256 x 256 tile count fills the last wave badly (a 4096 x 4096 weight gradient
+// is 256 tiles = 3.46 waves of 74 pairs) still keep every pair busy (512 tiles = 6.92 waves).
+template <int BN>
+struct Cfg2 {
+  static constexpr int kBBytes = (BN / 2) * kBK * 2;          // 16 KB / 8 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;       // 32 KB / 24 KB per CTA
+  static constexpr int kStages = BN == 256 ? 6 : 8;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kTmemCols = 2 * BN;                    // two accumulators
+};
 
 struct Args2 {
   void* out;
+  void* out2;  // optional: act'(z) in the layout and dtype of out (bf16 outputs only)
   const float* bias;
   int M, N, K;
   long long ldc;
@@ -92,9 +100,14 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
   n_blk = r / gsize;
 }
 
+template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const Args2 p) {
+  constexpr int kBN = BN;
+  constexpr int kStages = Cfg2<BN>::kStages;
+  constexpr int kStageBytes = Cfg2<BN>::kStageBytes;
+  constexpr int kTmemCols = Cfg2<BN>::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* bar_base = smem + kStages * kStageBytes;
@@ -273,11 +286,42 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             for (int i = 0; i < 32; ++i)
               if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
           }
+          const bool full = (col0 + 32 <= p.N) && vec_ok;
+          if (p.out2 != nullptr) {
+            // value and derivative of the activation, both stored as bf16
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + 0 + static_cast<long long>(row) * p.ldc + col0;
+            __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + 0 + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t wv[4], wd[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                float a0, d0, a1, d1;
+                act_both(v[q * 8 + h * 2], p.act, a0, d0);
+                act_both(v[q * 8 + h * 2 + 1], p.act, a1, d1);
+                __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pd = __floats2bfloat162_rn(d0, d1);
+                wv[h] = *reinterpret_cast<uint32_t*>(&pa);
+                wd[h] = *reinterpret_cast<uint32_t*>(&pd);
+              }
+              if (full) {
+                reinterpret_cast<uint4*>(o)[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                reinterpret_cast<uint4*>(o2)[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+              } else {
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  const int c = q * 8 + h * 2;
+                  const __nv_bfloat162 pa = *reinterpret_cast<__nv_bfloat162*>(&wv[h]);
+                  const __nv_bfloat162 pd = *reinterpret_cast<__nv_bfloat162*>(&wd[h]);
+                  if (col0 + c < p.N) { o[c] = pa.x; o2[c] = pd.x; }
+                  if (col0 + c + 1 < p.N) { o[c + 1] = pa.y; o2[c + 1] = pd.y; }
+                }
+              }
+            }
+          } else {
           if (p.act != FB_ACT_NONE) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = apply_act2(v[i], p.act);
           }
-          const bool full = (col0 + 32 <= p.N) && vec_ok;
           if (p.out_bf16) {
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
@@ -314,6 +358,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                 if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
             }
           }
+          }  // out2 == nullptr
         }
       }
       ptx::tc_fence_before();
@@ -368,11 +413,13 @@ bool make_map2(CUtensorMap* map, const void* ptr, long long inner, long long out
 }
 
 // Number of CTA pairs that can be resident at once (0 if cluster launch is unavailable).
+template <int BN>
 int max_pairs() {
+  constexpr int kSmemBytes = Cfg2<BN>::kSmemBytes;
   static int n = -1;
   if (n < 0) {
     n = 0;
-    if (cudaFuncSetAttribute(gemm_bf16_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+    if (cudaFuncSetAttribute(gemm_bf16_2cta_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
         cudaSuccess) {
       cudaGetLastError();
       return n;
@@ -389,33 +436,51 @@ int max_pairs() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_2cta_kernel, &cfg) == cudaSuccess) n = clusters;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_2cta_kernel<BN>, &cfg) == cudaSuccess) n = clusters;
     else cudaGetLastError();
   }
   return n;
 }
 
+// Fraction of pair-slots doing useful work when `tiles` tiles run in waves of `pairs`.
+double wave_efficiency(long long tiles, int pairs) {
+  const long long waves = (tiles + pairs - 1) / pairs;
+  return static_cast<double>(tiles) / static_cast<double>(waves * pairs);
+}
+
+template <int BN>
+int launch2(const void* a, const void* b, Args2& args, long long lda, long long ldb, int pairs, long long num_tiles,
+            cudaStream_t stream) {
+  CUtensorMap ma, mb;
+  bool ok = args.a_mn_major ? make_map2(&ma, a, args.M, args.K, lda, 64) : make_map2(&ma, a, args.K, args.M, lda, kBM);
+  if (!ok) return -2;
+  ok = args.b_mn_major ? make_map2(&mb, b, args.N, args.K, ldb, 64) : make_map2(&mb, b, args.K, args.N, ldb, BN / 2);
+  if (!ok) return -2;
+  if (num_tiles < pairs) pairs = static_cast<int>(num_tiles);
+  gemm_bf16_2cta_kernel<BN><<<2 * pairs, kThreads, Cfg2<BN>::kSmemBytes, stream>>>(ma, mb, args);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace
 }  // namespace fb
 
-extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs(); }
+extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs<256>(); }
 
 // Same arguments as fb_gemm_bf16.  Returns -3 when CTA pairs cannot be launched on this device.
-extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, const float* bias, int M, int N, int K,
+// Picks the 256- or the 128-column tile by how well each fills its last wave.
+extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N,
+                                 int K,
                                  long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
                                  int out_bf16, int act, int beta, int max_ctas, int32_t* status,
                                  cudaStream_t stream) {
   using namespace fb;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  const int pairs_avail = max_pairs();
+  if (out2 != nullptr && (!out_bf16 || beta)) return -1;
+  const int pairs_avail = max_pairs<256>();
   if (pairs_avail <= 0) return -3;
-  CUtensorMap ma, mb;
-  bool ok = a_mn_major ? make_map2(&ma, a, M, K, lda, 64) : make_map2(&ma, a, K, M, lda, kBM);
-  if (!ok) return -2;
-  ok = b_mn_major ? make_map2(&mb, b, N, K, ldb, 64) : make_map2(&mb, b, K, N, ldb, kBN / 2);
-  if (!ok) return -2;
   Args2 args;
   args.out = out;
+  args.out2 = out2;
   args.bias = bias;
   args.M = M;
   args.N = N;
@@ -428,10 +493,13 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, const 
   args.beta = beta;
   args.status = status;
   args.timeout_ns = 2000000000ull;
-  const int num_tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
   int pairs = pairs_avail;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
-  if (num_tiles < pairs) pairs = num_tiles;
-  gemm_bf16_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(ma, mb, args);
-  return static_cast<int>(cudaGetLastError());
+  const long long m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const long long tiles256 = m_tiles * ((N + 255) / 256), tiles128 = m_tiles * ((N + 127) / 128);
+  // The narrow tile re-reads A twice as often, so it has to win by a margin.
+  const bool narrow = max_pairs<128>() >= pairs &&
+                      0.96 * wave_efficiency(tiles128, pairs) > wave_efficiency(tiles256, pairs);
+  return narrow ? launch2<128>(a, b, args, lda, ldb, pairs, tiles128, stream)
+                : launch2<256>(a, b, args, lda, ldb, pairs, tiles256, stream);
 }

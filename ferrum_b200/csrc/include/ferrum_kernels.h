@@ -45,9 +45,25 @@ enum { FB_LOSS_MSE = 0, FB_LOSS_BCE = 1, FB_LOSS_L1 = 2, FB_LOSS_SMOOTH_L1 = 3 }
 // lda/ldb are the row pitches (elements) of the stored matrices: a K-major
 // operand is stored [rows=M|N][K], an MN-major operand is stored [rows=K][M|N].
 int fb_gemm_bf16_supported(const void* a, const void* b, long long lda, long long ldb);
-int fb_gemm_bf16(const void* a, const void* b, void* out, const float* bias, int M, int N, int K, long long lda,
-                 long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_bf16, int act, int beta,
-                 int max_ctas, int32_t* status, cudaStream_t stream);
+// out2 (optional, bf16 outputs without accumulate): receives act'(A*B^T + bias) in the layout of out, for
+// blocks whose backward would otherwise re-evaluate the activation.
+int fb_gemm_bf16(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
+                 long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_bf16, int act,
+                 int beta, int max_ctas, int32_t* status, cudaStream_t stream);
+// CTA-pair variant (tcgen05 cta_group::2; 256 x 256 or 256 x 128 tiles on two SMs, chosen by wave fill); same
+// arguments.  Returns -3 where clusters of two CTAs cannot be scheduled.  fb_gemm_bf16_2cta_pairs() = resident pairs.
+int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
+                      long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_bf16,
+                      int act, int beta, int max_ctas, int32_t* status, cudaStream_t stream);
+int fb_gemm_bf16_2cta_pairs(void);
+// Batched form over batch_outer x batch_inner slices: out[s] = alpha * A[s] * B[s]^T (+= out[s] when beta).
+// Each operand carries its own (outer, inner) slice strides in elements, so head-interleaved [B, S, H, D]
+// activations are multiplied in place.  Slice strides of A and B must be multiples of 8 elements.
+int fb_gemm_bf16_batched(const void* a, const void* b, void* out, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int batch_outer, int batch_inner, long long sa_outer, long long sa_inner,
+                         long long sb_outer, long long sb_inner, long long sc_outer, long long sc_inner,
+                         int a_mn_major, int b_mn_major, int out_bf16, int beta, float alpha, int32_t* status,
+                         cudaStream_t stream);
 // fp32 SIMT GEMM with arbitrary element strides (parity runs, odd shapes):
 // out[m,n] = act(sum_k A[m*sam + k*sak] * B[k*sbk + n*sbn] + bias[n]) (+= out when beta).
 int fb_gemm_f32_simt(const float* a, const float* b, float* out, const float* bias, int M, int N, int K,
@@ -59,6 +75,9 @@ int fb_gemm_f32_simt(const float* a, const float* b, float* out, const float* bi
 int fb_unary_fwd(const void* x, void* y, long long n, int op, float alpha, float beta, int dtype,
                  cudaStream_t stream);
 // dx = dy * f'(.) ; `saved` is x or y depending on the op (see elementwise.cu).
+// y = x * (*scalar) with the factor read on the device (fp32 or bf16 data).
+int fb_scale_by_device_scalar(const void* x, const float* scalar, void* y, long long n, int dtype,
+                              cudaStream_t stream);
 int fb_unary_bwd(const void* dy, const void* saved, void* dx, long long n, int op, float alpha, float beta,
                  int dtype, cudaStream_t stream);
 // Broadcasting binary op over up to 6 dims; strides in elements, 0 = broadcast.
@@ -84,9 +103,11 @@ int fb_colsum(const void* x, float* out, long long rows, long long cols, int dty
 int fb_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
                      long long rows, int cols, float eps, int pre_act, int dtype, cudaStream_t stream);
 // stats = [3][cols]: d_gamma, d_beta, column sum of dx (accumulated into); partial = [nblk][3][cols] workspace.
-int fb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
-                     void* dx, float* partial, float* stats, long long rows, int cols, int pre_act, int dtype,
-                     int nblk, int want_colsum, cudaStream_t stream);
+// act_grad (optional, dtype of x; excludes pre_act): x holds act(z) and act_grad holds act'(z) as written by
+// the producing GEMM's epilogue; dx is then the gradient of z.
+int fb_layernorm_bwd(const void* dy, const void* x, const void* act_grad, const float* gamma, const float* mean,
+                     const float* rstd, void* dx, float* partial, float* stats, long long rows, int cols,
+                     int pre_act, int dtype, int nblk, int want_colsum, cudaStream_t stream);
 int fb_layernorm_bwd_blocks(long long rows, int cols);
 int fb_batchnorm_fwd(const float* x, const float* gamma, const float* beta, float* y, float* save_mean,
                      float* save_rstd, float* running_mean, float* running_var, long long rows, int cols,
@@ -108,6 +129,29 @@ int fb_loss_fwd(const float* pred, const float* target, float* out, long long n,
                 cudaStream_t stream);
 int fb_loss_bwd(const float* pred, const float* target, const float* gout, float* dpred, long long n, int kind,
                 float scale, cudaStream_t stream);
+
+// ---- secondary layers: recurrent gates, convolution lowering, pooling ---------
+// LSTM: pre-activations xi + hh laid out [B, 4H] as (input, forget, cell, output); `gates` receives the
+// activated gates for the backward pass.  dh / dc may be NULL (no gradient from that output).
+int fb_lstm_gates_fwd(const float* xi, const float* hh, const float* c_prev, float* h_out, float* c_out,
+                      float* gates, long long B, int H, cudaStream_t stream);
+int fb_lstm_gates_bwd(const float* dh, const float* dc, const float* gates, const float* c_prev, const float* c_out,
+                      float* dpre, float* dc_prev, long long B, int H, cudaStream_t stream);
+// GRU: xi, hh are [B, 3H] as (reset, update, new); `saved` is [B, 4H] (r, z, n, hn).
+int fb_gru_gates_fwd(const float* xi, const float* hh, const float* h_prev, float* h_out, float* saved, long long B,
+                     int H, cudaStream_t stream);
+int fb_gru_gates_bwd(const float* dh, const float* saved, const float* h_prev, float* dxi, float* dhh,
+                     float* dh_prev, long long B, int H, cudaStream_t stream);
+// Window matrix of a convolution: cols[B*Ho*Wo, C*kh*kw] (row pitch ldk elements, fp32 or bf16) and its gradient.
+int fb_im2col(const float* x, void* cols, int B, int C, int H, int W, int kh, int kw, int Ho, int Wo, int sh, int sw,
+              int ph, int pw, int dh, int dw, long long ldk, int out_dtype, cudaStream_t stream);
+int fb_col2im(const float* dcols, float* dx, int B, int C, int H, int W, int kh, int kw, int Ho, int Wo, int sh,
+              int sw, int ph, int pw, int dh, int dw, long long ldk, cudaStream_t stream);
+// 2-D pooling without padding; op 0 = max (arg receives the winner's offset inside its plane), 1 = average.
+int fb_pool2d_fwd(const float* x, float* y, int* arg, int B, int C, int H, int W, int kh, int kw, int Ho, int Wo,
+                  int sh, int sw, int op, cudaStream_t stream);
+int fb_pool2d_bwd(const float* dy, const int* arg, float* dx, int B, int C, int H, int W, int kh, int kw, int Ho,
+                  int Wo, int sh, int sw, int op, cudaStream_t stream);
 
 // ---- dropout / embedding / collate ---------------------------------------------
 int fb_dropout_fwd(const void* x, void* y, uint8_t* mask, long long n, float p, unsigned long long seed,

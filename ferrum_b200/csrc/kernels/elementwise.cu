@@ -190,12 +190,24 @@ __global__ void unary_fwd_bf16(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (aligned) {
-    for (long long i = tid; i < n8; i += stride) {
+    // two independent 16-byte loads per thread per trip: bf16 rows carry half the bytes of fp32 ones, and
+    // the bytes in flight per SM are what buys HBM bandwidth
+    for (long long i = tid; i < n8; i += 2 * stride) {
+      const long long j = i + stride;
+      const uint4 r0 = reinterpret_cast<const uint4*>(x)[i];
+      uint4 r1 = make_uint4(0u, 0u, 0u, 0u);
+      if (j < n8) r1 = reinterpret_cast<const uint4*>(x)[j];
       float f[8];
-      bf16x8_to_f32(reinterpret_cast<const uint4*>(x)[i], f);
+      bf16x8_to_f32(r0, f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], op, a, b);
       reinterpret_cast<uint4*>(y)[i] = f32_to_bf16x8(f);
+      if (j < n8) {
+        bf16x8_to_f32(r1, f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], op, a, b);
+        reinterpret_cast<uint4*>(y)[j] = f32_to_bf16x8(f);
+      }
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
       y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), op, a, b));
@@ -214,13 +226,27 @@ __global__ void unary_bwd_bf16(const __nv_bfloat16* __restrict__ dy, const __nv_
       ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dx)) & 15) ==
       0;
   if (aligned) {
-    for (long long i = tid; i < n8; i += stride) {
+    for (long long i = tid; i < n8; i += 2 * stride) {
+      const long long j = i + stride;
+      const uint4 rg0 = reinterpret_cast<const uint4*>(dy)[i], rv0 = reinterpret_cast<const uint4*>(sp)[i];
+      uint4 rg1 = make_uint4(0u, 0u, 0u, 0u), rv1 = rg1;
+      if (j < n8) {
+        rg1 = reinterpret_cast<const uint4*>(dy)[j];
+        rv1 = reinterpret_cast<const uint4*>(sp)[j];
+      }
       float g[8], v[8];
-      bf16x8_to_f32(reinterpret_cast<const uint4*>(dy)[i], g);
-      bf16x8_to_f32(reinterpret_cast<const uint4*>(sp)[i], v);
+      bf16x8_to_f32(rg0, g);
+      bf16x8_to_f32(rv0, v);
 #pragma unroll
       for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], op, a, b);
       reinterpret_cast<uint4*>(dx)[i] = f32_to_bf16x8(g);
+      if (j < n8) {
+        bf16x8_to_f32(rg1, g);
+        bf16x8_to_f32(rv1, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], op, a, b);
+        reinterpret_cast<uint4*>(dx)[j] = f32_to_bf16x8(g);
+      }
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
       dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
@@ -374,12 +400,42 @@ __global__ void transpose_kernel(const T* __restrict__ s, T* __restrict__ d, int
   }
 }
 
+// y = x * (*scalar): the incoming gradient of a scalar loss applied to a stored gradient, without a host read.
+template <typename T>
+__global__ void scale_by_scalar_kernel(const T* __restrict__ x, const float* __restrict__ scalar, T* __restrict__ y,
+                                       long long n) {
+  const float sc = *scalar;
+  constexpr int kPer = 16 / sizeof(T);
+  const long long nv = n / kPer;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (aligned) {
+    for (long long i = tid; i < nv; i += stride) {
+      if constexpr (sizeof(T) == 2) {
+        float f[8];
+        bf16x8_to_f32(reinterpret_cast<const uint4*>(x)[i], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] *= sc;
+        reinterpret_cast<uint4*>(y)[i] = f32_to_bf16x8(f);
+      } else {
+        float4 v = reinterpret_cast<const float4*>(x)[i];
+        v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+        reinterpret_cast<float4*>(y)[i] = v;
+      }
+    }
+    for (long long i = nv * kPer + tid; i < n; i += stride) y[i] = static_cast<T>(static_cast<float>(x[i]) * sc);
+  } else {
+    for (long long i = tid; i < n; i += stride) y[i] = static_cast<T>(static_cast<float>(x[i]) * sc);
+  }
+}
+
 int grid_for(long long work_items, int block) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   long long need = (work_items + block - 1) / block;
-  const long long cap = static_cast<long long>(sms) * 8;
+  const long long cap = static_cast<long long>(sms) * 6;  // 6 x 256 threads: what 40-register kernels keep resident
   if (need > cap) need = cap;
   if (need < 1) need = 1;
   return static_cast<int>(need);
@@ -499,5 +555,19 @@ extern "C" int fb_transpose_2d(const void* src, void* dst, int rows, int cols, i
   } else {
     return -1;
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_scale_by_device_scalar(const void* x, const float* scalar, void* y, long long n, int dtype,
+                                         cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dtype == FB_DT_F32)
+    scale_by_scalar_kernel<float><<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(
+        static_cast<const float*>(x), scalar, static_cast<float*>(y), n);
+  else if (dtype == FB_DT_BF16)
+    scale_by_scalar_kernel<__nv_bfloat16><<<grid_for((n + 7) / 8, 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), scalar, static_cast<__nv_bfloat16*>(y), n);
+  else
+    return -1;
   return static_cast<int>(cudaGetLastError());
 }

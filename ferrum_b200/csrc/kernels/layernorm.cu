@@ -217,9 +217,10 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
 // written once to partial[blockIdx][3][cols].
 template <typename T, int TPR, int K>
 __global__ void __launch_bounds__(256, 2)
-ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
-              const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
-              float* __restrict__ partial, long long rows, int cols, int pre_act, int want_colsum) {
+ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ act_grad,
+              const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ rstd,
+              T* __restrict__ dx, float* __restrict__ partial, long long rows, int cols, int pre_act,
+              int want_colsum) {
   __shared__ float smem[8][8];
   constexpr int kRowsPerBlock = 256 / TPR;
   constexpr bool kFast = V8<T>::kFastMath;
@@ -300,7 +301,16 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
           const float h = (a - mu) * rs;
           const float d = gv[i] * (gamma ? w[i] : 1.f);
           o[i] = rs * (d - m1 - h * m2) * da;
-          if (want_colsum) acc_c[k][i] += o[i];
+        }
+        if (act_grad != nullptr) {  // x holds act(z); its derivative was stored by the producer
+          float ag[8];
+          V8<T>::unpack(V8<T>::ld(act_grad + row * cols + vi * 8), ag);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] *= ag[i];
+        }
+        if (want_colsum) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc_c[k][i] += o[i];
         }
         V8<T>::st(dx + row * cols + vi * 8, o);
       }
@@ -352,6 +362,138 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __
       }
       __threadfence_block();
     }
+  }
+}
+
+// Backward for rows of 2056..4096 bf16 elements whose activation derivative (if any) is given as a tensor:
+// pure streaming arithmetic, so the kernel is organised around bytes in flight.  One 512-thread block per
+// SM walks its rows one at a time; a thread owns ONE 16-byte vector of each operand, keeps the loads of the
+// next two rows outstanding while it works on the current one, and a row costs a single __syncthreads (the
+// two row sums travel together through a double-buffered shared-memory slot).  gamma and the three column
+// accumulators stay in registers for the whole kernel.
+__global__ void __launch_bounds__(512, 1)
+ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ act_grad, const float* __restrict__ gamma,
+                   const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ partial, long long rows, int cols, int want_colsum) {
+  using V = V8<__nv_bfloat16>;
+  __shared__ float2 red[2][16];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nvec = cols >> 3;
+  const bool has = t < nvec;
+  const float inv_n = 1.f / static_cast<float>(cols);
+  const long long stride = gridDim.x;
+  const bool use_ag = act_grad != nullptr;
+
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = 1.f;
+  if (has && gamma != nullptr) ld8f(gamma + t * 8, w);
+  float acc_g[8], acc_b[8], acc_c[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc_g[i] = acc_b[i] = acc_c[i] = 0.f;
+
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 g0 = zero, x0 = zero, a0 = zero, g1 = zero, x1 = zero, a1 = zero, g2 = zero, x2 = zero, a2 = zero;
+  float mu0 = 0.f, rs0 = 0.f, mu1 = 0.f, rs1 = 0.f, mu2 = 0.f, rs2 = 0.f;
+  long long row = blockIdx.x;
+  if (row < rows) {
+    mu0 = mean[row];
+    rs0 = rstd[row];
+    if (has) {
+      const long long o = row * cols + t * 8;
+      g0 = V::ld(dy + o);
+      x0 = V::ld(x + o);
+      if (use_ag) a0 = V::ld(act_grad + o);
+    }
+  }
+  if (row + stride < rows) {
+    const long long r = row + stride;
+    mu1 = mean[r];
+    rs1 = rstd[r];
+    if (has) {
+      const long long o = r * cols + t * 8;
+      g1 = V::ld(dy + o);
+      x1 = V::ld(x + o);
+      if (use_ag) a1 = V::ld(act_grad + o);
+    }
+  }
+  int par = 0;
+  for (; row < rows; row += stride) {
+    {  // third row in flight
+      const long long r = row + 2 * stride;
+      if (r < rows) {
+        mu2 = mean[r];
+        rs2 = rstd[r];
+        if (has) {
+          const long long o = r * cols + t * 8;
+          g2 = V::ld(dy + o);
+          x2 = V::ld(x + o);
+          if (use_ag) a2 = V::ld(act_grad + o);
+        }
+      }
+    }
+    float gv[8], h[8];
+    V::unpack(g0, gv);
+    V::unpack(x0, h);
+    const float shift = -mu0 * rs0;
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      h[i] = fmaf(h[i], rs0, shift);
+      acc_b[i] += gv[i];
+      acc_g[i] = fmaf(gv[i], h[i], acc_g[i]);
+      gv[i] *= w[i];  // d = dy * gamma
+      s1 += gv[i];
+      s2 = fmaf(gv[i], h[i], s2);
+    }
+    if (!has) s1 = s2 = 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane == 0) red[par][warp] = make_float2(s1, s2);
+    __syncthreads();
+    float m1 = 0.f, m2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 v = red[par][i];
+      m1 += v.x;
+      m2 += v.y;
+    }
+    m1 *= inv_n;
+    m2 *= inv_n;
+    if (has) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rs0 * (gv[i] - m1 - h[i] * m2);
+      if (use_ag) {
+        float ag[8];
+        V::unpack(a0, ag);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] *= ag[i];
+      }
+      if (want_colsum) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc_c[i] += o[i];
+      }
+      V::st(dx + row * cols + t * 8, o);
+    }
+    g0 = g1; x0 = x1; a0 = a1; mu0 = mu1; rs0 = rs1;
+    g1 = g2; x1 = x2; a1 = a2; mu1 = mu2; rs1 = rs2;
+    par ^= 1;
+  }
+  if (has) {
+    float* pg = partial + static_cast<long long>(blockIdx.x) * 3 * cols + t * 8;
+    float* pb = pg + cols;
+    float* pc = pb + cols;
+    *reinterpret_cast<float4*>(pg) = make_float4(acc_g[0], acc_g[1], acc_g[2], acc_g[3]);
+    *reinterpret_cast<float4*>(pg + 4) = make_float4(acc_g[4], acc_g[5], acc_g[6], acc_g[7]);
+    *reinterpret_cast<float4*>(pb) = make_float4(acc_b[0], acc_b[1], acc_b[2], acc_b[3]);
+    *reinterpret_cast<float4*>(pb + 4) = make_float4(acc_b[4], acc_b[5], acc_b[6], acc_b[7]);
+    *reinterpret_cast<float4*>(pc) = make_float4(acc_c[0], acc_c[1], acc_c[2], acc_c[3]);
+    *reinterpret_cast<float4*>(pc + 4) = make_float4(acc_c[4], acc_c[5], acc_c[6], acc_c[7]);
   }
 }
 
@@ -423,9 +565,10 @@ __global__ void ln_fwd_generic(const T* __restrict__ x, const float* __restrict_
 
 // stats = [3][cols] (d_gamma, d_beta, column sum of dx), accumulated into with atomics.
 template <typename T>
-__global__ void ln_bwd_generic(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
-                               const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
-                               float* __restrict__ stats, long long rows, int cols, int pre_act, int want_colsum) {
+__global__ void ln_bwd_generic(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ act_grad,
+                               const float* __restrict__ gamma, const float* __restrict__ mean,
+                               const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ stats,
+                               long long rows, int cols, int pre_act, int want_colsum) {
   __shared__ float smem[8][8];
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mu = mean[row], rs = rstd[row];
@@ -449,7 +592,8 @@ __global__ void ln_bwd_generic(const T* __restrict__ dy, const T* __restrict__ x
       if (pre_act == FB_ACT_GELU) gelu_both<false>(raw, a, da);
       const float h = (a - mu) * rs;
       const float d = V8<T>::ld1(dy + row * cols + c) * (gamma ? gamma[c] : 1.f);
-      const float o = rs * (d - m1 - h * m2) * da;
+      float o = rs * (d - m1 - h * m2) * da;
+      if (act_grad != nullptr) o *= V8<T>::ld1(act_grad + row * cols + c);
       if (want_colsum) atomicAdd(stats + 2 * cols + c, o);
       V8<T>::st1(dx + row * cols + c, o);
     }
@@ -513,18 +657,41 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
 }
 
 template <typename T>
-int bwd_t(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
-          float* partial, float* stats, long long rows, int cols, int pre_act, int nblk, int want_colsum,
-          cudaStream_t st) {
+bool launch_wide(const T*, const T*, const T*, const float*, const float*, const float*, T*, float*, long long, int,
+                 int, int, cudaStream_t) {
+  return false;
+}
+// bf16 rows of 257..512 vectors with no activation to re-evaluate: the streaming kernel, one block per SM.
+template <>
+bool launch_wide<__nv_bfloat16>(const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* ag,
+                                const float* gamma, const float* mean, const float* rstd, __nv_bfloat16* dx,
+                                float* partial, long long rows, int cols, int blocks, int want_colsum,
+                                cudaStream_t st) {
+  ln_bwd_wide_kernel<<<blocks, 512, 0, st>>>(dy, x, ag, gamma, mean, rstd, dx, partial, rows, cols, want_colsum);
+  return true;
+}
+
+template <typename T>
+int bwd_t(const void* dy, const void* x, const void* act_grad, const float* gamma, const float* mean,
+          const float* rstd, void* dx, float* partial, float* stats, long long rows, int cols, int pre_act, int nblk,
+          int want_colsum, cudaStream_t st) {
   const T* dyp = static_cast<const T*>(dy);
   const T* xp = static_cast<const T*>(x);
+  const T* agp = static_cast<const T*>(act_grad);
   T* dxp = static_cast<T*>(dx);
   Geo g;
   const bool fast = nblk > 0 && partial != nullptr && geometry(cols, &g) && aligned16(dy, x, dx, gamma) &&
-                    aligned16(partial, stats, nullptr, nullptr);
+                    aligned16(partial, stats, act_grad, nullptr);
   if (fast) {
+    int used = nblk;
+    const int nvec = cols / 8;
+    const int wide_blocks = nblk < sm_count() ? nblk : sm_count();
+    if (pre_act == FB_ACT_NONE && nvec > 256 && nvec <= 512 &&
+        launch_wide<T>(dyp, xp, agp, gamma, mean, rstd, dxp, partial, rows, cols, wide_blocks, want_colsum, st)) {
+      used = wide_blocks;
+    } else {
 #define FB_LN_BWD(TPR, K) \
-  ln_bwd_kernel<T, TPR, K><<<nblk, 256, 0, st>>>(dyp, xp, gamma, mean, rstd, dxp, partial, rows, cols, pre_act, \
+  ln_bwd_kernel<T, TPR, K><<<nblk, 256, 0, st>>>(dyp, xp, agp, gamma, mean, rstd, dxp, partial, rows, cols, pre_act, \
                                                  want_colsum)
     if (g.tpr == 32 && g.k == 1) FB_LN_BWD(32, 1);
     else if (g.tpr == 32) FB_LN_BWD(32, 2);
@@ -533,17 +700,18 @@ int bwd_t(const void* dy, const void* x, const float* gamma, const float* mean, 
     else if (g.k == 2) FB_LN_BWD(256, 2);
     else FB_LN_BWD(256, 4);
 #undef FB_LN_BWD
+    }
     const int ncols = 3 * cols;
     const int col_blocks = (ncols + 127) / 128;
     int row_blocks = (sm_count() * 2 + col_blocks - 1) / col_blocks;
-    const int max_rb = (nblk + 15) / 16;
+    const int max_rb = (used + 15) / 16;
     if (row_blocks > max_rb) row_blocks = max_rb;
     if (row_blocks < 1) row_blocks = 1;
-    const int rpb = (nblk + row_blocks - 1) / row_blocks;
-    ln_fold_kernel<<<dim3(col_blocks, row_blocks), 256, 0, st>>>(partial, stats, nblk, ncols, rpb);
+    const int rpb = (used + row_blocks - 1) / row_blocks;
+    ln_fold_kernel<<<dim3(col_blocks, row_blocks), 256, 0, st>>>(partial, stats, used, ncols, rpb);
   } else {
     const int grid = static_cast<int>(rows < sm_count() * 4LL ? rows : sm_count() * 4LL);
-    ln_bwd_generic<T><<<grid, 256, 0, st>>>(dyp, xp, gamma, mean, rstd, dxp, stats, rows, cols, pre_act,
+    ln_bwd_generic<T><<<grid, 256, 0, st>>>(dyp, xp, agp, gamma, mean, rstd, dxp, stats, rows, cols, pre_act,
                                             want_colsum);
   }
   return static_cast<int>(cudaGetLastError());
@@ -577,17 +745,20 @@ extern "C" int fb_layernorm_fwd(const void* x, const float* gamma, const float* 
 
 // stats = [3][cols] fp32: d_gamma, d_beta and the column sum of dx.  All three are ACCUMULATED into
 // (zero the buffer for a fresh gradient); the column sum is produced only when want_colsum != 0.
-extern "C" int fb_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean,
-                                const float* rstd, void* dx, float* partial, float* stats, long long rows,
-                                int cols, int pre_act, int dtype, int nblk, int want_colsum,
+// act_grad (optional, dtype of x): x then holds act(z) of an activation applied before the normalisation and
+// act_grad its derivative act'(z); dx is the gradient of z.  (pre_act instead re-evaluates a GELU from z.)
+extern "C" int fb_layernorm_bwd(const void* dy, const void* x, const void* act_grad, const float* gamma,
+                                const float* mean, const float* rstd, void* dx, float* partial, float* stats,
+                                long long rows, int cols, int pre_act, int dtype, int nblk, int want_colsum,
                                 cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (stats == nullptr) return -1;
+  if (act_grad != nullptr && pre_act != FB_ACT_NONE) return -1;
   if (dtype == FB_DT_F32)
-    return bwd_t<float>(dy, x, gamma, mean, rstd, dx, partial, stats, rows, cols, pre_act, nblk, want_colsum,
-                        stream);
+    return bwd_t<float>(dy, x, act_grad, gamma, mean, rstd, dx, partial, stats, rows, cols, pre_act, nblk,
+                        want_colsum, stream);
   if (dtype == FB_DT_BF16)
-    return bwd_t<__nv_bfloat16>(dy, x, gamma, mean, rstd, dx, partial, stats, rows, cols, pre_act, nblk,
+    return bwd_t<__nv_bfloat16>(dy, x, act_grad, gamma, mean, rstd, dx, partial, stats, rows, cols, pre_act, nblk,
                                 want_colsum, stream);
   return -1;
 }

@@ -95,6 +95,53 @@ __global__ void reduce_cols_kernel(const float* __restrict__ x, float* __restric
   out[static_cast<long long>(blockIdx.y) * outer * inner + col] = acc * scale;
 }
 
+// x: [outer, R, inner] with inner % 4 == 0: block = 128 adjacent columns x a chunk of R (blockIdx.y) of one
+// outer slice (blockIdx.z); lanes own 4 columns (16-byte loads), the 8 warps walk the rows four at a time and
+// meet in shared memory.  Output layout [row_blocks, outer * inner]; a second launch folds the row blocks.
+__global__ void __launch_bounds__(256)
+reduce_cols_vec_kernel(const float* __restrict__ x, float* __restrict__ out, long long R, long long inner, int op,
+                       float scale, long long rows_per_block, long long outs) {
+  __shared__ float sm[8][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long c0 = static_cast<long long>(blockIdx.x) * 128 + lane * 4;
+  const long long r_lo = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r_hi = min(R, r_lo + rows_per_block);
+  const int cop = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
+  const float id = red_identity(cop);
+  float a0 = id, a1 = id, a2 = id, a3 = id;
+  const float* base = x + static_cast<long long>(blockIdx.z) * R * inner;
+  if (c0 < inner) {
+    for (long long r = r_lo + warp; r < r_hi; r += 32) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long rr = r + 8 * u;
+        v[u] = rr < r_hi ? *reinterpret_cast<const float4*>(base + rr * inner + c0) : make_float4(id, id, id, id);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a0 = red_combine(a0, v[u].x, cop);
+        a1 = red_combine(a1, v[u].y, cop);
+        a2 = red_combine(a2, v[u].z, cop);
+        a3 = red_combine(a3, v[u].w, cop);
+      }
+    }
+  }
+  sm[warp][lane * 4 + 0] = a0;
+  sm[warp][lane * 4 + 1] = a1;
+  sm[warp][lane * 4 + 2] = a2;
+  sm[warp][lane * 4 + 3] = a3;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float s = sm[0][threadIdx.x];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) s = red_combine(s, sm[w][threadIdx.x], cop);
+    const long long c = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
+    if (c < inner)
+      out[static_cast<long long>(blockIdx.y) * outs + static_cast<long long>(blockIdx.z) * inner + c] = s * scale;
+  }
+}
+
 __global__ void arg_rows_kernel(const float* __restrict__ x, long long* __restrict__ idx, float* __restrict__ val,
                                 long long R, int is_max) {
   __shared__ float sv[128];
@@ -166,19 +213,38 @@ colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, 
   const long long r_hi = min(rows, r_lo + rows_per_block);
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   const bool vec = (cols % 4 == 0) && (c0 + 3 < cols) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-  for (long long r = r_lo + warp; r < r_hi; r += 8) {
-    const T* p = x + r * cols + c0;
-    if (vec) {
+  if (vec) {
+    // four rows per trip: the loads are independent, so each thread keeps four of them in flight
+    for (long long r = r_lo + warp; r < r_hi; r += 32) {
       if constexpr (sizeof(T) == 4) {
-        const float4 v = *reinterpret_cast<const float4*>(p);
-        a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long rr = r + 8 * u;
+          v[u] = rr < r_hi ? *reinterpret_cast<const float4*>(x + rr * cols + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a0 += v[u].x; a1 += v[u].y; a2 += v[u].z; a3 += v[u].w;
+        }
       } else {
-        const uint2 u = *reinterpret_cast<const uint2*>(p);
-        const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-        const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-        a0 += f0.x; a1 += f0.y; a2 += f1.x; a3 += f1.y;
+        uint2 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long rr = r + 8 * u;
+          v[u] = rr < r_hi ? *reinterpret_cast<const uint2*>(x + rr * cols + c0) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].x));
+          const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].y));
+          a0 += f0.x; a1 += f0.y; a2 += f1.x; a3 += f1.y;
+        }
       }
-    } else {
+    }
+  } else {
+    for (long long r = r_lo + warp; r < r_hi; r += 8) {
+      const T* p = x + r * cols + c0;
       if (c0 < cols) a0 += static_cast<float>(p[0]);
       if (c0 + 1 < cols) a1 += static_cast<float>(p[1]);
       if (c0 + 2 < cols) a2 += static_cast<float>(p[2]);
@@ -212,9 +278,26 @@ int sm_count() {
 using namespace fb;
 
 // Number of scratch floats fb_reduce wants for this problem (0 = single pass).
+// Row blocks the vectorised column reduction uses for [outer, R, inner] (0 = not applicable).
+static long long vec_row_blocks(long long outer, long long R, long long inner) {
+  if (inner % 4 != 0 || inner < 4 || outer > 65535) return 0;
+  const long long col_blocks = ((inner + 127) / 128) * outer;
+  long long rb = (static_cast<long long>(sm_count()) * 4 + col_blocks - 1) / col_blocks;
+  const long long max_rb = (R + 31) / 32;
+  if (rb > max_rb) rb = max_rb;
+  if (rb > 65535) rb = 65535;
+  return rb < 1 ? 1 : rb;
+}
+
+// Number of scratch floats fb_reduce wants for this problem (0 = single pass).
 extern "C" long long fb_reduce_scratch_elems(long long outer, long long R, long long inner) {
   const long long outs = outer * inner;
-  if (R < 4096 || outs <= 0) return 0;
+  if (outs <= 0) return 0;
+  if (inner > 1) {
+    const long long rb = vec_row_blocks(outer, R, inner);
+    if (rb > 1) return rb * outs;
+  }
+  if (R < 4096) return 0;
   // blocks a single pass would launch: one per row (inner == 1) or one per 256 columns
   const long long blocks = inner == 1 ? outs : (outs + 255) / 256;
   const long long target = static_cast<long long>(sm_count()) * 4;
@@ -247,6 +330,20 @@ extern "C" int fb_reduce(const float* x, float* out, long long outer, long long 
                                                                                            1.f, splits);
       reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), 1), 256, 0, stream>>>(scratch, out, splits, stage_op,
                                                                                       final_scale, 1);
+    }
+  } else if (vec_row_blocks(outer, R, inner) > 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+             (vec_row_blocks(outer, R, inner) == 1 ||
+              (scratch != nullptr && scratch_elems >= vec_row_blocks(outer, R, inner) * outs))) {
+    const long long rb = vec_row_blocks(outer, R, inner);
+    const long long rpb = (R + rb - 1) / rb;
+    const dim3 grid(static_cast<unsigned>((inner + 127) / 128), static_cast<unsigned>(rb),
+                    static_cast<unsigned>(outer));
+    if (rb == 1) {
+      reduce_cols_vec_kernel<<<grid, 256, 0, stream>>>(x, out, R, inner, op, final_scale, rpb, outs);
+    } else {
+      reduce_cols_vec_kernel<<<grid, 256, 0, stream>>>(x, scratch, R, inner, stage_op, 1.f, rpb, outs);
+      const unsigned gx = static_cast<unsigned>((outs + 255) / 256);
+      reduce_cols_kernel<<<dim3(gx, 1), 256, 0, stream>>>(scratch, out, 1, rb, outs, stage_op, final_scale, 1);
     }
   } else {
     const unsigned gx = static_cast<unsigned>((outs + 255) / 256);

@@ -1,9 +1,10 @@
 """Convolutions and pooling (ferrum-nn/src/conv.rs:9-497; forward-only host loops there).
 
-Convolution is lowered to GEMM: the input windows are gathered into an im2col matrix and the product with the
-flattened filters runs on this package's GEMM kernels (tcgen05 under bf16 autocast, fp32 SIMT otherwise), so the
-backward — dgrad / wgrad GEMMs plus the col2im scatter — comes with it.  Groups, dilation, stride and padding follow
-the reference; weights ~ U(+-1/sqrt(fan_in)).  Pooling reduces the same window view with the reduction kernels.
+Convolution is lowered to GEMM: an im2col kernel writes the input windows as a K-major matrix (one row per output
+position) and the product with the flattened filters runs on this package's GEMM kernels (tcgen05 under bf16
+autocast, fp32 SIMT otherwise); the backward is the dgrad / wgrad GEMMs plus a gather-form col2im kernel.  Groups,
+dilation, stride and padding follow the reference; weights ~ U(+-1/sqrt(fan_in)).  Max / average pooling are
+their own forward / backward kernels.
 """
 from __future__ import annotations
 
@@ -20,16 +21,12 @@ def _pair(v):
     return (int(v), int(v)) if isinstance(v, int) else (int(v[0]), int(v[1]))
 
 
-def _windows(x, kernel, stride, padding, dilation):
-    """[B, C, H, W] -> ([B, C*kh*kw, L], (Ho, Wo)) window matrix (data movement only)."""
-    B, C, H, W = x.shape
-    kh, kw = kernel
-    Ho = (H + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
-    Wo = (W + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+def _out_hw(x, kernel, stride, padding, dilation):
+    Ho = F.conv_out_size(x.shape[2], kernel[0], stride[0], padding[0], dilation[0])
+    Wo = F.conv_out_size(x.shape[3], kernel[1], stride[1], padding[1], dilation[1])
     if Ho <= 0 or Wo <= 0:
         raise ShapeMismatch("conv/pool", "input at least as large as the kernel", list(x.shape))
-    cols = torch.nn.functional.unfold(x, kernel, dilation=dilation, padding=padding, stride=stride)
-    return cols, (Ho, Wo)
+    return Ho, Wo
 
 
 def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1):
@@ -37,14 +34,15 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
     O, Cg, kh, kw = weight.shape
     if C != Cg * groups or O % groups:
         raise ShapeMismatch("conv2d", f"{Cg * groups} input channels", C)
-    cols, (Ho, Wo) = _windows(x, (kh, kw), stride, padding, dilation)  # [B, C*kh*kw, L]
+    Ho, Wo = _out_hw(x, (kh, kw), stride, padding, dilation)
+    cols = F.im2col(x, (kh, kw), stride, padding, dilation)              # [B*L, C*kh*kw], K contiguous
     L = Ho * Wo
     outs = []
     og = O // groups
+    kg = Cg * kh * kw
     for g in range(groups):
-        cg = cols[:, g * Cg * kh * kw:(g + 1) * Cg * kh * kw, :]          # [B, K, L]
-        a = cg.transpose(1, 2).reshape(B * L, Cg * kh * kw)               # [B*L, K]
-        wg = weight[g * og:(g + 1) * og].reshape(og, Cg * kh * kw)        # [og, K]
+        a = cols if groups == 1 else cols[:, g * kg:(g + 1) * kg].contiguous()
+        wg = weight[g * og:(g + 1) * og].reshape(og, kg)                  # [og, K]
         bg = bias[g * og:(g + 1) * og] if bias is not None else None
         outs.append(F.linear(a, wg, bg).reshape(B, L, og))
     y = outs[0] if groups == 1 else torch.cat(outs, 2)
@@ -150,11 +148,8 @@ class _Pool2d(Module):
     def forward(self, x):
         if x.dim() != 4:
             raise ShapeMismatch("pool.forward", "[B, C, H, W]", list(x.shape))
-        B, C, H, W = x.shape
-        kh, kw = self.kernel_size
-        cols, (Ho, Wo) = _windows(x, (kh, kw), self._stride, (0, 0), (1, 1))
-        win = cols.reshape(B, C, kh * kw, Ho * Wo)
-        return F.reduce(win, self.op, 2).reshape(B, C, Ho, Wo)
+        _out_hw(x, self.kernel_size, self._stride, (0, 0), (1, 1))
+        return F.pool2d(x, self.kernel_size, self._stride, self.op)
 
 
 class MaxPool2d(_Pool2d):

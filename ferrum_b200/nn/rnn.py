@@ -2,8 +2,8 @@
 
 Input is sequence-first ``[T, B, F]``.  The reference executes only layer 0 in the forward direction and computes
 the LSTM / GRU gates on host vectors without autograd; here every layer runs, the per-step projections are GEMMs
-of this package (the input projection of a whole sequence is one GEMM), the gate arithmetic uses the elementwise
-kernels and everything is differentiable.
+of this package (the input projection of a whole sequence is one GEMM), the gate arithmetic of an LSTM / GRU step
+is one fused kernel forward and one backward, and everything is differentiable.
 """
 from __future__ import annotations
 
@@ -94,13 +94,8 @@ class LSTMCell(_CellBase):
     gates = 4  # input, forget, cell, output
 
     def step(self, xi, h, c):
-        pre = F.binary(xi, F.linear(h, self.weight_hh, self.bias_hh), "add")
-        i, f, g, o = _chunks(pre, 4)
-        i, f, o = F.unary(i, "sigmoid"), F.unary(f, "sigmoid"), F.unary(o, "sigmoid")
-        g = F.unary(g, "tanh")
-        c2 = F.binary(F.binary(f, c, "mul"), F.binary(i, g, "mul"), "add")
-        h2 = F.binary(o, F.unary(c2, "tanh"), "mul")
-        return h2, c2
+        # hidden projection (GEMM) + one fused gate kernel
+        return F.lstm_gates(xi, F.linear(h, self.weight_hh, self.bias_hh), c)
 
     def forward(self, input, hx):
         wrapped = isinstance(input, Tensor)
@@ -113,14 +108,8 @@ class GRUCell(_CellBase):
     gates = 3  # reset, update, new
 
     def step(self, xi, h):
-        hh = F.linear(h, self.weight_hh, self.bias_hh)
-        xr, xz, xn = _chunks(xi, 3)
-        hr, hz, hn = _chunks(hh, 3)
-        r = F.unary(F.binary(xr, hr, "add"), "sigmoid")
-        z = F.unary(F.binary(xz, hz, "add"), "sigmoid")
-        n = F.unary(F.binary(xn, F.binary(r, hn, "mul"), "add"), "tanh")
-        # h' = (1 - z) * n + z * h
-        return F.binary(F.binary(F.unary(z, "rsub_scalar", 1.0), n, "mul"), F.binary(z, h, "mul"), "add")
+        # h' = (1 - z) * n + z * h, n = tanh(xn + r * hn): hidden projection (GEMM) + one fused gate kernel
+        return F.gru_gates(xi, F.linear(h, self.weight_hh, self.bias_hh), h)
 
     def forward(self, input, hidden):
         wrapped = isinstance(input, Tensor)

@@ -2,7 +2,9 @@
 
 ``MultiHeadAttention`` projects with Linear layers (GEMM kernels; 3-D inputs work, unlike the reference where the
 3-D matmul is unimplemented), computes ``softmax(Q K^T / sqrt(d)) V`` per head with the batched GEMM and the row
-softmax kernel, and is differentiable.  ``TransformerEncoderLayer`` is post-LayerNorm with a ReLU feed-forward, as
+softmax kernel, and is differentiable.  Under autocast both products run on the batched tcgen05 kernel directly
+on the head-interleaved ``[B, S, H, D]`` projections (4-D TMA maps; no head-split or transpose copies), with the
+1/sqrt(d) scale in the first product's epilogue and the second product written back in ``[B, S, H, D]`` order.  ``TransformerEncoderLayer`` is post-LayerNorm with a ReLU feed-forward, as
 in the reference; ``PositionalEncoding`` is the fixed sinusoid table.
 """
 from __future__ import annotations
@@ -43,14 +45,13 @@ class MultiHeadAttention(Module):
         q = self._split(self.q_proj(query), B, Sq)
         k = self._split(self.k_proj(key), B, Sk)
         v = self._split(self.v_proj(value), B, Sk)
-        scores = F.matmul(q, k.transpose(-1, -2))
-        scores = F.scalar_op(scores, "mul", 1.0 / math.sqrt(self.head_dim))
+        scores = F.bmm_scaled(q, k.transpose(-1, -2), 1.0 / math.sqrt(self.head_dim))  # scale in the GEMM epilogue
         if mask is not None:
             m = mask.to(scores.dtype) if mask.dtype != torch.bool else torch.zeros_like(
                 mask, dtype=scores.dtype).masked_fill(~mask, -1e9)
             scores = F.binary(scores, m, "add")
         attn = F.softmax(scores, -1)
-        ctx = F.matmul(attn, v)                                       # [B, H, Sq, D]
+        ctx = F.bmm_scaled(attn, v, 1.0, heads_inner=True)            # [B, H, Sq, D], stored [B, Sq, H, D]
         ctx = ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim)
         return self.out_proj(ctx)
 

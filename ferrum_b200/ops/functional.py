@@ -513,6 +513,51 @@ class _BmmFn(Function):
         return ga, gb
 
 
+def _bmm_operand(t):
+    t = t if t.dtype == torch.bfloat16 else raw_cast(t, torch.bfloat16)
+    return t if _gemm.batched_operand_ok(t) else t.contiguous()
+
+
+class _BmmLowFn(Function):
+    """Batched ``alpha * a @ b`` over 4-D operands on the tcgen05 kernel (bf16 in, bf16 out, fp32 accumulate);
+    strided views (heads interleaved in the feature dimension, transposes) are consumed without copies."""
+
+    @staticmethod
+    def forward(ctx, a, b, alpha, heads_inner=False):
+        a, b = _bmm_operand(a), _bmm_operand(b)
+        ctx.save_for_backward(a, b)
+        ctx.alpha = alpha
+        bt = b.transpose(-1, -2)
+        out = None
+        if heads_inner:  # result stored [Bo, M, Bi, N] so that merging the heads afterwards is a view
+            Bo, Bi, M, _ = a.shape
+            out = torch.empty((Bo, M, Bi, b.shape[-1]), device=a.device, dtype=torch.bfloat16).permute(0, 2, 1, 3)
+        return _gemm.gemm_bf16_batched(a, bt if _gemm.batched_operand_ok(bt) else bt.contiguous(), out=out,
+                                       alpha=alpha)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        g = _bmm_operand(g)
+        ga = gb = None
+        if ctx.needs_input_grad[0]:   # dA = alpha * g @ b^T
+            ga = _gemm.gemm_bf16_batched(g, b, alpha=ctx.alpha)
+        if ctx.needs_input_grad[1]:   # dB = alpha * a^T @ g
+            gb = _gemm.gemm_bf16_batched(a.transpose(-1, -2), g.transpose(-1, -2), alpha=ctx.alpha)
+        return ga, gb, None, None
+
+
+def bmm_scaled(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, heads_inner: bool = False) -> torch.Tensor:
+    """``alpha * a @ b`` for 4-D ``[Bo, Bi, M, K] @ [Bo, Bi, K, N]``: tensor cores under autocast for TMA-describable
+    operands (feature extents multiples of 8), the fp32 batched kernel otherwise.  ``heads_inner`` stores the
+    result as ``[Bo, M, Bi, N]`` (returned as the permuted view)."""
+    if (_native(a) and _native(b) and config.low_precision_active() and a.shape[-1] % 8 == 0
+            and b.shape[-1] % 8 == 0):
+        return _BmmLowFn.apply(a, b, float(alpha), heads_inner)
+    out = matmul(a, b)
+    return scalar_op(out, "mul", float(alpha)) if alpha != 1.0 else out
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """2D@2D, 2D@1D, 1D@2D (tensor.rs:2433-2485) and batched ND@ND / ND@2D."""
     if not (_native(a) and _native(b)):
@@ -529,8 +574,12 @@ def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     if b.dim() == 2:  # [..., M, K] @ [K, N]
         lead = a.shape[:-1]
         return _MatmulFn.apply(a.reshape(-1, a.shape[-1]), b, low).reshape(*lead, b.shape[1])
-    # batched: broadcast batch dims, run the fp32 batched kernel
+    # batched: broadcast batch dims; tensor cores under autocast, else the fp32 batched kernel
     bs = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    if low and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0:
+        a4 = a.expand(*bs, *a.shape[-2:]).reshape(1, -1, *a.shape[-2:])
+        b4 = b.expand(*bs, *b.shape[-2:]).reshape(1, -1, *b.shape[-2:])
+        return _BmmLowFn.apply(a4, b4, 1.0).reshape(*bs, a.shape[-2], b.shape[-1])
     a3 = _f32(a.expand(*bs, *a.shape[-2:]).reshape(-1, *a.shape[-2:]).contiguous())
     b3 = _f32(b.expand(*bs, *b.shape[-2:]).reshape(-1, *b.shape[-2:]).contiguous())
     out = _BmmFn.apply(a3, b3)
@@ -661,7 +710,7 @@ class _LayerNormFn(Function):
         nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
         partial = torch.empty((max(nblk, 1), 3, cols), device=x2.device, dtype=torch.float32)
         stats = torch.zeros((3, cols), device=x2.device, dtype=torch.float32)
-        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), x2.data_ptr(), _ptr(g), mean.data_ptr(), rstd.data_ptr(),
+        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), x2.data_ptr(), None, _ptr(g), mean.data_ptr(), rstd.data_ptr(),
                                         dx.data_ptr(), partial.data_ptr(), stats.data_ptr(), rows, cols,
                                         UNARY[ctx.pre_act or "none"], _dt(x2), nblk, 1 if ctx.want_colsum else 0,
                                         _stream()), "fb_layernorm_bwd")
@@ -697,9 +746,10 @@ def layer_norm(x: torch.Tensor, gamma=None, beta=None, eps: float = 1e-5, pre_ac
 class _LinearActNormFn(Function):
     """One autograd node for the block ``LayerNorm(act(x W^T + b))``.
 
-    Forward: GEMM with bias epilogue writes the pre-activation z once; the fused activation+LayerNorm kernel
-    reads z and writes y.  Backward: one kernel turns dy into dz and also yields d_gamma, d_beta and the column
-    sum of dz (= the bias gradient), then the dgrad and wgrad GEMMs run on dz.
+    Forward (tensor-core path): the GEMM epilogue writes act(z) and act'(z) in bf16, the LayerNorm kernel reads
+    act(z) and writes y.  Backward: one streaming kernel turns dy into dz (using the stored derivative) and also
+    yields d_gamma, d_beta and the column sum of dz (= the bias gradient), then the dgrad and wgrad GEMMs run on
+    dz.  On the fp32 path z itself is stored and the activation is evaluated inside the normalisation kernels.
     """
 
     @staticmethod
@@ -711,7 +761,18 @@ class _LinearActNormFn(Function):
             ws = w_low if w_low is not None else raw_cast(weight.detach().contiguous(), torch.bfloat16)
         else:
             xs, ws = _f32(x2), weight.detach()
-        z = _gemm_nt(xs, ws, bias=bias, act=None, low=low)
+        # Tensor-core path: the GEMM epilogue stores act(z) and act'(z), so the normalisation kernels are pure
+        # streaming code.  fp32 path: z is stored and the GELU is evaluated inside the normalisation kernels.
+        dual = low and act is not None and xs.dtype == torch.bfloat16 and _gemm.bf16_operand_ok(xs) \
+            and _gemm.bf16_operand_ok(ws)
+        if dual:
+            z = torch.empty((xs.shape[0], ws.shape[0]), device=xs.device, dtype=torch.bfloat16)
+            dact = torch.empty_like(z)
+            _gemm.gemm_bf16(xs, ws, bias=bias, act=act, out=z, act_grad=dact)
+            pre = "none"
+        else:
+            z = _gemm_nt(xs, ws, bias=bias, act=None, low=low)
+            dact, pre = None, act or "none"
         rows, cols = z.shape
         y = torch.empty_like(z)
         mean = torch.empty(rows, device=z.device, dtype=torch.float32)
@@ -719,16 +780,24 @@ class _LinearActNormFn(Function):
         g = gamma.detach().contiguous()
         b = beta.detach().contiguous()
         _lib.check(_lib.cuda().fb_layernorm_fwd(z.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
-                                                mean.data_ptr(), rstd.data_ptr(), rows, cols, eps, UNARY[act], _dt(z),
+                                                mean.data_ptr(), rstd.data_ptr(), rows, cols, eps, UNARY[pre], _dt(z),
                                                 _stream()), "fb_layernorm_fwd")
-        ctx.save_for_backward(xs, ws, z, g, mean, rstd)
-        ctx.low, ctx.act, ctx.sink, ctx.weight_ref = low, act, sink, weight
+        if dual:
+            ctx.save_for_backward(xs, ws, z, g, mean, rstd, dact)
+        else:
+            ctx.save_for_backward(xs, ws, z, g, mean, rstd)
+        ctx.dual = dual
+        ctx.low, ctx.act, ctx.sink, ctx.weight_ref = low, pre, sink, weight
         ctx.x_dtype, ctx.lead, ctx.has_bias = x.dtype, lead, bias is not None
         return y.reshape(*lead, cols)
 
     @staticmethod
     def backward(ctx, gy):
-        xs, ws, z, g, mean, rstd = ctx.saved_tensors
+        if ctx.dual:
+            xs, ws, z, g, mean, rstd, dact = ctx.saved_tensors
+        else:
+            xs, ws, z, g, mean, rstd = ctx.saved_tensors
+            dact = None
         rows, cols = z.shape
         low = ctx.low
         gy2 = gy.reshape(rows, cols).contiguous()
@@ -739,9 +808,9 @@ class _LinearActNormFn(Function):
         nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
         partial = torch.empty((max(nblk, 1), 3, cols), device=z.device, dtype=torch.float32)
         stats = torch.zeros((3, cols), device=z.device, dtype=torch.float32)  # d_gamma, d_beta, colsum(dz)
-        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), z.data_ptr(), g.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
-                                        dz.data_ptr(), partial.data_ptr(), stats.data_ptr(), rows, cols,
-                                        UNARY[ctx.act], _dt(z), nblk, 1, _stream()), "fb_layernorm_bwd")
+        _lib.check(lib.fb_layernorm_bwd(gy2.data_ptr(), z.data_ptr(), _ptr(dact), g.data_ptr(), mean.data_ptr(),
+                                        rstd.data_ptr(), dz.data_ptr(), partial.data_ptr(), stats.data_ptr(), rows,
+                                        cols, UNARY[ctx.act], _dt(z), nblk, 1, _stream()), "fb_layernorm_bwd")
         gx = gw = None
         if ctx.needs_input_grad[0]:
             gx = raw_cast(_gemm_nt(dz, ws.t(), low=low), ctx.x_dtype).reshape(*ctx.lead, ws.shape[1])
@@ -905,11 +974,10 @@ class _CEFn(Function):
     def backward(ctx, g):
         (dl,) = ctx.saved_tensors
         # dl already carries the 1/rows factor; scale by the incoming scalar gradient
-        gf = _f32(g).reshape(1)
-        if dl.dtype == torch.float32:
-            out = raw_binary(dl, gf, "mul")
-        else:
-            out = raw_cast(raw_binary(_f32(dl), gf, "mul"), dl.dtype)
+        gf = _f32(g).reshape(1).contiguous()
+        out = torch.empty_like(dl)
+        _lib.check(_lib.cuda().fb_scale_by_device_scalar(dl.data_ptr(), gf.data_ptr(), out.data_ptr(), dl.numel(),
+                                                         _dt(dl), _stream()), "fb_scale_by_device_scalar")
         return out, None, None
 
 
@@ -1110,3 +1178,149 @@ def transpose_2d(x: torch.Tensor) -> torch.Tensor:
     _lib.check(_lib.cuda().fb_transpose_2d(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], x.element_size(),
                                            _stream()), "fb_transpose_2d")
     return out
+
+
+# ============================================================ secondary layers: recurrent gates, conv lowering, pooling
+class _LstmGatesFn(Function):
+    """(h', c') from the gate pre-activations ``xi + hh`` ([B, 4H]: input, forget, cell, output) in one kernel."""
+
+    @staticmethod
+    def forward(ctx, xi, hh, c_prev):
+        xi, hh, c_prev = _f32(xi).contiguous(), _f32(hh).contiguous(), _f32(c_prev).contiguous()
+        B, H = c_prev.shape
+        h, c = torch.empty_like(c_prev), torch.empty_like(c_prev)
+        gates = torch.empty_like(xi)
+        _lib.check(_lib.cuda().fb_lstm_gates_fwd(xi.data_ptr(), hh.data_ptr(), c_prev.data_ptr(), h.data_ptr(),
+                                                 c.data_ptr(), gates.data_ptr(), B, H, _stream()), "fb_lstm_gates_fwd")
+        ctx.save_for_backward(gates, c_prev, c)
+        return h, c
+
+    @staticmethod
+    def backward(ctx, dh, dc):
+        gates, c_prev, c = ctx.saved_tensors
+        B, H = c_prev.shape
+        dh = _f32(dh).contiguous() if dh is not None else None
+        dc = _f32(dc).contiguous() if dc is not None else None
+        dpre, dc_prev = torch.empty_like(gates), torch.empty_like(c_prev)
+        _lib.check(_lib.cuda().fb_lstm_gates_bwd(dh.data_ptr() if dh is not None else None,
+                                                 dc.data_ptr() if dc is not None else None, gates.data_ptr(),
+                                                 c_prev.data_ptr(), c.data_ptr(), dpre.data_ptr(), dc_prev.data_ptr(),
+                                                 B, H, _stream()), "fb_lstm_gates_bwd")
+        return dpre, dpre, dc_prev
+
+
+def lstm_gates(xi, hh, c_prev):
+    """LSTM cell update from the two projections (ferrum-nn/src/rnn.rs:188-227)."""
+    if _native(xi) and xi.dim() == 2:
+        return _LstmGatesFn.apply(xi, hh, c_prev)
+    i, f, g, o = (xi + hh).chunk(4, -1)
+    c = torch.sigmoid(f) * c_prev + torch.sigmoid(i) * torch.tanh(g)
+    return torch.sigmoid(o) * torch.tanh(c), c
+
+
+class _GruGatesFn(Function):
+    """h' = (1 - z) n + z h with r, z = sigmoid, n = tanh(xn + r * hn), from xi, hh [B, 3H] in one kernel."""
+
+    @staticmethod
+    def forward(ctx, xi, hh, h_prev):
+        xi, hh, h_prev = _f32(xi).contiguous(), _f32(hh).contiguous(), _f32(h_prev).contiguous()
+        B, H = h_prev.shape
+        h = torch.empty_like(h_prev)
+        saved = torch.empty((B, 4 * H), device=h.device, dtype=torch.float32)
+        _lib.check(_lib.cuda().fb_gru_gates_fwd(xi.data_ptr(), hh.data_ptr(), h_prev.data_ptr(), h.data_ptr(),
+                                                saved.data_ptr(), B, H, _stream()), "fb_gru_gates_fwd")
+        ctx.save_for_backward(saved, h_prev)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        saved, h_prev = ctx.saved_tensors
+        B, H = h_prev.shape
+        dh = _f32(dh).contiguous()
+        dxi = torch.empty((B, 3 * H), device=dh.device, dtype=torch.float32)
+        dhh, dhp = torch.empty_like(dxi), torch.empty_like(h_prev)
+        _lib.check(_lib.cuda().fb_gru_gates_bwd(dh.data_ptr(), saved.data_ptr(), h_prev.data_ptr(), dxi.data_ptr(),
+                                                dhh.data_ptr(), dhp.data_ptr(), B, H, _stream()), "fb_gru_gates_bwd")
+        return dxi, dhh, dhp
+
+
+def gru_gates(xi, hh, h_prev):
+    """GRU cell update from the two projections (ferrum-nn/src/rnn.rs:318-372)."""
+    if _native(xi) and xi.dim() == 2:
+        return _GruGatesFn.apply(xi, hh, h_prev)
+    xr, xz, xn = xi.chunk(3, -1)
+    hr, hz, hn = hh.chunk(3, -1)
+    r, z = torch.sigmoid(xr + hr), torch.sigmoid(xz + hz)
+    n = torch.tanh(xn + r * hn)
+    return (1 - z) * n + z * h_prev
+
+
+def conv_out_size(size, k, stride, pad, dil):
+    return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+
+class _Im2colFn(Function):
+    """[B, C, H, W] -> window matrix [B*Ho*Wo, C*kh*kw], K contiguous: the A operand of the convolution GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, kernel, stride, padding, dilation):
+        x = _f32(x).contiguous()
+        B, C, H, W = x.shape
+        (kh, kw), (sh, sw), (ph, pw), (dh, dw) = kernel, stride, padding, dilation
+        Ho, Wo = conv_out_size(H, kh, sh, ph, dh), conv_out_size(W, kw, sw, pw, dw)
+        K = C * kh * kw
+        cols = torch.empty((B * Ho * Wo, K), device=x.device, dtype=torch.float32)
+        ctx.geom = (B, C, H, W, kh, kw, Ho, Wo, sh, sw, ph, pw, dh, dw)
+        _lib.check(_lib.cuda().fb_im2col(x.data_ptr(), cols.data_ptr(), *ctx.geom, K, _dt(cols), _stream()),
+                   "fb_im2col")
+        return cols
+
+    @staticmethod
+    def backward(ctx, g):
+        g = _f32(g).contiguous()
+        B, C, H, W = ctx.geom[:4]
+        dx = torch.empty((B, C, H, W), device=g.device, dtype=torch.float32)
+        _lib.check(_lib.cuda().fb_col2im(g.data_ptr(), dx.data_ptr(), *ctx.geom, g.shape[1], _stream()), "fb_col2im")
+        return dx, None, None, None, None
+
+
+def im2col(x, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+    """Window matrix of a convolution with rows ordered (b, oh, ow) and columns (c, ki, kj)."""
+    if _native(x):
+        return _Im2colFn.apply(x, tuple(kernel), tuple(stride), tuple(padding), tuple(dilation))
+    cols = torch.nn.functional.unfold(x, kernel, dilation=dilation, padding=padding, stride=stride)
+    return cols.transpose(1, 2).reshape(-1, cols.shape[1])
+
+
+class _Pool2dFn(Function):
+    @staticmethod
+    def forward(ctx, x, kernel, stride, op):
+        x = _f32(x).contiguous()
+        B, C, H, W = x.shape
+        (kh, kw), (sh, sw) = kernel, stride
+        Ho, Wo = (H - kh) // sh + 1, (W - kw) // sw + 1
+        y = torch.empty((B, C, Ho, Wo), device=x.device, dtype=torch.float32)
+        arg = torch.empty((B, C, Ho, Wo), device=x.device, dtype=torch.int32) if op == 0 else None
+        ctx.geom, ctx.op = (B, C, H, W, kh, kw, Ho, Wo, sh, sw), op
+        _lib.check(_lib.cuda().fb_pool2d_fwd(x.data_ptr(), y.data_ptr(), arg.data_ptr() if arg is not None else None,
+                                             *ctx.geom, op, _stream()), "fb_pool2d_fwd")
+        ctx.save_for_backward(arg) if arg is not None else None
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        g = _f32(g).contiguous()
+        arg = ctx.saved_tensors[0] if ctx.op == 0 else None
+        B, C, H, W = ctx.geom[:4]
+        dx = torch.empty((B, C, H, W), device=g.device, dtype=torch.float32)
+        _lib.check(_lib.cuda().fb_pool2d_bwd(g.data_ptr(), arg.data_ptr() if arg is not None else None, dx.data_ptr(),
+                                             *ctx.geom, ctx.op, _stream()), "fb_pool2d_bwd")
+        return dx, None, None, None
+
+
+def pool2d(x, kernel, stride, op: str):
+    """Max / average pooling over unpadded windows (ferrum-nn/src/conv.rs:340-441)."""
+    if _native(x) and x.dim() == 4:
+        return _Pool2dFn.apply(x, tuple(kernel), tuple(stride), 0 if op == "max" else 1)
+    fn = torch.nn.functional.max_pool2d if op == "max" else torch.nn.functional.avg_pool2d
+    return fn(x, kernel, stride)

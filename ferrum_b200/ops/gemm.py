@@ -66,11 +66,12 @@ def _major(t: torch.Tensor):
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
               out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
-              accumulate: bool = False) -> torch.Tensor:
+              accumulate: bool = False, act_grad: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M,N] = act(a[M,K] @ b[N,K]^T + bias)`` on the tcgen05 tensor cores.
 
     ``a`` and ``b`` are bf16 2-D tensors with one unit stride (any of the two);
     a transposed view (``x.t()``) is consumed as an MN-major operand without a copy.
+    ``act_grad`` (bf16, shaped and strided like a bf16 ``out``) additionally receives ``act'(a @ b^T + bias)``.
     """
     assert a.is_cuda and b.is_cuda and a.dim() == 2 and b.dim() == 2
     M, K = a.shape
@@ -83,16 +84,62 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     assert out.stride(1) == 1 and out.shape == (M, N)
     if accumulate:
         assert out.dtype == torch.float32, "accumulate needs an fp32 output"
+    if act_grad is not None:
+        assert out.dtype == torch.bfloat16 and act_grad.dtype == torch.bfloat16 and act_grad.shape == out.shape
+        assert act_grad.stride() == out.stride()
+    aux = act_grad.data_ptr() if act_grad is not None else None
     lib = _lib.cuda()
-    fn = lib.fb_gemm_bf16_2cta if (_use_2cta and M >= 512 and N >= 256) else lib.fb_gemm_bf16
-    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+    fn = lib.fb_gemm_bf16_2cta if (_use_2cta and M >= 512 and N >= 128) else lib.fb_gemm_bf16
+    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), aux, bias.data_ptr() if bias is not None else None,
             M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
             ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
     if rc == -3:  # CTA pairs cannot be scheduled on this device
-        rc = lib.fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
-                              M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
+        rc = lib.fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), aux,
+                              bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,
                               ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(), _stream())
     _lib.check(rc, "fb_gemm_bf16")
+    return out
+
+
+def batched_operand_ok(t: torch.Tensor) -> bool:
+    """True when a 4-D bf16 tensor ``[Bo, Bi, rows, cols]`` can be described by a 4-D TMA map."""
+    if t.dtype != torch.bfloat16 or t.dim() != 4 or t.data_ptr() % 16:
+        return False
+    so, si, s0, s1 = t.stride()
+    if s1 == 1:
+        ld, ok = s0, s0 >= t.shape[3]
+    elif s0 == 1:
+        ld, ok = s1, s1 >= t.shape[2]
+    else:
+        return False
+    if not ok or ld % 8:
+        return False
+    return (t.shape[0] == 1 or (so > 0 and so % 8 == 0)) and (t.shape[1] == 1 or (si > 0 and si % 8 == 0))
+
+
+def gemm_bf16_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
+                      out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
+                      accumulate: bool = False) -> torch.Tensor:
+    """``out[o,i] = alpha * a[o,i] @ b[o,i]^T`` for 4-D operands ``a [Bo,Bi,M,K]``, ``b [Bo,Bi,N,K]``.
+
+    Any strides over the two batch dimensions (multiples of 8 elements) and either unit-stride major in the
+    last two, so ``x.view(B, S, H, D).permute(0, 2, 1, 3)`` and ``.transpose(-1, -2)`` views are used in place.
+    """
+    assert a.dim() == 4 and b.dim() == 4 and a.shape[:2] == b.shape[:2] and a.shape[3] == b.shape[3]
+    Bo, Bi, M, K = a.shape
+    N = b.shape[2]
+    a_mn, lda = _major(a[0, 0])
+    b_mn, ldb = _major(b[0, 0])
+    if out is None:
+        out = torch.empty((Bo, Bi, M, N), device=a.device, dtype=out_dtype)
+    assert out.shape == (Bo, Bi, M, N) and out.stride(3) == 1
+    if accumulate:
+        assert out.dtype == torch.float32
+    rc = _lib.cuda().fb_gemm_bf16_batched(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, lda, ldb, out.stride(2), Bo, Bi,
+        a.stride(0), a.stride(1), b.stride(0), b.stride(1), out.stride(0), out.stride(1), a_mn, b_mn,
+        1 if out.dtype == torch.bfloat16 else 0, 1 if accumulate else 0, float(alpha), _rt.status_ptr(), _stream())
+    _lib.check(rc, "fb_gemm_bf16_batched")
     return out
 
 

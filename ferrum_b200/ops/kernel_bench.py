@@ -66,11 +66,24 @@ def _cases(small: bool):
     dxb = torch.empty_like(xb)
 
     def ln_bwd():
-        lib.fb_layernorm_bwd(gb.data_ptr(), xb.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+        lib.fb_layernorm_bwd(gb.data_ptr(), xb.data_ptr(), None, gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                              dxb.data_ptr(), partial.data_ptr(), stats.data_ptr(), R, C, 2, 3, nblk, 1, st())
+
+    def ln_fwd_plain():
+        lib.fb_layernorm_fwd(xb.data_ptr(), gamma.data_ptr(), beta.data_ptr(), yb.data_ptr(), mean.data_ptr(),
+                             rstd.data_ptr(), R, C, 1e-5, 0, 3, st())
+
+    dact = torch.rand(R, C, device=dev).to(bf)
+
+    def ln_bwd_stored():
+        lib.fb_layernorm_bwd(gb.data_ptr(), xb.data_ptr(), dact.data_ptr(), gamma.data_ptr(), mean.data_ptr(),
+                             rstd.data_ptr(), dxb.data_ptr(), partial.data_ptr(), stats.data_ptr(), R, C, 0, 3, nblk, 1,
+                             st())
 
     case("layernorm_gelu_fwd_bf16", ln_fwd, n * 4, "K7 fused GELU+LN")
     case("layernorm_gelu_bwd_bf16", ln_bwd, n * 6, "K7 bwd + dgamma/dbeta/colsum")
+    case("layernorm_fwd_bf16", ln_fwd_plain, n * 4, "K7 (activation done by the GEMM epilogue)")
+    case("layernorm_bwd_stored_act_bf16", ln_bwd_stored, n * 8, "K7 bwd, act'(z) read from memory")
 
     Cs = 1000
     lg = torch.randn(R, Cs, device=dev).to(bf)

@@ -1,0 +1,133 @@
+"""Batched tcgen05 GEMM (4-D TMA maps) and the attention built on it, against fp32 PyTorch."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("Bo,Bi,M,N,K", [(1, 3, 128, 256, 64), (2, 4, 200, 72, 96), (1, 16, 512, 512, 64),
+                                         (3, 1, 77, 130, 40), (2, 8, 256, 64, 256)])
+def test_batched_gemm_contiguous(Bo, Bi, M, N, K):
+    from ferrum_b200.ops import gemm
+
+    torch.manual_seed(0)
+    a = torch.randn(Bo, Bi, M, K, device="cuda").bfloat16()
+    b = torch.randn(Bo, Bi, N, K, device="cuda").bfloat16()
+    ref = torch.matmul(a.float(), b.float().transpose(-1, -2)) * 0.5
+    out = gemm.gemm_bf16_batched(a, b, alpha=0.5)
+    assert out.shape == (Bo, Bi, M, N) and _rel(out, ref) < 6e-3
+    out32 = gemm.gemm_bf16_batched(a, b, out_dtype=torch.float32, alpha=0.5)
+    assert _rel(out32, ref) < 1e-5
+    acc = torch.ones_like(out32)
+    gemm.gemm_bf16_batched(a, b, out=acc, alpha=0.5, accumulate=True)
+    assert _rel(acc, ref + 1) < 1e-5
+
+
+def test_batched_gemm_strided_head_views():
+    from ferrum_b200.ops import gemm
+
+    torch.manual_seed(1)
+    B, S, H, D = 2, 192, 4, 64
+    q = torch.randn(B, S, H * D, device="cuda").bfloat16()
+    k = torch.randn(B, S, H * D, device="cuda").bfloat16()
+    v = torch.randn(B, S, H * D, device="cuda").bfloat16()
+    qh, kh, vh = (t.view(B, S, H, D).permute(0, 2, 1, 3) for t in (q, k, v))  # no copies
+    assert gemm.batched_operand_ok(qh) and gemm.batched_operand_ok(vh.transpose(-1, -2))
+    s = gemm.gemm_bf16_batched(qh, kh, out_dtype=torch.float32, alpha=0.125)
+    assert _rel(s, torch.matmul(qh.float(), kh.float().transpose(-1, -2)) * 0.125) < 1e-5
+    p = torch.softmax(s, -1).bfloat16()
+    # P @ V: V^T as the [N, K] operand is an MN-major view; output written in [B, S, H, D] order
+    out = torch.empty(B, S, H, D, device="cuda", dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    gemm.gemm_bf16_batched(p, vh.transpose(-1, -2), out=out)
+    assert _rel(out, torch.matmul(p.float(), vh.float())) < 6e-3
+    # both operands MN-major (the dV = P^T dO product)
+    do = torch.randn(B, H, S, D, device="cuda").bfloat16()
+    dv = gemm.gemm_bf16_batched(p.transpose(-1, -2), do.transpose(-1, -2), out_dtype=torch.float32)
+    assert _rel(dv, torch.matmul(p.float().transpose(-1, -2), do.float())) < 1e-5
+
+
+def test_matmul_batched_autocast_uses_tensor_cores_and_differentiates():
+    import ferrum_b200 as fb
+    from ferrum_b200 import _lib
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(2)
+    a = torch.randn(6, 96, 64, device="cuda", requires_grad=True)
+    b = torch.randn(6, 64, 80, device="cuda", requires_grad=True)
+    before = _lib.launch_count()
+    with fb.autocast():
+        y = F.matmul(a, b)
+    y.float().square().mean().backward()
+    assert _lib.launch_count() > before
+    ar, br = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = torch.matmul(ar, br)
+    yr.square().mean().backward()
+    assert _rel(y, yr) < 1e-2 and _rel(a.grad, ar.grad) < 2e-2 and _rel(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_multi_head_attention_matches_fp32_reference(masked):
+    import ferrum_b200 as fb
+    from ferrum_b200.nn import MultiHeadAttention
+
+    torch.manual_seed(3)
+    B, S, E, H = 2, 128, 256, 4
+    mha = MultiHeadAttention(E, H, device=fb.Device.Cuda(0))
+    x = torch.randn(B, S, E, device="cuda", requires_grad=True)
+    mask = torch.tril(torch.ones(S, S, device="cuda", dtype=torch.bool)) if masked else None
+
+    def reference(xr):
+        Wq, Wk, Wv, Wo = (m.weight.detach().float() for m in (mha.q_proj, mha.k_proj, mha.v_proj, mha.out_proj))
+        bq, bk, bv, bo = (m.bias.detach().float() for m in (mha.q_proj, mha.k_proj, mha.v_proj, mha.out_proj))
+        sp = lambda t: t.view(B, S, H, E // H).transpose(1, 2)
+        q, k, v = sp(xr @ Wq.t() + bq), sp(xr @ Wk.t() + bk), sp(xr @ Wv.t() + bv)
+        s = q @ k.transpose(-1, -2) / math.sqrt(E // H)
+        if mask is not None:
+            s = s.masked_fill(~mask, -1e9)
+        return (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, S, E) @ Wo.t() + bo
+
+    # fp32 path (SIMT batched kernel)
+    y32 = mha.forward_attn(x, x, x, mask)
+    xr = x.detach().clone().requires_grad_(True)
+    yr = reference(xr)
+    assert _rel(y32, yr) < 1e-4
+    y32.square().mean().backward()
+    yr.square().mean().backward()
+    assert _rel(x.grad, xr.grad) < 1e-3
+    # bf16 tensor-core path
+    x.grad = None
+    with fb.autocast():
+        y16 = mha.forward_attn(x, x, x, mask)
+    assert _rel(y16, yr) < 3e-2
+    y16.float().square().mean().backward()
+    assert _rel(x.grad, xr.grad) < 6e-2
+
+
+def test_transformer_encoder_layer_trains_under_autocast():
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+
+    torch.manual_seed(4)
+    dev = fb.Device.Cuda(0)
+    layer = nn.TransformerEncoderLayer(128, 4, 256, device=dev)
+    head = nn.Linear(128, 5, device=dev)
+    opt = optim.Adam(list(layer.parameters()) + list(head.parameters()), optim.AdamConfig(lr=1e-3))
+    x = torch.randn(8, 32, 128, device="cuda")
+    y = torch.randint(0, 5, (8,), device="cuda")
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        with fb.autocast():
+            h = layer(x)
+            logits = head(h.float().mean(1))
+            loss = nn.cross_entropy(logits, y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.5 * losses[0]

@@ -101,9 +101,10 @@ def test_gemm_f32_batched():
 
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
 @pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 512, 256), (1024, 1000, 520), (776, 264, 1000),
-                                   (2048, 4096, 1024)])
+                                   (2048, 4096, 1024), (4096, 4096, 256), (8192, 4096, 128)])
 def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn, M, N, K):
-    """cta_group::2 kernel (256x256 tile per CTA pair) against the fp32 reference, all operand layouts."""
+    """cta_group::2 kernel (256x256 and 256x128 tiles per CTA pair, chosen by wave fill) against the fp32
+    reference, all operand layouts."""
     from ferrum_b200.ops import gemm as g
     from ferrum_b200.utils.runtime import check_status
 
@@ -111,6 +112,7 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn, M, N, K):
     a = _mk(M, K, a_mn, 0.5)
     b = _mk(N, K, b_mn, 0.5)
     bias = torch.randn(N, device="cuda")
+    prev = g._use_2cta
     g.set_gemm_2cta(True)
     try:
         out = g.gemm_bf16(a, b, bias=bias, out_dtype=torch.float32)
@@ -119,7 +121,7 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn, M, N, K):
         outb = g.gemm_bf16(a, b, act="relu")
         check_status()
     finally:
-        g.set_gemm_2cta(False)
+        g.set_gemm_2cta(prev)
     ref = _ref(a, b, bias, None)
     tol = 2e-3 * (K ** 0.5) * 0.25 + 1e-3
     assert (out - ref).abs().max().item() < tol

@@ -413,3 +413,96 @@ def test_fused_linear_gelu_layernorm_block(low):
     for a, b in zip(mine, theirs):
         scale = max(1.0, b.abs().max().item())
         assert (a.float() - b).abs().max().item() < (0.15 if low else 2e-3) * scale
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 4096), (150, 2560), (64, 4000), (70, 1024), (33, 264)])
+@pytest.mark.parametrize("with_act_grad", [False, True])
+def test_layernorm_bwd_with_stored_activation_derivative(rows, cols, with_act_grad):
+    """LayerNorm backward on bf16 rows where the activation derivative comes as a tensor: the 512-thread
+    streaming kernel for 2056..4096 columns, the register-tiled kernels otherwise."""
+    from ferrum_b200 import _lib
+
+    lib = _lib.cuda()
+    torch.manual_seed(rows + cols)
+    a = torch.randn(rows, cols, device="cuda").bfloat16()
+    dy = torch.randn(rows, cols, device="cuda").bfloat16()
+    da = (torch.rand(rows, cols, device="cuda") * 1.5).bfloat16() if with_act_grad else None
+    gamma = torch.rand(cols, device="cuda") + 0.5
+    af = a.float().requires_grad_(True)
+    gr = gamma.clone().requires_grad_(True)
+    br = torch.zeros(cols, device="cuda", requires_grad=True)
+    yr = torch.nn.functional.layer_norm(af, (cols,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    ref_dx = af.grad * (da.float() if with_act_grad else 1.0)
+    mean = a.float().mean(1)
+    rstd = torch.rsqrt(a.float().var(1, unbiased=False) + 1e-5)
+    dx = torch.empty_like(a)
+    nblk = lib.fb_layernorm_bwd_blocks(rows, cols)
+    partial = torch.empty(max(nblk, 1), 3, cols, device="cuda")
+    stats = torch.zeros(3, cols, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.fb_layernorm_bwd(dy.data_ptr(), a.data_ptr(), da.data_ptr() if with_act_grad else None, gamma.data_ptr(),
+                              mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), partial.data_ptr(), stats.data_ptr(),
+                              rows, cols, 0, 3, nblk, 1, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    scale = max(1.0, ref_dx.abs().max().item())
+    assert (dx.float() - ref_dx).abs().max().item() < 2e-2 * scale
+    assert torch.allclose(stats[0], gr.grad, atol=2e-2 * max(1.0, gr.grad.abs().max().item()))
+    assert torch.allclose(stats[1], br.grad, atol=2e-2 * max(1.0, br.grad.abs().max().item()))
+    ref_cs = ref_dx.sum(0)
+    assert torch.allclose(stats[2], ref_cs, atol=3e-2 * max(1.0, ref_cs.abs().max().item()))
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu", "silu", "tanh", "sigmoid"])
+@pytest.mark.parametrize("M,N,K", [(640, 512, 128), (200, 264, 136), (1024, 1000, 64)])
+def test_gemm_epilogue_stores_activation_and_derivative(act, M, N, K):
+    from ferrum_b200.ops import gemm
+
+    torch.manual_seed(M + N)
+    a = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    der = torch.empty_like(out)
+    gemm.gemm_bf16(a, b, bias=bias, act=act, out=out, act_grad=der)
+    z = (a.float() @ b.float().t() + bias).requires_grad_(True)
+    fn = {"gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "relu": torch.relu,
+          "silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid}[act]
+    val = fn(z)
+    val.sum().backward()
+    assert (out.float() - val).abs().max().item() < 3e-2 * max(1.0, val.abs().max().item())
+    mism = (der.float() - z.grad).abs()
+    if act == "relu":  # pre-activations within rounding of zero may land on either side
+        assert (mism > 1e-2).float().mean().item() < 1e-3
+    else:
+        assert mism.max().item() < 2e-2
+
+
+@pytest.mark.parametrize("op", ["sum", "mean", "max", "min", "prod"])
+@pytest.mark.parametrize("shape,dim", [((8192, 256), 0), ((3, 700, 132), 1), ((5000, 4), 0), ((2, 33, 8), 1)])
+def test_reduce_columns_vectorised(op, shape, dim):
+    F = _F()
+    torch.manual_seed(7)
+    x = torch.randn(*shape, device="cuda")
+    if op == "prod":
+        x = 1.0 + 0.001 * x
+    got = F.raw_reduce(x, op, dim)
+    xd = x.double()
+    ref = {"sum": xd.sum(dim), "mean": xd.mean(dim), "max": xd.max(dim).values, "min": xd.min(dim).values,
+           "prod": xd.prod(dim)}[op]
+    assert got.shape == ref.shape
+    assert torch.allclose(got.double(), ref, rtol=1e-4, atol=1e-3)
+
+
+def test_cross_entropy_backward_scales_by_incoming_gradient_on_device():
+    F = _F()
+    torch.manual_seed(9)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(257, 1000, device="cuda").to(dtype)
+        labels = torch.randint(0, 1000, (257,), device="cuda")
+        x1 = x.clone().requires_grad_(True)
+        x2 = x.float().clone().requires_grad_(True)
+        (F.cross_entropy_logits(x1, labels) * -3.5).backward()
+        (torch.nn.functional.cross_entropy(x2, labels) * -3.5).backward()
+        assert torch.allclose(x1.grad.float(), x2.grad, atol=1e-6 if dtype == torch.float32 else 2e-4, rtol=2e-2)

@@ -106,3 +106,25 @@ def test_step_timer_and_peaks_file():
     assert len(lines) == 2 and "samples_per_s" in lines[0] and len(t.history) == 2
     pk = measured_peaks()
     assert pk is None or "hbm_gbs" in pk
+
+
+def test_core_autograd_hook_names():
+    from ferrum_b200 import autograd as ag
+
+    a, b = ag.new_tensor_id(), ag.new_tensor_id()
+    assert b == a + 1
+    n1, n2 = ag.NodeId.new(), ag.NodeId.new()
+    assert n2 == n1 + 1 and isinstance(n1, int)
+    seen = []
+    ag.register_autograd_callbacks(lambda *a, **k: seen.append(("rec", a)), lambda out: seen.append(("bwd", out)))
+    ag.record_operation("add", 1, 2)
+    ag.execute_backward("loss")
+    with ag.no_grad():
+        ag.record_operation("skipped")
+    ag.unregister_autograd_callbacks()
+    ag.record_operation("ignored")
+    assert seen == [("rec", ("add", 1, 2)), ("bwd", "loss")]
+    assert ag.is_autograd_enabled()
+    ag.set_autograd_enabled(False)
+    assert not ag.is_autograd_enabled()
+    ag.set_autograd_enabled(True)

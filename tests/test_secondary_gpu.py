@@ -1,0 +1,145 @@
+"""Recurrent gate kernels, im2col / col2im convolution lowering and pooling kernels against PyTorch fp32."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol=1e-4):
+    assert a.shape == b.shape
+    assert (a.float() - b.float()).abs().max().item() <= tol * max(1.0, b.float().abs().max().item())
+
+
+def test_lstm_gate_kernel_matches_reference_formulas():
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    B, H = 37, 96
+    xi, hh, c = (torch.randn(B, 4 * H, device="cuda", requires_grad=True),
+                 torch.randn(B, 4 * H, device="cuda", requires_grad=True),
+                 torch.randn(B, H, device="cuda", requires_grad=True))
+    h2, c2 = F.lstm_gates(xi, hh, c)
+    (h2.square().sum() + (c2 * 0.5).sum()).backward()
+    xr, hr, cr = (t.detach().clone().requires_grad_(True) for t in (xi, hh, c))
+    i, f, g, o = (xr + hr).chunk(4, -1)
+    cref = torch.sigmoid(f) * cr + torch.sigmoid(i) * torch.tanh(g)
+    href = torch.sigmoid(o) * torch.tanh(cref)
+    (href.square().sum() + (cref * 0.5).sum()).backward()
+    _close(h2, href), _close(c2, cref)
+    _close(xi.grad, xr.grad), _close(hh.grad, hr.grad), _close(c.grad, cr.grad)
+
+
+def test_gru_gate_kernel_matches_reference_formulas():
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(1)
+    B, H = 29, 64
+    xi, hh, h = (torch.randn(B, 3 * H, device="cuda", requires_grad=True),
+                 torch.randn(B, 3 * H, device="cuda", requires_grad=True),
+                 torch.randn(B, H, device="cuda", requires_grad=True))
+    out = F.gru_gates(xi, hh, h)
+    out.square().sum().backward()
+    xr, hr, pr = (t.detach().clone().requires_grad_(True) for t in (xi, hh, h))
+    a, b_, c_ = xr.chunk(3, -1)
+    d, e, f = hr.chunk(3, -1)
+    r, z = torch.sigmoid(a + d), torch.sigmoid(b_ + e)
+    n = torch.tanh(c_ + r * f)
+    ref = (1 - z) * n + z * pr
+    ref.square().sum().backward()
+    _close(out, ref)
+    _close(xi.grad, xr.grad), _close(hh.grad, hr.grad), _close(h.grad, pr.grad)
+
+
+@pytest.mark.parametrize("cls", ["LSTM", "GRU"])
+def test_recurrent_modules_match_torch(cls):
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    torch.manual_seed(2)
+    T, B, Fi, H = 7, 5, 12, 16
+    ours = getattr(nn, cls)(Fi, H, 2, device=fb.Device.Cuda(0))
+    ref = getattr(torch.nn, cls)(Fi, H, 2).cuda()
+    for l, cell in enumerate(ours.cells):
+        for ours_name, ref_name in (("weight_ih", f"weight_ih_l{l}"), ("weight_hh", f"weight_hh_l{l}"),
+                                    ("bias_ih", f"bias_ih_l{l}"), ("bias_hh", f"bias_hh_l{l}")):
+            getattr(ref, ref_name).data.copy_(getattr(cell, ours_name).data)
+    x = torch.randn(T, B, Fi, device="cuda", requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    y = ours(x)
+    yr, _ = ref(xr)
+    _close(y, yr, 1e-4)
+    y.square().mean().backward()
+    yr.square().mean().backward()
+    _close(x.grad, xr.grad, 1e-4)
+    _close(ours.cells[0].weight_hh.grad, ref.weight_hh_l0.grad, 1e-4)
+
+
+@pytest.mark.parametrize("cfg", [(3, 8, 3, 1, 1, 1, 1), (4, 6, 5, 2, 2, 1, 2), (6, 4, 3, 1, 0, 2, 1), (2, 2, 2, 3, 1, 1, 1)])
+def test_conv2d_forward_backward_matches_torch(cfg):
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    cin, cout, k, stride, pad, dil, groups = cfg
+    torch.manual_seed(3)
+    conv = nn.Conv2d(cin, cout, k, stride, pad, dil, groups, device=fb.Device.Cuda(0))
+    x = torch.randn(3, cin, 17, 13, device="cuda", requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    y = conv(x)
+    wr, br = conv.weight.detach().clone().requires_grad_(True), conv.bias.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.conv2d(xr, wr, br, stride, pad, dil, groups)
+    _close(y, yr, 1e-4)
+    y.square().mean().backward()
+    yr.square().mean().backward()
+    _close(x.grad, xr.grad, 1e-4), _close(conv.weight.grad, wr.grad, 1e-4), _close(conv.bias.grad, br.grad, 1e-4)
+
+
+def test_im2col_rows_are_gemm_ready():
+    from ferrum_b200.ops import functional as F
+
+    x = torch.randn(2, 3, 6, 5, device="cuda")
+    cols = F.im2col(x, (3, 2), (1, 2), (1, 0), (1, 1))
+    ref = torch.nn.functional.unfold(x, (3, 2), dilation=1, padding=(1, 0), stride=(1, 2))
+    assert cols.is_contiguous() and cols.shape == (2 * ref.shape[2], 3 * 3 * 2)
+    _close(cols, ref.transpose(1, 2).reshape(cols.shape), 0)
+
+
+@pytest.mark.parametrize("op", ["max", "avg"])
+@pytest.mark.parametrize("k,s", [(2, 2), (3, 2), (3, 1)])
+def test_pool2d_forward_backward(op, k, s):
+    from ferrum_b200 import nn
+
+    torch.manual_seed(4)
+    x = torch.randn(2, 5, 11, 14, device="cuda", requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    pool = (nn.MaxPool2d if op == "max" else nn.AvgPool2d).with_stride(k, s)
+    y = pool(x)
+    yr = (torch.nn.functional.max_pool2d if op == "max" else torch.nn.functional.avg_pool2d)(xr, k, s)
+    _close(y, yr, 1e-6)
+    (y * torch.arange(y.numel(), device="cuda").reshape(y.shape)).sum().backward()
+    (yr * torch.arange(y.numel(), device="cuda").reshape(y.shape)).sum().backward()
+    _close(x.grad, xr.grad, 1e-5)
+
+
+def test_small_cnn_trains():
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+
+    class Flatten(nn.Module):
+        def forward(self, t):
+            return t.reshape(t.shape[0], -1)
+
+    torch.manual_seed(5)
+    dev = fb.Device.Cuda(0)
+    net = nn.Sequential(nn.Conv2d(1, 8, 3, 1, 1, device=dev), nn.ReLU(), nn.MaxPool2d(2), Flatten(),
+                        nn.Linear(8 * 4 * 4, 3, device=dev))
+    opt = optim.Adam(net.parameters(), optim.AdamConfig(lr=1e-2))
+    x = torch.randn(24, 1, 8, 8, device="cuda")
+    y = torch.randint(0, 3, (24,), device="cuda")
+    losses = []
+    for _ in range(40):
+        opt.zero_grad()
+        loss = nn.cross_entropy(net(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.5 * losses[0]
