@@ -33,6 +33,18 @@ from . import parallel as distributed  # noqa: E402
 from .autograd import GradientTape, NoGradGuard, backward, is_grad_enabled, no_grad  # noqa: E402
 from .serialize import load, save  # noqa: E402
 
+
+
+def manual_seed(seed: int) -> None:
+    """Seed every random source the package draws from (the reference is unseeded: ferrum-core/src/tensor.rs:216):
+    tensor factories, parameter initialisers and dropout take their streams from the torch generators."""
+    import torch
+
+    torch.manual_seed(int(seed))
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(int(seed))
+
+
 Result = object  # Rust's Result<T> maps to "returns T or raises FerrumError"
 
 

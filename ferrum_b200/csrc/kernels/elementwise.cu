@@ -136,7 +136,8 @@ __device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
   return u;
 }
 
-__global__ void unary_fwd_f32(const float* __restrict__ x, float* __restrict__ y, long long n, int op, float a,
+template <int OP>
+__global__ void unary_fwd_f32(const float* __restrict__ x, float* __restrict__ y, long long n, int, float a,
                               float b) {
   const long long n4 = n >> 2;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -145,20 +146,21 @@ __global__ void unary_fwd_f32(const float* __restrict__ x, float* __restrict__ y
   if (aligned) {
     for (long long i = tid; i < n4; i += stride) {
       float4 v = reinterpret_cast<const float4*>(x)[i];
-      v.x = unary_f(v.x, op, a, b);
-      v.y = unary_f(v.y, op, a, b);
-      v.z = unary_f(v.z, op, a, b);
-      v.w = unary_f(v.w, op, a, b);
+      v.x = unary_f(v.x, OP, a, b);
+      v.y = unary_f(v.y, OP, a, b);
+      v.z = unary_f(v.z, OP, a, b);
+      v.w = unary_f(v.w, OP, a, b);
       reinterpret_cast<float4*>(y)[i] = v;
     }
-    for (long long i = (n4 << 2) + tid; i < n; i += stride) y[i] = unary_f(x[i], op, a, b);
+    for (long long i = (n4 << 2) + tid; i < n; i += stride) y[i] = unary_f(x[i], OP, a, b);
   } else {
-    for (long long i = tid; i < n; i += stride) y[i] = unary_f(x[i], op, a, b);
+    for (long long i = tid; i < n; i += stride) y[i] = unary_f(x[i], OP, a, b);
   }
 }
 
+template <int OP>
 __global__ void unary_bwd_f32(const float* __restrict__ dy, const float* __restrict__ s, float* __restrict__ dx,
-                              long long n, int op, float a, float b) {
+                              long long n, int, float a, float b) {
   const long long n4 = n >> 2;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -171,20 +173,21 @@ __global__ void unary_bwd_f32(const float* __restrict__ dy, const float* __restr
       const float4 g = reinterpret_cast<const float4*>(dy)[i];
       const float4 v = reinterpret_cast<const float4*>(sp)[i];
       float4 o;
-      o.x = unary_grad(g.x, v.x, op, a, b);
-      o.y = unary_grad(g.y, v.y, op, a, b);
-      o.z = unary_grad(g.z, v.z, op, a, b);
-      o.w = unary_grad(g.w, v.w, op, a, b);
+      o.x = unary_grad(g.x, v.x, OP, a, b);
+      o.y = unary_grad(g.y, v.y, OP, a, b);
+      o.z = unary_grad(g.z, v.z, OP, a, b);
+      o.w = unary_grad(g.w, v.w, OP, a, b);
       reinterpret_cast<float4*>(dx)[i] = o;
     }
-    for (long long i = (n4 << 2) + tid; i < n; i += stride) dx[i] = unary_grad(dy[i], sp[i], op, a, b);
+    for (long long i = (n4 << 2) + tid; i < n; i += stride) dx[i] = unary_grad(dy[i], sp[i], OP, a, b);
   } else {
-    for (long long i = tid; i < n; i += stride) dx[i] = unary_grad(dy[i], sp[i], op, a, b);
+    for (long long i = tid; i < n; i += stride) dx[i] = unary_grad(dy[i], sp[i], OP, a, b);
   }
 }
 
+template <int OP>
 __global__ void unary_fwd_bf16(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n,
-                               int op, float a, float b) {
+                               int, float a, float b) {
   const long long n8 = n >> 3;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -200,24 +203,25 @@ __global__ void unary_fwd_bf16(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
       float f[8];
       bf16x8_to_f32(r0, f);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], op, a, b);
+      for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], OP, a, b);
       reinterpret_cast<uint4*>(y)[i] = f32_to_bf16x8(f);
       if (j < n8) {
         bf16x8_to_f32(r1, f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], op, a, b);
+        for (int k = 0; k < 8; ++k) f[k] = unary_f_fast(f[k], OP, a, b);
         reinterpret_cast<uint4*>(y)[j] = f32_to_bf16x8(f);
       }
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
-      y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), op, a, b));
+      y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), OP, a, b));
   } else {
-    for (long long i = tid; i < n; i += stride) y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), op, a, b));
+    for (long long i = tid; i < n; i += stride) y[i] = __float2bfloat16_rn(unary_f_fast(__bfloat162float(x[i]), OP, a, b));
   }
 }
 
+template <int OP>
 __global__ void unary_bwd_bf16(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ s,
-                               __nv_bfloat16* __restrict__ dx, long long n, int op, float a, float b) {
+                               __nv_bfloat16* __restrict__ dx, long long n, int, float a, float b) {
   const long long n8 = n >> 3;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -238,21 +242,21 @@ __global__ void unary_bwd_bf16(const __nv_bfloat16* __restrict__ dy, const __nv_
       bf16x8_to_f32(rg0, g);
       bf16x8_to_f32(rv0, v);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], op, a, b);
+      for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], OP, a, b);
       reinterpret_cast<uint4*>(dx)[i] = f32_to_bf16x8(g);
       if (j < n8) {
         bf16x8_to_f32(rg1, g);
         bf16x8_to_f32(rv1, v);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], op, a, b);
+        for (int k = 0; k < 8; ++k) g[k] = unary_grad_fast(g[k], v[k], OP, a, b);
         reinterpret_cast<uint4*>(dx)[j] = f32_to_bf16x8(g);
       }
     }
     for (long long i = (n8 << 3) + tid; i < n; i += stride)
-      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
+      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), OP, a, b));
   } else {
     for (long long i = tid; i < n; i += stride)
-      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), op, a, b));
+      dx[i] = __float2bfloat16_rn(unary_grad_fast(__bfloat162float(dy[i]), __bfloat162float(sp[i]), OP, a, b));
   }
 }
 
@@ -446,15 +450,44 @@ int grid_for(long long work_items, int block) {
 
 using namespace fb;
 
+// The op is a template parameter of the kernels (a switch evaluated per element costs more issue slots than
+// the arithmetic of most ops); this turns the runtime op into the instantiation.
+#define FB_UNARY_DISPATCH(OPV, CALL) \
+  switch (OPV) {                     \
+    case 0: { constexpr int OP = 0; CALL; } break;   \
+    case 1: { constexpr int OP = 1; CALL; } break;   \
+    case 2: { constexpr int OP = 2; CALL; } break;   \
+    case 3: { constexpr int OP = 3; CALL; } break;   \
+    case 4: { constexpr int OP = 4; CALL; } break;   \
+    case 5: { constexpr int OP = 5; CALL; } break;   \
+    case 6: { constexpr int OP = 6; CALL; } break;   \
+    case 7: { constexpr int OP = 7; CALL; } break;   \
+    case 8: { constexpr int OP = 8; CALL; } break;   \
+    case 9: { constexpr int OP = 9; CALL; } break;   \
+    case 10: { constexpr int OP = 10; CALL; } break; \
+    case 11: { constexpr int OP = 11; CALL; } break; \
+    case 12: { constexpr int OP = 12; CALL; } break; \
+    case 13: { constexpr int OP = 13; CALL; } break; \
+    case 14: { constexpr int OP = 14; CALL; } break; \
+    case 15: { constexpr int OP = 15; CALL; } break; \
+    case 16: { constexpr int OP = 16; CALL; } break; \
+    case 17: { constexpr int OP = 17; CALL; } break; \
+    case 18: { constexpr int OP = 18; CALL; } break; \
+    case 19: { constexpr int OP = 19; CALL; } break; \
+    case 20: { constexpr int OP = 20; CALL; } break; \
+    case 21: { constexpr int OP = 21; CALL; } break; \
+    default: return -1;              \
+  }
+
 extern "C" int fb_unary_fwd(const void* x, void* y, long long n, int op, float alpha, float beta, int dtype,
                             cudaStream_t stream) {
   if (n <= 0) return 0;
   if (dtype == FB_DT_F32) {
-    unary_fwd_f32<<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(static_cast<const float*>(x),
-                                                                 static_cast<float*>(y), n, op, alpha, beta);
+    FB_UNARY_DISPATCH(op, (unary_fwd_f32<OP><<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(
+                              static_cast<const float*>(x), static_cast<float*>(y), n, op, alpha, beta)))
   } else if (dtype == FB_DT_BF16) {
-    unary_fwd_bf16<<<grid_for((n + 7) / 8, 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, op, alpha, beta);
+    FB_UNARY_DISPATCH(op, (unary_fwd_bf16<OP><<<grid_for((n + 7) / 8, 256), 256, 0, stream>>>(
+                              static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, op, alpha, beta)))
   } else {
     return -1;
   }
@@ -465,12 +498,13 @@ extern "C" int fb_unary_bwd(const void* dy, const void* saved, void* dx, long lo
                             float beta, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (dtype == FB_DT_F32) {
-    unary_bwd_f32<<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(
-        static_cast<const float*>(dy), static_cast<const float*>(saved), static_cast<float*>(dx), n, op, alpha, beta);
+    FB_UNARY_DISPATCH(op, (unary_bwd_f32<OP><<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(
+                              static_cast<const float*>(dy), static_cast<const float*>(saved), static_cast<float*>(dx),
+                              n, op, alpha, beta)))
   } else if (dtype == FB_DT_BF16) {
-    unary_bwd_bf16<<<grid_for((n + 7) / 8, 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(saved),
-        static_cast<__nv_bfloat16*>(dx), n, op, alpha, beta);
+    FB_UNARY_DISPATCH(op, (unary_bwd_bf16<OP><<<grid_for((n + 7) / 8, 256), 256, 0, stream>>>(
+                              static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(saved),
+                              static_cast<__nv_bfloat16*>(dx), n, op, alpha, beta)))
   } else {
     return -1;
   }

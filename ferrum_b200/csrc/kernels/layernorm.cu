@@ -126,7 +126,7 @@ __device__ __forceinline__ float row_sum(float v, float (*smem)[8]) {
 
 // Forward.  A row lives in registers: TPR threads x K vectors of 8 elements.
 template <typename T, int TPR, int K>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (K * sizeof(T) <= 2) ? 4 : ((K * sizeof(T) <= 4) ? 3 : ((K * sizeof(T) <= 8) ? 2 : 1)))
 ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows,
               int cols, float eps, int pre_act) {
@@ -138,26 +138,16 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
   const int nvec = cols >> 3;
   const float inv_n = 1.f / static_cast<float>(cols);
   const long long row_stride = static_cast<long long>(gridDim.x) * kRowsPerBlock;
-  typename V8<T>::Raw raw[K], nxt[K];
-  {
-    const long long r0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock + sub;
+  using Raw = typename V8<T>::Raw;
+  auto load = [&](long long r, Raw (&buf)[K]) {
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int vi = t + k * TPR;
-      if (r0 < rows && vi < nvec) raw[k] = V8<T>::ld(x + r0 * cols + vi * 8);
+      if (r < rows && vi < nvec) buf[k] = V8<T>::ld(x + r * cols + vi * 8);
     }
-  }
-  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows; row0 += row_stride) {
-    const long long row = row0 + sub;
+  };
+  auto process = [&](long long row, const Raw (&raw)[K]) {
     const bool live = row < rows;
-    {  // the next row's loads are in flight while this row is reduced and written
-      const long long rn = row + row_stride;
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const int vi = t + k * TPR;
-        if (rn < rows && vi < nvec) nxt[k] = V8<T>::ld(x + rn * cols + vi * 8);
-      }
-    }
     float v[K][8];
     float s = 0.f;
 #pragma unroll
@@ -207,8 +197,26 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
         V8<T>::st(y + row * cols + vi * 8, o);
       }
     }
-#pragma unroll
-    for (int k = 0; k < K; ++k) raw[k] = nxt[k];
+  };
+  // Three register sets rotating by name (loop unrolled by three): the loads of the next two rows stay in
+  // flight while a row is reduced and written, and no register-to-register rotation waits on the newest load.
+  // Row slots of a block advance in lockstep (row0 is uniform), so the barriers inside row_sum stay uniform.
+  Raw b0[K], b1[K], b2[K];
+  long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock;
+  load(row0 + sub, b0);
+  load(row0 + row_stride + sub, b1);
+  while (row0 < rows) {
+    load(row0 + 2 * row_stride + sub, b2);
+    process(row0 + sub, b0);
+    row0 += row_stride;
+    if (row0 >= rows) break;
+    load(row0 + 2 * row_stride + sub, b0);
+    process(row0 + sub, b1);
+    row0 += row_stride;
+    if (row0 >= rows) break;
+    load(row0 + 2 * row_stride + sub, b1);
+    process(row0 + sub, b2);
+    row0 += row_stride;
   }
 }
 
@@ -367,10 +375,16 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
 
 // Backward for rows of 2056..4096 bf16 elements whose activation derivative (if any) is given as a tensor:
 // pure streaming arithmetic, so the kernel is organised around bytes in flight.  One 512-thread block per
-// SM walks its rows one at a time; a thread owns ONE 16-byte vector of each operand, keeps the loads of the
-// next two rows outstanding while it works on the current one, and a row costs a single __syncthreads (the
-// two row sums travel together through a double-buffered shared-memory slot).  gamma and the three column
-// accumulators stay in registers for the whole kernel.
+// SM walks its rows one at a time; a thread owns ONE 16-byte vector of each operand and keeps the loads of
+// the next two rows outstanding while it works on the current one.  The three register sets rotate by NAME
+// (the row loop is unrolled by three): a register-to-register rotation would make every trip wait for the
+// newest load.  A row costs a single __syncthreads (the two row sums travel together through a
+// double-buffered shared-memory slot).  gamma and the three column accumulators stay in registers.
+struct WideRow {
+  uint4 g, x, a;
+  float mu, rs;
+};
+
 __global__ void __launch_bounds__(512, 1)
 ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ act_grad, const float* __restrict__ gamma,
@@ -392,55 +406,29 @@ ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   float acc_g[8], acc_b[8], acc_c[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc_g[i] = acc_b[i] = acc_c[i] = 0.f;
-
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  uint4 g0 = zero, x0 = zero, a0 = zero, g1 = zero, x1 = zero, a1 = zero, g2 = zero, x2 = zero, a2 = zero;
-  float mu0 = 0.f, rs0 = 0.f, mu1 = 0.f, rs1 = 0.f, mu2 = 0.f, rs2 = 0.f;
-  long long row = blockIdx.x;
-  if (row < rows) {
-    mu0 = mean[row];
-    rs0 = rstd[row];
-    if (has) {
-      const long long o = row * cols + t * 8;
-      g0 = V::ld(dy + o);
-      x0 = V::ld(x + o);
-      if (use_ag) a0 = V::ld(act_grad + o);
-    }
-  }
-  if (row + stride < rows) {
-    const long long r = row + stride;
-    mu1 = mean[r];
-    rs1 = rstd[r];
-    if (has) {
-      const long long o = r * cols + t * 8;
-      g1 = V::ld(dy + o);
-      x1 = V::ld(x + o);
-      if (use_ag) a1 = V::ld(act_grad + o);
-    }
-  }
   int par = 0;
-  for (; row < rows; row += stride) {
-    {  // third row in flight
-      const long long r = row + 2 * stride;
-      if (r < rows) {
-        mu2 = mean[r];
-        rs2 = rstd[r];
-        if (has) {
-          const long long o = r * cols + t * 8;
-          g2 = V::ld(dy + o);
-          x2 = V::ld(x + o);
-          if (use_ag) a2 = V::ld(act_grad + o);
-        }
+
+  auto load = [&](long long r, WideRow& b) {
+    if (r < rows) {
+      b.mu = mean[r];
+      b.rs = rstd[r];
+      if (has) {
+        const long long o = r * cols + t * 8;
+        b.g = V::ld(dy + o);
+        b.x = V::ld(x + o);
+        if (use_ag) b.a = V::ld(act_grad + o);
       }
     }
+  };
+  auto process = [&](long long row, const WideRow& b) {
     float gv[8], h[8];
-    V::unpack(g0, gv);
-    V::unpack(x0, h);
-    const float shift = -mu0 * rs0;
+    V::unpack(b.g, gv);
+    V::unpack(b.x, h);
+    const float shift = -b.mu * b.rs;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      h[i] = fmaf(h[i], rs0, shift);
+      h[i] = fmaf(h[i], b.rs, shift);
       acc_b[i] += gv[i];
       acc_g[i] = fmaf(gv[i], h[i], acc_g[i]);
       gv[i] *= w[i];  // d = dy * gamma
@@ -462,15 +450,16 @@ ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       m1 += v.x;
       m2 += v.y;
     }
+    par ^= 1;
     m1 *= inv_n;
     m2 *= inv_n;
     if (has) {
       float o[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = rs0 * (gv[i] - m1 - h[i] * m2);
+      for (int i = 0; i < 8; ++i) o[i] = b.rs * (gv[i] - m1 - h[i] * m2);
       if (use_ag) {
         float ag[8];
-        V::unpack(a0, ag);
+        V::unpack(b.a, ag);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] *= ag[i];
       }
@@ -480,9 +469,26 @@ ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       }
       V::st(dx + row * cols + t * 8, o);
     }
-    g0 = g1; x0 = x1; a0 = a1; mu0 = mu1; rs0 = rs1;
-    g1 = g2; x1 = x2; a1 = a2; mu1 = mu2; rs1 = rs2;
-    par ^= 1;
+  };
+
+  WideRow b0, b1, b2;
+  b0.g = b0.x = b0.a = b1.g = b1.x = b1.a = b2.g = b2.x = b2.a = make_uint4(0u, 0u, 0u, 0u);
+  b0.mu = b0.rs = b1.mu = b1.rs = b2.mu = b2.rs = 0.f;
+  long long row = blockIdx.x;
+  load(row, b0);
+  load(row + stride, b1);
+  while (row < rows) {  // every condition below is uniform over the block
+    load(row + 2 * stride, b2);
+    process(row, b0);
+    row += stride;
+    if (row >= rows) break;
+    load(row + 2 * stride, b0);
+    process(row, b1);
+    row += stride;
+    if (row >= rows) break;
+    load(row + 2 * stride, b1);
+    process(row, b2);
+    row += stride;
   }
   if (has) {
     float* pg = partial + static_cast<long long>(blockIdx.x) * 3 * cols + t * 8;
@@ -630,6 +636,19 @@ bool aligned16(const void* a, const void* b, const void* c, const void* d) {
            reinterpret_cast<uintptr_t>(d)) & 15) == 0;
 }
 
+// Persistent grid: exactly the blocks that are resident at once, so every block walks the same number of rows.
+template <typename T, int TPR, int K>
+void launch_fwd(const T* xp, const float* gamma, const float* beta, T* yp, float* mean, float* rstd, long long rows,
+                int cols, float eps, int pre_act, long long nb, cudaStream_t st) {
+  static int occ = 0;
+  if (occ == 0 &&
+      (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, ln_fwd_kernel<T, TPR, K>, 256, 0) != cudaSuccess || occ < 1))
+    occ = 1;
+  const long long cap = static_cast<long long>(sm_count()) * occ;
+  const int grid = static_cast<int>(nb < cap ? nb : cap);
+  ln_fwd_kernel<T, TPR, K><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act);
+}
+
 template <typename T>
 int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, long long rows,
           int cols, float eps, int pre_act, cudaStream_t st) {
@@ -639,9 +658,8 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
   if (geometry(cols, &g) && aligned16(x, y, gamma, beta)) {
     const long long rpb = 256 / g.tpr;
     const long long nb = (rows + rpb - 1) / rpb;
-    const int grid = static_cast<int>(nb < sm_count() * 8LL ? nb : sm_count() * 8LL);
 #define FB_LN_FWD(TPR, K) \
-  ln_fwd_kernel<T, TPR, K><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act)
+  launch_fwd<T, TPR, K>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, nb, st)
     if (g.tpr == 32 && g.k == 1) FB_LN_FWD(32, 1);
     else if (g.tpr == 32) FB_LN_FWD(32, 2);
     else if (g.tpr == 128 && g.k == 1) FB_LN_FWD(128, 1);

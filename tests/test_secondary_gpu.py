@@ -58,20 +58,20 @@ def test_recurrent_modules_match_torch(cls):
     torch.manual_seed(2)
     T, B, Fi, H = 7, 5, 12, 16
     ours = getattr(nn, cls)(Fi, H, 2, device=fb.Device.Cuda(0))
-    ref = getattr(torch.nn, cls)(Fi, H, 2).cuda()
+    ref = getattr(torch.nn, cls)(Fi, H, 2).double()  # CPU float64: cuDNN's fp32 RNN may run on TF32
     for l, cell in enumerate(ours.cells):
         for ours_name, ref_name in (("weight_ih", f"weight_ih_l{l}"), ("weight_hh", f"weight_hh_l{l}"),
                                     ("bias_ih", f"bias_ih_l{l}"), ("bias_hh", f"bias_hh_l{l}")):
-            getattr(ref, ref_name).data.copy_(getattr(cell, ours_name).data)
+            getattr(ref, ref_name).data.copy_(getattr(cell, ours_name).data.double().cpu())
     x = torch.randn(T, B, Fi, device="cuda", requires_grad=True)
-    xr = x.detach().clone().requires_grad_(True)
+    xr = x.detach().double().cpu().requires_grad_(True)
     y = ours(x)
     yr, _ = ref(xr)
-    _close(y, yr, 1e-4)
+    _close(y.cpu(), yr, 1e-4)
     y.square().mean().backward()
     yr.square().mean().backward()
-    _close(x.grad, xr.grad, 1e-4)
-    _close(ours.cells[0].weight_hh.grad, ref.weight_hh_l0.grad, 1e-4)
+    _close(x.grad.cpu(), xr.grad, 1e-4)
+    _close(ours.cells[0].weight_hh.grad.cpu(), ref.weight_hh_l0.grad, 1e-4)
 
 
 @pytest.mark.parametrize("cfg", [(3, 8, 3, 1, 1, 1, 1), (4, 6, 5, 2, 2, 1, 2), (6, 4, 3, 1, 0, 2, 1), (2, 2, 2, 3, 1, 1, 1)])
