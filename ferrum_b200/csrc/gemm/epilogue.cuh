@@ -53,4 +53,59 @@ __device__ __forceinline__ void act_both(float x, int act, float& val, float& de
   }
 }
 
+
+template <int ACT>
+__device__ __forceinline__ float act_value(float x) {
+  if (ACT == FB_ACT_RELU) return fmaxf(x, 0.f);
+  if (ACT == FB_ACT_GELU) {
+    const float t = tanh_approx(x * fmaf(x * x, 0.7978845608028654f * 0.044715f, 0.7978845608028654f));
+    const float hx = 0.5f * x;
+    return fmaf(hx, t, hx);
+  }
+  if (ACT == FB_ACT_SILU) return x / (1.f + __expf(-x));
+  if (ACT == FB_ACT_TANH) return tanh_approx(x);
+  if (ACT == FB_ACT_SIGMOID) return 1.f / (1.f + __expf(-x));
+  return x;
+}
+
+// The activation is chosen ONCE per 32-column chunk; a switch evaluated per element costs more issue slots
+// than the activation itself and made the epilogue the bottleneck of the GEMM.
+template <int ACT>
+__device__ __forceinline__ void act_chunk_t(float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = act_value<ACT>(v[i]);
+}
+__device__ __forceinline__ void act_chunk(float (&v)[32], int act) {
+  switch (act) {
+    case FB_ACT_RELU: act_chunk_t<FB_ACT_RELU>(v); break;
+    case FB_ACT_GELU: act_chunk_t<FB_ACT_GELU>(v); break;
+    case FB_ACT_SILU: act_chunk_t<FB_ACT_SILU>(v); break;
+    case FB_ACT_TANH: act_chunk_t<FB_ACT_TANH>(v); break;
+    case FB_ACT_SIGMOID: act_chunk_t<FB_ACT_SIGMOID>(v); break;
+    default: break;
+  }
+}
+
+// v <- act(v), d <- act'(v) for a 32-column chunk.
+template <int ACT>
+__device__ __forceinline__ void act_both_chunk_t(float (&v)[32], float (&d)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float a, g;
+    act_both(v[i], ACT, a, g);  // ACT is a constant here: the switch folds away
+    v[i] = a;
+    d[i] = g;
+  }
+}
+__device__ __forceinline__ void act_both_chunk(float (&v)[32], float (&d)[32], int act) {
+  switch (act) {
+    case FB_ACT_RELU: act_both_chunk_t<FB_ACT_RELU>(v, d); break;
+    case FB_ACT_GELU: act_both_chunk_t<FB_ACT_GELU>(v, d); break;
+    case FB_ACT_SILU: act_both_chunk_t<FB_ACT_SILU>(v, d); break;
+    case FB_ACT_TANH: act_both_chunk_t<FB_ACT_TANH>(v, d); break;
+    case FB_ACT_SIGMOID: act_both_chunk_t<FB_ACT_SIGMOID>(v, d); break;
+    default: act_both_chunk_t<FB_ACT_NONE>(v, d); break;
+  }
+}
+
 }  // namespace fb

@@ -74,30 +74,6 @@ struct GemmArgs {
   float alpha;
 };
 
-__device__ __forceinline__ float apply_act(float x, int act) {
-  switch (act) {
-    case FB_ACT_RELU:
-      return fmaxf(x, 0.f);
-    case FB_ACT_GELU: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      float t;
-      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-      return 0.5f * x * (1.f + t);
-    }
-    case FB_ACT_SILU:
-      return x / (1.f + __expf(-x));
-    case FB_ACT_TANH: {
-      float t;
-      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
-      return t;
-    }
-    case FB_ACT_SIGMOID:
-      return 1.f / (1.f + __expf(-x));
-    default:
-      return x;
-  }
-}
-
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
   const int per_group = kGroupM * num_n;
   const int g = t / per_group;
@@ -327,15 +303,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // value and derivative of the activation, both stored as bf16
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + slice_off + static_cast<long long>(row) * p.ldc + col0;
             __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + slice_off + static_cast<long long>(row) * p.ldc + col0;
+            float dv[32];
+            act_both_chunk(v, dv, p.act);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint32_t wv[4], wd[4];
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
-                float a0, d0, a1, d1;
-                act_both(v[q * 8 + h * 2], p.act, a0, d0);
-                act_both(v[q * 8 + h * 2 + 1], p.act, a1, d1);
-                __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pd = __floats2bfloat162_rn(d0, d1);
+                __nv_bfloat162 pa = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
+                __nv_bfloat162 pd = __floats2bfloat162_rn(dv[q * 8 + h * 2], dv[q * 8 + h * 2 + 1]);
                 wv[h] = *reinterpret_cast<uint32_t*>(&pa);
                 wd[h] = *reinterpret_cast<uint32_t*>(&pd);
               }
@@ -354,10 +330,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               }
             }
           } else {
-          if (p.act != FB_ACT_NONE) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
-          }
+          if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
           if (p.out_bf16) {
             __nv_bfloat16* o =
                 reinterpret_cast<__nv_bfloat16*>(p.out) + slice_off + static_cast<long long>(row) * p.ldc + col0;

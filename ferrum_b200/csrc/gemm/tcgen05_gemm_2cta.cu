@@ -15,7 +15,8 @@
 //               on the leader's "full" mbarrier (plain cta_group::2 loads, no multicast)
 //   warp 1      TMEM allocation (both CTAs); in the leader (cluster rank 0) one lane
 //               issues every MMA and commits to the mbarriers of both CTAs
-//   warps 2..5  epilogue of this CTA's 128 rows; "accumulator drained" is signalled
+//   warps 2..5  epilogue of this CTA's 128 rows (eight warps, two per TMEM lane quarter, measured slower: the
+//               value + derivative epilogue dropped from 1500 to 1413 TFLOP/s); "accumulator drained" is signalled
 //               to the leader's mbarrier from both CTAs
 // Every wait is bounded; the two cluster barriers (after set-up, before exit) are
 // reached on every path, including the abort path.
@@ -24,6 +25,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "../common/ptx.cuh"
 #include "../common/status.h"
@@ -37,6 +39,7 @@ constexpr int kBM = 128;       // rows per CTA; the pair covers 256
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
 constexpr int kGroupM = 8;     // pair-tiles (256 rows) per rasterisation group
 constexpr int kABytes = kBM * kBK * 2;          // 16 KB
 
@@ -63,31 +66,13 @@ struct Args2 {
   int beta;
   int32_t* status;
   unsigned long long timeout_ns;
+  // Optional per-pair timing record (4 x 64-bit per pair, nanoseconds): MMA thread waiting for a drained
+  // accumulator, MMA thread waiting for operands, one epilogue warp busy, whole kernel.  NULL = off.
+  unsigned long long* prof;
+  int stream_stores;  // bf16 outputs leave with st.global.cs (evict-first) so they do not displace operand tiles in L2
 };
 
-__device__ __forceinline__ float apply_act2(float x, int act) {
-  switch (act) {
-    case FB_ACT_RELU:
-      return fmaxf(x, 0.f);
-    case FB_ACT_GELU: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      float t;
-      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-      return 0.5f * x * (1.f + t);
-    }
-    case FB_ACT_SILU:
-      return x / (1.f + __expf(-x));
-    case FB_ACT_TANH: {
-      float t;
-      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
-      return t;
-    }
-    case FB_ACT_SIGMOID:
-      return 1.f / (1.f + __expf(-x));
-    default:
-      return x;
-  }
-}
+unsigned long long* g_prof_buffer = nullptr;
 
 __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
   const int per_group = kGroupM * num_n;
@@ -136,7 +121,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&tmem_full[a], 1);
-      ptx::mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each of the two CTAs
+      ptx::mbar_init(&tmem_empty[a], 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tma_a);
@@ -217,19 +202,25 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      unsigned long long w_acc = 0, w_ops = 0;
+      const unsigned long long k_start = p.prof ? ptx::globaltimer() : 0;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        unsigned long long t0 = p.prof ? ptx::globaltimer() : 0;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 12, blockIdx.x, acc);
           break;
         }
+        if (p.prof) w_acc += ptx::globaltimer() - t0;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          t0 = p.prof ? ptx::globaltimer() : 0;
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 13, blockIdx.x, stage);
             ok = false;
             break;
           }
+          if (p.prof) w_ops += ptx::globaltimer() - t0;
           ptx::tc_fence_after();
           const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
           const uint32_t sb = sa + kABytes;
@@ -250,20 +241,27 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+      if (p.prof) {
+        p.prof[pair * 4 + 0] = w_acc;
+        p.prof[pair * 4 + 1] = w_ops;
+        p.prof[pair * 4 + 3] = ptx::globaltimer() - k_start;
+      }
     }
   } else {
     // ------------------------------------------------ epilogue (both CTAs, own 128 rows)
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;          // TMEM lanes a warp may read: 32 * (warp % 4) ...
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    unsigned long long e_busy = 0;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int m_blk, n_blk;
       tile_coords2(t, num_m, num_n, m_blk, n_blk);
       const int row = m_blk * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
       const int n0 = n_blk * kBN;
       const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
+      const unsigned long long e0 = p.prof ? ptx::globaltimer() : 0;
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) report_status(p.status, kStatusGemmTimeout, 14, blockIdx.x, acc);
         break;
@@ -290,21 +288,26 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             // value and derivative of the activation, both stored as bf16
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + 0 + static_cast<long long>(row) * p.ldc + col0;
             __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + 0 + static_cast<long long>(row) * p.ldc + col0;
+            float dv[32];
+            act_both_chunk(v, dv, p.act);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint32_t wv[4], wd[4];
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
-                float a0, d0, a1, d1;
-                act_both(v[q * 8 + h * 2], p.act, a0, d0);
-                act_both(v[q * 8 + h * 2 + 1], p.act, a1, d1);
-                __nv_bfloat162 pa = __floats2bfloat162_rn(a0, a1), pd = __floats2bfloat162_rn(d0, d1);
+                __nv_bfloat162 pa = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
+                __nv_bfloat162 pd = __floats2bfloat162_rn(dv[q * 8 + h * 2], dv[q * 8 + h * 2 + 1]);
                 wv[h] = *reinterpret_cast<uint32_t*>(&pa);
                 wd[h] = *reinterpret_cast<uint32_t*>(&pd);
               }
               if (full) {
-                reinterpret_cast<uint4*>(o)[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                reinterpret_cast<uint4*>(o2)[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                if (p.stream_stores) {
+                  __stcs(reinterpret_cast<uint4*>(o) + q, make_uint4(wv[0], wv[1], wv[2], wv[3]));
+                  __stcs(reinterpret_cast<uint4*>(o2) + q, make_uint4(wd[0], wd[1], wd[2], wd[3]));
+                } else {
+                  reinterpret_cast<uint4*>(o)[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                  reinterpret_cast<uint4*>(o2)[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                }
               } else {
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
@@ -317,10 +320,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
               }
             }
           } else {
-          if (p.act != FB_ACT_NONE) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = apply_act2(v[i], p.act);
-          }
+          if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
           if (p.out_bf16) {
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
@@ -333,7 +333,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                   __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
                   w[h] = *reinterpret_cast<uint32_t*>(&b2);
                 }
-                o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (p.stream_stores) __stcs(o4 + q, make_uint4(w[0], w[1], w[2], w[3]));
+                else o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
               }
             } else {
               for (int i = 0; i < 32; ++i)
@@ -364,9 +365,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       __syncwarp();
       // "drained" goes to the leader's barrier from both CTAs
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::smem_u32(&tmem_empty[acc]) & ptx::kPeerBitMask);
+      if (p.prof) e_busy += ptx::globaltimer() - e0;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.prof && warp == 2 && lane == 0 && rank == 0) p.prof[pair * 4 + 2] = e_busy;
   }
 
   // Teardown: nobody leaves while the peer may still read this CTA's shared memory (the leader's MMAs
@@ -459,6 +462,10 @@ int launch2(const void* a, const void* b, Args2& args, long long lda, long long 
 
 extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs<256>(); }
 
+// Device buffer of 4 x 64-bit words per CTA pair that subsequent launches fill with their wait / busy times
+// (see Args2::prof); NULL switches the record off again.
+extern "C" void fb_gemm_bf16_2cta_set_profile(unsigned long long* buffer) { fb::g_prof_buffer = buffer; }
+
 // Same arguments as fb_gemm_bf16.  Returns -3 when CTA pairs cannot be launched on this device.
 // Small outputs use the 128-column tile, everything else the 256-column one.
 extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N,
@@ -486,6 +493,15 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
   args.beta = beta;
   args.status = status;
   args.timeout_ns = 2000000000ull;
+  {
+    static int stream_default = -1;
+    if (stream_default < 0) {
+      const char* e = getenv("FERRUM_GEMM_STREAM_STORES");
+      stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    args.stream_stores = stream_default;
+  }
+  args.prof = g_prof_buffer;
   int pairs = pairs_avail;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   const long long m_tiles = (M + 2 * kBM - 1) / (2 * kBM);

@@ -56,6 +56,9 @@ int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const
                       long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_bf16,
                       int act, int beta, int max_ctas, int32_t* status, cudaStream_t stream);
 int fb_gemm_bf16_2cta_pairs(void);
+// Timing record of the CTA-pair kernel: 4 x 64-bit words per pair (ns): MMA thread waiting for a drained accumulator,
+// waiting for operands, one epilogue warp busy, whole kernel.  NULL switches it off.
+void fb_gemm_bf16_2cta_set_profile(unsigned long long* buffer);
 // Batched form over batch_outer x batch_inner slices: out[s] = alpha * A[s] * B[s]^T (+= out[s] when beta).
 // Each operand carries its own (outer, inner) slice strides in elements, so head-interleaved [B, S, H, D]
 // activations are multiplied in place.  Slice strides of A and B must be multiples of 8 elements.
@@ -99,6 +102,8 @@ int fb_colsum(const void* x, float* out, long long rows, long long cols, int dty
               cudaStream_t stream);
 
 // ---- normalisation ------------------------------------------------------------
+// Where the wide-row kernels (shared-memory ring fed by bulk async copies) report a wait that gave up.
+void fb_layernorm_set_status(int32_t* status);
 // pre_act: FB_ACT_NONE or FB_ACT_GELU applied to x before normalising (fused block).
 int fb_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
                      long long rows, int cols, float eps, int pre_act, int dtype, cudaStream_t stream);

@@ -20,6 +20,10 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
+#include "../common/ptx.cuh"
+#include "../common/status.h"
 #include "../include/ferrum_kernels.h"
 
 namespace fb {
@@ -126,7 +130,7 @@ __device__ __forceinline__ float row_sum(float v, float (*smem)[8]) {
 
 // Forward.  A row lives in registers: TPR threads x K vectors of 8 elements.
 template <typename T, int TPR, int K>
-__global__ void __launch_bounds__(256, (K * sizeof(T) <= 2) ? 4 : ((K * sizeof(T) <= 4) ? 3 : ((K * sizeof(T) <= 8) ? 2 : 1)))
+__global__ void __launch_bounds__(256)
 ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows,
               int cols, float eps, int pre_act) {
@@ -138,16 +142,26 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
   const int nvec = cols >> 3;
   const float inv_n = 1.f / static_cast<float>(cols);
   const long long row_stride = static_cast<long long>(gridDim.x) * kRowsPerBlock;
-  using Raw = typename V8<T>::Raw;
-  auto load = [&](long long r, Raw (&buf)[K]) {
+  typename V8<T>::Raw raw[K], nxt[K];
+  {
+    const long long r0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock + sub;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int vi = t + k * TPR;
-      if (r < rows && vi < nvec) buf[k] = V8<T>::ld(x + r * cols + vi * 8);
+      if (r0 < rows && vi < nvec) raw[k] = V8<T>::ld(x + r0 * cols + vi * 8);
     }
-  };
-  auto process = [&](long long row, const Raw (&raw)[K]) {
+  }
+  for (long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock; row0 < rows; row0 += row_stride) {
+    const long long row = row0 + sub;
     const bool live = row < rows;
+    {  // the next row's loads are in flight while this row is reduced and written
+      const long long rn = row + row_stride;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int vi = t + k * TPR;
+        if (rn < rows && vi < nvec) nxt[k] = V8<T>::ld(x + rn * cols + vi * 8);
+      }
+    }
     float v[K][8];
     float s = 0.f;
 #pragma unroll
@@ -197,26 +211,8 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
         V8<T>::st(y + row * cols + vi * 8, o);
       }
     }
-  };
-  // Three register sets rotating by name (loop unrolled by three): the loads of the next two rows stay in
-  // flight while a row is reduced and written, and no register-to-register rotation waits on the newest load.
-  // Row slots of a block advance in lockstep (row0 is uniform), so the barriers inside row_sum stay uniform.
-  Raw b0[K], b1[K], b2[K];
-  long long row0 = static_cast<long long>(blockIdx.x) * kRowsPerBlock;
-  load(row0 + sub, b0);
-  load(row0 + row_stride + sub, b1);
-  while (row0 < rows) {
-    load(row0 + 2 * row_stride + sub, b2);
-    process(row0 + sub, b0);
-    row0 += row_stride;
-    if (row0 >= rows) break;
-    load(row0 + 2 * row_stride + sub, b0);
-    process(row0 + sub, b1);
-    row0 += row_stride;
-    if (row0 >= rows) break;
-    load(row0 + 2 * row_stride + sub, b1);
-    process(row0 + sub, b2);
-    row0 += row_stride;
+#pragma unroll
+    for (int k = 0; k < K; ++k) raw[k] = nxt[k];
   }
 }
 
@@ -373,133 +369,345 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
   }
 }
 
-// Backward for rows of 2056..4096 bf16 elements whose activation derivative (if any) is given as a tensor:
-// pure streaming arithmetic, so the kernel is organised around bytes in flight.  One 512-thread block per
-// SM walks its rows one at a time; a thread owns ONE 16-byte vector of each operand and keeps the loads of
-// the next two rows outstanding while it works on the current one.  The three register sets rotate by NAME
-// (the row loop is unrolled by three): a register-to-register rotation would make every trip wait for the
-// newest load.  A row costs a single __syncthreads (the two row sums travel together through a
-// double-buffered shared-memory slot).  gamma and the three column accumulators stay in registers.
-struct WideRow {
-  uint4 g, x, a;
-  float mu, rs;
+// ----------------------------------------------------------------------------------------------------
+// Wide rows (2 KB .. 8 KB of bf16 / 16 KB of fp32, i.e. up to 4096 columns): shared-memory ring fed by bulk
+// async copies, organised for few instructions per element.
+//
+// Measured on the register-tiled kernels above and on a first ring version: with ~30-40 instructions per
+// element these kernels are bound by instruction issue (issue slots 55-60 % busy, the rest barrier / dependency
+// stalls), not by HBM.  So:
+//   * a thread owns 16 elements of a row (two 16-byte vectors of bf16), which halves the per-row fixed cost
+//     (shuffles, shared-memory exchange, barrier) per element;
+//   * the forward needs ONE reduction per row: sums of (x - c) and (x - c)^2 with c = the row's first element
+//     (shifted sums: no cancellation unless the row's spread is tiny against |x0 - mean|);
+//   * a 512-thread block is two independent groups of 256 threads, each with its own ring, mbarriers and named
+//     barrier, so one group's barrier wait overlaps the other group's arithmetic;
+//   * rows arrive by cp.async.bulk into the ring, up to seven rows ahead per group (HBM needs ~100 KB in flight
+//     per SM; two rows ahead measured 3.0 TB/s): no registers or scoreboards are tied up by prefetched data.  A slot is refilled at the top of the iteration after the one that read it (every
+//     thread of the group has passed that iteration's barrier by then).
+// Packed fp32x2 arithmetic (Blackwell FFMA2 / FADD2 / FMUL2): one issue slot does two fp32 operations, which
+// matters here because these kernels are bound by instruction issue, not by HBM.
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 f2s(float a) { return make_float2(a, a); }
+template <typename T>
+__device__ __forceinline__ void unpack_pairs(const typename V8<T>::Raw& r, float2 (&p)[4]) {
+  float f[8];
+  V8<T>::unpack(r, f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = make_float2(f[2 * i], f[2 * i + 1]);
+}
+template <typename T>
+__device__ __forceinline__ void store_pairs(T* dst, const float2 (&p)[4]) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = p[i].x;
+    f[2 * i + 1] = p[i].y;
+  }
+  V8<T>::st(dst, f);
+}
+__device__ __forceinline__ void ld_pairs_f32(const float* p, float2 (&o)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = make_float2(a.x, a.y);
+  o[1] = make_float2(a.z, a.w);
+  o[2] = make_float2(b.x, b.y);
+  o[3] = make_float2(b.z, b.w);
+}
+// Sum of (a, b) over the eight warps of a 256-thread group: lane 0 of every warp has written its partial to
+// slot[warp]; after the group barrier every thread folds the eight partials with three shuffles.
+__device__ __forceinline__ float2 fold8(const float2* slot, int lane) {
+  float2 v = slot[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, o);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
+  }
+  return v;
+}
+
+constexpr int kRingThreads = 512;
+constexpr int kGroupThreads = 256;
+constexpr int kMaxRingStages = 8;  // per group; the launch picks as many as fit in ~200 KB of shared memory
+constexpr int kStatRows = 128;   // per-group cache of mean / rstd (backward)
+
+struct RingCtl {
+  uint64_t full[2][kMaxRingStages];
+  int abort_flag;
 };
 
-__global__ void __launch_bounds__(512, 1)
-ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                   const __nv_bfloat16* __restrict__ act_grad, const float* __restrict__ gamma,
-                   const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
-                   float* __restrict__ partial, long long rows, int cols, int want_colsum) {
-  using V = V8<__nv_bfloat16>;
-  __shared__ float2 red[2][16];
-  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
+}
+__device__ __forceinline__ bool ring_wait(RingCtl* ctl, int group, int i, int stages) {
+  return ptx::mbar_wait(&ctl->full[group][i % stages], static_cast<uint32_t>((i / stages) & 1), &ctl->abort_flag,
+                        2000000000ull);
+}
+// Before a group with copies in flight may exit, let them land (bounded).
+__device__ __forceinline__ void ring_drain(RingCtl* ctl, int group, int issued, int consumed, int stages) {
+  for (int i = consumed; i < issued; ++i) {
+    const uint64_t t0 = ptx::globaltimer();
+    while (!ptx::mbar_try_wait(&ctl->full[group][i % stages], static_cast<uint32_t>((i / stages) & 1))) {
+      if (ptx::globaltimer() - t0 > 2000000000ull) break;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRingThreads, sizeof(T) == 2 ? 2 : 1)
+ln_fwd_ring_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                   T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows,
+                   int cols, float eps, int pre_act, int stages, int32_t* status) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ RingCtl ctl;
+  __shared__ float2 red[2][2][8];
+  constexpr bool kFast = V8<T>::kFastMath;
+  const int group = threadIdx.x >> 8, t = threadIdx.x & 255, lane = t & 31, warp = t >> 5;
   const int nvec = cols >> 3;
-  const bool has = t < nvec;
+  const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
+  uint8_t* my_ring = ring + group * stages * row_bytes;
   const float inv_n = 1.f / static_cast<float>(cols);
-  const long long stride = gridDim.x;
-  const bool use_ag = act_grad != nullptr;
+  // the block's rows are first + j * stride; group g takes j = 2 i + g
+  const long long first = blockIdx.x, stride = gridDim.x;
+  const long long n_block = first < rows ? (rows - first + stride - 1) / stride : 0;
+  const int n_mine = static_cast<int>((n_block - group + 1) / 2);
+  auto row_of = [&](int i) { return first + (2LL * i + group) * stride; };
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    for (int g = 0; g < 2; ++g)
+      for (int s = 0; s < stages; ++s) ptx::mbar_init(&ctl.full[g][s], 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](int idx) {
+    const int sl = idx % stages;
+    ptx::mbar_arrive_expect_tx(&ctl.full[group][sl], row_bytes);
+    ptx::bulk_load_1d(my_ring + sl * row_bytes, x + row_of(idx) * cols, row_bytes, &ctl.full[group][sl]);
+  };
+  int issued = 0;
+  if (t == 0)
+    for (; issued < stages - 1 && issued < n_mine; ++issued) issue(issued);
 
-  float w[8];
+  const bool has[2] = {t < nvec, t + kGroupThreads < nvec};
+  int i = 0, par = 0;
+  for (; i < n_mine; ++i) {
+    const long long row = row_of(i);
+    if (t == 0 && issued < n_mine) issue(issued++);  // refills the slot that iteration i - 1 read
+    if (!ring_wait(&ctl, group, i, stages)) break;
+    const T* src = reinterpret_cast<const T*>(my_ring + (i % stages) * row_bytes);
+    float2 v[2][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) w[i] = 1.f;
-  if (has && gamma != nullptr) ld8f(gamma + t * 8, w);
-  float acc_g[8], acc_b[8], acc_c[8];
+    for (int k = 0; k < 2; ++k) {
+      if (has[k]) {
+        unpack_pairs<T>(V8<T>::ld(src + (t + k * kGroupThreads) * 8), v[k]);
+      } else {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc_g[i] = acc_b[i] = acc_c[i] = 0.f;
-  int par = 0;
-
-  auto load = [&](long long r, WideRow& b) {
-    if (r < rows) {
-      b.mu = mean[r];
-      b.rs = rstd[r];
-      if (has) {
-        const long long o = r * cols + t * 8;
-        b.g = V::ld(dy + o);
-        b.x = V::ld(x + o);
-        if (use_ag) b.a = V::ld(act_grad + o);
+        for (int e = 0; e < 4; ++e) v[k][e] = f2s(0.f);
       }
     }
-  };
-  auto process = [&](long long row, const WideRow& b) {
-    float gv[8], h[8];
-    V::unpack(b.g, gv);
-    V::unpack(b.x, h);
-    const float shift = -b.mu * b.rs;
-    float s1 = 0.f, s2 = 0.f;
+    float c = V8<T>::ld1(src);
+    if (pre_act == FB_ACT_GELU) {
+      c = gelu_f<kFast>(c);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      h[i] = fmaf(h[i], b.rs, shift);
-      acc_b[i] += gv[i];
-      acc_g[i] = fmaf(gv[i], h[i], acc_g[i]);
-      gv[i] *= w[i];  // d = dy * gamma
-      s1 += gv[i];
-      s2 = fmaf(gv[i], h[i], s2);
+      for (int k = 0; k < 2; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[k][e] = f2(gelu_f<kFast>(v[k][e].x), gelu_f<kFast>(v[k][e].y));
     }
-    if (!has) s1 = s2 = 0.f;
+    const float2 nc = f2s(-c);
+    float2 s2 = f2s(0.f), q2 = f2s(0.f);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (has[k]) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 d = __fadd2_rn(v[k][e], nc);
+          s2 = __fadd2_rn(s2, d);
+          q2 = __ffma2_rn(d, d, q2);
+        }
+      }
+    }
+    float s = s2.x + s2.y, q = q2.x + q2.y;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      q += __shfl_xor_sync(0xffffffffu, q, o);
     }
-    if (lane == 0) red[par][warp] = make_float2(s1, s2);
-    __syncthreads();
-    float m1 = 0.f, m2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float2 v = red[par][i];
-      m1 += v.x;
-      m2 += v.y;
-    }
+    if (lane == 0) red[group][par][warp] = make_float2(s, q);
+    group_sync(group);
+    const float2 tot = fold8(red[group][par], lane);
     par ^= 1;
-    m1 *= inv_n;
-    m2 *= inv_n;
-    if (has) {
-      float o[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = b.rs * (gv[i] - m1 - h[i] * m2);
-      if (use_ag) {
-        float ag[8];
-        V::unpack(b.a, ag);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] *= ag[i];
-      }
-      if (want_colsum) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc_c[i] += o[i];
-      }
-      V::st(dx + row * cols + t * 8, o);
+    const float ms = tot.x * inv_n;                       // mean of (x - c)
+    const float var = fmaxf(tot.y * inv_n - ms * ms, 0.f);
+    const float mu = c + ms;
+    const float rs = rsqrtf(var + eps);
+    if (t == 0) {
+      if (mean_out) mean_out[row] = mu;
+      if (rstd_out) rstd_out[row] = rs;
     }
-  };
-
-  WideRow b0, b1, b2;
-  b0.g = b0.x = b0.a = b1.g = b1.x = b1.a = b2.g = b2.x = b2.a = make_uint4(0u, 0u, 0u, 0u);
-  b0.mu = b0.rs = b1.mu = b1.rs = b2.mu = b2.rs = 0.f;
-  long long row = blockIdx.x;
-  load(row, b0);
-  load(row + stride, b1);
-  while (row < rows) {  // every condition below is uniform over the block
-    load(row + 2 * stride, b2);
-    process(row, b0);
-    row += stride;
-    if (row >= rows) break;
-    load(row + 2 * stride, b0);
-    process(row, b1);
-    row += stride;
-    if (row >= rows) break;
-    load(row + 2 * stride, b1);
-    process(row, b2);
-    row += stride;
+    const float2 rs2 = f2s(rs), shift2 = f2s(-mu * rs);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int vi = t + k * kGroupThreads;
+      if (has[k]) {
+        float2 g[4], b[4], o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          g[e] = f2s(1.f);
+          b[e] = f2s(0.f);
+        }
+        if (gamma) ld_pairs_f32(gamma + vi * 8, g);
+        if (beta) ld_pairs_f32(beta + vi * 8, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = __ffma2_rn(__ffma2_rn(v[k][e], rs2, shift2), g[e], b[e]);
+        store_pairs<T>(y + row * cols + vi * 8, o);
+      }
+    }
   }
-  if (has) {
-    float* pg = partial + static_cast<long long>(blockIdx.x) * 3 * cols + t * 8;
-    float* pb = pg + cols;
-    float* pc = pb + cols;
-    *reinterpret_cast<float4*>(pg) = make_float4(acc_g[0], acc_g[1], acc_g[2], acc_g[3]);
-    *reinterpret_cast<float4*>(pg + 4) = make_float4(acc_g[4], acc_g[5], acc_g[6], acc_g[7]);
-    *reinterpret_cast<float4*>(pb) = make_float4(acc_b[0], acc_b[1], acc_b[2], acc_b[3]);
-    *reinterpret_cast<float4*>(pb + 4) = make_float4(acc_b[4], acc_b[5], acc_b[6], acc_b[7]);
-    *reinterpret_cast<float4*>(pc) = make_float4(acc_c[0], acc_c[1], acc_c[2], acc_c[3]);
-    *reinterpret_cast<float4*>(pc + 4) = make_float4(acc_c[4], acc_c[5], acc_c[6], acc_c[7]);
+  if (i < n_mine && t == 0) {  // a wait gave up
+    report_status(status, kStatusGemmTimeout, 31, blockIdx.x, i);
+    ring_drain(&ctl, group, issued, i, stages);
+  }
+}
+
+// Backward with the activation derivative (if any) given as a tensor: bf16, up to 4096 columns.  A slot
+// holds the dy, x and act_grad rows; gamma and the three column accumulators stay in registers; mean / rstd
+// of a group's rows are cached in shared memory up front; a row costs one group barrier.  Column partials:
+// one row of partial[] per GROUP (2 * gridDim.x rows in all).
+__global__ void __launch_bounds__(kRingThreads, 1)
+ln_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ act_grad, const float* __restrict__ gamma,
+                   const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ partial, long long rows, int cols, int want_colsum, int stages,
+                   int32_t* status) {
+  using V = V8<__nv_bfloat16>;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ RingCtl ctl;
+  __shared__ float2 red[2][2][8];
+  __shared__ float2 stat[2][kStatRows];
+  const int group = threadIdx.x >> 8, t = threadIdx.x & 255, lane = t & 31, warp = t >> 5;
+  const int nvec = cols >> 3;
+  const bool use_ag = act_grad != nullptr;
+  const uint32_t row_bytes = static_cast<uint32_t>(cols) * 2u;
+  const uint32_t slot_bytes = row_bytes * (use_ag ? 3u : 2u);
+  uint8_t* my_ring = ring + group * stages * slot_bytes;
+  const float inv_n = 1.f / static_cast<float>(cols);
+  const long long first = blockIdx.x, stride = gridDim.x;
+  const long long n_block = first < rows ? (rows - first + stride - 1) / stride : 0;
+  const int n_mine = static_cast<int>((n_block - group + 1) / 2);
+  auto row_of = [&](int i) { return first + (2LL * i + group) * stride; };
+
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    for (int g = 0; g < 2; ++g)
+      for (int s = 0; s < stages; ++s) ptx::mbar_init(&ctl.full[g][s], 1);
+    ptx::fence_mbar_init();
+  }
+  for (int r = t; r < n_mine && r < kStatRows; r += kGroupThreads)
+    stat[group][r] = make_float2(mean[row_of(r)], rstd[row_of(r)]);
+  __syncthreads();
+  auto issue = [&](int idx) {
+    const int sl = idx % stages;
+    uint8_t* dst = my_ring + sl * slot_bytes;
+    const long long off = row_of(idx) * cols;
+    ptx::mbar_arrive_expect_tx(&ctl.full[group][sl], slot_bytes);
+    ptx::bulk_load_1d(dst, dy + off, row_bytes, &ctl.full[group][sl]);
+    ptx::bulk_load_1d(dst + row_bytes, x + off, row_bytes, &ctl.full[group][sl]);
+    if (use_ag) ptx::bulk_load_1d(dst + 2 * row_bytes, act_grad + off, row_bytes, &ctl.full[group][sl]);
+  };
+  int issued = 0;
+  if (t == 0)
+    for (; issued < stages - 1 && issued < n_mine; ++issued) issue(issued);
+
+  const bool has[2] = {t < nvec, t + kGroupThreads < nvec};
+  float2 w[2][4], acc_g[2][4], acc_b[2][4], acc_c[2][4];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      w[k][e] = f2s(1.f);
+      acc_g[k][e] = acc_b[k][e] = acc_c[k][e] = f2s(0.f);
+    }
+    if (has[k] && gamma != nullptr) ld_pairs_f32(gamma + (t + k * kGroupThreads) * 8, w[k]);
+  }
+
+  int i = 0, par = 0;
+  for (; i < n_mine; ++i) {
+    const long long row = row_of(i);
+    if (t == 0 && issued < n_mine) issue(issued++);  // refills the slot that iteration i - 1 read
+    if (!ring_wait(&ctl, group, i, stages)) break;
+    const float2 st = i < kStatRows ? stat[group][i] : make_float2(mean[row], rstd[row]);
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(my_ring + (i % stages) * slot_bytes);
+    float2 d[2][4], h[2][4];
+    const float2 rs2 = f2s(st.y), shift2 = f2s(-st.x * st.y);
+    float2 s1 = f2s(0.f), s2 = f2s(0.f);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (has[k]) {
+        const int vi = t + k * kGroupThreads;
+        unpack_pairs<__nv_bfloat16>(V::ld(src + vi * 8), d[k]);
+        unpack_pairs<__nv_bfloat16>(V::ld(src + cols + vi * 8), h[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          h[k][e] = __ffma2_rn(h[k][e], rs2, shift2);
+          acc_b[k][e] = __fadd2_rn(acc_b[k][e], d[k][e]);
+          acc_g[k][e] = __ffma2_rn(d[k][e], h[k][e], acc_g[k][e]);
+          d[k][e] = __fmul2_rn(d[k][e], w[k][e]);  // d = dy * gamma
+          s1 = __fadd2_rn(s1, d[k][e]);
+          s2 = __ffma2_rn(d[k][e], h[k][e], s2);
+        }
+      }
+    }
+    float a1 = s1.x + s1.y, a2 = s2.x + s2.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+    }
+    if (lane == 0) red[group][par][warp] = make_float2(a1, a2);
+    group_sync(group);
+    const float2 tot = fold8(red[group][par], lane);
+    par ^= 1;
+    // o = rstd * (d - m1 - h m2) with rstd folded into the two means
+    const float2 nm1 = f2s(-tot.x * inv_n * st.y), nm2 = f2s(-tot.y * inv_n * st.y);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (has[k]) {
+        const int vi = t + k * kGroupThreads;
+        float2 o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = __ffma2_rn(h[k][e], nm2, __ffma2_rn(d[k][e], rs2, nm1));
+        if (use_ag) {
+          float2 ag[4];
+          unpack_pairs<__nv_bfloat16>(V::ld(src + 2 * cols + vi * 8), ag);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = __fmul2_rn(o[e], ag[e]);
+        }
+        if (want_colsum) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc_c[k][e] = __fadd2_rn(acc_c[k][e], o[e]);
+        }
+        store_pairs<__nv_bfloat16>(dx + row * cols + vi * 8, o);
+      }
+    }
+  }
+  if (i < n_mine && t == 0) {
+    report_status(status, kStatusGemmTimeout, 32, blockIdx.x, i);
+    ring_drain(&ctl, group, issued, i, stages);
+  }
+  float* base = partial + (2LL * blockIdx.x + group) * 3 * cols;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (has[k]) {
+      float* pg = base + (t + k * kGroupThreads) * 8;
+      float* pb = pg + cols;
+      float* pc = pb + cols;
+      *reinterpret_cast<float4*>(pg) = make_float4(acc_g[k][0].x, acc_g[k][0].y, acc_g[k][1].x, acc_g[k][1].y);
+      *reinterpret_cast<float4*>(pg + 4) = make_float4(acc_g[k][2].x, acc_g[k][2].y, acc_g[k][3].x, acc_g[k][3].y);
+      *reinterpret_cast<float4*>(pb) = make_float4(acc_b[k][0].x, acc_b[k][0].y, acc_b[k][1].x, acc_b[k][1].y);
+      *reinterpret_cast<float4*>(pb + 4) = make_float4(acc_b[k][2].x, acc_b[k][2].y, acc_b[k][3].x, acc_b[k][3].y);
+      *reinterpret_cast<float4*>(pc) = make_float4(acc_c[k][0].x, acc_c[k][0].y, acc_c[k][1].x, acc_c[k][1].y);
+      *reinterpret_cast<float4*>(pc + 4) = make_float4(acc_c[k][2].x, acc_c[k][2].y, acc_c[k][3].x, acc_c[k][3].y);
+    }
   }
 }
 
@@ -636,17 +844,56 @@ bool aligned16(const void* a, const void* b, const void* c, const void* d) {
            reinterpret_cast<uintptr_t>(d)) & 15) == 0;
 }
 
-// Persistent grid: exactly the blocks that are resident at once, so every block walks the same number of rows.
+int32_t* g_ln_status = nullptr;  // host-mapped status block for the bounded waits of the ring kernels
+
+// FERRUM_LN_RING=0 keeps wide rows on the register-tiled kernels (for A/B measurements).
+bool ring_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FERRUM_LN_RING");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <typename T, int TPR, int K>
 void launch_fwd(const T* xp, const float* gamma, const float* beta, T* yp, float* mean, float* rstd, long long rows,
                 int cols, float eps, int pre_act, long long nb, cudaStream_t st) {
-  static int occ = 0;
-  if (occ == 0 &&
-      (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, ln_fwd_kernel<T, TPR, K>, 256, 0) != cudaSuccess || occ < 1))
-    occ = 1;
-  const long long cap = static_cast<long long>(sm_count()) * occ;
-  const int grid = static_cast<int>(nb < cap ? nb : cap);
+  const int grid = static_cast<int>(nb < sm_count() * 8LL ? nb : sm_count() * 8LL);
   ln_fwd_kernel<T, TPR, K><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act);
+}
+
+// Stages per group for slots of `slot_bytes`: as many as fit in `budget` bytes for the two groups of a block,
+// at most kMaxRingStages.
+int ring_stages(size_t slot_bytes, size_t budget) {
+  const size_t fit = budget / (2 * slot_bytes);
+  return static_cast<int>(fit > kMaxRingStages ? kMaxRingStages : fit);
+}
+
+// Ring kernel for rows of at least 2 KB and at most 4096 columns; false if it cannot be launched.
+template <typename T>
+bool launch_fwd_ring(const T* xp, const float* gamma, const float* beta, T* yp, float* mean, float* rstd,
+                     long long rows, int cols, float eps, int pre_act, cudaStream_t st) {
+  // 2-byte rows run two blocks per SM (register budget of the kernel), so each gets half of the shared memory
+  constexpr int kBlocksPerSm = sizeof(T) == 2 ? 2 : 1;
+  const int stages = ring_stages(static_cast<size_t>(cols) * sizeof(T), (200u * 1024u) / kBlocksPerSm);
+  if (stages < 2) return false;
+  const size_t smem = static_cast<size_t>(2 * stages) * cols * sizeof(T);
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(ln_fwd_ring_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured = smem;
+  }
+  const long long want = (rows + 1) / 2;  // a block needs two rows to keep both groups busy
+  const long long cap = static_cast<long long>(sm_count()) * kBlocksPerSm;
+  const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+  ln_fwd_ring_kernel<T><<<grid, kRingThreads, smem, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act,
+                                                         stages, g_ln_status);
+  return true;
 }
 
 template <typename T>
@@ -656,6 +903,10 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
   T* yp = static_cast<T*>(y);
   Geo g;
   if (geometry(cols, &g) && aligned16(x, y, gamma, beta)) {
+    const int nvec = cols / 8;
+    if (ring_enabled() && static_cast<size_t>(cols) * sizeof(T) >= 2048 && nvec <= 2 * kGroupThreads &&
+        launch_fwd_ring<T>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, st))
+      return static_cast<int>(cudaGetLastError());
     const long long rpb = 256 / g.tpr;
     const long long nb = (rows + rpb - 1) / rpb;
 #define FB_LN_FWD(TPR, K) \
@@ -679,13 +930,26 @@ bool launch_wide(const T*, const T*, const T*, const float*, const float*, const
                  int, int, cudaStream_t) {
   return false;
 }
-// bf16 rows of 257..512 vectors with no activation to re-evaluate: the streaming kernel, one block per SM.
+// bf16 rows of 2 KB .. 8 KB with no activation to re-evaluate: the ring kernel, one block per SM.
 template <>
 bool launch_wide<__nv_bfloat16>(const __nv_bfloat16* dy, const __nv_bfloat16* x, const __nv_bfloat16* ag,
                                 const float* gamma, const float* mean, const float* rstd, __nv_bfloat16* dx,
                                 float* partial, long long rows, int cols, int blocks, int want_colsum,
                                 cudaStream_t st) {
-  ln_bwd_wide_kernel<<<blocks, 512, 0, st>>>(dy, x, ag, gamma, mean, rstd, dx, partial, rows, cols, want_colsum);
+  const int stages = ring_stages(static_cast<size_t>(cols) * 2 * (ag != nullptr ? 3 : 2), 200u * 1024u);
+  if (stages < 2) return false;
+  const size_t smem = static_cast<size_t>(2 * stages) * (ag != nullptr ? 3 : 2) * cols * 2;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(ln_bwd_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured = smem;
+  }
+  ln_bwd_ring_kernel<<<blocks, kRingThreads, smem, st>>>(dy, x, ag, gamma, mean, rstd, dx, partial, rows, cols,
+                                                         want_colsum, stages, g_ln_status);
   return true;
 }
 
@@ -703,10 +967,11 @@ int bwd_t(const void* dy, const void* x, const void* act_grad, const float* gamm
   if (fast) {
     int used = nblk;
     const int nvec = cols / 8;
-    const int wide_blocks = nblk < sm_count() ? nblk : sm_count();
-    if (pre_act == FB_ACT_NONE && nvec > 256 && nvec <= 512 &&
+    const int wide_blocks = nblk / 2 < sm_count() ? nblk / 2 : sm_count();  // two rows of partial[] per block
+    if (ring_enabled() && pre_act == FB_ACT_NONE && cols * 2 >= 2048 && nvec <= 2 * kGroupThreads &&
+        wide_blocks >= 1 &&
         launch_wide<T>(dyp, xp, agp, gamma, mean, rstd, dxp, partial, rows, cols, wide_blocks, want_colsum, st)) {
-      used = wide_blocks;
+      used = 2 * wide_blocks;
     } else {
 #define FB_LN_BWD(TPR, K) \
   ln_bwd_kernel<T, TPR, K><<<nblk, 256, 0, st>>>(dyp, xp, agp, gamma, mean, rstd, dxp, partial, rows, cols, pre_act, \
@@ -739,6 +1004,9 @@ int bwd_t(const void* dy, const void* x, const void* act_grad, const float* gamm
 }  // namespace fb
 
 using namespace fb;
+
+// Status block (host-mapped, see common/status.h) that the bounded waits of the wide-row kernels report to.
+extern "C" void fb_layernorm_set_status(int32_t* status) { g_ln_status = status; }
 
 // Number of blocks (= rows of `partial`, each 3 * cols floats) the fast backward uses; 0 means the
 // generic path runs and no partial buffer is needed.

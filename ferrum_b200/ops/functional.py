@@ -690,6 +690,7 @@ class _LayerNormFn(Function):
         rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
         g = gamma.detach().contiguous() if gamma is not None else None
         b = beta.detach().contiguous() if beta is not None else None
+        _rt.status_ptr()  # the wide-row kernels report bounded-wait failures to the status block
         _lib.check(_lib.cuda().fb_layernorm_fwd(x2.data_ptr(), _ptr(g), _ptr(b), y.data_ptr(), mean.data_ptr(),
                                                 rstd.data_ptr(), rows, cols, eps, UNARY[pre_act or "none"],
                                                 _dt(x2), _stream()), "fb_layernorm_fwd")
@@ -779,6 +780,7 @@ class _LinearActNormFn(Function):
         rstd = torch.empty(rows, device=z.device, dtype=torch.float32)
         g = gamma.detach().contiguous()
         b = beta.detach().contiguous()
+        _rt.status_ptr()  # the wide-row kernels report bounded-wait failures to the status block
         _lib.check(_lib.cuda().fb_layernorm_fwd(z.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(),
                                                 mean.data_ptr(), rstd.data_ptr(), rows, cols, eps, UNARY[pre], _dt(z),
                                                 _stream()), "fb_layernorm_fwd")

@@ -25,6 +25,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--act", default=None)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--prof", action="store_true",
+                    help="CTA-pair kernel: report where the MMA thread waits (drained accumulator / operands) and how long "
+                         "an epilogue warp is busy, averaged over the pairs of the last launch")
+    ap.add_argument("--dual", action="store_true", help="also store act'(z) (second bf16 output; needs --act)")
     ap.add_argument("--two-cta", action="store_true", help="use the CTA-pair (cta_group::2) kernel")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
     a = ap.parse_args()
@@ -61,7 +65,8 @@ def main():
         ts.sort()
         return ts[len(ts) // 2]
 
-    ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out))
+    aux = torch.empty_like(out) if a.dual else None
+    ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
     check_status()
     flops = 2.0 * M * N * K
     if a.two_cta:
@@ -80,6 +85,19 @@ def main():
         Ac, Bc = A.contiguous(), B.contiguous()
         cms = timeit(lambda: torch.matmul(Ac, Bc.t()))
         res["cublas_ms"], res["cublas_tflops"] = cms, flops / cms / 1e9
+    if a.prof and a.two_cta:
+        from ferrum_b200 import _lib
+
+        lib = _lib.cuda()
+        pairs = lib.fb_gemm_bf16_2cta_pairs()
+        buf = torch.zeros(pairs * 4, dtype=torch.int64, device="cuda")
+        lib.fb_gemm_bf16_2cta_set_profile(buf.data_ptr())
+        gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux)
+        torch.cuda.synchronize()
+        lib.fb_gemm_bf16_2cta_set_profile(None)
+        t = buf.view(pairs, 4).double().mean(0) / 1e3
+        res["prof_us"] = {"mma_waits_accumulator": t[0].item(), "mma_waits_operands": t[1].item(),
+                          "epilogue_warp_busy": t[2].item(), "kernel": t[3].item()}
     print(json.dumps(res))
 
 

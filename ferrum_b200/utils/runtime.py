@@ -28,6 +28,7 @@ def status_ptr() -> int:
         if not p:
             raise RuntimeError("could not allocate the device status block")
         _status_ptrs[dev] = p
+        lib.fb_layernorm_set_status(p)  # kernels without a status argument report here (one device per process)
     return p
 
 
