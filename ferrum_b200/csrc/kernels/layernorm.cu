@@ -382,8 +382,12 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
 //     (shifted sums: no cancellation unless the row's spread is tiny against |x0 - mean|);
 //   * a 512-thread block is two independent groups of 256 threads, each with its own ring, mbarriers and named
 //     barrier, so one group's barrier wait overlaps the other group's arithmetic;
-//   * rows arrive by cp.async.bulk into the ring, up to seven rows ahead per group (HBM needs ~100 KB in flight
-//     per SM; two rows ahead measured 3.0 TB/s): no registers or scoreboards are tied up by prefetched data.  A slot is refilled at the top of the iteration after the one that read it (every
+//   * rows arrive by cp.async.bulk into the ring, up to three rows ahead per group: no registers or scoreboards
+//     are tied up by prefetched data;
+//   * the arithmetic is packed fp32x2 (FFMA2 / FADD2 / FMUL2).
+// Measured at 8192 x 4096 bf16: backward 64-66 us against 128 us for the register-tiled kernel; the forward
+// (42-45 us) does not beat the register-tiled forward (39-40 us), so the forward ring is opt-in
+// (FERRUM_LN_RING_FWD=1) and the default forward stays on the register-tiled kernel.  A slot is refilled at the top of the iteration after the one that read it (every
 //     thread of the group has passed that iteration's barrier by then).
 // Packed fp32x2 arithmetic (Blackwell FFMA2 / FADD2 / FMUL2): one issue slot does two fp32 operations, which
 // matters here because these kernels are bound by instruction issue, not by HBM.
@@ -428,7 +432,7 @@ __device__ __forceinline__ float2 fold8(const float2* slot, int lane) {
 
 constexpr int kRingThreads = 512;
 constexpr int kGroupThreads = 256;
-constexpr int kMaxRingStages = 8;  // per group; the launch picks as many as fit in ~200 KB of shared memory
+constexpr int kMaxRingStages = 4;  // per group (measured: 2 .. 6 stages perform alike; the kernels are issue-bound)
 constexpr int kStatRows = 128;   // per-group cache of mean / rstd (backward)
 
 struct RingCtl {
@@ -863,10 +867,17 @@ void launch_fwd(const T* xp, const float* gamma, const float* beta, T* yp, float
   ln_fwd_kernel<T, TPR, K><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act);
 }
 
+int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e != nullptr ? atoi(e) : dflt;
+}
+
 // Stages per group for slots of `slot_bytes`: as many as fit in `budget` bytes for the two groups of a block,
 // at most kMaxRingStages.
 int ring_stages(size_t slot_bytes, size_t budget) {
-  const size_t fit = budget / (2 * slot_bytes);
+  size_t fit = budget / (2 * slot_bytes);
+  static const int forced = env_int("FERRUM_LN_STAGES", 0);  // measurement knob
+  if (forced >= 2 && static_cast<size_t>(forced) < fit) fit = forced;
   return static_cast<int>(fit > kMaxRingStages ? kMaxRingStages : fit);
 }
 
@@ -904,7 +915,8 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
   Geo g;
   if (geometry(cols, &g) && aligned16(x, y, gamma, beta)) {
     const int nvec = cols / 8;
-    if (ring_enabled() && static_cast<size_t>(cols) * sizeof(T) >= 2048 && nvec <= 2 * kGroupThreads &&
+    static const int ring_fwd = env_int("FERRUM_LN_RING_FWD", 0);
+    if (ring_fwd && ring_enabled() && static_cast<size_t>(cols) * sizeof(T) >= 2048 && nvec <= 2 * kGroupThreads &&
         launch_fwd_ring<T>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, st))
       return static_cast<int>(cudaGetLastError());
     const long long rpb = 256 / g.tpr;

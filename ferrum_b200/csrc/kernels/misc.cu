@@ -8,7 +8,7 @@
 //                                      zero, out-of-range index is an error, no backward)
 //   ferrum-nn/src/norm.rs:75-165,242-283 BatchNorm1d (reference uses one global mean /
 //                                      variance and never updates running stats; this is
-//                                      per feature with running-stat update)
+//                                      per feature with running-stat update, full-grid passes)
 //   ferrum-data/src/dataloader.rs:144-165 per-index dataset.get (here: one row-gather launch)
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -202,85 +202,224 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, const long l
 }
 
 // --------------------------------------------------------------- BatchNorm
-// Block = 32 columns x 8 row groups.  Column statistics by two passes.
-__device__ __forceinline__ float col_sum_8(float v, float (*sm)[33]) {
-  __syncthreads();
-  sm[threadIdx.y][threadIdx.x] = v;
-  __syncthreads();
-  float s = 0.f;
+// BatchNorm1d over [rows, cols] fp32.  Column statistics come from full-grid passes (a block = 128 columns x a
+// chunk of rows, lanes own 4 adjacent columns with 16-byte loads, warps walk the rows four at a time, partials
+// meet in shared memory and leave with one atomicAdd per column per block), so a 1024-feature layer uses the
+// whole GPU instead of 32 blocks.  Training forward = mean pass, centred second-moment pass (two-pass variance:
+// no cancellation), finalize, apply; backward = one two-statistic pass (d_beta, d_gamma) and one elementwise pass.
+//   MODE 0: a += x                          b unused
+//   MODE 1: a += (x - mean)^2               b unused
+//   MODE 2: a += dy, b += dy * (x - mean) * rstd
+template <int MODE>
+__global__ void __launch_bounds__(256)
+bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mean,
+                   const float* __restrict__ rstd, float* __restrict__ out_a, float* __restrict__ out_b,
+                   long long rows, int cols, long long rows_per_block) {
+  __shared__ float sm_a[8][128];
+  __shared__ float sm_b[MODE == 2 ? 8 : 1][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.x * 128 + lane * 4;
+  const long long r_lo = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r_hi = min(rows, r_lo + rows_per_block);
+  const bool vec = (cols % 4 == 0) && (c0 + 3 < cols);
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+  float mu[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
+  if (MODE != 0) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) s += sm[j][threadIdx.x];
-  return s;
-}
-
-__global__ void batchnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                     const float* __restrict__ beta, float* __restrict__ y,
-                                     float* __restrict__ save_mean, float* __restrict__ save_rstd,
-                                     float* __restrict__ running_mean, float* __restrict__ running_var,
-                                     long long rows, int cols, float eps, float momentum, int training) {
-  __shared__ float sm[8][33];
-  const int c = blockIdx.x * 32 + threadIdx.x;
-  const bool live = c < cols;
-  float mu, rs;
-  if (training) {
-    float s = 0.f;
-    if (live)
-      for (long long r = threadIdx.y; r < rows; r += 8) s += x[r * cols + c];
-    mu = col_sum_8(s, sm) / static_cast<float>(rows);
-    float q = 0.f;
-    if (live)
-      for (long long r = threadIdx.y; r < rows; r += 8) {
-        const float d = x[r * cols + c] - mu;
-        q += d * d;
+    for (int j = 0; j < 4; ++j)
+      if (c0 + j < cols) {
+        mu[j] = mean[c0 + j];
+        if (MODE == 2) rs[j] = rstd[c0 + j];
       }
-    const float var = col_sum_8(q, sm) / static_cast<float>(rows);
-    rs = rsqrtf(var + eps);
-    if (live && threadIdx.y == 0) {
-      if (save_mean) save_mean[c] = mu;
-      if (save_rstd) save_rstd[c] = rs;
-      if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
-      if (running_var) {
-        const float unbiased = rows > 1 ? var * static_cast<float>(rows) / static_cast<float>(rows - 1) : var;
-        running_var[c] = (1.f - momentum) * running_var[c] + momentum * unbiased;
+  }
+  auto accum = [&](const float (&xv)[4], const float (&gv)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (MODE == 0) a[j] += xv[j];
+      if (MODE == 1) {
+        const float d = xv[j] - mu[j];
+        a[j] = fmaf(d, d, a[j]);
+      }
+      if (MODE == 2) {
+        a[j] += gv[j];
+        b[j] = fmaf(gv[j], (xv[j] - mu[j]) * rs[j], b[j]);
+      }
+    }
+  };
+  if (vec) {
+    for (long long r = r_lo + warp; r < r_hi; r += 32) {
+      float4 xv[4], gv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {  // four independent rows in flight per thread
+        const long long rr = r + 8 * u;
+        const bool ok = rr < r_hi;
+        xv[u] = ok ? *reinterpret_cast<const float4*>(x + rr * cols + c0) : make_float4(mu[0], mu[1], mu[2], mu[3]);
+        if (MODE == 2) gv[u] = ok ? *reinterpret_cast<const float4*>(dy + rr * cols + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (MODE == 0 && r + 8 * u >= r_hi) continue;  // padded rows equal the mean: no effect in modes 1, 2
+        const float xa[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+        const float ga[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+        accum(xa, ga);
       }
     }
   } else {
-    mu = live ? running_mean[c] : 0.f;
-    rs = live ? rsqrtf(running_var[c] + eps) : 0.f;
+    for (long long r = r_lo + warp; r < r_hi; r += 8) {
+      float xa[4] = {mu[0], mu[1], mu[2], mu[3]}, ga[4] = {0.f, 0.f, 0.f, 0.f};
+      bool any = false;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c0 + j < cols) {
+          xa[j] = x[r * cols + c0 + j];
+          if (MODE == 2) ga[j] = dy[r * cols + c0 + j];
+          any = true;
+        }
+      if (MODE == 0 && !any) continue;
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c0 + j >= cols) xa[j] = 0.f;
+      }
+      accum(xa, ga);
+    }
   }
-  if (live) {
-    const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
-    for (long long r = threadIdx.y; r < rows; r += 8) y[r * cols + c] = (x[r * cols + c] - mu) * rs * g + b;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sm_a[warp][lane * 4 + j] = a[j];
+    if (MODE == 2) sm_b[warp][lane * 4 + j] = b[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      ta += sm_a[w][threadIdx.x];
+      if (MODE == 2) tb += sm_b[w][threadIdx.x];
+    }
+    if (c < cols) {
+      atomicAdd(out_a + c, ta);
+      if (MODE == 2) atomicAdd(out_b + c, tb);
+    }
   }
 }
 
-__global__ void batchnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x,
-                                     const float* __restrict__ gamma, const float* __restrict__ save_mean,
-                                     const float* __restrict__ save_rstd, float* __restrict__ dx,
-                                     float* __restrict__ dgamma, float* __restrict__ dbeta, long long rows,
-                                     int cols) {
-  __shared__ float sm[8][33];
-  const int c = blockIdx.x * 32 + threadIdx.x;
-  const bool live = c < cols;
-  const float mu = live ? save_mean[c] : 0.f, rs = live ? save_rstd[c] : 0.f;
-  float sg = 0.f, sb = 0.f;
-  if (live)
-    for (long long r = threadIdx.y; r < rows; r += 8) {
-      const float g = dy[r * cols + c];
-      sg += g * (x[r * cols + c] - mu) * rs;
-      sb += g;
+// stage 0: mean <- sum / rows.   stage 1: rstd <- rsqrt(m2 / rows + eps), running statistics.
+__global__ void bn_finalize_kernel(float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ running_mean,
+                                   float* __restrict__ running_var, long long rows, int cols, float eps,
+                                   float momentum, int stage) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  if (stage == 0) {
+    mean[c] = mean[c] / static_cast<float>(rows);
+    return;
+  }
+  const float var = rstd[c] / static_cast<float>(rows);
+  rstd[c] = rsqrtf(var + eps);
+  if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean[c];
+  if (running_var) {
+    const float unbiased = rows > 1 ? var * static_cast<float>(rows) / static_cast<float>(rows - 1) : var;
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * unbiased;
+  }
+}
+
+// y = (x - mean) * rstd * gamma + beta  (eval: statistics from the running buffers).  A thread owns four fixed
+// columns (when cols % 4 == 0 and the grid stride is a multiple of cols / 4), so scale and shift sit in registers.
+__global__ void __launch_bounds__(256)
+bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                const float* __restrict__ mean, const float* __restrict__ rstd_or_var, float* __restrict__ y,
+                long long rows, int cols, float eps, int stats_are_running) {
+  const long long n = rows * cols;
+  auto scale_shift = [&](int c, float& sc, float& sh) {
+    const float rs = stats_are_running ? rsqrtf(rstd_or_var[c] + eps) : rstd_or_var[c];
+    sc = rs * (gamma ? gamma[c] : 1.f);
+    sh = (beta ? beta[c] : 0.f) - mean[c] * sc;
+  };
+  if (cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    const int vpr = cols / 4;  // vectors per row
+    const long long nv = n / 4;
+    // stride chosen by the launcher as a multiple of vpr: the thread's columns never change
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (first >= nv) return;
+    const bool fixed = stride % vpr == 0;
+    float sc[4], sh[4];
+    const int c0 = static_cast<int>(first % vpr) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) scale_shift(c0 + j, sc[j], sh[j]);
+    for (long long i = first; i < nv; i += stride) {
+      if (!fixed) {
+        const int c = static_cast<int>(i % vpr) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) scale_shift(c + j, sc[j], sh[j]);
+      }
+      float4 v = reinterpret_cast<const float4*>(x)[i];
+      v.x = fmaf(v.x, sc[0], sh[0]);
+      v.y = fmaf(v.y, sc[1], sh[1]);
+      v.z = fmaf(v.z, sc[2], sh[2]);
+      v.w = fmaf(v.w, sc[3], sh[3]);
+      reinterpret_cast<float4*>(y)[i] = v;
     }
-  const float dg = col_sum_8(sg, sm);
-  const float db = col_sum_8(sb, sm);
-  if (live) {
-    if (threadIdx.y == 0) {
-      if (dgamma) dgamma[c] = dg;
-      if (dbeta) dbeta[c] = db;
+  } else {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float sc, sh;
+      scale_shift(static_cast<int>(i % cols), sc, sh);
+      y[i] = fmaf(x[i], sc, sh);
     }
-    const float w = (gamma ? gamma[c] : 1.f) * rs / static_cast<float>(rows);
-    for (long long r = threadIdx.y; r < rows; r += 8) {
-      const float h = (x[r * cols + c] - mu) * rs;
-      dx[r * cols + c] = w * (static_cast<float>(rows) * dy[r * cols + c] - db - h * dg);
+  }
+}
+
+// dx = gamma * rstd / rows * (rows * dy - d_beta - xhat * d_gamma), rewritten per column as
+// dx = A * dy + B * x + C with A = gamma rstd, B = -gamma rstd^2 d_gamma / rows,
+// C = -(gamma rstd / rows) d_beta - B mean.  Thread-fixed columns as in bn_apply_kernel.
+__global__ void __launch_bounds__(256)
+bn_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ gamma,
+             const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ dgamma,
+             const float* __restrict__ dbeta, float* __restrict__ dx, long long rows, int cols) {
+  const long long n = rows * cols;
+  const float inv_rows = 1.f / static_cast<float>(rows);
+  auto coeffs = [&](int c, float& A, float& B, float& C) {
+    const float rs = rstd[c], g = gamma ? gamma[c] : 1.f;
+    A = g * rs;
+    B = -g * rs * rs * dgamma[c] * inv_rows;
+    C = -A * inv_rows * dbeta[c] - B * mean[c];
+  };
+  const bool vec = cols % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                                      reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+  if (vec) {
+    const int vpr = cols / 4;
+    const long long nv = n / 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (first >= nv) return;
+    const bool fixed = stride % vpr == 0;
+    float A[4], B[4], C[4];
+    const int c0 = static_cast<int>(first % vpr) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) coeffs(c0 + j, A[j], B[j], C[j]);
+    for (long long i = first; i < nv; i += stride) {
+      if (!fixed) {
+        const int c = static_cast<int>(i % vpr) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) coeffs(c + j, A[j], B[j], C[j]);
+      }
+      const float4 g = reinterpret_cast<const float4*>(dy)[i];
+      const float4 v = reinterpret_cast<const float4*>(x)[i];
+      float4 o;
+      o.x = fmaf(A[0], g.x, fmaf(B[0], v.x, C[0]));
+      o.y = fmaf(A[1], g.y, fmaf(B[1], v.y, C[1]));
+      o.z = fmaf(A[2], g.z, fmaf(B[2], v.z, C[2]));
+      o.w = fmaf(A[3], g.w, fmaf(B[3], v.w, C[3]));
+      reinterpret_cast<float4*>(dx)[i] = o;
+    }
+  } else {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float A, B, C;
+      coeffs(static_cast<int>(i % cols), A, B, C);
+      dx[i] = fmaf(A, dy[i], fmaf(B, x[i], C));
     }
   }
 }
@@ -396,22 +535,75 @@ extern "C" int fb_gather_rows(const void* src, const long long* idx, void* dst, 
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace {
+// 2-D grid of the column-statistics passes: 128-column blocks x enough row blocks to fill the GPU.
+dim3 bn_stats_grid(long long rows, int cols, long long* rows_per_block) {
+  const long long col_blocks = (cols + 127) / 128;
+  long long rb = (static_cast<long long>(fb::sm_count()) * 4 + col_blocks - 1) / col_blocks;
+  const long long max_rb = (rows + 31) / 32;
+  if (rb > max_rb) rb = max_rb;
+  if (rb < 1) rb = 1;
+  if (rb > 65535) rb = 65535;
+  *rows_per_block = (rows + rb - 1) / rb;
+  return dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(rb));
+}
+// Grid of the elementwise passes (256 threads): the grid stride is a multiple of the vectors per row where
+// possible, so a thread keeps its columns and their per-column coefficients stay in registers.
+int bn_elementwise_grid(long long rows, int cols) {
+  long long blocks = static_cast<long long>(fb::sm_count()) * 6;
+  const long long nv = (rows * cols + 3) / 4;
+  if (cols % 4 == 0) {
+    const long long vpr = cols / 4;            // vectors per row
+    long long threads = blocks * 256;
+    if (threads > vpr && (threads / vpr * vpr) % 256 == 0) blocks = threads / vpr * vpr / 256;
+  }
+  const long long need = (nv + 255) / 256;
+  if (blocks > need) blocks = need;
+  return static_cast<int>(blocks < 1 ? 1 : blocks);
+}
+}  // namespace
+
+// Training: save_mean / save_rstd are required (they double as the accumulators of the statistics passes).
 extern "C" int fb_batchnorm_fwd(const float* x, const float* gamma, const float* beta, float* y, float* save_mean,
                                 float* save_rstd, float* running_mean, float* running_var, long long rows, int cols,
                                 float eps, float momentum, int training, cudaStream_t stream) {
+  using namespace fb;
   if (rows <= 0 || cols <= 0) return 0;
   if (!training && (running_mean == nullptr || running_var == nullptr)) return -1;
-  dim3 block(32, 8), grid((cols + 31) / 32);
-  batchnorm_fwd_kernel<<<grid, block, 0, stream>>>(x, gamma, beta, y, save_mean, save_rstd, running_mean,
-                                                   running_var, rows, cols, eps, momentum, training);
+  const int apply_grid = bn_elementwise_grid(rows, cols);
+  if (training) {
+    if (save_mean == nullptr || save_rstd == nullptr) return -1;
+    cudaError_t e = cudaMemsetAsync(save_mean, 0, cols * sizeof(float), stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(save_rstd, 0, cols * sizeof(float), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    long long rpb = 0;
+    const dim3 grid = bn_stats_grid(rows, cols, &rpb);
+    const int fgrid = (cols + 255) / 256;
+    bn_colstats_kernel<0><<<grid, 256, 0, stream>>>(x, nullptr, nullptr, nullptr, save_mean, nullptr, rows, cols, rpb);
+    bn_finalize_kernel<<<fgrid, 256, 0, stream>>>(save_mean, save_rstd, nullptr, nullptr, rows, cols, eps, momentum, 0);
+    bn_colstats_kernel<1><<<grid, 256, 0, stream>>>(x, nullptr, save_mean, nullptr, save_rstd, nullptr, rows, cols, rpb);
+    bn_finalize_kernel<<<fgrid, 256, 0, stream>>>(save_mean, save_rstd, running_mean, running_var, rows, cols, eps,
+                                                  momentum, 1);
+    bn_apply_kernel<<<apply_grid, 256, 0, stream>>>(x, gamma, beta, save_mean, save_rstd, y, rows, cols, eps, 0);
+  } else {
+    bn_apply_kernel<<<apply_grid, 256, 0, stream>>>(x, gamma, beta, running_mean, running_var, y, rows, cols, eps, 1);
+  }
   return static_cast<int>(cudaGetLastError());
 }
+// dgamma / dbeta are required (they are the accumulators of the statistics pass).
 extern "C" int fb_batchnorm_bwd(const float* dy, const float* x, const float* gamma, const float* save_mean,
                                 const float* save_rstd, float* dx, float* dgamma, float* dbeta, long long rows,
                                 int cols, cudaStream_t stream) {
+  using namespace fb;
   if (rows <= 0 || cols <= 0) return 0;
-  dim3 block(32, 8), grid((cols + 31) / 32);
-  batchnorm_bwd_kernel<<<grid, block, 0, stream>>>(dy, x, gamma, save_mean, save_rstd, dx, dgamma, dbeta, rows,
-                                                   cols);
+  if (dgamma == nullptr || dbeta == nullptr) return -1;
+  cudaError_t e = cudaMemsetAsync(dgamma, 0, cols * sizeof(float), stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(dbeta, 0, cols * sizeof(float), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  long long rpb = 0;
+  const dim3 grid = bn_stats_grid(rows, cols, &rpb);
+  bn_colstats_kernel<2><<<grid, 256, 0, stream>>>(x, dy, save_mean, save_rstd, dbeta, dgamma, rows, cols, rpb);
+  bn_dx_kernel<<<bn_elementwise_grid(rows, cols), 256, 0, stream>>>(dy, x, gamma, save_mean, save_rstd, dgamma, dbeta,
+                                                                    dx, rows, cols);
   return static_cast<int>(cudaGetLastError());
 }

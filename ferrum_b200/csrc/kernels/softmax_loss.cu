@@ -150,6 +150,79 @@ ce_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, fl
   }
 }
 
+
+// bf16 rows of 264..4096 columns (multiples of 8, 16-byte aligned): a warp owns a row, every lane keeps its
+// elements in registers (K vectors of 8), so the row is read once, exp is evaluated once per element and the
+// three reductions are warp shuffles without a block barrier.
+template <int K>
+__global__ void __launch_bounds__(256)
+ce_warp_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+               float* __restrict__ row_loss, __nv_bfloat16* __restrict__ dlogits, long long rows, int cols,
+               float grad_scale) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp_id; row < rows; row += nwarps) {
+    const __nv_bfloat16* xr = logits + row * cols;
+    float v[K][8];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + vi * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[k][2 * e] = f.x;
+          v[k][2 * e + 1] = f.y;
+          m = fmaxf(m, fmaxf(f.x, f.y));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[k][e] = -FLT_MAX;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[k][e] = __expf(v[k][e] - m);  // padded lanes: exp(-huge) = 0
+        s += v[k][e];
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const long long lab = labels[row];
+    const bool valid = lab >= 0 && lab < cols;
+    if (lane == 0 && row_loss) row_loss[row] = valid ? (m + logf(s) - __bfloat162float(xr[lab])) : 0.f;
+    if (dlogits) {
+      const float inv = valid ? grad_scale / s : 0.f;
+      __nv_bfloat16* gr = dlogits + row * cols;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int vi = lane + 32 * k;
+        if (vi < nvec) {
+          uint4 out;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float a = v[k][2 * e] * inv, b = v[k][2 * e + 1] * inv;
+            if (valid && vi * 8 + 2 * e == lab) a -= grad_scale;
+            if (valid && vi * 8 + 2 * e + 1 == lab) b -= grad_scale;
+            h[e] = __floats2bfloat162_rn(a, b);
+          }
+          *reinterpret_cast<uint4*>(gr + vi * 8) = out;
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------- elementwise losses
 __device__ __forceinline__ float loss_elem(float p, float t, int kind) {
   const float d = p - t;
@@ -239,9 +312,29 @@ int softmax_bwd_t(const void* dy, const void* y, void* dx, long long rows, int c
         static_cast<const T*>(dy), static_cast<const T*>(y), static_cast<T*>(dx), rows, cols, log_mode);
   return static_cast<int>(cudaGetLastError());
 }
+// bf16 logits with bf16 gradient, vectorisable rows: the warp-per-row kernel.
+bool ce_warp_launch(const void* logits, const long long* labels, float* row_loss, void* dlogits, long long rows,
+                    int cols, float gs, cudaStream_t st) {
+  if (cols % 8 != 0 || cols < 264 || cols > 4096) return false;
+  if (((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) != 0) return false;
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(logits);
+  __nv_bfloat16* g = static_cast<__nv_bfloat16*>(dlogits);
+  const int grid = row_grid(rows, 8);
+  const int k = (cols / 8 + 31) / 32;
+  if (k <= 4)
+    ce_warp_kernel<4><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+  else if (k <= 8)
+    ce_warp_kernel<8><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+  else
+    ce_warp_kernel<16><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+  return true;
+}
+
 template <typename T, typename G>
 int ce_t(const void* logits, const long long* labels, float* row_loss, void* dlogits, long long rows, int cols,
          float gs, cudaStream_t st) {
+  if (sizeof(T) == 2 && sizeof(G) == 2 && ce_warp_launch(logits, labels, row_loss, dlogits, rows, cols, gs, st))
+    return static_cast<int>(cudaGetLastError());
   if (cols <= 512)
     ce_kernel<T, G, 32><<<row_grid(rows, 8), 256, 0, st>>>(static_cast<const T*>(logits), labels, row_loss,
                                                           static_cast<G*>(dlogits), rows, cols, gs);

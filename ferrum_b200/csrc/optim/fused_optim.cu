@@ -169,18 +169,41 @@ __global__ void sgd_multi_kernel(const SgdTable t, const fb_sgd_hparams h) {
 }
 
 // ------------------------------------------------------------------- AMP
+// All three walk the tensors with 16-byte accesses, two independent vectors per thread per trip (the head
+// up to the first 16-byte boundary and the tail are done element-wise).
+template <typename F4, typename F1>
+__device__ __forceinline__ void walk_rw(float* p, long long n, long long tid, long long stride, F4 f4, F1 f1) {
+  const long long head = min(n, static_cast<long long>((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / 4);
+  for (long long i = tid; i < head; i += stride) p[i] = f1(p[i]);
+  float4* q = reinterpret_cast<float4*>(p + head);
+  const long long nv = (n - head) >> 2;
+  for (long long i = tid; i < nv; i += 2 * stride) {
+    const long long j = i + stride;
+    float4 a = q[i], b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j < nv) b = q[j];
+    q[i] = f4(a);
+    if (j < nv) q[j] = f4(b);
+  }
+  for (long long i = head + (nv << 2) + tid; i < n; i += stride) p[i] = f1(p[i]);
+}
+
 __global__ void unscale_check_kernel(const GradTable tb, float inv_scale, float* found_inf) {
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   bool bad = false;
-  for (int t = 0; t < tb.count; ++t) {
-    float* p = tb.g[t];
-    for (long long i = tid; i < tb.n[t]; i += stride) {
-      const float v = p[i] * inv_scale;
-      if (!isfinite(v)) bad = true;
-      p[i] = v;
-    }
-  }
+  auto f1 = [&](float v) {
+    v *= inv_scale;
+    if (!isfinite(v)) bad = true;
+    return v;
+  };
+  auto f4 = [&](float4 v) {
+    v.x *= inv_scale; v.y *= inv_scale; v.z *= inv_scale; v.w *= inv_scale;
+    // a non-finite lane makes the sum of (v - v) NaN: one test for four values
+    const float z = (v.x - v.x) + (v.y - v.y) + (v.z - v.z) + (v.w - v.w);
+    if (z != 0.f) bad = true;
+    return v;
+  };
+  for (int t = 0; t < tb.count; ++t) walk_rw(tb.g[t], tb.n[t], tid, stride, f4, f1);
   if (bad) *found_inf = 1.f;
 }
 
@@ -188,11 +211,25 @@ __global__ void sumsq_multi_kernel(const GradTable tb, float* out) {
   __shared__ float smem[8];
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  float acc = 0.f;
+  float acc0 = 0.f, acc1 = 0.f;
   for (int t = 0; t < tb.count; ++t) {
     const float* p = tb.g[t];
-    for (long long i = tid; i < tb.n[t]; i += stride) acc += p[i] * p[i];
+    const long long n = tb.n[t];
+    const long long head = min(n, static_cast<long long>((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / 4);
+    for (long long i = tid; i < head; i += stride) acc0 = fmaf(p[i], p[i], acc0);
+    const float4* q = reinterpret_cast<const float4*>(p + head);
+    const long long nv = (n - head) >> 2;
+    for (long long i = tid; i < nv; i += 2 * stride) {
+      const long long j = i + stride;
+      const float4 a = q[i];
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < nv) b = q[j];
+      acc0 = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, acc0))));
+      acc1 = fmaf(b.x, b.x, fmaf(b.y, b.y, fmaf(b.z, b.z, fmaf(b.w, b.w, acc1))));
+    }
+    for (long long i = head + (nv << 2) + tid; i < n; i += stride) acc0 = fmaf(p[i], p[i], acc0);
   }
+  float acc = acc0 + acc1;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = acc;
@@ -213,11 +250,13 @@ __global__ void scale_multi_kernel(const GradTable tb, const float* total_sumsq,
   if (mode == 0) {
     coef = max_norm / (sqrtf(*total_sumsq) + 1e-6f);
     if (coef >= 1.f) return;
-  }
-  for (int t = 0; t < tb.count; ++t) {
-    float* p = tb.g[t];
-    for (long long i = tid; i < tb.n[t]; i += stride)
-      p[i] = mode == 0 ? p[i] * coef : fminf(fmaxf(p[i], -clip_value), clip_value);
+    auto f1 = [&](float v) { return v * coef; };
+    auto f4 = [&](float4 v) { return make_float4(v.x * coef, v.y * coef, v.z * coef, v.w * coef); };
+    for (int t = 0; t < tb.count; ++t) walk_rw(tb.g[t], tb.n[t], tid, stride, f4, f1);
+  } else {
+    auto f1 = [&](float v) { return fminf(fmaxf(v, -clip_value), clip_value); };
+    auto f4 = [&](float4 v) { return make_float4(f1(v.x), f1(v.y), f1(v.z), f1(v.w)); };
+    for (int t = 0; t < tb.count; ++t) walk_rw(tb.g[t], tb.n[t], tid, stride, f4, f1);
   }
 }
 

@@ -21,7 +21,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=float, default=1024.0)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--blocks", type=int, default=64)
+    ap.add_argument("--blocks", type=int, default=128)
     ap.add_argument("--threads", type=int, default=256)
     ap.add_argument("--shard-master", action="store_true", help="publish only the bf16 copy to peers")
     ap.add_argument("--out", default="")

@@ -111,7 +111,7 @@ class DistributedDataParallel(Module, GradSink):
         self._opt = None
         self._shard_master = os.environ.get("FERRUM_SHARD_MASTER", "0") == "1"
         self._master_stale = False
-        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "48"))
+        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "128"))
         self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
         if optimizer is not None:
             self.fuse_optimizer(optimizer)

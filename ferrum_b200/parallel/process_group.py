@@ -111,7 +111,7 @@ class ProcessGroup:
         return torch.cuda.current_stream().cuda_stream
 
     def _blocks(self, nbytes: int) -> int:
-        return max(1, min(64, nbytes // (128 * 1024) + 1))
+        return max(1, min(128, nbytes // (128 * 1024) + 1))
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, tensor, op: ReduceOp = ReduceOp.Sum):

@@ -102,8 +102,17 @@ class SymmetricArena:
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
 
+        name = dist.group.WORLD.group_name
+        try:  # needed by some torch versions, a deprecated no-op in others
+            import warnings
+
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                symm.enable_symm_mem_for_group(name)
+        except Exception:
+            pass
         t = symm.empty(total, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
-        hdl = symm.rendezvous(t, dist.group.WORLD.group_name)
+        hdl = symm.rendezvous(t, name)
         t.zero_()
         torch.cuda.synchronize()
         dist.barrier()

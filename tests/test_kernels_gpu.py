@@ -506,3 +506,32 @@ def test_cross_entropy_backward_scales_by_incoming_gradient_on_device():
         (F.cross_entropy_logits(x1, labels) * -3.5).backward()
         (torch.nn.functional.cross_entropy(x2, labels) * -3.5).backward()
         assert torch.allclose(x1.grad.float(), x2.grad, atol=1e-6 if dtype == torch.float32 else 2e-4, rtol=2e-2)
+
+
+def test_layernorm_forward_ring_variant_in_subprocess():
+    """The opt-in forward ring kernel (FERRUM_LN_RING_FWD=1, read once per process) against PyTorch."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import torch, sys
+sys.path.insert(0, %r)
+from ferrum_b200.ops import functional as F
+torch.manual_seed(0)
+for dtype, tol in ((torch.bfloat16, 4e-2), (torch.float32, 2e-4)):
+    for rows, cols in ((300, 4096), (77, 2048), (5, 1024 if dtype == torch.float32 else 4000)):
+        x = (torch.randn(rows, cols, device="cuda") * 2 + 0.7).to(dtype)
+        g = torch.rand(cols, device="cuda") + 0.5
+        b = torch.randn(cols, device="cuda")
+        y = F.layer_norm(x, g, b, 1e-5)
+        ref = torch.nn.functional.layer_norm(x.float(), (cols,), g, b, 1e-5)
+        err = (y.float() - ref).abs().max().item()
+        assert err < tol, (dtype, rows, cols, err)
+from ferrum_b200.utils.runtime import check_status
+check_status()
+print("RING_OK")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, FERRUM_LN_RING_FWD="1")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert "RING_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
