@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--depth", type=int, default=MODEL["depth"])
     ap.add_argument("--width", type=int, default=MODEL["width"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-overlap-optimizer", action="store_true",
+                    help="1 GPU: run Adam as one pass after backward instead of per-bucket behind each weight "
+                         "gradient (the engine every multi-GPU run uses)")
     ap.add_argument("--shard-master", action="store_true",
                     help="DDP: publish only bf16 weights to peers, fp32 master weights stay with the shard owner")
     return ap.parse_args()
@@ -142,13 +145,14 @@ def run_ours(args):
     from ferrum_b200.models import wide_mlp
 
     dev = fb.Device.Cuda(local)
-    if world > 1:
+    use_engine = world > 1 or not args.no_overlap_optimizer
+    if use_engine:
         fb.distributed.init_process_group_from_env(backend="nvlink")
     torch.manual_seed(1234)
     model = wide_mlp(MODEL["in_features"], args.width, args.depth, MODEL["num_classes"], device=dev)
     opt = optim.Adam(model.parameters(), optim.AdamConfig(lr=LR))
     engine = None
-    if world > 1:
+    if use_engine:
         engine = fb.distributed.DistributedDataParallel(model, fb.distributed.get_world()).bucket_size_mb(25)
         engine.fuse_optimizer(opt)
         if args.shard_master:
@@ -213,7 +217,11 @@ def run_ours(args):
     fb.utils.runtime.check_status()
     if engine is not None:
         engine.shutdown()
-    return ms, launches, clocks, e2e, ("nvlink-fused-ddp" + ("-sharded-master" if args.shard_master else "")) if world > 1 else "single"
+    if world > 1:
+        par = "nvlink-fused-ddp" + ("-sharded-master" if args.shard_master else "")
+    else:
+        par = "single, optimizer overlapped with backward" if use_engine else "single"
+    return ms, launches, clocks, e2e, par
 
 
 def run_torch(args):
@@ -227,9 +235,9 @@ def main():
     args = parse()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
-                          "unavailable": "reference is a Rust workspace (no Python package; pip install of "
-                                         "/root/reference fails: no setup.py/pyproject.toml) and cargo/rustc are not "
-                                         "in this image, so it cannot be built or run here"}))
+                          "unavailable": "reference is a Rust workspace (no Python package: pip install of its "
+                                         "source tree fails with 'neither setup.py nor pyproject.toml found') and "
+                                         "cargo/rustc are not in this image, so it cannot be built or run here"}))
         return 0
     rank, world, _ = dist_env()
     if world != args.gpus and args.gpus > 1:

@@ -404,6 +404,32 @@ __global__ void transpose_kernel(const T* __restrict__ s, T* __restrict__ d, int
   }
 }
 
+// 2-byte elements, even rows / cols, 4-byte aligned pitches: 64 x 64 tiles moved as 32-bit pairs, so global
+// loads and stores are 128 bytes per warp row (the 32 x 32 kernel above moves 64) and a block has 8 KB in flight.
+__global__ void __launch_bounds__(256)
+transpose16_pairs_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ d, int rows, int cols) {
+  __shared__ uint16_t tile[64][66];  // pitch 132 B: 4-byte aligned rows, conflict-free pair stores
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int x = threadIdx.x, y = threadIdx.y;  // 32 x 8
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r = r0 + y + 8 * j, c = c0 + 2 * x;
+    uint32_t v = 0;
+    if (r < rows && c < cols) v = *reinterpret_cast<const uint32_t*>(s + static_cast<long long>(r) * cols + c);
+    *reinterpret_cast<uint32_t*>(&tile[y + 8 * j][2 * x]) = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = c0 + y + 8 * j, r = r0 + 2 * x;  // output row c holds input rows r, r + 1
+    if (c < cols && r < rows) {
+      const uint32_t v = static_cast<uint32_t>(tile[2 * x][y + 8 * j]) |
+                         (static_cast<uint32_t>(tile[2 * x + 1][y + 8 * j]) << 16);
+      *reinterpret_cast<uint32_t*>(d + static_cast<long long>(c) * rows + r) = v;
+    }
+  }
+}
+
 // y = x * (*scalar): the incoming gradient of a scalar loss applied to a stored gradient, without a host read.
 template <typename T>
 __global__ void scale_by_scalar_kernel(const T* __restrict__ x, const float* __restrict__ scalar, T* __restrict__ y,
@@ -583,6 +609,10 @@ extern "C" int fb_transpose_2d(const void* src, void* dst, int rows, int cols, i
   if (elem_size == 4) {
     transpose_kernel<uint32_t><<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src),
                                                           static_cast<uint32_t*>(dst), rows, cols);
+  } else if (elem_size == 2 && rows % 2 == 0 && cols % 2 == 0 &&
+             ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 3) == 0) {
+    transpose16_pairs_kernel<<<dim3((cols + 63) / 64, (rows + 63) / 64), block, 0, stream>>>(
+        static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), rows, cols);
   } else if (elem_size == 2) {
     transpose_kernel<uint16_t><<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(src),
                                                           static_cast<uint16_t*>(dst), rows, cols);

@@ -216,6 +216,91 @@ ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma, const fl
   }
 }
 
+__device__ __forceinline__ void ld_pairs_f32(const float* p, float2 (&o)[4]);
+
+// Forward, one WARP per row (bf16, 1024..4096 columns): a lane keeps its K 16-byte vectors packed in registers,
+// all K loads are issued back to back (up to 8 KB in flight per warp), the statistics are one pass of shifted sums
+// (x - c with c = the row's first element) reduced by warp shuffles, and there is no block barrier at all: warps
+// stream rows independently.  Packed fp32x2 arithmetic; gamma / beta come through L1.
+template <int K>
+__global__ void __launch_bounds__(256, 2)
+ln_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                   long long rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const float inv_n = 1.f / static_cast<float>(cols);
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp_id; row < rows; row += nwarps) {
+    const __nv_bfloat16* xr = x + row * cols;
+    uint4 raw[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      raw[k] = vi < nvec ? *reinterpret_cast<const uint4*>(xr + vi * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // c = element 0 of the row = low half of lane 0's first word
+    const float c = __uint_as_float(__shfl_sync(0xffffffffu, raw[0].x, 0) << 16);
+    const float2 nc = make_float2(-c, -c);
+    float2 s2 = make_float2(0.f, 0.f), q2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      if (lane + 32 * k < nvec) {
+        const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 v = make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+          const float2 d = __fadd2_rn(v, nc);
+          s2 = __fadd2_rn(s2, d);
+          q2 = __ffma2_rn(d, d, q2);
+        }
+      }
+    }
+    float s = s2.x + s2.y, q = q2.x + q2.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    const float ms = s * inv_n;
+    const float var = fmaxf(q * inv_n - ms * ms, 0.f);
+    const float mu = c + ms;
+    const float rs = rsqrtf(var + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mu;
+      if (rstd_out) rstd_out[row] = rs;
+    }
+    const float2 rs2 = make_float2(rs, rs), sh2 = make_float2(-mu * rs, -mu * rs);
+    __nv_bfloat16* yr = y + row * cols;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+        float2 g[4], b[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          g[e] = make_float2(1.f, 1.f);
+          b[e] = make_float2(0.f, 0.f);
+        }
+        if (gamma) ld_pairs_f32(gamma + vi * 8, g);
+        if (beta) ld_pairs_f32(beta + vi * 8, b);
+        uint4 out;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 v = make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+          const float2 o = __ffma2_rn(__ffma2_rn(v, rs2, sh2), g[e], b[e]);
+          const __nv_bfloat162 pk = __float22bfloat162_rn(o);
+          ow[e] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(yr + vi * 8) = out;
+      }
+    }
+  }
+}
+
 // Backward.  x and dy stay packed in registers between the statistics pass and the output pass; the
 // three column partials (dy*xhat, dy, dx) accumulate in registers over all rows the block visits and are
 // written once to partial[blockIdx][3][cols].
@@ -881,6 +966,31 @@ int ring_stages(size_t slot_bytes, size_t budget) {
   return static_cast<int>(fit > kMaxRingStages ? kMaxRingStages : fit);
 }
 
+// Warp-per-row forward: bf16 rows of 1024 .. 4096 columns without a fused activation (FERRUM_LN_WARP_FWD=0 = off).
+template <typename T>
+bool launch_fwd_warp(const T*, const float*, const float*, T*, float*, float*, long long, int, float, int,
+                     cudaStream_t) {
+  return false;
+}
+template <>
+bool launch_fwd_warp<__nv_bfloat16>(const __nv_bfloat16* xp, const float* gamma, const float* beta,
+                                    __nv_bfloat16* yp, float* mean, float* rstd, long long rows, int cols, float eps,
+                                    int pre_act, cudaStream_t st) {
+  static const int enabled = env_int("FERRUM_LN_WARP_FWD", 1);
+  if (!enabled || pre_act != FB_ACT_NONE || cols < 1024 || cols > 4096) return false;
+  const int k = (cols / 8 + 31) / 32;
+  const long long want = (rows + 7) / 8;  // eight warps per block
+  const long long cap = static_cast<long long>(sm_count()) * 2;
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  if (k <= 4)
+    ln_fwd_warp_kernel<4><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps);
+  else if (k <= 8)
+    ln_fwd_warp_kernel<8><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps);
+  else
+    ln_fwd_warp_kernel<16><<<grid, 256, 0, st>>>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps);
+  return true;
+}
+
 // Ring kernel for rows of at least 2 KB and at most 4096 columns; false if it cannot be launched.
 template <typename T>
 bool launch_fwd_ring(const T* xp, const float* gamma, const float* beta, T* yp, float* mean, float* rstd,
@@ -915,6 +1025,8 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
   Geo g;
   if (geometry(cols, &g) && aligned16(x, y, gamma, beta)) {
     const int nvec = cols / 8;
+    if (launch_fwd_warp<T>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, st))
+      return static_cast<int>(cudaGetLastError());
     static const int ring_fwd = env_int("FERRUM_LN_RING_FWD", 0);
     if (ring_fwd && ring_enabled() && static_cast<size_t>(cols) * sizeof(T) >= 2048 && nvec <= 2 * kGroupThreads &&
         launch_fwd_ring<T>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, st))

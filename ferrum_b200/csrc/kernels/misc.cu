@@ -65,34 +65,115 @@ template <>
 __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // One Philox call covers 4 consecutive elements.
+// One Philox call yields 128 random bits = eight 16-bit draws: a thread handles eight consecutive elements per
+// call (one 16-byte load / store of bf16, two of fp32, one 8-byte mask store).  Keep-probability resolution 2^-16.
 template <typename T>
-__global__ void dropout_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ mask,
-                                   long long n, float p, unsigned long long seed, unsigned long long offset) {
+__global__ void __launch_bounds__(256)
+dropout_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ mask, long long n, float p,
+                   unsigned long long seed, unsigned long long offset) {
   const float scale = 1.f / (1.f - p);
-  const uint32_t thresh = static_cast<uint32_t>(fminf(p, 1.f) * 4294967295.0f);
+  const uint32_t thresh = static_cast<uint32_t>(fminf(fmaxf(p, 0.f), 1.f) * 65536.0f);  // keep when draw >= thresh
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  const long long n4 = (n + 3) >> 2;
-  for (long long q = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; q < n4; q += stride) {
+  const long long n8 = (n + 7) >> 3;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(mask) & 7) == 0;
+  for (long long q = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; q < n8; q += stride) {
     uint32_t r[4];
     philox4x32_10(seed, static_cast<unsigned long long>(q), offset, r);
+    bool keep[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const long long i = q * 4 + j;
-      if (i < n) {
-        const bool keep = r[j] >= thresh;
-        mask[i] = keep ? 1 : 0;
-        stf(y + i, keep ? ldf(x + i) * scale : 0.f);
+    for (int j = 0; j < 8; ++j) keep[j] = ((r[j >> 1] >> ((j & 1) * 16)) & 0xffffu) >= thresh;
+    const long long i0 = q * 8;
+    if (aligned && i0 + 8 <= n) {
+      float v[8];
+      if constexpr (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + i0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[2 * e] = f.x;
+          v[2 * e + 1] = f.y;
+        }
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(x + i0);
+        const float4 b = *reinterpret_cast<const float4*>(x + i0 + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      }
+      uint32_t m0 = 0, m1 = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[j] = keep[j] ? v[j] * scale : 0.f;
+        if (keep[j]) (j < 4 ? m0 : m1) |= 1u << ((j & 3) * 8);
+      }
+      *reinterpret_cast<uint2*>(mask + i0) = make_uint2(m0, m1);
+      if constexpr (sizeof(T) == 2) {
+        uint4 out;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+        *reinterpret_cast<uint4*>(y + i0) = out;
+      } else {
+        *reinterpret_cast<float4*>(y + i0) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(y + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const long long i = i0 + j;
+        if (i < n) {
+          mask[i] = keep[j] ? 1 : 0;
+          stf(y + i, keep[j] ? ldf(x + i) * scale : 0.f);
+        }
       }
     }
   }
 }
 template <typename T>
-__global__ void dropout_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ mask, T* __restrict__ dx,
-                                   long long n, float p) {
+__global__ void __launch_bounds__(256)
+dropout_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ mask, T* __restrict__ dx, long long n,
+                   float p) {
   const float scale = 1.f / (1.f - p);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    stf(dx + i, mask[i] ? ldf(dy + i) * scale : 0.f);
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(mask) & 7) == 0;
+  const long long n8 = aligned ? (n >> 3) : 0;
+  for (long long q = tid; q < n8; q += stride) {
+    const long long i0 = q * 8;
+    const uint2 m = *reinterpret_cast<const uint2*>(mask + i0);
+    float v[8];
+    if constexpr (sizeof(T) == 2) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(dy + i0);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        v[2 * e] = f.x;
+        v[2 * e + 1] = f.y;
+      }
+    } else {
+      const float4 a = *reinterpret_cast<const float4*>(dy + i0);
+      const float4 b = *reinterpret_cast<const float4*>(dy + i0 + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t bits = (j < 4 ? m.x : m.y) >> ((j & 3) * 8);
+      v[j] = (bits & 0xffu) ? v[j] * scale : 0.f;
+    }
+    if constexpr (sizeof(T) == 2) {
+      uint4 out;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+      *reinterpret_cast<uint4*>(dx + i0) = out;
+    } else {
+      *reinterpret_cast<float4*>(dx + i0) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(dx + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+  for (long long i = (n8 << 3) + tid; i < n; i += stride) stf(dx + i, mask[i] ? ldf(dy + i) * scale : 0.f);
 }
 
 // --------------------------------------------------------------- Embedding
@@ -156,31 +237,74 @@ __global__ void embedding_meanpool_kernel(const float* __restrict__ w, const lon
   }
 }
 
-// Scatter-add over a SORTED index list: a block walks a chunk of 32 consecutive
-// positions, sums runs of equal indices in registers and flushes each run with
-// one atomicAdd per element, so heavily repeated tokens cost one flush per
-// chunk instead of one per occurrence.  perm[i] is the original position.
+// Scatter-add over a SORTED index list: a block walks a chunk of 32 consecutive positions, sums runs of equal
+// indices in registers and flushes each run once, so heavily repeated tokens cost one flush per chunk instead of
+// one per occurrence.  perm[i] is the original position.  The chunk's ids and source rows are staged in shared
+// memory once (one 64-bit division per position instead of one per thread and position); with dim % 4 == 0 a
+// thread owns four adjacent columns: 8- or 16-byte loads of dout and one vector atomic (red.global.add.v4.f32)
+// per run.
 template <typename G>
 __global__ void embedding_bwd_sorted_kernel(const G* __restrict__ dout, const long long* __restrict__ sorted_idx,
                                             const long long* __restrict__ perm, float* __restrict__ dw,
                                             long long n_idx, int dim, int group, float scale,
                                             long long padding_idx) {
   constexpr int kChunk = 32;
+  __shared__ long long s_id[kChunk];
+  __shared__ long long s_row[kChunk];
   const long long lo = static_cast<long long>(blockIdx.x) * kChunk;
-  const long long hi = min(n_idx, lo + kChunk);
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float acc = 0.f;
-    long long cur = -1;
-    for (long long i = lo; i < hi; ++i) {
-      const long long id = sorted_idx[i];
-      if (id != cur) {
-        if (cur >= 0 && cur != padding_idx) atomicAdd(dw + cur * dim + c, acc * scale);
-        cur = id;
-        acc = 0.f;
+  const int cnt = static_cast<int>(min(n_idx, lo + kChunk) - lo);
+  if (threadIdx.x < cnt) {
+    s_id[threadIdx.x] = sorted_idx[lo + threadIdx.x];
+    s_row[threadIdx.x] = perm[lo + threadIdx.x] / group;
+  }
+  __syncthreads();
+  const bool vec = dim % 4 == 0 && (reinterpret_cast<uintptr_t>(dw) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dout) & (4 * sizeof(G) - 1)) == 0;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      long long cur = -1;
+      auto flush = [&]() {
+        if (cur >= 0 && cur != padding_idx)
+          atomicAdd(reinterpret_cast<float4*>(dw + cur * dim + c),
+                    make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale));
+      };
+#pragma unroll 4
+      for (int k = 0; k < cnt; ++k) {
+        const long long id = s_id[k];
+        if (id != cur) {
+          flush();
+          cur = id;
+          acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        const G* src = dout + s_row[k] * dim + c;
+        if constexpr (sizeof(G) == 2) {
+          const uint2 u = *reinterpret_cast<const uint2*>(src);
+          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+          const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+          acc.x += f0.x; acc.y += f0.y; acc.z += f1.x; acc.w += f1.y;
+        } else {
+          const float4 f = *reinterpret_cast<const float4*>(src);
+          acc.x += f.x; acc.y += f.y; acc.z += f.z; acc.w += f.w;
+        }
       }
-      acc += ldf(dout + (perm[i] / group) * dim + c);
+      flush();
     }
-    if (cur >= 0 && cur != padding_idx) atomicAdd(dw + cur * dim + c, acc * scale);
+  } else {
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      float acc = 0.f;
+      long long cur = -1;
+      for (int k = 0; k < cnt; ++k) {
+        const long long id = s_id[k];
+        if (id != cur) {
+          if (cur >= 0 && cur != padding_idx) atomicAdd(dw + cur * dim + c, acc * scale);
+          cur = id;
+          acc = 0.f;
+        }
+        acc += ldf(dout + s_row[k] * dim + c);
+      }
+      if (cur >= 0 && cur != padding_idx) atomicAdd(dw + cur * dim + c, acc * scale);
+    }
   }
 }
 
@@ -447,7 +571,7 @@ extern "C" int fb_dropout_fwd(const void* x, void* y, uint8_t* mask, long long n
                               unsigned long long offset, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (p < 0.f || p >= 1.f) return -1;
-  const int g = grid1d((n + 3) / 4, 256);
+  const int g = grid1d((n + 7) / 8, 256);
   if (dtype == FB_DT_F32)
     dropout_fwd_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(y), mask, n,
                                                     p, seed, offset);
@@ -461,7 +585,7 @@ extern "C" int fb_dropout_fwd(const void* x, void* y, uint8_t* mask, long long n
 extern "C" int fb_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, long long n, float p, int dtype,
                               cudaStream_t stream) {
   if (n <= 0) return 0;
-  const int g = grid1d(n, 256);
+  const int g = grid1d((n + 7) / 8, 256);
   if (dtype == FB_DT_F32)
     dropout_bwd_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(dy), mask, static_cast<float*>(dx),
                                                     n, p);

@@ -142,41 +142,63 @@ reduce_cols_vec_kernel(const float* __restrict__ x, float* __restrict__ out, lon
   }
 }
 
-__global__ void arg_rows_kernel(const float* __restrict__ x, long long* __restrict__ idx, float* __restrict__ val,
-                                long long R, int is_max) {
-  __shared__ float sv[128];
-  __shared__ long long si[128];
+// One 128-thread block per row: 16-byte loads (two in flight per thread), then a warp-shuffle tournament on
+// (value, index) with ties going to the lower index, then four warp winners through shared memory.
+__global__ void __launch_bounds__(128)
+arg_rows_kernel(const float* __restrict__ x, long long* __restrict__ idx, float* __restrict__ val, long long R,
+                int is_max) {
+  __shared__ float sv[4];
+  __shared__ long long si[4];
   const long long row = blockIdx.x;
   const float* p = x + row * R;
   float best = is_max ? -FLT_MAX : FLT_MAX;
   long long bi = 0x7fffffffffffffffLL;
-  for (long long i = threadIdx.x; i < R; i += blockDim.x) {
-    const float v = p[i];
-    if (is_max ? (v > best) : (v < best)) {
+  auto consider = [&](float v, long long i) {
+    if (is_max ? (v > best) : (v < best)) {  // strict: the first occurrence wins inside a thread (i increases)
       best = v;
       bi = i;
     }
-  }
-  sv[threadIdx.x] = best;
-  si[threadIdx.x] = bi;
-  __syncthreads();
-  for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
-    if (threadIdx.x < s) {
-      const float ov = sv[threadIdx.x + s];
-      const long long oi = si[threadIdx.x + s];
-      const float mv = sv[threadIdx.x];
-      const long long mi = si[threadIdx.x];
-      const bool better = is_max ? (ov > mv) : (ov < mv);
-      if (better || (ov == mv && oi < mi)) {
-        sv[threadIdx.x] = ov;
-        si[threadIdx.x] = oi;
-      }
+  };
+  const long long head = min(R, static_cast<long long>((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / 4);
+  for (long long i = threadIdx.x; i < head; i += blockDim.x) consider(p[i], i);
+  const float4* q = reinterpret_cast<const float4*>(p + head);
+  const long long nv = (R - head) >> 2;
+  for (long long i = threadIdx.x; i < nv; i += 2 * blockDim.x) {
+    const long long j = i + blockDim.x;
+    const float4 a = q[i];
+    float4 b = a;
+    if (j < nv) b = q[j];
+    const long long ia = head + 4 * i, ib = head + 4 * j;
+    consider(a.x, ia); consider(a.y, ia + 1); consider(a.z, ia + 2); consider(a.w, ia + 3);
+    if (j < nv) {
+      consider(b.x, ib); consider(b.y, ib + 1); consider(b.z, ib + 2); consider(b.w, ib + 3);
     }
-    __syncthreads();
   }
+  for (long long i = head + (nv << 2) + threadIdx.x; i < R; i += blockDim.x) consider(p[i], i);
+  auto merge = [&](float ov, long long oi) {
+    const bool better = is_max ? (ov > best) : (ov < best);
+    if (better || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    merge(ov, oi);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
-    idx[row] = si[0] == 0x7fffffffffffffffLL ? 0 : si[0];
-    if (val) val[row] = sv[0];
+    const int nw = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < nw; ++w) merge(sv[w], si[w]);
+    idx[row] = bi == 0x7fffffffffffffffLL ? 0 : bi;
+    if (val) val[row] = best;
   }
 }
 

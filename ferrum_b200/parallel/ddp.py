@@ -180,7 +180,11 @@ class DistributedDataParallel(Module, GradSink):
 
     # ------------------------------------------------------------------ build
     def _native(self) -> bool:
-        return (self._pg.backend() is Backend.Nvlink and self._pg.world_size() > 1 and
+        # A single rank also takes the native path once an optimizer is fused: the "reduction" then has nothing to
+        # fetch, and what remains is the per-bucket optimizer update launched behind each weight gradient on the
+        # side stream, i.e. the update overlapped with the rest of backward instead of a separate pass after it.
+        world = self._pg.world_size()
+        return (self._pg.backend() is Backend.Nvlink and (world > 1 or (world == 1 and self._opt is not None)) and
                 all(p.is_cuda for p in torch.nn.Module.parameters(self.inner)))
 
     def _build(self) -> None:
