@@ -51,6 +51,129 @@ __device__ __forceinline__ float group_reduce(float v, float* smem) {
   return t;
 }
 
+
+// Rows of 8-element-multiple width up to 4096 (16-byte aligned): a warp owns a row and keeps it in registers
+// (K vectors of 8 per lane), so the row is read once, exp is evaluated once per element and the reductions are
+// warp shuffles.  Used for both dtypes; the scalar kernels below remain for ragged widths and very wide rows.
+template <typename T>
+__device__ __forceinline__ void ld8(const T* p, float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 t = __bfloat1622float2(h[e]);
+      f[2 * e] = t.x;
+      f[2 * e + 1] = t.y;
+    }
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void st8(T* p, const float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+    *reinterpret_cast<uint4*>(p) = out;
+  } else {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(256)
+softmax_fwd_warp_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int cols, int log_mode) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp_id; row < rows; row += nwarps) {
+    const T* xr = x + row * cols;
+    float v[K][8];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        ld8(xr + vi * 8, v[k]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, v[k][e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[k][e] = -FLT_MAX;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.f;
+    float ex[K][8];
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        ex[k][e] = expf(v[k][e] - m);
+        s += ex[k][e];
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.f / s, lse = m + logf(s);
+    T* yr = y + row * cols;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = log_mode ? v[k][e] - lse : ex[k][e] * inv;
+        st8(yr + vi * 8, o);
+      }
+    }
+  }
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(256)
+softmax_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, long long rows,
+                        int cols, int log_mode) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp_id; row < rows; row += nwarps) {
+    const long long base = row * cols;
+    float g[K][8], v[K][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        ld8(dy + base + vi * 8, g[k]);
+        ld8(y + base + vi * 8, v[k]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += log_mode ? g[k][e] : g[k][e] * v[k][e];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = log_mode ? g[k][e] - expf(v[k][e]) * s : v[k][e] * (g[k][e] - s);
+        st8(dx + base + vi * 8, o);
+      }
+    }
+  }
+}
+
 // One group of TPR threads per row; 256 threads per block.
 template <typename T, int TPR>
 __global__ void __launch_bounds__(256)
@@ -291,8 +414,22 @@ int row_grid(long long rows, int rpb) {
   return static_cast<int>(nb < cap ? nb : cap);
 }
 
+bool warp_rows_ok(const void* a, const void* b, const void* c, int cols) {
+  return cols % 8 == 0 && cols >= 64 && cols <= 2048 &&
+         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
 template <typename T>
 int softmax_fwd_t(const void* x, void* y, long long rows, int cols, int log_mode, cudaStream_t st) {
+  if (warp_rows_ok(x, y, nullptr, cols)) {
+    const int k = (cols / 8 + 31) / 32, grid = row_grid(rows, 8);
+    const T* xp = static_cast<const T*>(x);
+    T* yp = static_cast<T*>(y);
+    if (k <= 2) softmax_fwd_warp_kernel<T, 2><<<grid, 256, 0, st>>>(xp, yp, rows, cols, log_mode);
+    else if (k <= 4) softmax_fwd_warp_kernel<T, 4><<<grid, 256, 0, st>>>(xp, yp, rows, cols, log_mode);
+    else softmax_fwd_warp_kernel<T, 8><<<grid, 256, 0, st>>>(xp, yp, rows, cols, log_mode);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (cols <= 1024)
     softmax_fwd_kernel<T, 32><<<row_grid(rows, 8), 256, 0, st>>>(static_cast<const T*>(x), static_cast<T*>(y), rows,
                                                                 cols, log_mode);
@@ -304,6 +441,16 @@ int softmax_fwd_t(const void* x, void* y, long long rows, int cols, int log_mode
 template <typename T>
 int softmax_bwd_t(const void* dy, const void* y, void* dx, long long rows, int cols, int log_mode,
                   cudaStream_t st) {
+  if (warp_rows_ok(dy, y, dx, cols)) {
+    const int kk = (cols / 8 + 31) / 32, grid = row_grid(rows, 8);
+    const T* gp = static_cast<const T*>(dy);
+    const T* yp = static_cast<const T*>(y);
+    T* dp = static_cast<T*>(dx);
+    if (kk <= 2) softmax_bwd_warp_kernel<T, 2><<<grid, 256, 0, st>>>(gp, yp, dp, rows, cols, log_mode);
+    else if (kk <= 4) softmax_bwd_warp_kernel<T, 4><<<grid, 256, 0, st>>>(gp, yp, dp, rows, cols, log_mode);
+    else softmax_bwd_warp_kernel<T, 8><<<grid, 256, 0, st>>>(gp, yp, dp, rows, cols, log_mode);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (cols <= 1024)
     softmax_bwd_kernel<T, 32><<<row_grid(rows, 8), 256, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(y),
                                                                 static_cast<T*>(dx), rows, cols, log_mode);

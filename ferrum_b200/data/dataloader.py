@@ -161,3 +161,62 @@ class CollatedDataLoader:
 
     def len(self):
         return self.loader.len()
+
+
+class DevicePrefetcher:
+    """Wraps any iterable of batches (tensors or tuples / lists of tensors, ideally in pinned host memory) and hands
+    them out on the GPU one step ahead: while the caller computes on batch ``i``, batch ``i + 1`` is already being
+    copied on a side stream, so the host-to-device copy is off the critical path of the step.
+
+    The reference's loader fetches a batch synchronously when it is asked for it
+    (ferrum-data/src/dataloader.rs:144-165); on a GPU that serialises a PCIe copy with every step.
+    """
+
+    def __init__(self, batches, device=None):
+        self._it = iter(batches)
+        self._device = _as_device(device if device is not None else "cuda").to_torch()
+        self._stream = torch.cuda.Stream(device=self._device)
+        self._next = None
+        self._preload()
+
+    def _to_device(self, obj):
+        if isinstance(obj, Tensor):
+            return Tensor(obj._t.to(self._device, non_blocking=True))
+        if isinstance(obj, torch.Tensor):
+            return obj.to(self._device, non_blocking=True)
+        if isinstance(obj, (tuple, list)):
+            return type(obj)(self._to_device(o) for o in obj)
+        return obj
+
+    def _preload(self) -> None:
+        try:
+            batch = next(self._it)
+        except StopIteration:
+            self._next = None
+            return
+        with torch.cuda.stream(self._stream):
+            self._next = self._to_device(batch)
+
+    @staticmethod
+    def _record(obj, stream) -> None:
+        if isinstance(obj, Tensor):
+            obj = obj._t
+        if isinstance(obj, torch.Tensor):
+            if obj.is_cuda:
+                obj.record_stream(stream)
+        elif isinstance(obj, (tuple, list)):
+            for o in obj:
+                DevicePrefetcher._record(o, stream)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if self._next is None:
+            raise StopIteration
+        cur = torch.cuda.current_stream(self._device)
+        cur.wait_stream(self._stream)      # the copy of this batch is complete before the step reads it
+        batch = self._next
+        self._record(batch, cur)           # its memory is not reused while the step is still running
+        self._preload()                    # start copying the following batch
+        return batch

@@ -133,3 +133,17 @@ def test_profiler_collects_kernel_timings():
     assert all(v["total_ms"] >= 0 and v["calls"] >= 1 for v in rep.values())
     assert "fb_unary_fwd" in prof.table()
     assert y.shape == (512,)
+
+
+def test_device_prefetcher_delivers_batches_in_order():
+    import ferrum_b200 as fb
+
+    host = [(torch.full((1024, 64), float(i)).pin_memory(), torch.tensor([i])) for i in range(5)]
+    seen = []
+    for x, y in fb.data.DevicePrefetcher(iter(host), device=fb.Device.Cuda(0)):
+        assert x.is_cuda and y.is_cuda
+        seen.append((float(x.mean()), int(y)))
+    assert seen == [(float(i), i) for i in range(5)]
+    wrapped = [fb.Tensor(torch.ones(4) * i) for i in range(3)]
+    out = [t.to_vec()[0] for t in fb.data.DevicePrefetcher(iter(wrapped), device=fb.Device.Cuda(0))]
+    assert out == [0.0, 1.0, 2.0]
