@@ -27,6 +27,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--bf16", action="store_true", help="bf16 tensor-core GEMMs (default for embedding)")
+    ap.add_argument("--graph", action="store_true",
+                    help="ours, 1 GPU, mnist: record the step (zero_grad, forward, backward, Adam) in a CUDA graph and "
+                         "replay it (the batch fetch and the LR schedule stay outside)")
     a = ap.parse_args()
 
     import torch
@@ -108,9 +111,25 @@ def main():
                 yield xb.torch(), yb.torch()
 
     it = batches()
+    graphed = None
+    if a.graph:
+        if a.impl != "ours" or world > 1 or a.config != "mnist":
+            raise SystemExit("--graph: ours, one GPU, mnist (the embedding config draws a dropout mask per step)")
+
+        def train(xb, yb):
+            opt.zero_grad()
+            with fb.autocast(enabled=low):
+                loss = loss_fn(net(xb), yb)
+            loss.backward()
+            opt.step()
+            return loss
+
+        graphed = fb.cuda.GraphedStep(train, next(it), optimizer=opt)
 
     def step():
         xb, yb = next(it)
+        if graphed is not None:
+            return graphed(xb, yb)
         if a.impl == "ours":
             if sched is not None:
                 opt.set_learning_rate(sched.get_lr())
@@ -152,7 +171,8 @@ def main():
     if rank == 0:
         print(json.dumps({"config": a.config, "impl": a.impl, "n_gpus": world, "steps": a.steps,
                           "ms_per_step": ms / a.steps, "samples_per_s": a.steps * batch * world / (ms / 1e3),
-                          "dtype": "bf16" if low else "fp32", "final_loss": float(loss), "data": "synthetic"}))
+                          "dtype": "bf16" if low else "fp32", "final_loss": float(loss), "data": "synthetic",
+                          "cuda_graph": bool(a.graph)}))
     if engine is not None:
         engine.shutdown()
     if world > 1 and a.impl == "ours":

@@ -138,6 +138,7 @@ _CUDA_SIGS = {
     "fb_loss_bwd": (I, [P, P, P, P, LL, I, F, P]),
     # dropout / embedding / gather
     "fb_dropout_fwd": (I, [P, P, P, LL, F, U64, U64, I, P]),
+    "fb_dropout_fwd_dyn": (I, [P, P, P, LL, F, U64, U64, P, I, P]),
     "fb_dropout_bwd": (I, [P, P, P, LL, F, I, P]),
     "fb_embedding_fwd": (I, [P, P, P, LL, I, LL, LL, I, P, P]),
     "fb_embedding_meanpool_fwd": (I, [P, P, P, LL, I, I, LL, I, P]),
@@ -148,6 +149,9 @@ _CUDA_SIGS = {
     "fb_sgd_flat": (I, [P, P, P, P, LL, SgdH, P]),
     "fb_adam_multi": (I, [P, P, P, P, P, P, I, AdamH, P]),
     "fb_sgd_multi": (I, [P, P, P, P, P, I, SgdH, P]),
+    "fb_adam_multi_dyn": (I, [P, P, P, P, P, P, I, AdamH, P, P]),
+    "fb_sgd_multi_dyn": (I, [P, P, P, P, P, I, SgdH, P, P]),
+    "fb_optim_advance": (I, [P, F, F, P]),
     # amp
     "fb_unscale_check": (I, [P, P, I, F, P, P]),
     "fb_sumsq_multi": (I, [P, P, I, P, P]),

@@ -30,6 +30,8 @@
 // on expiry the block records {peer, epoch} in the status block, the kernel skips
 // the rest of its work and returns.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "../common/ptx.cuh"
@@ -84,6 +86,8 @@ struct ArArgs {
   float* m;  // this rank's moment / velocity storage for ITS shard (index 0 = first element of the shard)
   float* v;
   int publish_master;  // 1: new fp32 parameters go to every rank; 0: only the bf16 copy does (owner keeps fp32)
+  int streaming;       // local optimizer state moves with evict-first hints (ld/st.global.cs): it is touched once per
+                       // step and should not displace the operand tiles of the GEMMs this kernel runs beside
 };
 
 __device__ __forceinline__ float4 combine4(float4 a, float4 b, int op) {
@@ -182,8 +186,13 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
         if (i4 < n4) {
           p[u] = *(reinterpret_cast<const float4*>(c.arena[c.rank] + a.param_off) + lo4 + i4);
           if (FUSE == FB_FUSE_ADAM) {
-            m[u] = reinterpret_cast<const float4*>(a.m)[i4];
-            v[u] = reinterpret_cast<const float4*>(a.v)[i4];
+            if (a.streaming) {
+              m[u] = __ldcs(reinterpret_cast<const float4*>(a.m) + i4);
+              v[u] = __ldcs(reinterpret_cast<const float4*>(a.v) + i4);
+            } else {
+              m[u] = reinterpret_cast<const float4*>(a.m)[i4];
+              v[u] = reinterpret_cast<const float4*>(a.v)[i4];
+            }
           } else {
             m[u] = a.m != nullptr ? reinterpret_cast<const float4*>(a.m)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
           }
@@ -198,8 +207,13 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
           adam1(p[u].y, g[u].y, m[u].y, v[u].y, a.adam);
           adam1(p[u].z, g[u].z, m[u].z, v[u].z, a.adam);
           adam1(p[u].w, g[u].w, m[u].w, v[u].w, a.adam);
-          reinterpret_cast<float4*>(a.m)[i4] = m[u];
-          reinterpret_cast<float4*>(a.v)[i4] = v[u];
+          if (a.streaming) {
+            __stcs(reinterpret_cast<float4*>(a.m) + i4, m[u]);
+            __stcs(reinterpret_cast<float4*>(a.v) + i4, v[u]);
+          } else {
+            reinterpret_cast<float4*>(a.m)[i4] = m[u];
+            reinterpret_cast<float4*>(a.v)[i4] = v[u];
+          }
         } else {
           sgd1(p[u].x, g[u].x, m[u].x, a.sgd);
           sgd1(p[u].y, g[u].y, m[u].y, a.sgd);
@@ -424,6 +438,14 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
   a.m = m;
   a.v = v;
   a.publish_master = publish_master;
+  {
+    static int streaming = -1;
+    if (streaming < 0) {
+      const char* e = getenv("FERRUM_COMM_STREAMING");
+      streaming = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    a.streaming = streaming;
+  }
   switch (fuse) {
     case FB_FUSE_NONE: return launch_ar<FB_FUSE_NONE>(*ctx, a, use_mc, nblocks, nthreads, stream);
     case FB_FUSE_SGD: return launch_ar<FB_FUSE_SGD>(*ctx, a, use_mc, nblocks, nthreads, stream);

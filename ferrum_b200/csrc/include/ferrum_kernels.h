@@ -161,6 +161,9 @@ int fb_pool2d_bwd(const float* dy, const int* arg, float* dx, int B, int C, int 
 // ---- dropout / embedding / collate ---------------------------------------------
 int fb_dropout_fwd(const void* x, void* y, uint8_t* mask, long long n, float p, unsigned long long seed,
                    unsigned long long offset, int dtype, cudaStream_t stream);
+// Graph-capturable dropout: Philox offset = offset + *dev_counter; the counter advances on the stream after the launch.
+int fb_dropout_fwd_dyn(const void* x, void* y, uint8_t* mask, long long n, float p, unsigned long long seed,
+                       unsigned long long offset, unsigned long long* dev_counter, int dtype, cudaStream_t stream);
 int fb_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, long long n, float p, int dtype,
                    cudaStream_t stream);
 int fb_embedding_fwd(const float* weight, const long long* idx, void* out, long long n_idx, int dim,
@@ -193,6 +196,15 @@ int fb_adam_multi(float* const* p, const float* const* g, float* const* m, float
                   cudaStream_t stream);
 int fb_sgd_multi(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
                  const long long* sizes, int ntensors, fb_sgd_hparams h, cudaStream_t stream);
+// Graph-capturable forms: the step-dependent factors are device scalars dyn = {lr, bias_corr1, bias_corr2,
+// beta1^t, beta2^t, t} (initialise to {lr, 0, 0, 1, 1, 0}); fb_optim_advance moves them one step on the stream
+// before the update launches, so a captured step replays correctly.  SGD only reads dyn[0] (lr).
+int fb_optim_advance(float* dyn, float beta1, float beta2, cudaStream_t stream);
+int fb_adam_multi_dyn(float* const* p, const float* const* g, float* const* m, float* const* v,
+                      void* const* shadow, const long long* sizes, int ntensors, fb_adam_hparams h,
+                      const float* dyn, cudaStream_t stream);
+int fb_sgd_multi_dyn(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
+                     const long long* sizes, int ntensors, fb_sgd_hparams h, const float* dyn, cudaStream_t stream);
 
 // ---- AMP helpers -----------------------------------------------------------------
 int fb_unscale_check(float* const* g, const long long* sizes, int ntensors, float inv_scale, float* found_inf,

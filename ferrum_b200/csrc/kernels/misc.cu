@@ -70,7 +70,9 @@ __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { 
 template <typename T>
 __global__ void __launch_bounds__(256)
 dropout_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ mask, long long n, float p,
-                   unsigned long long seed, unsigned long long offset) {
+                   unsigned long long seed, unsigned long long offset,
+                   const unsigned long long* __restrict__ dev_offset) {
+  if (dev_offset != nullptr) offset += *dev_offset;  // advanced on the stream between calls: graph replays differ
   const float scale = 1.f / (1.f - p);
   const uint32_t thresh = static_cast<uint32_t>(fminf(fmaxf(p, 0.f), 1.f) * 65536.0f);  // keep when draw >= thresh
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -174,6 +176,10 @@ dropout_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ mask, T
     }
   }
   for (long long i = (n8 << 3) + tid; i < n; i += stride) stf(dx + i, mask[i] ? ldf(dy + i) * scale : 0.f);
+}
+
+__global__ void counter_add_kernel(unsigned long long* ctr, unsigned long long inc) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *ctr += inc;
 }
 
 // --------------------------------------------------------------- Embedding
@@ -574,12 +580,32 @@ extern "C" int fb_dropout_fwd(const void* x, void* y, uint8_t* mask, long long n
   const int g = grid1d((n + 7) / 8, 256);
   if (dtype == FB_DT_F32)
     dropout_fwd_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(y), mask, n,
-                                                    p, seed, offset);
+                                                    p, seed, offset, nullptr);
   else if (dtype == FB_DT_BF16)
-    dropout_fwd_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                            static_cast<__nv_bfloat16*>(y), mask, n, p, seed, offset);
+    dropout_fwd_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), mask, n, p, seed, offset, nullptr);
   else
     return -1;
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Graph-capturable form: the Philox offset is `offset + *dev_counter`, and the counter is advanced by one on the
+// stream after the launch, so every replay of a captured step draws a new mask.
+extern "C" int fb_dropout_fwd_dyn(const void* x, void* y, uint8_t* mask, long long n, float p,
+                                  unsigned long long seed, unsigned long long offset,
+                                  unsigned long long* dev_counter, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (p < 0.f || p >= 1.f || dev_counter == nullptr) return -1;
+  const int g = grid1d((n + 7) / 8, 256);
+  if (dtype == FB_DT_F32)
+    dropout_fwd_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<float*>(y), mask, n,
+                                                    p, seed, offset, dev_counter);
+  else if (dtype == FB_DT_BF16)
+    dropout_fwd_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), mask, n, p, seed, offset, dev_counter);
+  else
+    return -1;
+  counter_add_kernel<<<1, 32, 0, stream>>>(dev_counter, 1ull);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int fb_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, long long n, float p, int dtype,

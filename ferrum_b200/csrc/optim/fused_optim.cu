@@ -155,17 +155,36 @@ struct GradTable {
   int count;
 };
 
-__global__ void adam_multi_kernel(const AdamTable t, const fb_adam_hparams h) {
+// dyn (optional): device scalars {lr, bias_corr1, bias_corr2, beta1^t, beta2^t, t} kept current by
+// optim_advance_kernel, so that a captured CUDA graph replays with the right step-dependent factors.
+__global__ void adam_multi_kernel(const AdamTable t, fb_adam_hparams h, const float* __restrict__ dyn) {
+  if (dyn != nullptr) {
+    h.lr = dyn[0];
+    h.bias_corr1 = dyn[1];
+    h.bias_corr2 = dyn[2];
+  }
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int i = 0; i < t.count; ++i)
     adam_range(t.p[i], t.g[i], t.m[i], t.v[i], static_cast<__nv_bfloat16*>(t.sh[i]), t.n[i], h, tid, stride);
 }
-__global__ void sgd_multi_kernel(const SgdTable t, const fb_sgd_hparams h) {
+__global__ void sgd_multi_kernel(const SgdTable t, fb_sgd_hparams h, const float* __restrict__ dyn) {
+  if (dyn != nullptr) h.lr = dyn[0];
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int i = 0; i < t.count; ++i)
     sgd_range(t.p[i], t.g[i], t.buf[i], static_cast<__nv_bfloat16*>(t.sh[i]), t.n[i], h, tid, stride);
+}
+
+// One thread: t += 1, beta^t products and the two bias corrections (Adam) for the launches that follow.
+__global__ void optim_advance_kernel(float* dyn, float beta1, float beta2) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    dyn[3] *= beta1;
+    dyn[4] *= beta2;
+    dyn[1] = 1.f - dyn[3];
+    dyn[2] = 1.f - dyn[4];
+    dyn[5] += 1.f;
+  }
 }
 
 // ------------------------------------------------------------------- AMP
@@ -292,9 +311,30 @@ extern "C" int fb_sgd_flat(float* p, const float* g, float* buf, void* shadow, l
   return static_cast<int>(cudaGetLastError());
 }
 // The `multi` entry points take HOST arrays of device pointers (NULL gradient = skip the tensor).
+static int adam_multi_impl(float* const* p, const float* const* g, float* const* m, float* const* v,
+                           void* const* shadow, const long long* sizes, int ntensors, fb_adam_hparams h,
+                           const float* dyn, cudaStream_t stream);
 extern "C" int fb_adam_multi(float* const* p, const float* const* g, float* const* m, float* const* v,
                              void* const* shadow, const long long* sizes, int ntensors, fb_adam_hparams h,
                              cudaStream_t stream) {
+  return adam_multi_impl(p, g, m, v, shadow, sizes, ntensors, h, nullptr, stream);
+}
+// Graph-capturable form: lr and the bias corrections are read from the device scalars `dyn`
+// ({lr, bias_corr1, bias_corr2, beta1^t, beta2^t, t}; see fb_optim_advance).
+extern "C" int fb_adam_multi_dyn(float* const* p, const float* const* g, float* const* m, float* const* v,
+                                 void* const* shadow, const long long* sizes, int ntensors, fb_adam_hparams h,
+                                 const float* dyn, cudaStream_t stream) {
+  if (dyn == nullptr) return -1;
+  return adam_multi_impl(p, g, m, v, shadow, sizes, ntensors, h, dyn, stream);
+}
+extern "C" int fb_optim_advance(float* dyn, float beta1, float beta2, cudaStream_t stream) {
+  if (dyn == nullptr) return -1;
+  optim_advance_kernel<<<1, 32, 0, stream>>>(dyn, beta1, beta2);
+  return static_cast<int>(cudaGetLastError());
+}
+static int adam_multi_impl(float* const* p, const float* const* g, float* const* m, float* const* v,
+                           void* const* shadow, const long long* sizes, int ntensors, fb_adam_hparams h,
+                           const float* dyn, cudaStream_t stream) {
   AdamTable t;
   t.count = 0;
   for (int i = 0; i <= ntensors; ++i) {
@@ -305,14 +345,28 @@ extern "C" int fb_adam_multi(float* const* p, const float* const* g, float* cons
       t.n[k] = sizes[i];
     }
     if (t.count == kChunk || (i == ntensors && t.count > 0)) {
-      adam_multi_kernel<<<big_grid(), 256, 0, stream>>>(t, h);
+      adam_multi_kernel<<<big_grid(), 256, 0, stream>>>(t, h, dyn);
       t.count = 0;
     }
   }
   return static_cast<int>(cudaGetLastError());
 }
+static int sgd_multi_impl(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
+                          const long long* sizes, int ntensors, fb_sgd_hparams h, const float* dyn,
+                          cudaStream_t stream);
 extern "C" int fb_sgd_multi(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
                             const long long* sizes, int ntensors, fb_sgd_hparams h, cudaStream_t stream) {
+  return sgd_multi_impl(p, g, buf, shadow, sizes, ntensors, h, nullptr, stream);
+}
+extern "C" int fb_sgd_multi_dyn(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
+                                const long long* sizes, int ntensors, fb_sgd_hparams h, const float* dyn,
+                                cudaStream_t stream) {
+  if (dyn == nullptr) return -1;
+  return sgd_multi_impl(p, g, buf, shadow, sizes, ntensors, h, dyn, stream);
+}
+static int sgd_multi_impl(float* const* p, const float* const* g, float* const* buf, void* const* shadow,
+                          const long long* sizes, int ntensors, fb_sgd_hparams h, const float* dyn,
+                          cudaStream_t stream) {
   SgdTable t;
   t.count = 0;
   for (int i = 0; i <= ntensors; ++i) {
@@ -324,7 +378,7 @@ extern "C" int fb_sgd_multi(float* const* p, const float* const* g, float* const
       t.n[k] = sizes[i];
     }
     if (t.count == kChunk || (i == ntensors && t.count > 0)) {
-      sgd_multi_kernel<<<big_grid(), 256, 0, stream>>>(t, h);
+      sgd_multi_kernel<<<big_grid(), 256, 0, stream>>>(t, h, dyn);
       t.count = 0;
     }
   }

@@ -1045,14 +1045,32 @@ def elementwise_loss(pred: torch.Tensor, target: torch.Tensor, kind: str) -> tor
 _dropout_offset = 0
 
 
+_capturable_rng = {}  # device index -> uint64 counter tensor; non-empty while steps are recorded in CUDA graphs
+
+
+def set_capturable_rng(flag: bool) -> None:
+    """Draw dropout offsets from a device-side counter that advances on the stream, so a step recorded in a CUDA
+    graph draws a new mask at every replay (a host-side counter would be frozen into the graph)."""
+    if not flag:
+        _capturable_rng.clear()
+    elif torch.cuda.is_available() and torch.cuda.current_device() not in _capturable_rng:
+        _capturable_rng[torch.cuda.current_device()] = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+
 class _DropoutFn(Function):
     @staticmethod
     def forward(ctx, x, p, seed, offset):
         x2 = x.contiguous()
         y = torch.empty_like(x2)
         mask = torch.empty(x2.shape, device=x.device, dtype=torch.uint8)
-        _lib.check(_lib.cuda().fb_dropout_fwd(x2.data_ptr(), y.data_ptr(), mask.data_ptr(), x2.numel(), p, seed,
-                                              offset, _dt(x2), _stream()), "fb_dropout_fwd")
+        ctr = _capturable_rng.get(x.device.index)
+        if ctr is not None:
+            _lib.check(_lib.cuda().fb_dropout_fwd_dyn(x2.data_ptr(), y.data_ptr(), mask.data_ptr(), x2.numel(), p,
+                                                      seed, offset << 20, ctr.data_ptr(), _dt(x2), _stream()),
+                       "fb_dropout_fwd_dyn")
+        else:
+            _lib.check(_lib.cuda().fb_dropout_fwd(x2.data_ptr(), y.data_ptr(), mask.data_ptr(), x2.numel(), p, seed,
+                                                  offset, _dt(x2), _stream()), "fb_dropout_fwd")
         ctx.save_for_backward(mask)
         ctx.p = p
         return y

@@ -94,6 +94,7 @@ class Optimizer:
     def __init__(self, params):
         self.params = _collect(params)
         self._engine = None  # a DDP engine that applies the update inside its reduction kernel
+        self._dyn = None     # device scalars {lr, bias_corr1, bias_corr2, beta1^t, beta2^t, t} (capturable mode)
 
     # -- reference API
     def learning_rate(self) -> float:
@@ -101,6 +102,25 @@ class Optimizer:
 
     def set_learning_rate(self, lr: float) -> None:
         self.config.lr = float(lr)
+        if self._dyn is not None:
+            self._dyn[0:1].fill_(float(lr))  # picked up by the next launch or graph replay
+
+    def capturable(self, flag: bool = True) -> "Optimizer":
+        """Keep the step-dependent factors (learning rate, Adam's bias corrections) in device memory and advance
+        them with a kernel, so that a step captured in a CUDA graph replays with the right values.  The update
+        rule is unchanged; ``set_learning_rate`` keeps working between replays."""
+        if not flag:
+            self._dyn = None
+            return self
+        dev = next((p.device for p in self.params if p.is_cuda), None)
+        if dev is None:
+            raise ValueError("capturable mode needs parameters on a CUDA device")
+        t = int(getattr(self, "step_count", 0))
+        b1 = float(getattr(self.config, "beta1", 1.0))
+        b2 = float(getattr(self.config, "beta2", 1.0))
+        self._dyn = torch.tensor([self.config.lr, 1.0 - b1 ** t, 1.0 - b2 ** t, b1 ** t, b2 ** t, float(t)],
+                                 dtype=torch.float32, device=dev)
+        return self
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self._engine is not None:
@@ -182,9 +202,15 @@ class SGD(Optimizer):
             # buffers start at zero, so mu * 0 + g == g reproduces the reference's first step (sgd.rs:95-104)
             h = self.hparams()
             n = len(ps)
-            _lib.check(_lib.cuda().fb_sgd_multi(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(bs),
-                                                self._ptr_array(shs), (ctypes.c_longlong * n)(*ns), n, h,
-                                                torch.cuda.current_stream().cuda_stream), "fb_sgd_multi")
+            st = torch.cuda.current_stream().cuda_stream
+            if self._dyn is not None:
+                _lib.check(_lib.cuda().fb_sgd_multi_dyn(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(bs),
+                                                        self._ptr_array(shs), (ctypes.c_longlong * n)(*ns), n, h,
+                                                        self._dyn.data_ptr(), st), "fb_sgd_multi_dyn")
+            else:
+                _lib.check(_lib.cuda().fb_sgd_multi(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(bs),
+                                                    self._ptr_array(shs), (ctypes.c_longlong * n)(*ns), n, h, st),
+                           "fb_sgd_multi")
         with torch.no_grad():
             for i in cpu_idx:
                 p = self.params[i]
@@ -253,10 +279,19 @@ class Adam(Optimizer):
                 shs.append(self._shadow_ptr(p))
                 ns.append(p.numel())
             n = len(ps)
-            _lib.check(_lib.cuda().fb_adam_multi(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(ms),
+            st = torch.cuda.current_stream().cuda_stream
+            if self._dyn is not None:
+                lib = _lib.cuda()
+                _lib.check(lib.fb_optim_advance(self._dyn.data_ptr(), c.beta1, c.beta2, st), "fb_optim_advance")
+                _lib.check(lib.fb_adam_multi_dyn(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(ms),
                                                  self._ptr_array(vs), self._ptr_array(shs),
                                                  (ctypes.c_longlong * n)(*ns), n, self.hparams(t),
-                                                 torch.cuda.current_stream().cuda_stream), "fb_adam_multi")
+                                                 self._dyn.data_ptr(), st), "fb_adam_multi_dyn")
+            else:
+                _lib.check(_lib.cuda().fb_adam_multi(self._ptr_array(ps), self._ptr_array(gs), self._ptr_array(ms),
+                                                     self._ptr_array(vs), self._ptr_array(shs),
+                                                     (ctypes.c_longlong * n)(*ns), n, self.hparams(t), st),
+                           "fb_adam_multi")
         with torch.no_grad():
             for i in cpu_idx:
                 p = self.params[i]

@@ -268,7 +268,7 @@ class DistributedDataParallel(Module, GradSink):
         # per-shard optimizer state (owner only) — allocated lazily in _launch_bucket
         self._state_m = None
         self._state_v = None
-        self._comm_stream = torch.cuda.Stream(device=dev, priority=-1)
+        self._comm_stream = torch.cuda.Stream(device=dev, priority=int(os.environ.get("FERRUM_COMM_PRIORITY", "-1")))
         self._ready_event = torch.cuda.Event()
         self._done_event = torch.cuda.Event()
         # A reduction block (256 threads, no shared memory) fits on an SM beside a persistent GEMM CTA, so the

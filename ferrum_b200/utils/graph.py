@@ -1,0 +1,72 @@
+"""Whole-step CUDA graphs: capture ``zero_grad -> forward -> backward -> optimizer.step`` once, replay it with one
+launch per step.
+
+Small models are bound by launch latency, not by the GPU (a 784-256-10 MLP step is a dozen kernels of a few
+microseconds each); every launcher of this package enqueues on the current stream and takes its step-dependent
+scalars either by value (constant over replays) or, for the optimizers in capturable mode, from device memory, so a
+step can be recorded in a graph and replayed.  No tracing compiler is involved: the graph is the recorded launches.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..core import Tensor, _unwrap
+
+
+class GraphedStep:
+    """``step = GraphedStep(fn, example_inputs, optimizer)``; ``loss = step(x, y)``.
+
+    ``fn(*inputs)`` runs one full training step on device tensors and returns a tensor (typically the loss).  The
+    inputs of every later call are copied into the static buffers the graph reads; the returned tensor is the
+    graph's static output (read it, or copy it, before the next call).  ``optimizer`` is switched to capturable mode
+    (device-side learning rate and bias corrections); ``optimizer.set_learning_rate`` keeps working between calls.
+    Dropout draws its mask offset from a device-side counter from now on, so replays differ as they should.
+    Not for use with the distributed engine (its epochs are host-side).
+    """
+
+    def __init__(self, fn, example_inputs, optimizer=None, warmup: int = 3):
+        if not torch.cuda.is_available():
+            raise RuntimeError("GraphedStep needs a CUDA device")
+        self._fn, self._opt = fn, optimizer
+        if optimizer is not None:
+            if getattr(optimizer, "_engine", None) is not None:
+                raise ValueError("GraphedStep cannot capture a step whose optimizer is fused into the DDP engine")
+            optimizer.capturable(True)
+        from ..ops import functional as _F
+
+        _F.set_capturable_rng(True)  # dropout masks: device-side counter, a new mask at every replay
+        self._wrapped = [isinstance(t, Tensor) for t in example_inputs]
+        self._static_in = [_unwrap(t).detach().clone() for t in example_inputs]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # eager warm-up: lazy state, scratch buffers and attributes get created here
+            for _ in range(max(1, warmup)):
+                self._call_fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._steps_before = int(getattr(optimizer, "step_count", 0)) if optimizer is not None else 0
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            out = self._call_fn()
+        self._out_wrapped = isinstance(out, Tensor)
+        self._static_out = _unwrap(out)
+        if optimizer is not None and hasattr(optimizer, "step_count"):
+            optimizer.step_count = self._steps_before  # recording ran the Python of a step, not its kernels
+
+    def _call_fn(self):
+        args = [Tensor(t) if w else t for t, w in zip(self._static_in, self._wrapped)]
+        return self._fn(*args)
+
+    def __call__(self, *inputs):
+        if len(inputs) != len(self._static_in):
+            raise ValueError(f"expected {len(self._static_in)} inputs, got {len(inputs)}")
+        for s, t in zip(self._static_in, inputs):
+            s.copy_(_unwrap(t), non_blocking=True)
+        self._graph.replay()
+        if self._opt is not None and hasattr(self._opt, "step_count"):
+            self._opt.step_count += 1  # host-side bookkeeping (checkpoints); the kernels use the device counter
+        return Tensor(self._static_out) if self._out_wrapped else self._static_out
+
+    @property
+    def graph(self):
+        return self._graph

@@ -147,3 +147,75 @@ def test_device_prefetcher_delivers_batches_in_order():
     wrapped = [fb.Tensor(torch.ones(4) * i) for i in range(3)]
     out = [t.to_vec()[0] for t in fb.data.DevicePrefetcher(iter(wrapped), device=fb.Device.Cuda(0))]
     assert out == [0.0, 1.0, 2.0]
+
+
+@pytest.mark.parametrize("which", ["adam", "sgd"])
+def test_graphed_step_matches_eager_training(which):
+    """A step recorded in a CUDA graph (capturable optimizer: device-side lr and bias corrections) follows the
+    eager trajectory, including a learning-rate change between replays."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+
+    torch.manual_seed(0)
+    dev = fb.Device.Cuda(0)
+    ref = nn.Sequential(nn.Linear(32, 64, device=dev), nn.ReLU(), nn.LayerNorm([64], device=dev),
+                        nn.Linear(64, 10, device=dev), nn.LogSoftmax(-1))
+    cap = copy.deepcopy(ref)
+
+    def make(ps):
+        if which == "adam":
+            return optim.Adam(ps, optim.AdamConfig(lr=1e-2))
+        return optim.SGD(ps, optim.SGDConfig(lr=0.05, momentum=0.9))
+
+    opt_ref, opt_cap = make(ref.parameters()), make(cap.parameters())
+    xs = [torch.randn(48, 32, device="cuda") for _ in range(9)]
+    ys = [torch.randint(0, 10, (48,), device="cuda") for _ in range(9)]
+
+    def train_on(model, opt):
+        def fn(x, y):
+            opt.zero_grad()
+            loss = nn.nll_loss(model(x), y)
+            loss.backward()
+            opt.step()
+            return loss
+        return fn
+
+    eager, fn_cap = train_on(ref, opt_ref), train_on(cap, opt_cap)
+    graphed = fb.cuda.GraphedStep(fn_cap, (xs[0], ys[0]), optimizer=opt_cap, warmup=2)   # 2 eager steps on batch 0
+    for _ in range(2):
+        eager(xs[0], ys[0])
+    losses_e, losses_g = [], []
+    for i in range(1, 9):
+        if i == 5:
+            opt_ref.set_learning_rate(opt_ref.learning_rate() * 0.5)
+            opt_cap.set_learning_rate(opt_cap.learning_rate() * 0.5)
+        losses_e.append(float(eager(xs[i], ys[i])))
+        losses_g.append(float(graphed(xs[i], ys[i])))
+    assert opt_cap.step_count == opt_ref.step_count == 10
+    assert losses_g == pytest.approx(losses_e, rel=1e-4, abs=1e-5)
+    for a, b in zip(ref.torch_parameters(), cap.torch_parameters()):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+
+
+def test_graphed_step_draws_fresh_dropout_masks():
+    import ferrum_b200 as fb
+    from ferrum_b200.ops import functional as F
+
+    x = torch.ones(4096, device="cuda")
+    outs = []
+
+    def fn(t):
+        return F.dropout(t, 0.5, True, seed=7)
+
+    try:
+        g = fb.cuda.GraphedStep(fn, (x,), optimizer=None, warmup=1)
+        for _ in range(3):
+            outs.append(g(x).clone())
+    finally:
+        F.set_capturable_rng(False)
+    assert not torch.equal(outs[0], outs[1]) and not torch.equal(outs[1], outs[2])
+    for o in outs:
+        kept = (o != 0).float().mean().item()
+        assert 0.4 < kept < 0.6 and torch.all((o == 0) | (o == 2.0))
