@@ -69,6 +69,7 @@ struct Args2 {
   // Optional per-pair timing record (4 x 64-bit per pair, nanoseconds): MMA thread waiting for a drained
   // accumulator, MMA thread waiting for operands, one epilogue warp busy, whole kernel.  NULL = off.
   unsigned long long* prof;
+  int l2_prefetch;    // k-blocks of look-ahead of the TMA L2 prefetch (0 = off)
   int stream_stores;  // bf16 outputs leave with st.global.cs (evict-first) so they do not displace operand tiles in L2
 };
 
@@ -175,6 +176,38 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           } else {
             ptx::tma_load_2d_2cta(sb, &tma_b, bar, k0, n0);
           }
+          if (p.l2_prefetch > 0) {
+            // L2 prefetch of the k-block `l2_prefetch` positions further on (same tile, or the head of this
+            // pair's next tile): the ring covers ~2 us of latency, a first touch of a panel in DRAM costs more.
+            int pk = kb + p.l2_prefetch, pm0 = m0, pn0 = n0;
+            bool have = true;
+            if (pk >= num_kb) {
+              pk -= num_kb;
+              const int nt = t + num_pairs;
+              have = nt < num_tiles && pk < num_kb;
+              if (have) {
+                int nm, nn;
+                tile_coords2(nt, num_m, num_n, nm, nn);
+                pm0 = nm * 2 * kBM + static_cast<int>(rank) * kBM;
+                pn0 = nn * kBN + static_cast<int>(rank) * (kBN / 2);
+              }
+            }
+            if (have) {
+              const int pk0 = pk * kBK;
+              if (p.a_mn_major) {
+#pragma unroll
+                for (int c = 0; c < kBM / 64; ++c) ptx::tma_prefetch_2d(&tma_a, pm0 + c * 64, pk0);
+              } else {
+                ptx::tma_prefetch_2d(&tma_a, pk0, pm0);
+              }
+              if (p.b_mn_major) {
+#pragma unroll
+                for (int c = 0; c < (kBN / 2) / 64; ++c) ptx::tma_prefetch_2d(&tma_b, pn0 + c * 64, pk0);
+              } else {
+                ptx::tma_prefetch_2d(&tma_b, pk0, pn0);
+              }
+            }
+          }
           ++issued;
           if (++stage == kStages) {
             stage = 0;
@@ -279,9 +312,17 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
           if (p.bias != nullptr) {
+            if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias + col0) & 15) == 0) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+              for (int q = 0; q < 8; ++q) {  // eight 16-byte loads instead of 32 guarded scalar ones
+                const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + q);
+                v[4 * q] += b4.x; v[4 * q + 1] += b4.y; v[4 * q + 2] += b4.z; v[4 * q + 3] += b4.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
+            }
           }
           const bool full = (col0 + 32 <= p.N) && vec_ok;
           if (p.out2 != nullptr) {
@@ -500,6 +541,13 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
       stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     args.stream_stores = stream_default;
+    static int l2_prefetch = -1;
+    if (l2_prefetch < 0) {
+      const char* e = getenv("FERRUM_GEMM_L2_PREFETCH");
+      l2_prefetch = e != nullptr ? atoi(e) : 0;
+      if (l2_prefetch < 0 || l2_prefetch > 64) l2_prefetch = 0;
+    }
+    args.l2_prefetch = l2_prefetch;
   }
   args.prof = g_prof_buffer;
   int pairs = pairs_avail;
