@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true",
                     help="1 GPU: launch every kernel of the end-to-end step from Python instead of replaying the "
                          "step recorded in a CUDA graph")
+    ap.add_argument("--graph-ddp", action="store_true",
+                    help="multi-GPU: also replay the end-to-end step from a CUDA graph (engine in capturable mode)")
     ap.add_argument("--shard-master", action="store_true",
                     help="DDP: publish only bf16 weights to peers, fp32 master weights stay with the shard owner")
     return ap.parse_args()
@@ -198,11 +200,13 @@ def run_ours(args):
         """One GPU, no engine: the whole step (zero_grad, forward, backward, Adam) is recorded once in a CUDA graph
         and replayed, so the read-back of the loss at the end of a step does not expose ~70 Python-issued launches
         at the start of the next one.  Falls back to eager launches if the step cannot be captured."""
-        if engine is not None or args.no_graph:
+        if args.no_graph or (engine is not None and not args.graph_ddp):
             return
         try:
             graph_box[0] = fb.cuda.GraphedStep(train_step, (x_dev, y_dev), optimizer=opt)
         except Exception as exc:  # noqa: BLE001 - any capture failure means: run eagerly
+            if engine is not None:
+                raise  # ranks must not diverge between recorded and eager steps
             if rank == 0:
                 print(f"[bench] CUDA-graph capture unavailable ({type(exc).__name__}: {exc}); eager e2e",
                       file=sys.stderr)

@@ -86,6 +86,10 @@ struct ArArgs {
   float* m;  // this rank's moment / velocity storage for ITS shard (index 0 = first element of the shard)
   float* v;
   int publish_master;  // 1: new fp32 parameters go to every rank; 0: only the bf16 copy does (owner keeps fp32)
+  // Graph-capturable launches: the handshake epoch and the step-dependent optimizer factors come from device
+  // memory (advanced by tiny kernels on the same stream), not from the by-value arguments a graph would freeze.
+  const uint32_t* dev_epoch;  // NULL = use `epoch`
+  const float* dyn;           // NULL = use adam / sgd as given; else {lr, bias_corr1, bias_corr2, ...}
   int streaming;       // local optimizer state moves with evict-first hints (ld/st.global.cs): it is touched once per
                        // step and should not displace the operand tiles of the GEMMs this kernel runs beside
 };
@@ -122,7 +126,16 @@ __device__ __forceinline__ void sgd1(float& p, float g, float& vel, const fb_sgd
 // NVLink (microseconds), so throughput is set by the bytes outstanding per SM, not by the thread count.
 template <int FUSE, bool MC, int U, int W>
 __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, const ArArgs& a, int* s_fail) {
-  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 100)) return;
+  const uint32_t epoch = a.dev_epoch != nullptr ? *a.dev_epoch : a.epoch;
+  fb_adam_hparams adam = a.adam;
+  fb_sgd_hparams sgd = a.sgd;
+  if (a.dyn != nullptr) {
+    adam.lr = a.dyn[0];
+    adam.bias_corr1 = a.dyn[1];
+    adam.bias_corr2 = a.dyn[2];
+    sgd.lr = a.dyn[0];
+  }
+  if (!block_handshake(c, a.channel, vblock, epoch, s_fail, 100)) return;
 
   long long per = (a.n + c.world - 1) / c.world;
   per = (per + 3) & ~3LL;
@@ -203,10 +216,10 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
         const long long i4 = base + u * stride;
         if (i4 >= n4) continue;
         if (FUSE == FB_FUSE_ADAM) {
-          adam1(p[u].x, g[u].x, m[u].x, v[u].x, a.adam);
-          adam1(p[u].y, g[u].y, m[u].y, v[u].y, a.adam);
-          adam1(p[u].z, g[u].z, m[u].z, v[u].z, a.adam);
-          adam1(p[u].w, g[u].w, m[u].w, v[u].w, a.adam);
+          adam1(p[u].x, g[u].x, m[u].x, v[u].x, adam);
+          adam1(p[u].y, g[u].y, m[u].y, v[u].y, adam);
+          adam1(p[u].z, g[u].z, m[u].z, v[u].z, adam);
+          adam1(p[u].w, g[u].w, m[u].w, v[u].w, adam);
           if (a.streaming) {
             __stcs(reinterpret_cast<float4*>(a.m) + i4, m[u]);
             __stcs(reinterpret_cast<float4*>(a.v) + i4, v[u]);
@@ -215,10 +228,10 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
             reinterpret_cast<float4*>(a.v)[i4] = v[u];
           }
         } else {
-          sgd1(p[u].x, g[u].x, m[u].x, a.sgd);
-          sgd1(p[u].y, g[u].y, m[u].y, a.sgd);
-          sgd1(p[u].z, g[u].z, m[u].z, a.sgd);
-          sgd1(p[u].w, g[u].w, m[u].w, a.sgd);
+          sgd1(p[u].x, g[u].x, m[u].x, sgd);
+          sgd1(p[u].y, g[u].y, m[u].y, sgd);
+          sgd1(p[u].z, g[u].z, m[u].z, sgd);
+          sgd1(p[u].w, g[u].w, m[u].w, sgd);
           if (a.m != nullptr) reinterpret_cast<float4*>(a.m)[i4] = m[u];
         }
         uint2 sh;
@@ -245,7 +258,7 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
       }
     }
   }
-  block_handshake(c, a.channel, vblock, a.epoch + 1, s_fail, 101);
+  block_handshake(c, a.channel, vblock, epoch + 1, s_fail, 101);
 }
 
 template <int FUSE, bool MC, int U, int W>
@@ -390,6 +403,10 @@ bool ctx_ok(const fb_dist_ctx* c) {
   return c != nullptr && c->world >= 1 && c->world <= FB_MAX_RANKS && c->rank >= 0 && c->rank < c->world;
 }
 
+__global__ void epoch_advance_kernel(unsigned* ctr, unsigned inc) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *ctr += inc;
+}
+
 template <int FUSE>
 int launch_ar(const fb_dist_ctx& c, const ArArgs& a, int use_mc, int nblocks, int nthreads, cudaStream_t st) {
   // bytes in flight per thread = U * world * 16 (peer loads) = 128: deeper unrolling for small worlds
@@ -415,11 +432,11 @@ extern "C" int fb_dist_query_channels() { return FB_FLAG_CHANNELS; }
 
 // Fused all-reduce of one gradient bucket.  `epoch` and `epoch + 1` are consumed on `channel`.
 // fuse: FB_FUSE_NONE (in-place all-reduce of the region at grad_off), FB_FUSE_SGD, FB_FUSE_ADAM.
-extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
-                                 long long grad_off, long long param_off, long long shadow_off, long long n,
-                                 int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
-                                 float* m, float* v, int publish_master, int nblocks, int nthreads,
-                                 cudaStream_t stream) {
+static int allreduce_impl(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
+                          long long grad_off, long long param_off, long long shadow_off, long long n, int op,
+                          float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd, float* m, float* v,
+                          int publish_master, int nblocks, int nthreads, const unsigned* dev_epoch, const float* dyn,
+                          cudaStream_t stream) {
   if (!ctx_ok(ctx) || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || nthreads < 32 ||
       nthreads > 256 || channel < 0 || channel >= FB_FLAG_CHANNELS)
     return -1;
@@ -438,6 +455,8 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
   a.m = m;
   a.v = v;
   a.publish_master = publish_master;
+  a.dev_epoch = dev_epoch;
+  a.dyn = dyn;
   {
     static int streaming = -1;
     if (streaming < 0) {
@@ -454,6 +473,30 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
       return launch_ar<FB_FUSE_ADAM>(*ctx, a, use_mc, nblocks, nthreads, stream);
     default: return -1;
   }
+}
+
+extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
+                                 long long grad_off, long long param_off, long long shadow_off, long long n,
+                                 int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
+                                 float* m, float* v, int publish_master, int nblocks, int nthreads,
+                                 cudaStream_t stream) {
+  return allreduce_impl(ctx, fuse, use_mc, channel, epoch, grad_off, param_off, shadow_off, n, op, scale, adam, sgd, m,
+                        v, publish_master, nblocks, nthreads, nullptr, nullptr, stream);
+}
+
+// Graph-capturable form: the handshake epoch is read from *dev_epoch (every rank keeps its own counter; they move
+// in lockstep) and advanced by 2 on the stream after the launch; lr / bias corrections come from `dyn` when given.
+extern "C" int fb_dist_allreduce_dyn(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned* dev_epoch,
+                                     long long grad_off, long long param_off, long long shadow_off, long long n,
+                                     int op, float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
+                                     float* m, float* v, int publish_master, int nblocks, int nthreads,
+                                     const float* dyn, cudaStream_t stream) {
+  if (dev_epoch == nullptr) return -1;
+  const int rc = allreduce_impl(ctx, fuse, use_mc, channel, 0u, grad_off, param_off, shadow_off, n, op, scale, adam,
+                                sgd, m, v, publish_master, nblocks, nthreads, dev_epoch, dyn, stream);
+  if (rc != 0) return rc;
+  epoch_advance_kernel<<<1, 32, 0, stream>>>(dev_epoch, 2u);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // Same computation with all `world` ranks emulated on the current GPU in one cooperative launch.

@@ -109,6 +109,9 @@ class DistributedDataParallel(Module, GradSink):
         self._find_unused = False
         self._built = False
         self._opt = None
+        self._capturable = False
+        self._dev_epoch = None        # uint32 device counter of the bucket kernels' handshake epochs (capturable mode)
+        self._advanced = False        # the optimizer's device scalars were advanced in this step
         self._shard_master = os.environ.get("FERRUM_SHARD_MASTER", "0") == "1"
         self._master_stale = False
         self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "128"))
@@ -171,6 +174,18 @@ class DistributedDataParallel(Module, GradSink):
             _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 6, 2, e, 0, self._off_param + bk.start * 4, 0,
                                                       per * 4, 0, 1.0, 32, st), "fb_dist_collective")
         self._master_stale = False
+
+    def capturable(self, flag: bool = True) -> "DistributedDataParallel":
+        """Make the step recordable in a CUDA graph: the handshake epochs of the bucket kernels and the optimizer's
+        step-dependent factors are then read from device memory and advanced by kernels on the communication stream
+        (a graph would freeze the by-value arguments).  Needs a fused optimizer in capturable mode.  One-way: after
+        the switch every step, recorded or not, uses the device-side counters."""
+        if flag and self._opt is None:
+            raise CommunicationError("capturable() needs fuse_optimizer() first")
+        self._capturable = bool(flag)
+        if flag and self._opt._dyn is None:
+            self._opt.capturable(True)
+        return self
 
     def fuse_optimizer(self, optimizer) -> "DistributedDataParallel":
         """Apply ``optimizer``'s update inside the bucket reduction kernels (SGD or Adam)."""
@@ -314,6 +329,7 @@ class DistributedDataParallel(Module, GradSink):
         self._pending = [set(b.param_indices) for b in self.buckets]
         self._launched = [False] * len(self.buckets)
         self._written = [False] * len(self._params)
+        self._advanced = False
         self._sync_enabled = True
         for b in self.buckets:
             b.ready = False
@@ -366,11 +382,27 @@ class DistributedDataParallel(Module, GradSink):
                 raise CommunicationError(f"cannot fuse optimizer of type {type(opt).__name__}")
         e = a.next_epoch(2)
         use_mc = 1 if a.has_multicast() else 0
-        rc = lib.fb_dist_allreduce(a.ctx, fuse, use_mc, 2, e, self._off_grad + bk.start * 4,
-                                   self._off_param + bk.start * 4, self._off_shadow + bk.start * 2, bk.length,
-                                   4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr,
-                                   0 if (self._shard_master and fuse) else 1, self._comm_blocks,
-                                   self._comm_threads, self._comm_stream.cuda_stream)
+        if self._capturable and fuse:
+            if self._dev_epoch is None:  # continue the host-side sequence on the device
+                self._dev_epoch = torch.tensor([e], dtype=torch.int32, device=self._flat_params.device)
+            dyn = opt._dyn
+            if not self._advanced:
+                self._advanced = True
+                if fuse == 2:  # Adam: one advance of beta^t / bias corrections per step, before the first bucket
+                    _lib.check(lib.fb_optim_advance(dyn.data_ptr(), opt.config.beta1, opt.config.beta2,
+                                                    self._comm_stream.cuda_stream), "fb_optim_advance")
+            rc = lib.fb_dist_allreduce_dyn(a.ctx, fuse, use_mc, 2, self._dev_epoch.data_ptr(),
+                                           self._off_grad + bk.start * 4, self._off_param + bk.start * 4,
+                                           self._off_shadow + bk.start * 2, bk.length, 4, 1.0 / world, adam_h, sgd_h,
+                                           m_ptr, v_ptr, 0 if (self._shard_master and fuse) else 1,
+                                           self._comm_blocks, self._comm_threads, dyn.data_ptr(),
+                                           self._comm_stream.cuda_stream)
+        else:
+            rc = lib.fb_dist_allreduce(a.ctx, fuse, use_mc, 2, e, self._off_grad + bk.start * 4,
+                                       self._off_param + bk.start * 4, self._off_shadow + bk.start * 2, bk.length,
+                                       4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr,
+                                       0 if (self._shard_master and fuse) else 1, self._comm_blocks,
+                                       self._comm_threads, self._comm_stream.cuda_stream)
         if self._shard_master and fuse:
             self._master_stale = True
         _lib.check(rc, "fb_dist_allreduce")

@@ -21,7 +21,8 @@ class GraphedStep:
     graph's static output (read it, or copy it, before the next call).  ``optimizer`` is switched to capturable mode
     (device-side learning rate and bias corrections); ``optimizer.set_learning_rate`` keeps working between calls.
     Dropout draws its mask offset from a device-side counter from now on, so replays differ as they should.
-    Not for use with the distributed engine (its epochs are host-side).
+    With the distributed engine (optimizer fused into the bucket reduction) the engine is switched to capturable
+    mode too: handshake epochs come from a device counter, and every rank must record / replay the same steps.
     """
 
     def __init__(self, fn, example_inputs, optimizer=None, warmup: int = 3):
@@ -29,9 +30,10 @@ class GraphedStep:
             raise RuntimeError("GraphedStep needs a CUDA device")
         self._fn, self._opt = fn, optimizer
         if optimizer is not None:
-            if getattr(optimizer, "_engine", None) is not None:
-                raise ValueError("GraphedStep cannot capture a step whose optimizer is fused into the DDP engine")
             optimizer.capturable(True)
+            engine = getattr(optimizer, "_engine", None)
+            if engine is not None:  # fused into the distributed engine: its epochs move to the device as well
+                engine.capturable(True)
         from ..ops import functional as _F
 
         _F.set_capturable_rng(True)  # dropout masks: device-side counter, a new mask at every replay

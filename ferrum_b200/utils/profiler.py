@@ -1,4 +1,4 @@
-"""Tracing and metrics (the reference has none: SURVEY of ferrum shows only ``name()`` strings and a simulated
+"""Tracing and metrics (the reference has none: a search of its sources shows only ``name()`` strings and a simulated
 ``CudaEvent::elapsed_time``).
 
 ``profile()``    context manager that times every native kernel launcher with CUDA events on the launching stream

@@ -119,6 +119,30 @@ def main(out_dir):
     pg.all_gather(allp, flat)
     check("bf16 ddp replicas identical", all(torch.equal(allp[0], a) for a in allp))
     ddp.shutdown()
+
+    # ---- the fused DDP step recorded in a CUDA graph (engine in capturable mode: device-side epochs and Adam
+    #      factors): 2 eager warm-up steps + 3 replays must equal the 5-step single-process reference above
+    model = make_model()
+    opt = fb.optim.Adam(model.parameters(), fb.optim.AdamConfig(lr=1e-2, weight_decay=0.01))
+    ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.005)
+    ddp.fuse_optimizer(opt)
+
+    def graph_step(xb, yb):
+        opt.zero_grad()
+        loss = fb.nn.cross_entropy(ddp(xb), yb)
+        loss.backward()
+        opt.step()
+        return loss
+
+    graphed = fb.cuda.GraphedStep(graph_step, (xs, ys), optimizer=opt, warmup=2)
+    for _ in range(3):
+        graphed(xs, ys)
+    torch.cuda.synchronize()
+    check(f"graphed ddp step count {opt.step_count}", opt.step_count == 5)
+    for i, (p, q) in enumerate(zip(model.torch_parameters(), ref.torch_parameters())):
+        check(f"graphed ddp param {i} (max err {(p - q).abs().max().item():.2e})",
+              torch.allclose(p, q, atol=5e-5, rtol=1e-3))
+    ddp.shutdown()
     fb.utils.runtime.check_status()
     d.destroy_process_group()
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
