@@ -88,14 +88,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
-// Ask the TMA unit to bring a tile into L2 only (no shared-memory destination, nothing to wait for): issued a few
-// k-blocks ahead of the shared-memory ring, it takes DRAM latency off the loads that follow.
-__device__ __forceinline__ void tma_prefetch_2d(const void* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y)
-               : "memory");
-}
 // Untiled bulk copy global -> shared (no tensor map): both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(

@@ -69,7 +69,6 @@ struct Args2 {
   // Optional per-pair timing record (4 x 64-bit per pair, nanoseconds): MMA thread waiting for a drained
   // accumulator, MMA thread waiting for operands, one epilogue warp busy, whole kernel.  NULL = off.
   unsigned long long* prof;
-  int l2_prefetch;    // k-blocks of look-ahead of the TMA L2 prefetch (0 = off)
   int stream_stores;  // bf16 outputs leave with st.global.cs (evict-first) so they do not displace operand tiles in L2
 };
 
@@ -176,38 +175,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           } else {
             ptx::tma_load_2d_2cta(sb, &tma_b, bar, k0, n0);
           }
-          if (p.l2_prefetch > 0) {
-            // L2 prefetch of the k-block `l2_prefetch` positions further on (same tile, or the head of this
-            // pair's next tile): the ring covers ~2 us of latency, a first touch of a panel in DRAM costs more.
-            int pk = kb + p.l2_prefetch, pm0 = m0, pn0 = n0;
-            bool have = true;
-            if (pk >= num_kb) {
-              pk -= num_kb;
-              const int nt = t + num_pairs;
-              have = nt < num_tiles && pk < num_kb;
-              if (have) {
-                int nm, nn;
-                tile_coords2(nt, num_m, num_n, nm, nn);
-                pm0 = nm * 2 * kBM + static_cast<int>(rank) * kBM;
-                pn0 = nn * kBN + static_cast<int>(rank) * (kBN / 2);
-              }
-            }
-            if (have) {
-              const int pk0 = pk * kBK;
-              if (p.a_mn_major) {
-#pragma unroll
-                for (int c = 0; c < kBM / 64; ++c) ptx::tma_prefetch_2d(&tma_a, pm0 + c * 64, pk0);
-              } else {
-                ptx::tma_prefetch_2d(&tma_a, pk0, pm0);
-              }
-              if (p.b_mn_major) {
-#pragma unroll
-                for (int c = 0; c < (kBN / 2) / 64; ++c) ptx::tma_prefetch_2d(&tma_b, pn0 + c * 64, pk0);
-              } else {
-                ptx::tma_prefetch_2d(&tma_b, pk0, pn0);
-              }
-            }
-          }
+          // (A TMA prefetch into L2 a few k-blocks ahead of the ring was measured and removed: the prefetches
+          // queue in front of the real loads, operand waits grew from 32 us to 117 us, 1534 -> 1082 TFLOP/s.)
           ++issued;
           if (++stage == kStages) {
             stage = 0;
@@ -541,13 +510,6 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
       stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
     }
     args.stream_stores = stream_default;
-    static int l2_prefetch = -1;
-    if (l2_prefetch < 0) {
-      const char* e = getenv("FERRUM_GEMM_L2_PREFETCH");
-      l2_prefetch = e != nullptr ? atoi(e) : 0;
-      if (l2_prefetch < 0 || l2_prefetch > 64) l2_prefetch = 0;
-    }
-    args.l2_prefetch = l2_prefetch;
   }
   args.prof = g_prof_buffer;
   int pairs = pairs_avail;
