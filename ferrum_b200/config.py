@@ -5,11 +5,13 @@ GEMMs on the bf16 tensor cores with fp32 accumulation and fp32 master weights;
 that is opt-in so that parity runs keep exact fp32 arithmetic:
 
 * ``matmul_precision("fp32")`` (default) — fp32 SIMT GEMM, bit-for-bit fp32 math.
+* ``matmul_precision("tf32")`` — tensors stay fp32 but GEMMs run on the tensor cores as TF32 (tcgen05 kind::tf32:
+  10-bit mantissa operands, fp32 accumulation), several times the SIMT rate at ~1e-3 relative error.
 * ``matmul_precision("bf16")`` or ``with autocast():`` — tcgen05 GEMMs on bf16
   operands; activations flow in bf16, normalisation / softmax / loss statistics
   stay in fp32 inside the kernels.
 
-Environment overrides: ``FERRUM_MATMUL_PRECISION`` (``fp32`` | ``bf16``).
+Environment overrides: ``FERRUM_MATMUL_PRECISION`` (``fp32`` | ``tf32`` | ``bf16``).
 """
 from __future__ import annotations
 
@@ -24,12 +26,12 @@ _default_precision = os.environ.get("FERRUM_MATMUL_PRECISION", "fp32").lower()
 
 
 def matmul_precision(value: str | None = None) -> str:
-    """Get or set the default GEMM precision (``"fp32"`` or ``"bf16"``)."""
+    """Get or set the default GEMM precision (``"fp32"``, ``"tf32"`` or ``"bf16"``)."""
     global _default_precision
     if value is not None:
         value = value.lower()
-        if value not in ("fp32", "bf16"):
-            raise ValueError("matmul precision must be 'fp32' or 'bf16'")
+        if value not in ("fp32", "tf32", "bf16"):
+            raise ValueError("matmul precision must be 'fp32', 'tf32' or 'bf16'")
         _default_precision = value
     return _default_precision
 
@@ -44,6 +46,11 @@ def compute_dtype() -> torch.dtype:
 
 def low_precision_active() -> bool:
     return compute_dtype() == torch.bfloat16
+
+
+def tf32_active() -> bool:
+    """fp32 tensors, TF32 tensor-core GEMMs (only when no autocast block overrides the default)."""
+    return _default_precision == "tf32" and not getattr(_state, "autocast", None)
 
 
 @contextlib.contextmanager

@@ -39,15 +39,23 @@ namespace fb {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kBK = 64;      // 64 bf16 = one 128-byte swizzle row
-constexpr int kUmmaK = 16;   // K extent of one tcgen05.mma for 16-bit inputs
+// One 128-byte swizzle row of K per k-block and 32 bytes of K per tcgen05.mma, whatever the element type:
+// bf16 (kind::f16): 64 / 16 elements; fp32 read as tf32 (kind::tf32): 32 / 8 elements.
+constexpr int kRowBytes = 128;
+template <bool kTf32>
+struct El {
+  static constexpr int kBytes = kTf32 ? 4 : 2;
+  static constexpr int kBK = kRowBytes / kBytes;   // K elements per k-block
+  static constexpr int kUmmaK = 32 / kBytes;       // K elements per MMA
+  static constexpr int kMnChunk = kRowBytes / kBytes;  // MN elements per 128-byte row of an MN-major operand
+};
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;  // m-blocks per rasterisation group (L2 reuse)
 
 template <int BN>
 struct Cfg {
-  static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kBarrierBytes = 256;
@@ -84,11 +92,12 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gsize;
 }
 
-template <int BN, bool kBatched>
+template <int BN, bool kBatched, bool kTf32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmArgs p) {
   using C = Cfg<BN>;
+  constexpr int kBK = El<kTf32>::kBK, kUmmaK = El<kTf32>::kUmmaK, kMnChunk = El<kTf32>::kMnChunk;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,30 +167,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if constexpr (kBatched) {
             if (p.a_mn_major) {
 #pragma unroll
-              for (int c = 0; c < kBM / 64; ++c)
-                ptx::tma_load_4d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0, bz, bw);
+              for (int c = 0; c < kBM / kMnChunk; ++c)
+                ptx::tma_load_4d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * kMnChunk, k0, bz, bw);
             } else {
               ptx::tma_load_4d(sa, &tma_a, &full_bar[stage], k0, m0, bz, bw);
             }
             if (p.b_mn_major) {
 #pragma unroll
-              for (int c = 0; c < BN / 64; ++c)
-                ptx::tma_load_4d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0, bz, bw);
+              for (int c = 0; c < BN / kMnChunk; ++c)
+                ptx::tma_load_4d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * kMnChunk, k0, bz, bw);
             } else {
               ptx::tma_load_4d(sb, &tma_b, &full_bar[stage], k0, n0, bz, bw);
             }
           } else {
             if (p.a_mn_major) {
 #pragma unroll
-              for (int c = 0; c < kBM / 64; ++c)
-                ptx::tma_load_2d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * 64, k0);
+              for (int c = 0; c < kBM / kMnChunk; ++c)
+                ptx::tma_load_2d(sa + c * (kBK * 128), &tma_a, &full_bar[stage], m0 + c * kMnChunk, k0);
             } else {
               ptx::tma_load_2d(sa, &tma_a, &full_bar[stage], k0, m0);
             }
             if (p.b_mn_major) {
 #pragma unroll
-              for (int c = 0; c < BN / 64; ++c)
-                ptx::tma_load_2d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * 64, k0);
+              for (int c = 0; c < BN / kMnChunk; ++c)
+                ptx::tma_load_2d(sb + c * (kBK * 128), &tma_b, &full_bar[stage], n0 + c * kMnChunk, k0);
             } else {
               ptx::tma_load_2d(sb, &tma_b, &full_bar[stage], k0, n0);
             }
@@ -211,11 +220,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else if (warp == 1) {
     // --------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = ptx::make_idesc(1u, kBM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = ptx::make_idesc(kTf32 ? 2u : 1u, kBM, BN, p.a_mn_major, p.b_mn_major);
       const uint32_t a_lbo = p.a_mn_major ? kBK * 128 : 16;
       const uint32_t b_lbo = p.b_mn_major ? kBK * 128 : 16;
-      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : kUmmaK * 2;
-      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : 32;  // MN-major: kUmmaK rows of 128 B; K-major: 32 B
+      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : 32;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -241,7 +250,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (kTf32)
+              ptx::umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(&empty_bar[stage]);  // frees the smem slot when the MMAs retire
           if (++stage == C::kStages) {
@@ -414,17 +426,19 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows,
-// row pitch `ld` elements, box = 64 x box_outer, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+// 2-D tensor map of bf16 (elem_bytes 2) or fp32 (4) data: `inner` contiguous elements per row, `outer` rows,
+// row pitch `ld` elements, box = one 128-byte row segment x box_outer, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer,
+              int elem_bytes = 2) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return false;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -465,13 +479,13 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool kBatched>
+template <int BN, bool kBatched, bool kTf32 = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kBatched>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kBatched, kTf32>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -481,7 +495,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, i
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_bf16_kernel<BN, kBatched><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
+  gemm_bf16_kernel<BN, kBatched, kTf32><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -581,4 +595,43 @@ extern "C" int fb_gemm_bf16_batched(const void* a, const void* b, void* out, int
   args.sc_inner = sc_inner;
   args.alpha = alpha;
   return small_n ? launch<128, true>(ma, mb, args, 0, stream) : launch<256, true>(ma, mb, args, 0, stream);
+}
+
+// fp32 operands multiplied on the tensor cores as TF32 (tcgen05.mma kind::tf32: 10-bit mantissa inputs, fp32
+// accumulate) with an fp32 result: out[M,N] = act(A * B^T + bias) (+= out when beta).  Same operand layouts as
+// fb_gemm_bf16 (K-major or MN-major per operand); lda / ldb in elements, multiples of 4.
+extern "C" int fb_gemm_tf32(const float* a, const float* b, float* out, const float* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act,
+                            int beta, int max_ctas, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const bool small_n = N <= 128;
+  const int bn = small_n ? 128 : 256;
+  constexpr int kChunk = El<true>::kMnChunk;
+  CUtensorMap ma, mb;
+  bool ok = a_mn_major ? make_map(&ma, a, M, K, lda, kChunk, 4) : make_map(&ma, a, K, M, lda, kBM, 4);
+  if (!ok) return -2;
+  ok = b_mn_major ? make_map(&mb, b, N, K, ldb, kChunk, 4) : make_map(&mb, b, K, N, ldb, bn, 4);
+  if (!ok) return -2;
+  GemmArgs args;
+  args.out = out;
+  args.out2 = nullptr;
+  args.bias = bias;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = 0;
+  args.act = act;
+  args.beta = beta;
+  args.status = status;
+  args.timeout_ns = 2000000000ull;
+  args.batch_inner = 1;
+  args.batch_total = 1;
+  args.sc_outer = args.sc_inner = 0;
+  args.alpha = 1.f;
+  return small_n ? launch<128, false, true>(ma, mb, args, max_ctas, stream)
+                 : launch<256, false, true>(ma, mb, args, max_ctas, stream);
 }

@@ -50,6 +50,10 @@ int fb_gemm_bf16_supported(const void* a, const void* b, long long lda, long lon
 int fb_gemm_bf16(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
                  long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_bf16, int act,
                  int beta, int max_ctas, int32_t* status, cudaStream_t stream);
+// fp32 operands on the tensor cores as TF32 (tcgen05.mma kind::tf32), fp32 result; lda / ldb multiples of 4.
+int fb_gemm_tf32(const float* a, const float* b, float* out, const float* bias, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act, int beta, int max_ctas,
+                 int32_t* status, cudaStream_t stream);
 // CTA-pair variant (tcgen05 cta_group::2; 256 x 256 tiles on two SMs, 256 x 128 for small outputs); same
 // arguments.  Returns -3 where clusters of two CTAs cannot be scheduled.  fb_gemm_bf16_2cta_pairs() = resident pairs.
 int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,

@@ -465,7 +465,12 @@ def _gemm_nt(a: torch.Tensor, b_nt: torch.Tensor, bias=None, act=None, low: bool
             out.copy_(res)
             return out
         return raw_cast(res, out_dtype or torch.bfloat16)
-    res = _gemm.gemm_f32(_f32(a), _f32(b_nt), bias=bias, act=act, out=out, accumulate=accumulate)
+    af, bf = _f32(a), _f32(b_nt)
+    if (config.tf32_active() and _gemm.tf32_operand_ok(af) and _gemm.tf32_operand_ok(bf)
+            and (out is None or (out.dtype == torch.float32 and out.stride(-1) == 1))
+            and (bias is None or bias.dtype == torch.float32)):
+        return _gemm.gemm_tf32(af, bf, bias=bias, act=act, out=out, accumulate=accumulate)
+    res = _gemm.gemm_f32(af, bf, bias=bias, act=act, out=out, accumulate=accumulate)
     return res
 
 

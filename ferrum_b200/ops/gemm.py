@@ -101,6 +101,39 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     return out
 
 
+def tf32_operand_ok(t: torch.Tensor) -> bool:
+    """True when a 2-D fp32 tensor can be described by a TMA map (either major): 16-byte aligned base and pitch."""
+    if t.dtype != torch.float32 or t.dim() != 2 or t.data_ptr() % 16:
+        return False
+    s0, s1 = t.stride()
+    if s1 == 1:
+        return s0 % 4 == 0 and s0 >= t.shape[1]
+    if s0 == 1:
+        return s1 % 4 == 0 and s1 >= t.shape[0]
+    return False
+
+
+def gemm_tf32(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
+              out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``out[M,N] = act(a[M,K] @ b[N,K]^T + bias)`` with fp32 tensors on the tensor cores (TF32 operands, fp32
+    accumulation and output).  Same layout rules as :func:`gemm_bf16`."""
+    assert a.is_cuda and a.dim() == 2 and b.dim() == 2 and a.dtype == torch.float32 and b.dtype == torch.float32
+    M, K = a.shape
+    N, Kb = b.shape
+    assert K == Kb, f"inner dimensions differ: {a.shape} x {b.shape}^T"
+    a_mn, lda = _major(a)
+    b_mn, ldb = _major(b)
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.float32)
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (M, N)
+    rc = _lib.cuda().fb_gemm_tf32(a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                  bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, out.stride(0),
+                                  a_mn, b_mn, ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(),
+                                  _stream())
+    _lib.check(rc, "fb_gemm_tf32")
+    return out
+
+
 def batched_operand_ok(t: torch.Tensor) -> bool:
     """True when a 4-D bf16 tensor ``[Bo, Bi, rows, cols]`` can be described by a 4-D TMA map."""
     if t.dtype != torch.bfloat16 or t.dim() != 4 or t.data_ptr() % 16:

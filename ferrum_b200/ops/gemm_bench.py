@@ -25,6 +25,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--act", default=None)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--tf32", action="store_true", help="fp32 operands on the tensor cores (kind::tf32, fp32 output)")
     ap.add_argument("--prof", action="store_true",
                     help="CTA-pair kernel: report where the MMA thread waits (drained accumulator / operands) and how long "
                          "an epilogue warp is busy, averaged over the pairs of the last launch")
@@ -34,7 +35,7 @@ def main():
     a = ap.parse_args()
 
     from ferrum_b200.ops import gemm as _g
-    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.ops.gemm import gemm_bf16, gemm_tf32
 
     _g.set_gemm_2cta(a.two_cta)
     from ferrum_b200.utils.runtime import check_status
@@ -46,7 +47,9 @@ def main():
         torch.bfloat16)
     B = torch.randn(K, N, device="cuda").to(torch.bfloat16).t() if b_mn else torch.randn(N, K, device="cuda").to(
         torch.bfloat16)
-    out = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.layout == "tn" else torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32 if (a.layout == "tn" or a.tf32) else torch.bfloat16)
+    if a.tf32:
+        A, B = A.float().t().contiguous().t() if a_mn else A.float(), B.float().t().contiguous().t() if b_mn else B.float()
     bias = torch.randn(N, device="cuda") if a.bias else None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
@@ -66,13 +69,16 @@ def main():
         return ts[len(ts) // 2]
 
     aux = torch.empty_like(out) if a.dual else None
-    ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
+    if a.tf32:
+        ms = timeit(lambda: gemm_tf32(A, B, bias=bias, act=a.act, out=out))
+    else:
+        ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
     check_status()
     flops = 2.0 * M * N * K
     if a.two_cta:
         ref = (A[:256].float() @ B.float().t())
         res_err = (out[:256].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
-    res = {"kernel": "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+    res = {"kernel": "gemm_tf32_tcgen05" if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
            "tflops": flops / ms / 1e9}
     if a.two_cta:
         res["rel_err_first_rows"] = res_err
@@ -82,6 +88,8 @@ def main():
         pk = json.load(open(peaks))
         res["frac_of_measured_bf16_burst"] = res["tflops"] / pk["bf16_tflops"]
     if a.cublas:
+        if a.tf32:
+            torch.backends.cuda.matmul.allow_tf32 = True  # compare against cuBLAS' TF32 path, not its fp32 SIMT one
         Ac, Bc = A.contiguous(), B.contiguous()
         cms = timeit(lambda: torch.matmul(Ac, Bc.t()))
         res["cublas_ms"], res["cublas_tflops"] = cms, flops / cms / 1e9

@@ -128,3 +128,71 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn, M, N, K):
     assert (acc - (1.0 + _ref(a, b, None, None))).abs().max().item() < tol
     refb = torch.relu(_ref(a, b, None, None))
     assert (outb.float() - refb).abs().max().item() < 3e-2 * max(1.0, refb.abs().max().item())
+
+
+def _mk32(rows, cols, mn_major, scale=1.0):
+    """fp32 [rows(MN), cols(K)] view, stored K-major or MN-major."""
+    if mn_major:
+        return (torch.randn(cols, rows, device="cuda") * scale).t()
+    return torch.randn(rows, cols, device="cuda") * scale
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 32), (128, 128, 96), (256, 512, 512), (384, 200, 328), (136, 72, 1000),
+                                   (1024, 1000, 2048)])
+def test_gemm_tf32_layouts(a_mn, b_mn, M, N, K):
+    """fp32 operands on the tensor cores (tcgen05 kind::tf32) against a float64 product."""
+    from ferrum_b200.ops.gemm import gemm_tf32
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(M * 5 + N * 3 + K + a_mn * 2 + b_mn)
+    a = _mk32(M, K, a_mn, 0.5)
+    b = _mk32(N, K, b_mn, 0.5)
+    out = gemm_tf32(a, b)
+    check_status()
+    ref = (a.double() @ b.double().t()).float()
+    err = (out - ref).abs().max().item()
+    tol = 1e-3 * (K ** 0.5) * 0.25 + 1e-3  # TF32 operands: 2^-11 relative per element, random-walk over K
+    assert err < tol, f"max err {err} (tol {tol}) for {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}"
+    # not merely bf16-accurate: the error must be well below what 8-bit mantissas would give
+    bf = (a.bfloat16().float() @ b.bfloat16().float().t())
+    assert err < 0.5 * (bf - ref).abs().max().item() + 1e-4
+
+
+def test_gemm_tf32_epilogue_and_accumulate():
+    from ferrum_b200.ops.gemm import gemm_tf32
+
+    torch.manual_seed(3)
+    M, N, K = 300, 520, 192
+    a, b = _mk32(M, K, 0, 0.3), _mk32(N, K, 0, 0.3)
+    bias = torch.randn(N, device="cuda")
+    out = gemm_tf32(a, b, bias=bias, act="gelu")
+    ref = _ref(a, b, bias, "gelu")
+    assert (out - ref).abs().max().item() < 5e-3
+    acc = torch.ones(M, N, device="cuda")
+    gemm_tf32(a, b, out=acc, accumulate=True)
+    assert (acc - (1.0 + _ref(a, b, None, None))).abs().max().item() < 5e-3
+
+
+def test_tf32_precision_mode_trains_a_linear_layer():
+    import ferrum_b200 as fb
+    from ferrum_b200 import _lib, nn
+
+    torch.manual_seed(4)
+    dev = fb.Device.Cuda(0)
+    lin = nn.Linear(128, 64, device=dev)
+    x = torch.randn(96, 128, device="cuda", requires_grad=True)
+    prev = fb.config.matmul_precision()
+    fb.config.matmul_precision("tf32")
+    try:
+        before = _lib.launch_count()
+        y = lin(x)
+        y.square().mean().backward()
+        assert _lib.launch_count() > before and y.dtype == torch.float32
+    finally:
+        fb.config.matmul_precision(prev)
+    xr = x.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, lin.weight.detach(), lin.bias.detach())
+    yr.square().mean().backward()
+    assert (y - yr).abs().max().item() < 5e-3
+    assert (x.grad - xr.grad).abs().max().item() < 1e-4 + 5e-3 * xr.grad.abs().max().item()
