@@ -46,10 +46,10 @@ def parse():
                          "multi-GPU run uses) instead of one pass after backward; measured slower at one GPU "
                          "(7.22 vs 6.69 ms/step: the update kernels contend with the GEMMs for HBM)")
     ap.add_argument("--no-graph", action="store_true",
-                    help="1 GPU: launch every kernel of the end-to-end step from Python instead of replaying the "
-                         "step recorded in a CUDA graph")
-    ap.add_argument("--graph-ddp", action="store_true",
-                    help="multi-GPU: also replay the end-to-end step from a CUDA graph (engine in capturable mode)")
+                    help="launch every kernel of the end-to-end step from Python instead of replaying the step "
+                         "recorded in a CUDA graph (multi-GPU: the engine in capturable mode; measured at 2 GPUs: "
+                         "2.372 M samples/s replayed vs 2.273 M launched from Python)")
+    ap.add_argument("--graph-ddp", action="store_true", help="accepted for compatibility; the graph is the default")
     ap.add_argument("--shard-master", action="store_true",
                     help="DDP: publish only bf16 weights to peers, fp32 master weights stay with the shard owner")
     return ap.parse_args()
@@ -197,19 +197,24 @@ def run_ours(args):
     graph_box = [None]
 
     def make_graph():
-        """One GPU, no engine: the whole step (zero_grad, forward, backward, Adam) is recorded once in a CUDA graph
+        """The whole step (zero_grad, forward, backward, bucket reductions, Adam) is recorded once in a CUDA graph
         and replayed, so the read-back of the loss at the end of a step does not expose ~70 Python-issued launches
-        at the start of the next one.  Falls back to eager launches if the step cannot be captured."""
-        if args.no_graph or (engine is not None and not args.graph_ddp):
+        at the start of the next one.  Falls back to eager launches if the step cannot be captured; with several
+        ranks they agree on it first, so that recorded and eager steps never mix."""
+        if args.no_graph:
             return
         try:
             graph_box[0] = fb.cuda.GraphedStep(train_step, (x_dev, y_dev), optimizer=opt)
         except Exception as exc:  # noqa: BLE001 - any capture failure means: run eagerly
-            if engine is not None:
-                raise  # ranks must not diverge between recorded and eager steps
-            if rank == 0:
-                print(f"[bench] CUDA-graph capture unavailable ({type(exc).__name__}: {exc}); eager e2e",
-                      file=sys.stderr)
+            print(f"[bench] rank {rank}: CUDA-graph capture unavailable ({type(exc).__name__}: {exc}); eager e2e",
+                  file=sys.stderr)
+        if world > 1:
+            import torch.distributed as dist
+
+            ok = torch.tensor([1 if graph_box[0] is not None else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                graph_box[0] = None
 
     def step_e2e():
         x, y = next(feed)                  # host -> device copy of this step's inputs (issued one step ahead)

@@ -30,6 +30,8 @@ CSRC = ROOT / "csrc"
 OBJ = ROOT / "_obj"
 LIB = ROOT / "lib"
 CUDA_LIB = LIB / "libferrum_b200_cuda.so"
+OBJ_BOUNDS = ROOT / "_obj_bounds"
+CUDA_LIB_BOUNDS = LIB / "libferrum_b200_cuda_bounds.so"  # debug build with device-side index checks
 HOST_LIB = LIB / "libferrum_b200_host.so"
 
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
@@ -53,17 +55,20 @@ def _headers_digest() -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, flags_key: str, hdr: str, verbose: bool) -> Path:
+def _compile_one(src: Path, flags_key: str, hdr: str, verbose: bool, bounds: bool = False) -> Path:
     rel = src.relative_to(CSRC)
-    obj = OBJ / (str(rel).replace("/", "__") + ".o")
+    extra = ["-DFERRUM_BOUNDS=1"] if bounds else []
+    flags_key += " ".join(extra)
+    obj = (OBJ_BOUNDS if bounds else OBJ) / (str(rel).replace("/", "__") + ".o")
     stamp = obj.with_suffix(".hash")
     key = hashlib.sha256((flags_key + hdr).encode() + src.read_bytes()).hexdigest()
     if obj.exists() and stamp.exists() and stamp.read_text() == key:
         return obj
     if src.suffix == ".cu":
-        cmd = [NVCC, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [NVCC, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [CXX, *CXX_FLAGS, "-I", str(CSRC), "-I", f"{CUDA_HOME}/include", "-c", str(src), "-o", str(obj)]
+        cmd = [CXX, *CXX_FLAGS, *extra, "-I", str(CSRC), "-I", f"{CUDA_HOME}/include", "-c", str(src), "-o",
+               str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     log = obj.with_suffix(".log")
     log.write_text(" ".join(cmd) + "\n" + r.stdout + r.stderr)
@@ -90,9 +95,26 @@ def _link(objs: list[Path], out: Path, cuda: bool) -> None:
 
 
 def sources() -> tuple[list[Path], list[Path]]:
-    host = sorted((CSRC / "host").glob("*.cpp"))
+    host = sorted(p for p in (CSRC / "host").glob("*.cpp") if p.name != "selftest.cpp")
     cuda = sorted(p for p in CSRC.rglob("*") if p.suffix in (".cu", ".cpp") and (CSRC / "host") not in p.parents)
     return cuda, host
+
+
+def build_bounds(verbose: bool = True, jobs: int | None = None) -> None:
+    """The kernel library again with ``-DFERRUM_BOUNDS=1`` (device-side index checks that report and skip);
+    loaded instead of the normal one when ``FERRUM_BOUNDS=1`` is set at import time."""
+    OBJ_BOUNDS.mkdir(exist_ok=True)
+    cuda_src, _ = sources()
+    hdr = _headers_digest()
+    jobs = jobs or min(8, os.cpu_count() or 4)
+    with ThreadPoolExecutor(jobs) as ex:
+        futs = [ex.submit(_compile_one, s, " ".join(NVCC_FLAGS if s.suffix == ".cu" else CXX_FLAGS), hdr, verbose,
+                          True) for s in cuda_src]
+        objs = [f.result() for f in futs]
+    if (not CUDA_LIB_BOUNDS.exists()) or any(o.stat().st_mtime > CUDA_LIB_BOUNDS.stat().st_mtime for o in objs):
+        _link(objs, CUDA_LIB_BOUNDS, cuda=True)
+        if verbose:
+            print(f"[ferrum_b200 build] linked {CUDA_LIB_BOUNDS.name}")
 
 
 def build(verbose: bool = True, jobs: int | None = None) -> None:
@@ -123,6 +145,37 @@ def build(verbose: bool = True, jobs: int | None = None) -> None:
             print(f"[ferrum_b200 build] linked {HOST_LIB.name}")
 
 
+def build_host_selftest(out_dir, sanitizer: str = "address,undefined") -> Path:
+    """Compile the host library's sources together with ``csrc/host/selftest.cpp`` under a gcc sanitizer
+    (``"address,undefined"`` or ``"thread"``) into ``out_dir/selftest_<sanitizer>`` and return the path.
+    The binary takes a scratch directory and a thread count; it needs no GPU."""
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / ("selftest_" + sanitizer.replace(",", "_"))
+    srcs = [str(p) for p in sorted((CSRC / "host").glob("*.cpp"))]
+    # The configured compiler may ship without the sanitizer runtimes; the system g++ is tried next.
+    tried, last = [], None
+    for cxx in (CXX, shutil.which("g++"), "/usr/bin/g++"):
+        if not cxx or cxx in tried or shutil.which(cxx) is None:
+            continue
+        tried.append(cxx)
+        cmd = [cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={sanitizer}",
+               "-fno-sanitize-recover=all", "-pthread", *srcs, "-o", str(exe)]
+        last = subprocess.run(cmd, capture_output=True, text=True)
+        if last.returncode == 0:
+            return exe
+        if "sanitize" not in last.stderr and "asan" not in last.stderr and "tsan" not in last.stderr \
+                and "ubsan" not in last.stderr:
+            break  # a genuine compile error, not a missing runtime
+    missing = last is not None and any(k in last.stderr for k in ("-lasan", "-ltsan", "-lubsan", "preinit"))
+    err = SanitizerUnavailable if missing else RuntimeError
+    raise err(f"self-test build failed with {tried}\n{last.stdout if last else ''}\n{last.stderr if last else ''}")
+
+
+class SanitizerUnavailable(RuntimeError):
+    """No compiler on this machine can link the requested sanitizer runtime."""
+
+
 def ptxas_report() -> str:
     """Registers / spills / shared memory per kernel, as printed by ``-Xptxas -v``."""
     out = []
@@ -137,5 +190,7 @@ def ptxas_report() -> str:
 
 if __name__ == "__main__":
     build(verbose=True)
+    if os.environ.get("FERRUM_BOUNDS") == "1" or "--bounds" in sys.argv:
+        build_bounds(verbose=True)
     if "--ptxas" in sys.argv:
         print(ptxas_report())

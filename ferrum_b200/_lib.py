@@ -24,12 +24,20 @@ class NativeLibraryError(RuntimeError):
     pass
 
 
+def bounds_build_active() -> bool:
+    """True when this process uses the debug kernel library with device-side index checks."""
+    return os.environ.get("FERRUM_BOUNDS") == "1"
+
+
 def _ensure(path) -> None:
     if path.exists():
         return
     if os.environ.get("FERRUM_B200_NO_AUTOBUILD") == "1":
         raise NativeLibraryError(f"{path} is missing; run `python -m ferrum_b200._build`")
-    _build.build(verbose=False)
+    if path == _build.CUDA_LIB_BOUNDS:
+        _build.build_bounds(verbose=False)
+    else:
+        _build.build(verbose=False)
     if not path.exists():
         raise NativeLibraryError(f"building {path} failed")
 
@@ -100,6 +108,7 @@ _CUDA_SIGS = {
     "fb_gemm_bf16_2cta": (I, [P, P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, I, P, P]),
     "fb_gemm_bf16_2cta_pairs": (I, []),
     "fb_gemm_tf32": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, P, P]),
+    "fb_gemm_tf32_2cta": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, P, P]),
     "fb_gemm_bf16_2cta_set_profile": (None, [P]),
     "fb_gemm_bf16_batched": (I, [P, P, P, I, I, I, LL, LL, LL, I, I, LL, LL, LL, LL, LL, LL, I, I, I, I, F, P, P]),
     "fb_gemm_f32_simt": (I, [P, P, P, P, I, I, I, LL, LL, LL, LL, LL, I, I, I, LL, LL, LL, P]),
@@ -143,8 +152,8 @@ _CUDA_SIGS = {
     "fb_dropout_bwd": (I, [P, P, P, LL, F, I, P]),
     "fb_embedding_fwd": (I, [P, P, P, LL, I, LL, LL, I, P, P]),
     "fb_embedding_meanpool_fwd": (I, [P, P, P, LL, I, I, LL, I, P]),
-    "fb_embedding_bwd_sorted": (I, [P, P, P, P, LL, I, I, F, LL, I, P]),
-    "fb_gather_rows": (I, [P, P, P, LL, LL, P]),
+    "fb_embedding_bwd_sorted": (I, [P, P, P, P, LL, I, I, F, LL, LL, I, P]),
+    "fb_gather_rows": (I, [P, P, P, LL, LL, LL, P, P]),
     # optimizers
     "fb_adam_flat": (I, [P, P, P, P, P, LL, AdamH, P]),
     "fb_sgd_flat": (I, [P, P, P, P, LL, SgdH, P]),
@@ -216,8 +225,9 @@ def cuda():
     if _cuda is None:
         with _lock:
             if _cuda is None:
-                _ensure(_build.CUDA_LIB)
-                lib = ctypes.CDLL(str(_build.CUDA_LIB), mode=ctypes.RTLD_GLOBAL)
+                path = _build.CUDA_LIB_BOUNDS if bounds_build_active() else _build.CUDA_LIB
+                _ensure(path)
+                lib = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
                 _bind(lib, _CUDA_SIGS)
                 from . import _lib_dist  # signatures of the inter-GPU entry points
                 _bind(lib, _lib_dist.SIGS)

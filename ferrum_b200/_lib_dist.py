@@ -31,6 +31,9 @@ def _sigs():
                                   P, P, I, I, I, P]),
         "fb_dist_allreduce_dyn": (I, [POINTER(DistCtx), I, I, I, P, LL, LL, LL, LL, I, F, POINTER(AdamH), POINTER(SgdH),
                                       P, P, I, I, I, P, P]),
+        "fb_dist_allreduce_staged": (I, [POINTER(DistCtx), I, I, U, LL, LL, I, F, P, P, LL, I, I, P]),
+        "fb_dist_allreduce_staged_emulated": (I, [POINTER(DistCtx), I, I, U, LL, LL, I, F, POINTER(c_void_p),
+                                                  POINTER(c_void_p), LL, I, I, P]),
         "fb_dist_allreduce_emulated": (I, [POINTER(DistCtx), I, I, I, U, LL, LL, LL, LL, I, F, POINTER(AdamH),
                                            POINTER(SgdH), POINTER(c_void_p), POINTER(c_void_p), I, I, I, P]),
         "fb_dist_collective": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, LL, I, F, I, P]),

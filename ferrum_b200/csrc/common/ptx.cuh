@@ -233,6 +233,17 @@ __device__ __forceinline__ void umma_f16_2cta(uint32_t tmem_d, uint64_t adesc, u
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_tf32_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrives on the mbarrier at this offset in every CTA named by `cta_mask` once the MMAs issued so far retire.
 __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar, uint16_t cta_mask) {
   asm volatile(
@@ -250,14 +261,17 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t mbar_cluster_addr) 
 //   K-major operand : SBO = distance between 8-row groups, LBO unused.
 //   MN-major operand: LBO = distance between 64-element chunks along M/N,
 //                     SBO = distance between 8-deep groups along K.
+// `layout`: 2 = 128-byte swizzle of 16-byte chunks (every case but one), 1 = 128-byte swizzle of 32-byte chunks,
+// the only layout the tensor core accepts for MN-major 32-bit (TF32) operands; its swizzle pattern repeats every
+// 4 rows, so SBO is then the distance between 4-deep groups along K.
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes) {
+                                                         uint32_t sbo_bytes, uint32_t layout = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version (Blackwell)
-  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  d |= static_cast<uint64_t>(layout) << 61;
   return d;
 }
 

@@ -37,6 +37,26 @@ __device__ __forceinline__ void report_status(int32_t* status, int32_t code, int
     __threadfence_system();
   }
 }
+
+// Index checks of the debug build (-DFERRUM_BOUNDS=1, `FERRUM_BOUNDS=1 python -m ferrum_b200._build`): an index
+// outside [0, limit) records {site, index, limit} in the status block and the caller skips the access; nothing
+// traps.  In the normal build the macro is the constant `true` and costs nothing.
+__device__ __forceinline__ bool check_index(int32_t* status, int32_t site, long long idx, long long limit) {
+  if (idx >= 0 && idx < limit) return true;
+  report_status(status, kStatusBoundsViolation, site, static_cast<int32_t>(idx), static_cast<int32_t>(limit));
+  return false;
+}
+#ifdef FERRUM_BOUNDS
+#define FB_INDEX_OK(status, site, idx, limit) (::fb::check_index((status), (site), (idx), (limit)))
+#else
+#define FB_INDEX_OK(status, site, idx, limit) (true)
 #endif
+#endif
+
+// Status block that kernels without a status argument report to in the debug build (set by fb_bounds_set_status).
+inline int32_t*& bounds_status_ref() {
+  static int32_t* p = nullptr;
+  return p;
+}
 
 }  // namespace fb

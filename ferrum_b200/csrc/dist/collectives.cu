@@ -90,6 +90,13 @@ struct ArArgs {
   // memory (advanced by tiny kernels on the same stream), not from the by-value arguments a graph would freeze.
   const uint32_t* dev_epoch;  // NULL = use `epoch`
   const float* dyn;           // NULL = use adam / sgd as given; else {lr, bias_corr1, bias_corr2, ...}
+  // Plain all-reduce of a tensor that lives OUTSIDE the arena: each block copies the positions it will handshake
+  // for from stage_in into the region at grad_off before the entry handshake and copies the reduced values back to
+  // stage_out after the exit handshake, so no separate staging launches are needed.  n_valid <= n elements are
+  // real; the rest of the region is zero-filled and never copied back.
+  const float* stage_in;
+  float* stage_out;
+  long long n_valid;
   int streaming;       // local optimizer state moves with evict-first hints (ld/st.global.cs): it is touched once per
                        // step and should not displace the operand tiles of the GEMMs this kernel runs beside
 };
@@ -121,6 +128,50 @@ __device__ __forceinline__ void sgd1(float& p, float g, float& vel, const fb_sgd
   p -= h.lr * upd;
 }
 
+// Copies between a local tensor and this rank's arena region for the positions block `vblock` owns in EVERY
+// shard (the same relative positions that the peers' blocks of this index read and write).
+template <bool IN>
+__device__ void stage_block(const fb_dist_ctx& c, int vblock, int nvblocks, const ArArgs& a) {
+  long long per = (a.n + c.world - 1) / c.world;
+  per = (per + 3) & ~3LL;
+  const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
+  float4* region = reinterpret_cast<float4*>(c.arena[c.rank] + a.grad_off);
+  const bool vec = ((reinterpret_cast<uintptr_t>(IN ? static_cast<const void*>(a.stage_in)
+                                                    : static_cast<const void*>(a.stage_out)) & 15) == 0);
+  for (int r = 0; r < c.world; ++r) {
+    const long long lo = min(a.n, per * r);
+    const long long hi = min(a.n, lo + per);
+    const long long n4 = (hi - lo) >> 2, lo4 = lo >> 2;
+    for (long long i4 = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+      const long long e = (lo4 + i4) << 2;  // first element of this float4
+      if (IN) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vec && e + 4 <= a.n_valid) {
+          x = *reinterpret_cast<const float4*>(a.stage_in + e);
+        } else {
+          if (e < a.n_valid) x.x = a.stage_in[e];
+          if (e + 1 < a.n_valid) x.y = a.stage_in[e + 1];
+          if (e + 2 < a.n_valid) x.z = a.stage_in[e + 2];
+          if (e + 3 < a.n_valid) x.w = a.stage_in[e + 3];
+        }
+        region[lo4 + i4] = x;
+      } else {
+        if (e >= a.n_valid) continue;
+        // read at the L2 (the peers' stores arrive there; this SM's L1 may still hold what stage-in wrote)
+        const float4 x = ptx::ld_relaxed_sys_f4(region + lo4 + i4);
+        if (vec && e + 4 <= a.n_valid) {
+          *reinterpret_cast<float4*>(a.stage_out + e) = x;
+        } else {
+          a.stage_out[e] = x.x;
+          if (e + 1 < a.n_valid) a.stage_out[e + 1] = x.y;
+          if (e + 2 < a.n_valid) a.stage_out[e + 2] = x.z;
+          if (e + 3 < a.n_valid) a.stage_out[e + 3] = x.w;
+        }
+      }
+    }
+  }
+}
+
 // Reduce the shard of rank c.rank over all ranks, (optionally) update, publish to all ranks.
 // Each thread keeps U independent float4 positions in flight: a peer load costs a round trip over
 // NVLink (microseconds), so throughput is set by the bytes outstanding per SM, not by the thread count.
@@ -135,6 +186,7 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
     adam.bias_corr2 = a.dyn[2];
     sgd.lr = a.dyn[0];
   }
+  if (FUSE == FB_FUSE_NONE && a.stage_in != nullptr) stage_block<true>(c, vblock, nvblocks, a);
   if (!block_handshake(c, a.channel, vblock, epoch, s_fail, 100)) return;
 
   long long per = (a.n + c.world - 1) / c.world;
@@ -258,7 +310,8 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
       }
     }
   }
-  block_handshake(c, a.channel, vblock, epoch + 1, s_fail, 101);
+  const bool done = block_handshake(c, a.channel, vblock, epoch + 1, s_fail, 101);
+  if (FUSE == FB_FUSE_NONE && a.stage_out != nullptr && done) stage_block<false>(c, vblock, nvblocks, a);
 }
 
 template <int FUSE, bool MC, int U, int W>
@@ -277,6 +330,8 @@ struct EmuPack {
   fb_dist_ctx c[FB_MAX_RANKS];
   float* m[FB_MAX_RANKS];
   float* v[FB_MAX_RANKS];
+  const float* stage_in[FB_MAX_RANKS];  // per virtual rank: tensor outside the arena (NULL = none)
+  float* stage_out[FB_MAX_RANKS];
   int blocks_per_rank;
 };
 
@@ -290,6 +345,8 @@ allreduce_emulated_kernel(const EmuPack pk, ArArgs a) {
   const int vb = blockIdx.x % pk.blocks_per_rank;
   a.m = pk.m[vr];
   a.v = pk.v[vr];
+  a.stage_in = pk.stage_in[vr];
+  a.stage_out = pk.stage_out[vr];
   allreduce_body<FUSE, false, 1, FB_MAX_RANKS>(pk.c[vr], vb, pk.blocks_per_rank, a, &s_fail);
 }
 
@@ -436,7 +493,8 @@ static int allreduce_impl(const fb_dist_ctx* ctx, int fuse, int use_mc, int chan
                           long long grad_off, long long param_off, long long shadow_off, long long n, int op,
                           float scale, const fb_adam_hparams* adam, const fb_sgd_hparams* sgd, float* m, float* v,
                           int publish_master, int nblocks, int nthreads, const unsigned* dev_epoch, const float* dyn,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const float* stage_in = nullptr, float* stage_out = nullptr,
+                          long long n_valid = 0) {
   if (!ctx_ok(ctx) || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || nthreads < 32 ||
       nthreads > 256 || channel < 0 || channel >= FB_FLAG_CHANNELS)
     return -1;
@@ -457,6 +515,9 @@ static int allreduce_impl(const fb_dist_ctx* ctx, int fuse, int use_mc, int chan
   a.publish_master = publish_master;
   a.dev_epoch = dev_epoch;
   a.dyn = dyn;
+  a.stage_in = stage_in;
+  a.stage_out = stage_out;
+  a.n_valid = n_valid;
   {
     static int streaming = -1;
     if (streaming < 0) {
@@ -482,6 +543,18 @@ extern "C" int fb_dist_allreduce(const fb_dist_ctx* ctx, int fuse, int use_mc, i
                                  cudaStream_t stream) {
   return allreduce_impl(ctx, fuse, use_mc, channel, epoch, grad_off, param_off, shadow_off, n, op, scale, adam, sgd, m,
                         v, publish_master, nblocks, nthreads, nullptr, nullptr, stream);
+}
+
+// In-place all-reduce of a local fp32 tensor of n_valid elements through the arena region at region_off
+// (n elements, a multiple of 4 * world, n >= n_valid): staging in and out happens inside the one kernel.
+extern "C" int fb_dist_allreduce_staged(const fb_dist_ctx* ctx, int use_mc, int channel, unsigned epoch,
+                                        long long region_off, long long n, int op, float scale, const float* in,
+                                        float* out, long long n_valid, int nblocks, int nthreads,
+                                        cudaStream_t stream) {
+  if (in == nullptr || out == nullptr || n_valid <= 0 || n_valid > n) return -1;
+  if ((reinterpret_cast<uintptr_t>(in) & 3) || (reinterpret_cast<uintptr_t>(out) & 3)) return -1;
+  return allreduce_impl(ctx, FB_FUSE_NONE, use_mc, channel, epoch, region_off, 0, -1, n, op, scale, nullptr, nullptr,
+                        nullptr, nullptr, 1, nblocks, nthreads, nullptr, nullptr, stream, in, out, n_valid);
 }
 
 // Graph-capturable form: the handshake epoch is read from *dev_epoch (every rank keeps its own counter; they move
@@ -533,6 +606,38 @@ extern "C" int fb_dist_allreduce_emulated(const fb_dist_ctx* ctxs, int world, in
                    : fuse == FB_FUSE_SGD ? reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_SGD>)
                                          : reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_NONE>);
   return static_cast<int>(cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream));
+}
+
+// The staged all-reduce with every rank emulated in one cooperative launch: in[r] / out[r] are rank r's tensors.
+extern "C" int fb_dist_allreduce_staged_emulated(const fb_dist_ctx* ctxs, int world, int channel, unsigned epoch,
+                                                 long long region_off, long long n, int op, float scale,
+                                                 const float* const* in, float* const* out, long long n_valid,
+                                                 int nblocks, int nthreads, cudaStream_t stream) {
+  if (world < 1 || world > FB_MAX_RANKS || n <= 0 || (n & 3) || nblocks < 1 || nblocks > FB_FLAG_BLOCKS ||
+      in == nullptr || out == nullptr || n_valid <= 0 || n_valid > n)
+    return -1;
+  EmuPack pk{};
+  for (int r = 0; r < world; ++r) {
+    if (!ctx_ok(&ctxs[r]) || ctxs[r].world != world || ctxs[r].rank != r) return -1;
+    pk.c[r] = ctxs[r];
+    pk.stage_in[r] = in[r];
+    pk.stage_out[r] = out[r];
+  }
+  pk.blocks_per_rank = nblocks;
+  ArArgs a{};
+  a.channel = channel;
+  a.epoch = epoch;
+  a.grad_off = region_off;
+  a.shadow_off = -1;
+  a.n = n;
+  a.n_valid = n_valid;
+  a.op = op;
+  a.scale = scale;
+  a.publish_master = 1;
+  void* args[] = {&pk, &a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(
+      reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_NONE>), dim3(world * nblocks), dim3(nthreads),
+      args, 0, stream));
 }
 
 extern "C" int fb_dist_collective(const fb_dist_ctx* ctx, int mode, int channel, unsigned epoch, int root,

@@ -225,6 +225,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t b_lbo = p.b_mn_major ? kBK * 128 : 16;
       const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : 32;  // MN-major: kUmmaK rows of 128 B; K-major: 32 B
       const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : 32;
+      // MN-major fp32 operands sit in shared memory with the 32-byte-chunk swizzle (4-row groups, 512 B apart)
+      const uint32_t a_layout = (kTf32 && p.a_mn_major) ? 1u : 2u, a_sbo = (kTf32 && p.a_mn_major) ? 512u : 1024u;
+      const uint32_t b_layout = (kTf32 && p.b_mn_major) ? 1u : 2u, b_sbo = (kTf32 && p.b_mn_major) ? 512u : 1024u;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -248,8 +251,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint32_t sb = sa + C::kABytes;
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
-            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, a_sbo, a_layout);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, b_sbo, b_layout);
             if constexpr (kTf32)
               ptx::umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
             else
@@ -429,7 +432,7 @@ EncodeTiledFn get_encode_fn() {
 // 2-D tensor map of bf16 (elem_bytes 2) or fp32 (4) data: `inner` contiguous elements per row, `outer` rows,
 // row pitch `ld` elements, box = one 128-byte row segment x box_outer, 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer,
-              int elem_bytes = 2) {
+              int elem_bytes = 2, bool atom32 = false) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return false;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return false;
@@ -438,9 +441,9 @@ bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long oute
   cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                   const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -609,9 +612,10 @@ extern "C" int fb_gemm_tf32(const float* a, const float* b, float* out, const fl
   const int bn = small_n ? 128 : 256;
   constexpr int kChunk = El<true>::kMnChunk;
   CUtensorMap ma, mb;
-  bool ok = a_mn_major ? make_map(&ma, a, M, K, lda, kChunk, 4) : make_map(&ma, a, K, M, lda, kBM, 4);
+  // MN-major fp32 tiles are written with the 32-byte-chunk swizzle the tensor core requires for them
+  bool ok = a_mn_major ? make_map(&ma, a, M, K, lda, kChunk, 4, true) : make_map(&ma, a, K, M, lda, kBM, 4);
   if (!ok) return -2;
-  ok = b_mn_major ? make_map(&mb, b, N, K, ldb, kChunk, 4) : make_map(&mb, b, K, N, ldb, bn, 4);
+  ok = b_mn_major ? make_map(&mb, b, N, K, ldb, kChunk, 4, true) : make_map(&mb, b, K, N, ldb, bn, 4);
   if (!ok) return -2;
   GemmArgs args;
   args.out = out;

@@ -36,18 +36,17 @@ namespace fb {
 namespace {
 
 constexpr int kBM = 128;       // rows per CTA; the pair covers 256
-constexpr int kBK = 64;
-constexpr int kUmmaK = 16;
+constexpr int kRowBytes = 128;  // one swizzled shared-memory row = one k-block of a K-major operand
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr int kGroupM = 8;     // pair-tiles (256 rows) per rasterisation group
-constexpr int kABytes = kBM * kBK * 2;          // 16 KB
+constexpr int kABytes = kBM * kRowBytes;        // 16 KB
 
 // BN = columns per pair (each CTA stages half of them).  256 is the high-intensity shape; 128 halves the
 // tile for small outputs that would otherwise occupy less than half of the CTA pairs.
 template <int BN>
 struct Cfg2 {
-  static constexpr int kBBytes = (BN / 2) * kBK * 2;          // 16 KB / 8 KB
+  static constexpr int kBBytes = (BN / 2) * kRowBytes;        // 16 KB / 8 KB
   static constexpr int kStageBytes = kABytes + kBBytes;       // 32 KB / 24 KB per CTA
   static constexpr int kStages = BN == 256 ? 6 : 8;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
@@ -84,11 +83,15 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
   n_blk = r / gsize;
 }
 
-template <int BN>
+// kTf32: fp32 operands multiplied as TF32 (kind::tf32).  A k-block is always one 128-byte row, so it holds 32
+// fp32 or 64 bf16 K elements, one MMA covers 32 bytes of K (8 / 16 elements), and an MN-major operand arrives in
+// chunks of 32 / 64 MN elements; the byte geometry of a stage is the same for both element types.
+template <int BN, bool kTf32 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const Args2 p) {
   constexpr int kBN = BN;
+  constexpr int kBK = kTf32 ? 32 : 64, kUmmaK = kTf32 ? 8 : 16, kChunk = kTf32 ? 32 : 64;
   constexpr int kStages = Cfg2<BN>::kStages;
   constexpr int kStageBytes = Cfg2<BN>::kStageBytes;
   constexpr int kTmemCols = Cfg2<BN>::kTmemCols;
@@ -164,14 +167,15 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           const int k0 = kb * kBK;
           if (p.a_mn_major) {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d_2cta(sa + c * (kBK * 128), &tma_a, bar, m0 + c * 64, k0);
+            for (int c = 0; c < kBM / kChunk; ++c)
+              ptx::tma_load_2d_2cta(sa + c * (kBK * 128), &tma_a, bar, m0 + c * kChunk, k0);
           } else {
             ptx::tma_load_2d_2cta(sa, &tma_a, bar, k0, m0);
           }
           if (p.b_mn_major) {
 #pragma unroll
-            for (int c = 0; c < (kBN / 2) / 64; ++c)
-              ptx::tma_load_2d_2cta(sb + c * (kBK * 128), &tma_b, bar, n0 + c * 64, k0);
+            for (int c = 0; c < (kBN / 2) / kChunk; ++c)
+              ptx::tma_load_2d_2cta(sb + c * (kBK * 128), &tma_b, bar, n0 + c * kChunk, k0);
           } else {
             ptx::tma_load_2d_2cta(sb, &tma_b, bar, k0, n0);
           }
@@ -194,11 +198,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = ptx::make_idesc(1u, 2 * kBM, kBN, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = ptx::make_idesc(kTf32 ? 2u : 1u, 2 * kBM, kBN, p.a_mn_major, p.b_mn_major);
       const uint32_t a_lbo = p.a_mn_major ? kBK * 128 : 16;
       const uint32_t b_lbo = p.b_mn_major ? kBK * 128 : 16;
-      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : kUmmaK * 2;
-      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : kUmmaK * 2;
+      const uint32_t a_kstep = p.a_mn_major ? kUmmaK * 128 : 32;
+      const uint32_t b_kstep = p.b_mn_major ? kUmmaK * 128 : 32;
+      // MN-major fp32 operands sit in shared memory with the 32-byte-chunk swizzle (4-row groups, 512 B apart)
+      const uint32_t a_layout = (kTf32 && p.a_mn_major) ? 1u : 2u, a_sbo = (kTf32 && p.a_mn_major) ? 512u : 1024u;
+      const uint32_t b_layout = (kTf32 && p.b_mn_major) ? 1u : 2u, b_sbo = (kTf32 && p.b_mn_major) ? 512u : 1024u;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -228,9 +235,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           const uint32_t sb = sa + kABytes;
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
-            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, a_sbo, a_layout);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, b_sbo, b_layout);
+            if constexpr (kTf32)
+              ptx::umma_tf32_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit_2cta(&empty_bar[stage], 0x3);  // frees the slot in both CTAs
           if (++stage == kStages) {
@@ -411,27 +421,29 @@ EncodeTiledFn2 encode_fn2() {
   return fn;
 }
 
-bool make_map2(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+bool make_map2(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld, int box_outer,
+               int elem_bytes, bool atom32 = false) {
   EncodeTiledFn2 enc = encode_fn2();
   if (enc == nullptr) return false;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+             const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Number of CTA pairs that can be resident at once (0 if cluster launch is unavailable).
-template <int BN>
+template <int BN, bool kTf32 = false>
 int max_pairs() {
   constexpr int kSmemBytes = Cfg2<BN>::kSmemBytes;
   static int n = -1;
   if (n < 0) {
     n = 0;
-    if (cudaFuncSetAttribute(gemm_bf16_2cta_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+    if (cudaFuncSetAttribute(gemm_bf16_2cta_kernel<BN, kTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
         cudaSuccess) {
       cudaGetLastError();
       return n;
@@ -448,23 +460,40 @@ int max_pairs() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_2cta_kernel<BN>, &cfg) == cudaSuccess) n = clusters;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_2cta_kernel<BN, kTf32>, &cfg) == cudaSuccess) n = clusters;
     else cudaGetLastError();
   }
   return n;
 }
 
-template <int BN>
+template <int BN, bool kTf32 = false>
 int launch2(const void* a, const void* b, Args2& args, long long lda, long long ldb, int pairs, long long num_tiles,
             cudaStream_t stream) {
+  constexpr int kEb = kTf32 ? 4 : 2, kChunk = kRowBytes / kEb;
   CUtensorMap ma, mb;
-  bool ok = args.a_mn_major ? make_map2(&ma, a, args.M, args.K, lda, 64) : make_map2(&ma, a, args.K, args.M, lda, kBM);
+  // MN-major fp32 tiles are written with the 32-byte-chunk swizzle the tensor core requires for them
+  bool ok = args.a_mn_major ? make_map2(&ma, a, args.M, args.K, lda, kChunk, kEb, kTf32)
+                            : make_map2(&ma, a, args.K, args.M, lda, kBM, kEb);
   if (!ok) return -2;
-  ok = args.b_mn_major ? make_map2(&mb, b, args.N, args.K, ldb, 64) : make_map2(&mb, b, args.K, args.N, ldb, BN / 2);
+  ok = args.b_mn_major ? make_map2(&mb, b, args.N, args.K, ldb, kChunk, kEb, kTf32)
+                       : make_map2(&mb, b, args.K, args.N, ldb, BN / 2, kEb);
   if (!ok) return -2;
   if (num_tiles < pairs) pairs = static_cast<int>(num_tiles);
-  gemm_bf16_2cta_kernel<BN><<<2 * pairs, kThreads, Cfg2<BN>::kSmemBytes, stream>>>(ma, mb, args);
+  gemm_bf16_2cta_kernel<BN, kTf32><<<2 * pairs, kThreads, Cfg2<BN>::kSmemBytes, stream>>>(ma, mb, args);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Arguments every entry point fills the same way.
+void fill_common(Args2& args, int32_t* status) {
+  args.status = status;
+  args.timeout_ns = 2000000000ull;
+  static int stream_default = -1;
+  if (stream_default < 0) {
+    const char* e = getenv("FERRUM_GEMM_STREAM_STORES");
+    stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  args.stream_stores = stream_default;
+  args.prof = g_prof_buffer;
 }
 
 }  // namespace
@@ -501,17 +530,7 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
   args.out_bf16 = out_bf16;
   args.act = act;
   args.beta = beta;
-  args.status = status;
-  args.timeout_ns = 2000000000ull;
-  {
-    static int stream_default = -1;
-    if (stream_default < 0) {
-      const char* e = getenv("FERRUM_GEMM_STREAM_STORES");
-      stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
-    }
-    args.stream_stores = stream_default;
-  }
-  args.prof = g_prof_buffer;
+  fill_common(args, status);
   int pairs = pairs_avail;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   const long long m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
@@ -522,4 +541,32 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
   const bool narrow = max_pairs<128>() >= pairs && 2 * tiles256 <= pairs;
   return narrow ? launch2<128>(a, b, args, lda, ldb, pairs, tiles128, stream)
                 : launch2<256>(a, b, args, lda, ldb, pairs, tiles256, stream);
+}
+
+// fp32 operands as TF32 on CTA pairs, fp32 result; same arguments as fb_gemm_tf32 (256 x 256 pair tiles only).
+extern "C" int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, const float* bias, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                 int act, int beta, int max_ctas, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int pairs_avail = max_pairs<256, true>();
+  if (pairs_avail <= 0) return -3;
+  Args2 args;
+  args.out = out;
+  args.out2 = nullptr;
+  args.bias = bias;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = 0;
+  args.act = act;
+  args.beta = beta;
+  fill_common(args, status);
+  int pairs = pairs_avail;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  const long long tiles = static_cast<long long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
+  return launch2<256, true>(a, b, args, lda, ldb, pairs, tiles, stream);
 }

@@ -54,6 +54,9 @@ int fb_gemm_bf16(const void* a, const void* b, void* out, void* out2, const floa
 int fb_gemm_tf32(const float* a, const float* b, float* out, const float* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act, int beta, int max_ctas,
                  int32_t* status, cudaStream_t stream);
+int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, const float* bias, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act, int beta, int max_ctas,
+                 int32_t* status, cudaStream_t stream);
 // CTA-pair variant (tcgen05 cta_group::2; 256 x 256 tiles on two SMs, 256 x 128 for small outputs); same
 // arguments.  Returns -3 where clusters of two CTAs cannot be scheduled.  fb_gemm_bf16_2cta_pairs() = resident pairs.
 int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
@@ -177,10 +180,10 @@ int fb_embedding_meanpool_fwd(const float* weight, const long long* idx, void* o
                               int dim, long long vocab, int out_dtype, cudaStream_t stream);
 // dW[idx[i]] += scale * dout[i / group] ; `sorted_idx/perm` come from a radix sort of idx.
 int fb_embedding_bwd_sorted(const void* dout, const long long* sorted_idx, const long long* perm, float* dweight,
-                            long long n_idx, int dim, int group, float scale, long long padding_idx, int dtype,
-                            cudaStream_t stream);
+                            long long n_idx, int dim, int group, float scale, long long padding_idx,
+                            long long vocab, int dtype, cudaStream_t stream);
 int fb_gather_rows(const void* src, const long long* idx, void* dst, long long n_idx, long long row_bytes,
-                   cudaStream_t stream);
+                   long long n_rows, int32_t* status, cudaStream_t stream);
 
 // ---- optimizers (multi-tensor; chunk tables built on the host) -------------------
 typedef struct {

@@ -253,15 +253,20 @@ template <typename G>
 __global__ void embedding_bwd_sorted_kernel(const G* __restrict__ dout, const long long* __restrict__ sorted_idx,
                                             const long long* __restrict__ perm, float* __restrict__ dw,
                                             long long n_idx, int dim, int group, float scale,
-                                            long long padding_idx) {
+                                            long long padding_idx, long long vocab, int32_t* bstatus) {
   constexpr int kChunk = 32;
   __shared__ long long s_id[kChunk];
   __shared__ long long s_row[kChunk];
   const long long lo = static_cast<long long>(blockIdx.x) * kChunk;
   const int cnt = static_cast<int>(min(n_idx, lo + kChunk) - lo);
   if (threadIdx.x < cnt) {
-    s_id[threadIdx.x] = sorted_idx[lo + threadIdx.x];
-    s_row[threadIdx.x] = perm[lo + threadIdx.x] / group;
+    long long id = sorted_idx[lo + threadIdx.x];
+    const long long row = perm[lo + threadIdx.x] / group;
+    // ids outside the table were reported by the forward pass; their gradient rows are dropped, never written.
+    if (id >= vocab) id = -1;
+    if (!FB_INDEX_OK(bstatus, 40, row, (n_idx + group - 1) / group)) id = -1;
+    s_id[threadIdx.x] = id;
+    s_row[threadIdx.x] = id < 0 ? 0 : row;
   }
   __syncthreads();
   const bool vec = dim % 4 == 0 && (reinterpret_cast<uintptr_t>(dw) & 15) == 0 &&
@@ -314,19 +319,25 @@ __global__ void embedding_bwd_sorted_kernel(const G* __restrict__ dout, const lo
   }
 }
 
+// An index outside [0, n_rows) is reported (site 11) and its output row is zero-filled; the source is not read.
 __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, const long long* __restrict__ idx,
-                                   uint8_t* __restrict__ dst, long long n_idx, long long row_bytes) {
+                                   uint8_t* __restrict__ dst, long long n_idx, long long row_bytes,
+                                   long long n_rows, int32_t* status) {
   const bool vec = (row_bytes % 16 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
                    ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
   for (long long i = blockIdx.x; i < n_idx; i += gridDim.x) {
-    const uint8_t* s = src + idx[i] * row_bytes;
+    const long long id = idx[i];
+    const bool oob = id < 0 || id >= n_rows;
+    if (oob && threadIdx.x == 0)
+      report_status(status, kStatusBoundsViolation, 11, static_cast<int32_t>(i), static_cast<int32_t>(id));
+    const uint8_t* s = src + (oob ? 0 : id) * row_bytes;
     uint8_t* d = dst + i * row_bytes;
     if (vec) {
       const long long nv = row_bytes >> 4;
       for (long long k = threadIdx.x; k < nv; k += blockDim.x)
-        reinterpret_cast<uint4*>(d)[k] = reinterpret_cast<const uint4*>(s)[k];
+        reinterpret_cast<uint4*>(d)[k] = oob ? make_uint4(0, 0, 0, 0) : reinterpret_cast<const uint4*>(s)[k];
     } else {
-      for (long long k = threadIdx.x; k < row_bytes; k += blockDim.x) d[k] = s[k];
+      for (long long k = threadIdx.x; k < row_bytes; k += blockDim.x) d[k] = oob ? uint8_t(0) : s[k];
     }
   }
 }
@@ -658,7 +669,7 @@ extern "C" int fb_embedding_meanpool_fwd(const float* weight, const long long* i
 
 extern "C" int fb_embedding_bwd_sorted(const void* dout, const long long* sorted_idx, const long long* perm,
                                        float* dweight, long long n_idx, int dim, int group, float scale,
-                                       long long padding_idx, int dtype, cudaStream_t stream) {
+                                       long long padding_idx, long long vocab, int dtype, cudaStream_t stream) {
   if (n_idx <= 0 || dim <= 0) return 0;
   if (group < 1) return -1;
   const long long nb = (n_idx + 31) / 32;
@@ -666,22 +677,25 @@ extern "C" int fb_embedding_bwd_sorted(const void* dout, const long long* sorted
   const int threads = dim >= 256 ? 256 : (dim >= 128 ? 128 : 64);
   if (dtype == FB_DT_F32)
     embedding_bwd_sorted_kernel<float><<<static_cast<unsigned>(nb), threads, 0, stream>>>(
-        static_cast<const float*>(dout), sorted_idx, perm, dweight, n_idx, dim, group, scale, padding_idx);
+        static_cast<const float*>(dout), sorted_idx, perm, dweight, n_idx, dim, group, scale, padding_idx, vocab,
+        bounds_status_ref());
   else if (dtype == FB_DT_BF16)
     embedding_bwd_sorted_kernel<__nv_bfloat16><<<static_cast<unsigned>(nb), threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dout), sorted_idx, perm, dweight, n_idx, dim, group, scale, padding_idx);
+        static_cast<const __nv_bfloat16*>(dout), sorted_idx, perm, dweight, n_idx, dim, group, scale, padding_idx,
+        vocab, bounds_status_ref());
   else
     return -1;
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int fb_gather_rows(const void* src, const long long* idx, void* dst, long long n_idx,
-                              long long row_bytes, cudaStream_t stream) {
+                              long long row_bytes, long long n_rows, int32_t* status, cudaStream_t stream) {
   if (n_idx <= 0 || row_bytes <= 0) return 0;
+  if (n_rows <= 0) return -1;
   const int g = static_cast<int>(n_idx < sm_count() * 16LL ? n_idx : sm_count() * 16LL);
   const int threads = row_bytes >= 4096 ? 256 : 64;
   gather_rows_kernel<<<g, threads, 0, stream>>>(static_cast<const uint8_t*>(src), idx, static_cast<uint8_t*>(dst),
-                                                n_idx, row_bytes);
+                                                n_idx, row_bytes, n_rows, status);
   return static_cast<int>(cudaGetLastError());
 }
 

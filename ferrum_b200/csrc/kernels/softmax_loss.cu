@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <float.h>
 
+#include "../common/status.h"
 #include "../include/ferrum_kernels.h"
 
 namespace fb {
@@ -239,7 +240,7 @@ softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restr
 template <typename T, typename G, int TPR>
 __global__ void __launch_bounds__(256)
 ce_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ row_loss,
-          G* __restrict__ dlogits, long long rows, int cols, float grad_scale) {
+          G* __restrict__ dlogits, long long rows, int cols, float grad_scale, int32_t* bstatus) {
   __shared__ float smem[8];
   constexpr int kRPB = 256 / TPR;
   const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
@@ -259,6 +260,7 @@ ce_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, fl
     if (live) {
       long long lab = labels[row];
       const bool valid = lab >= 0 && lab < cols;  // out-of-range labels contribute nothing
+      if (!valid && t == 0) (void)FB_INDEX_OK(bstatus, 41, lab, cols);  // the debug build also reports them
       if (t == 0 && row_loss) row_loss[row] = valid ? (m + logf(s) - ldf(xr + lab)) : 0.f;
       if (dlogits) {
         const float inv = 1.f / s;
@@ -281,7 +283,7 @@ template <int K>
 __global__ void __launch_bounds__(256)
 ce_warp_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                float* __restrict__ row_loss, __nv_bfloat16* __restrict__ dlogits, long long rows, int cols,
-               float grad_scale) {
+               float grad_scale, int32_t* bstatus) {
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -322,6 +324,7 @@ ce_warp_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __rest
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const long long lab = labels[row];
     const bool valid = lab >= 0 && lab < cols;
+    if (!valid && lane == 0) (void)FB_INDEX_OK(bstatus, 41, lab, cols);
     if (lane == 0 && row_loss) row_loss[row] = valid ? (m + logf(s) - __bfloat162float(xr[lab])) : 0.f;
     if (dlogits) {
       const float inv = valid ? grad_scale / s : 0.f;
@@ -469,11 +472,11 @@ bool ce_warp_launch(const void* logits, const long long* labels, float* row_loss
   const int grid = row_grid(rows, 8);
   const int k = (cols / 8 + 31) / 32;
   if (k <= 4)
-    ce_warp_kernel<4><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+    ce_warp_kernel<4><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs, bounds_status_ref());
   else if (k <= 8)
-    ce_warp_kernel<8><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+    ce_warp_kernel<8><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs, bounds_status_ref());
   else
-    ce_warp_kernel<16><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs);
+    ce_warp_kernel<16><<<grid, 256, 0, st>>>(x, labels, row_loss, g, rows, cols, gs, bounds_status_ref());
   return true;
 }
 
@@ -484,10 +487,12 @@ int ce_t(const void* logits, const long long* labels, float* row_loss, void* dlo
     return static_cast<int>(cudaGetLastError());
   if (cols <= 512)
     ce_kernel<T, G, 32><<<row_grid(rows, 8), 256, 0, st>>>(static_cast<const T*>(logits), labels, row_loss,
-                                                          static_cast<G*>(dlogits), rows, cols, gs);
+                                                          static_cast<G*>(dlogits), rows, cols, gs,
+                                                          bounds_status_ref());
   else
     ce_kernel<T, G, 256><<<row_grid(rows, 1), 256, 0, st>>>(static_cast<const T*>(logits), labels, row_loss,
-                                                           static_cast<G*>(dlogits), rows, cols, gs);
+                                                           static_cast<G*>(dlogits), rows, cols, gs,
+                                                          bounds_status_ref());
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -1152,7 +1152,7 @@ class _EmbeddingFn(Function):
         scale = 1.0 / ctx.group if ctx.pool else 1.0
         _lib.check(_lib.cuda().fb_embedding_bwd_sorted(g2.data_ptr(), sidx.data_ptr(), perm.data_ptr(),
                                                        dw.data_ptr(), flat.numel(), D, ctx.group, scale,
-                                                       -1 if ctx.padding_idx is None else ctx.padding_idx,
+                                                       -1 if ctx.padding_idx is None else ctx.padding_idx, V,
                                                        _dt(g2), _stream()), "fb_embedding_bwd_sorted")
         if ctx.sink is not None:
             ctx.sink.ready(ctx.weight_ref)
@@ -1189,8 +1189,11 @@ def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     idx = idx.to(device=src.device, dtype=torch.int64).contiguous()
     out = torch.empty((idx.numel(), *src.shape[1:]), device=src.device, dtype=src.dtype)
     row_bytes = src[0].numel() * src.element_size() if src.shape[0] else 0
+    if idx.numel() == 0 or row_bytes == 0:
+        return out
+    # an index outside the source is reported through the status block and its row comes back as zeros
     _lib.check(_lib.cuda().fb_gather_rows(src.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), row_bytes,
-                                          _stream()), "fb_gather_rows")
+                                          src.shape[0], _rt.status_ptr(), _stream()), "fb_gather_rows")
     return out
 
 

@@ -114,9 +114,10 @@ def tf32_operand_ok(t: torch.Tensor) -> bool:
 
 
 def gemm_tf32(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
-              out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+              out: torch.Tensor | None = None, accumulate: bool = False, kernel: str | None = None) -> torch.Tensor:
     """``out[M,N] = act(a[M,K] @ b[N,K]^T + bias)`` with fp32 tensors on the tensor cores (TF32 operands, fp32
-    accumulation and output).  Same layout rules as :func:`gemm_bf16`."""
+    accumulation and output).  Same layout rules as :func:`gemm_bf16`.  ``kernel`` forces "1cta" or "2cta";
+    by default outputs of at least 512 x 256 run on CTA pairs."""
     assert a.is_cuda and a.dim() == 2 and b.dim() == 2 and a.dtype == torch.float32 and b.dtype == torch.float32
     M, K = a.shape
     N, Kb = b.shape
@@ -126,10 +127,16 @@ def gemm_tf32(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     if out is None:
         out = torch.empty((M, N), device=a.device, dtype=torch.float32)
     assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (M, N)
-    rc = _lib.cuda().fb_gemm_tf32(a.data_ptr(), b.data_ptr(), out.data_ptr(),
-                                  bias.data_ptr() if bias is not None else None, M, N, K, lda, ldb, out.stride(0),
-                                  a_mn, b_mn, ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(),
-                                  _stream())
+    pair = (M >= 512 and N >= 256) if kernel is None else kernel == "2cta"
+    lib = _lib.cuda()
+    args = (a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None, M, N, K,
+            lda, ldb, out.stride(0), a_mn, b_mn, ACT[act], 1 if accumulate else 0, _max_ctas, _rt.status_ptr(),
+            _stream())
+    rc = -3
+    if pair:
+        rc = lib.fb_gemm_tf32_2cta(*args)
+    if rc == -3:  # CTA pairs not used or not launchable on this device
+        rc = lib.fb_gemm_tf32(*args)
     _lib.check(rc, "fb_gemm_tf32")
     return out
 

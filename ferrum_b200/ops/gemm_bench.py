@@ -70,7 +70,7 @@ def main():
 
     aux = torch.empty_like(out) if a.dual else None
     if a.tf32:
-        ms = timeit(lambda: gemm_tf32(A, B, bias=bias, act=a.act, out=out))
+        ms = timeit(lambda: gemm_tf32(A, B, bias=bias, act=a.act, out=out, kernel="2cta" if a.two_cta else "1cta"))
     else:
         ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
     check_status()
@@ -78,7 +78,7 @@ def main():
     if a.two_cta:
         ref = (A[:256].float() @ B.float().t())
         res_err = (out[:256].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
-    res = {"kernel": "gemm_tf32_tcgen05" if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+    res = {"kernel": ("gemm_tf32_tcgen05_2cta" if a.two_cta else "gemm_tf32_tcgen05") if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
            "tflops": flops / ms / 1e9}
     if a.two_cta:
         res["rel_err_first_rows"] = res_err

@@ -114,7 +114,7 @@ def _cases(small: bool):
     dw = torch.zeros(V, D, device=dev)
     case("embedding_scatter_add_bwd",
          lambda: lib.fb_embedding_bwd_sorted(gout.data_ptr(), sidx.data_ptr(), perm.data_ptr(), dw.data_ptr(),
-                                             Bt * S, D, S, 1.0 / S, -1, 3, st()), Bt * S * D * 2, "K10 bwd")
+                                             Bt * S, D, S, 1.0 / S, -1, V, 3, st()), Bt * S * D * 2, "K10 bwd")
     gi = torch.randint(0, R, (R,), device=dev)
     case("gather_rows_f32", lambda: F.gather_rows(x32, gi), n * 8, "K18 collate")
 

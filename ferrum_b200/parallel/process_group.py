@@ -148,15 +148,13 @@ class ProcessGroup:
         for lo in range(0, n, per):
             cnt = min(per, n - lo)
             padded = (cnt + 4 * self._world - 1) // (4 * self._world) * (4 * self._world)
-            stage = arena.view(off, (padded,), torch.float32)
-            stage[:cnt].copy_(work[lo:lo + cnt])
-            if padded > cnt:
-                stage[cnt:].zero_()  # the padding is reduced too but never copied back
             e = arena.next_epoch(0)
-            _lib.check(lib.fb_dist_allreduce(arena.ctx, 0, use_mc, 0, e, off, 0, -1, padded, _OP_CODE[op], scale,
-                                             None, None, None, None, 1, self._blocks(padded * 4), 256, self._stream()),
-                       "fb_dist_allreduce")
-            work[lo:lo + cnt].copy_(stage[:cnt])
+            # staging into and out of the arena happens inside the kernel (each block moves the positions it
+            # handshakes for), so an all-reduce of any fp32 tensor is ONE launch
+            ptr = work.data_ptr() + lo * 4
+            _lib.check(lib.fb_dist_allreduce_staged(arena.ctx, use_mc, 0, e, off, padded, _OP_CODE[op], scale, ptr,
+                                                    ptr, cnt, self._blocks(padded * 4), 256, self._stream()),
+                       "fb_dist_allreduce_staged")
         if work.data_ptr() != flat.data_ptr():
             flat.copy_(work)
         if flat.data_ptr() != t.data_ptr():

@@ -47,6 +47,34 @@ def test_allreduce_average_emulated(world, n):
         a.close()
 
 
+@pytest.mark.parametrize("world,n_valid,offset", [(2, 8000, 0), (4, 4097, 0), (8, 333, 1), (3, 1, 3)])
+def test_staged_allreduce_emulated(world, n_valid, offset):
+    """All-reduce of tensors that live outside the arena: the kernel stages them in and out itself (ragged
+    lengths, tensors that do not start on a 16-byte boundary)."""
+    from ferrum_b200.utils.runtime import check_status
+
+    n = (n_valid + 4 * world - 1) // (4 * world) * (4 * world)
+    lib, arenas, ctxs = _setup(world, n)
+    off = arenas[0].data_offset()
+    torch.manual_seed(world + n_valid)
+    bufs = [torch.randn(n_valid + offset + 5, device="cuda") for _ in range(world)]
+    data = [b[offset:offset + n_valid] for b in bufs]
+    before = [b.clone() for b in bufs]
+    ref = torch.stack([d.clone() for d in data]).sum(0) / world
+    ptrs = (ctypes.c_void_p * world)(*[d.data_ptr() for d in data])
+    for epoch in (1, 3):  # twice: the second round reduces the first round's results
+        rc = lib.fb_dist_allreduce_staged_emulated(ctxs, world, 0, epoch, off, n, 4, 1.0 / world, ptrs, ptrs,
+                                                   n_valid, 3, 128, _stream())
+        assert rc == 0
+        check_status()
+        for d in data:
+            assert torch.allclose(d, ref, atol=1e-5, rtol=1e-5)
+    for b, b0 in zip(bufs, before):  # nothing outside [offset, offset + n_valid) was touched
+        assert torch.equal(b[:offset], b0[:offset]) and torch.equal(b[offset + n_valid:], b0[offset + n_valid:])
+    for a in arenas:
+        a.close()
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_fused_allreduce_adam_emulated(world):
     from ferrum_b200 import _lib as L
