@@ -38,6 +38,9 @@ def _sigs():
                                            POINTER(SgdH), POINTER(c_void_p), POINTER(c_void_p), I, I, I, P]),
         "fb_dist_collective": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, LL, I, F, I, P]),
         "fb_dist_collective_emulated": (I, [POINTER(DistCtx), I, I, I, U, I, LL, LL, LL, I, F, I, P]),
+        "fb_dist_collective_staged": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, I, F, P, P, I, P]),
+        "fb_dist_collective_staged_emulated": (I, [POINTER(DistCtx), I, I, I, U, I, LL, LL, I, F, POINTER(c_void_p),
+                                                   POINTER(c_void_p), I, P]),
         "fb_dist_barrier": (I, [POINTER(DistCtx), I, U, P]),
     }
 

@@ -142,7 +142,26 @@ __device__ void stage_block(const fb_dist_ctx& c, int vblock, int nvblocks, cons
     const long long lo = min(a.n, per * r);
     const long long hi = min(a.n, lo + per);
     const long long n4 = (hi - lo) >> 2, lo4 = lo >> 2;
-    for (long long i4 = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+    long long i4 = static_cast<long long>(vblock) * blockDim.x + threadIdx.x;
+    if (vec && hi <= a.n_valid) {
+      // whole shard is real data and 16-byte aligned on both sides: eight independent vectors in flight per thread
+      constexpr int kU = 8;
+      for (; i4 + (kU - 1) * stride < n4; i4 += stride * kU) {
+        float4 x[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const long long k = lo4 + i4 + u * stride;
+          x[u] = IN ? reinterpret_cast<const float4*>(a.stage_in)[k] : ptx::ld_relaxed_sys_f4(region + k);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const long long k = lo4 + i4 + u * stride;
+          if (IN) region[k] = x[u];
+          else reinterpret_cast<float4*>(a.stage_out)[k] = x[u];
+        }
+      }
+    }
+    for (; i4 < n4; i4 += stride) {
       const long long e = (lo4 + i4) << 2;  // first element of this float4
       if (IN) {
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -360,20 +379,97 @@ struct CollArgs {
   long long n_bytes;          // bytes per chunk
   int op;
   float scale;
+  // Tensors outside the arena (optional).  stage_in: this rank's contribution, copied into the arena's input
+  // region by the kernel itself before the entry handshake; direct_out: where this rank's result goes instead
+  // of the arena's output region (results are always local, so any device pointer works).
+  const unsigned char* stage_in;
+  unsigned char* direct_out;
 };
 
+// Which bytes a thread moves is decided by the ARENA-side address and the length only, so the block that stages a
+// chunk and the peer block of the same index that later pulls it cover exactly the same bytes; the alignment of the
+// pointer outside the arena only changes how a thread loads or stores its unit.
+__device__ __forceinline__ bool arena_vec_ok(const unsigned char* arena_ptr) {
+  return (reinterpret_cast<uintptr_t>(arena_ptr) & 15) == 0;
+}
+
+// peer (or own) arena -> any local pointer
 __device__ __forceinline__ void copy_bytes(const unsigned char* src, unsigned char* dst, long long nbytes,
                                            long long tid, long long stride) {
-  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+  if (arena_vec_ok(src)) {
     const long long nv = nbytes >> 4;
-    for (long long i = tid; i < nv; i += stride) {
-      const float4 v = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + i);
-      reinterpret_cast<float4*>(dst)[i] = v;
+    const uintptr_t da = reinterpret_cast<uintptr_t>(dst);
+    long long i = tid;
+    if ((da & 15) == 0) {  // eight independent 16-byte loads in flight per thread (a peer load is a round trip)
+      constexpr int kU = 8;
+      for (; i + (kU - 1) * stride < nv; i += stride * kU) {
+        float4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) v[u] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) reinterpret_cast<float4*>(dst)[i + u * stride] = v[u];
+      }
     }
-    for (long long i = (nv << 4) + tid; i < nbytes; i += stride) dst[i] = src[i];
+    for (; i < nv; i += stride) {
+      const float4 v = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(src) + i);
+      if ((da & 15) == 0) {
+        reinterpret_cast<float4*>(dst)[i] = v;
+      } else if ((da & 3) == 0) {
+        float* d = reinterpret_cast<float*>(dst) + i * 4;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      } else {
+        const unsigned char* b = reinterpret_cast<const unsigned char*>(&v);
+        for (int k = 0; k < 16; ++k) dst[i * 16 + k] = b[k];
+      }
+    }
+    for (long long i = (nv << 4) + tid; i < nbytes; i += stride)
+      dst[i] = *reinterpret_cast<const volatile unsigned char*>(src + i);
   } else {
-    for (long long i = tid; i < nbytes; i += stride) dst[i] = src[i];
+    for (long long i = tid; i < nbytes; i += stride) dst[i] = *reinterpret_cast<const volatile unsigned char*>(src + i);
   }
+}
+
+// any local pointer -> own arena, same byte ownership as copy_bytes reading that arena address
+__device__ __forceinline__ void stage_bytes(const unsigned char* src, unsigned char* arena_dst, long long nbytes,
+                                            long long tid, long long stride) {
+  if (arena_vec_ok(arena_dst)) {
+    const long long nv = nbytes >> 4;
+    const uintptr_t sa = reinterpret_cast<uintptr_t>(src);
+    long long i = tid;
+    if ((sa & 15) == 0) {
+      constexpr int kU = 8;
+      for (; i + (kU - 1) * stride < nv; i += stride * kU) {
+        float4 v[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) v[u] = reinterpret_cast<const float4*>(src)[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) reinterpret_cast<float4*>(arena_dst)[i + u * stride] = v[u];
+      }
+    }
+    for (; i < nv; i += stride) {
+      float4 v;
+      if ((sa & 15) == 0) {
+        v = reinterpret_cast<const float4*>(src)[i];
+      } else if ((sa & 3) == 0) {
+        const float* f = reinterpret_cast<const float*>(src) + i * 4;
+        v = make_float4(f[0], f[1], f[2], f[3]);
+      } else {
+        unsigned char* b = reinterpret_cast<unsigned char*>(&v);
+        for (int k = 0; k < 16; ++k) b[k] = src[i * 16 + k];
+      }
+      reinterpret_cast<float4*>(arena_dst)[i] = v;
+    }
+    for (long long i = (nv << 4) + tid; i < nbytes; i += stride) arena_dst[i] = src[i];
+  } else {
+    for (long long i = tid; i < nbytes; i += stride) arena_dst[i] = src[i];
+  }
+}
+
+// The reductions own data per float: float i of a chunk belongs to thread i mod stride, on both sides.
+__device__ __forceinline__ void stage_floats(const unsigned char* src, unsigned char* arena_dst, long long nfloats,
+                                             long long tid, long long stride) {
+  for (long long i = tid; i < nfloats; i += stride)
+    reinterpret_cast<float*>(arena_dst)[i] = reinterpret_cast<const float*>(src)[i];
 }
 
 __device__ void reduce_floats(const fb_dist_ctx& c, long long src_off, unsigned char* dst, long long nfloats,
@@ -393,20 +489,49 @@ __device__ void reduce_floats(const fb_dist_ctx& c, long long src_off, unsigned 
 }
 
 __device__ void collective_body(const fb_dist_ctx& c, int vblock, int nvblocks, const CollArgs& a, int* s_fail) {
-  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 200)) return;
   const long long tid = static_cast<long long>(vblock) * blockDim.x + threadIdx.x;
   const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
   unsigned char* self = c.arena[c.rank];
+  if (a.stage_in != nullptr) {
+    // every block brings the bytes its peers' blocks of the same index will ask for
+    switch (a.mode) {
+      case FB_COLL_BROADCAST:
+        if (c.rank == a.root) stage_bytes(a.stage_in, self + a.in_off, a.n_bytes, tid, stride);
+        break;
+      case FB_COLL_SCATTER:
+        if (c.rank == a.root)
+          for (int q = 0; q < c.world; ++q)
+            stage_bytes(a.stage_in + q * a.n_bytes, self + a.in_off + q * a.n_bytes, a.n_bytes, tid, stride);
+        break;
+      case FB_COLL_GATHER:
+      case FB_COLL_ALL_GATHER:
+        stage_bytes(a.stage_in, self + a.in_off, a.n_bytes, tid, stride);
+        break;
+      case FB_COLL_REDUCE_SCATTER:
+        for (int q = 0; q < c.world; ++q)
+          stage_floats(a.stage_in + q * a.n_bytes, self + a.in_off + q * a.n_bytes, a.n_bytes >> 2, tid, stride);
+        break;
+      case FB_COLL_REDUCE:
+        stage_floats(a.stage_in, self + a.in_off, a.n_bytes >> 2, tid, stride);
+        break;
+      default:
+        break;
+    }
+  }
+  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 200)) return;
+  unsigned char* out = a.direct_out != nullptr ? a.direct_out : self + a.out_off;
   switch (a.mode) {
     case FB_COLL_BROADCAST:
-      if (c.rank != a.root) copy_bytes(c.arena[a.root] + a.in_off, self + a.in_off, a.n_bytes, tid, stride);
+      if (c.rank != a.root)
+        copy_bytes(c.arena[a.root] + a.in_off, a.direct_out != nullptr ? a.direct_out : self + a.in_off, a.n_bytes,
+                   tid, stride);
       break;
     case FB_COLL_GATHER:
       if (c.rank != a.root) break;
       // fallthrough
     case FB_COLL_ALL_GATHER:
       for (int p = 0; p < c.world; ++p)
-        copy_bytes(c.arena[p] + a.in_off, self + a.out_off + p * a.n_bytes, a.n_bytes, tid, stride);
+        copy_bytes(c.arena[p] + a.in_off, out + p * a.n_bytes, a.n_bytes, tid, stride);
       break;
     case FB_COLL_ALL_GATHER_INPLACE:
       for (int p = 0; p < c.world; ++p)
@@ -414,13 +539,13 @@ __device__ void collective_body(const fb_dist_ctx& c, int vblock, int nvblocks, 
           copy_bytes(c.arena[p] + a.in_off + p * a.n_bytes, self + a.in_off + p * a.n_bytes, a.n_bytes, tid, stride);
       break;
     case FB_COLL_SCATTER:
-      copy_bytes(c.arena[a.root] + a.in_off + c.rank * a.n_bytes, self + a.out_off, a.n_bytes, tid, stride);
+      copy_bytes(c.arena[a.root] + a.in_off + c.rank * a.n_bytes, out, a.n_bytes, tid, stride);
       break;
     case FB_COLL_REDUCE_SCATTER:
-      reduce_floats(c, a.in_off + c.rank * a.n_bytes, self + a.out_off, a.n_bytes >> 2, a.op, a.scale, tid, stride);
+      reduce_floats(c, a.in_off + c.rank * a.n_bytes, out, a.n_bytes >> 2, a.op, a.scale, tid, stride);
       break;
     case FB_COLL_REDUCE:
-      if (c.rank == a.root) reduce_floats(c, a.in_off, self + a.out_off, a.n_bytes >> 2, a.op, a.scale, tid, stride);
+      if (c.rank == a.root) reduce_floats(c, a.in_off, out, a.n_bytes >> 2, a.op, a.scale, tid, stride);
       break;
     default:
       break;
@@ -438,15 +563,19 @@ collective_kernel(const fb_dist_ctx c, const CollArgs a) {
 
 struct EmuCtxPack {
   fb_dist_ctx c[FB_MAX_RANKS];
+  const unsigned char* stage_in[FB_MAX_RANKS];  // per virtual rank (NULL = data already in the arena)
+  unsigned char* direct_out[FB_MAX_RANKS];
   int blocks_per_rank;
 };
 __global__ void __launch_bounds__(512)
-collective_emulated_kernel(const EmuCtxPack pk, const CollArgs a) {
+collective_emulated_kernel(const EmuCtxPack pk, CollArgs a) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
-  collective_body(pk.c[blockIdx.x / pk.blocks_per_rank], blockIdx.x % pk.blocks_per_rank, pk.blocks_per_rank, a,
-                  &s_fail);
+  const int vr = blockIdx.x / pk.blocks_per_rank;
+  a.stage_in = pk.stage_in[vr];
+  a.direct_out = pk.direct_out[vr];
+  collective_body(pk.c[vr], blockIdx.x % pk.blocks_per_rank, pk.blocks_per_rank, a, &s_fail);
 }
 
 __global__ void barrier_kernel(const fb_dist_ctx c, int channel, uint32_t epoch) {
@@ -646,7 +775,30 @@ extern "C" int fb_dist_collective(const fb_dist_ctx* ctx, int mode, int channel,
   if (!ctx_ok(ctx) || n_bytes < 0 || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || channel < 0 ||
       channel >= FB_FLAG_CHANNELS || root < 0 || root >= ctx->world)
     return -1;
-  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale};
+  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale, nullptr, nullptr};
+  collective_kernel<<<nblocks, 512, 0, stream>>>(*ctx, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same collectives on tensors OUTSIDE the arena, in one launch: `in` (this rank's contribution; may be NULL
+// where the rank contributes nothing, e.g. a non-root of broadcast / scatter) is staged into the arena region at
+// in_off by the kernel, and the result is written straight to `out` (NULL where the rank receives nothing).
+// Reductions need 4-byte aligned pointers.
+extern "C" int fb_dist_collective_staged(const fb_dist_ctx* ctx, int mode, int channel, unsigned epoch, int root,
+                                         long long in_off, long long n_bytes, int op, float scale, const void* in,
+                                         void* out, int nblocks, cudaStream_t stream) {
+  if (!ctx_ok(ctx) || n_bytes < 0 || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || channel < 0 ||
+      channel >= FB_FLAG_CHANNELS || root < 0 || root >= ctx->world || mode == FB_COLL_ALL_GATHER_INPLACE)
+    return -1;
+  const bool reduces = mode == FB_COLL_REDUCE_SCATTER || mode == FB_COLL_REDUCE;
+  if (reduces && ((n_bytes & 3) || (reinterpret_cast<uintptr_t>(in) & 3) || (reinterpret_cast<uintptr_t>(out) & 3)))
+    return -1;
+  const bool receives = mode == FB_COLL_GATHER || mode == FB_COLL_REDUCE ? ctx->rank == root
+                        : mode == FB_COLL_BROADCAST                     ? ctx->rank != root
+                                                                        : true;
+  if (receives && out == nullptr) return -1;
+  CollArgs a{mode, channel, epoch, root, in_off, 0, n_bytes, op, scale, static_cast<const unsigned char*>(in),
+             static_cast<unsigned char*>(out)};
   collective_kernel<<<nblocks, 512, 0, stream>>>(*ctx, a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -659,7 +811,28 @@ extern "C" int fb_dist_collective_emulated(const fb_dist_ctx* ctxs, int world, i
   EmuCtxPack pk{};
   for (int r = 0; r < world; ++r) pk.c[r] = ctxs[r];
   pk.blocks_per_rank = nblocks;
-  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale};
+  CollArgs a{mode, channel, epoch, root, in_off, out_off, n_bytes, op, scale, nullptr, nullptr};
+  void* args[] = {&pk, &a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(collective_emulated_kernel),
+                                                      dim3(world * nblocks), dim3(512), args, 0, stream));
+}
+
+// fb_dist_collective_staged with every rank emulated in one cooperative launch; in[r] / out[r] may be NULL.
+extern "C" int fb_dist_collective_staged_emulated(const fb_dist_ctx* ctxs, int world, int mode, int channel,
+                                                  unsigned epoch, int root, long long in_off, long long n_bytes,
+                                                  int op, float scale, const void* const* in, void* const* out,
+                                                  int nblocks, cudaStream_t stream) {
+  if (world < 1 || world > FB_MAX_RANKS || nblocks < 1 || nblocks > FB_FLAG_BLOCKS || in == nullptr ||
+      out == nullptr || mode == FB_COLL_ALL_GATHER_INPLACE)
+    return -1;
+  EmuCtxPack pk{};
+  for (int r = 0; r < world; ++r) {
+    pk.c[r] = ctxs[r];
+    pk.stage_in[r] = static_cast<const unsigned char*>(in[r]);
+    pk.direct_out[r] = static_cast<unsigned char*>(out[r]);
+  }
+  pk.blocks_per_rank = nblocks;
+  CollArgs a{mode, channel, epoch, root, in_off, 0, n_bytes, op, scale, nullptr, nullptr};
   void* args[] = {&pk, &a};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(collective_emulated_kernel),
                                                       dim3(world * nblocks), dim3(512), args, 0, stream));

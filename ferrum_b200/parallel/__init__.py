@@ -1,6 +1,6 @@
 """Distributed training (ferrum-distributed): process groups, collectives over NVLink, DistributedDataParallel."""
 from .backend import (AlreadyInitialized, Backend, BackendConfig, CommunicationError, DistributedError,
-                      InvalidConfiguration, InvalidRank, NotInitialized, ReduceOp, TensorError, Timeout,
+                      InternalError, InvalidConfiguration, InvalidRank, NotInitialized, ReduceOp, TensorError, Timeout,
                       UnsupportedBackend)
 from .ddp import DistributedDataParallel, GradientBucket, GradientHook
 from .process_group import (ProcessGroup, barrier, destroy_process_group, get_rank, get_world, get_world_size,
@@ -16,4 +16,5 @@ __all__ = [
     "get_world_size", "is_main_process", "barrier", "DistributedDataParallel", "GradientBucket", "GradientHook",
     "SymmetricArena", "DistributedError", "AlreadyInitialized", "NotInitialized", "InvalidRank",
     "CommunicationError", "Timeout", "UnsupportedBackend", "InvalidConfiguration", "TensorError",
+    "InternalError",
 ]

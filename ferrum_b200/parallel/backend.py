@@ -55,6 +55,13 @@ class TensorError(DistributedError):
         super().__init__(f"Tensor error: {msg}")
 
 
+class InternalError(DistributedError):
+    """``DistributedError::InternalError`` (ferrum-distributed/src/error.rs:40-42)."""
+
+    def __init__(self, msg):
+        super().__init__(f"Internal error: {msg}")
+
+
 class Backend(enum.Enum):
     """``Nvlink`` is this package's own transport (sm_100a kernels over peer memory); ``Nccl`` is the library
     baseline; ``Gloo`` runs CPU ranks; ``Mpi`` is declared by the reference and not provided."""

@@ -31,9 +31,12 @@ from ..nn.modules import Embedding, Linear, Module, tensor_io
 from ..ops import gemm as _gemm
 from ..ops.functional import GradSink
 from ..utils import runtime as _rt
-from .backend import Backend, CommunicationError, ReduceOp, Timeout
+from .backend import Backend, CommunicationError, InternalError, ReduceOp, Timeout
 from .process_group import ProcessGroup, get_world
 from .symm import SymmetricArena
+
+_GUARD_BYTES = 65536   # keeps every region on the 64 KiB alignment it has without the bands
+_GUARD_PATTERN = 0xA5
 
 
 class GradientBucket:
@@ -263,12 +266,23 @@ class DistributedDataParallel(Module, GradSink):
         world, rank = self._pg.world_size(), self._pg.rank()
         lib = _lib.cuda()
         fb = lib.fb_dist_query_flag_bytes()
-        self._off_param = fb
-        self._off_grad = fb + total * 4
-        self._off_shadow = fb + total * 8
-        self._arena = SymmetricArena.create(total * 10, rank, world, self._pg.exchange,
+        # FERRUM_GUARD_BANDS=1 (debug): 64 KiB of a fixed byte pattern before, between and after the three regions;
+        # check_guard_bands() tells whether any kernel, local or a peer's, wrote outside its region.
+        gb = _GUARD_BYTES if os.environ.get("FERRUM_GUARD_BANDS") == "1" else 0
+        self._off_param = fb + gb
+        self._off_grad = self._off_param + total * 4 + gb
+        self._off_shadow = self._off_grad + total * 4 + gb
+        self._arena = SymmetricArena.create(total * 10 + 4 * gb, rank, world, self._pg.exchange,
                                             self._pg.config().device_wait_ns())
         a = self._arena
+        self._guards = []
+        if gb:
+            for name, off in (("before the parameters", fb), ("parameters | gradients", self._off_grad - gb),
+                              ("gradients | bf16 copies", self._off_shadow - gb),
+                              ("after the bf16 copies", self._off_shadow + total * 2)):
+                band = a.view(off, (gb,), torch.uint8)
+                band.fill_(_GUARD_PATTERN)
+                self._guards.append((name, band))
         self._flat_params = a.view(self._off_param, (total,), torch.float32)
         self._flat_grads = a.view(self._off_grad, (total,), torch.float32)
         self._flat_shadow = a.view(self._off_shadow, (total,), torch.bfloat16)
@@ -531,11 +545,27 @@ class DistributedDataParallel(Module, GradSink):
             out[name] = full
         return out
 
+    def check_guard_bands(self) -> int:
+        """Debug aid (``FERRUM_GUARD_BANDS=1`` when the engine is built): verify that the pattern-filled bands
+        around the parameter, gradient and bf16 regions of the arena are intact.  Returns the number of bands
+        checked (0 when the feature is off); raises ``InternalError`` naming the band and the first damaged byte."""
+        guards = getattr(self, "_guards", None) or []
+        if guards:
+            torch.cuda.synchronize()
+        for name, band in guards:
+            bad = (band != _GUARD_PATTERN).nonzero()
+            if bad.numel():
+                raise InternalError(f"guard band '{name}' of the gradient arena was overwritten at byte "
+                                    f"{int(bad[0])} (value {int(band[int(bad[0])])}) on rank {self._pg.rank()}")
+        return len(guards)
+
     def shutdown(self) -> None:
         """Release the arena (collective: every rank should call it after its last step)."""
         if getattr(self, "_use_native", False) and getattr(self, "_arena", None) is not None:
             self.sync_master_weights()
             torch.cuda.synchronize()
+            self.check_guard_bands()
+            self._guards = []
             _gemm.set_gemm_cta_limit(0)
             try:
                 self._pg.barrier()

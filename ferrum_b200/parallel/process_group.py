@@ -111,7 +111,8 @@ class ProcessGroup:
         return torch.cuda.current_stream().cuda_stream
 
     def _blocks(self, nbytes: int) -> int:
-        return max(1, min(128, nbytes // (128 * 1024) + 1))
+        # one block per 32 KiB up to 128: mid-sized messages are latency-bound, so they want many short loops
+        return max(1, min(128, nbytes // (32 * 1024) + 1))
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, tensor, op: ReduceOp = ReduceOp.Sum):
@@ -160,21 +161,28 @@ class ProcessGroup:
         if flat.data_ptr() != t.data_ptr():
             t.copy_(flat.view(t.shape))
 
-    def _native_pull(self, mode: int, root: int, src: torch.Tensor | None, nbytes_chunk: int, op: ReduceOp,
-                     out_chunks: int) -> torch.Tensor:
-        """Stage ``src`` at the arena's input region, run the pull kernel, return a view of the output region."""
+    def _staged(self, mode: int, root: int, src: torch.Tensor | None, dst: torch.Tensor | None, nbytes_chunk: int,
+                op: ReduceOp = ReduceOp.Sum) -> None:
+        """One pull-collective launch on tensors outside the arena: the kernel stages ``src`` (contiguous, or None
+        where this rank contributes nothing) into the arena's input region itself and writes this rank's result
+        straight into ``dst`` (contiguous, or None where it receives nothing)."""
         arena = self.comm_arena()
-        in_off = arena.data_offset()
-        out_off = in_off + self._chunk
-        if src is not None:
-            sb = src.contiguous().view(-1).view(torch.uint8)
-            arena.view(in_off, (sb.numel(),), torch.uint8).copy_(sb)
         e = arena.next_epoch(0)
         scale = 1.0 / self._world if op is ReduceOp.Average else 1.0
-        _lib.check(_lib.cuda().fb_dist_collective(arena.ctx, mode, 0, e, root, in_off, out_off, nbytes_chunk,
-                                                  _OP_CODE[op], scale, self._blocks(nbytes_chunk), self._stream()),
-                   "fb_dist_collective")
-        return arena.view(out_off, (nbytes_chunk * max(out_chunks, 1),), torch.uint8)
+        _lib.check(_lib.cuda().fb_dist_collective_staged(
+            arena.ctx, mode, 0, e, root, arena.data_offset(), nbytes_chunk, _OP_CODE[op], scale,
+            src.data_ptr() if src is not None else None, dst.data_ptr() if dst is not None else None,
+            self._blocks(nbytes_chunk), self._stream()), "fb_dist_collective_staged")
+
+    @staticmethod
+    def _as_one_buffer(tensors, nbytes: int):
+        """The tensors as ONE contiguous buffer when they already are consecutive slices of one (the usual
+        ``buf.chunk(world)`` case), else None."""
+        base = tensors[0].data_ptr()
+        for r, t in enumerate(tensors):
+            if not t.is_contiguous() or t.data_ptr() != base + r * nbytes:
+                return None
+        return tensors[0]
 
     def broadcast(self, tensor, root: int = 0):
         t = _unwrap(tensor)
@@ -184,19 +192,11 @@ class ProcessGroup:
         if self._world == 1:
             return tensor
         if self._native(t):
-            arena = self.comm_arena()
             flat = t.contiguous().view(-1).view(torch.uint8)
-            off = arena.data_offset()
             for lo in range(0, flat.numel(), self._chunk):
-                cnt = min(self._chunk, flat.numel() - lo)
-                stage = arena.view(off, (cnt,), torch.uint8)
-                if self._rank == root:
-                    stage.copy_(flat[lo:lo + cnt])
-                e = arena.next_epoch(0)
-                _lib.check(_lib.cuda().fb_dist_collective(arena.ctx, 0, 0, e, root, off, off, cnt, 0, 1.0,
-                                                          self._blocks(cnt), self._stream()), "fb_dist_collective")
-                if self._rank != root:
-                    flat[lo:lo + cnt].copy_(stage)
+                part = flat[lo:lo + min(self._chunk, flat.numel() - lo)]
+                is_root = self._rank == root
+                self._staged(0, root, part if is_root else None, None if is_root else part, part.numel())
             if flat.data_ptr() != t.data_ptr():
                 t.copy_(flat.view(t.dtype).view(t.shape))
             return tensor
@@ -213,9 +213,10 @@ class ProcessGroup:
         if self._world == 1:
             return tensor
         if self._native(t) and t.dtype == torch.float32 and t.numel() * 4 <= self._chunk:
-            out = self._native_pull(5, dst, t, t.numel() * 4, op, 1)
-            if self._rank == dst:
-                t.copy_(out.view(torch.float32).view(t.shape))
+            work = t if t.is_contiguous() else t.contiguous()
+            self._staged(5, dst, work, work if self._rank == dst else None, t.numel() * 4, op)
+            if self._rank == dst and work.data_ptr() != t.data_ptr():
+                t.copy_(work)
             return tensor
         import torch.distributed as dist
 
@@ -223,6 +224,19 @@ class ProcessGroup:
         if op is ReduceOp.Average and self._rank == dst:
             t.div_(self._world)
         return tensor
+
+    def _gather_like(self, mode: int, root: int, x: torch.Tensor, outs, nbytes: int) -> None:
+        receives = mode == 1 or self._rank == root
+        buf = None
+        if receives:
+            buf = self._as_one_buffer(outs, nbytes)
+            direct = buf is not None
+            if not direct:
+                buf = torch.empty(nbytes * self._world, device=x.device, dtype=torch.uint8)
+        self._staged(mode, root, x.contiguous(), buf, nbytes)
+        if receives and not direct:
+            for r, o in enumerate(outs):
+                o.copy_(buf[r * nbytes:(r + 1) * nbytes].view(x.dtype).view(o.shape))
 
     def all_gather(self, output, input):
         """``output[r]`` receives rank ``r``'s ``input``."""
@@ -236,9 +250,7 @@ class ProcessGroup:
             return output
         nbytes = x.numel() * x.element_size()
         if self._native(x) and nbytes <= self._chunk:
-            res = self._native_pull(1, 0, x, nbytes, ReduceOp.Sum, self._world)
-            for r, o in enumerate(outs):
-                o.copy_(res[r * nbytes:(r + 1) * nbytes].view(x.dtype).view(o.shape))
+            self._gather_like(1, 0, x, outs, nbytes)
             return output
         import torch.distributed as dist
 
@@ -258,15 +270,23 @@ class ProcessGroup:
             return output
         nbytes = x.numel() * x.element_size()
         if self._native(x) and nbytes <= self._chunk:
-            res = self._native_pull(2, dst, x, nbytes, ReduceOp.Sum, self._world)
-            if self._rank == dst:
-                for r, o in enumerate(outs):
-                    o.copy_(res[r * nbytes:(r + 1) * nbytes].view(x.dtype).view(o.shape))
+            self._gather_like(2, dst, x, outs, nbytes)
             return output
         import torch.distributed as dist
 
         dist.gather(x, outs if self._rank == dst else None, dst=self._ranks[dst], group=self._tg)
         return output
+
+    def _scatter_like(self, mode: int, root: int, ins, o: torch.Tensor, nbytes: int, op: ReduceOp) -> None:
+        src = None
+        if ins is not None:
+            src = self._as_one_buffer(ins, nbytes)
+            if src is None:
+                src = torch.cat([i.contiguous().view(-1) for i in ins])
+        dst = o if o.is_contiguous() else torch.empty_like(o, memory_format=torch.contiguous_format)
+        self._staged(mode, root, src, dst, nbytes, op)
+        if dst.data_ptr() != o.data_ptr():
+            o.copy_(dst)
 
     def scatter(self, output, input, src: int = 0):
         o = _unwrap(output)
@@ -281,9 +301,7 @@ class ProcessGroup:
             return output
         nbytes = o.numel() * o.element_size()
         if self._native(o) and nbytes * self._world <= self._chunk:
-            stacked = torch.cat([i.contiguous().view(-1) for i in ins]) if self._rank == src else None
-            res = self._native_pull(3, src, stacked, nbytes, ReduceOp.Sum, 1)
-            o.copy_(res.view(o.dtype).view(o.shape))
+            self._scatter_like(3, src, ins if self._rank == src else None, o, nbytes, ReduceOp.Sum)
             return output
         import torch.distributed as dist
 
@@ -302,9 +320,7 @@ class ProcessGroup:
             return output
         nbytes = o.numel() * 4
         if self._native(o) and o.dtype == torch.float32 and nbytes * self._world <= self._chunk:
-            stacked = torch.cat([i.contiguous().view(-1) for i in ins])
-            res = self._native_pull(4, 0, stacked, nbytes, op, 1)
-            o.copy_(res.view(torch.float32).view(o.shape))
+            self._scatter_like(4, 0, ins, o, nbytes, op)
             return output
         import torch.distributed as dist
 

@@ -206,6 +206,73 @@ def test_pull_collectives_emulated():
         a.close()
 
 
+@pytest.mark.parametrize("world,n,shift", [(4, 1000, 0), (4, 333, 1), (3, 5, 0), (8, 4099, 3)])
+def test_staged_pull_collectives_emulated(world, n, shift):
+    """The pull collectives on tensors outside the arena: the kernel stages the inputs itself and writes results
+    straight to the destination.  Chunk sizes that are not multiples of 16 bytes and pointers that are only
+    4-byte aligned take the element-wise paths."""
+    from ferrum_b200.utils.runtime import check_status
+
+    lib, arenas, ctxs = _setup(world, n * world + 16)
+    in_off = arenas[0].data_offset()
+    torch.manual_seed(world * 7 + n)
+    src = [torch.randn(n * world + shift, device="cuda")[shift:] for _ in range(world)]
+    outs = [torch.full((n * world + shift + 3,), -7.0, device="cuda") for _ in range(world)]
+    VP = ctypes.c_void_p * world
+    none = VP(*[None] * world)
+
+    def run(mode, root, ins, dsts, epoch, op=0):
+        rc = lib.fb_dist_collective_staged_emulated(ctxs, world, mode, 0, epoch, root, in_off, n * 4, op, 1.0,
+                                                    ins, dsts, 2, _stream())
+        assert rc == 0
+        check_status()
+
+    def reset():
+        for o in outs:
+            o.fill_(-7.0)
+
+    o_ptr = VP(*[o[shift:].data_ptr() for o in outs])
+    s_ptr = VP(*[x.data_ptr() for x in src])
+    root = world - 1
+    # broadcast: only the root contributes, everybody else receives
+    reset()
+    run(0, root, VP(*[src[r].data_ptr() if r == root else None for r in range(world)]),
+        VP(*[None if r == root else outs[r][shift:].data_ptr() for r in range(world)]), 1)
+    for r in range(world):
+        if r != root:
+            assert torch.equal(outs[r][shift:shift + n], src[root][:n])
+            assert (outs[r][shift + n:] == -7).all() and (outs[r][:shift] == -7).all()
+    # all-gather of the first n floats of every rank
+    reset()
+    run(1, 0, s_ptr, o_ptr, 3)
+    want = torch.cat([x[:n] for x in src])
+    for o in outs:
+        assert torch.equal(o[shift:shift + n * world], want) and (o[shift + n * world:] == -7).all()
+    # gather to the root only
+    reset()
+    run(2, root, s_ptr, VP(*[outs[r][shift:].data_ptr() if r == root else None for r in range(world)]), 5)
+    assert torch.equal(outs[root][shift:shift + n * world], want)
+    assert all((outs[r] == -7).all() for r in range(world) if r != root)
+    # scatter from rank 0
+    reset()
+    run(3, 0, VP(*[src[0].data_ptr() if r == 0 else None for r in range(world)]), o_ptr, 7)
+    for r in range(world):
+        assert torch.equal(outs[r][shift:shift + n], src[0][r * n:(r + 1) * n]) and (outs[r][shift + n:] == -7).all()
+    # reduce-scatter (sum) and reduce (max) to the root
+    reset()
+    run(4, 0, s_ptr, o_ptr, 9)
+    tot = torch.stack([x[:n * world] for x in src]).sum(0)
+    for r in range(world):
+        assert torch.allclose(outs[r][shift:shift + n], tot[r * n:(r + 1) * n], atol=1e-5)
+    reset()
+    run(5, root, s_ptr, VP(*[outs[r][shift:].data_ptr() if r == root else None for r in range(world)]), 11, op=3)
+    assert torch.equal(outs[root][shift:shift + n], torch.stack([x[:n] for x in src]).max(0).values)
+    assert (outs[root][shift + n:] == -7).all()
+    del none
+    for a in arenas:
+        a.close()
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     """A handshake whose peer never signals gives up after the configured bound and reports it."""
     from ferrum_b200 import _lib
@@ -303,3 +370,35 @@ def test_single_rank_engine_overlaps_optimizer_and_matches_plain_training():
         for a, b in zip(ref.torch_parameters(), eng_model.torch_parameters()):
             assert torch.allclose(a, b, atol=2e-3, rtol=2e-2), (a - b).abs().max().item()
         eng.shutdown()
+
+
+def test_guard_bands_around_the_engine_arena_detect_a_stray_write(monkeypatch):
+    """FERRUM_GUARD_BANDS=1: pattern-filled bands around the parameter / gradient / bf16 regions stay intact over
+    training steps, and a write into one of them (made from the host side here) is reported with its position."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+    from ferrum_b200.parallel import Backend, DistributedDataParallel, InternalError, ProcessGroup
+
+    monkeypatch.setenv("FERRUM_GUARD_BANDS", "1")
+    dev = fb.Device.Cuda(0)
+    torch.manual_seed(2)
+    model = nn.Sequential(nn.Linear(64, 256, device=dev), nn.GELU(), nn.LayerNorm([256], device=dev),
+                          nn.Linear(256, 10, device=dev))
+    opt = optim.Adam(model.parameters(), optim.AdamConfig(lr=1e-2))
+    eng = DistributedDataParallel(model, ProcessGroup(Backend.Nvlink, 0, 1)).bucket_size_mb(0.1)
+    eng.fuse_optimizer(opt)
+    x = torch.randn(96, 64, device="cuda")
+    y = torch.randint(0, 10, (96,), device="cuda")
+    for _ in range(3):
+        opt.zero_grad()
+        with fb.autocast():
+            loss = nn.cross_entropy(eng(x), y)
+        loss.backward()
+        opt.step()
+    assert eng.check_guard_bands() == 4
+    name, band = eng._guards[1]
+    band[123] = 7  # what a kernel writing past the end of the parameter region would do
+    with pytest.raises(InternalError, match="byte 123"):
+        eng.check_guard_bands()
+    band[123] = 0xA5
+    eng.shutdown()
