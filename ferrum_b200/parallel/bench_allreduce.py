@@ -17,6 +17,57 @@ import statistics
 import torch
 
 
+def emulated(args):
+    """The fused all-reduce + Adam body with every rank's arena on this GPU: device time per bucket size and the
+    local-memory bandwidth it reaches (world reads of the gradients + parameter, moment and bf16 traffic)."""
+    from ferrum_b200 import _lib
+    from ferrum_b200._lib_dist import DistCtx
+    from ferrum_b200.parallel.symm import SymmetricArena
+    from ferrum_b200.utils import runtime as rt
+
+    world = args.emulated
+    lib = _lib.cuda()
+    max_elems = int(args.max_mb * (1 << 20)) // 4 // (4 * world) * (4 * world)
+    arenas = SymmetricArena.emulated(max_elems * 10, world)
+    ctxs = (DistCtx * world)(*[a.ctx for a in arenas])
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + max_elems * 4, base + max_elems * 8
+    for a in arenas:
+        a.view(off_p, (max_elems,), torch.float32).normal_()
+        a.view(off_g, (max_elems,), torch.float32).normal_(0, 1e-2)
+    per = max_elems // world + 4
+    ms_ = [torch.zeros(per, device="cuda") for _ in range(world)]
+    vs_ = [torch.zeros(per, device="cuda") for _ in range(world)]
+    mp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in ms_])
+    vp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in vs_])
+    stream = torch.cuda.current_stream().cuda_stream
+    blocks = max(1, min(args.blocks, 128 // world))  # world x blocks must be co-resident (cooperative launch)
+    epoch, n = 1, max_elems
+    ts = []
+    for i in range(args.iters + 3):
+        t = i + 1
+        h = _lib.AdamH(3e-4, 0.9, 0.999, 1e-8, 0.0, 1 - 0.9 ** t, 1 - 0.999 ** t, 1.0 / world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = lib.fb_dist_allreduce_emulated(ctxs, world, 2, 0, epoch, off_g, off_p, off_s, n, 0, 1.0,
+                                            ctypes.byref(h), None, mp, vp, 1, blocks, args.threads, stream)
+        e1.record()
+        assert rc == 0, rc
+        epoch += 2
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(e0.elapsed_time(e1))
+    rt.check_status()
+    ms = statistics.median(ts)
+    # per element over all virtual ranks: world gradient reads, 1 parameter read, 2 + 2 moment accesses,
+    # world parameter writes and world bf16 writes
+    moved = n * (4 * world + 4 + 16 + 4 * world + 2 * world)
+    print(json.dumps({"kernel": "allreduce_emulated_kernel<adam>", "world": world, "bucket_bytes": n * 4,
+                      "blocks_per_rank": blocks, "ms": ms, "local_GBps": moved / 1e9 / (ms / 1e3)}), flush=True)
+    for a in arenas:
+        a.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=float, default=1024.0)
@@ -25,7 +76,12 @@ def main():
     ap.add_argument("--threads", type=int, default=256)
     ap.add_argument("--shard-master", action="store_true", help="publish only the bf16 copy to peers")
     ap.add_argument("--out", default="")
+    ap.add_argument("--emulated", type=int, default=0, metavar="W",
+                    help="one process, one GPU: W ranks emulated by one cooperative launch of the same device code "
+                         "(all 'peer' loads stay on this GPU); the form that a profiler may wrap")
     args = ap.parse_args()
+    if args.emulated:
+        return emulated(args)
 
     import torch.distributed as dist
 

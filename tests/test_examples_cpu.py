@@ -37,3 +37,19 @@ def test_feature_tour_runs(capsys):
     out = capsys.readouterr().out
     for word in ("conv + pool", "LSTM", "attention", "embedding", "batch sizes"):
         assert word in out
+
+
+def test_ddp_example_runs_as_two_gloo_ranks(tmp_path):
+    """The data-parallel example as two CPU processes over gloo: both ranks finish and the loss falls."""
+    import subprocess
+    import sys
+
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29733", os.path.join(EX, "train_ddp_mlp.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("world 2:")]
+    assert line, r.stdout[-2000:]
+    first, last = (float(v) for v in line[0].split("loss")[1].split("after")[0].split("->"))
+    assert last < first
