@@ -25,6 +25,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--act", default=None)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--simt", action="store_true",
+                    help="the exact-fp32 SIMT kernel (FFMA pipe; compared with cuBLAS fp32 without TF32)")
     ap.add_argument("--tf32", action="store_true", help="fp32 operands on the tensor cores (kind::tf32, fp32 output)")
     ap.add_argument("--prof", action="store_true",
                     help="CTA-pair kernel: report where the MMA thread waits (drained accumulator / operands) and how long "
@@ -35,7 +37,7 @@ def main():
     a = ap.parse_args()
 
     from ferrum_b200.ops import gemm as _g
-    from ferrum_b200.ops.gemm import gemm_bf16, gemm_tf32
+    from ferrum_b200.ops.gemm import gemm_bf16, gemm_f32, gemm_tf32
 
     _g.set_gemm_2cta(a.two_cta)
     from ferrum_b200.utils.runtime import check_status
@@ -47,8 +49,9 @@ def main():
         torch.bfloat16)
     B = torch.randn(K, N, device="cuda").to(torch.bfloat16).t() if b_mn else torch.randn(N, K, device="cuda").to(
         torch.bfloat16)
-    out = torch.empty(M, N, device="cuda", dtype=torch.float32 if (a.layout == "tn" or a.tf32) else torch.bfloat16)
-    if a.tf32:
+    out = torch.empty(M, N, device="cuda",
+                      dtype=torch.float32 if (a.layout == "tn" or a.tf32 or a.simt) else torch.bfloat16)
+    if a.tf32 or a.simt:
         A, B = A.float().t().contiguous().t() if a_mn else A.float(), B.float().t().contiguous().t() if b_mn else B.float()
     bias = torch.randn(N, device="cuda") if a.bias else None
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -69,7 +72,9 @@ def main():
         return ts[len(ts) // 2]
 
     aux = torch.empty_like(out) if a.dual else None
-    if a.tf32:
+    if a.simt:
+        ms = timeit(lambda: gemm_f32(A, B, bias=bias, act=a.act, out=out))
+    elif a.tf32:
         ms = timeit(lambda: gemm_tf32(A, B, bias=bias, act=a.act, out=out, kernel="2cta" if a.two_cta else "1cta"))
     else:
         ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
@@ -78,16 +83,22 @@ def main():
     if a.two_cta:
         ref = (A[:256].float() @ B.float().t())
         res_err = (out[:256].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
-    res = {"kernel": ("gemm_tf32_tcgen05_2cta" if a.two_cta else "gemm_tf32_tcgen05") if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+    res = {"kernel": "gemm_f32_simt" if a.simt else ("gemm_tf32_tcgen05_2cta" if a.two_cta else "gemm_tf32_tcgen05") if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
            "tflops": flops / ms / 1e9}
     if a.two_cta:
         res["rel_err_first_rows"] = res_err
+    if a.simt:
+        ref = (A[:256].double() @ B.double().t()).float()
+        res["rel_err_first_rows"] = (out[:256] - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        # FFMA ceiling of this GPU: SMs x 128 lanes x 2 flops x clock (the clock is whatever the run gets)
+        res["ffma_peak_tflops_at_max_clock"] = 148 * 128 * 2 * 1.965e9 / 1e12
     peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                          "MEASURED_PEAKS.json")
     if os.path.exists(peaks):
         pk = json.load(open(peaks))
         res["frac_of_measured_bf16_burst"] = res["tflops"] / pk["bf16_tflops"]
     if a.cublas:
+        torch.backends.cuda.matmul.allow_tf32 = False
         if a.tf32:
             torch.backends.cuda.matmul.allow_tf32 = True  # compare against cuBLAS' TF32 path, not its fp32 SIMT one
         Ac, Bc = A.contiguous(), B.contiguous()

@@ -130,6 +130,34 @@ def _cases(small: bool):
     gsc = optim.GradScaler.with_scale(2.0)
     case("amp_unscale_check", lambda: gsc.unscale_gradients([pp]), P * 8, "K17")
     case("amp_clip_grad_norm", lambda: optim.clip_grad_norm([pp], 1e9), P * 4, "K17 (sum of squares pass)")
+
+    # secondary layers: recurrent gate kernels, convolution window matrix, pooling, attention
+    Bq, Hq = (2048 if small else 8192), 1024
+    xi4, hh4 = torch.randn(Bq, 4 * Hq, device=dev), torch.randn(Bq, 4 * Hq, device=dev)
+    cprev = torch.randn(Bq, Hq, device=dev)
+    case("lstm_gates_fwd_f32", lambda: F.lstm_gates(xi4, hh4, cprev), Bq * Hq * 4 * (8 + 1 + 2 + 4),
+         "K15 (2 x [B,4H] + c read; h, c, 4 gate activations written)")
+    xi3, hh3 = torch.randn(Bq, 3 * Hq, device=dev), torch.randn(Bq, 3 * Hq, device=dev)
+    case("gru_gates_fwd_f32", lambda: F.gru_gates(xi3, hh3, cprev), Bq * Hq * 4 * (6 + 1 + 1 + 3),
+         "K15 (2 x [B,3H] + h read; h' and r, z, n written)")
+    img = torch.randn(16 if small else 64, 64, 56, 56, device=dev)
+    case("im2col_3x3_f32", lambda: F.im2col(img, (3, 3), (1, 1), (1, 1), (1, 1)),
+         img.numel() * 4 * (1 + 9), "K14 (input read once, 9x window matrix written)")
+    case("maxpool2d_2x2_f32", lambda: F.pool2d(img, (2, 2), (2, 2), "max"), img.numel() * 4 * 1.25 + img.numel(),
+         "K14 (input read, quarter-size output + int32 argmax written)")
+    Ba, Ha, Sa, Da = (2 if small else 8), 16, 1024, 64
+    qa = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)
+    ka = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)
+    va = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)
+
+    def attn():
+        import ferrum_b200 as fb
+        with fb.autocast():
+            p_ = F.softmax(F.bmm_scaled(qa, ka.transpose(-1, -2), Da ** -0.5), -1)
+            return F.bmm_scaled(p_, va, 1.0, heads_inner=True)
+
+    case("attention_fwd_bf16_S1024_D64", attn, Ba * Ha * Sa * Sa * 2 * 4 + 4 * Ba * Ha * Sa * Da * 2,
+         "K16 (batched tcgen05 QK^T, row softmax, batched PV; bytes = score matrix written + read twice + q, k, v, o)")
     return cases
 
 

@@ -89,6 +89,41 @@ def test_gemm_f32_simt(ta, tb):
     assert torch.allclose(out, ref, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 16), (64, 64, 20), (300, 520, 100), (257, 132, 64), (1000, 1024, 516)])
+def test_gemm_f32_simt_fast_path(ta, tb, M, N, K):
+    """The register-tiled fp32 kernel (regular operands: unit stride along K or along M / N, 16-byte aligned
+    pitch) against a float64 product, with bias, activation and accumulation, ragged edges in every dimension."""
+    from ferrum_b200.ops.gemm import gemm_f32
+
+    torch.manual_seed(M + N + K)
+    a = torch.randn(K, M, device="cuda").t() if ta else torch.randn(M, K, device="cuda")
+    b = torch.randn(K, N, device="cuda").t() if tb else torch.randn(N, K, device="cuda")
+    bias = torch.randn(N, device="cuda")
+    ref = (a.double() @ b.double().t())
+    out = gemm_f32(a, b)
+    assert (out - ref.float()).abs().max().item() < 2e-4 * K ** 0.5
+    out = gemm_f32(a, b, bias=bias, act="relu")
+    assert (out - torch.relu(ref + bias).float()).abs().max().item() < 2e-4 * K ** 0.5
+    acc = torch.ones(M, N, device="cuda")
+    gemm_f32(a, b, out=acc, accumulate=True)
+    assert (acc - (1 + ref).float()).abs().max().item() < 2e-4 * K ** 0.5
+
+
+def test_gemm_f32_simt_fast_path_batched_and_strided_output():
+    from ferrum_b200.ops.gemm import gemm_f32
+
+    torch.manual_seed(8)
+    a = torch.randn(3, 130, 64, device="cuda")
+    b = torch.randn(3, 96, 64, device="cuda")
+    out = gemm_f32(a, b)
+    assert torch.allclose(out, a @ b.transpose(1, 2), atol=2e-4, rtol=1e-4)
+    wide = torch.zeros(130, 200, device="cuda")
+    gemm_f32(a[0], b[0], out=wide[:, 8:104])  # row pitch 200, column offset 8: 16-byte aligned, not contiguous
+    assert torch.allclose(wide[:, 8:104], a[0] @ b[0].t(), atol=2e-4, rtol=1e-4)
+    assert wide[:, :8].abs().sum().item() == 0 and wide[:, 104:].abs().sum().item() == 0
+
+
 def test_gemm_f32_batched():
     from ferrum_b200.ops.gemm import gemm_f32
 
