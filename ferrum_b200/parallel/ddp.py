@@ -117,7 +117,11 @@ class DistributedDataParallel(Module, GradSink):
         self._advanced = False        # the optimizer's device scalars were advanced in this step
         self._shard_master = os.environ.get("FERRUM_SHARD_MASTER", "0") == "1"
         self._master_stale = False
-        self._comm_blocks = int(os.environ.get("FERRUM_COMM_BLOCKS", "128"))
+        # Blocks of a bucket kernel.  A rank updates 1 / world of every bucket, so two ranks want many blocks
+        # (measured: 6.9 ms/step with 128 vs 7.4 with 48) while at four and eight ranks more blocks only take
+        # issue slots and memory bandwidth from the GEMMs they run beside (7.1 with 48 vs 7.3 - 7.7 with 128).
+        env_blocks = os.environ.get("FERRUM_COMM_BLOCKS")
+        self._comm_blocks = int(env_blocks) if env_blocks else (128 if self._pg.world_size() <= 2 else 48)
         self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
         if optimizer is not None:
             self.fuse_optimizer(optimizer)
@@ -173,8 +177,10 @@ class DistributedDataParallel(Module, GradSink):
         st = torch.cuda.current_stream().cuda_stream
         for bk in self.buckets:
             per = bk.length // world
-            e = a.next_epoch(2)
-            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 6, 2, e, 0, self._off_param + bk.start * 4, 0,
+            # channel 3: its epochs are only ever advanced from the host.  The bucket kernels' channel (2) is
+            # advanced on the device when a recorded step is replayed, so a host-side epoch for it can be stale.
+            e = a.next_epoch(3)
+            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 6, 3, e, 0, self._off_param + bk.start * 4, 0,
                                                       per * 4, 0, 1.0, 32, st), "fb_dist_collective")
         self._master_stale = False
 
@@ -474,8 +480,8 @@ class DistributedDataParallel(Module, GradSink):
         if self._use_native:
             a = self._arena
             torch.cuda.current_stream().synchronize()
-            e = a.next_epoch(2)
-            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 0, 2, e, 0, self._off_param, self._off_param,
+            e = a.next_epoch(3)  # host-advanced channel (see sync_master_weights)
+            _lib.check(_lib.cuda().fb_dist_collective(a.ctx, 0, 3, e, 0, self._off_param, self._off_param,
                                                       self._total * 4, 0, 1.0, 32,
                                                       torch.cuda.current_stream().cuda_stream), "fb_dist_collective")
             self._refresh_shadow()
