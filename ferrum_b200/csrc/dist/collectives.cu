@@ -530,13 +530,18 @@ __device__ void collective_body(const fb_dist_ctx& c, int vblock, int nvblocks, 
       if (c.rank != a.root) break;
       // fallthrough
     case FB_COLL_ALL_GATHER:
-      for (int p = 0; p < c.world; ++p)
+      // every rank starts with a different source (its right-hand neighbour), so that at any moment each GPU's
+      // outbound links serve one reader instead of all of them at once
+      for (int i = 0; i < c.world; ++i) {
+        const int p = (c.rank + 1 + i) % c.world;
         copy_bytes(c.arena[p] + a.in_off, out + p * a.n_bytes, a.n_bytes, tid, stride);
+      }
       break;
     case FB_COLL_ALL_GATHER_INPLACE:
-      for (int p = 0; p < c.world; ++p)
-        if (p != c.rank)
-          copy_bytes(c.arena[p] + a.in_off + p * a.n_bytes, self + a.in_off + p * a.n_bytes, a.n_bytes, tid, stride);
+      for (int i = 0; i + 1 < c.world; ++i) {
+        const int p = (c.rank + 1 + i) % c.world;
+        copy_bytes(c.arena[p] + a.in_off + p * a.n_bytes, self + a.in_off + p * a.n_bytes, a.n_bytes, tid, stride);
+      }
       break;
     case FB_COLL_SCATTER:
       copy_bytes(c.arena[a.root] + a.in_off + c.rank * a.n_bytes, out, a.n_bytes, tid, stride);

@@ -14,6 +14,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
 #include "../include/ferrum_kernels.h"
 
 namespace fb {
@@ -148,6 +150,69 @@ __global__ void im2col_kernel(const float* __restrict__ x, T* __restrict__ cols,
       cols[row * ldk + k] = __float2bfloat16_rn(v);
     else
       cols[row * ldk + k] = v;
+  }
+}
+
+// Same result, organised so that index arithmetic is paid once per row and once per four columns: a warp owns one
+// output position (row of the window matrix), decomposes it into (b, oh, ow) once, and its lanes walk the K columns
+// in groups of four — (c, ki, kj) of the group's first column by two 32-bit divisions, the next three by
+// increment-with-carry — and store 16 bytes (fp32) or 8 bytes (bf16) at a time.  The element-per-thread kernel above
+// spends seven 64-bit divisions per element and reached 8 % of the memory rate; it remains for pitches or pointers
+// that rule out vector stores.
+template <typename T>
+__global__ void __launch_bounds__(256)
+im2col_rows_kernel(const float* __restrict__ x, T* __restrict__ cols, ConvGeom g, long long ldk, long long rows) {
+  const int Kc = g.C * g.kh * g.kw;
+  const int khw = g.kh * g.kw;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long plane = static_cast<long long>(g.H) * g.W;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const unsigned hw = static_cast<unsigned>(g.Ho) * g.Wo;
+    const unsigned b = static_cast<unsigned>(row / hw);
+    const unsigned l = static_cast<unsigned>(row - static_cast<long long>(b) * hw);
+    const int oh = static_cast<int>(l / static_cast<unsigned>(g.Wo));
+    const int ow = static_cast<int>(l - static_cast<unsigned>(oh) * g.Wo);
+    const int ih0 = oh * g.sh - g.ph, iw0 = ow * g.sw - g.pw;
+    const float* xb = x + static_cast<long long>(b) * g.C * plane;
+    T* out = cols + row * ldk;
+    for (int k = lane * 4; k < Kc; k += 128) {
+      int c = static_cast<unsigned>(k) / static_cast<unsigned>(khw);
+      const int rem = k - c * khw;
+      int ki = static_cast<unsigned>(rem) / static_cast<unsigned>(g.kw);
+      int kj = rem - ki * g.kw;
+      float v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int ih = ih0 + ki * g.dh, iw = iw0 + kj * g.dw;
+        v[q] = 0.f;
+        if (k + q < Kc && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v[q] = __ldg(xb + c * plane + ih * g.W + iw);
+        if (++kj == g.kw) {
+          kj = 0;
+          if (++ki == g.kh) {
+            ki = 0;
+            ++c;
+          }
+        }
+      }
+      if (k + 3 < Kc) {
+        if constexpr (sizeof(T) == 2) {
+          const __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+          uint2 w;
+          w.x = *reinterpret_cast<const uint32_t*>(&p0);
+          w.y = *reinterpret_cast<const uint32_t*>(&p1);
+          *reinterpret_cast<uint2*>(out + k) = w;
+        } else {
+          *reinterpret_cast<float4*>(out + k) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+      } else {
+        for (int q = 0; q < 4 && k + q < Kc; ++q) {
+          if constexpr (sizeof(T) == 2) out[k + q] = __float2bfloat16_rn(v[q]);
+          else out[k + q] = v[q];
+        }
+      }
+    }
   }
 }
 
@@ -288,6 +353,18 @@ extern "C" int fb_im2col(const float* x, void* cols, int B, int C, int H, int W,
   const long long total = static_cast<long long>(B) * Ho * Wo * C * kh * kw;
   if (total <= 0) return 0;
   const ConvGeom g = geom(B, C, H, W, kh, kw, Ho, Wo, sh, sw, ph, pw, dh, dw);
+  const long long rows = static_cast<long long>(B) * Ho * Wo;
+  const int esz = out_dtype == FB_DT_BF16 ? 2 : 4;
+  // warp-per-row kernel: needs vector stores to be legal (pitch and base multiples of 4 elements)
+  if (ldk % 4 == 0 && (reinterpret_cast<uintptr_t>(cols) % (4 * esz)) == 0 && static_cast<long long>(Ho) * Wo < (1LL << 31) &&
+      static_cast<long long>(C) * H * W < (1LL << 31)) {
+    const int grid = grid_for(rows * 32, 256);
+    if (out_dtype == FB_DT_BF16)
+      im2col_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(x, static_cast<__nv_bfloat16*>(cols), g, ldk, rows);
+    else
+      im2col_rows_kernel<float><<<grid, 256, 0, st>>>(x, static_cast<float*>(cols), g, ldk, rows);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (out_dtype == FB_DT_BF16)
     im2col_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>(x, static_cast<__nv_bfloat16*>(cols), g, ldk);
   else

@@ -103,6 +103,22 @@ def test_im2col_rows_are_gemm_ready():
     _close(cols, ref.transpose(1, 2).reshape(cols.shape), 0)
 
 
+@pytest.mark.parametrize("C,k,stride,pad,dil", [(4, (3, 3), (1, 1), (1, 1), (1, 1)), (8, (3, 3), (2, 1), (0, 2), (1, 2)),
+                                                 (2, (3, 2), (1, 2), (1, 0), (2, 1)), (12, (1, 1), (1, 1), (0, 0), (1, 1)),
+                                                 (5, (2, 2), (1, 1), (1, 1), (1, 1)), (16, (5, 5), (2, 2), (2, 2), (1, 1))])
+def test_im2col_warp_per_row_kernel_matches_unfold(C, k, stride, pad, dil):
+    """Window matrices whose row length is a multiple of 4 take the warp-per-row kernel (vector stores, index
+    arithmetic once per four columns); every geometry must reproduce torch's unfold exactly."""
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(C)
+    x = torch.randn(3, C, 19, 14, device="cuda")
+    cols = F.im2col(x, k, stride, pad, dil)
+    ref = torch.nn.functional.unfold(x, k, dilation=dil, padding=pad, stride=stride)
+    assert cols.shape == (3 * ref.shape[2], C * k[0] * k[1])
+    assert torch.equal(cols, ref.transpose(1, 2).reshape(cols.shape))
+
+
 @pytest.mark.parametrize("op", ["max", "avg"])
 @pytest.mark.parametrize("k,s", [(2, 2), (3, 2), (3, 1)])
 def test_pool2d_forward_backward(op, k, s):
