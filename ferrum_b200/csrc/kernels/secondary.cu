@@ -222,9 +222,11 @@ __global__ void col2im_kernel(const float* __restrict__ dcols, float* __restrict
   const long long total = static_cast<long long>(g.B) * g.C * g.H * g.W;
   for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
        e += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int iw = static_cast<int>(e % g.W), ih = static_cast<int>((e / g.W) % g.H);
-    const int c = static_cast<int>((e / (static_cast<long long>(g.W) * g.H)) % g.C);
-    const int b = static_cast<int>(e / (static_cast<long long>(g.W) * g.H * g.C));
+    const unsigned hw = static_cast<unsigned>(g.H) * g.W;
+    const long long bcq = e / hw;  // b * C + c
+    const unsigned l = static_cast<unsigned>(e - bcq * hw);
+    const int ih = static_cast<int>(l / static_cast<unsigned>(g.W)), iw = static_cast<int>(l - (l / g.W) * g.W);
+    const int b = static_cast<int>(bcq / g.C), c = static_cast<int>(bcq - static_cast<long long>(b) * g.C);
     float acc = 0.f;
     for (int ki = 0; ki < g.kh; ++ki) {
       const int th = ih + g.ph - ki * g.dh;
@@ -251,8 +253,11 @@ __global__ void pool2d_fwd_kernel(const float* __restrict__ x, float* __restrict
   const long long total = static_cast<long long>(g.B) * g.C * g.Ho * g.Wo;
   for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
        e += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int ow = static_cast<int>(e % g.Wo), oh = static_cast<int>((e / g.Wo) % g.Ho);
-    const long long bc = e / (static_cast<long long>(g.Wo) * g.Ho);
+    // one 64-bit and one 32-bit division per element instead of three 64-bit ones
+    const unsigned hw = static_cast<unsigned>(g.Ho) * g.Wo;
+    const long long bc = e / hw;
+    const unsigned l = static_cast<unsigned>(e - bc * hw);
+    const int oh = static_cast<int>(l / static_cast<unsigned>(g.Wo)), ow = static_cast<int>(l - (l / g.Wo) * g.Wo);
     const float* plane = x + bc * g.H * g.W;
     float best = -INFINITY, sum = 0.f;
     int besti = 0;
@@ -282,8 +287,10 @@ __global__ void pool2d_bwd_kernel(const float* __restrict__ dy, const int* __res
   const float inv = 1.f / static_cast<float>(g.kh * g.kw);
   for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
        e += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int iw = static_cast<int>(e % g.W), ih = static_cast<int>((e / g.W) % g.H);
-    const long long bc = e / (static_cast<long long>(g.W) * g.H);
+    const unsigned hw = static_cast<unsigned>(g.H) * g.W;
+    const long long bc = e / hw;
+    const unsigned l = static_cast<unsigned>(e - bc * hw);
+    const int ih = static_cast<int>(l / static_cast<unsigned>(g.W)), iw = static_cast<int>(l - (l / g.W) * g.W);
     const int me = ih * g.W + iw;
     float acc = 0.f;
     for (int ki = 0; ki < g.kh; ++ki) {
