@@ -41,6 +41,8 @@ def _sigs():
         "fb_dist_collective_staged": (I, [POINTER(DistCtx), I, I, U, I, LL, LL, I, F, P, P, I, P]),
         "fb_dist_collective_staged_emulated": (I, [POINTER(DistCtx), I, I, I, U, I, LL, LL, I, F, POINTER(c_void_p),
                                                    POINTER(c_void_p), I, P]),
+        "fb_gemm_bf16_2cta_push": (I, [P, P, I, I, I, LL, LL, LL, I, I, POINTER(DistCtx), LL, LL, LL, LL, I, P, P]),
+        "fb_dist_set_pushed_ranges": (I, [I, POINTER(ctypes.c_longlong), POINTER(ctypes.c_longlong)]),
         "fb_dist_barrier": (I, [POINTER(DistCtx), I, U, P]),
     }
 

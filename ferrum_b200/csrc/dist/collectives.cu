@@ -97,6 +97,11 @@ struct ArArgs {
   const float* stage_in;
   float* stage_out;
   long long n_valid;
+  // Ranges [lo, hi) of the bucket (elements, multiples of 4) whose gradients were PUSHED by the producing GEMMs:
+  // source rank s stored its values for shard o at element s * per + j of rank o's bucket region, so the owner
+  // finds all contributions in its own memory and reads no peer for them.
+  int n_pushed;
+  long long pushed_lo[4], pushed_hi[4];
   int streaming;       // local optimizer state moves with evict-first hints (ld/st.global.cs): it is touched once per
                        // step and should not displace the operand tiles of the GEMMs this kernel runs beside
 };
@@ -231,10 +236,25 @@ __device__ void allreduce_body(const fb_dist_ctx& c, int vblock, int nvblocks, c
       for (int u = 0; u < U; ++u) {
         const long long i4 = base + u * stride;
         if (i4 < n4) {
+          bool pushed = false;
+          if (a.n_pushed > 0) {
+            const long long e = lo + (i4 << 2);
 #pragma unroll
-          for (int r = 0; r < W; ++r)
-            if (r < c.world)
-              part[u][r] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + lo4 + i4);
+            for (int q = 0; q < 4; ++q) pushed |= (q < a.n_pushed && e >= a.pushed_lo[q] && e < a.pushed_hi[q]);
+          }
+          if (pushed) {
+            // contributions of all ranks already sit in this rank's memory, one slot of `per` elements per source
+            const float4* mine = reinterpret_cast<const float4*>(c.arena[c.rank] + a.grad_off);
+#pragma unroll
+            for (int r = 0; r < W; ++r)
+              if (r < c.world) part[u][r] = ptx::ld_relaxed_sys_f4(mine + r * (per >> 2) + i4);
+          } else {
+#pragma unroll
+            for (int r = 0; r < W; ++r)
+              if (r < c.world)
+                part[u][r] =
+                    ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + lo4 + i4);
+          }
         }
       }
 #pragma unroll
@@ -621,6 +641,21 @@ extern "C" int fb_dist_query_flag_bytes() { return FB_FLAG_BYTES; }
 extern "C" int fb_dist_query_max_blocks() { return FB_FLAG_BLOCKS; }
 extern "C" int fb_dist_query_channels() { return FB_FLAG_CHANNELS; }
 
+// Ranges of the NEXT fused all-reduce launched from this host thread whose gradients were pushed into the shard
+// owners' memory by the producing GEMMs (see ArArgs::pushed_lo).  Consumed by that launch.
+static thread_local int g_pending_pushed = 0;
+static thread_local long long g_pending_lo[4], g_pending_hi[4];
+extern "C" int fb_dist_set_pushed_ranges(int n, const long long* lo, const long long* hi) {
+  if (n < 0 || n > 4) return -1;
+  for (int i = 0; i < n; ++i) {
+    if ((lo[i] & 3) || (hi[i] & 3) || lo[i] < 0 || hi[i] < lo[i]) return -1;
+    g_pending_lo[i] = lo[i];
+    g_pending_hi[i] = hi[i];
+  }
+  g_pending_pushed = n;
+  return 0;
+}
+
 // Fused all-reduce of one gradient bucket.  `epoch` and `epoch + 1` are consumed on `channel`.
 // fuse: FB_FUSE_NONE (in-place all-reduce of the region at grad_off), FB_FUSE_SGD, FB_FUSE_ADAM.
 static int allreduce_impl(const fb_dist_ctx* ctx, int fuse, int use_mc, int channel, unsigned epoch,
@@ -652,6 +687,16 @@ static int allreduce_impl(const fb_dist_ctx* ctx, int fuse, int use_mc, int chan
   a.stage_in = stage_in;
   a.stage_out = stage_out;
   a.n_valid = n_valid;
+  a.n_pushed = g_pending_pushed;
+  for (int i = 0; i < g_pending_pushed; ++i) {
+    a.pushed_lo[i] = g_pending_lo[i];
+    a.pushed_hi[i] = g_pending_hi[i];
+  }
+  g_pending_pushed = 0;
+  if (a.n_pushed > 0) {
+    if (n % (4LL * ctx->world) != 0) return -4;  // slots of equal length need n = world * per
+    use_mc = 0;                                   // the switch-side reduction reads every rank's copy of the shard
+  }
   {
     static int streaming = -1;
     if (streaming < 0) {
@@ -734,6 +779,13 @@ extern "C" int fb_dist_allreduce_emulated(const fb_dist_ctx* ctxs, int world, in
   if (adam) a.adam = *adam;
   if (sgd) a.sgd = *sgd;
   a.publish_master = publish_master;
+  a.n_pushed = g_pending_pushed;
+  for (int i = 0; i < g_pending_pushed; ++i) {
+    a.pushed_lo[i] = g_pending_lo[i];
+    a.pushed_hi[i] = g_pending_hi[i];
+  }
+  g_pending_pushed = 0;
+  if (a.n_pushed > 0 && n % (4LL * world) != 0) return -4;
   void* args[] = {&pk, &a};
   const dim3 grid(world * nblocks), block(nthreads);
   const void* fn = fuse == FB_FUSE_ADAM  ? reinterpret_cast<const void*>(allreduce_emulated_kernel<FB_FUSE_ADAM>)

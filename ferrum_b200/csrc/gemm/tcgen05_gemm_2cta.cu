@@ -29,6 +29,7 @@
 
 #include "../common/ptx.cuh"
 #include "../common/status.h"
+#include "../dist/dist_ctx.h"
 #include "../include/ferrum_kernels.h"
 #include "epilogue.cuh"
 
@@ -69,6 +70,16 @@ struct Args2 {
   // accumulator, MMA thread waiting for operands, one epilogue warp busy, whole kernel.  NULL = off.
   unsigned long long* prof;
   int stream_stores;  // bf16 outputs leave with st.global.cs (evict-first) so they do not displace operand tiles in L2
+  // Push mode (weight gradients of a data-parallel job): instead of a local fp32 matrix, every 16-byte piece of the
+  // result goes straight to the rank that OWNS it — element e of the bucket belongs to shard o = e / per, and
+  // source rank s deposits its value at element s * per + (e - o * per) of rank o's bucket region — over NVLink
+  // peer stores issued from this epilogue, so the gradient reduce-scatter travels while the next tiles are
+  // multiplied and the bucket kernel finds all contributions in local memory.  push_world <= 1: off.
+  int push_world, push_rank;
+  unsigned char* push_arena[8];
+  long long push_bucket_off;  // byte offset of the bucket's gradient region inside every arena
+  long long push_rel;         // bucket-relative element index of out[0][0] (multiple of 4)
+  long long push_per;         // elements per shard (multiple of 4)
 };
 
 unsigned long long* g_prof_buffer = nullptr;
@@ -360,6 +371,24 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
               for (int i = 0; i < 32; ++i)
                 if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
             }
+          } else if (p.push_world > 1) {
+            // one division per 32-column chunk, then (owner, offset) advance with the columns
+            const long long rel = p.push_rel + static_cast<long long>(row) * p.ldc + col0;
+            int owner = static_cast<int>(rel / p.push_per);
+            long long j = rel - static_cast<long long>(owner) * p.push_per;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (col0 + 4 * q < p.N) {  // N is a multiple of 4 in push mode
+                float4* dst = reinterpret_cast<float4*>(p.push_arena[owner] + p.push_bucket_off +
+                                                        (static_cast<long long>(p.push_rank) * p.push_per + j) * 4);
+                ptx::st_relaxed_sys_f4(dst, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+              }
+              j += 4;
+              if (j >= p.push_per) {
+                j -= p.push_per;
+                ++owner;
+              }
+            }
           } else {
             float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
@@ -485,6 +514,11 @@ int launch2(const void* a, const void* b, Args2& args, long long lda, long long 
 
 // Arguments every entry point fills the same way.
 void fill_common(Args2& args, int32_t* status) {
+  args.push_world = 0;
+  args.push_rank = 0;
+  args.push_bucket_off = args.push_rel = 0;
+  args.push_per = 4;
+  for (int i = 0; i < 8; ++i) args.push_arena[i] = nullptr;
   args.status = status;
   args.timeout_ns = 2000000000ull;
   static int stream_default = -1;
@@ -569,4 +603,51 @@ extern "C" int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, con
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   const long long tiles = static_cast<long long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
   return launch2<256, true>(a, b, args, lda, ldb, pairs, tiles, stream);
+}
+
+// Weight-gradient GEMM of a data-parallel job with the reduce-scatter fused into the epilogue (see Args2::push_*):
+// result[M, N] = A * B^T in fp32, every 16-byte piece stored into the bucket region of the rank that owns it.
+// ctx: this rank's view of all arenas; bucket_off: byte offset of the bucket's gradient region in every arena;
+// out_rel: bucket-relative element index of result[0][0]; ldc: row pitch of the result inside the bucket (elements);
+// per: elements per shard (bucket length / world).  N, ldc, out_rel and per must be multiples of 4 and the result
+// must lie inside the bucket.  Returns -3 where CTA pairs cannot be launched.
+extern "C" int fb_gemm_bf16_2cta_push(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                                      long long ldc, int a_mn_major, int b_mn_major, const fb_dist_ctx* ctx,
+                                      long long bucket_off, long long out_rel, long long per, long long bucket_len,
+                                      int max_ctas, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (M <= 0 || N <= 0 || K <= 0 || ctx == nullptr || ctx->world < 2 || ctx->world > FB_MAX_RANKS ||
+      ctx->rank < 0 || ctx->rank >= ctx->world)
+    return -1;
+  if ((N & 3) || (ldc & 3) || (out_rel & 3) || (per & 3) || per <= 0 || (bucket_off & 15) || out_rel < 0 ||
+      ldc < N || bucket_len != per * ctx->world || out_rel + static_cast<long long>(M - 1) * ldc + N > bucket_len)
+    return -1;
+  for (int r = 0; r < ctx->world; ++r)
+    if (ctx->arena[r] == nullptr) return -1;
+  const int pairs_avail = max_pairs<256>();
+  if (pairs_avail <= 0) return -3;
+  Args2 args;
+  args.out = nullptr;
+  args.out2 = nullptr;
+  args.bias = nullptr;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.a_mn_major = a_mn_major;
+  args.b_mn_major = b_mn_major;
+  args.out_bf16 = 0;
+  args.act = FB_ACT_NONE;
+  args.beta = 0;
+  fill_common(args, status);
+  args.push_world = ctx->world;
+  args.push_rank = ctx->rank;
+  for (int r = 0; r < ctx->world; ++r) args.push_arena[r] = ctx->arena[r];
+  args.push_bucket_off = bucket_off;
+  args.push_rel = out_rel;
+  args.push_per = per;
+  int pairs = pairs_avail;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  const long long tiles = static_cast<long long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
+  return launch2<256>(a, b, args, lda, ldb, pairs, tiles, stream);
 }

@@ -607,6 +607,17 @@ class GradSink:
         raise NotImplementedError
 
 
+def _wgrad_to_sink(sink, weight_ref, g_t: torch.Tensor, x_t: torch.Tensor, low: bool) -> None:
+    """dW = g_t @ x_t^T written where the sink wants it: pushed to the shard owners from the GEMM epilogue when the
+    sink supports that (data-parallel engine in push mode, bf16 operands), else into the sink's buffer."""
+    push = getattr(sink, "try_push", None)
+    if push is not None and low and g_t.dtype == torch.bfloat16 and x_t.dtype == torch.bfloat16 and push(
+            weight_ref, g_t, x_t):
+        return
+    buf, acc = sink.acquire(weight_ref)
+    _gemm_nt(g_t, x_t, low=low, out=buf, out_dtype=torch.float32, accumulate=acc)
+
+
 class _LinearFn(Function):
     @staticmethod
     def forward(ctx, x, weight, bias, act, low, w_low, sink):
@@ -651,8 +662,7 @@ class _LinearFn(Function):
         if ctx.needs_input_grad[1]:
             sink = ctx.sink
             if sink is not None:
-                buf, acc = sink.acquire(ctx.weight_ref)
-                _gemm_nt(g2.t(), x2.t(), low=low, out=buf, out_dtype=torch.float32, accumulate=acc)
+                _wgrad_to_sink(sink, ctx.weight_ref, g2.t(), x2.t(), low)
             else:
                 gw = _gemm_nt(g2.t(), x2.t(), low=low, out_dtype=torch.float32)
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -823,8 +833,7 @@ class _LinearActNormFn(Function):
             gx = raw_cast(_gemm_nt(dz, ws.t(), low=low), ctx.x_dtype).reshape(*ctx.lead, ws.shape[1])
         if ctx.needs_input_grad[1]:
             if ctx.sink is not None:
-                buf, acc = ctx.sink.acquire(ctx.weight_ref)
-                _gemm_nt(dz.t(), xs.t(), low=low, out=buf, out_dtype=torch.float32, accumulate=acc)
+                _wgrad_to_sink(ctx.sink, ctx.weight_ref, dz.t(), xs.t(), low)
                 ctx.sink.ready(ctx.weight_ref)
             else:
                 gw = _gemm_nt(dz.t(), xs.t(), low=low, out_dtype=torch.float32)

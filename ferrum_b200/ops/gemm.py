@@ -101,6 +101,33 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     return out
 
 
+def push_operands_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when ``a @ b^T`` can run on the CTA-pair kernel with the pushing epilogue."""
+    return (_use_2cta and bf16_operand_ok(a) and bf16_operand_ok(b) and a.shape[0] >= 512 and b.shape[0] >= 128
+            and b.shape[0] % 4 == 0)
+
+
+def gemm_bf16_push(a: torch.Tensor, b: torch.Tensor, ctx, bucket_off: int, out_rel: int, per: int,
+                   bucket_len: int) -> bool:
+    """``a[M,K] @ b[N,K]^T`` in fp32 with the gradient reduce-scatter fused into the epilogue: every 16-byte piece
+    of the result is stored over NVLink into the bucket region of the rank that owns it (element ``e`` of the
+    bucket belongs to shard ``e // per``; this rank's value lands in its slot of that shard).  ``ctx`` is the
+    arena context (``SymmetricArena.ctx``), ``bucket_off`` the byte offset of the bucket's gradient region,
+    ``out_rel`` the bucket-relative element index of the result's first element (row pitch = N).  Returns False
+    where CTA pairs cannot be launched (the caller then takes the ordinary path)."""
+    M, K = a.shape
+    N = b.shape[0]
+    a_mn, lda = _major(a)
+    b_mn, ldb = _major(b)
+    rc = _lib.cuda().fb_gemm_bf16_2cta_push(a.data_ptr(), b.data_ptr(), M, N, K, lda, ldb, N, a_mn, b_mn, ctx,
+                                            bucket_off, out_rel, per, bucket_len, _max_ctas, _rt.status_ptr(),
+                                            _stream())
+    if rc == -3:
+        return False
+    _lib.check(rc, "fb_gemm_bf16_2cta_push")
+    return True
+
+
 def tf32_operand_ok(t: torch.Tensor) -> bool:
     """True when a 2-D fp32 tensor can be described by a TMA map (either major): 16-byte aligned base and pitch."""
     if t.dtype != torch.float32 or t.dim() != 2 or t.data_ptr() % 16:

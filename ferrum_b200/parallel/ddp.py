@@ -117,6 +117,10 @@ class DistributedDataParallel(Module, GradSink):
         self._advanced = False        # the optimizer's device scalars were advanced in this step
         self._shard_master = os.environ.get("FERRUM_SHARD_MASTER", "0") == "1"
         self._master_stale = False
+        # Push mode: the weight-gradient GEMMs store their results straight into the shard owners' memory.
+        self._push = os.environ.get("FERRUM_GEMM_PUSH", "0") == "1"
+        self._pushed = []
+        self._pushed_params = set()
         # Blocks of a bucket kernel.  A rank updates 1 / world of every bucket, so two ranks want many blocks
         # (measured: 6.9 ms/step with 128 vs 7.4 with 48) while at four and eight ranks more blocks only take
         # issue slots and memory bandwidth from the GEMMs they run beside (7.1 with 48 vs 7.3 - 7.7 with 128).
@@ -165,6 +169,52 @@ class DistributedDataParallel(Module, GradSink):
         """
         self._shard_master = bool(flag)
         return self
+
+    def push_gradients(self, flag: bool = True) -> "DistributedDataParallel":
+        """Fuse the gradient reduce-scatter into the weight-gradient GEMMs: the epilogue of each (bf16, CTA-pair
+        sized) wgrad GEMM stores every 16-byte piece of dW over NVLink into the bucket region of the rank that owns
+        it, so the transfer overlaps the following tiles and the bucket kernel reads only local memory for those
+        ranges.  In this mode ``param.grad`` of such a weight holds no usable values on any rank (the owner's
+        region contains one slot per source rank), so gradient clipping or inspection of those tensors is not
+        available; a weight used twice in one step is not supported.  Off by default (``FERRUM_GEMM_PUSH=1``)."""
+        self._push = bool(flag)
+        return self
+
+    def try_push(self, param, a: torch.Tensor, b: torch.Tensor) -> bool:
+        """GradSink extension used by the Linear backward: run ``dW = a @ b^T`` with the pushing epilogue if this
+        parameter's gradient may be delivered that way.  Returns False when the ordinary path must be taken."""
+        # Needs the fused optimizer: a plain all-reduce writes its results back into the gradient region, where the
+        # other ranks' contribution slots live.
+        if not (self._push and getattr(self, "_use_native", False) and self._sync_enabled and self._opt is not None):
+            return False
+        world = self._pg.world_size()
+        if world < 2 or not _gemm.push_operands_ok(a, b):
+            return False
+        i = self._index[id(param)]
+        if self._written[i] or tuple(param.shape) != (a.shape[0], b.shape[0]):
+            return False
+        bi = self._bucket_of[i]
+        bk = self.buckets[bi]
+        # Only a bucket that holds this one tensor: the slot a source rank writes in the owner's region would
+        # otherwise alias the ordinarily laid-out gradients of the bucket's other tensors.
+        if bk.length % (4 * world) or len(bk.param_indices) != 1 or self._pushed[bi]:
+            return False
+        rel = self._offs[i] - bk.start
+        if rel % 4 or rel < 0 or rel + param.numel() > bk.length:
+            return False
+        if not _gemm.gemm_bf16_push(a, b, self._arena.ctx, self._off_grad + bk.start * 4, rel, bk.length // world,
+                                    bk.length):
+            return False
+        self._written[i] = True
+        self._pushed_params.add(i)
+        ranges = self._pushed[bi]
+        if ranges and ranges[-1][1] == rel:       # extends the previous range
+            ranges[-1] = (ranges[-1][0], rel + param.numel())
+        elif ranges and ranges[-1][0] == rel + param.numel():
+            ranges[-1] = (rel, ranges[-1][1])
+        else:
+            ranges.append((rel, rel + param.numel()))
+        return True
 
     def sync_master_weights(self) -> None:
         """All-gather the fp32 parameter shards so that every rank holds the full, current master weights."""
@@ -321,6 +371,9 @@ class DistributedDataParallel(Module, GradSink):
     # ------------------------------------------------------------------ GradSink (called from Linear backward)
     def acquire(self, param):
         i = self._index[id(param)]
+        if i in self._pushed_params:
+            raise CommunicationError("a weight whose gradient was pushed to its shard owners cannot receive a "
+                                     "second gradient in the same step (push_gradients(False) for such models)")
         o, n = self._offs[i], param.numel()
         acc = self._written[i]
         self._written[i] = True
@@ -349,6 +402,8 @@ class DistributedDataParallel(Module, GradSink):
         self._pending = [set(b.param_indices) for b in self.buckets]
         self._launched = [False] * len(self.buckets)
         self._written = [False] * len(self._params)
+        self._pushed = [[] for _ in self.buckets]
+        self._pushed_params = set()
         self._advanced = False
         self._sync_enabled = True
         for b in self.buckets:
@@ -402,6 +457,11 @@ class DistributedDataParallel(Module, GradSink):
                 raise CommunicationError(f"cannot fuse optimizer of type {type(opt).__name__}")
         e = a.next_epoch(2)
         use_mc = 1 if a.has_multicast() else 0
+        if self._pushed[b]:  # consumed by the launch below: these ranges are already complete in local memory
+            rng = self._pushed[b]
+            LLn = ctypes.c_longlong * len(rng)
+            _lib.check(lib.fb_dist_set_pushed_ranges(len(rng), LLn(*[r[0] for r in rng]), LLn(*[r[1] for r in rng])),
+                       "fb_dist_set_pushed_ranges")
         if self._capturable and fuse:
             if self._dev_epoch is None:  # continue the host-side sequence on the device
                 self._dev_epoch = torch.tensor([e], dtype=torch.int32, device=self._flat_params.device)

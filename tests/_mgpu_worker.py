@@ -143,6 +143,40 @@ def main(out_dir):
         check(f"graphed ddp param {i} (max err {(p - q).abs().max().item():.2e})",
               torch.allclose(p, q, atol=5e-5, rtol=1e-3))
     ddp.shutdown()
+
+    # ---- push mode: the wgrad GEMMs of the two wide layers store their tiles into the shard owners' memory
+    #      (reduce-scatter inside the GEMM epilogue); the trajectory must equal the pull-mode engine's
+    def wide_model():
+        torch.manual_seed(11)
+        return fb.nn.Sequential(fb.nn.Linear(128, 640), fb.nn.GELU(), fb.nn.LayerNorm([640]),
+                                fb.nn.Linear(640, 512), fb.nn.GELU(), fb.nn.LayerNorm([512]),
+                                fb.nn.Linear(512, 8)).to_device(fb.Device.Cuda(dev.index))
+
+    gen = torch.Generator().manual_seed(13 + rank)
+    xw = torch.randn(96, 128, generator=gen).to(dev)
+    yw = torch.randint(0, 8, (96,), generator=gen).to(dev)
+    finals = []
+    for push in (False, True):
+        model = wide_model()
+        opt = fb.optim.Adam(model.parameters(), fb.optim.AdamConfig(lr=1e-3))
+        ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.05).fuse_optimizer(opt).push_gradients(push)
+        for _ in range(4):
+            opt.zero_grad()
+            with fb.autocast():
+                loss = fb.nn.cross_entropy(ddp(xw), yw)
+            loss.backward()
+            if push:
+                check("two weights pushed", len(ddp._pushed_params) == 2)
+            opt.step()
+        torch.cuda.synchronize()
+        fb.utils.runtime.check_status()
+        ddp.shutdown()
+        finals.append(torch.cat([p.detach().reshape(-1) for p in model.torch_parameters()]))
+    err = (finals[0] - finals[1]).abs().max().item()
+    check(f"push-mode trajectory equals pull mode (max err {err:.2e})", err < 2e-5)
+    allp = [torch.empty_like(finals[1]) for _ in range(world)]
+    pg.all_gather(allp, finals[1])
+    check("push-mode replicas identical", all(torch.equal(allp[0], a) for a in allp))
     fb.utils.runtime.check_status()
     d.destroy_process_group()
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:

@@ -402,3 +402,51 @@ def test_guard_bands_around_the_engine_arena_detect_a_stray_write(monkeypatch):
         eng.check_guard_bands()
     band[123] = 0xA5
     eng.shutdown()
+
+
+@pytest.mark.parametrize("world,M,N,K,small", [(2, 512, 260, 128, 0), (4, 1024, 388, 64, 0), (2, 776, 128, 96, 0),
+                                               (8, 520, 132, 64, 0)])
+def test_wgrad_gemm_pushes_its_tiles_to_the_shard_owners_emulated(world, M, N, K, small):
+    """GEMM + reduce-scatter in one kernel: every virtual rank runs the CTA-pair wgrad GEMM whose epilogue stores
+    each 16-byte piece into the owner's bucket region (its own slot), then the bucket kernel reduces the pushed
+    range from local memory only.  The bucket holds the one weight (plus alignment padding, pulled the ordinary
+    way); shard boundaries fall inside rows and inside 32-column chunks."""
+    from ferrum_b200 import _lib as L
+    from ferrum_b200.utils.runtime import check_status
+
+    wsz = M * N
+    n = (wsz + small + 4 * world - 1) // (4 * world) * (4 * world)
+    lib, arenas, ctxs = _setup(world, n * 3)
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + n * 4, base + n * 8
+    torch.manual_seed(M + N + world)
+    p0 = torch.randn(n, device="cuda")
+    As = [(torch.randn(M, K, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    Bs = [(torch.randn(N, K, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    smalls = [torch.randn(n - wsz, device="cuda") for _ in range(world)]
+    for a, sm in zip(arenas, smalls):
+        a.view(off_p, (n,), torch.float32).copy_(p0)
+        g = a.view(off_g, (n,), torch.float32)
+        g.fill_(float("nan"))            # whatever the GEMMs do not overwrite must not be read for the weight
+        g[wsz:].copy_(sm)                # alignment padding of the bucket: ordinary layout, pulled from the peers
+    per = n // world
+    for r in range(world):
+        rc = lib.fb_gemm_bf16_2cta_push(As[r].data_ptr(), Bs[r].data_ptr(), M, N, K, K, K, N, 0, 0,
+                                        ctypes.byref(ctxs[r]), off_g, 0, per, n, 0, None, _stream())
+        assert rc == 0, rc
+    # NaN fill survives only outside the slots: inside the pushed range every slot of every owner was written
+    LLn = ctypes.c_longlong * 1
+    assert lib.fb_dist_set_pushed_ranges(1, LLn(0), LLn(wsz)) == 0
+    h = L.SgdH(0.5, 0.0, 0.0, 1.0 / world, 0, 1)
+    rc = lib.fb_dist_allreduce_emulated(ctxs, world, 1, 0, 1, off_g, off_p, off_s, n, 0, 1.0, None, ctypes.byref(h),
+                                        None, None, 1, 3, 256, _stream())
+    assert rc == 0
+    check_status()
+    gw = torch.stack([a.float() @ b.float().t() for a, b in zip(As, Bs)]).sum(0).reshape(-1) / world
+    ref = p0[:wsz] - 0.5 * gw
+    for a in arenas:
+        got = a.view(off_p, (n,), torch.float32)[:wsz]
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got, ref, atol=2e-3, rtol=1e-3), (got - ref).abs().max().item()
+    for a in arenas:
+        a.close()
