@@ -37,3 +37,31 @@ def test_absent_rank_makes_everyone_time_out_not_hang(world, absent):
     assert res.ok, res.violation  # no deadlock, no read of data that never arrived
     for final in res.finals:
         assert all(final[r] for r in range(world) if r != absent), final
+
+
+# ---- layout of the push mode (GEMM epilogue stores into the shard owners' memory)
+from ferrum_b200.parallel.push_layout import check_layout, owner_reads, push_destination  # noqa: E402
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_push_layout_of_a_single_tensor_bucket_is_sound(world):
+    n = 4 * world * 37
+    assert check_layout(world, n, [(0, n)]) == []
+    # with alignment padding behind the tensor (ordinary layout): the padding belongs to no parameter, but its
+    # positions are slot positions too, which the checker reports — harmless only because nothing reads padding
+    assert check_layout(world, n, [(0, n - 4 * world)]) != []
+
+
+def test_push_layout_rejects_a_bucket_shared_with_ordinarily_laid_out_tensors():
+    # a pushed weight followed by small tensors in the same bucket: the last source's slot in every other owner's
+    # region lands on the small tensors' positions
+    problems = check_layout(2, 4 * 2 * 100, [(0, 4 * 2 * 90)])
+    assert problems and "aliases" in " ".join(problems)
+
+
+def test_push_destination_and_owner_reads_agree():
+    world, per = 4, 24
+    for e in range(world * per):
+        o = e // per
+        assert sorted(push_destination(e, s, per)[1] for s in range(world)) == owner_reads(e, world, per)
+        assert all(push_destination(e, s, per)[0] == o for s in range(world))
