@@ -50,7 +50,9 @@ struct Cfg2 {
   static constexpr int kBBytes = (BN / 2) * kRowBytes;        // 16 KB / 8 KB
   static constexpr int kStageBytes = kABytes + kBBytes;       // 32 KB / 24 KB per CTA
   static constexpr int kStages = BN == 256 ? 6 : 8;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  // + one 32 x 33 fp32 transposing buffer per epilogue warp (push mode writes rows, not columns, to the peers)
+  static constexpr int kTransposeBytes = kEpilogueWarps * 32 * 33 * 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kTransposeBytes;
   static constexpr int kTmemCols = 2 * BN;                    // two accumulators
 };
 
@@ -80,6 +82,8 @@ struct Args2 {
   long long push_bucket_off;  // byte offset of the bucket's gradient region inside every arena
   long long push_rel;         // bucket-relative element index of out[0][0] (multiple of 4)
   long long push_per;         // elements per shard (multiple of 4)
+  int push_coalesced;         // 1: rows leave as 128-byte stores through a shared-memory transpose
+  int f32_rows;               // 1: plain fp32 results are stored row-wise the same way (FERRUM_GEMM_F32_ROWS)
 };
 
 unsigned long long* g_prof_buffer = nullptr;
@@ -115,6 +119,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   uint64_t* tmem_empty = tmem_full + 2;                         // used in the leader only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* transpose_buf = reinterpret_cast<float*>(bar_base + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -297,7 +302,63 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         ptx::tmem_ld_32x32b_x32(taddr + j * 32, r);
         ptx::tmem_wait_ld();
         const int col0 = n0 + j * 32;
-        if (row < p.M && col0 < p.N) {
+        if (p.push_world > 1 && p.push_coalesced) {
+          // Push mode, coalesced: the 32 x 32 block of this warp is turned through shared memory so that one store
+          // instruction writes 128 contiguous bytes of ONE row (a full line per NVLink write) instead of 16 bytes
+          // of 32 different rows.  Every lane takes part (rows past M are skipped at the store).
+          if (col0 < p.N) {
+            float* tb = transpose_buf + (warp - 2) * (32 * 33);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = __uint_as_float(r[i]);
+            __syncwarp();
+            const int row_base = row - lane;  // first of this warp's 32 rows
+            long long rel = p.push_rel + static_cast<long long>(row_base) * p.ldc + col0;
+            int owner = static_cast<int>(rel / p.push_per);
+            long long jj = rel - static_cast<long long>(owner) * p.push_per;
+            const bool col_ok = col0 + lane < p.N;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; ++rr) {
+              if (row_base + rr < p.M && col_ok) {
+                int o2 = owner;
+                long long j2 = jj + lane;
+                if (j2 >= p.push_per) {
+                  j2 -= p.push_per;
+                  ++o2;
+                }
+                float* dst = reinterpret_cast<float*>(p.push_arena[o2] + p.push_bucket_off) +
+                             static_cast<long long>(p.push_rank) * p.push_per + j2;
+                asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(dst), "f"(tb[rr * 33 + lane]) : "memory");
+              }
+              jj += p.ldc;
+              while (jj >= p.push_per) {
+                jj -= p.push_per;
+                ++owner;
+              }
+            }
+            __syncwarp();
+          }
+        } else if (p.f32_rows && !p.out_bf16 && p.out2 == nullptr && p.bias == nullptr && p.act == FB_ACT_NONE) {
+          // Plain fp32 result (weight gradients), row-wise stores: the same shared-memory turn as the push mode,
+          // so that a store instruction writes one full 128-byte line instead of 16 bytes of 32 rows.
+          if (col0 < p.N) {
+            float* tb = transpose_buf + (warp - 2) * (32 * 33);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = __uint_as_float(r[i]);
+            __syncwarp();
+            const int row_base = row - lane;
+            const bool col_ok = col0 + lane < p.N;
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row_base) * p.ldc + col0 + lane;
+#pragma unroll 8
+            for (int rr = 0; rr < 32; ++rr) {
+              if (row_base + rr < p.M && col_ok) {
+                const float x = tb[rr * 33 + lane];
+                o[0] = p.beta ? o[0] + x : x;
+              }
+              o += p.ldc;
+            }
+            __syncwarp();
+          }
+        } else if (row < p.M && col0 < p.N) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -371,7 +432,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
               for (int i = 0; i < 32; ++i)
                 if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
             }
-          } else if (p.push_world > 1) {
+          } else if (p.push_world > 1 && !p.push_coalesced) {
             // one division per 32-column chunk, then (owner, offset) advance with the columns
             const long long rel = p.push_rel + static_cast<long long>(row) * p.ldc + col0;
             int owner = static_cast<int>(rel / p.push_per);
@@ -518,6 +579,15 @@ void fill_common(Args2& args, int32_t* status) {
   args.push_rank = 0;
   args.push_bucket_off = args.push_rel = 0;
   args.push_per = 4;
+  args.push_coalesced = 0;
+  {
+    static int f32_rows = -1;
+    if (f32_rows < 0) {
+      const char* e = getenv("FERRUM_GEMM_F32_ROWS");
+      f32_rows = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    args.f32_rows = f32_rows;
+  }
   for (int i = 0; i < 8; ++i) args.push_arena[i] = nullptr;
   args.status = status;
   args.timeout_ns = 2000000000ull;
@@ -646,6 +716,14 @@ extern "C" int fb_gemm_bf16_2cta_push(const void* a, const void* b, int M, int N
   args.push_bucket_off = bucket_off;
   args.push_rel = out_rel;
   args.push_per = per;
+  {
+    static int coalesced = -1;
+    if (coalesced < 0) {
+      const char* e = getenv("FERRUM_PUSH_COALESCED");
+      coalesced = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    args.push_coalesced = coalesced;
+  }
   int pairs = pairs_avail;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   const long long tiles = static_cast<long long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
