@@ -13,6 +13,7 @@ import math
 
 import torch
 
+from .. import config
 from ..core import ShapeMismatch, _as_device
 from ..ops import functional as F
 from .modules import LayerNorm, Linear, Module, tensor_io
@@ -45,6 +46,11 @@ class MultiHeadAttention(Module):
         q = self._split(self.q_proj(query), B, Sq)
         k = self._split(self.k_proj(key), B, Sk)
         v = self._split(self.v_proj(value), B, Sk)
+        if (mask is None and self.head_dim == 64 and config.low_precision_active()
+                and F.flash_attention_ok(q, k, v)):
+            # inference (no gradient needed), bf16: blockwise attention, the score matrix is never materialised
+            ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim))
+            return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
         scores = F.bmm_scaled(q, k.transpose(-1, -2), 1.0 / math.sqrt(self.head_dim))  # scale in the GEMM epilogue
         if mask is not None:
             m = mask.to(scores.dtype) if mask.dtype != torch.bool else torch.zeros_like(

@@ -563,6 +563,41 @@ def bmm_scaled(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, heads_inner
     return scalar_op(out, "mul", float(alpha)) if alpha != 1.0 else out
 
 
+def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """True when ``flash_attention`` can take these ``[B, H, S, 64]`` operands: CUDA, head dimension 64 contiguous,
+    other strides multiples of 8 elements, no gradient needed (the kernel is forward-only)."""
+    if not (q.is_cuda and q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and q.shape[-1] == 64):
+        return False
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return False
+    if k.shape != v.shape or q.shape[:2] != k.shape[:2] or k.shape[-1] != 64:
+        return False
+    for t in (q, k, v):
+        if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.stride(2) < 64:
+            return False
+    return True
+
+
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                    return_lse: bool = False):
+    """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, 64]`` operands without materialising the score matrix:
+    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  Forward only.  The result is stored as
+    ``[B, Sq, H, 64]`` and returned as the ``[B, H, Sq, 64]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
+    B, H, Sq, _ = q.shape
+    Skv = k.shape[2]
+    qb, kb, vb = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (q.detach(), k.detach(), v.detach()))
+    out = torch.empty((B, Sq, H, 64), device=q.device, dtype=torch.bfloat16)
+    lse = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32) if return_lse else None
+    rc = _lib.cuda().fb_attention_fwd(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), out.data_ptr(),
+                                      lse.data_ptr() if lse is not None else None, B, H, Sq, Skv,
+                                      qb.stride(0), qb.stride(1), qb.stride(2), kb.stride(0), kb.stride(1),
+                                      kb.stride(2), vb.stride(0), vb.stride(1), vb.stride(2), float(scale),
+                                      _rt.status_ptr(), _stream())
+    _lib.check(rc, "fb_attention_fwd")
+    res = out.permute(0, 2, 1, 3)
+    return (res, lse) if return_lse else res
+
+
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """2D@2D, 2D@1D, 1D@2D (tensor.rs:2433-2485) and batched ND@ND / ND@2D."""
     if not (_native(a) and _native(b)):

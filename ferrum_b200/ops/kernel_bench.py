@@ -158,6 +158,8 @@ def _cases(small: bool):
 
     case("attention_fwd_bf16_S1024_D64", attn, Ba * Ha * Sa * Sa * 2 * 4 + 4 * Ba * Ha * Sa * Da * 2,
          "K16 (batched tcgen05 QK^T, row softmax, batched PV; bytes = score matrix written + read twice + q, k, v, o)")
+    case("attention_flash_fwd_bf16_S1024_D64", lambda: F.flash_attention(qa, ka, va, Da ** -0.5),
+         4 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 attention (bytes = q, k, v, o only)")
     return cases
 
 

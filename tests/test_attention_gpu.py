@@ -131,3 +131,44 @@ def test_transformer_encoder_layer_trains_under_autocast():
         opt.step()
         losses.append(float(loss))
     assert losses[-1] < 0.5 * losses[0]
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv", [(2, 3, 128, 128), (1, 2, 256, 384), (2, 2, 200, 200), (1, 4, 64, 1000),
+                                        (1, 16, 1024, 1024)])
+def test_flash_attention_forward_matches_softmax_attention(B, H, Sq, Skv):
+    """Blockwise tcgen05 attention (online softmax, scores never materialised) against fp32 softmax(QK^T)V, with
+    head-interleaved [B, S, H, D] storage, ragged sequence lengths and several key tiles."""
+    from ferrum_b200.ops import functional as F
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(B * 7 + Sq + Skv)
+    D = 64
+    q = (torch.randn(B, Sq, H, D, device="cuda") * 0.8).bfloat16().permute(0, 2, 1, 3)
+    k = (torch.randn(B, Skv, H, D, device="cuda") * 0.8).bfloat16().permute(0, 2, 1, 3)
+    v = torch.randn(B, Skv, H, D, device="cuda").bfloat16().permute(0, 2, 1, 3)
+    assert F.flash_attention_ok(q, k, v)
+    scale = D ** -0.5
+    out, lse = F.flash_attention(q, k, v, scale, return_lse=True)
+    check_status()
+    s = (q.float() @ k.float().transpose(-1, -2)) * scale
+    ref = torch.softmax(s, -1) @ v.float()
+    assert out.shape == ref.shape
+    err = (out.float() - ref).abs().max().item()
+    assert err < 2e-2, err  # bf16 probabilities and bf16 output
+    assert torch.allclose(lse, torch.logsumexp(s, -1), atol=2e-3, rtol=1e-4)
+    assert out.permute(0, 2, 1, 3).is_contiguous()  # stored [B, Sq, H, D]
+
+
+def test_attention_module_uses_the_blockwise_kernel_without_gradients():
+    import ferrum_b200 as fb
+    from ferrum_b200 import _lib, nn
+
+    torch.manual_seed(5)
+    mha = nn.MultiHeadAttention(256, 4, device=fb.Device.Cuda(0))  # head dimension 64
+    x = torch.randn(2, 192, 256, device="cuda")
+    with fb.autocast():
+        y_train = mha(x)              # differentiable path: batched GEMMs + softmax kernel
+        with fb.no_grad():
+            y_eval = mha(x)           # blockwise kernel
+    assert y_eval.shape == y_train.shape
+    assert (y_eval.float() - y_train.float()).abs().max().item() < 6e-2  # two bf16 roundings of values near 2
