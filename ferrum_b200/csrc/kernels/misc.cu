@@ -330,14 +330,18 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, const long l
     const bool oob = id < 0 || id >= n_rows;
     if (oob && threadIdx.x == 0)
       report_status(status, kStatusBoundsViolation, 11, static_cast<int32_t>(i), static_cast<int32_t>(id));
-    const uint8_t* s = src + (oob ? 0 : id) * row_bytes;
     uint8_t* d = dst + i * row_bytes;
+    if (oob) {  // block-uniform: the whole row is zero-filled, the source is not read
+      for (long long k = threadIdx.x; k < row_bytes; k += blockDim.x) d[k] = 0;
+      continue;
+    }
+    const uint8_t* s = src + id * row_bytes;
     if (vec) {
       const long long nv = row_bytes >> 4;
       for (long long k = threadIdx.x; k < nv; k += blockDim.x)
-        reinterpret_cast<uint4*>(d)[k] = oob ? make_uint4(0, 0, 0, 0) : reinterpret_cast<const uint4*>(s)[k];
+        reinterpret_cast<uint4*>(d)[k] = reinterpret_cast<const uint4*>(s)[k];
     } else {
-      for (long long k = threadIdx.x; k < row_bytes; k += blockDim.x) d[k] = oob ? uint8_t(0) : s[k];
+      for (long long k = threadIdx.x; k < row_bytes; k += blockDim.x) d[k] = s[k];
     }
   }
 }

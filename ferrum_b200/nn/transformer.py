@@ -20,8 +20,12 @@ from .modules import LayerNorm, Linear, Module, tensor_io
 
 
 class MultiHeadAttention(Module):
-    def __init__(self, embed_dim: int, num_heads: int, device=None):
+    """``memory_efficient=True``: under autocast with head dimension 64 the training forward uses the blockwise
+    kernel and saves no S x S activations (the backward recomputes the scores)."""
+
+    def __init__(self, embed_dim: int, num_heads: int, device=None, memory_efficient: bool = False):
         super().__init__()
+        self.memory_efficient = bool(memory_efficient)
         if embed_dim % num_heads:
             raise ValueError("embed_dim must be divisible by num_heads")
         self.embed_dim, self.num_heads, self.head_dim = int(embed_dim), int(num_heads), embed_dim // num_heads
@@ -50,6 +54,11 @@ class MultiHeadAttention(Module):
                 and F.flash_attention_ok(q, k, v)):
             # inference (no gradient needed), bf16: blockwise attention, the score matrix is never materialised
             ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim))
+            return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
+        if (self.memory_efficient and mask is None and self.head_dim == 64 and config.low_precision_active()
+                and F.flash_attention_ok(q, k, v, need_no_grad=False)):
+            # training without S x S activations: blockwise forward, scores recomputed in the backward pass
+            ctx = F.attention_checkpointed(q, k, v, 1.0 / math.sqrt(self.head_dim))
             return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
         scores = F.bmm_scaled(q, k.transpose(-1, -2), 1.0 / math.sqrt(self.head_dim))  # scale in the GEMM epilogue
         if mask is not None:

@@ -563,12 +563,12 @@ def bmm_scaled(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, heads_inner
     return scalar_op(out, "mul", float(alpha)) if alpha != 1.0 else out
 
 
-def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_no_grad: bool = True) -> bool:
     """True when ``flash_attention`` can take these ``[B, H, S, 64]`` operands: CUDA, head dimension 64 contiguous,
-    other strides multiples of 8 elements, no gradient needed (the kernel is forward-only)."""
+    other strides multiples of 8 elements and (``need_no_grad``) no gradient needed — the kernel is forward-only."""
     if not (q.is_cuda and q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and q.shape[-1] == 64):
         return False
-    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+    if need_no_grad and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
         return False
     if k.shape != v.shape or q.shape[:2] != k.shape[:2] or k.shape[-1] != 64:
         return False
@@ -596,6 +596,34 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
     _lib.check(rc, "fb_attention_fwd")
     res = out.permute(0, 2, 1, 3)
     return (res, lse) if return_lse else res
+
+
+class _CheckpointedAttentionFn(Function):
+    """Attention core with the blockwise kernel in the forward pass and NOTHING of size S x S kept for the backward
+    pass: the backward recomputes the scores with the differentiable batched-GEMM path (activation checkpointing
+    of the attention core).  Trades one extra score computation for S x S x heads of saved activations."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        ctx.scale = scale
+        ctx.save_for_backward(q, k, v)
+        return flash_attention(q, k, v, scale)
+
+    @staticmethod
+    def backward(ctx, g):
+        q, k, v = ctx.saved_tensors
+        with torch.enable_grad():
+            qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
+            attn = softmax(bmm_scaled(qd, kd.transpose(-1, -2), ctx.scale), -1)
+            out = bmm_scaled(attn, vd, 1.0, heads_inner=True)
+            gq, gk, gv = torch.autograd.grad(out, (qd, kd, vd), g.to(out.dtype))
+        return gq, gk, gv, None
+
+
+def attention_checkpointed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+    """Differentiable ``softmax(scale q k^T) v`` that saves only q, k, v (see ``_CheckpointedAttentionFn``);
+    operands as for :func:`flash_attention`."""
+    return _CheckpointedAttentionFn.apply(q, k, v, float(scale))
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

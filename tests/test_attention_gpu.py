@@ -172,3 +172,29 @@ def test_attention_module_uses_the_blockwise_kernel_without_gradients():
             y_eval = mha(x)           # blockwise kernel
     assert y_eval.shape == y_train.shape
     assert (y_eval.float() - y_train.float()).abs().max().item() < 6e-2  # two bf16 roundings of values near 2
+
+
+def test_memory_efficient_attention_gradients_match_the_materialising_path():
+    """memory_efficient=True: blockwise forward + recomputing backward gives the same gradients as the path that
+    keeps the probabilities."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    torch.manual_seed(6)
+    ref = nn.MultiHeadAttention(128, 2, device=fb.Device.Cuda(0))
+    eff = copy.deepcopy(ref)
+    eff.memory_efficient = True
+    x = torch.randn(2, 160, 128, device="cuda")
+    outs, grads = [], []
+    for m in (ref, eff):
+        xi = x.clone().requires_grad_(True)
+        with fb.autocast():
+            y = m(xi)
+        (y.float() * torch.linspace(-1, 1, y.numel(), device="cuda").reshape(y.shape)).sum().backward()
+        outs.append(y.float().detach())
+        grads.append([xi.grad] + [p.grad for p in m.torch_parameters()])
+    assert _rel(outs[1], outs[0]) < 2e-2
+    for a, b in zip(grads[1], grads[0]):
+        assert _rel(a, b) < 3e-2, _rel(a, b)
