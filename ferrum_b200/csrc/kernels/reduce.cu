@@ -51,31 +51,62 @@ __device__ __forceinline__ float block_reduce(float v, int op, float* smem) {
   return v;  // valid in thread 0
 }
 
-// x: [outer, R]; block (row = blockIdx.x, split = blockIdx.y) reduces its segment.
-__global__ void reduce_rows_kernel(const float* __restrict__ x, float* __restrict__ out, long long R, int op,
-                                   float scale, int splits) {
+// x: [outer, R]; block (row = blockIdx.x, split = blockIdx.y) reduces its segment.  The combining op is a template
+// parameter (a per-element switch made the kernel issue-bound) and four 16-byte loads are in flight per thread.
+template <int OP>
+__device__ __forceinline__ float combine_t(float a, float b) {
+  if (OP == FB_RED_MAX) return fmaxf(a, b);
+  if (OP == FB_RED_MIN) return fminf(a, b);
+  if (OP == FB_RED_PROD) return a * b;
+  return a + b;
+}
+template <int OP>
+__device__ __forceinline__ float fold4(float acc, const float4 v) {
+  return combine_t<OP>(acc, combine_t<OP>(combine_t<OP>(v.x, v.y), combine_t<OP>(v.z, v.w)));
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel_t(const float* __restrict__ x, float* __restrict__ out, long long R, float scale, int splits) {
   __shared__ float smem[32];
   const long long row = blockIdx.x;
   const long long seg = (R + splits - 1) / splits;
   const long long lo = blockIdx.y * seg;
   const long long hi = min(R, lo + seg);
   const float* p = x + row * R;
-  const int cop = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
-  float acc = red_identity(cop);
+  float acc = red_identity(OP);
   // vector body when the segment start is 16-byte aligned
   long long i = lo + threadIdx.x;
   if (((reinterpret_cast<uintptr_t>(p + lo) & 15) == 0) && hi - lo >= 4) {
     const long long n4 = (hi - lo) >> 2;
     const float4* p4 = reinterpret_cast<const float4*>(p + lo);
-    for (long long k = threadIdx.x; k < n4; k += blockDim.x) {
-      const float4 v = p4[k];
-      acc = red_combine(acc, red_combine(red_combine(v.x, v.y, cop), red_combine(v.z, v.w, cop), cop), cop);
+    long long k = threadIdx.x;
+    float a1 = red_identity(OP), a2 = red_identity(OP), a3 = red_identity(OP);
+    for (; k + 3 * blockDim.x < n4; k += 4 * blockDim.x) {
+      const float4 v0 = p4[k], v1 = p4[k + blockDim.x], v2 = p4[k + 2 * blockDim.x], v3 = p4[k + 3 * blockDim.x];
+      acc = fold4<OP>(acc, v0);
+      a1 = fold4<OP>(a1, v1);
+      a2 = fold4<OP>(a2, v2);
+      a3 = fold4<OP>(a3, v3);
     }
+    for (; k < n4; k += blockDim.x) acc = fold4<OP>(acc, p4[k]);
+    acc = combine_t<OP>(combine_t<OP>(acc, a1), combine_t<OP>(a2, a3));
     i = lo + (n4 << 2) + threadIdx.x;
   }
-  for (; i < hi; i += blockDim.x) acc = red_combine(acc, p[i], cop);
-  acc = block_reduce(acc, cop, smem);
+  for (; i < hi; i += blockDim.x) acc = combine_t<OP>(acc, p[i]);
+  acc = block_reduce(acc, OP, smem);
   if (threadIdx.x == 0) out[row * splits + blockIdx.y] = acc * scale;
+}
+
+void launch_reduce_rows(dim3 grid, cudaStream_t stream, const float* x, float* out, long long R, int op, float scale,
+                        int splits) {
+  const int cop = (op == FB_RED_MEAN) ? FB_RED_SUM : op;
+  switch (cop) {
+    case FB_RED_MAX: reduce_rows_kernel_t<FB_RED_MAX><<<grid, 256, 0, stream>>>(x, out, R, scale, splits); break;
+    case FB_RED_MIN: reduce_rows_kernel_t<FB_RED_MIN><<<grid, 256, 0, stream>>>(x, out, R, scale, splits); break;
+    case FB_RED_PROD: reduce_rows_kernel_t<FB_RED_PROD><<<grid, 256, 0, stream>>>(x, out, R, scale, splits); break;
+    default: reduce_rows_kernel_t<FB_RED_SUM><<<grid, 256, 0, stream>>>(x, out, R, scale, splits); break;
+  }
 }
 
 // x: [outer, R, inner]; thread per (outer, inner), optional split of R over blockIdx.y.
@@ -346,12 +377,11 @@ extern "C" int fb_reduce(const float* x, float* out, long long outer, long long 
   if (inner == 1) {
     if (outer > 2147483647LL) return -1;
     if (splits == 1) {
-      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), 1), 256, 0, stream>>>(x, out, R, op, final_scale, 1);
+      launch_reduce_rows(dim3(static_cast<unsigned>(outer), 1), stream, x, out, R, op, final_scale, 1);
     } else {
-      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), splits), 256, 0, stream>>>(x, scratch, R, stage_op,
-                                                                                           1.f, splits);
-      reduce_rows_kernel<<<dim3(static_cast<unsigned>(outer), 1), 256, 0, stream>>>(scratch, out, splits, stage_op,
-                                                                                      final_scale, 1);
+      launch_reduce_rows(dim3(static_cast<unsigned>(outer), splits), stream, x, scratch, R, stage_op, 1.f, splits);
+      launch_reduce_rows(dim3(static_cast<unsigned>(outer), 1), stream, scratch, out, splits, stage_op, final_scale,
+                         1);
     }
   } else if (vec_row_blocks(outer, R, inner) > 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
              (vec_row_blocks(outer, R, inner) == 1 ||

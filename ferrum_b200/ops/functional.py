@@ -612,7 +612,8 @@ class _CheckpointedAttentionFn(Function):
     @staticmethod
     def backward(ctx, g):
         q, k, v = ctx.saved_tensors
-        with torch.enable_grad():
+        # the backward pass runs outside the caller's autocast block: re-enter it for the recomputation
+        with torch.enable_grad(), config.autocast():
             qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
             attn = softmax(bmm_scaled(qd, kd.transpose(-1, -2), ctx.scale), -1)
             out = bmm_scaled(attn, vd, 1.0, heads_inner=True)
