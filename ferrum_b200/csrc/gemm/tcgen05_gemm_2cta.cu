@@ -84,9 +84,38 @@ struct Args2 {
   long long push_per;         // elements per shard (multiple of 4)
   int push_coalesced;         // 1: rows leave as 128-byte stores through a shared-memory transpose
   int f32_rows;               // 1: plain fp32 results are stored row-wise the same way (FERRUM_GEMM_F32_ROWS)
+  // Split-K tail (on only while a workspace is set; measured neutral on B200 — 204.8 us with and without on the
+  // 4096 x 4096 x 8192 weight-gradient shape, because the kernel is bound by operand delivery from L2, not by the
+  // number of tile rounds: a half-empty last round simply runs faster).  When the tile count leaves a last round in which at most half of the CTA pairs have work, each of
+  // those `splitk_tail` tiles is shared by two pairs — the owner multiplies the first half of K, a helper the
+  // second half, deposits its fp32 partial in `splitk_ws` and raises a flag; the owner adds it in its epilogue.
+  // Helpers never wait, every pair of the grid is resident, and the owner's wait is bounded.  0 = off.
+  int splitk_tail;
+  float* splitk_ws;           // [slot][256][256] fp32
+  unsigned* splitk_flags;     // [slot][2 CTAs][4 epilogue warps]
 };
 
+// A unit of work of a CTA pair: a whole tile, or one half of the K range of a tile of the last round.
+struct Unit2 {
+  int tile, k_lo, k_hi, role, slot;  // role 0 = whole tile, 1 = owner (first half of K), 2 = helper (second half)
+};
+__device__ __forceinline__ Unit2 decode_unit2(int u, int num_tiles, int tail, int num_kb) {
+  Unit2 x;
+  const int full = num_tiles - tail;
+  if (u < full) {
+    x.tile = u; x.k_lo = 0; x.k_hi = num_kb; x.role = 0; x.slot = 0;
+  } else if (u < full + tail) {
+    x.tile = u; x.k_lo = 0; x.k_hi = num_kb >> 1; x.role = 1; x.slot = u - full;
+  } else {
+    x.slot = u - full - tail; x.tile = full + x.slot; x.k_lo = num_kb >> 1; x.k_hi = num_kb; x.role = 2;
+  }
+  return x;
+}
+
 unsigned long long* g_prof_buffer = nullptr;
+unsigned char* g_splitk_base = nullptr;  // 4 KB of flags, then 256 KB per slot
+int g_splitk_slots = 0;
+int g_last_splitk_tail = 0;  // tiles shared by two pairs in the most recent launch (introspection for benches / tests)
 
 __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
   const int per_group = kGroupM * num_n;
@@ -131,6 +160,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const int num_n = (p.N + kBN - 1) / kBN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + kBK - 1) / kBK;
+  const int num_units = num_tiles + p.splitk_tail;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -165,12 +195,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int u = pair; u < num_units && ok; u += num_pairs) {
+        const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
         int m_blk, n_blk;
-        tile_coords2(t, num_m, num_n, m_blk, n_blk);
+        tile_coords2(un.tile, num_m, num_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * kBM + static_cast<int>(rank) * kBM;        // this CTA's 128 rows of A
         const int n0 = n_blk * kBN + static_cast<int>(rank) * (kBN / 2);      // this CTA's 128 rows of B
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = un.k_lo; kb < un.k_hi; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 11, blockIdx.x, stage);
             ok = false;
@@ -229,7 +260,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       bool ok = true;
       unsigned long long w_acc = 0, w_ops = 0;
       const unsigned long long k_start = p.prof ? ptx::globaltimer() : 0;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int u = pair; u < num_units && ok; u += num_pairs) {
+        const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
         unsigned long long t0 = p.prof ? ptx::globaltimer() : 0;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 12, blockIdx.x, acc);
@@ -238,7 +270,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (p.prof) w_acc += ptx::globaltimer() - t0;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = un.k_lo; kb < un.k_hi; ++kb) {
           t0 = p.prof ? ptx::globaltimer() : 0;
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 13, blockIdx.x, stage);
@@ -254,9 +286,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, a_sbo, a_layout);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, b_sbo, b_layout);
             if constexpr (kTf32)
-              ptx::umma_tf32_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_tf32_2cta(d_tmem, adesc, bdesc, idesc, (kb != un.k_lo || k != 0) ? 1u : 0u);
             else
-              ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb != un.k_lo || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit_2cta(&empty_bar[stage], 0x3);  // frees the slot in both CTAs
           if (++stage == kStages) {
@@ -283,9 +315,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     unsigned long long e_busy = 0;
-    for (int t = pair; t < num_tiles; t += num_pairs) {
+    for (int u = pair; u < num_units; u += num_pairs) {
+      const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
       int m_blk, n_blk;
-      tile_coords2(t, num_m, num_n, m_blk, n_blk);
+      tile_coords2(un.tile, num_m, num_n, m_blk, n_blk);
       const int row = m_blk * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
       const int n0 = n_blk * kBN;
       const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
@@ -295,6 +328,37 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         break;
       }
       ptx::tc_fence_after();
+      // split-K tail: this warp's 32 rows of the partial live at ws_rows; its flag at ws_flag
+      float* ws_rows = nullptr;
+      unsigned* ws_flag = nullptr;
+      if (un.role != 0) {
+        ws_rows = p.splitk_ws + (static_cast<long long>(un.slot) * 256 + static_cast<int>(rank) * kBM + quarter * 32 +
+                                 lane) * 256;
+        ws_flag = p.splitk_flags + un.slot * 8 + static_cast<int>(rank) * 4 + (warp - 2);
+      }
+      if (un.role == 1) {
+        // owner: the helper's partial must have arrived (bounded wait; the helper never waits for anybody)
+        bool got = true;
+        if (lane == 0) {
+          const unsigned long long w0 = ptx::globaltimer();
+          unsigned it = 0;
+          while (ptx::ld_acquire_gpu(ws_flag) == 0u) {
+            if (((++it) & 63u) == 0u && (*abort_flag || ptx::globaltimer() - w0 > p.timeout_ns)) {
+              got = false;
+              break;
+            }
+          }
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            report_status(p.status, kStatusGemmTimeout, 15, blockIdx.x, un.slot);
+          }
+          break;
+        }
+        __syncwarp();
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBN;
 #pragma unroll 1
       for (int j = 0; j < kBN / 32; ++j) {
@@ -302,6 +366,26 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         ptx::tmem_ld_32x32b_x32(taddr + j * 32, r);
         ptx::tmem_wait_ld();
         const int col0 = n0 + j * 32;
+        if (un.role == 2) {
+          // helper: raw partial sums into the workspace (this lane's row, 32 columns)
+          float4* dst = reinterpret_cast<float4*>(ws_rows + j * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            dst[q] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                                 __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+          continue;
+        }
+        if (un.role == 1) {
+          const float4* src = reinterpret_cast<const float4*>(ws_rows + j * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 x = __ldcg(src + q);
+            r[q * 4] = __float_as_uint(__uint_as_float(r[q * 4]) + x.x);
+            r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
+            r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
+            r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
+          }
+        }
         if (p.push_world > 1 && p.push_coalesced) {
           // Push mode, coalesced: the 32 x 32 block of this warp is turned through shared memory so that one store
           // instruction writes 128 contiguous bytes of ONE row (a full line per NVLink write) instead of 16 bytes
@@ -471,6 +555,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           }  // out2 == nullptr
         }
       }
+      if (un.role == 2) {          // helper: publish the partial
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) ptx::st_release_gpu(ws_flag, 1u);
+      } else if (un.role == 1) {   // owner: the slot is free for the next launch
+        __syncwarp();
+        if (lane == 0) *ws_flag = 0u;
+      }
       ptx::tc_fence_before();
       __syncwarp();
       // "drained" goes to the leader's barrier from both CTAs
@@ -580,6 +672,9 @@ void fill_common(Args2& args, int32_t* status) {
   args.push_bucket_off = args.push_rel = 0;
   args.push_per = 4;
   args.push_coalesced = 0;
+  args.splitk_tail = 0;
+  args.splitk_ws = nullptr;
+  args.splitk_flags = nullptr;
   {
     static int f32_rows = -1;
     if (f32_rows < 0) {
@@ -608,6 +703,24 @@ extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs<256>(); }
 // Device buffer of 4 x 64-bit words per CTA pair that subsequent launches fill with their wait / busy times
 // (see Args2::prof); NULL switches the record off again.
 extern "C" void fb_gemm_bf16_2cta_set_profile(unsigned long long* buffer) { fb::g_prof_buffer = buffer; }
+
+// Zero-initialised device buffer for the split-K tail (4 KB of flags followed by 256 KB per shared tile; 40 slots
+// = 10 MB cover every grid of up to 80 CTA pairs).  The caller owns it and must keep GEMMs that use it on one
+// stream at a time.  NULL switches the tail split off.
+extern "C" int fb_gemm_bf16_2cta_last_splitk_tail() { return fb::g_last_splitk_tail; }
+
+extern "C" int fb_gemm_bf16_2cta_set_splitk_workspace(void* buffer, long long bytes) {
+  if (buffer == nullptr || bytes < 4096 + 262144) {
+    fb::g_splitk_base = nullptr;
+    fb::g_splitk_slots = 0;
+    return 0;
+  }
+  if (reinterpret_cast<uintptr_t>(buffer) & 15) return -1;
+  fb::g_splitk_base = static_cast<unsigned char*>(buffer);
+  const long long slots = (bytes - 4096) / 262144;
+  fb::g_splitk_slots = static_cast<int>(slots > 128 ? 128 : slots);  // 128 slots x 8 flags x 4 B = the 4 KB of flags
+  return fb::g_splitk_slots;
+}
 
 // Same arguments as fb_gemm_bf16.  Returns -3 when CTA pairs cannot be launched on this device.
 // Small outputs use the 128-column tile, everything else the 256-column one.
@@ -642,7 +755,21 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
   // The 256 x 128 tile moves a third more operand bytes per flop through shared memory and measured ~0.6 of the
   // wide tile's rate on large problems, so it only pays where the wide tiling leaves at least half of the pairs
   // without any tile at all.
-  const bool narrow = max_pairs<128>() >= pairs && 2 * tiles256 <= pairs;
+  {
+    // split-K tail (see Args2::splitk_tail): plain fp32 results only, a last round that fills at most half of the grid
+    const long long used = tiles256 < pairs ? tiles256 : pairs;
+    const long long tail = used > 0 ? tiles256 % used : 0;
+    const int num_kb = (K + 63) / 64;
+    if (g_splitk_base != nullptr && !out_bf16 && out2 == nullptr && bias == nullptr &&
+        act == FB_ACT_NONE && tiles256 > used && tail > 0 && 2 * tail <= used && tail <= g_splitk_slots &&
+        num_kb >= 16) {
+      args.splitk_tail = static_cast<int>(tail);
+      args.splitk_flags = reinterpret_cast<unsigned*>(g_splitk_base);
+      args.splitk_ws = reinterpret_cast<float*>(g_splitk_base + 4096);
+    }
+    g_last_splitk_tail = args.splitk_tail;
+  }
+  const bool narrow = args.splitk_tail == 0 && max_pairs<128>() >= pairs && 2 * tiles256 <= pairs;
   return narrow ? launch2<128>(a, b, args, lda, ldb, pairs, tiles128, stream)
                 : launch2<256>(a, b, args, lda, ldb, pairs, tiles256, stream);
 }

@@ -57,6 +57,8 @@ int fb_gemm_tf32(const float* a, const float* b, float* out, const float* bias, 
 int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, const float* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act, int beta, int max_ctas,
                  int32_t* status, cudaStream_t stream);
+// Workspace of the CTA-pair kernel's split-K tail (zeroed device memory: 4 KB + 256 KB per slot); NULL = off.
+int fb_gemm_bf16_2cta_set_splitk_workspace(void* buffer, long long bytes);
 // CTA-pair variant (tcgen05 cta_group::2; 256 x 256 tiles on two SMs, 256 x 128 for small outputs); same
 // arguments.  Returns -3 where clusters of two CTAs cannot be scheduled.  fb_gemm_bf16_2cta_pairs() = resident pairs.
 int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,

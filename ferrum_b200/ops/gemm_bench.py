@@ -87,6 +87,9 @@ def main():
            "tflops": flops / ms / 1e9}
     if a.two_cta:
         res["rel_err_first_rows"] = res_err
+        from ferrum_b200 import _lib as _l
+
+        res["splitk_tail_tiles"] = _l.cuda().fb_gemm_bf16_2cta_last_splitk_tail()
     if a.simt:
         ref = (A[:256].double() @ B.double().t()).float()
         res["rel_err_first_rows"] = (out[:256] - ref).abs().max().item() / max(1.0, ref.abs().max().item())

@@ -240,3 +240,37 @@ def test_tf32_precision_mode_trains_a_linear_layer():
     yr.square().mean().backward()
     assert (y - yr).abs().max().item() < 5e-3
     assert (x.grad - xr.grad).abs().max().item() < 1e-4 + 5e-3 * xr.grad.abs().max().item()
+
+
+@pytest.mark.parametrize("M,N,K,acc", [(4096, 4096, 2048, False), (4096, 4096, 1024, True), (2560, 7680, 1536, False),
+                                       (4088, 3704, 1104, False)])
+def test_cta_pair_gemm_splitk_tail(M, N, K, acc):
+    """fp32 results whose tile count leaves a last round that fills at most half of the CTA pairs: those tiles are
+    shared by two pairs (halves of K), the helper's partial goes through the workspace.  Checked against a float64
+    product, also accumulating into an existing matrix and with ragged edges; run twice to exercise the flag reset."""
+    from ferrum_b200 import _lib
+    from ferrum_b200.ops.gemm import gemm_bf16
+    from ferrum_b200.utils.runtime import check_status
+
+    pairs = _lib.cuda().fb_gemm_bf16_2cta_pairs()
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if pairs <= 0 or tiles <= pairs or not (0 < tiles % pairs <= pairs // 2):
+        pytest.skip(f"{tiles} tiles on {pairs} pairs leave no splittable tail")
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(K, M, device="cuda") * 0.5).bfloat16().t()      # both operands MN-major, like a wgrad
+    b = (torch.randn(K, N, device="cuda") * 0.5).bfloat16().t()
+    ref = (a.double() @ b.double().t())
+    from ferrum_b200.ops import gemm as g
+
+    g.enable_splitk_tail(True)
+    try:
+        for _ in range(2):
+            out = torch.full((M, N), 2.0, device="cuda") if acc else torch.empty(M, N, device="cuda")
+            gemm_bf16(a, b, out=out, out_dtype=torch.float32, accumulate=acc)
+            check_status()
+            assert _lib.cuda().fb_gemm_bf16_2cta_last_splitk_tail() == tiles % pairs  # the tail really was shared
+            want = (ref + 2.0) if acc else ref
+            err = (out.double() - want).abs().max().item()
+            assert err < 2e-3 * K ** 0.5 * 0.25 + 1e-3, err
+    finally:
+        g.enable_splitk_tail(False)
