@@ -128,3 +128,26 @@ def test_core_autograd_hook_names():
     ag.set_autograd_enabled(False)
     assert not ag.is_autograd_enabled()
     ag.set_autograd_enabled(True)
+
+
+def test_new_switches_are_inert_without_a_gpu():
+    """Options added for the GPU paths must not disturb CPU use: the blockwise attention is not selected for CPU
+    tensors, the split-K switch only records a flag, the engine's push mode and guard bands stay off."""
+    import torch
+
+    import ferrum_b200 as fb
+    from ferrum_b200.ops import functional as F
+    from ferrum_b200.ops import gemm
+    from ferrum_b200.parallel import Backend, DistributedDataParallel, ProcessGroup
+
+    q = torch.randn(1, 2, 16, 64)
+    assert not F.flash_attention_ok(q, q, q)
+    gemm.enable_splitk_tail(True)
+    gemm.enable_splitk_tail(False)
+    model = fb.nn.Sequential(fb.nn.Linear(4, 3))
+    ddp = DistributedDataParallel(model, ProcessGroup(Backend.Gloo, 0, 1))
+    assert ddp.push_gradients(True) is ddp
+    assert ddp.check_guard_bands() == 0
+    mha = fb.nn.MultiHeadAttention(128, 2, memory_efficient=True)
+    y = mha(torch.randn(2, 5, 128))
+    assert tuple(y.shape) == (2, 5, 128)
