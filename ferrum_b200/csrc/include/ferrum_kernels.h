@@ -188,7 +188,8 @@ int fb_embedding_bwd_sorted(const void* dout, const long long* sorted_idx, const
 // [B, H, S, 64] views given by element strides; lse (optional) [B, H, Sq].  -2: operand not describable by TMA.
 int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int Sq, int Skv,
                      long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
-                     long long v_sb, long long v_sh, long long v_ss, float scale, int32_t* status, cudaStream_t stream);
+                     long long v_sb, long long v_sh, long long v_ss, float scale, int causal, int32_t* status,
+                     cudaStream_t stream);
 int fb_gather_rows(const void* src, const long long* idx, void* dst, long long n_idx, long long row_bytes,
                    long long n_rows, int32_t* status, cudaStream_t stream);
 

@@ -43,6 +43,7 @@ struct AttnArgs {
   float* lse;           // [B, H, Sq] or NULL
   int B, H, Sq, Skv;
   float scale_log2;     // softmax scale * log2(e)
+  int causal;           // 1: query i attends keys j <= i + (Skv - Sq) (needs Skv >= Sq)
   int32_t* status;
   unsigned long long timeout_ns;
 };
@@ -77,7 +78,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * kBQ;
   const int h = blockIdx.y % p.H, b = blockIdx.y / p.H;
-  const int n_tiles = (p.Skv + kBKV - 1) / kBKV;
+  // causal: this tile's last query row bounds the keys any of its rows may see
+  const int kv_end = p.causal ? min(p.Skv, q0 + kBQ + (p.Skv - p.Sq)) : p.Skv;
+  const int n_tiles = (kv_end + kBKV - 1) / kBKV;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -194,7 +197,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         break;
       }
       ptx::tc_fence_after();
-      const int valid = min(kBKV, p.Skv - j * kBKV);  // columns past it are padding
+      int valid = min(kBKV, p.Skv - j * kBKV);  // columns past it are padding
+      if (p.causal) valid = max(0, min(valid, q0 + row + (p.Skv - p.Sq) + 1 - j * kBKV));  // this row's keys only
+      // (0 is possible from the second tile on — all of the row's keys lie in earlier tiles — and harmless: the
+      // running maximum is finite by then, so alpha = 1 and every p = 0; the first tile always holds key 0)
       const bool full_tile = valid == kBKV;
       // pass 1: row maximum of the raw scores (the scale is positive, applied once afterwards)
       float mx = -INFINITY;
@@ -342,13 +348,13 @@ bool make_map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long 
 // out[b, s, h, :] = softmax(scale * q[b,h,s,:] . k[b,h,:,:]^T) v[b,h,:,:]  for head dimension 64, bf16 operands given
 // as [B, H, S, 64] views with element strides (last dimension contiguous, strides multiples of 8).  out is
 // [B, Sq, H, 64] contiguous; lse (optional) [B, H, Sq] fp32.  Returns -2 when an operand cannot be described by a
-// TMA map.
+// TMA map.  causal: query i sees keys j <= i + (Skv - Sq); key tiles past the diagonal are skipped.
 extern "C" int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H,
                                 int Sq, int Skv, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                                 long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss,
-                                float scale, int32_t* status, cudaStream_t stream) {
+                                float scale, int causal, int32_t* status, cudaStream_t stream) {
   using namespace fb;
-  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0) return -1;
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || (causal && Skv < Sq)) return -1;
   if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
   CUtensorMap mq, mk, mv;
   if (!make_map_bhsd(&mq, q, B, H, Sq, q_sb, q_sh, q_ss) || !make_map_bhsd(&mk, k, B, H, Skv, k_sb, k_sh, k_ss) ||
@@ -368,6 +374,7 @@ extern "C" int fb_attention_fwd(const void* q, const void* k, const void* v, voi
   a.Sq = Sq;
   a.Skv = Skv;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal ? 1 : 0;
   a.status = status;
   a.timeout_ns = 2000000000ull;
   const dim3 grid((Sq + kBQ - 1) / kBQ, B * H);

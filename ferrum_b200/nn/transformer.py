@@ -42,7 +42,7 @@ class MultiHeadAttention(Module):
         return t.reshape(B, S, self.num_heads, self.head_dim).transpose(1, 2)  # [B, H, S, D]
 
     @tensor_io
-    def forward_attn(self, query, key, value, mask=None):
+    def forward_attn(self, query, key, value, mask=None, causal: bool = False):
         if query.dim() != 3 or query.shape[-1] != self.embed_dim:
             raise ShapeMismatch("MultiHeadAttention", f"[B, S, {self.embed_dim}]", list(query.shape))
         B, Sq, _ = query.shape
@@ -50,11 +50,18 @@ class MultiHeadAttention(Module):
         q = self._split(self.q_proj(query), B, Sq)
         k = self._split(self.k_proj(key), B, Sk)
         v = self._split(self.v_proj(value), B, Sk)
+        if causal and Sk < Sq:
+            raise ShapeMismatch("MultiHeadAttention(causal)", "at least as many keys as queries", [Sq, Sk])
         if (mask is None and self.head_dim == 64 and config.low_precision_active()
                 and F.flash_attention_ok(q, k, v)):
             # inference (no gradient needed), bf16: blockwise attention, the score matrix is never materialised
-            ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim))
+            ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim), causal=causal)
             return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
+        if causal:  # the differentiable paths take the causal structure as an additive mask
+            i = torch.arange(Sq, device=q.device)[:, None]
+            j = torch.arange(Sk, device=q.device)[None, :]
+            cm = j <= i + (Sk - Sq)
+            mask = cm if mask is None else (mask & cm if mask.dtype == torch.bool else mask.masked_fill(~cm, -1e9))
         if (self.memory_efficient and mask is None and self.head_dim == 64 and config.low_precision_active()
                 and F.flash_attention_ok(q, k, v, need_no_grad=False)):
             # training without S x S activations: blockwise forward, scores recomputed in the backward pass

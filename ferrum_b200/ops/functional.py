@@ -579,9 +579,10 @@ def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_n
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                    return_lse: bool = False):
+                    return_lse: bool = False, causal: bool = False):
     """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, 64]`` operands without materialising the score matrix:
-    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  Forward only.  The result is stored as
+    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  Forward only.  ``causal``: query ``i`` sees
+    keys ``j <= i + (Skv - Sq)`` and key tiles past the diagonal are skipped.  The result is stored as
     ``[B, Sq, H, 64]`` and returned as the ``[B, H, Sq, 64]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
     B, H, Sq, _ = q.shape
     Skv = k.shape[2]
@@ -592,7 +593,7 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
                                       lse.data_ptr() if lse is not None else None, B, H, Sq, Skv,
                                       qb.stride(0), qb.stride(1), qb.stride(2), kb.stride(0), kb.stride(1),
                                       kb.stride(2), vb.stride(0), vb.stride(1), vb.stride(2), float(scale),
-                                      _rt.status_ptr(), _stream())
+                                      1 if causal else 0, _rt.status_ptr(), _stream())
     _lib.check(rc, "fb_attention_fwd")
     res = out.permute(0, 2, 1, 3)
     return (res, lse) if return_lse else res

@@ -198,3 +198,25 @@ def test_memory_efficient_attention_gradients_match_the_materialising_path():
     assert _rel(outs[1], outs[0]) < 2e-2
     for a, b in zip(grads[1], grads[0]):
         assert _rel(a, b) < 3e-2, _rel(a, b)
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 256, 256), (2, 2, 200, 300), (1, 3, 128, 640), (1, 1, 384, 384)])
+def test_flash_attention_causal(B, H, Sq, Skv):
+    """Causal (bottom-right aligned) masking inside the blockwise kernel: key tiles past the diagonal are skipped,
+    the diagonal tiles masked per row, also when the offset Skv - Sq is not a multiple of the tile."""
+    from ferrum_b200.ops import functional as F
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(Sq + Skv)
+    D = 64
+    q = torch.randn(B, H, Sq, D, device="cuda").bfloat16()
+    k = torch.randn(B, H, Skv, D, device="cuda").bfloat16()
+    v = torch.randn(B, H, Skv, D, device="cuda").bfloat16()
+    out = F.flash_attention(q, k, v, D ** -0.5, causal=True)
+    check_status()
+    s = (q.float() @ k.float().transpose(-1, -2)) * D ** -0.5
+    i = torch.arange(Sq, device="cuda")[:, None]
+    j = torch.arange(Skv, device="cuda")[None, :]
+    s = s.masked_fill(j > i + (Skv - Sq), float("-inf"))
+    ref = torch.softmax(s, -1) @ v.float()
+    assert (out.float() - ref).abs().max().item() < 3e-2

@@ -324,3 +324,22 @@ def test_xor_training_matches_the_cpu_restatement():
     pred = model(x).to_vec()
     assert [round(v) for v in pred] == [0, 1, 1, 0]  # 4/4 accuracy
     assert mine[-1] < 0.01
+
+
+def test_causal_attention_ignores_later_positions():
+    """forward_attn(causal=True): the output at position t does not change when later positions change."""
+    import torch
+
+    import ferrum_b200 as fb
+
+    torch.manual_seed(0)
+    m = fb.nn.MultiHeadAttention(32, 2)
+    x = torch.randn(2, 6, 32)
+    x2 = x.clone()
+    x2[:, 4:] += 1.0
+    with fb.no_grad():
+        y, y2 = m.forward_attn(x, x, x, causal=True), m.forward_attn(x2, x2, x2, causal=True)
+        z, z2 = m.forward_attn(x, x, x), m.forward_attn(x2, x2, x2)
+    y, y2, z, z2 = (t.torch() if hasattr(t, "torch") else t for t in (y, y2, z, z2))
+    assert float((y[:, :4] - y2[:, :4]).abs().max()) == 0.0
+    assert float((z[:, :4] - z2[:, :4]).abs().max()) > 0.0
