@@ -28,7 +28,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--bf16", action="store_true", help="bf16 tensor-core GEMMs (default for embedding)")
     ap.add_argument("--graph", action="store_true",
-                    help="ours, 1 GPU, mnist: record the step (zero_grad, forward, backward, Adam) in a CUDA graph and "
+                    help="ours, mnist (any number of GPUs): record the step (zero_grad, forward, backward, Adam) in a CUDA graph and "
                          "replay it (the batch fetch and the LR schedule stay outside)")
     a = ap.parse_args()
 
@@ -113,8 +113,8 @@ def main():
     it = batches()
     graphed = None
     if a.graph:
-        if a.impl != "ours" or world > 1 or a.config != "mnist":
-            raise SystemExit("--graph: ours, one GPU, mnist (the embedding config draws a dropout mask per step)")
+        if a.impl != "ours" or a.config != "mnist":
+            raise SystemExit("--graph: ours, mnist (the embedding config changes its learning rate from the host)")
 
         def train(xb, yb):
             opt.zero_grad()
