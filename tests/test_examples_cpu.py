@@ -44,9 +44,14 @@ def test_ddp_example_runs_as_two_gloo_ranks(tmp_path):
     import subprocess
     import sys
 
+    import socket
+
+    with socket.socket() as sock:  # a free port, so that parallel test runs do not collide
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29733", os.path.join(EX, "train_ddp_mlp.py")]
+           "127.0.0.1", "--master-port", str(port), os.path.join(EX, "train_ddp_mlp.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("world 2:")]
