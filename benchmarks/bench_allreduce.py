@@ -1,6 +1,6 @@
 """Sweep of the fused all-reduce + Adam kernel against NCCL all-reduce followed by a separate torch Adam.
 
-    python -m torch.distributed.run --nproc-per-node N -m ferrum_b200.parallel.bench_allreduce [--max-mb 1024]
+    python -m torch.distributed.run --nproc-per-node N -m benchmarks.bench_allreduce [--max-mb 1024]
 
 fp32 gradient buckets of 4 KB ... 1 GB filled ~ N(0, 1e-2), random Adam state.  Times are CUDA-event durations
 on the launching stream, max over ranks, median of the timed iterations; "bus GB/s" uses the all-reduce

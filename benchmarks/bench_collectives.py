@@ -1,6 +1,6 @@
 """Latency / bandwidth of the native collectives against their NCCL counterparts.
 
-    python -m torch.distributed.run --nproc-per-node N -m ferrum_b200.parallel.bench_collectives [--max-mb 256]
+    python -m torch.distributed.run --nproc-per-node N -m benchmarks.bench_collectives [--max-mb 256]
 
 For fp32 messages of 4 KB ... --max-mb: all_reduce(sum), broadcast, all_gather (message = per-rank chunk),
 reduce_scatter (message = full input), plus the barrier; every call goes through the public ``ProcessGroup`` methods

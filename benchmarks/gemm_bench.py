@@ -1,6 +1,6 @@
 """Time the tcgen05 GEMM on one shape (also the small case used for kernel profiles).
 
-    python -m ferrum_b200.ops.gemm_bench --m 8192 --n 4096 --k 4096 --layout nt --iters 20 [--cublas]
+    python -m benchmarks.gemm_bench --m 8192 --n 4096 --k 4096 --layout nt --iters 20 [--cublas]
 
 ``--layout``: ``nt`` forward (A, B K-major), ``nn`` dgrad (B MN-major), ``tn`` wgrad (both MN-major, fp32 out).
 Prints one JSON line: median CUDA-event time after warm-up with an L2 flush between iterations, TFLOP/s, and the
@@ -34,6 +34,11 @@ def main():
     ap.add_argument("--dual", action="store_true", help="also store act'(z) (second bf16 output; needs --act)")
     ap.add_argument("--two-cta", action="store_true", help="use the CTA-pair (cta_group::2) kernel")
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) on the same operands")
+    ap.add_argument("--out", default=None, choices=["bf16", "fp32"],
+                    help="result dtype of the bf16 GEMM (default: fp32 for the tn layout, bf16 otherwise)")
+    ap.add_argument("--accumulate", action="store_true", help="add the product to the existing fp32 result")
+    ap.add_argument("--group-m", type=int, default=0,
+                    help="CTA-pair kernel: 256-row blocks per rasterisation group (default: the library's)")
     a = ap.parse_args()
 
     from ferrum_b200.ops import gemm as _g
@@ -49,8 +54,12 @@ def main():
         torch.bfloat16)
     B = torch.randn(K, N, device="cuda").to(torch.bfloat16).t() if b_mn else torch.randn(N, K, device="cuda").to(
         torch.bfloat16)
-    out = torch.empty(M, N, device="cuda",
-                      dtype=torch.float32 if (a.layout == "tn" or a.tf32 or a.simt) else torch.bfloat16)
+    f32_out = (a.out == "fp32") if a.out is not None else a.layout == "tn"
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float32 if (f32_out or a.tf32 or a.simt) else torch.bfloat16)
+    if a.group_m > 0:
+        from ferrum_b200 import _lib as _l0
+
+        _l0.cuda().fb_gemm_bf16_2cta_set_group_m(a.group_m)
     if a.tf32 or a.simt:
         A, B = A.float().t().contiguous().t() if a_mn else A.float(), B.float().t().contiguous().t() if b_mn else B.float()
     bias = torch.randn(N, device="cuda") if a.bias else None
@@ -77,26 +86,28 @@ def main():
     elif a.tf32:
         ms = timeit(lambda: gemm_tf32(A, B, bias=bias, act=a.act, out=out, kernel="2cta" if a.two_cta else "1cta"))
     else:
-        ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux))
+        ms = timeit(lambda: gemm_bf16(A, B, bias=bias, act=a.act, out=out, act_grad=aux, accumulate=a.accumulate))
     check_status()
     flops = 2.0 * M * N * K
-    if a.two_cta:
+    if a.two_cta and not a.accumulate:
         ref = (A[:256].float() @ B.float().t())
+        if bias is not None:
+            ref = ref + bias
+        if a.act == "gelu":
+            ref = torch.nn.functional.gelu(ref, approximate="tanh")
+        elif a.act == "relu":
+            ref = torch.relu(ref)
         res_err = (out[:256].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
-    res = {"kernel": "gemm_f32_simt" if a.simt else ("gemm_tf32_tcgen05_2cta" if a.two_cta else "gemm_tf32_tcgen05") if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms,
+    res = {"kernel": "gemm_f32_simt" if a.simt else ("gemm_tf32_tcgen05_2cta" if a.two_cta else "gemm_tf32_tcgen05") if a.tf32 else "gemm_bf16_tcgen05_2cta" if a.two_cta else "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "layout": a.layout, "out": str(out.dtype).replace("torch.", ""), "ms": ms,
            "tflops": flops / ms / 1e9}
-    if a.two_cta:
+    if a.two_cta and not a.accumulate:
         res["rel_err_first_rows"] = res_err
-        from ferrum_b200 import _lib as _l
-
-        res["splitk_tail_tiles"] = _l.cuda().fb_gemm_bf16_2cta_last_splitk_tail()
     if a.simt:
         ref = (A[:256].double() @ B.double().t()).float()
         res["rel_err_first_rows"] = (out[:256] - ref).abs().max().item() / max(1.0, ref.abs().max().item())
         # FFMA ceiling of this GPU: SMs x 128 lanes x 2 flops x clock (the clock is whatever the run gets)
         res["ffma_peak_tflops_at_max_clock"] = 148 * 128 * 2 * 1.965e9 / 1e12
-    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
-                         "MEASURED_PEAKS.json")
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(peaks):
         pk = json.load(open(peaks))
         res["frac_of_measured_bf16_burst"] = res["tflops"] / pk["bf16_tflops"]

@@ -1,6 +1,6 @@
 """Time the memory-bound kernels on benchmark-sized inputs and report achieved bandwidth against the roofline.
 
-    python -m ferrum_b200.ops.kernel_bench [--only NAME[,NAME...]] [--iters 20] [--small] [--out FILE]
+    python -m benchmarks.kernel_bench [--only NAME[,NAME...]] [--iters 20] [--small] [--out FILE]
 
 Each case launches one kernel entry point on inputs larger than the L2 (so DRAM figures mean something), is
 timed with CUDA events after warm-up (median), and reports ``GB/s = algorithmic bytes / time`` and the fraction of

@@ -110,8 +110,7 @@ _CUDA_SIGS = {
     "fb_gemm_tf32": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, P, P]),
     "fb_gemm_tf32_2cta": (I, [P, P, P, P, I, I, I, LL, LL, LL, I, I, I, I, I, P, P]),
     "fb_gemm_bf16_2cta_set_profile": (None, [P]),
-    "fb_gemm_bf16_2cta_set_splitk_workspace": (I, [P, LL]),
-    "fb_gemm_bf16_2cta_last_splitk_tail": (I, []),
+    "fb_gemm_bf16_2cta_set_group_m": (I, [I]),
     "fb_gemm_bf16_batched": (I, [P, P, P, I, I, I, LL, LL, LL, I, I, LL, LL, LL, LL, LL, LL, I, I, I, I, F, P, P]),
     "fb_gemm_f32_simt": (I, [P, P, P, P, I, I, I, LL, LL, LL, LL, LL, I, I, I, LL, LL, LL, P]),
     # secondary layers

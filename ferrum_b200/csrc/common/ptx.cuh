@@ -112,11 +112,24 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* map, uin
       "r"(w)
       : "memory");
 }
+// 2-D tiled store shared -> global as part of the issuing thread's current bulk group.  Same rule on x; a box that
+// reaches past the extent of the map is clipped.  The writes to shared memory must be made visible to the async
+// proxy first (fence_proxy_async_smem by the writers, then a barrier, then the store).
 __device__ __forceinline__ void tma_store_2d(const void* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
+}
+// Same slab added element-wise to what global memory holds (fp32 / bf16 maps); x is subject to the same rule.
+__device__ __forceinline__ void tma_reduce_add_2d(const void* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t smem_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>

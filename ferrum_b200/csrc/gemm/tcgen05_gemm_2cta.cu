@@ -18,6 +18,14 @@
 //   warps 2..5  epilogue of this CTA's 128 rows (eight warps, two per TMEM lane quarter, measured slower: the
 //               value + derivative epilogue dropped from 1500 to 1413 TFLOP/s); "accumulator drained" is signalled
 //               to the leader's mbarrier from both CTAs
+//
+// Epilogue.  A warp reads its 32 accumulator rows from tensor memory 32 columns at a time (tcgen05.ld), applies
+// bias / activation in registers, writes the 32 x 128-byte slab into 128-byte-swizzled shared memory (conflict-free
+// 16-byte stores) and one lane hands the slab to the TMA unit (cp.async.bulk.tensor store; cp.reduce...add when the
+// result is accumulated into an existing fp32 matrix).  Global memory therefore sees whole 128-byte lines instead of
+// 16-byte pieces of 32 different rows, and the warp is free for the next slab while the copy drains; each warp
+// double-buffers its slab (bulk groups, wait_group.read before a buffer is rewritten).  Results whose base or row
+// pitch is not 16-byte aligned leave through plain register stores.
 // Every wait is bounded; the two cluster barriers (after set-up, before exit) are
 // reached on every path, including the abort path.
 #include <cuda.h>
@@ -40,8 +48,8 @@ constexpr int kBM = 128;       // rows per CTA; the pair covers 256
 constexpr int kRowBytes = 128;  // one swizzled shared-memory row = one k-block of a K-major operand
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
-constexpr int kGroupM = 8;     // pair-tiles (256 rows) per rasterisation group
 constexpr int kABytes = kBM * kRowBytes;        // 16 KB
+constexpr int kSlabBytes = 32 * kRowBytes;      // one output slab of a warp: 32 rows x 128 bytes
 
 // BN = columns per pair (each CTA stages half of them).  256 is the high-intensity shape; 128 halves the
 // tile for small outputs that would otherwise occupy less than half of the CTA pairs.
@@ -50,11 +58,13 @@ struct Cfg2 {
   static constexpr int kBBytes = (BN / 2) * kRowBytes;        // 16 KB / 8 KB
   static constexpr int kStageBytes = kABytes + kBBytes;       // 32 KB / 24 KB per CTA
   static constexpr int kStages = BN == 256 ? 6 : 8;
-  // + one 32 x 33 fp32 transposing buffer per epilogue warp (push mode writes rows, not columns, to the peers)
-  static constexpr int kTransposeBytes = kEpilogueWarps * 32 * 33 * 4;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kTransposeBytes;
+  // two output slabs per epilogue warp (the push mode uses a warp's 8 KB as a 32 x 33 fp32 transposing buffer)
+  static constexpr int kStoreBytes = kEpilogueWarps * 2 * kSlabBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
   static constexpr int kTmemCols = 2 * BN;                    // two accumulators
 };
+
+enum : int { kOutRegs = 0, kOutTma = 1, kOutPush = 2 };
 
 struct Args2 {
   void* out;
@@ -66,65 +76,42 @@ struct Args2 {
   int out_bf16;
   int act;
   int beta;
+  int out_mode;  // kOutTma: slabs leave through the TMA unit; kOutRegs: register stores (unaligned results); kOutPush
+  int group_m;   // pair-tiles (256 rows) per rasterisation group
   int32_t* status;
   unsigned long long timeout_ns;
   // Optional per-pair timing record (4 x 64-bit per pair, nanoseconds): MMA thread waiting for a drained
   // accumulator, MMA thread waiting for operands, one epilogue warp busy, whole kernel.  NULL = off.
   unsigned long long* prof;
-  int stream_stores;  // bf16 outputs leave with st.global.cs (evict-first) so they do not displace operand tiles in L2
-  // Push mode (weight gradients of a data-parallel job): instead of a local fp32 matrix, every 16-byte piece of the
+  // Push mode (weight gradients of a data-parallel job): instead of a local fp32 matrix, every piece of the
   // result goes straight to the rank that OWNS it — element e of the bucket belongs to shard o = e / per, and
   // source rank s deposits its value at element s * per + (e - o * per) of rank o's bucket region — over NVLink
   // peer stores issued from this epilogue, so the gradient reduce-scatter travels while the next tiles are
-  // multiplied and the bucket kernel finds all contributions in local memory.  push_world <= 1: off.
+  // multiplied and the bucket kernel finds all contributions in local memory.  The 32 x 32 block of a warp is
+  // turned through shared memory so that one store instruction writes 128 contiguous bytes of ONE row.
   int push_world, push_rank;
   unsigned char* push_arena[8];
   long long push_bucket_off;  // byte offset of the bucket's gradient region inside every arena
   long long push_rel;         // bucket-relative element index of out[0][0] (multiple of 4)
   long long push_per;         // elements per shard (multiple of 4)
-  int push_coalesced;         // 1: rows leave as 128-byte stores through a shared-memory transpose
-  int f32_rows;               // 1: plain fp32 results are stored row-wise the same way (FERRUM_GEMM_F32_ROWS)
-  // Split-K tail (on only while a workspace is set; measured neutral on B200 — 204.8 us with and without on the
-  // 4096 x 4096 x 8192 weight-gradient shape, because the kernel is bound by operand delivery from L2, not by the
-  // number of tile rounds: a half-empty last round simply runs faster).  When the tile count leaves a last round in which at most half of the CTA pairs have work, each of
-  // those `splitk_tail` tiles is shared by two pairs — the owner multiplies the first half of K, a helper the
-  // second half, deposits its fp32 partial in `splitk_ws` and raises a flag; the owner adds it in its epilogue.
-  // Helpers never wait, every pair of the grid is resident, and the owner's wait is bounded.  0 = off.
-  int splitk_tail;
-  float* splitk_ws;           // [slot][256][256] fp32
-  unsigned* splitk_flags;     // [slot][2 CTAs][4 epilogue warps]
 };
-
-// A unit of work of a CTA pair: a whole tile, or one half of the K range of a tile of the last round.
-struct Unit2 {
-  int tile, k_lo, k_hi, role, slot;  // role 0 = whole tile, 1 = owner (first half of K), 2 = helper (second half)
-};
-__device__ __forceinline__ Unit2 decode_unit2(int u, int num_tiles, int tail, int num_kb) {
-  Unit2 x;
-  const int full = num_tiles - tail;
-  if (u < full) {
-    x.tile = u; x.k_lo = 0; x.k_hi = num_kb; x.role = 0; x.slot = 0;
-  } else if (u < full + tail) {
-    x.tile = u; x.k_lo = 0; x.k_hi = num_kb >> 1; x.role = 1; x.slot = u - full;
-  } else {
-    x.slot = u - full - tail; x.tile = full + x.slot; x.k_lo = num_kb >> 1; x.k_hi = num_kb; x.role = 2;
-  }
-  return x;
-}
 
 unsigned long long* g_prof_buffer = nullptr;
-unsigned char* g_splitk_base = nullptr;  // 4 KB of flags, then 256 KB per slot
-int g_splitk_slots = 0;
-int g_last_splitk_tail = 0;  // tiles shared by two pairs in the most recent launch (introspection for benches / tests)
+int g_group_m = 8;
 
-__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
-  const int per_group = kGroupM * num_n;
+__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int group_m, int& m_blk, int& n_blk) {
+  const int per_group = group_m * num_n;
   const int g = t / per_group;
-  const int first_m = g * kGroupM;
-  const int gsize = min(num_m - first_m, kGroupM);
+  const int first_m = g * group_m;
+  const int gsize = min(num_m - first_m, group_m);
   const int r = t - g * per_group;
   m_blk = first_m + (r % gsize);
   n_blk = r / gsize;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&b2);
 }
 
 // kTf32: fp32 operands multiplied as TF32 (kind::tf32).  A k-block is always one 128-byte row, so it holds 32
@@ -133,6 +120,7 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
 template <int BN, bool kTf32 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
                       const Args2 p) {
   constexpr int kBN = BN;
   constexpr int kBK = kTf32 ? 32 : 64, kUmmaK = kTf32 ? 8 : 16, kChunk = kTf32 ? 32 : 64;
@@ -141,14 +129,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   constexpr int kTmemCols = Cfg2<BN>::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bar_base = smem + kStages * kStageBytes;
+  uint8_t* slab_base = smem + kStages * kStageBytes;             // 1024-byte aligned (swizzle atom of the stores)
+  uint8_t* bar_base = slab_base + Cfg2<BN>::kStoreBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader only
   uint64_t* empty_bar = full_bar + kStages;                     // one set per CTA
   uint64_t* tmem_full = empty_bar + kStages;                    // one set per CTA
   uint64_t* tmem_empty = tmem_full + 2;                         // used in the leader only
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* transpose_buf = reinterpret_cast<float*>(bar_base + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,7 +148,6 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const int num_n = (p.N + kBN - 1) / kBN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int num_units = num_tiles + p.splitk_tail;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -175,6 +162,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tma_a);
     ptx::prefetch_tensormap(&tma_b);
+    if (p.out_mode == kOutTma) {
+      ptx::prefetch_tensormap(&tma_c);
+      if (p.out2 != nullptr) ptx::prefetch_tensormap(&tma_c2);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_2cta(tmem_slot, kTmemCols);
@@ -195,13 +186,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
-      for (int u = pair; u < num_units && ok; u += num_pairs) {
-        const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int m_blk, n_blk;
-        tile_coords2(un.tile, num_m, num_n, m_blk, n_blk);
+        tile_coords2(t, num_m, num_n, p.group_m, m_blk, n_blk);
         const int m0 = m_blk * 2 * kBM + static_cast<int>(rank) * kBM;        // this CTA's 128 rows of A
         const int n0 = n_blk * kBN + static_cast<int>(rank) * (kBN / 2);      // this CTA's 128 rows of B
-        for (int kb = un.k_lo; kb < un.k_hi; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 11, blockIdx.x, stage);
             ok = false;
@@ -260,8 +250,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       bool ok = true;
       unsigned long long w_acc = 0, w_ops = 0;
       const unsigned long long k_start = p.prof ? ptx::globaltimer() : 0;
-      for (int u = pair; u < num_units && ok; u += num_pairs) {
-        const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         unsigned long long t0 = p.prof ? ptx::globaltimer() : 0;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 12, blockIdx.x, acc);
@@ -270,7 +259,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (p.prof) w_acc += ptx::globaltimer() - t0;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = un.k_lo; kb < un.k_hi; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {
           t0 = p.prof ? ptx::globaltimer() : 0;
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 13, blockIdx.x, stage);
@@ -286,9 +275,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, a_sbo, a_layout);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, b_sbo, b_layout);
             if constexpr (kTf32)
-              ptx::umma_tf32_2cta(d_tmem, adesc, bdesc, idesc, (kb != un.k_lo || k != 0) ? 1u : 0u);
+              ptx::umma_tf32_2cta(d_tmem, adesc, bdesc, idesc, (kb != 0 || k != 0) ? 1u : 0u);
             else
-              ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb != un.k_lo || k != 0) ? 1u : 0u);
+              ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb != 0 || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit_2cta(&empty_bar[stage], 0x3);  // frees the slot in both CTAs
           if (++stage == kStages) {
@@ -314,12 +303,18 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint32_t acc_phase = 0;
     const bool vec_ok = ((p.ldc * (p.out_bf16 ? 2 : 4)) % 16 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    uint8_t* my_slabs = slab_base + (warp - 2) * (2 * kSlabBytes);
+    const uint32_t slab_u32 = ptx::smem_u32(my_slabs);
+    const uint32_t row_off = static_cast<uint32_t>(lane) * kRowBytes;  // this lane's row inside a slab
+    const uint32_t sw = static_cast<uint32_t>(lane) & 7u;              // 128-byte swizzle: chunk ^= row % 8
+    const bool dual = p.out2 != nullptr;
+    int slot = 0;  // slab the next single-output store fills (the other one may still be read by the TMA unit)
     unsigned long long e_busy = 0;
-    for (int u = pair; u < num_units; u += num_pairs) {
-      const Unit2 un = decode_unit2(u, num_tiles, p.splitk_tail, num_kb);
+    for (int t = pair; t < num_tiles; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords2(un.tile, num_m, num_n, m_blk, n_blk);
-      const int row = m_blk * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+      tile_coords2(t, num_m, num_n, p.group_m, m_blk, n_blk);
+      const int row_base = m_blk * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32;  // first of this warp's rows
+      const int row = row_base + lane;
       const int n0 = n_blk * kBN;
       const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
       const unsigned long long e0 = p.prof ? ptx::globaltimer() : 0;
@@ -328,37 +323,6 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         break;
       }
       ptx::tc_fence_after();
-      // split-K tail: this warp's 32 rows of the partial live at ws_rows; its flag at ws_flag
-      float* ws_rows = nullptr;
-      unsigned* ws_flag = nullptr;
-      if (un.role != 0) {
-        ws_rows = p.splitk_ws + (static_cast<long long>(un.slot) * 256 + static_cast<int>(rank) * kBM + quarter * 32 +
-                                 lane) * 256;
-        ws_flag = p.splitk_flags + un.slot * 8 + static_cast<int>(rank) * 4 + (warp - 2);
-      }
-      if (un.role == 1) {
-        // owner: the helper's partial must have arrived (bounded wait; the helper never waits for anybody)
-        bool got = true;
-        if (lane == 0) {
-          const unsigned long long w0 = ptx::globaltimer();
-          unsigned it = 0;
-          while (ptx::ld_acquire_gpu(ws_flag) == 0u) {
-            if (((++it) & 63u) == 0u && (*abort_flag || ptx::globaltimer() - w0 > p.timeout_ns)) {
-              got = false;
-              break;
-            }
-          }
-        }
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) {
-          if (lane == 0) {
-            *abort_flag = 1;
-            report_status(p.status, kStatusGemmTimeout, 15, blockIdx.x, un.slot);
-          }
-          break;
-        }
-        __syncwarp();
-      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBN;
 #pragma unroll 1
       for (int j = 0; j < kBN / 32; ++j) {
@@ -366,36 +330,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         ptx::tmem_ld_32x32b_x32(taddr + j * 32, r);
         ptx::tmem_wait_ld();
         const int col0 = n0 + j * 32;
-        if (un.role == 2) {
-          // helper: raw partial sums into the workspace (this lane's row, 32 columns)
-          float4* dst = reinterpret_cast<float4*>(ws_rows + j * 32);
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            dst[q] = make_float4(__uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
-                                 __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
-          continue;
-        }
-        if (un.role == 1) {
-          const float4* src = reinterpret_cast<const float4*>(ws_rows + j * 32);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 x = __ldcg(src + q);
-            r[q * 4] = __float_as_uint(__uint_as_float(r[q * 4]) + x.x);
-            r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + x.y);
-            r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + x.z);
-            r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + x.w);
-          }
-        }
-        if (p.push_world > 1 && p.push_coalesced) {
-          // Push mode, coalesced: the 32 x 32 block of this warp is turned through shared memory so that one store
-          // instruction writes 128 contiguous bytes of ONE row (a full line per NVLink write) instead of 16 bytes
-          // of 32 different rows.  Every lane takes part (rows past M are skipped at the store).
+        if (p.out_mode == kOutPush) {
+          // every lane takes part (rows past M are skipped at the store)
           if (col0 < p.N) {
-            float* tb = transpose_buf + (warp - 2) * (32 * 33);
+            float* tb = reinterpret_cast<float*>(my_slabs);
 #pragma unroll
             for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = __uint_as_float(r[i]);
             __syncwarp();
-            const int row_base = row - lane;  // first of this warp's 32 rows
             long long rel = p.push_rel + static_cast<long long>(row_base) * p.ldc + col0;
             int owner = static_cast<int>(rel / p.push_per);
             long long jj = rel - static_cast<long long>(owner) * p.push_per;
@@ -421,147 +362,148 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             }
             __syncwarp();
           }
-        } else if (p.f32_rows && !p.out_bf16 && p.out2 == nullptr && p.bias == nullptr && p.act == FB_ACT_NONE) {
-          // Plain fp32 result (weight gradients), row-wise stores: the same shared-memory turn as the push mode,
-          // so that a store instruction writes one full 128-byte line instead of 16 bytes of 32 rows.
-          if (col0 < p.N) {
-            float* tb = transpose_buf + (warp - 2) * (32 * 33);
+          continue;
+        }
+        float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = __uint_as_float(r[i]);
-            __syncwarp();
-            const int row_base = row - lane;
-            const bool col_ok = col0 + lane < p.N;
-            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row_base) * p.ldc + col0 + lane;
-#pragma unroll 8
-            for (int rr = 0; rr < 32; ++rr) {
-              if (row_base + rr < p.M && col_ok) {
-                const float x = tb[rr * 33 + lane];
-                o[0] = p.beta ? o[0] + x : x;
-              }
-              o += p.ldc;
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        if (p.bias != nullptr && col0 < p.N) {
+          if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias + col0) & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {  // eight 16-byte loads instead of 32 guarded scalar ones
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + q);
+              v[4 * q] += b4.x; v[4 * q + 1] += b4.y; v[4 * q + 2] += b4.z; v[4 * q + 3] += b4.w;
             }
-            __syncwarp();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
           }
-        } else if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.bias != nullptr) {
-            if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.bias + col0) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {  // eight 16-byte loads instead of 32 guarded scalar ones
-                const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + q);
-                v[4 * q] += b4.x; v[4 * q + 1] += b4.y; v[4 * q + 2] += b4.z; v[4 * q + 3] += b4.w;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) v[i] += __ldg(p.bias + col0 + i);
-            }
-          }
-          const bool full = (col0 + 32 <= p.N) && vec_ok;
-          if (p.out2 != nullptr) {
-            // value and derivative of the activation, both stored as bf16
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + 0 + static_cast<long long>(row) * p.ldc + col0;
-            __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + 0 + static_cast<long long>(row) * p.ldc + col0;
+        }
+        if (p.out_mode == kOutTma) {
+          // Columns or rows past the edge of the matrix are computed like the rest (the operand tiles were
+          // zero-filled there) and clipped by the TMA unit.
+          if (p.out_bf16) {
+            // two 32-column chunks (64 bf16 = 128 bytes per row) fill one slab
+            const int half = j & 1;
+            const uint32_t s_val = slab_u32 + (dual ? 0u : static_cast<uint32_t>(slot) * kSlabBytes) + row_off;
+            const uint32_t s_der = slab_u32 + kSlabBytes + row_off;
             float dv[32];
-            act_both_chunk(v, dv, p.act);
+            if (dual) act_both_chunk(v, dv, p.act);
+            else if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
+            if (half == 0) {
+              // the slab(s) about to be rewritten must have been read by the store issued from them
+              if (lane == 0) {
+                if (dual) ptx::tma_store_wait_read<0>();
+                else ptx::tma_store_wait_read<1>();
+              }
+              __syncwarp();
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              uint32_t wv[4], wd[4];
-#pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                __nv_bfloat162 pa = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
-                __nv_bfloat162 pd = __floats2bfloat162_rn(dv[q * 8 + h * 2], dv[q * 8 + h * 2 + 1]);
-                wv[h] = *reinterpret_cast<uint32_t*>(&pa);
-                wd[h] = *reinterpret_cast<uint32_t*>(&pd);
-              }
-              if (full) {
-                if (p.stream_stores) {
-                  __stcs(reinterpret_cast<uint4*>(o) + q, make_uint4(wv[0], wv[1], wv[2], wv[3]));
-                  __stcs(reinterpret_cast<uint4*>(o2) + q, make_uint4(wd[0], wd[1], wd[2], wd[3]));
-                } else {
-                  reinterpret_cast<uint4*>(o)[q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                  reinterpret_cast<uint4*>(o2)[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+              const uint32_t off = ((static_cast<uint32_t>(half * 4 + q)) ^ sw) << 4;
+              ptx::st_shared_v4(s_val + off, pack_bf16(v[q * 8], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
+                                pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7]));
+              if (dual)
+                ptx::st_shared_v4(s_der + off, pack_bf16(dv[q * 8], dv[q * 8 + 1]),
+                                  pack_bf16(dv[q * 8 + 2], dv[q * 8 + 3]), pack_bf16(dv[q * 8 + 4], dv[q * 8 + 5]),
+                                  pack_bf16(dv[q * 8 + 6], dv[q * 8 + 7]));
+            }
+            if (half == 1) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (row_base < p.M && col0 - 32 < p.N) {
+                  ptx::tma_store_2d(&tma_c, my_slabs + (dual ? 0 : slot * kSlabBytes), col0 - 32, row_base);
+                  if (dual) ptx::tma_store_2d(&tma_c2, my_slabs + kSlabBytes, col0 - 32, row_base);
                 }
-              } else {
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                  const int c = q * 8 + h * 2;
-                  const __nv_bfloat162 pa = *reinterpret_cast<__nv_bfloat162*>(&wv[h]);
-                  const __nv_bfloat162 pd = *reinterpret_cast<__nv_bfloat162*>(&wd[h]);
-                  if (col0 + c < p.N) { o[c] = pa.x; o2[c] = pd.x; }
-                  if (col0 + c + 1 < p.N) { o[c + 1] = pa.y; o2[c + 1] = pd.y; }
-                }
+                ptx::tma_store_commit();  // always, so that the group count stays in step with `slot`
               }
+              slot ^= 1;
             }
           } else {
-          if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
-          if (p.out_bf16) {
+            if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
+            const uint32_t s_val = slab_u32 + static_cast<uint32_t>(slot) * kSlabBytes + row_off;
+            if (lane == 0) ptx::tma_store_wait_read<1>();
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              ptx::st_shared_v4(s_val + ((static_cast<uint32_t>(q) ^ sw) << 4), __float_as_uint(v[q * 4]),
+                                __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
+                                __float_as_uint(v[q * 4 + 3]));
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (row_base < p.M && col0 < p.N) {
+                if (p.beta) ptx::tma_reduce_add_2d(&tma_c, my_slabs + slot * kSlabBytes, col0, row_base);
+                else ptx::tma_store_2d(&tma_c, my_slabs + slot * kSlabBytes, col0, row_base);
+              }
+              ptx::tma_store_commit();
+            }
+            slot ^= 1;
+          }
+          continue;
+        }
+        // ---- register stores (results the TMA unit cannot address)
+        if (row < p.M && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N) && vec_ok;
+          if (dual) {
+            // value and derivative of the activation, both stored as bf16
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+            __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<long long>(row) * p.ldc + col0;
+            float dv[32];
+            act_both_chunk(v, dv, p.act);
             if (full) {
-              uint4* o4 = reinterpret_cast<uint4*>(o);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                uint32_t w[4];
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                  __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
-                  w[h] = *reinterpret_cast<uint32_t*>(&b2);
-                }
-                if (p.stream_stores) __stcs(o4 + q, make_uint4(w[0], w[1], w[2], w[3]));
-                else o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                reinterpret_cast<uint4*>(o)[q] =
+                    make_uint4(pack_bf16(v[q * 8], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
+                               pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7]));
+                reinterpret_cast<uint4*>(o2)[q] =
+                    make_uint4(pack_bf16(dv[q * 8], dv[q * 8 + 1]), pack_bf16(dv[q * 8 + 2], dv[q * 8 + 3]),
+                               pack_bf16(dv[q * 8 + 4], dv[q * 8 + 5]), pack_bf16(dv[q * 8 + 6], dv[q * 8 + 7]));
               }
             } else {
               for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
-            }
-          } else if (p.push_world > 1 && !p.push_coalesced) {
-            // one division per 32-column chunk, then (owner, offset) advance with the columns
-            const long long rel = p.push_rel + static_cast<long long>(row) * p.ldc + col0;
-            int owner = static_cast<int>(rel / p.push_per);
-            long long j = rel - static_cast<long long>(owner) * p.push_per;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              if (col0 + 4 * q < p.N) {  // N is a multiple of 4 in push mode
-                float4* dst = reinterpret_cast<float4*>(p.push_arena[owner] + p.push_bucket_off +
-                                                        (static_cast<long long>(p.push_rank) * p.push_per + j) * 4);
-                ptx::st_relaxed_sys_f4(dst, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
-              }
-              j += 4;
-              if (j >= p.push_per) {
-                j -= p.push_per;
-                ++owner;
-              }
+                if (col0 + i < p.N) {
+                  o[i] = __float2bfloat16_rn(v[i]);
+                  o2[i] = __float2bfloat16_rn(dv[i]);
+                }
             }
           } else {
-            float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
-            if (full) {
-              float4* o4 = reinterpret_cast<float4*>(o);
+            if (p.act != FB_ACT_NONE) act_chunk(v, p.act);
+            if (p.out_bf16) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+              if (full) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 x = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                if (p.beta) {
-                  const float4 old = o4[q];
-                  x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
-                }
-                o4[q] = x;
+                for (int q = 0; q < 4; ++q)
+                  reinterpret_cast<uint4*>(o)[q] =
+                      make_uint4(pack_bf16(v[q * 8], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
+                                 pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7]));
+              } else {
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) o[i] = __float2bfloat16_rn(v[i]);
               }
             } else {
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
+              float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldc + col0;
+              if (full) {
+                float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  float4 x = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                  if (p.beta) {
+                    const float4 old = o4[q];
+                    x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                  }
+                  o4[q] = x;
+                }
+              } else {
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) o[i] = p.beta ? o[i] + v[i] : v[i];
+              }
             }
           }
-          }  // out2 == nullptr
         }
-      }
-      if (un.role == 2) {          // helper: publish the partial
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) ptx::st_release_gpu(ws_flag, 1u);
-      } else if (un.role == 1) {   // owner: the slot is free for the next launch
-        __syncwarp();
-        if (lane == 0) *ws_flag = 0u;
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -571,6 +513,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    // the slabs belong to the TMA unit until its stores have completed (reached on the abort path too)
+    if (lane == 0) ptx::tma_store_wait<0>();
     if (p.prof && warp == 2 && lane == 0 && rank == 0) p.prof[pair * 4 + 2] = e_busy;
   }
 
@@ -652,7 +596,7 @@ template <int BN, bool kTf32 = false>
 int launch2(const void* a, const void* b, Args2& args, long long lda, long long ldb, int pairs, long long num_tiles,
             cudaStream_t stream) {
   constexpr int kEb = kTf32 ? 4 : 2, kChunk = kRowBytes / kEb;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc, mc2;
   // MN-major fp32 tiles are written with the 32-byte-chunk swizzle the tensor core requires for them
   bool ok = args.a_mn_major ? make_map2(&ma, a, args.M, args.K, lda, kChunk, kEb, kTf32)
                             : make_map2(&ma, a, args.K, args.M, lda, kBM, kEb);
@@ -660,38 +604,33 @@ int launch2(const void* a, const void* b, Args2& args, long long lda, long long 
   ok = args.b_mn_major ? make_map2(&mb, b, args.N, args.K, ldb, kChunk, kEb, kTf32)
                        : make_map2(&mb, b, args.K, args.N, ldb, BN / 2, kEb);
   if (!ok) return -2;
+  // Result maps: 32-row x 128-byte slabs.  A result the TMA unit cannot address (base or pitch not 16-byte
+  // aligned) is stored from registers instead.
+  mc = ma;
+  mc2 = ma;
+  if (args.out_mode != kOutPush) {
+    const int eb = args.out_bf16 ? 2 : 4;
+    bool tma = make_map2(&mc, args.out, args.N, args.M, args.ldc, 32, eb);
+    if (tma && args.out2 != nullptr) tma = make_map2(&mc2, args.out2, args.N, args.M, args.ldc, 32, eb);
+    if (!tma) mc = mc2 = ma;
+    args.out_mode = tma ? kOutTma : kOutRegs;
+  }
   if (num_tiles < pairs) pairs = static_cast<int>(num_tiles);
-  gemm_bf16_2cta_kernel<BN, kTf32><<<2 * pairs, kThreads, Cfg2<BN>::kSmemBytes, stream>>>(ma, mb, args);
+  gemm_bf16_2cta_kernel<BN, kTf32><<<2 * pairs, kThreads, Cfg2<BN>::kSmemBytes, stream>>>(ma, mb, mc, mc2, args);
   return static_cast<int>(cudaGetLastError());
 }
 
 // Arguments every entry point fills the same way.
 void fill_common(Args2& args, int32_t* status) {
+  args.out_mode = kOutTma;  // launch2 falls back to register stores where no map can be built
+  args.group_m = g_group_m;
   args.push_world = 0;
   args.push_rank = 0;
   args.push_bucket_off = args.push_rel = 0;
   args.push_per = 4;
-  args.push_coalesced = 0;
-  args.splitk_tail = 0;
-  args.splitk_ws = nullptr;
-  args.splitk_flags = nullptr;
-  {
-    static int f32_rows = -1;
-    if (f32_rows < 0) {
-      const char* e = getenv("FERRUM_GEMM_F32_ROWS");
-      f32_rows = (e != nullptr && e[0] == '1') ? 1 : 0;
-    }
-    args.f32_rows = f32_rows;
-  }
   for (int i = 0; i < 8; ++i) args.push_arena[i] = nullptr;
   args.status = status;
   args.timeout_ns = 2000000000ull;
-  static int stream_default = -1;
-  if (stream_default < 0) {
-    const char* e = getenv("FERRUM_GEMM_STREAM_STORES");
-    stream_default = (e != nullptr && e[0] == '1') ? 1 : 0;
-  }
-  args.stream_stores = stream_default;
   args.prof = g_prof_buffer;
 }
 
@@ -704,22 +643,12 @@ extern "C" int fb_gemm_bf16_2cta_pairs() { return fb::max_pairs<256>(); }
 // (see Args2::prof); NULL switches the record off again.
 extern "C" void fb_gemm_bf16_2cta_set_profile(unsigned long long* buffer) { fb::g_prof_buffer = buffer; }
 
-// Zero-initialised device buffer for the split-K tail (4 KB of flags followed by 256 KB per shared tile; 40 slots
-// = 10 MB cover every grid of up to 80 CTA pairs).  The caller owns it and must keep GEMMs that use it on one
-// stream at a time.  NULL switches the tail split off.
-extern "C" int fb_gemm_bf16_2cta_last_splitk_tail() { return fb::g_last_splitk_tail; }
-
-extern "C" int fb_gemm_bf16_2cta_set_splitk_workspace(void* buffer, long long bytes) {
-  if (buffer == nullptr || bytes < 4096 + 262144) {
-    fb::g_splitk_base = nullptr;
-    fb::g_splitk_slots = 0;
-    return 0;
-  }
-  if (reinterpret_cast<uintptr_t>(buffer) & 15) return -1;
-  fb::g_splitk_base = static_cast<unsigned char*>(buffer);
-  const long long slots = (bytes - 4096) / 262144;
-  fb::g_splitk_slots = static_cast<int>(slots > 128 ? 128 : slots);  // 128 slots x 8 flags x 4 B = the 4 KB of flags
-  return fb::g_splitk_slots;
+// Rasterisation: tiles are walked in groups of `group_m` 256-row blocks x all column blocks, so that the pairs
+// working at the same time share operand tiles in L2.  Returns the previous value; values < 1 only query.
+extern "C" int fb_gemm_bf16_2cta_set_group_m(int group_m) {
+  const int prev = fb::g_group_m;
+  if (group_m >= 1) fb::g_group_m = group_m;
+  return prev;
 }
 
 // Same arguments as fb_gemm_bf16.  Returns -3 when CTA pairs cannot be launched on this device.
@@ -755,21 +684,7 @@ extern "C" int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* 
   // The 256 x 128 tile moves a third more operand bytes per flop through shared memory and measured ~0.6 of the
   // wide tile's rate on large problems, so it only pays where the wide tiling leaves at least half of the pairs
   // without any tile at all.
-  {
-    // split-K tail (see Args2::splitk_tail): plain fp32 results only, a last round that fills at most half of the grid
-    const long long used = tiles256 < pairs ? tiles256 : pairs;
-    const long long tail = used > 0 ? tiles256 % used : 0;
-    const int num_kb = (K + 63) / 64;
-    if (g_splitk_base != nullptr && !out_bf16 && out2 == nullptr && bias == nullptr &&
-        act == FB_ACT_NONE && tiles256 > used && tail > 0 && 2 * tail <= used && tail <= g_splitk_slots &&
-        num_kb >= 16) {
-      args.splitk_tail = static_cast<int>(tail);
-      args.splitk_flags = reinterpret_cast<unsigned*>(g_splitk_base);
-      args.splitk_ws = reinterpret_cast<float*>(g_splitk_base + 4096);
-    }
-    g_last_splitk_tail = args.splitk_tail;
-  }
-  const bool narrow = args.splitk_tail == 0 && max_pairs<128>() >= pairs && 2 * tiles256 <= pairs;
+  const bool narrow = max_pairs<128>() >= pairs && 2 * tiles256 <= pairs;
   return narrow ? launch2<128>(a, b, args, lda, ldb, pairs, tiles128, stream)
                 : launch2<256>(a, b, args, lda, ldb, pairs, tiles256, stream);
 }
@@ -803,7 +718,7 @@ extern "C" int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, con
 }
 
 // Weight-gradient GEMM of a data-parallel job with the reduce-scatter fused into the epilogue (see Args2::push_*):
-// result[M, N] = A * B^T in fp32, every 16-byte piece stored into the bucket region of the rank that owns it.
+// result[M, N] = A * B^T in fp32, every row piece stored into the bucket region of the rank that owns it.
 // ctx: this rank's view of all arenas; bucket_off: byte offset of the bucket's gradient region in every arena;
 // out_rel: bucket-relative element index of result[0][0]; ldc: row pitch of the result inside the bucket (elements);
 // per: elements per shard (bucket length / world).  N, ldc, out_rel and per must be multiples of 4 and the result
@@ -837,20 +752,13 @@ extern "C" int fb_gemm_bf16_2cta_push(const void* a, const void* b, int M, int N
   args.act = FB_ACT_NONE;
   args.beta = 0;
   fill_common(args, status);
+  args.out_mode = kOutPush;
   args.push_world = ctx->world;
   args.push_rank = ctx->rank;
   for (int r = 0; r < ctx->world; ++r) args.push_arena[r] = ctx->arena[r];
   args.push_bucket_off = bucket_off;
   args.push_rel = out_rel;
   args.push_per = per;
-  {
-    static int coalesced = -1;
-    if (coalesced < 0) {
-      const char* e = getenv("FERRUM_PUSH_COALESCED");
-      coalesced = (e != nullptr && e[0] == '0') ? 0 : 1;
-    }
-    args.push_coalesced = coalesced;
-  }
   int pairs = pairs_avail;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   const long long tiles = static_cast<long long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);

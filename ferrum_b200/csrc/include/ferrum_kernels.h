@@ -57,8 +57,6 @@ int fb_gemm_tf32(const float* a, const float* b, float* out, const float* bias, 
 int fb_gemm_tf32_2cta(const float* a, const float* b, float* out, const float* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn_major, int b_mn_major, int act, int beta, int max_ctas,
                  int32_t* status, cudaStream_t stream);
-// Workspace of the CTA-pair kernel's split-K tail (zeroed device memory: 4 KB + 256 KB per slot); NULL = off.
-int fb_gemm_bf16_2cta_set_splitk_workspace(void* buffer, long long bytes);
 // CTA-pair variant (tcgen05 cta_group::2; 256 x 256 tiles on two SMs, 256 x 128 for small outputs); same
 // arguments.  Returns -3 where clusters of two CTAs cannot be scheduled.  fb_gemm_bf16_2cta_pairs() = resident pairs.
 int fb_gemm_bf16_2cta(const void* a, const void* b, void* out, void* out2, const float* bias, int M, int N, int K,
@@ -68,6 +66,9 @@ int fb_gemm_bf16_2cta_pairs(void);
 // Timing record of the CTA-pair kernel: 4 x 64-bit words per pair (ns): MMA thread waiting for a drained accumulator,
 // waiting for operands, one epilogue warp busy, whole kernel.  NULL switches it off.
 void fb_gemm_bf16_2cta_set_profile(unsigned long long* buffer);
+// Tiles are walked in groups of `group_m` 256-row blocks x all column blocks (default 8); returns the previous
+// value, values < 1 only query.
+int fb_gemm_bf16_2cta_set_group_m(int group_m);
 // Batched form over batch_outer x batch_inner slices: out[s] = alpha * A[s] * B[s]^T (+= out[s] when beta).
 // Each operand carries its own (outer, inner) slice strides in elements, so head-interleaved [B, S, H, D]
 // activations are multiplied in place.  Slice strides of A and B must be multiples of 8 elements.

@@ -64,28 +64,6 @@ def _major(t: torch.Tensor):
     raise ValueError("GEMM operand needs one unit stride")
 
 
-_splitk_ws = None
-_splitk_on = os.environ.get("FERRUM_GEMM_SPLITK", "0") == "1"
-
-
-def enable_splitk_tail(flag: bool = True) -> None:
-    """Share the tiles of a half-empty last round between two CTA pairs (halves of K) for plain fp32 results.
-    Off by default: measured neutral on B200 (the kernel is bound by operand delivery, not by tile rounds)."""
-    global _splitk_on, _splitk_ws
-    _splitk_on = bool(flag)
-    if not flag and _splitk_ws is not None:
-        _lib.cuda().fb_gemm_bf16_2cta_set_splitk_workspace(None, 0)
-        _splitk_ws = None
-
-
-def _ensure_splitk_workspace(device) -> None:
-    """Hand the CTA-pair kernel its (zero-initialised, 10 MB) workspace for the split-K tail of fp32 results, once."""
-    global _splitk_ws
-    if _splitk_on and _splitk_ws is None:
-        _splitk_ws = torch.zeros(4096 + 40 * 262144, dtype=torch.uint8, device=device)
-        _lib.cuda().fb_gemm_bf16_2cta_set_splitk_workspace(_splitk_ws.data_ptr(), _splitk_ws.numel())
-
-
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: str | None = None,
               out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
               accumulate: bool = False, act_grad: torch.Tensor | None = None) -> torch.Tensor:
@@ -112,8 +90,6 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     aux = act_grad.data_ptr() if act_grad is not None else None
     lib = _lib.cuda()
     pair = _use_2cta and M >= 512 and N >= 128
-    if pair and out.dtype == torch.float32 and bias is None and act is None:
-        _ensure_splitk_workspace(a.device)
     fn = lib.fb_gemm_bf16_2cta if pair else lib.fb_gemm_bf16
     rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), aux, bias.data_ptr() if bias is not None else None,
             M, N, K, lda, ldb, out.stride(0), a_mn, b_mn, 1 if out.dtype == torch.bfloat16 else 0,

@@ -242,35 +242,44 @@ def test_tf32_precision_mode_trains_a_linear_layer():
     assert (x.grad - xr.grad).abs().max().item() < 1e-4 + 5e-3 * xr.grad.abs().max().item()
 
 
-@pytest.mark.parametrize("M,N,K,acc", [(4096, 4096, 2048, False), (4096, 4096, 1024, True), (2560, 7680, 1536, False),
-                                       (4088, 3704, 1104, False)])
-def test_cta_pair_gemm_splitk_tail(M, N, K, acc):
-    """fp32 results whose tile count leaves a last round that fills at most half of the CTA pairs: those tiles are
-    shared by two pairs (halves of K), the helper's partial goes through the workspace.  Checked against a float64
-    product, also accumulating into an existing matrix and with ragged edges; run twice to exercise the flag reset."""
-    from ferrum_b200 import _lib
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 512), (2560, 1000, 192), (776, 264, 136)])
+def test_cta_pair_gemm_store_paths(M, N, K):
+    """The three ways a result leaves the CTA-pair kernel: slabs through the TMA unit (store, and reduce-add when
+    accumulating), both outputs of the value + derivative epilogue, and register stores for a result whose row
+    pitch the TMA unit cannot address (an odd-pitched view).  Run twice so that slab reuse across launches shows."""
     from ferrum_b200.ops.gemm import gemm_bf16
     from ferrum_b200.utils.runtime import check_status
 
-    pairs = _lib.cuda().fb_gemm_bf16_2cta_pairs()
-    tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    if pairs <= 0 or tiles <= pairs or not (0 < tiles % pairs <= pairs // 2):
-        pytest.skip(f"{tiles} tiles on {pairs} pairs leave no splittable tail")
     torch.manual_seed(M + N + K)
-    a = (torch.randn(K, M, device="cuda") * 0.5).bfloat16().t()      # both operands MN-major, like a wgrad
-    b = (torch.randn(K, N, device="cuda") * 0.5).bfloat16().t()
-    ref = (a.double() @ b.double().t())
-    from ferrum_b200.ops import gemm as g
-
-    g.enable_splitk_tail(True)
-    try:
-        for _ in range(2):
-            out = torch.full((M, N), 2.0, device="cuda") if acc else torch.empty(M, N, device="cuda")
-            gemm_bf16(a, b, out=out, out_dtype=torch.float32, accumulate=acc)
-            check_status()
-            assert _lib.cuda().fb_gemm_bf16_2cta_last_splitk_tail() == tiles % pairs  # the tail really was shared
-            want = (ref + 2.0) if acc else ref
-            err = (out.double() - want).abs().max().item()
-            assert err < 2e-3 * K ** 0.5 * 0.25 + 1e-3, err
-    finally:
-        g.enable_splitk_tail(False)
+    a = (torch.randn(K, M, device="cuda") * 0.5).bfloat16().t()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    ref = a.double() @ b.double().t()
+    tol = 2e-3 * K ** 0.5 * 0.25 + 1e-3
+    for _ in range(2):
+        out = torch.full((M, N), 2.0, device="cuda")
+        gemm_bf16(a, b, out=out, accumulate=True)
+        assert (out.double() - (ref + 2.0)).abs().max().item() < tol
+        # odd pitch: columns 1 .. N of a wider matrix (base and pitch off the 16-byte grid); neighbours stay untouched
+        wide = torch.full((M, N + 3), -7.0, device="cuda")
+        gemm_bf16(a, b, bias=bias, out=wide[:, 1:N + 1])
+        assert (wide[:, 1:N + 1].double() - (ref + bias)).abs().max().item() < tol
+        assert (wide[:, 0] == -7.0).all() and (wide[:, N + 1:] == -7.0).all()
+        wide_b = torch.full((M, N + 3), -7.0, device="cuda", dtype=torch.bfloat16)
+        gemm_bf16(a, b, bias=bias, act="relu", out=wide_b[:, 1:N + 1])
+        want = torch.relu(ref + bias)
+        assert (wide_b[:, 1:N + 1].double() - want).abs().max().item() < 3e-2 * max(1.0, want.abs().max().item())
+        assert (wide_b[:, 0] == -7.0).all() and (wide_b[:, N + 1:] == -7.0).all()
+        # TMA path next to memory that must stay untouched: a [M, N] block inside a wider 16-byte-pitched matrix
+        pad = (-N) % 8 + 8
+        host = torch.full((M + 2, N + pad), 5.0, device="cuda", dtype=torch.bfloat16)
+        der = torch.full((M + 2, N + pad), 5.0, device="cuda", dtype=torch.bfloat16)
+        gemm_bf16(a, b, bias=bias, act="gelu", out=host[1:M + 1, :N], act_grad=der[1:M + 1, :N])
+        z = (ref + bias).float().requires_grad_(True)
+        val = torch.nn.functional.gelu(z, approximate="tanh")
+        val.sum().backward()
+        assert (host[1:M + 1, :N].float() - val).abs().max().item() < 3e-2 * max(1.0, val.abs().max().item())
+        assert (der[1:M + 1, :N].float() - z.grad).abs().max().item() < 2e-2
+        for t in (host, der):
+            assert (t[0] == 5.0).all() and (t[M + 1] == 5.0).all() and (t[:, N:] == 5.0).all()
+        check_status()

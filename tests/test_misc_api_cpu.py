@@ -132,18 +132,15 @@ def test_core_autograd_hook_names():
 
 def test_new_switches_are_inert_without_a_gpu():
     """Options added for the GPU paths must not disturb CPU use: the blockwise attention is not selected for CPU
-    tensors, the split-K switch only records a flag, the engine's push mode and guard bands stay off."""
+    tensors, the engine's push mode and guard bands stay off."""
     import torch
 
     import ferrum_b200 as fb
     from ferrum_b200.ops import functional as F
-    from ferrum_b200.ops import gemm
     from ferrum_b200.parallel import Backend, DistributedDataParallel, ProcessGroup
 
     q = torch.randn(1, 2, 16, 64)
     assert not F.flash_attention_ok(q, q, q)
-    gemm.enable_splitk_tail(True)
-    gemm.enable_splitk_tail(False)
     model = fb.nn.Sequential(fb.nn.Linear(4, 3))
     ddp = DistributedDataParallel(model, ProcessGroup(Backend.Gloo, 0, 1))
     assert ddp.push_gradients(True) is ddp
