@@ -15,15 +15,18 @@ def build(model_cfg, depth, width, device):
     return torch.nn.Sequential(*layers).to(device)
 
 
-def run(args, model_cfg, lr, dist_env, timed_steps, ClockSampler):
+def run(args, model_cfg, lr, dist_env, timed_steps, ClockSampler, merge_clocks=None):
     import torch
 
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
+    own_group = False
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if not dist.is_initialized():  # bench.py's own arm may have left its rendezvous (gloo + NCCL) up
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            own_group = True
     torch.manual_seed(1234)
     model = build(model_cfg, args.depth, args.width, "cuda")
     net = model
@@ -50,9 +53,31 @@ def run(args, model_cfg, lr, dist_env, timed_steps, ClockSampler):
     def step_device():
         train_step(x_dev, y_dev)
 
+    # same read-back discipline as the other arm: the loss is copied to pinned host memory behind its step and read
+    # one step later, so the host never drains the GPU's queue
+    slots = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(3)]
+    events = [torch.cuda.Event() for _ in range(3)]
+    inflight = []
+    counter = [0]
+
+    def pop_loss():
+        i = inflight.pop(0)
+        events[i].synchronize()
+        losses.append(float(slots[i]))
+
     def step_e2e():
         loss = train_step(x_pin.to("cuda", non_blocking=True), y_pin.to("cuda", non_blocking=True))
-        losses.append(float(loss.item()))
+        i = counter[0] % 3
+        counter[0] += 1
+        slots[i].copy_(loss.detach().float(), non_blocking=True)
+        events[i].record()
+        inflight.append(i)
+        if len(inflight) > 1:
+            pop_loss()
+
+    def drain_e2e():
+        while inflight:
+            pop_loss()
 
     if world > 1:
         barrier = dist.barrier
@@ -64,18 +89,20 @@ def run(args, model_cfg, lr, dist_env, timed_steps, ClockSampler):
         step_device()
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()
     ms = timed_steps(step_device, args.steps, world, barrier)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
+    if merge_clocks is not None:
+        clocks = merge_clocks(clocks, world)
     e2e = None
     if not args.no_e2e:
         for _ in range(2):
             step_e2e()
-        ms2 = timed_steps(step_e2e, args.steps, world, barrier)
+        drain_e2e()
+        ms2 = timed_steps(step_e2e, args.steps, world, barrier, finish=drain_e2e)
         e2e = {"value": args.steps * B * world / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
                "h2d_bytes_per_step": x_pin.numel() * 4 + y_pin.numel() * 8, "d2h_bytes_per_step": 4,
                "final_loss": losses[-1] if losses else None}
-    if world > 1:
+    if own_group:
         dist.destroy_process_group()
     return ms, 0, clocks, e2e, "torch-ddp-nccl" if world > 1 else "torch-single"

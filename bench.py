@@ -12,8 +12,15 @@ timed with CUDA events between barrier + synchronize pairs; the reported time is
 prints one JSON line.
 
 ``--impl torch`` runs the stock torch DDP (NCCL + cuBLAS, bf16 autocast, fused Adam) build of the same model:
-the comparison baseline.  ``--impl reference`` is the arm for the unmodified reference; it is a Rust workspace
-with no Python package and no toolchain to build it in this image, so that arm reports itself unavailable.
+the comparison baseline.  ``--impl ours`` (the default) runs that baseline too, in the same invocation after its own
+arm (same N, steps, warm-up, its own clock samples), and reports ``vs_baseline`` = its samples/s divided by the
+baseline's, with the baseline's figures under ``baseline``; ``--no-baseline`` skips it.  ``--impl reference`` is the
+arm for the unmodified reference; it is a Rust workspace with no Python package and no toolchain to build it in this
+image, so that arm reports itself unavailable.
+
+End-to-end arm (``e2e``): every step's batch is drawn by a seeded ``RandomSampler`` from a dataset of several
+batches held in pinned host memory, assembled by the ``DataLoader``'s native worker threads, copied to the GPU
+(one step ahead, on a side stream) and the loss is read back to the host every step.
 """
 from __future__ import annotations
 
@@ -41,6 +48,11 @@ def parse():
     ap.add_argument("--depth", type=int, default=MODEL["depth"])
     ap.add_argument("--width", type=int, default=MODEL["width"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the torch-DDP baseline arm that --impl ours runs after its own (vs_baseline = null)")
+    ap.add_argument("--dataset-batches", type=int, default=8,
+                    help="batches in the pinned-host dataset the end-to-end arm samples from")
+    ap.add_argument("--loader-workers", type=int, default=6, help="gather threads of the end-to-end DataLoader")
     ap.add_argument("--overlap-optimizer", action="store_true",
                     help="1 GPU: run Adam per bucket behind each weight gradient on a side stream (the engine every "
                          "multi-GPU run uses) instead of one pass after backward; measured slower at one GPU "
@@ -115,6 +127,22 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def merge_clocks(mine: dict, world: int):
+    """Rank 0 gets its own record plus the slowest median clock and the union of reasons over all ranks' GPUs."""
+    if world <= 1:
+        return mine
+    import torch.distributed as dist
+
+    allc = [None] * world
+    dist.all_gather_object(allc, mine)
+    out = dict(allc[0])
+    meds = [c["sm_mhz"] for c in allc if c and c.get("sm_mhz") is not None]
+    out["sm_mhz_min_over_ranks"] = min(meds) if meds else None
+    out["sm_mhz_per_rank"] = [c.get("sm_mhz") if c else None for c in allc]
+    out["reasons"] = sorted({r for c in allc if c for r in c.get("reasons", [])})
+    return out
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -122,7 +150,8 @@ def dist_env():
     return rank, world, local
 
 
-def timed_steps(step_fn, steps, world, barrier):
+def timed_steps(step_fn, steps, world, barrier, finish=None):
+    """K calls of ``step_fn`` (and ``finish()``, which collects results still in flight) between two events."""
     import torch
 
     barrier()
@@ -131,6 +160,8 @@ def timed_steps(step_fn, steps, world, barrier):
     e0.record()
     for _ in range(steps):
         step_fn()
+    if finish is not None:
+        finish()
     e1.record()
     barrier()
     torch.cuda.synchronize()
@@ -174,8 +205,14 @@ def run_ours(args):
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     x_dev = torch.randn(B, MODEL["in_features"], device="cuda", generator=g)
     y_dev = torch.randint(0, MODEL["num_classes"], (B,), device="cuda", generator=g)
-    x_pin = x_dev.cpu().pin_memory()
-    y_pin = y_dev.cpu().pin_memory()
+    # end-to-end input pipeline: a dataset of several batches in pinned host memory, a seeded shuffle per epoch,
+    # rows gathered by the loader's native worker threads, device copy one step ahead on a side stream
+    nb = max(2, args.dataset_batches)
+    gh = torch.Generator().manual_seed(200 + rank)
+    x_pin = torch.empty(nb * B, MODEL["in_features"]).pin_memory()
+    y_pin = torch.empty(nb * B, dtype=torch.int64).pin_memory()
+    x_pin.normal_(generator=gh)
+    y_pin.random_(0, MODEL["num_classes"], generator=gh)
 
     def train_step(x, y):
         opt.zero_grad()
@@ -191,12 +228,10 @@ def run_ours(args):
 
     losses = []
 
-    def host_batches():  # the input pipeline: every step's batch starts in pinned host memory
-        while True:
-            yield x_pin, y_pin
-
-    # public input path: the prefetcher copies batch i + 1 on a side stream while step i computes
-    feed = fb.data.DevicePrefetcher(host_batches(), device=dev)
+    loader = (fb.data.DataLoader(fb.data.TensorDataset.from_tensors(x_pin, y_pin)).batch_size(B).shuffle(True)
+              .seed(77 + rank).drop_last(True).num_workers(args.loader_workers).pin_memory(True).to(dev).repeat(True))
+    feed = iter(loader)
+    readback = fb.cuda.HostReadback()
 
     graph_box = [None]
 
@@ -221,9 +256,16 @@ def run_ours(args):
                 graph_box[0] = None
 
     def step_e2e():
-        x, y = next(feed)                  # host -> device copy of this step's inputs (issued one step ahead)
+        xb, yb = next(feed)                # host -> device copy of this step's inputs (issued one step ahead)
+        x, y = xb._t, yb._t
         loss = graph_box[0](x, y) if graph_box[0] is not None else train_step(x, y)
-        losses.append(float(loss.item()))  # device -> host read of the step result
+        readback.push(loss)                # device -> host copy of the step result, enqueued behind the step
+        if readback.pending() > 1:         # read the previous step's loss while this step runs
+            losses.append(readback.pop())
+
+    def drain_e2e():
+        while readback.pending():
+            losses.append(readback.pop())
 
     if world > 1:
         import torch.distributed as dist
@@ -237,8 +279,7 @@ def run_ours(args):
         step_device()
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()
     launches0 = _lib.launch_count()
     ms_eager = timed_steps(step_device, args.steps, world, barrier)
     launches = _lib.launch_count() - launches0
@@ -253,20 +294,32 @@ def run_ours(args):
         for _ in range(3):
             step_graph()
         ms = timed_steps(step_graph, args.steps, world, barrier)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = merge_clocks(sampler.stop(), world)
     e2e = None
     if not args.no_e2e:
-        for _ in range(2):
+        for _ in range(3):
             step_e2e()
-        ms_e2e = timed_steps(step_e2e, args.steps, world, barrier)
+        drain_e2e()
+        ms_e2e = timed_steps(step_e2e, args.steps, world, barrier, finish=drain_e2e)
+        assert len(losses) == args.steps + 3, "every step's loss is read on the host"
         e2e = {"value": args.steps * B * world / (ms_e2e / 1e3), "unit": "samples/s",
                "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": (x_pin.numel() * x_pin.element_size() + y_pin.numel() * y_pin.element_size()),
+               "h2d_bytes_per_step": B * (x_pin.shape[1] * x_pin.element_size() + y_pin.element_size()),
                "d2h_bytes_per_step": 4, "final_loss": losses[-1] if losses else None,
-               "cuda_graph": graph_box[0] is not None, "input_prefetch": "side stream, one step ahead"}
+               "cuda_graph": graph_box[0] is not None,
+               "loss_readback": "every step, read on the host one step later (pinned buffer + event)",
+               "input_pipeline": f"DataLoader over {nb} batches in pinned host memory, seeded RandomSampler per "
+                                 f"epoch, {args.loader_workers} native gather threads, device copy one step ahead "
+                                 "on a side stream"}
+    feed.close()
+    loader.close()
     fb.utils.runtime.check_status()
     if engine is not None:
         engine.shutdown()
+    if use_engine:
+        # the torch.distributed rendezvous stays up for the baseline arm that follows in this process
+        fb.distributed.destroy_process_group(keep_torch=True)
+
     if world > 1:
         par = "nvlink-fused-ddp" + ("-sharded-master" if shard else "")
     else:
@@ -279,12 +332,14 @@ def run_torch(args):
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
     import torch_ddp_mlp
 
-    return torch_ddp_mlp.run(args, MODEL, LR, dist_env, timed_steps, ClockSampler)
+    return torch_ddp_mlp.run(args, MODEL, LR, dist_env, timed_steps, ClockSampler, merge_clocks)
 
 
 def main():
     args = parse()
     if args.impl == "reference":
+        if dist_env()[0] != 0:
+            return 0  # one line per job, from rank 0
         print(json.dumps({"impl": "reference",
                           "unavailable": "reference is a Rust workspace (no Python package: pip install of its "
                                          "source tree fails with 'neither setup.py nor pyproject.toml found') and "
@@ -294,18 +349,33 @@ def main():
     if world != args.gpus and args.gpus > 1:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
     ms_eager = None
+    base = None
     if args.impl == "ours":
         ms, launches, clocks, e2e, par, ms_eager = run_ours(args)
+        if not args.no_baseline:
+            import gc
+
+            import torch
+
+            gc.collect()              # the first arm's model, optimizer state and graphs go before the second starts
+            torch.cuda.empty_cache()
+            bms, _, bclocks, be2e, bpar = run_torch(args)
+            base = {"impl": "torch", "engine": bpar, "value": args.steps * args.batch * world / (bms / 1e3),
+                    "ms_per_step": bms / args.steps, "e2e_value": be2e["value"] if be2e else None,
+                    "clocks": bclocks}
     else:
         ms, launches, clocks, e2e, par = run_torch(args)
     if rank != 0:
         return 0
     steps = args.steps
     value = steps * args.batch * world / (ms / 1e3)
+    if base is not None:
+        base["ratio"] = value / base["value"]
+        base["e2e_ratio"] = (e2e["value"] / base["e2e_value"]) if (e2e and base["e2e_value"]) else None
     out = {
         "metric": "MLP-4096x8 DDP train samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
         "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+        "scaling": "weak", "vs_baseline": base["ratio"] if base is not None else None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
         "config": {"model": f"MLP {args.depth}x[Linear({args.width})-GELU-LayerNorm] + 1000-way head, 1024 inputs",
                    "global_batch": args.batch * world, "per_gpu_batch": args.batch, "seq_len": 1,
                    "parallelism": f"dp{world}" if world > 1 else "single-gpu", "engine": par,
@@ -313,6 +383,9 @@ def main():
                    "l2": "working set per step (>700 MB of weights, activations, optimizer state) exceeds the "
                          "126 MB L2, no explicit flush"},
         "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+        # the stock torch (cuBLAS + NCCL DDP + fused Adam) build of the same model, run after this arm in the same
+        # process on the same GPUs; vs_baseline = value / baseline.value
+        "baseline": base,
     }
     if ms_eager is not None:
         # same K steps launched kernel by kernel from Python; gpu_launches was counted in that region

@@ -22,6 +22,11 @@ SIGS = {
     "fb_sampler_num_batches": (LL, [LL, LL, I]),
     "fb_sampler_subset": (None, [P, LL, U64, P]),
     "fb_sampler_zipf": (I, [LL, D, LL, U64, P]),
+    # batch assembler of the DataLoader
+    "fb_loader_create": (P, [I, POINTER(c_void_p), PLL, LL, I, POINTER(c_void_p), I]),
+    "fb_loader_submit": (I, [P, I, P, LL]),
+    "fb_loader_wait": (I, [P, I]),
+    "fb_loader_destroy": (None, [P]),
     # bucket planner
     "fb_plan_buckets": (LL, [I, PLL, LL, LL, LL, PLL, PI, PLL, PLL, PI]),
     "fb_plan_shard": (None, [LL, I, I, PLL, PLL]),

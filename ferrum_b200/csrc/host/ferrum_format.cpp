@@ -18,6 +18,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -60,21 +61,21 @@ struct Cursor {
   size_t pos = 0;
   bool ok = true;
   uint32_t u32() {
-    if (pos + 4 > n) { ok = false; return 0; }
+    if (n - pos < 4) { ok = false; return 0; }
     uint32_t v = 0;
     for (int i = 0; i < 4; ++i) v |= static_cast<uint32_t>(p[pos + i]) << (8 * i);
     pos += 4;
     return v;
   }
   uint64_t u64() {
-    if (pos + 8 > n) { ok = false; return 0; }
+    if (n - pos < 8) { ok = false; return 0; }
     uint64_t v = 0;
     for (int i = 0; i < 8; ++i) v |= static_cast<uint64_t>(p[pos + i]) << (8 * i);
     pos += 8;
     return v;
   }
   std::string str(uint64_t len) {
-    if (pos + len > n) { ok = false; return {}; }
+    if (len > n - pos) { ok = false; return {}; }  // subtraction form: a huge length cannot wrap
     std::string s(reinterpret_cast<const char*>(p + pos), static_cast<size_t>(len));
     pos += static_cast<size_t>(len);
     return s;
@@ -142,7 +143,8 @@ FB_API int fb_ser_save(const char* path, int n, const char* const* names, const 
   return 0;
 }
 
-FB_API void* fb_ser_open(const char* path, char* err, int errlen) {
+namespace {
+void* open_impl(const char* path, char* err, int errlen) {
   FILE* f = std::fopen(path, "rb");
   if (f == nullptr) {
     set_err(err, errlen, std::string("Failed to open file: ") + path);
@@ -183,6 +185,9 @@ FB_API void* fb_ser_open(const char* path, char* err, int errlen) {
   r->data_size = c.u64();
   const uint64_t map_len = c.u64();
   (void)num;
+  // an entry takes at least 36 header bytes (name length, rank, dtype, offset, size), so a count the header
+  // cannot hold is rejected before anything is reserved for it
+  if (map_len > hlen / 36) c.ok = false;
   for (uint64_t i = 0; c.ok && i < map_len; ++i) {
     Entry e;
     e.name = c.str(c.u64());
@@ -192,7 +197,7 @@ FB_API void* fb_ser_open(const char* path, char* err, int errlen) {
     e.dtype = c.u32();
     e.offset = c.u64();
     e.size = c.u64();
-    if (e.dtype > 7 || e.offset + e.size > r->data_size) c.ok = false;
+    if (e.dtype > 7 || e.size > r->data_size || e.offset > r->data_size - e.size) c.ok = false;
     r->entries.push_back(std::move(e));
   }
   if (!c.ok) {
@@ -202,13 +207,25 @@ FB_API void* fb_ser_open(const char* path, char* err, int errlen) {
     return nullptr;
   }
   r->data_start = 16 + hlen;
-  if (r->data_start + r->data_size > static_cast<uint64_t>(fsize)) {
+  if (r->data_start > static_cast<uint64_t>(fsize) || r->data_size > static_cast<uint64_t>(fsize) - r->data_start) {
     std::fclose(f);
     delete r;
     set_err(err, errlen, "Failed to read data: file is truncated");
     return nullptr;
   }
   return r;
+}
+}  // namespace
+
+// No C++ exception crosses the C boundary: an allocation failure while parsing a hostile header becomes an error
+// string like every other defect of the file.
+FB_API void* fb_ser_open(const char* path, char* err, int errlen) {
+  try {
+    return open_impl(path, err, errlen);
+  } catch (const std::exception& e) {
+    set_err(err, errlen, std::string("Failed to deserialize header: ") + e.what());
+    return nullptr;
+  }
 }
 
 FB_API int fb_ser_count(void* h) { return static_cast<int>(static_cast<Reader*>(h)->entries.size()); }

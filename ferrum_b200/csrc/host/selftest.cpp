@@ -47,6 +47,11 @@ long long fb_sampler_distributed(long long len, int replicas, int rank, int do_s
 long long fb_sampler_num_batches(long long n, long long batch, int drop_last);
 void fb_sampler_subset(const long long* src, long long n, unsigned long long seed, long long* out);
 int fb_sampler_zipf(long long vocab, double s, long long n, unsigned long long seed, long long* out);
+void* fb_loader_create(int nfields, const void* const* src, const long long* row_bytes, long long rows, int depth,
+                       void* const* slot_ptrs, int threads);
+int fb_loader_submit(void* handle, int slot, const long long* idx, long long n);
+int fb_loader_wait(void* handle, int slot);
+void fb_loader_destroy(void* handle);
 }
 
 namespace {
@@ -272,6 +277,56 @@ void test_serializer(const std::string& dir, int id) {
   std::remove(path.c_str());
 }
 
+// Batch assembler: two fields, three slots, four workers; ragged batch sizes, a bad index, a busy slot, and a
+// destroy while jobs are still queued.
+void test_loader() {
+  const long long rows = 257, wx = 37, wy = 1;
+  std::vector<float> x(rows * wx);
+  std::vector<long long> y(rows * wy);
+  for (long long r = 0; r < rows; ++r) {
+    for (long long c = 0; c < wx; ++c) x[r * wx + c] = static_cast<float>(r * 1000 + c);
+    y[r] = r * 7;
+  }
+  const int depth = 3, cap = 64;
+  std::vector<std::vector<float>> sx(depth, std::vector<float>(cap * wx));
+  std::vector<std::vector<long long>> sy(depth, std::vector<long long>(cap));
+  const void* src[2] = {x.data(), y.data()};
+  const long long rb[2] = {wx * 4, wy * 8};
+  std::vector<void*> slots;
+  for (int s = 0; s < depth; ++s) {
+    slots.push_back(sx[s].data());
+    slots.push_back(sy[s].data());
+  }
+  void* h = fb_loader_create(2, src, rb, rows, depth, slots.data(), 4);
+  EXPECT(h != nullptr);
+  if (h == nullptr) return;
+  std::vector<long long> perm(rows);
+  fb_sampler_permutation(rows, 99, perm.data());
+  const long long sizes[5] = {64, 1, 33, 64, 0};
+  long long off = 0;
+  for (int b = 0; b < 5; ++b) {
+    const int slot = b % depth;
+    EXPECT(fb_loader_submit(h, slot, perm.data() + off, sizes[b]) == 0);
+    EXPECT(fb_loader_wait(h, slot) == 0);
+    for (long long i = 0; i < sizes[b]; ++i) {
+      const long long r = perm[off + i];
+      EXPECT(sx[slot][i * wx] == static_cast<float>(r * 1000) && sx[slot][i * wx + wx - 1] == x[r * wx + wx - 1]);
+      EXPECT(sy[slot][i] == r * 7);
+    }
+    off += sizes[b];
+  }
+  const long long bad[3] = {0, rows, 5};
+  EXPECT(fb_loader_submit(h, 0, bad, 3) == 0);
+  EXPECT(fb_loader_wait(h, 0) == -2);
+  EXPECT(fb_loader_submit(h, depth, perm.data(), 1) == -1);
+  // all slots in flight, then destroyed without waiting
+  for (int s = 0; s < depth; ++s) fb_loader_submit(h, s, perm.data() + s * cap, cap);
+  const int busy = fb_loader_submit(h, 0, perm.data(), 1);
+  EXPECT(busy == 0 || busy == -3);
+  fb_loader_destroy(h);
+  EXPECT(fb_loader_create(0, src, rb, rows, depth, slots.data(), 4) == nullptr);
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -282,6 +337,7 @@ int main(int argc, char** argv) {
     test_cpu_ref();
     test_samplers(0);
     test_serializer(dir, 0);
+    test_loader();
   } else {
     // the library keeps no shared mutable state, so concurrent callers must not race
     std::vector<std::thread> pool;
@@ -290,6 +346,7 @@ int main(int argc, char** argv) {
         test_planner();
         test_samplers(static_cast<unsigned long long>(t));
         test_serializer(dir, t + 1);
+        test_loader();  // each caller owns its loader; its workers run beside everybody else's
         if (t == 0) test_cpu_ref();
       });
     for (auto& th : pool) th.join();

@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 from .core import AllocationError, Device, DType, FerrumError, Tensor
-from .utils.graph import GraphedStep  # noqa: F401
+from .utils.graph import GraphedStep, HostReadback  # noqa: F401
 from .utils.runtime import DeviceStatusError, check_status, read_status  # noqa: F401
 
 

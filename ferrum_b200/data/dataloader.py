@@ -6,11 +6,19 @@ Builder-style configuration as in the reference (``batch_size`` / ``shuffle`` / 
 stacked tensors the batch is fetched with one row-gather kernel on the device that holds the data;
 ``num_workers > 0`` fetches samples of map-style datasets on a thread pool.  ``pin_memory(True)``
 together with ``to(device)`` stages batches in pinned host memory and copies them asynchronously.
+
+A dataset of stacked HOST tensors with ``num_workers > 0`` takes the native path: the worker threads of the host
+library (``csrc/host/loader.cpp``) gather the sampled rows into a ring of staging buffers a few batches ahead,
+and with ``to(device)`` the loader itself copies batch ``i + 1`` to the GPU on a side stream while the caller
+computes on batch ``i``.  ``repeat(True)`` runs epoch after epoch without draining that pipeline.
 """
 from __future__ import annotations
 
+import ctypes
+from collections import deque
 from concurrent.futures import ThreadPoolExecutor
 
+import numpy as np
 import torch
 
 from ..core import Tensor, _as_device, _unwrap
@@ -38,6 +46,8 @@ class DataLoader:
         self._pin, self._device = False, None
         self._epoch = 0
         self._pool = None
+        self._repeat = False
+        self._native = None  # (handle, slot tensors, copy stream) of the native batch assembler, built on first use
 
     @classmethod
     def new(cls, dataset):
@@ -81,6 +91,12 @@ class DataLoader:
         self._device = _as_device(device).to_torch()
         return self
 
+    def repeat(self, flag: bool = True) -> "DataLoader":
+        """Iterate epoch after epoch without end (a new shuffle per epoch); batches keep being prepared across
+        the epoch boundary."""
+        self._repeat = bool(flag)
+        return self
+
     def dataset(self) -> Dataset:
         return self._dataset
 
@@ -114,13 +130,139 @@ class DataLoader:
             return Tensor(src.to(self._device, non_blocking=True))
         return t
 
+    # ------------------------------------------------------------------ native batch assembler
+    _DEPTH = 3  # staging slots: one being copied to the device, one complete, one being gathered
+
+    def _native_ok(self, ds) -> bool:
+        return (self._num_workers > 0 and isinstance(ds, TensorDataset) and ds.stacked
+                and self._collate is default_collate and not ds.inputs.is_cuda and not ds.targets.is_cuda
+                and ds.inputs.is_contiguous() and ds.targets.is_contiguous() and ds.len() > 0)
+
+    def _native_state(self, ds):
+        if self._native is None:
+            from .. import _lib
+
+            to_gpu = self._device is not None and self._device.type == "cuda"
+            pin = (self._pin or to_gpu) and torch.cuda.is_available()
+            fields = (ds.inputs, ds.targets)
+            slots = [[torch.empty((self._batch_size,) + tuple(f.shape[1:]), dtype=f.dtype, pin_memory=pin)
+                      for f in fields] for _ in range(self._DEPTH)]
+            src = (ctypes.c_void_p * 2)(*(f.data_ptr() for f in fields))
+            rb = (ctypes.c_longlong * 2)(*(f.stride(0) * f.element_size() if f.dim() > 1 else f.element_size()
+                                           for f in fields))
+            ptrs = (ctypes.c_void_p * (2 * self._DEPTH))(*(t.data_ptr() for s in slots for t in s))
+            h = _lib.host().fb_loader_create(2, src, rb, ds.len(), self._DEPTH, ptrs, self._num_workers)
+            if not h:
+                raise RuntimeError("fb_loader_create failed")
+            stream = torch.cuda.Stream(device=self._device) if to_gpu else None
+            self._native = (h, slots, stream)
+        return self._native
+
+    def close(self) -> None:
+        """Stops the worker threads of the native batch assembler (also done when the loader is collected)."""
+        if self._native is not None:
+            from .. import _lib
+
+            h, self._native = self._native[0], None
+            _lib.host().fb_loader_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+    def _iter_native(self, ds):
+        from .. import _lib
+
+        lib = _lib.host()
+        h, slots, stream = self._native_state(ds)
+        to_gpu = stream is not None
+        state = {"bs": BatchSampler(self._make_sampler(), self._batch_size, self._drop_last)}
+        self._epoch += 1
+        pending = deque()                 # (slot, rows) handed to the workers, in order
+        copied = [None] * self._DEPTH     # event after the device copy that last read the slot
+        free = deque(range(self._DEPTH))
+
+        def next_indices():
+            idx = state["bs"].next_batch()
+            if idx is None and self._repeat:
+                state["bs"] = BatchSampler(self._make_sampler(), self._batch_size, self._drop_last)
+                self._epoch += 1
+                idx = state["bs"].next_batch()
+            return idx
+
+        def refill():
+            while free:
+                idx = next_indices()
+                if idx is None:
+                    return
+                slot = free.popleft()
+                if copied[slot] is not None:
+                    copied[slot].synchronize()    # the copy that read this slot has finished (long ago, normally)
+                    copied[slot] = None
+                idx = np.ascontiguousarray(idx, dtype=np.int64)
+                rc = lib.fb_loader_submit(h, slot, idx.ctypes.data, len(idx))
+                if rc != 0:
+                    raise RuntimeError(f"fb_loader_submit failed ({rc})")
+                pending.append((slot, len(idx)))
+
+        def stage():
+            """The next finished slot as a batch: on the GPU path its copy is enqueued on the side stream."""
+            if self._native is None or self._native[0] != h:
+                raise RuntimeError("the DataLoader was closed while it was being iterated")
+            refill()
+            if not pending:
+                return None
+            slot, n = pending.popleft()
+            rc = lib.fb_loader_wait(h, slot)
+            if rc == -2:
+                raise IndexError("sampler produced an index outside the dataset")
+            views = [t[:n] for t in slots[slot]]
+            if to_gpu:
+                with torch.cuda.stream(stream):
+                    dev = [v.to(self._device, non_blocking=True) for v in views]
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                copied[slot] = ev
+                free.append(slot)
+                return dev, ev
+            out = [v.clone() for v in views]      # the slot is rewritten a few batches later
+            free.append(slot)
+            return out, None
+
+        try:
+            staged = stage()
+            while staged is not None:
+                cur, ev = staged
+                staged = stage()                   # batch i + 1 is on its way before batch i is consumed
+                if ev is not None:
+                    consumer = torch.cuda.current_stream(self._device)
+                    consumer.wait_event(ev)
+                    for t in cur:
+                        t.record_stream(consumer)
+                yield Tensor(cur[0]), Tensor(cur[1])
+        finally:
+            # an abandoned iteration leaves slots in flight: wait for them so the ring can be reused
+            # (not after close(): the workers and the handle are gone then)
+            while pending and self._native is not None and self._native[0] == h:
+                slot, _ = pending.popleft()
+                lib.fb_loader_wait(h, slot)
+
     def iter(self):
+        ds = self._dataset
+        if self._native_ok(ds):
+            yield from self._iter_native(ds)
+            return
         bs = BatchSampler(self._make_sampler(), self._batch_size, self._drop_last)
         self._epoch += 1
-        ds = self._dataset
         fast = isinstance(ds, TensorDataset) and ds.stacked and self._collate is default_collate
         while True:
             idx = bs.next_batch()
+            if idx is None and self._repeat:
+                bs = BatchSampler(self._make_sampler(), self._batch_size, self._drop_last)
+                self._epoch += 1
+                idx = bs.next_batch()
             if idx is None:
                 return
             if fast:

@@ -115,12 +115,27 @@ class Optimizer:
         dev = next((p.device for p in self.params if p.is_cuda), None)
         if dev is None:
             raise ValueError("capturable mode needs parameters on a CUDA device")
+        vals = self._dyn_values()
+        if self._dyn is None:
+            self._dyn = torch.tensor(vals, dtype=torch.float32, device=dev)
+        else:  # in place: a recorded graph keeps reading the same device memory
+            self._dyn.copy_(torch.tensor(vals, dtype=torch.float32))
+        return self
+
+    def _dyn_values(self) -> list:
         t = int(getattr(self, "step_count", 0))
         b1 = float(getattr(self.config, "beta1", 1.0))
         b2 = float(getattr(self.config, "beta2", 1.0))
-        self._dyn = torch.tensor([self.config.lr, 1.0 - b1 ** t, 1.0 - b2 ** t, b1 ** t, b2 ** t, float(t)],
-                                 dtype=torch.float32, device=dev)
-        return self
+        return [self.config.lr, 1.0 - b1 ** t, 1.0 - b2 ** t, b1 ** t, b2 ** t, float(t)]
+
+    def _engine_owns_state(self) -> bool:
+        e = self._engine
+        return e is not None and hasattr(e, "owns_optimizer_state") and e.owns_optimizer_state()
+
+    def _after_state_load(self) -> None:
+        """The device-side step factors follow a restored step count (capturable mode)."""
+        if self._dyn is not None:
+            self.capturable(True)
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         if self._engine is not None:
@@ -226,17 +241,26 @@ class SGD(Optimizer):
         self.step_count += 1
 
     def state_tensors(self) -> dict:
-        out = {f"optim.velocity.{i}": v for i, v in enumerate(self.velocity) if v is not None}
+        """Momentum buffers and the step count.  With a fused data-parallel engine the buffers live in the
+        engine's shards and are gathered from their owners (collective: every rank calls it)."""
+        if self._engine_owns_state():
+            out = self._engine.export_optimizer_state(self)
+        else:
+            out = {f"optim.velocity.{i}": v for i, v in enumerate(self.velocity) if v is not None}
         out["optim.step"] = torch.tensor(self.step_count, dtype=torch.int64)
         return out
 
     def load_state_tensors(self, tensors: dict) -> None:
-        for i, p in enumerate(self.params):
-            v = tensors.get(f"optim.velocity.{i}")
-            if v is not None:
-                self.velocity[i] = v.to(p.device, p.dtype).clone()
+        if self._engine_owns_state():
+            self._engine.import_optimizer_state(self, tensors)
+        else:
+            for i, p in enumerate(self.params):
+                v = tensors.get(f"optim.velocity.{i}")
+                if v is not None:
+                    self.velocity[i] = v.to(p.device, p.dtype).clone()
         if "optim.step" in tensors:
             self.step_count = int(tensors["optim.step"].item())
+        self._after_state_load()
 
 
 class Adam(Optimizer):
@@ -308,19 +332,28 @@ class Adam(Optimizer):
                 p.sub_(c.lr * mh / (vh.sqrt() + c.eps))
 
     def state_tensors(self) -> dict:
+        """Both moments per parameter and the step count.  With a fused data-parallel engine the moments live in
+        the engine's shards and are gathered from their owners (collective: every rank calls it)."""
         out = {}
-        for i in range(len(self.params)):
-            if self.m[i] is not None:
-                out[f"optim.m.{i}"] = self.m[i]
-                out[f"optim.v.{i}"] = self.v[i]
+        if self._engine_owns_state():
+            out = self._engine.export_optimizer_state(self)
+        else:
+            for i in range(len(self.params)):
+                if self.m[i] is not None:
+                    out[f"optim.m.{i}"] = self.m[i]
+                    out[f"optim.v.{i}"] = self.v[i]
         out["optim.step"] = torch.tensor(self.step_count, dtype=torch.int64)
         return out
 
     def load_state_tensors(self, tensors: dict) -> None:
-        for i, p in enumerate(self.params):
-            m, v = tensors.get(f"optim.m.{i}"), tensors.get(f"optim.v.{i}")
-            if m is not None and v is not None:
-                self.m[i] = m.to(p.device, p.dtype).clone()
-                self.v[i] = v.to(p.device, p.dtype).clone()
+        if self._engine_owns_state():
+            self._engine.import_optimizer_state(self, tensors)
+        else:
+            for i, p in enumerate(self.params):
+                m, v = tensors.get(f"optim.m.{i}"), tensors.get(f"optim.v.{i}")
+                if m is not None and v is not None:
+                    self.m[i] = m.to(p.device, p.dtype).clone()
+                    self.v[i] = v.to(p.device, p.dtype).clone()
         if "optim.step" in tensors:
             self.step_count = int(tensors["optim.step"].item())
+        self._after_state_load()

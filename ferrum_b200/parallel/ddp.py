@@ -290,11 +290,15 @@ class DistributedDataParallel(Module, GradSink):
                 p.grad = self._flat_grads[offs[i]:offs[i] + sizes[i]].view(p.shape)
         # sinks and hooks
         self._small_runs = []  # (start, length) runs of non-GEMM gradients, zeroed every step
+        self._hook_handles, self._sink_modules = [], []
         sink_ids = set()
         for mod in self.inner.modules():
             if ((type(mod) is Linear or isinstance(mod, Embedding)) and id(mod.weight) in self._index
                     and self._use_native):
-                mod.grad_sink = self
+                # through __dict__: a plain attribute assignment would register the engine as a SUBMODULE of the
+                # layer and close a cycle (engine -> inner -> layer -> engine) under state_dict() / apply()
+                mod.__dict__["grad_sink"] = self
+                self._sink_modules.append(mod)
                 sink_ids.add(id(mod.weight))
         run = None
         order = sorted(range(len(self._params)), key=lambda i: offs[i])
@@ -311,7 +315,7 @@ class DistributedDataParallel(Module, GradSink):
                 if run:
                     self._small_runs.append(tuple(run))
                 run = [offs[i], sizes[i]]
-            p.register_post_accumulate_grad_hook(self._make_hook(i))
+            self._hook_handles.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
         if run:
             self._small_runs.append(tuple(run))
         self._sink_ids = sink_ids
@@ -423,6 +427,12 @@ class DistributedDataParallel(Module, GradSink):
         lib = _lib.cuda()
         a = self._arena
         cur = torch.cuda.current_stream()
+        # A Linear / Embedding weight whose GEMM did not run in this step still holds the previous step's gradient
+        # (those slots are overwritten, never zeroed): it takes part as a zero gradient, as in torch.
+        for i in bk.param_indices:
+            if not self._written[i] and id(self._params[i]) in self._sink_ids:
+                o = self._offs[i]
+                self._flat_grads[o:o + self._params[i].numel()].zero_()
         self._ready_event.record(cur)
         self._comm_stream.wait_event(self._ready_event)
         opt = self._opt
@@ -432,16 +442,7 @@ class DistributedDataParallel(Module, GradSink):
         if opt is not None:
             from ..optim.optimizers import SGD, Adam
 
-            if self._state_m is None:
-                dev = self._flat_params.device
-                shard_total = sum(((x.length + world - 1) // world + 3) // 4 * 4 for x in self.buckets)
-                self._state_m = torch.zeros(shard_total, device=dev, dtype=torch.float32)
-                self._state_v = torch.zeros(shard_total, device=dev, dtype=torch.float32) if isinstance(
-                    opt, Adam) else None
-                acc, self._state_off = 0, []
-                for x in self.buckets:
-                    self._state_off.append(acc)
-                    acc += ((x.length + world - 1) // world + 3) // 4 * 4
+            self._ensure_state()
             so = self._state_off[b]
             if isinstance(opt, Adam):
                 fuse = 2
@@ -464,7 +465,8 @@ class DistributedDataParallel(Module, GradSink):
                        "fb_dist_set_pushed_ranges")
         if self._capturable and fuse:
             if self._dev_epoch is None:  # continue the host-side sequence on the device
-                self._dev_epoch = torch.tensor([e], dtype=torch.int32, device=self._flat_params.device)
+                self._dev_epoch = torch.tensor([e - (1 << 32) if e >= (1 << 31) else e], dtype=torch.int32,
+                                               device=self._flat_params.device)
             dyn = opt._dyn
             if not self._advanced:
                 self._advanced = True
@@ -486,6 +488,24 @@ class DistributedDataParallel(Module, GradSink):
         if self._shard_master and fuse:
             self._master_stale = True
         _lib.check(rc, "fb_dist_allreduce")
+
+    def _shard_len(self, bk) -> int:
+        world = self._pg.world_size()
+        return ((bk.length + world - 1) // world + 3) // 4 * 4
+
+    def _ensure_state(self) -> None:
+        """Optimizer moments of this rank's shards (1 / world of every bucket), allocated on first use."""
+        if self._state_m is not None:
+            return
+        from ..optim.optimizers import Adam
+
+        dev = self._flat_params.device
+        acc, self._state_off = 0, []
+        for x in self.buckets:
+            self._state_off.append(acc)
+            acc += self._shard_len(x)
+        self._state_m = torch.zeros(acc, device=dev, dtype=torch.float32)
+        self._state_v = torch.zeros(acc, device=dev, dtype=torch.float32) if isinstance(self._opt, Adam) else None
 
     def _flush(self) -> None:
         """Launch every bucket that has not been reduced in this step (unused parameters, explicit sync)."""
@@ -611,6 +631,77 @@ class DistributedDataParallel(Module, GradSink):
             out[name] = full
         return out
 
+    def owns_optimizer_state(self) -> bool:
+        """True when the moments of the fused optimizer live in this engine's shards, not in the optimizer."""
+        self._build()
+        return bool(self._use_native and self._opt is not None)
+
+    def export_optimizer_state(self, optimizer) -> dict:
+        """The fused optimizer's moments as one full tensor per parameter, named as the optimizer itself names
+        them (``optim.m.<i>`` / ``optim.v.<i>`` for Adam, ``optim.velocity.<i>`` for SGD).  Collective: every
+        rank calls it (the shards are gathered from their owners), every rank gets the full state."""
+        from ..optim.optimizers import Adam
+
+        self._build()
+        full = self.gather_optimizer_state()
+        out = {}
+        if not full:
+            return out
+        adam = isinstance(optimizer, Adam)
+        for j, p in enumerate(optimizer.params):
+            i = self._index.get(id(p))
+            if i is None:
+                continue
+            o, n = self._offs[i], p.numel()
+            if adam:
+                out[f"optim.m.{j}"] = full["m"][o:o + n].view(p.shape).clone()
+                out[f"optim.v.{j}"] = full["v"][o:o + n].view(p.shape).clone()
+            elif optimizer.config.momentum != 0.0:
+                out[f"optim.velocity.{j}"] = full["m"][o:o + n].view(p.shape).clone()
+        return out
+
+    def import_optimizer_state(self, optimizer, tensors: dict) -> None:
+        """Inverse of :meth:`export_optimizer_state`: every rank keeps the slices of its own shards."""
+        from ..optim.optimizers import Adam
+
+        self._build()
+        if not self._use_native:
+            return
+        self._ensure_state()
+        adam = isinstance(optimizer, Adam)
+        dev = self._flat_params.device
+        names = (("m", "optim.m."), ("v", "optim.v.")) if adam else (("m", "optim.velocity."),)
+        world, rank = self._pg.world_size(), self._pg.rank()
+        for key, prefix in names:
+            st = self._state_m if key == "m" else self._state_v
+            if st is None:
+                continue
+            full = torch.zeros(self._total, device=dev, dtype=torch.float32)
+            for j, p in enumerate(optimizer.params):
+                i, t = self._index.get(id(p)), tensors.get(f"{prefix}{j}")
+                if i is not None and t is not None:
+                    o = self._offs[i]
+                    full[o:o + p.numel()] = t.to(dev, torch.float32).reshape(-1)
+            for b, bk in enumerate(self.buckets):
+                per = self._shard_len(bk)
+                lo = min(bk.length, per * rank)
+                hi = min(bk.length, lo + per)
+                if hi > lo:
+                    st[self._state_off[b]:self._state_off[b] + hi - lo] = full[bk.start + lo:bk.start + hi]
+
+    def state_dict(self, *args, **kw):
+        """Parameters and buffers of the wrapped module under ``inner.``; with sharded master weights the fp32
+        shards are gathered from their owners first (collective: every rank calls it)."""
+        self.sync_master_weights()
+        return super().state_dict(*args, **kw)
+
+    def load_state_dict(self, state_dict, *args, **kw):
+        out = super().load_state_dict(state_dict, *args, **kw)
+        if getattr(self, "_use_native", False):
+            self._refresh_shadow()      # the bf16 copies follow the loaded fp32 weights
+            self._master_stale = False
+        return out
+
     def check_guard_bands(self) -> int:
         """Debug aid (``FERRUM_GUARD_BANDS=1`` when the engine is built): verify that the pattern-filled bands
         around the parameter, gradient and bf16 regions of the arena are intact.  Returns the number of bands
@@ -626,8 +717,26 @@ class DistributedDataParallel(Module, GradSink):
         return len(guards)
 
     def shutdown(self) -> None:
-        """Release the arena (collective: every rank should call it after its last step)."""
-        if getattr(self, "_use_native", False) and getattr(self, "_arena", None) is not None:
+        """Release the arena (collective: every rank should call it after its last step) and hand the wrapped
+        module back in a state in which it trains on its own: gradient sinks and hooks are removed."""
+        for mod in getattr(self, "_sink_modules", []):
+            mod.__dict__["grad_sink"] = None
+        for h in getattr(self, "_hook_handles", []):
+            h.remove()
+        self._sink_modules, self._hook_handles = [], []
+        opt = self._opt
+        native = getattr(self, "_use_native", False) and getattr(self, "_arena", None) is not None
+        if opt is not None and getattr(opt, "_engine", None) is self:
+            state = None
+            if native and self._state_m is not None:
+                try:  # the moments return to the optimizer, which carries on unfused
+                    state = self.export_optimizer_state(opt)
+                except Exception:  # noqa: BLE001 - a peer is gone: the shards of the others cannot be fetched
+                    state = None
+            opt._engine = None
+            if state:
+                opt.load_state_tensors(state)
+        if native:
             self.sync_master_weights()
             torch.cuda.synchronize()
             self.check_guard_bands()

@@ -429,7 +429,9 @@ def is_initialized() -> bool:
     return _default_group is not None
 
 
-def destroy_process_group() -> None:
+def destroy_process_group(keep_torch: bool = False) -> None:
+    """Closes the default group and its arenas.  ``keep_torch`` leaves the ``torch.distributed`` rendezvous up for
+    code that runs afterwards in the same process (a later ``init_process_group`` reuses it)."""
     global _default_group
     with _lock:
         g, _default_group = _default_group, None
@@ -437,7 +439,7 @@ def destroy_process_group() -> None:
         g.close()
         import torch.distributed as dist
 
-        if g.world_size() > 1 and dist.is_initialized():
+        if g.world_size() > 1 and dist.is_initialized() and not keep_torch:
             dist.destroy_process_group()
 
 

@@ -153,9 +153,11 @@ class SymmetricArena:
         return self.flag_bytes
 
     def next_epoch(self, channel: int) -> int:
-        """Reserve the two epochs (entry, exit) a collective consumes on ``channel``."""
+        """Reserve the two epochs (entry, exit) a collective consumes on ``channel``.  Epochs live modulo 2^32,
+        the modulus of the device-side counter and of the kernels' wrap-safe comparison
+        ``(int32)(flag - epoch) >= 0``."""
         e = self._epochs[channel]
-        self._epochs[channel] = (e + 2) & 0x7FFFFFFF or 1
+        self._epochs[channel] = (e + 2) & 0xFFFFFFFF
         return e
 
     def has_multicast(self) -> bool:

@@ -72,3 +72,38 @@ class GraphedStep:
     @property
     def graph(self):
         return self._graph
+
+
+class HostReadback:
+    """Reads one small device tensor per step on the host without draining the GPU's queue.
+
+    ``loss.item()`` right after a step waits for that step and leaves the GPU idle while the host prepares the
+    next one.  ``push(t)`` instead enqueues a copy of ``t`` into pinned host memory behind the step that produced
+    it; ``pop()`` returns the oldest value once its copy has landed.  Popping the value of step ``i - 1`` after
+    step ``i`` has been launched keeps one step in the queue at all times; every step's value is still read.
+    """
+
+    def __init__(self, depth: int = 2, dtype: torch.dtype = torch.float32):
+        self._slots = [torch.empty((), dtype=dtype).pin_memory() for _ in range(depth + 1)]
+        self._events = [torch.cuda.Event() for _ in range(depth + 1)]
+        self._head = self._count = 0
+
+    def pending(self) -> int:
+        return self._count
+
+    def push(self, value) -> None:
+        if self._count == len(self._slots):
+            raise RuntimeError("HostReadback is full: pop() before pushing more")
+        i = (self._head + self._count) % len(self._slots)
+        self._slots[i].copy_(_unwrap(value).detach().reshape(()), non_blocking=True)
+        self._events[i].record()
+        self._count += 1
+
+    def pop(self) -> float:
+        if self._count == 0:
+            raise RuntimeError("HostReadback is empty")
+        i = self._head
+        self._events[i].synchronize()
+        self._head = (self._head + 1) % len(self._slots)
+        self._count -= 1
+        return float(self._slots[i])

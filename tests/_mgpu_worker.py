@@ -177,6 +177,107 @@ def main(out_dir):
     allp = [torch.empty_like(finals[1]) for _ in range(world)]
     pg.all_gather(allp, finals[1])
     check("push-mode replicas identical", all(torch.equal(allp[0], a) for a in allp))
+    # ---- the configuration bench.py runs with several GPUs: sharded fp32 master weights + fused Adam + bf16
+    #      autocast + the step replayed from a CUDA graph + default communication blocks.  Checked (a) against the
+    #      plain engine (eager launches, every rank keeps full masters) under the same autocast, which the fp32
+    #      sections above tie to the single-process trajectory, and (b) against one process on the whole batch.
+    def run_engine(bench_cfg, steps=6):
+        model = wide_model()
+        opt = fb.optim.Adam(model.parameters(), fb.optim.AdamConfig(lr=1e-3))
+        ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.5).fuse_optimizer(opt)
+        if bench_cfg:
+            ddp.shard_master_weights(True)
+
+        def one(xb, yb):
+            opt.zero_grad()
+            with fb.autocast():
+                loss = fb.nn.cross_entropy(ddp(xb), yb)
+            loss.backward()
+            opt.step()
+            return loss
+
+        if bench_cfg:
+            g = fb.cuda.GraphedStep(one, (xw, yw), optimizer=opt, warmup=2)
+            for _ in range(steps - 2):
+                g(xw, yw)
+        else:
+            for _ in range(steps):
+                one(xw, yw)
+        torch.cuda.synchronize()
+        fb.utils.runtime.check_status()
+        check(f"step count {opt.step_count}", opt.step_count == steps)
+        if bench_cfg:
+            ddp.sync_master_weights()
+        torch.cuda.synchronize()
+        flat = torch.cat([p.detach().reshape(-1) for p in model.torch_parameters()]).clone()
+        ddp.shutdown()
+        return flat
+
+    plain, benchlike = run_engine(False), run_engine(True)
+    err = (plain - benchlike).abs().max().item()
+    check(f"bench configuration equals the plain engine (max err {err:.2e})", err < 1e-6)
+    allp = [torch.empty_like(benchlike) for _ in range(world)]
+    pg.all_gather(allp, benchlike)
+    check("bench configuration: fp32 masters identical on every rank after sync_master_weights",
+          all(torch.equal(allp[0], a) for a in allp))
+    xs_all = [torch.empty_like(xw) for _ in range(world)]
+    ys_all = [torch.empty_like(yw) for _ in range(world)]
+    pg.all_gather(xs_all, xw)
+    pg.all_gather(ys_all, yw)
+    Xw, Yw = torch.cat(xs_all), torch.cat(ys_all)
+    single = wide_model()
+    sopt = fb.optim.Adam(single.parameters(), fb.optim.AdamConfig(lr=1e-3))
+    for _ in range(6):
+        sopt.zero_grad()
+        with fb.autocast():
+            loss = fb.nn.cross_entropy(single(Xw), Yw)
+        loss.backward()
+        sopt.step()
+    sflat = torch.cat([p.detach().reshape(-1) for p in single.torch_parameters()])
+    diff = (sflat - benchlike).abs()
+    # bf16 tolerance: the per-rank partial sums of a weight gradient are added in another order than the
+    # whole-batch GEMM adds them; Adam turns a sign change of a near-zero gradient into a full-size step, so a
+    # few elements may differ by up to steps x lr = 6e-3 while the bulk agrees to 1e-4
+    check(f"bench configuration vs one process on the whole batch (max {diff.max().item():.2e}, "
+          f"share > 1e-4: {(diff > 1e-4).float().mean().item():.4f})",
+          diff.max().item() < 6.5e-3 and (diff > 1e-4).float().mean().item() < 0.02)
+
+    # ---- checkpoint of a sharded engine: every rank saves (the moments are gathered from their owners, the fp32
+    #      masters synchronised), a fresh engine loads and continues like the uninterrupted run
+    def build_engine(seed):
+        torch.manual_seed(seed)
+        m = fb.nn.Sequential(fb.nn.Linear(128, 640), fb.nn.GELU(), fb.nn.LayerNorm([640]),
+                             fb.nn.Linear(640, 8)).to_device(fb.Device.Cuda(dev.index))
+        o = fb.optim.Adam(m.parameters(), fb.optim.AdamConfig(lr=1e-3, weight_decay=0.01))
+        e = d.DistributedDataParallel(m, pg).bucket_size_mb(0.1).fuse_optimizer(o).shard_master_weights(True)
+        return m, o, e
+
+    def steps_of(e, o, n):
+        for _ in range(n):
+            o.zero_grad()
+            with fb.autocast():
+                loss = fb.nn.cross_entropy(e(xw), yw)
+            loss.backward()
+            o.step()
+
+    m1, o1, e1 = build_engine(21)
+    steps_of(e1, o1, 3)
+    ck = os.path.join(out_dir, f"ck{rank}.ferrum")
+    fb.serialize.save_checkpoint(ck, model=e1, optimizer=o1)
+    steps_of(e1, o1, 2)
+    m2, o2, e2 = build_engine(22)
+    steps_of(e2, o2, 1)
+    fb.serialize.load_checkpoint(ck, model=e2, optimizer=o2, device=fb.Device.Cuda(dev.index))
+    check(f"resumed step count {o2.step_count}", o2.step_count == 3)
+    steps_of(e2, o2, 2)
+    e1.sync_master_weights()
+    e2.sync_master_weights()
+    torch.cuda.synchronize()
+    err = max((a - b).abs().max().item() for a, b in zip(m1.torch_parameters(), m2.torch_parameters()))
+    check(f"resumed sharded engine equals the uninterrupted run (max err {err:.2e})", err < 1e-6)
+    e1.shutdown()
+    e2.shutdown()
+
     fb.utils.runtime.check_status()
     d.destroy_process_group()
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:

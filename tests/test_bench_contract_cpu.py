@@ -18,6 +18,13 @@ def test_reference_arm_prints_one_json_line():
     assert rec["impl"] == "reference" and isinstance(rec.get("unavailable"), str) and rec["unavailable"]
 
 
+def test_reference_arm_prints_only_on_rank_zero():
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
+                       capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 0 and r.stdout.strip() == ""
+
+
 def test_flags_and_defaults():
     sys.path.insert(0, ROOT)
     try:
@@ -33,5 +40,6 @@ def test_flags_and_defaults():
                     "--no-e2e"]
         a = bench.parse()
         assert (a.gpus, a.steps, a.warmup) == (8, 5, 4) and a.no_graph and a.no_shard_master and a.no_e2e
+        assert not a.no_baseline and a.dataset_batches >= 2 and a.loader_workers >= 1
     finally:
         sys.argv = argv

@@ -68,6 +68,54 @@ def test_dataloader_batches_drop_last_shuffle():
     assert list(col) == [5, 5]
 
 
+def test_dataloader_native_worker_path_matches_the_plain_path():
+    """Stacked host tensors + ``num_workers > 0``: rows are gathered by the host library's worker threads into a
+    ring of staging slots.  Same batches as the single-threaded path for the same seed, ragged last batch,
+    ``repeat`` across epochs, an abandoned iteration, and a sampler that hands out a bad index."""
+    import numpy as np
+
+    from ferrum_b200.data import Sampler
+
+    x = torch.arange(1003 * 5, dtype=torch.float32).view(1003, 5)
+    y = torch.arange(1003) * 3
+    ds = data.TensorDataset.from_tensors(x, y)
+    plain = [(a._t.clone(), b._t.clone()) for a, b in data.DataLoader(ds).batch_size(64).shuffle(True).seed(5)]
+    native = data.DataLoader(ds).batch_size(64).shuffle(True).seed(5).num_workers(3)
+    got = [(a._t, b._t) for a, b in native]
+    assert len(got) == len(plain) == 16 and got[-1][0].shape[0] == 1003 - 15 * 64
+    for (a, b), (c, d) in zip(got, plain):
+        assert torch.equal(a, c) and torch.equal(b, d)
+    assert all(torch.equal(a[:, 0] / 5 * 3, b.float()) for a, b in got)
+    # second epoch of the same loader reshuffles; repeat never stops and keeps rows intact
+    again = torch.cat([b._t for _, b in native])
+    assert sorted(again.tolist()) == (torch.arange(1003) * 3).tolist() and not torch.equal(again, torch.cat(
+        [b for _, b in got]))
+    native.repeat(True).drop_last(True)
+    it = iter(native)
+    rows = 0
+    for _ in range(50):
+        a, b = next(it)
+        assert a._t.shape == (64, 5) and torch.equal(a._t[:, 0] / 5 * 3, b._t.float())
+        rows += 64
+    del it                      # abandoned with slots in flight
+    assert rows == 3200
+    native.repeat(False)
+    assert sum(b._t.numel() for _, b in native) == 15 * 64
+    it = iter(native)
+    next(it)
+    native.close()              # closed under a live iterator: the iterator must not touch the freed workers
+    del it
+
+    class Bad(Sampler):
+        def __init__(self):
+            super().__init__(np.array([0, 1, 5000, 2], dtype=np.int64))
+
+    bad = data.DataLoader(ds).batch_size(2).sampler(Bad()).num_workers(2)
+    with pytest.raises(IndexError):
+        list(bad)
+    bad.close()
+
+
 def test_samplers():
     s = data.SequentialSampler(5)
     assert s.len() == 5 and list(s) == [0, 1, 2, 3, 4] and s.next_index() is None
@@ -203,6 +251,36 @@ def test_bad_files_raise(tmp_path):
         fb.load(tmp_path / "missing.ferrum")
     with pytest.raises(fb.SerializationError):
         fb.save({"c": torch.zeros(2, dtype=torch.complex64)}, tmp_path / "c.ferrum")
+
+
+def test_corrupt_lengths_in_the_header_are_rejected_not_followed(tmp_path):
+    """Lengths an attacker controls (name length, entry count, offset, size) near 2^64 must not wrap the bounds
+    checks: every such file is refused with an error, nothing is read outside the data section."""
+    def entry(name_len, name, dims, dtype, off, size):
+        b = struct.pack("<Q", name_len) + name
+        b += struct.pack("<Q", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
+        return b + struct.pack("<IQQ", dtype, off, size)
+
+    def file(header, body=b"\0" * 24):
+        return b"FERRUM01" + struct.pack("<Q", len(header)) + header + body
+
+    big = (1 << 64) - 1
+    cases = {
+        "name length wraps pos + len": struct.pack("<IQQQ", 1, 1, 24, 1) + entry(big - 7, b"w", [2], 0, 0, 8),
+        "entry count far beyond the header": struct.pack("<IQQQ", 1, 1, 24, big // 2) + entry(1, b"w", [2], 0, 0, 8),
+        "offset + size wraps": struct.pack("<IQQQ", 1, 1, 24, 1) + entry(1, b"w", [2], 0, big - 3, 8),
+        "size beyond the data section": struct.pack("<IQQQ", 1, 1, 24, 1) + entry(1, b"w", [2], 0, 0, 1 << 40),
+        "data size wraps data_start + size": struct.pack("<IQQQ", 1, 1, big - 8, 1) + entry(1, b"w", [2], 0, 0, 8),
+    }
+    p = tmp_path / "evil.ferrum"
+    for what, header in cases.items():
+        p.write_bytes(file(header))
+        with pytest.raises(fb.SerializationError):
+            fb.load(p)
+    # header length field itself larger than the file
+    p.write_bytes(b"FERRUM01" + struct.pack("<Q", big) + b"\0" * 64)
+    with pytest.raises(fb.SerializationError):
+        fb.load(p)
 
 
 def test_checkpoint_resume_continues_identically(tmp_path):

@@ -372,6 +372,150 @@ def test_single_rank_engine_overlaps_optimizer_and_matches_plain_training():
         eng.shutdown()
 
 
+def _two_branch_model(dev):
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    class TwoBranch(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(32, 48, device=dev)
+            self.b = nn.Linear(32, 48, device=dev)
+            self.head = nn.Linear(48, 6, device=dev)
+
+        def forward(self, x, use_b=True):
+            h = self.a(x)
+            if use_b:
+                h = h + self.b(x)
+            return self.head(h)
+
+    return TwoBranch()
+
+
+def test_engine_weight_without_gradient_takes_a_zero_gradient():
+    """A Linear weight whose GEMM did not run in a step must not be updated with the previous step's gradient
+    (its arena slot is overwritten by the GEMM, never zeroed): with plain SGD it stays exactly where it was, and
+    with Adam the trajectory equals an unfused run in which the skipped weight is given an explicit zero gradient."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+    from ferrum_b200.parallel import Backend, DistributedDataParallel, ProcessGroup
+
+    dev = fb.Device.Cuda(0)
+    x = torch.randn(64, 32, device="cuda")
+    y = torch.randint(0, 6, (64,), device="cuda")
+    for kind in ("sgd", "adam"):
+        torch.manual_seed(3)
+        ref = _two_branch_model(dev)
+        model = copy.deepcopy(ref)
+        mk = (lambda ps: optim.SGD(ps, optim.SGDConfig(lr=0.1))) if kind == "sgd" else (
+            lambda ps: optim.Adam(ps, optim.AdamConfig(lr=1e-2)))
+        opt, ropt = mk(model.parameters()), mk(ref.parameters())
+        eng = DistributedDataParallel(model, ProcessGroup(Backend.Nvlink, 0, 1)).bucket_size_mb(0.002)
+        eng.fuse_optimizer(opt)
+        for step in range(4):
+            use_b = step % 2 == 0
+            before = model.b.weight.detach().clone()
+            opt.zero_grad()
+            nn.cross_entropy(eng(x, use_b=use_b), y).backward()
+            opt.step()
+            ropt.zero_grad(set_to_none=False)
+            nn.cross_entropy(ref(x, use_b=use_b), y).backward()
+            for p in ref.torch_parameters():
+                if p.grad is None:
+                    p.grad = torch.zeros_like(p)
+            ropt.step()
+            torch.cuda.synchronize()
+            if kind == "sgd" and not use_b:
+                assert torch.equal(model.b.weight.detach(), before)
+        for a, b in zip(model.torch_parameters(), ref.torch_parameters()):
+            assert torch.allclose(a, b, atol=1e-5, rtol=1e-4), (kind, (a - b).abs().max().item())
+        eng.shutdown()
+
+
+@pytest.mark.parametrize("capturable", [False, True])
+def test_engine_checkpoint_resume_matches_uninterrupted_run(tmp_path, capturable):
+    """save_checkpoint with a fused engine stores the moments that live in the engine's shards; a fresh model +
+    engine that loads the file continues exactly like the run that was never interrupted (also with the step
+    factors kept in device memory)."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim, serialize
+    from ferrum_b200.parallel import Backend, DistributedDataParallel, ProcessGroup
+
+    dev = fb.Device.Cuda(0)
+    x = torch.randn(64, 32, device="cuda")
+    y = torch.randint(0, 6, (64,), device="cuda")
+
+    def build(seed):
+        torch.manual_seed(seed)
+        m = nn.Sequential(nn.Linear(32, 64, device=dev), nn.GELU(), nn.LayerNorm([64], device=dev),
+                          nn.Linear(64, 6, device=dev))
+        o = optim.Adam(m.parameters(), optim.AdamConfig(lr=1e-2, weight_decay=0.01))
+        e = DistributedDataParallel(m, ProcessGroup(Backend.Nvlink, 0, 1)).bucket_size_mb(0.004)
+        e.fuse_optimizer(o)
+        if capturable:
+            e.capturable(True)
+        return m, o, e
+
+    def steps(e, o, n):
+        for _ in range(n):
+            o.zero_grad()
+            nn.cross_entropy(e(x), y).backward()
+            o.step()
+
+    m1, o1, e1 = build(1)
+    steps(e1, o1, 3)
+    path = tmp_path / "ck.ferrum"
+    serialize.save_checkpoint(path, model=m1, optimizer=o1)
+    saved = serialize.load(path)
+    assert any(k.startswith("optim.m.") for k in saved) and int(saved["optim.step"].item()) == 3
+    assert sum(saved[k]._t.abs().sum().item() for k in saved if k.startswith("optim.v.")) > 0
+    steps(e1, o1, 2)
+    m2, o2, e2 = build(99)               # different init: everything must come from the file
+    steps(e2, o2, 1)                     # its own state exists and gets replaced
+    serialize.load_checkpoint(path, model=m2, optimizer=o2, device=dev)
+    assert o2.step_count == 3
+    steps(e2, o2, 2)
+    torch.cuda.synchronize()
+    for a, b in zip(m1.torch_parameters(), m2.torch_parameters()):
+        assert torch.allclose(a, b, atol=1e-6, rtol=1e-5), (a - b).abs().max().item()
+    e1.shutdown()
+    e2.shutdown()
+
+
+def test_into_inner_hands_back_a_module_that_trains_without_the_engine():
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn, optim
+    from ferrum_b200.parallel import Backend, DistributedDataParallel, ProcessGroup
+
+    dev = fb.Device.Cuda(0)
+    torch.manual_seed(4)
+    model = nn.Sequential(nn.Linear(32, 64, device=dev), nn.ReLU(), nn.Linear(64, 6, device=dev))
+    opt = optim.Adam(model.parameters(), optim.AdamConfig(lr=1e-2))
+    eng = DistributedDataParallel(model, ProcessGroup(Backend.Nvlink, 0, 1)).bucket_size_mb(0.004)
+    eng.fuse_optimizer(opt)
+    x = torch.randn(64, 32, device="cuda")
+    y = torch.randint(0, 6, (64,), device="cuda")
+    for _ in range(2):
+        opt.zero_grad()
+        nn.cross_entropy(eng(x), y).backward()
+        opt.step()
+    inner = eng.into_inner()
+    assert inner is model and opt._engine is None
+    assert all(getattr(m, "grad_sink", None) is None for m in model.modules())
+    assert opt.m[0] is not None and opt.m[0].abs().sum().item() > 0     # the moments moved back to the optimizer
+    l0 = nn.cross_entropy(inner(x), y).item()
+    for _ in range(5):
+        opt.zero_grad()
+        loss = nn.cross_entropy(inner(x), y)
+        loss.backward()
+        opt.step()
+    assert opt.step_count == 7 and loss.item() < l0
+
+
 def test_guard_bands_around_the_engine_arena_detect_a_stray_write(monkeypatch):
     """FERRUM_GUARD_BANDS=1: pattern-filled bands around the parameter / gradient / bf16 regions stay intact over
     training steps, and a write into one of them (made from the host side here) is reported with its position."""

@@ -20,7 +20,7 @@ def _port():
 
 @pytest.mark.timeout(600)
 def test_native_collectives_and_fused_ddp(tmp_path):
-    n = min(torch.cuda.device_count(), 4)
+    n = min(torch.cuda.device_count(), 8)
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_mgpu_worker.py")
     env = dict(os.environ, FERRUM_DEVICE_WAIT_S="20")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",

@@ -65,3 +65,23 @@ def test_push_destination_and_owner_reads_agree():
         o = e // per
         assert sorted(push_destination(e, s, per)[1] for s in range(world)) == owner_reads(e, world, per)
         assert all(push_destination(e, s, per)[0] == o for s in range(world))
+
+
+def test_host_epoch_counter_wraps_with_the_device_modulus():
+    """``SymmetricArena.next_epoch`` advances modulo 2^32, like the device-side counter and the kernels' wrap-safe
+    comparison: through the wrap every entry epoch is 'not reached' by the previous exit flag and 'reached' by
+    its own, which a 31-bit host counter broke (a stale flag satisfied the first collective after the wrap)."""
+    from ferrum_b200.parallel.protocol_model import _reached
+    from ferrum_b200.parallel.symm import SymmetricArena
+
+    arena = SymmetricArena.__new__(SymmetricArena)
+    arena._epochs = {2: 0xFFFFFFF9}
+    flag = (0xFFFFFFF9 - 1) & 0xFFFFFFFF          # exit epoch of the collective before
+    for _ in range(8):
+        e = arena.next_epoch(2)
+        assert 0 <= e <= 0xFFFFFFFF and e % 2 == 1
+        assert not _reached(flag, e, True)        # nobody has arrived yet: the old flag must not pass
+        assert _reached(e, e, True)
+        flag = (e + 1) & 0xFFFFFFFF               # what the exit handshake leaves behind
+        assert _reached(flag, (e + 1) & 0xFFFFFFFF, True)
+    assert arena._epochs[2] == 0xFFFFFFF9 + 16 - (1 << 32)
