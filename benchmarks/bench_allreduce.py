@@ -75,6 +75,7 @@ def main():
     ap.add_argument("--blocks", type=int, default=128)
     ap.add_argument("--threads", type=int, default=256)
     ap.add_argument("--shard-master", action="store_true", help="publish only the bf16 copy to peers")
+    ap.add_argument("--sizes-mb", default="", help="comma-separated bucket sizes in MB instead of the 4 KB .. max sweep")
     ap.add_argument("--out", default="")
     ap.add_argument("--emulated", type=int, default=0, metavar="W",
                     help="one process, one GPU: W ranks emulated by one cooperative launch of the same device code "
@@ -116,6 +117,8 @@ def main():
         nb *= 4
     if sizes[-1] != int(args.max_mb * (1 << 20)):
         sizes.append(int(args.max_mb * (1 << 20)))
+    if args.sizes_mb:
+        sizes = [int(float(x) * (1 << 20)) for x in args.sizes_mb.split(",")]
     results = []
 
     def timed(fn, iters):

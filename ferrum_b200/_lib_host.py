@@ -29,6 +29,7 @@ SIGS = {
     "fb_loader_destroy": (None, [P]),
     # bucket planner
     "fb_plan_buckets": (LL, [I, PLL, LL, LL, LL, PLL, PI, PLL, PLL, PI]),
+    "fb_plan_buckets_kinds": (LL, [I, PLL, PI, LL, LL, LL, PLL, PI, PLL, PLL, PI]),
     "fb_plan_shard": (None, [LL, I, I, PLL, PLL]),
     # CPU reference loops
     "fb_ref_matmul": (None, [P, P, P, I, I, I]),

@@ -678,6 +678,25 @@ class Tensor:
     def to_vec(self):
         return self._t.detach().reshape(-1).tolist()
 
+    # raw access in the vocabulary of the reference's GPU tensor (ferrum-cuda/src/tensor.rs:120-159)
+    def ptr(self) -> int:
+        """Address of the first element (device address for a tensor on ``Device.Cuda``)."""
+        return self._t.data_ptr()
+
+    def size_bytes(self) -> int:
+        return self._t.numel() * self._t.element_size()
+
+    def to_host(self) -> bytes:
+        """The elements, in logical order, as raw bytes in host memory."""
+        return self._t.detach().contiguous().cpu().reshape(-1).view(torch.uint8).numpy().tobytes()
+
+    def to_f32(self) -> list:
+        """The elements converted to fp32, as a host list."""
+        return self._t.detach().to(torch.float32).reshape(-1).tolist()
+
+    def to_f64(self) -> list:
+        return self._t.detach().to(torch.float64).reshape(-1).tolist()
+
     tolist = to_vec
 
     def numpy(self):
@@ -890,6 +909,13 @@ class Tensor:
 
     def max_dim(self, dim: int, keepdim: bool = False):
         return self._red("max", dim, keepdim)
+
+    # names of the reference's GPU tensor (ferrum-cuda/src/tensor.rs:266-279): reduce one axis away
+    def sum_axis(self, axis: int):
+        return self._red("sum", axis, False)
+
+    def mean_axis(self, axis: int):
+        return self._red("mean", axis, False)
 
     def min_dim(self, dim: int, keepdim: bool = False):
         return self._red("min", dim, keepdim)

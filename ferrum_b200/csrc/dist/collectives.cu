@@ -38,39 +38,10 @@
 #include "../common/status.h"
 #include "../include/ferrum_kernels.h"
 #include "dist_ctx.h"
+#include "dist_device.cuh"
 
 namespace fb {
 namespace {
-
-__device__ __forceinline__ uint32_t* flag_slot(unsigned char* arena, int channel, int block, int src) {
-  return reinterpret_cast<uint32_t*>(arena) + ((channel * FB_FLAG_BLOCKS + block) * FB_MAX_RANKS + src);
-}
-
-// Called by every thread of the block.  Returns false (for the whole block) if a wait gave up.
-__device__ bool block_handshake(const fb_dist_ctx& c, int channel, int vblock, uint32_t epoch, int* s_fail,
-                                int site) {
-  __syncthreads();
-  if (threadIdx.x < c.world) {
-    const int peer = threadIdx.x;
-    __threadfence_system();
-    ptx::st_release_sys(flag_slot(c.arena[peer], channel, vblock, c.rank), epoch);
-    const uint32_t* mine = flag_slot(c.arena[c.rank], channel, vblock, peer);
-    const uint64_t t0 = ptx::globaltimer();
-    uint32_t it = 0;
-    while (static_cast<int32_t>(ptx::ld_acquire_sys(mine) - epoch) < 0) {
-      if (((++it) & 31u) == 0u) {
-        if (*reinterpret_cast<volatile int*>(s_fail)) break;
-        if (ptx::globaltimer() - t0 > c.timeout_ns) {
-          report_status(c.status, kStatusPeerTimeout, site, peer, static_cast<int32_t>(epoch));
-          *reinterpret_cast<volatile int*>(s_fail) = 1;
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  return *reinterpret_cast<volatile int*>(s_fail) == 0;
-}
 
 struct ArArgs {
   int channel;
@@ -113,24 +84,6 @@ __device__ __forceinline__ float4 combine4(float4 a, float4 b, int op) {
     case FB_OP_MAX: return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w));
     default: return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
   }
-}
-
-__device__ __forceinline__ void adam1(float& p, float g, float& m, float& v, const fb_adam_hparams& h) {
-  g *= h.grad_scale;
-  if (h.weight_decay != 0.f) p -= h.lr * h.weight_decay * p;
-  m = h.beta1 * m + (1.f - h.beta1) * g;
-  v = h.beta2 * v + (1.f - h.beta2) * g * g;
-  p -= h.lr * (m / h.bias_corr1) / (sqrtf(v / h.bias_corr2) + h.eps);
-}
-__device__ __forceinline__ void sgd1(float& p, float g, float& vel, const fb_sgd_hparams& h) {
-  g *= h.grad_scale;
-  if (h.weight_decay != 0.f) g += h.weight_decay * p;
-  float upd = g;
-  if (h.momentum != 0.f) {
-    vel = h.first_step ? g : h.momentum * vel + g;
-    upd = h.nesterov ? g + h.momentum * vel : vel;
-  }
-  p -= h.lr * upd;
 }
 
 // Copies between a local tensor and this rank's arena region for the positions block `vblock` owns in EVERY
@@ -608,10 +561,6 @@ __global__ void barrier_kernel(const fb_dist_ctx c, int channel, uint32_t epoch)
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
   block_handshake(c, channel, 0, epoch, &s_fail, 300);
-}
-
-bool ctx_ok(const fb_dist_ctx* c) {
-  return c != nullptr && c->world >= 1 && c->world <= FB_MAX_RANKS && c->rank >= 0 && c->rank < c->world;
 }
 
 __global__ void epoch_advance_kernel(unsigned* ctr, unsigned inc) {

@@ -8,9 +8,14 @@ collectives; its 25 MB ``bucket_size_mb`` and ``GradientBucket`` are never used.
 * during ``backward`` each Linear's weight-gradient GEMM writes straight into its arena slot; when the last
   gradient of a bucket is enqueued, the bucket's reduction kernel is launched on a separate high-priority
   stream, so the reduction of layer *l* overlaps the backward GEMMs of layer *l-1*;
-* with ``fuse_optimizer(opt)`` that kernel is the fused all-reduce + 1/world + SGD-momentum / Adam update +
-  parameter publish (``fb_dist_allreduce``): ``opt.step()`` then only joins the streams.  Optimizer moments are
-  kept only by the rank that owns a shard (1/world of the state per GPU);
+* with ``fuse_optimizer(opt)`` the reduction is split where the optimizer's memory traffic would otherwise land
+  on the backward GEMMs: per bucket a small reduce-scatter kernel (``fb_dist_reduce_scatter_shard``: each rank sums
+  its shard over the peers, 1/world folded in) runs beside the rest of backward, and after backward ONE kernel
+  (``fb_dist_shard_update``) applies SGD-momentum / Adam to the rank's shards and stores the new weights into
+  every rank's arena, i.e. the all-gather half of the all-reduce fused with the optimizer; ``opt.step()`` then only
+  joins the streams.  ``defer_update(False)`` selects the single-kernel form instead (all-reduce + update +
+  publish per bucket inside backward, ``fb_dist_allreduce``).  Optimizer moments are kept only by the rank that
+  owns a shard (1/world of the state per GPU);
 * without a fused optimizer the same kernel averages the gradients in place and ``opt.step()`` runs the usual
   multi-tensor update;
 * ``broadcast_parameters`` copies rank 0's arena to every rank with the pull-broadcast kernel.
@@ -88,15 +93,16 @@ class GradientHook:
         return all(b.is_ready() for b in self.buckets)
 
 
-def _plan(sizes, cap_elems: int, align: int, param_align: int):
+def _plan(sizes, cap_elems: int, align: int, param_align: int, kinds=None):
     n = len(sizes)
     LL, I = ctypes.c_longlong, ctypes.c_int
     szs = (LL * n)(*sizes)
     offs, bof = (LL * n)(), (I * n)()
     bstart, blen = (LL * max(n, 1))(), (LL * max(n, 1))()
     nb = I(0)
-    total = _lib.host().fb_plan_buckets(n, szs, cap_elems, align, param_align, offs, bof, bstart, blen,
-                                        ctypes.byref(nb))
+    kd = (I * n)(*kinds) if kinds is not None else None
+    total = _lib.host().fb_plan_buckets_kinds(n, szs, kd, cap_elems, align, param_align, offs, bof, bstart, blen,
+                                              ctypes.byref(nb))
     if total < 0:
         raise ValueError("bucket planning failed")
     return total, list(offs), list(bof), list(bstart)[:nb.value], list(blen)[:nb.value]
@@ -127,6 +133,16 @@ class DistributedDataParallel(Module, GradSink):
         env_blocks = os.environ.get("FERRUM_COMM_BLOCKS")
         self._comm_blocks = int(env_blocks) if env_blocks else (128 if self._pg.world_size() <= 2 else 48)
         self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
+        # Deferred update (default): reduce-scatter per bucket inside backward, one optimizer + publish kernel after
+        # it.  Measured at 2 GPUs on the 8 x 4096 MLP: the single-kernel form keeps 128 blocks of 200+ registers
+        # busy for 230 us per 64 MB bucket; they do not fit beside a persistent GEMM CTA and stream half of the
+        # optimizer state through the L2 the GEMMs live on (7.4 ms/step against 6.3 on one GPU).
+        self._defer = True
+        self._update_blocks = 296     # blocks of the update kernel: two per SM, it runs alone
+        self._dev_epoch_up = None
+        self._table = None
+        self._prof = None             # per-step timing events of the bucket kernels (comm_profile)
+        self._prof_last = None
         if optimizer is not None:
             self.fuse_optimizer(optimizer)
 
@@ -168,6 +184,13 @@ class DistributedDataParallel(Module, GradSink):
         accessors of this wrapper); use it only together with ``autocast``.
         """
         self._shard_master = bool(flag)
+        self._table = None  # the per-bucket publish flags follow
+        return self
+
+    def defer_update(self, flag: bool = True) -> "DistributedDataParallel":
+        """``True`` (default): reduce-scatter per bucket during backward, one optimizer + publish kernel after it.
+        ``False``: all-reduce, optimizer and publish in one kernel per bucket, inside backward."""
+        self._defer = bool(flag)
         return self
 
     def push_gradients(self, flag: bool = True) -> "DistributedDataParallel":
@@ -179,6 +202,44 @@ class DistributedDataParallel(Module, GradSink):
         available; a weight used twice in one step is not supported.  Off by default (``FERRUM_GEMM_PUSH=1``)."""
         self._push = bool(flag)
         return self
+
+    def comm_profile(self, flag: bool = True) -> "DistributedDataParallel":
+        """Time every bucket kernel with CUDA events (eager steps only, not while a step is recorded in or
+        replayed from a CUDA graph): when its last gradient was enqueued, when the kernel started and ended on the
+        communication stream, and when the backward pass itself ended.  ``last_comm_profile()`` returns the
+        record of the most recent finished step."""
+        self._prof = {} if flag else None
+        return self
+
+    def last_comm_profile(self) -> dict | None:
+        """``{"buckets": [{index, bytes, ready_ms, start_ms, end_ms, kernel_us, bus_gbs}], "backward_end_ms",
+        "step_end_ms", "exposed_tail_us", "comm_busy_us"}``: times relative to the step's ``zero_grad``;
+        ``bus_gbs`` = bytes x 2 (world - 1) / world / kernel time, the usual all-reduce bus bandwidth;
+        ``exposed_tail_us`` = how long after the last backward kernel the last bucket kernel ended."""
+        rec = self._prof_last
+        if rec is None:
+            return None
+        rec["done"].synchronize()
+        t0 = rec["t0"]
+        world = self._pg.world_size()
+        out = {"buckets": []}
+        busy = 0.0
+        # bytes x (world - 1) / world cross the link per half of an all-reduce; the single-kernel form does both
+        halves = 1.0 if (self._defer and self._opt is not None and not self._push) else 2.0
+        for b, (ready, start, end, nbytes) in sorted(rec["buckets"].items(), key=lambda kv: t0.elapsed_time(kv[1][1])):
+            us = start.elapsed_time(end) * 1e3
+            busy += us
+            out["buckets"].append({"index": b, "bytes": nbytes, "ready_ms": t0.elapsed_time(ready),
+                                   "start_ms": t0.elapsed_time(start), "end_ms": t0.elapsed_time(end),
+                                   "kernel_us": us,
+                                   "bus_gbs": (nbytes * halves * (world - 1) / world / (us * 1e-6) / 1e9) if us > 0
+                                   else 0.0})
+        out["backward_end_ms"] = t0.elapsed_time(rec["bwd_end"])
+        out["step_end_ms"] = t0.elapsed_time(rec["done"])
+        last_end = max((x["end_ms"] for x in out["buckets"]), default=out["backward_end_ms"])
+        out["exposed_tail_us"] = max(0.0, (last_end - out["backward_end_ms"]) * 1e3)
+        out["comm_busy_us"] = busy
+        return out
 
     def try_push(self, param, a: torch.Tensor, b: torch.Tensor) -> bool:
         """GradSink extension used by the Linear backward: run ``dW = a @ b^T`` with the pushing epilogue if this
@@ -271,16 +332,29 @@ class DistributedDataParallel(Module, GradSink):
         world, rank = self._pg.world_size(), self._pg.rank()
         cap = max(1, int(self._bucket_mb * (1 << 20)) // 4)
         sizes = [p.numel() for p in self._params]
-        total, offs, bof, bstart, blen = _plan(sizes, cap, 4 * world, 32)
+        self._index = {id(p): i for i, p in enumerate(self._params)}
+        # Linear / Embedding weights: their gradients are written into the arena by the producing kernel (a "sink").
+        # Under bf16 autocast forward and backward read Linear weights through their bf16 copies; everything else
+        # (biases, normalisation scales and shifts, embedding tables) is read in fp32.  A bucket holds one kind.
+        self._use_native = self._native()
+        sink_ids, sink_mods, bf16_ids = set(), [], set()
+        for mod in self.inner.modules():
+            if (type(mod) is Linear or isinstance(mod, Embedding)) and id(mod.weight) in self._index:
+                sink_ids.add(id(mod.weight))
+                sink_mods.append(mod)
+                if type(mod) is Linear:  # an embedding table is gathered from its fp32 values
+                    bf16_ids.add(id(mod.weight))
+        kinds = [1 if id(p) in bf16_ids else 0 for p in self._params]
+        total, offs, bof, bstart, blen = _plan(sizes, cap, 4 * world, 32, kinds)
         self._total, self._offs, self._bucket_of = total, offs, bof
         self.buckets = [GradientBucket(i, bstart[i], blen[i]) for i in range(len(bstart))]
         for i, b in enumerate(bof):
             self.buckets[b].param_indices.append(i)
             self.buckets[b].sizes.append(sizes[i])
-        self._index = {id(p): i for i, p in enumerate(self._params)}
+        # fp32 values of a bucket go to the peers unless every parameter in it is consumed through its bf16 copy
+        self._bucket_bf16_only = [all(kinds[i] == 1 for i in bk.param_indices) for bk in self.buckets]
         self._written = [False] * len(self._params)
         self._launched = [False] * len(self.buckets)
-        self._use_native = self._native()
         dev = self._params[0].device if self._params else torch.device("cpu")
         if self._use_native:
             self._build_native(total, dev)
@@ -291,15 +365,13 @@ class DistributedDataParallel(Module, GradSink):
         # sinks and hooks
         self._small_runs = []  # (start, length) runs of non-GEMM gradients, zeroed every step
         self._hook_handles, self._sink_modules = [], []
-        sink_ids = set()
-        for mod in self.inner.modules():
-            if ((type(mod) is Linear or isinstance(mod, Embedding)) and id(mod.weight) in self._index
-                    and self._use_native):
-                # through __dict__: a plain attribute assignment would register the engine as a SUBMODULE of the
-                # layer and close a cycle (engine -> inner -> layer -> engine) under state_dict() / apply()
-                mod.__dict__["grad_sink"] = self
-                self._sink_modules.append(mod)
-                sink_ids.add(id(mod.weight))
+        if not self._use_native:
+            sink_ids = set()  # gradients arrive through autograd hooks
+        for mod in sink_mods if self._use_native else []:
+            # through __dict__: a plain attribute assignment would register the engine as a SUBMODULE of the
+            # layer and close a cycle (engine -> inner -> layer -> engine) under state_dict() / apply()
+            mod.__dict__["grad_sink"] = self
+            self._sink_modules.append(mod)
         run = None
         order = sorted(range(len(self._params)), key=lambda i: offs[i])
         for i in order:
@@ -409,6 +481,7 @@ class DistributedDataParallel(Module, GradSink):
         self._pushed = [[] for _ in self.buckets]
         self._pushed_params = set()
         self._advanced = False
+        self._deferred = False
         self._sync_enabled = True
         for b in self.buckets:
             b.ready = False
@@ -435,6 +508,16 @@ class DistributedDataParallel(Module, GradSink):
                 self._flat_grads[o:o + self._params[i].numel()].zero_()
         self._ready_event.record(cur)
         self._comm_stream.wait_event(self._ready_event)
+        prof = self._prof if (self._prof is not None and not torch.cuda.is_current_stream_capturing()) else None
+        if prof is not None:
+            if "t0" not in prof:  # no zero_grad() seen: the step starts here
+                prof["t0"] = torch.cuda.Event(enable_timing=True)
+                prof["t0"].record(cur)
+                prof["buckets"] = {}
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record(cur)
+            ev[1].record(self._comm_stream)
+            prof["buckets"][b] = (ev[0], ev[1], ev[2], bk.length * 4)
         opt = self._opt
         fuse, adam_h, sgd_h, m_ptr, v_ptr = 0, None, None, None, None
         per = ((bk.length + world - 1) // world + 3) // 4 * 4
@@ -458,6 +541,24 @@ class DistributedDataParallel(Module, GradSink):
                 raise CommunicationError(f"cannot fuse optimizer of type {type(opt).__name__}")
         e = a.next_epoch(2)
         use_mc = 1 if a.has_multicast() else 0
+        if fuse and self._defer and not self._push:
+            # reduce-scatter only; the update of all shards follows in _flush
+            dev_e = None
+            if self._capturable:
+                if self._dev_epoch is None:
+                    self._dev_epoch = torch.tensor([e - (1 << 32) if e >= (1 << 31) else e], dtype=torch.int32,
+                                                   device=self._flat_params.device)
+                dev_e = self._dev_epoch.data_ptr()
+            rc = 0
+            if world > 1:
+                rc = lib.fb_dist_reduce_scatter_shard(a.ctx, use_mc, 2, e, dev_e, self._off_grad + bk.start * 4,
+                                                      bk.length, 1.0 / world, self._comm_blocks, self._comm_threads,
+                                                      self._comm_stream.cuda_stream)
+            if prof is not None:
+                prof["buckets"][b][2].record(self._comm_stream)
+            _lib.check(rc, "fb_dist_reduce_scatter_shard")
+            self._deferred = True
+            return
         if self._pushed[b]:  # consumed by the launch below: these ranges are already complete in local memory
             rng = self._pushed[b]
             LLn = ctypes.c_longlong * len(rng)
@@ -476,18 +577,67 @@ class DistributedDataParallel(Module, GradSink):
             rc = lib.fb_dist_allreduce_dyn(a.ctx, fuse, use_mc, 2, self._dev_epoch.data_ptr(),
                                            self._off_grad + bk.start * 4, self._off_param + bk.start * 4,
                                            self._off_shadow + bk.start * 2, bk.length, 4, 1.0 / world, adam_h, sgd_h,
-                                           m_ptr, v_ptr, 0 if (self._shard_master and fuse) else 1,
+                                           m_ptr, v_ptr, 0 if (self._shard_master and fuse and self._bucket_bf16_only[b]) else 1,
                                            self._comm_blocks, self._comm_threads, dyn.data_ptr(),
                                            self._comm_stream.cuda_stream)
         else:
             rc = lib.fb_dist_allreduce(a.ctx, fuse, use_mc, 2, e, self._off_grad + bk.start * 4,
                                        self._off_param + bk.start * 4, self._off_shadow + bk.start * 2, bk.length,
                                        4, 1.0 / world, adam_h, sgd_h, m_ptr, v_ptr,
-                                       0 if (self._shard_master and fuse) else 1, self._comm_blocks,
+                                       0 if (self._shard_master and fuse and self._bucket_bf16_only[b]) else 1, self._comm_blocks,
                                        self._comm_threads, self._comm_stream.cuda_stream)
         if self._shard_master and fuse:
             self._master_stale = True
+        if prof is not None:
+            prof["buckets"][b][2].record(self._comm_stream)
         _lib.check(rc, "fb_dist_allreduce")
+
+    def _launch_update(self, prof) -> None:
+        """Optimizer update of this rank's shards of every bucket + publication of the new weights, one kernel on
+        the communication stream behind everything the backward pass enqueued."""
+        from ..optim.optimizers import Adam
+
+        self._deferred = False
+        lib, a, opt = _lib.cuda(), self._arena, self._opt
+        world = self._pg.world_size()
+        cur = torch.cuda.current_stream()
+        self._ready_event.record(cur)              # the new weights must not land under a GEMM that still reads them
+        self._comm_stream.wait_event(self._ready_event)
+        self._ensure_state()
+        if self._table is None:
+            rows = [[bk.start, bk.length, self._state_off[i],
+                     0 if (self._shard_master and self._bucket_bf16_only[i]) else 1]
+                    for i, bk in enumerate(self.buckets)]
+            self._table = torch.tensor(rows, dtype=torch.int64, device=self._flat_params.device)
+        adam = isinstance(opt, Adam)
+        adam_h = ctypes.pointer(opt.hparams(opt.step_count + 1, 1.0)) if adam else None
+        sgd_h = None if adam else ctypes.pointer(opt.hparams(1.0))
+        m_ptr = self._state_m.data_ptr() if (adam or opt.config.momentum != 0.0) else None
+        v_ptr = self._state_v.data_ptr() if adam else None
+        e = a.next_epoch(4)
+        dev_e = dyn = None
+        st = self._comm_stream.cuda_stream
+        if self._capturable:
+            if self._dev_epoch_up is None:
+                self._dev_epoch_up = torch.tensor([e], dtype=torch.int32, device=self._flat_params.device)
+            dev_e = self._dev_epoch_up.data_ptr()
+            dyn = opt._dyn.data_ptr()
+            if adam:
+                _lib.check(lib.fb_optim_advance(dyn, opt.config.beta1, opt.config.beta2, st), "fb_optim_advance")
+        ev = None
+        if prof is not None and "buckets" in prof:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record(cur)
+            ev[1].record(self._comm_stream)
+        rc = lib.fb_dist_shard_update(a.ctx, 2 if adam else 1, 1 if a.has_multicast() else 0, 4, e, dev_e,
+                                      self._off_grad, self._off_param, self._off_shadow, self._table.data_ptr(),
+                                      len(self.buckets), adam_h, sgd_h, m_ptr, v_ptr, self._update_blocks, 256, dyn, st)
+        if ev is not None:
+            ev[2].record(self._comm_stream)
+            prof["buckets"]["update"] = (ev[0], ev[1], ev[2], self._total * 4)
+        if self._shard_master:
+            self._master_stale = True
+        _lib.check(rc, "fb_dist_shard_update")
 
     def _shard_len(self, bk) -> int:
         world = self._pg.world_size()
@@ -509,21 +659,37 @@ class DistributedDataParallel(Module, GradSink):
 
     def _flush(self) -> None:
         """Launch every bucket that has not been reduced in this step (unused parameters, explicit sync)."""
+        prof = self._prof if (self._prof is not None and self._use_native
+                              and not torch.cuda.is_current_stream_capturing()) else None
+        if prof is not None and "t0" in prof:
+            prof["bwd_end"] = torch.cuda.Event(enable_timing=True)
+            prof["bwd_end"].record(torch.cuda.current_stream())
         for b in range(len(self.buckets)):
             if not self._launched[b]:
                 self._launch_bucket(b)
+        if self._use_native and getattr(self, "_deferred", False):
+            self._launch_update(prof)
         if self._use_native:
             self._done_event.record(self._comm_stream)
             torch.cuda.current_stream().wait_event(self._done_event)
+        if prof is not None and "bwd_end" in prof and prof.get("buckets"):
+            prof["done"] = torch.cuda.Event(enable_timing=True)
+            prof["done"].record(torch.cuda.current_stream())
+            self._prof_last, self._prof = prof, {}
 
     # ------------------------------------------------------------------ step protocol
     def zero_grad(self) -> None:
         self._build()
+        if self._pg.world_size() > 1:
+            self._pg.check_peers(0.2)  # a rank that left between steps ends the step here, on the host
         for start, length in self._small_runs:
             self._flat_grads[start:start + length].zero_()
         if not self._use_native:
             self._flat_grads.zero_()
         self._reset_step_state()
+        if self._prof is not None and self._use_native and not torch.cuda.is_current_stream_capturing():
+            self._prof = {"t0": torch.cuda.Event(enable_timing=True), "buckets": {}}
+            self._prof["t0"].record(torch.cuda.current_stream())
 
     def finish_step(self, optimizer) -> None:
         """Called by ``optimizer.step()`` when the update is fused into the reduction."""

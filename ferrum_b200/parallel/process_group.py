@@ -50,6 +50,8 @@ class ProcessGroup:
         self._sync_arena: SymmetricArena | None = None
         self._chunk = int(float(os.environ.get("FERRUM_COMM_CHUNK_MB", "32")) * (1 << 20))
         self._seq = 0  # collective sequence number, identical on all ranks of a correct program
+        self._last_peer_check = 0.0
+        self._left = False
 
     # ------------------------------------------------------------------ accessors
     @classmethod
@@ -77,6 +79,70 @@ class ProcessGroup:
 
     def torch_group(self):
         return self._tg
+
+    # ------------------------------------------------------------------ liveness (error.rs:20-26, backend.rs:84-88)
+    # A rank that stops taking part between two steps says so in the rendezvous store before it goes
+    # (``leave()``); every collective of the others looks there first, so they fail with CommunicationError on
+    # the host instead of launching a kernel or a library call that would wait for the missing rank.  A rank
+    # that dies without a word is caught by the bounded waits: the process-group timeout on host collectives,
+    # the device-side wait limit on the NVLink kernels (Timeout).
+    _LEFT_KEY = "ferrum/left/"
+
+    def _store(self):
+        import torch.distributed as dist
+
+        if self._world == 1 or not dist.is_initialized():
+            return None
+        return dist.distributed_c10d._get_default_store()
+
+    def departed(self) -> list:
+        """Group ranks that announced their departure."""
+        st = self._store()
+        if st is None:
+            return []
+        return [r for r, g in enumerate(self._ranks) if g != self._ranks[self._rank] and st.check([f"{self._LEFT_KEY}{g}"])]
+
+    def check_peers(self, min_interval: float = 0.0) -> None:
+        """Raises ``CommunicationError`` if a rank of the group has left.  ``min_interval`` (seconds) skips the
+        look-up when the last one is younger (the per-step call of the data-parallel engine)."""
+        import time
+
+        now = time.monotonic()
+        if min_interval > 0.0 and now - self._last_peer_check < min_interval:
+            return
+        self._last_peer_check = now
+        gone = self.departed()
+        if gone:
+            raise CommunicationError(f"rank(s) {gone} left the job; destroy the process group and continue with "
+                                     f"the {self._world - len(gone)} remaining ranks from the last checkpoint")
+
+    def leave(self) -> None:
+        """Announce that this rank takes no further part (call it between steps, with no collective in flight),
+        then release this rank's arenas.  The other ranks learn of it at their next collective."""
+        st = self._store()
+        if st is not None and not self._left:
+            st.set(f"{self._LEFT_KEY}{self._ranks[self._rank]}", "1")
+        self._left = True
+        self.close()
+
+    def _begin(self) -> None:
+        """Start of every collective: count it, and do not start it if a peer is known to be gone."""
+        self._seq += 1
+        if self._world > 1:
+            # the look-up is a round trip to the store: always before a host collective (milliseconds anyway),
+            # at most five times a second in front of the NVLink kernels, whose waits are bounded on the device
+            self.check_peers(0.2 if self._backend is Backend.Nvlink else 0.0)
+
+    @staticmethod
+    def _host_call(what: str, fn, *args, **kw):
+        """A torch.distributed call with its failures mapped to this package's errors."""
+        try:
+            return fn(*args, **kw)
+        except RuntimeError as exc:  # includes DistBackendError / DistNetworkError
+            msg = str(exc)
+            if "imeout" in msg or "timed out" in msg:
+                raise Timeout(f"{what} ({msg.splitlines()[0]})") from None
+            raise CommunicationError(f"{what}: {msg.splitlines()[0] if msg else type(exc).__name__}") from None
 
     # ------------------------------------------------------------------ plumbing
     def exchange(self, obj) -> list:
@@ -118,7 +184,7 @@ class ProcessGroup:
     def all_reduce(self, tensor, op: ReduceOp = ReduceOp.Sum):
         """In-place reduction over all ranks; ``Average`` divides by the world size."""
         t = _unwrap(tensor)
-        self._seq += 1
+        self._begin()
         if self._world == 1:
             return tensor
         if self._native(t):
@@ -126,7 +192,7 @@ class ProcessGroup:
             return tensor
         import torch.distributed as dist
 
-        dist.all_reduce(t, op=_torch_op(op), group=self._tg)
+        self._host_call("all_reduce", dist.all_reduce, t, op=_torch_op(op), group=self._tg)
         if op is ReduceOp.Average:
             t.div_(self._world)
         return tensor
@@ -186,7 +252,7 @@ class ProcessGroup:
 
     def broadcast(self, tensor, root: int = 0):
         t = _unwrap(tensor)
-        self._seq += 1
+        self._begin()
         if not 0 <= root < self._world:
             raise InvalidRank(root, self._world)
         if self._world == 1:
@@ -202,12 +268,12 @@ class ProcessGroup:
             return tensor
         import torch.distributed as dist
 
-        dist.broadcast(t, src=self._ranks[root], group=self._tg)
+        self._host_call("broadcast", dist.broadcast, t, src=self._ranks[root], group=self._tg)
         return tensor
 
     def reduce(self, tensor, dst: int = 0, op: ReduceOp = ReduceOp.Sum):
         t = _unwrap(tensor)
-        self._seq += 1
+        self._begin()
         if not 0 <= dst < self._world:
             raise InvalidRank(dst, self._world)
         if self._world == 1:
@@ -220,7 +286,7 @@ class ProcessGroup:
             return tensor
         import torch.distributed as dist
 
-        dist.reduce(t, dst=self._ranks[dst], op=_torch_op(op), group=self._tg)
+        self._host_call("reduce", dist.reduce, t, dst=self._ranks[dst], op=_torch_op(op), group=self._tg)
         if op is ReduceOp.Average and self._rank == dst:
             t.div_(self._world)
         return tensor
@@ -242,7 +308,7 @@ class ProcessGroup:
         """``output[r]`` receives rank ``r``'s ``input``."""
         x = _unwrap(input)
         outs = [_unwrap(o) for o in output]
-        self._seq += 1
+        self._begin()
         if len(outs) != self._world:
             raise InvalidConfiguration(f"all_gather needs {self._world} output tensors, got {len(outs)}")
         if self._world == 1:
@@ -254,12 +320,12 @@ class ProcessGroup:
             return output
         import torch.distributed as dist
 
-        dist.all_gather(outs, x, group=self._tg)
+        self._host_call("all_gather", dist.all_gather, outs, x, group=self._tg)
         return output
 
     def gather(self, output, input, dst: int = 0):
         x = _unwrap(input)
-        self._seq += 1
+        self._begin()
         if not 0 <= dst < self._world:
             raise InvalidRank(dst, self._world)
         outs = [_unwrap(o) for o in output] if output is not None else None
@@ -274,7 +340,7 @@ class ProcessGroup:
             return output
         import torch.distributed as dist
 
-        dist.gather(x, outs if self._rank == dst else None, dst=self._ranks[dst], group=self._tg)
+        self._host_call("gather", dist.gather, x, outs if self._rank == dst else None, dst=self._ranks[dst], group=self._tg)
         return output
 
     def _scatter_like(self, mode: int, root: int, ins, o: torch.Tensor, nbytes: int, op: ReduceOp) -> None:
@@ -290,7 +356,7 @@ class ProcessGroup:
 
     def scatter(self, output, input, src: int = 0):
         o = _unwrap(output)
-        self._seq += 1
+        self._begin()
         if not 0 <= src < self._world:
             raise InvalidRank(src, self._world)
         ins = [_unwrap(i) for i in input] if input is not None else None
@@ -305,14 +371,14 @@ class ProcessGroup:
             return output
         import torch.distributed as dist
 
-        dist.scatter(o, ins if self._rank == src else None, src=self._ranks[src], group=self._tg)
+        self._host_call("scatter", dist.scatter, o, ins if self._rank == src else None, src=self._ranks[src], group=self._tg)
         return output
 
     def reduce_scatter(self, output, input, op: ReduceOp = ReduceOp.Sum):
         """``output`` receives the reduction over ranks of ``input[rank]``."""
         o = _unwrap(output)
         ins = [_unwrap(i) for i in input]
-        self._seq += 1
+        self._begin()
         if len(ins) != self._world:
             raise InvalidConfiguration(f"reduce_scatter needs {self._world} input tensors, got {len(ins)}")
         if self._world == 1:
@@ -324,13 +390,13 @@ class ProcessGroup:
             return output
         import torch.distributed as dist
 
-        dist.reduce_scatter(o, ins, op=_torch_op(op), group=self._tg)
+        self._host_call("reduce_scatter", dist.reduce_scatter, o, ins, op=_torch_op(op), group=self._tg)
         if op is ReduceOp.Average:
             o.div_(self._world)
         return output
 
     def barrier(self) -> None:
-        self._seq += 1
+        self._begin()
         if self._world == 1:
             return
         if self._backend is Backend.Nvlink and torch.cuda.is_available():
@@ -441,6 +507,17 @@ def destroy_process_group(keep_torch: bool = False) -> None:
 
         if g.world_size() > 1 and dist.is_initialized() and not keep_torch:
             dist.destroy_process_group()
+
+
+def leave_process_group() -> None:
+    """This rank stops taking part: it announces its departure in the rendezvous store (the remaining ranks get a
+    ``CommunicationError`` from their next collective instead of waiting for it) and closes its group.  Call it
+    between steps, with no collective of this rank in flight."""
+    global _default_group
+    with _lock:
+        g, _default_group = _default_group, None
+    if g is not None:
+        g.leave()
 
 
 def get_rank() -> int:

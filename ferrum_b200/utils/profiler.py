@@ -90,10 +90,16 @@ def measured_peaks() -> dict | None:
 
 
 class StepTimer:
-    """``with timer.step(batch): ...`` — emits one JSON line every ``every`` steps."""
+    """``with timer.step(batch): ...`` — emits one JSON line every ``every`` steps: samples/s, ms/step, with
+    ``flops_per_sample`` the TFLOP/s and the fraction of the measured sustained tensor-core rate, and with
+    ``engine`` (a ``DistributedDataParallel`` in ``comm_profile`` mode) the communication record of the last
+    step: bucket count, kernel time per bucket, achieved all-reduce bus GB/s and the exposed tail after backward."""
 
-    def __init__(self, every: int = 10, flops_per_sample: float | None = None, sink=print):
+    def __init__(self, every: int = 10, flops_per_sample: float | None = None, sink=print, engine=None):
         self.every, self.flops, self.sink = every, flops_per_sample, sink
+        self.engine = engine
+        if engine is not None:
+            engine.comm_profile(True)
         self._n = self._samples = 0
         self._t0 = None
         self.history = []
@@ -117,6 +123,14 @@ class StepTimer:
                 pk = measured_peaks()
                 if pk:
                     rec["frac_of_measured_bf16_sustained"] = rec["tflops"] / pk["bf16_tflops_sustained"]
+            comm = self.engine.last_comm_profile() if self.engine is not None else None
+            if comm and comm["buckets"]:
+                us = [b["kernel_us"] for b in comm["buckets"]]
+                nbytes = sum(b["bytes"] for b in comm["buckets"])
+                rec["comm"] = {"buckets": len(us), "bucket_kernel_us": [round(u, 1) for u in us],
+                               "comm_busy_us": round(comm["comm_busy_us"], 1),
+                               "bus_gbs": round(sum(b["bus_gbs"] * b["bytes"] for b in comm["buckets"]) / nbytes, 1),
+                               "exposed_tail_us": round(comm["exposed_tail_us"], 1)}
             self.history.append(rec)
             self.sink(json.dumps(rec))
             self._samples, self._t0 = 0, time.perf_counter()

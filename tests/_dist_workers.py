@@ -170,3 +170,87 @@ def leaving_rank_worker(rank, world, port, out_dir):
             d.destroy_process_group()
         except Exception:
             pass
+
+
+def recovery_worker(rank, world, port, out_dir):
+    """Three ranks train with DDP and checkpoint; rank 2 leaves between steps.  The survivors get
+    CommunicationError from the library at their next step, destroy the group, form a new one of two ranks, load
+    the checkpoint and train on."""
+    fb, d, pg = _init(rank, world, port, timeout=20)
+    from ferrum_b200 import nn, optim, serialize
+
+    def build():
+        torch.manual_seed(7)
+        m = nn.Sequential(nn.Linear(6, 16), nn.Tanh(), nn.Linear(16, 3))
+        o = optim.Adam(m.parameters(), optim.AdamConfig(lr=1e-2))
+        return m, o
+
+    g = torch.Generator().manual_seed(11)
+    X, Y = torch.randn(24, 6, generator=g), torch.randn(24, 3, generator=g)
+
+    def step(ddp, opt, r, w):
+        xs, ys = X[r::w], Y[r::w]
+        opt.zero_grad()
+        loss = nn.mse_loss(ddp(xs), ys)
+        loss.backward()
+        opt.step()
+        return loss.item()
+
+    model, opt = build()
+    ddp = d.DistributedDataParallel(model, pg).fuse_optimizer(opt)
+    for _ in range(2):
+        step(ddp, opt, rank, world)
+    ck = os.path.join(out_dir, "ck.ferrum")
+    if rank == 0:
+        serialize.save_checkpoint(ck, model=model, optimizer=opt)
+    pg.barrier()
+    if rank == 2:
+        d.leave_process_group()          # between steps, nothing of this rank in flight
+        open(os.path.join(out_dir, "rec2"), "w").write("left")
+        return
+    time.sleep(0.5)                      # the gap between two steps in which the departure becomes visible
+    try:
+        step(ddp, opt, rank, world)
+        res = "no error"
+    except d.CommunicationError as exc:  # raised on the host, before anything was launched
+        res = "detected" if "left the job" in str(exc) else f"other: {exc}"
+    d.destroy_process_group()
+    # the survivors regroup: same rank order, a fresh rendezvous next to the old one
+    new_world, new_rank = world - 1, rank
+    cfg = d.BackendConfig(master_addr="127.0.0.1", master_port=port + 1, timeout_seconds=20)
+    pg2 = d.init_process_group(d.Backend.Gloo, new_rank, new_world, cfg)
+    model2, opt2 = build()
+    with torch.no_grad():
+        for p in model2.torch_parameters():
+            p.add_(1.0)                   # nothing of the fresh model may survive the load
+    serialize.load_checkpoint(ck, model=model2, optimizer=opt2)
+    ddp2 = d.DistributedDataParallel(model2, pg2).fuse_optimizer(opt2)
+    l0 = step(ddp2, opt2, new_rank, new_world)
+    for _ in range(5):
+        l1 = step(ddp2, opt2, new_rank, new_world)
+    flat = torch.cat([p.detach().reshape(-1) for p in model2.torch_parameters()])
+    both = [torch.empty_like(flat) for _ in range(new_world)]
+    pg2.all_gather(both, flat)
+    same = all(torch.equal(both[0], b) for b in both)
+    d.destroy_process_group()
+    open(os.path.join(out_dir, f"rec{rank}"), "w").write(
+        f"{res} steps={opt2.step_count} same={same} improved={l1 < l0}")
+
+
+def silent_death_worker(rank, world, port, out_dir):
+    """Rank 1 exits without announcing anything; rank 0's next collective ends with Timeout / CommunicationError
+    after the (short) process-group timeout instead of hanging."""
+    fb, d, pg = _init(rank, world, port, timeout=4)
+    t = torch.ones(3)
+    pg.all_reduce(t)
+    if rank == 1:
+        os._exit(0)
+    time.sleep(0.5)
+    t0 = time.time()
+    try:
+        pg.all_reduce(t)
+        res = "no error"
+    except (d.Timeout, d.CommunicationError) as exc:
+        res = type(exc).__name__
+    open(os.path.join(out_dir, "silent0"), "w").write(f"{res} {time.time() - t0:.1f}")
+    os._exit(0)  # the group cannot be shut down cleanly any more

@@ -181,10 +181,10 @@ def main(out_dir):
     #      autocast + the step replayed from a CUDA graph + default communication blocks.  Checked (a) against the
     #      plain engine (eager launches, every rank keeps full masters) under the same autocast, which the fp32
     #      sections above tie to the single-process trajectory, and (b) against one process on the whole batch.
-    def run_engine(bench_cfg, steps=6):
+    def run_engine(bench_cfg, steps=6, defer=True):
         model = wide_model()
         opt = fb.optim.Adam(model.parameters(), fb.optim.AdamConfig(lr=1e-3))
-        ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.5).fuse_optimizer(opt)
+        ddp = d.DistributedDataParallel(model, pg).bucket_size_mb(0.5).fuse_optimizer(opt).defer_update(defer)
         if bench_cfg:
             ddp.shard_master_weights(True)
 
@@ -216,6 +216,13 @@ def main(out_dir):
     plain, benchlike = run_engine(False), run_engine(True)
     err = (plain - benchlike).abs().max().item()
     check(f"bench configuration equals the plain engine (max err {err:.2e})", err < 1e-6)
+    # the single-kernel form (all-reduce + update + publish per bucket inside backward), eager and as bench.py's
+    # configuration, must follow the same trajectory as the two-kernel form
+    for cfg in (False, True):
+        single_kernel = run_engine(cfg, defer=False)
+        err = (plain - single_kernel).abs().max().item()
+        check(f"single-kernel reduction (bench configuration: {cfg}) equals the two-kernel form "
+              f"(max err {err:.2e})", err < 1e-6)
     allp = [torch.empty_like(benchlike) for _ in range(world)]
     pg.all_gather(allp, benchlike)
     check("bench configuration: fp32 masters identical on every rank after sync_master_weights",

@@ -184,3 +184,17 @@ def test_error_messages():
     assert str(fb.NotImplemented_("x")) == "Not implemented: x"
     assert issubclass(fb.ReshapeError, fb.FerrumError)
     assert "Blackwell" in fb.banner()
+
+
+def test_gpu_tensor_vocabulary_of_the_reference():
+    """ptr / size_bytes / to_host / to_f32 / to_f64 / sum_axis / mean_axis (ferrum-cuda/src/tensor.rs:120-159,
+    266-279) exist on the one tensor class and agree with the plain accessors."""
+    import struct
+
+    t = Tensor.from_slice([1.0, 2.0, 3.0, 4.0, 5.0, 6.0], [2, 3])
+    assert t.ptr() != 0 and t.size_bytes() == 24
+    assert struct.unpack("<6f", t.to_host()) == (1.0, 2.0, 3.0, 4.0, 5.0, 6.0)
+    assert t.to_f32() == [1.0, 2.0, 3.0, 4.0, 5.0, 6.0] and t.to_f64() == t.to_f32()
+    assert t.transpose(0, 1).to_host() == Tensor.from_slice([1.0, 4.0, 2.0, 5.0, 3.0, 6.0], [3, 2]).to_host()
+    assert t.sum_axis(0).to_vec() == [5.0, 7.0, 9.0] and t.sum_axis(1).to_vec() == [6.0, 15.0]
+    assert t.mean_axis(1).to_vec() == [2.0, 5.0] and t.mean_axis(-2).shape == (3,)

@@ -75,6 +75,90 @@ def test_staged_allreduce_emulated(world, n_valid, offset):
         a.close()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fuse,publish_master", [(2, 1), (2, 0), (1, 1)])
+def test_reduce_scatter_then_shard_update_emulated(world, fuse, publish_master):
+    """The two-kernel form of the gradient reduction: a reduce-scatter per bucket (each rank sums its shard over
+    all ranks, 1 / world folded in, result left in its own arena) and one update kernel over all buckets (Adam or
+    SGD-momentum on the shard, new fp32 / bf16 weights stored into every rank's arena).  Three buckets of ragged
+    lengths inside one arena layout, three steps, against a float reference of the whole thing."""
+    from ferrum_b200 import _lib as L
+    from ferrum_b200.utils.runtime import check_status
+
+    lens = [4 * world * 257, 4 * world * 3, 4 * world * 1031]
+    starts = [0, lens[0], lens[0] + lens[1]]
+    n = sum(lens)
+    lib, arenas, ctxs = _setup(world, n * 3)
+    base = arenas[0].data_offset()
+    off_p, off_g, off_s = base, base + n * 4, base + n * 8
+    torch.manual_seed(17 + world)
+    p0 = torch.randn(n, device="cuda")
+    for a in arenas:
+        a.view(off_p, (n,), torch.float32).copy_(p0)
+    pers = [ln // world for ln in lens]
+    soffs = [0, pers[0], pers[0] + pers[1]]
+    ms = [torch.zeros(sum(pers), device="cuda") for _ in range(world)]
+    vs = [torch.zeros(sum(pers), device="cuda") for _ in range(world)]
+    mp = (ctypes.c_void_p * world)(*[m.data_ptr() for m in ms])
+    vp = (ctypes.c_void_p * world)(*[v.data_ptr() for v in vs])
+    # the middle bucket always publishes fp32 (a bucket of biases under sharded master weights)
+    pub = [publish_master, 1, publish_master]
+    table = torch.tensor([[starts[k], lens[k], soffs[k], pub[k]] for k in range(3)], dtype=torch.int64,
+                         device="cuda")
+    lr, b1, b2, eps, wd, mu = 1e-2, 0.9, 0.999, 1e-8, 0.05, 0.9
+    ref_p, ref_m, ref_v = p0.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    e_rs, e_up = 1, 1
+    for t in (1, 2, 3):
+        grads = [torch.randn(n, device="cuda") for _ in range(world)]
+        for a, g in zip(arenas, grads):
+            a.view(off_g, (n,), torch.float32).copy_(g)
+        for k in range(3):
+            rc = lib.fb_dist_reduce_scatter_shard_emulated(ctxs, world, 2, e_rs, off_g + starts[k] * 4, lens[k],
+                                                           1.0 / world, 3, 256, _stream())
+            assert rc == 0
+            e_rs += 2
+        if fuse == 2:
+            h = L.AdamH(lr, b1, b2, eps, wd, 1 - b1 ** t, 1 - b2 ** t, 1.0)
+            rc = lib.fb_dist_shard_update_emulated(ctxs, world, 2, 4, e_up, off_g, off_p, off_s, table.data_ptr(), 3,
+                                                   ctypes.byref(h), None, mp, vp, 5, 256, _stream())
+        else:
+            h = L.SgdH(lr, mu, wd, 1.0, 0, 1 if t == 1 else 0)
+            rc = lib.fb_dist_shard_update_emulated(ctxs, world, 1, 4, e_up, off_g, off_p, off_s, table.data_ptr(), 3,
+                                                   None, ctypes.byref(h), mp, None, 5, 256, _stream())
+        assert rc == 0
+        e_up += 2
+        g = torch.stack(grads).sum(0) / world
+        if fuse == 2:
+            ref_p = ref_p - lr * wd * ref_p
+            ref_m = b1 * ref_m + (1 - b1) * g
+            ref_v = b2 * ref_v + (1 - b2) * g * g
+            ref_p = ref_p - lr * (ref_m / (1 - b1 ** t)) / ((ref_v / (1 - b2 ** t)).sqrt() + eps)
+        else:
+            g = g + wd * ref_p
+            ref_m = g if t == 1 else mu * ref_m + g
+            ref_p = ref_p - lr * ref_m
+    check_status()
+    owner_p = torch.empty(n, device="cuda")
+    for k in range(3):          # the owner of a shard always holds its current fp32 values
+        for r in range(world):
+            lo, hi = starts[k] + r * pers[k], starts[k] + (r + 1) * pers[k]
+            owner_p[lo:hi] = arenas[r].view(off_p, (n,), torch.float32)[lo:hi]
+    assert torch.allclose(owner_p, ref_p, atol=2e-5, rtol=1e-5), (owner_p - ref_p).abs().max().item()
+    for a in arenas:
+        assert torch.equal(a.view(off_s, (n,), torch.bfloat16), owner_p.bfloat16())
+        got = a.view(off_p, (n,), torch.float32)
+        for k in range(3):
+            if pub[k]:
+                assert torch.equal(got[starts[k]:starts[k] + lens[k]], owner_p[starts[k]:starts[k] + lens[k]])
+    got_m = torch.empty(n, device="cuda")
+    for k in range(3):
+        for r in range(world):
+            got_m[starts[k] + r * pers[k]:starts[k] + (r + 1) * pers[k]] = ms[r][soffs[k]:soffs[k] + pers[k]]
+    assert torch.allclose(got_m, ref_m, atol=1e-5)
+    for a in arenas:
+        a.close()
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_fused_allreduce_adam_emulated(world):
     from ferrum_b200 import _lib as L

@@ -64,3 +64,21 @@ def test_skipped_collective_is_detected(tmp_path):
 def test_rank_leaving_between_steps_is_noticed(tmp_path):
     _spawn(W.leaving_rank_worker, 2, tmp_path)
     assert (tmp_path / "leave0").read_text().startswith("peer_left_at_")
+
+
+@pytest.mark.timeout(240)
+def test_survivors_regroup_and_resume_from_the_checkpoint(tmp_path):
+    """The whole recovery path on host ranks: a rank leaves between steps -> the library raises
+    CommunicationError at the survivors' next step -> destroy_process_group -> init_process_group with the
+    remaining world -> load_checkpoint -> training continues, replicas identical."""
+    _spawn(W.recovery_worker, 3, tmp_path)
+    assert (tmp_path / "rec2").read_text() == "left"
+    for r in (0, 1):
+        assert (tmp_path / f"rec{r}").read_text() == "detected steps=8 same=True improved=True"
+
+
+@pytest.mark.timeout(120)
+def test_rank_that_dies_silently_ends_the_next_collective_with_an_error(tmp_path):
+    _spawn(W.silent_death_worker, 2, tmp_path)
+    res, secs = (tmp_path / "silent0").read_text().split()
+    assert res in ("Timeout", "CommunicationError") and float(secs) < 60
