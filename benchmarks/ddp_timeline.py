@@ -30,7 +30,10 @@ def main():
     ap.add_argument("--depth", type=int, default=8)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--comm-blocks", type=int, default=0, help="0 = the engine's default for this world size")
+    ap.add_argument("--update-blocks", type=int, default=0, help="blocks of the update kernel (0 = engine default)")
     ap.add_argument("--no-shard-master", action="store_true")
+    ap.add_argument("--single-kernel", action="store_true",
+                    help="all-reduce + update + publish in one kernel per bucket inside backward (defer_update(False))")
     a = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -49,6 +52,10 @@ def main():
     eng.fuse_optimizer(opt)
     if world > 1 and not a.no_shard_master:
         eng.shard_master_weights(True)
+    if a.single_kernel:
+        eng.defer_update(False)
+    if a.update_blocks > 0:
+        eng._update_blocks = a.update_blocks
     if a.comm_blocks > 0:
         eng._comm_blocks = a.comm_blocks
     eng.comm_profile(True)
@@ -100,7 +107,8 @@ def main():
     fb.distributed.destroy_process_group()
     if rank == 0:
         print(json.dumps({"world": world, "comm_blocks": eng._comm_blocks, "shard_master": eng._shard_master,
-                          "bucket_mb": a.bucket_mb, "launches": "eager", "step_ms_max_over_ranks": float(t[0]),
+                          "bucket_mb": a.bucket_mb, "launches": "eager",
+                          "reduction": "single kernel per bucket" if a.single_kernel else "reduce-scatter per bucket + one update kernel", "step_ms_max_over_ranks": float(t[0]),
                           "exposed_tail_us_max_over_ranks": float(t[1]), "rank0": mine, "buckets_rank0": table}))
 
 

@@ -138,7 +138,7 @@ class DistributedDataParallel(Module, GradSink):
         # busy for 230 us per 64 MB bucket; they do not fit beside a persistent GEMM CTA and stream half of the
         # optimizer state through the L2 the GEMMs live on (7.4 ms/step against 6.3 on one GPU).
         self._defer = True
-        self._update_blocks = 296     # blocks of the update kernel: two per SM, it runs alone
+        self._update_blocks = 444     # blocks of the update kernel: three per SM, it runs alone
         self._dev_epoch_up = None
         self._table = None
         self._prof = None             # per-step timing events of the bucket kernels (comm_profile)
