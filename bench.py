@@ -68,6 +68,8 @@ def parse():
     ap.add_argument("--single-kernel-reduction", action="store_true",
                     help="DDP: all-reduce + Adam + publish in one kernel per bucket inside backward instead of a "
                          "reduce-scatter per bucket and one update kernel after backward (the default)")
+    ap.add_argument("--update-in-backward", action="store_true",
+                    help="DDP: launch the update kernel per bucket behind its reduce-scatter, inside backward")
     ap.add_argument("--no-shard-master", action="store_true",
                     help="DDP: every rank keeps the full fp32 master weights current after every step")
     return ap.parse_args()
@@ -198,8 +200,10 @@ def run_ours(args):
     if use_engine:
         engine = fb.distributed.DistributedDataParallel(model, fb.distributed.get_world()).bucket_size_mb(25)
         engine.fuse_optimizer(opt)
-        if args.single_kernel_reduction or args.overlap_optimizer:
+        if args.single_kernel_reduction:
             engine.defer_update(False)
+        if args.update_in_backward or args.overlap_optimizer:
+            engine.update_in_backward(True)
         shard = args.shard_master or (world >= 2 and not args.no_shard_master)
         if shard:
             engine.shard_master_weights(True)

@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--comm-blocks", type=int, default=0, help="0 = the engine's default for this world size")
     ap.add_argument("--update-blocks", type=int, default=0, help="blocks of the update kernel (0 = engine default)")
+    ap.add_argument("--update-in-backward", action="store_true",
+                    help="update kernel per bucket behind its reduce-scatter instead of once after backward")
     ap.add_argument("--no-shard-master", action="store_true")
     ap.add_argument("--single-kernel", action="store_true",
                     help="all-reduce + update + publish in one kernel per bucket inside backward (defer_update(False))")
@@ -54,6 +56,8 @@ def main():
         eng.shard_master_weights(True)
     if a.single_kernel:
         eng.defer_update(False)
+    if a.update_in_backward:
+        eng.update_in_backward(True)
     if a.update_blocks > 0:
         eng._update_blocks = a.update_blocks
     if a.comm_blocks > 0:

@@ -44,6 +44,9 @@ def _sigs():
         "fb_gemm_bf16_2cta_push": (I, [P, P, I, I, I, LL, LL, LL, I, I, POINTER(DistCtx), LL, LL, LL, LL, I, P, P]),
         "fb_dist_set_pushed_ranges": (I, [I, POINTER(ctypes.c_longlong), POINTER(ctypes.c_longlong)]),
         "fb_dist_barrier": (I, [POINTER(DistCtx), I, U, P]),
+        "fb_dist_allreduce_oneshot": (I, [POINTER(DistCtx), I, U, LL, LL, I, F, P, P, I, I, P]),
+        "fb_dist_allreduce_oneshot_emulated": (I, [POINTER(DistCtx), I, I, U, LL, LL, I, F, POINTER(c_void_p),
+                                                   POINTER(c_void_p), I, I, P]),
         "fb_dist_reduce_scatter_shard": (I, [POINTER(DistCtx), I, I, U, P, LL, LL, F, I, I, P]),
         "fb_dist_shard_update": (I, [POINTER(DistCtx), I, I, I, U, P, LL, LL, LL, P, I, POINTER(AdamH), POINTER(SgdH),
                                      P, P, I, I, P, P]),

@@ -342,6 +342,75 @@ allreduce_emulated_kernel(const EmuPack pk, ArArgs a) {
   allreduce_body<FUSE, false, 1, FB_MAX_RANKS>(pk.c[vr], vb, pk.blocks_per_rank, a, &s_fail);
 }
 
+// ------------------------------------------------------------- one-shot all-reduce (small messages)
+// Latency form for messages of a few hundred KB at most: every rank puts its tensor into its own arena region,
+// ONE handshake follows, then every rank reads all regions and reduces for itself, straight into its result
+// tensor.  The two-shot form above needs a second trip over the link (publication of the reduced shards) and a
+// second handshake.  No exit handshake is needed because the region alternates between two slots from call to
+// call: a slot is rewritten only after the next collective's handshake has been passed, and a peer that has
+// arrived at that collective has finished the kernel that read the slot (kernels of a stream run in order).
+// Block b stages and reads the same contiguous slice of positions on every rank.
+struct OneShotArgs {
+  int channel;
+  uint32_t epoch;
+  long long region_off;  // byte offset of the slot used by this call
+  long long n;           // elements (floats)
+  int op;
+  float scale;
+  const float* in;
+  float* out;
+};
+
+template <int W>
+__device__ void oneshot_body(const fb_dist_ctx& c, int vblock, int nvblocks, const OneShotArgs& a, const float* in,
+                             float* out, int* s_fail) {
+  const long long per = (a.n + nvblocks - 1) / nvblocks;
+  const long long lo = min(a.n, per * vblock), hi = min(a.n, lo + per);
+  float* mine = reinterpret_cast<float*>(c.arena[c.rank] + a.region_off);
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) mine[i] = in[i];
+  if (!block_handshake(c, a.channel, vblock, a.epoch, s_fail, 500)) return;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    float part[W];
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+      if (r < c.world) part[r] = *reinterpret_cast<const volatile float*>(c.arena[r] + a.region_off + i * 4);
+    float acc = part[0];
+#pragma unroll
+    for (int r = 1; r < W; ++r)
+      if (r < c.world) {
+        if (a.op == FB_OP_PROD) acc *= part[r];
+        else if (a.op == FB_OP_MIN) acc = fminf(acc, part[r]);
+        else if (a.op == FB_OP_MAX) acc = fmaxf(acc, part[r]);
+        else acc += part[r];
+      }
+    out[i] = acc * a.scale;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+oneshot_kernel(const fb_dist_ctx c, const OneShotArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  oneshot_body<FB_MAX_RANKS>(c, blockIdx.x, gridDim.x, a, a.in, a.out, &s_fail);
+}
+
+struct EmuOneShot {
+  fb_dist_ctx c[FB_MAX_RANKS];
+  const float* in[FB_MAX_RANKS];
+  float* out[FB_MAX_RANKS];
+  int blocks_per_rank;
+};
+__global__ void __launch_bounds__(256)
+oneshot_emulated_kernel(const EmuOneShot pk, const OneShotArgs a) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const int vr = blockIdx.x / pk.blocks_per_rank;
+  oneshot_body<FB_MAX_RANKS>(pk.c[vr], blockIdx.x % pk.blocks_per_rank, pk.blocks_per_rank, a, pk.in[vr], pk.out[vr],
+                             &s_fail);
+}
+
 // ------------------------------------------------------------- pull collectives
 struct CollArgs {
   int mode;
@@ -848,4 +917,39 @@ extern "C" int fb_dist_barrier(const fb_dist_ctx* ctx, int channel, unsigned epo
   if (!ctx_ok(ctx) || channel < 0 || channel >= FB_FLAG_CHANNELS) return -1;
   barrier_kernel<<<1, 32, 0, stream>>>(*ctx, channel, epoch);
   return static_cast<int>(cudaGetLastError());
+}
+
+// One-shot all-reduce of a local fp32 tensor of n elements (in and out may be the same pointer) through the
+// arena slot at region_off (n * 4 bytes): one launch, one handshake.  The caller alternates between two slots
+// from call to call and uses slots that no other collective writes (see the kernel's comment).
+extern "C" int fb_dist_allreduce_oneshot(const fb_dist_ctx* ctx, int channel, unsigned epoch, long long region_off,
+                                         long long n, int op, float scale, const float* in, float* out,
+                                         int nblocks, int nthreads, cudaStream_t stream) {
+  if (!ctx_ok(ctx) || n <= 0 || in == nullptr || out == nullptr || nblocks < 1 || nblocks > FB_FLAG_BLOCKS ||
+      nthreads < 32 || nthreads > 256 || channel < 0 || channel >= FB_FLAG_CHANNELS || (region_off & 3))
+    return -1;
+  OneShotArgs a{channel, epoch, region_off, n, op, scale, in, out};
+  oneshot_kernel<<<nblocks, nthreads, 0, stream>>>(*ctx, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_dist_allreduce_oneshot_emulated(const fb_dist_ctx* ctxs, int world, int channel, unsigned epoch,
+                                                  long long region_off, long long n, int op, float scale,
+                                                  const float* const* in, float* const* out, int nblocks,
+                                                  int nthreads, cudaStream_t stream) {
+  if (world < 1 || world > FB_MAX_RANKS || n <= 0 || in == nullptr || out == nullptr || nblocks < 1 ||
+      nblocks > FB_FLAG_BLOCKS)
+    return -1;
+  EmuOneShot pk{};
+  for (int r = 0; r < world; ++r) {
+    if (!ctx_ok(&ctxs[r]) || ctxs[r].world != world || ctxs[r].rank != r) return -1;
+    pk.c[r] = ctxs[r];
+    pk.in[r] = in[r];
+    pk.out[r] = out[r];
+  }
+  pk.blocks_per_rank = nblocks;
+  OneShotArgs a{channel, epoch, region_off, n, op, scale, nullptr, nullptr};
+  void* args[] = {&pk, &a};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(oneshot_emulated_kernel),
+                                                      dim3(world * nblocks), dim3(nthreads), args, 0, stream));
 }

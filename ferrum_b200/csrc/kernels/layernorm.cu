@@ -1025,17 +1025,6 @@ int fwd_t(const void* x, const float* gamma, const float* beta, void* y, float* 
   Geo g;
   if (geometry(cols, &g) && aligned16(x, y, gamma, beta)) {
     const int nvec = cols / 8;
-    // Measurement knob FERRUM_LN_FWD_TPR=64|128: rows of 4096 columns on 64 threads x 8 vectors (or 128 x 4)
-    // of the register-tiled kernel instead of the warp-per-row one.
-    static const int forced_tpr = env_int("FERRUM_LN_FWD_TPR", 0);
-    if (forced_tpr == 64 && nvec == 512) {
-      launch_fwd<T, 64, 8>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, (rows + 3) / 4, st);
-      return static_cast<int>(cudaGetLastError());
-    }
-    if (forced_tpr == 128 && nvec == 512) {
-      launch_fwd<T, 128, 4>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, (rows + 1) / 2, st);
-      return static_cast<int>(cudaGetLastError());
-    }
     if (launch_fwd_warp<T>(xp, gamma, beta, yp, mean, rstd, rows, cols, eps, pre_act, st))
       return static_cast<int>(cudaGetLastError());
     static const int ring_fwd = env_int("FERRUM_LN_RING_FWD", 0);

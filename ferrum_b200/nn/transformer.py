@@ -20,8 +20,11 @@ from .modules import LayerNorm, Linear, Module, tensor_io
 
 
 class MultiHeadAttention(Module):
-    """``memory_efficient=True``: under autocast with head dimension 64 the training forward uses the blockwise
-    kernel and saves no S x S activations (the backward recomputes the scores)."""
+    """Under autocast with head dimension 64 and no explicit mask (``causal=True`` is fine) the attention core runs
+    on the blockwise tcgen05 kernels in both directions: no S x S matrix is stored for the backward pass, the
+    probabilities are recomputed tile by tile from one log-sum-exp per row.  Other head dimensions, explicit
+    masks and fp32 precision take the batched-GEMM + softmax path (``memory_efficient=True`` then recomputes the
+    scores in the backward pass where the blockwise forward applies)."""
 
     def __init__(self, embed_dim: int, num_heads: int, device=None, memory_efficient: bool = False):
         super().__init__()
@@ -56,6 +59,11 @@ class MultiHeadAttention(Module):
                 and F.flash_attention_ok(q, k, v)):
             # inference (no gradient needed), bf16: blockwise attention, the score matrix is never materialised
             ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim), causal=causal)
+            return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
+        if (mask is None and self.head_dim == 64 and config.low_precision_active()
+                and F.flash_attention_ok(q, k, v, need_no_grad=False)):
+            # training, bf16: blockwise forward AND backward, nothing of size S x S in memory
+            ctx = F.attention_blockwise(q, k, v, 1.0 / math.sqrt(self.head_dim), causal=causal)
             return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
         if causal:  # the differentiable paths take the causal structure as an additive mask
             i = torch.arange(Sq, device=q.device)[:, None]

@@ -581,7 +581,8 @@ def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_n
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                     return_lse: bool = False, causal: bool = False):
     """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, 64]`` operands without materialising the score matrix:
-    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  Forward only.  ``causal``: query ``i`` sees
+    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  No autograd node is recorded here
+    (:func:`attention_blockwise` is the differentiable form).  ``causal``: query ``i`` sees
     keys ``j <= i + (Skv - Sq)`` and key tiles past the diagonal are skipped.  The result is stored as
     ``[B, Sq, H, 64]`` and returned as the ``[B, H, Sq, 64]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
     B, H, Sq, _ = q.shape
@@ -597,6 +598,54 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
     _lib.check(rc, "fb_attention_fwd")
     res = out.permute(0, 2, 1, 3)
     return (res, lse) if return_lse else res
+
+
+class _BlockwiseAttentionFn(Function):
+    """``softmax(scale q k^T) v`` with the blockwise tcgen05 kernels in BOTH directions: the forward saves q, k, v,
+    the output and one log-sum-exp per row; the backward recomputes the probabilities tile by tile
+    (csrc/kernels/attention_bwd.cu).  Nothing of size S x S is ever stored."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal):
+        out, lse = flash_attention(q, k, v, scale, return_lse=True, causal=causal)
+        qb, kb, vb = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (q, k, v))
+        ctx.save_for_backward(qb, kb, vb, out, lse)
+        ctx.scale, ctx.causal = scale, causal
+        ctx.in_dtypes = (q.dtype, k.dtype, v.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        q, k, v, out, lse = ctx.saved_tensors
+        B, H, Sq, _ = q.shape
+        Skv = k.shape[2]
+        o = out.permute(0, 2, 1, 3)                      # the kernel's own [B, Sq, H, 64] storage
+        if not o.is_contiguous():
+            o = o.contiguous()
+        go = g.permute(0, 2, 1, 3)
+        if go.dtype != torch.bfloat16 or not go.is_contiguous():
+            go = go.to(torch.bfloat16).contiguous()
+        dq = torch.empty((B, Sq, H, 64), device=q.device, dtype=torch.bfloat16)
+        dk = torch.empty((B, Skv, H, 64), device=q.device, dtype=torch.bfloat16)
+        dv = torch.empty((B, Skv, H, 64), device=q.device, dtype=torch.bfloat16)
+        delta = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32)
+        rc = _lib.cuda().fb_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), go.data_ptr(),
+                                          lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                          dv.data_ptr(), B, H, Sq, Skv, q.stride(0), q.stride(1), q.stride(2),
+                                          k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
+                                          v.stride(2), float(ctx.scale), 1 if ctx.causal else 0, _rt.status_ptr(),
+                                          _stream())
+        _lib.check(rc, "fb_attention_bwd")
+        grads = [t.permute(0, 2, 1, 3) for t in (dq, dk, dv)]
+        grads = [gr if gr.dtype == dt else gr.to(dt) for gr, dt in zip(grads, ctx.in_dtypes)]
+        return grads[0], grads[1], grads[2], None, None
+
+
+def attention_blockwise(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                        causal: bool = False) -> torch.Tensor:
+    """Differentiable blockwise attention for ``[B, H, S, 64]`` operands (see ``flash_attention_ok``): forward and
+    backward on the tcgen05 kernels, no S x S matrix in memory in either direction."""
+    return _BlockwiseAttentionFn.apply(q, k, v, float(scale), bool(causal))
 
 
 class _CheckpointedAttentionFn(Function):

@@ -138,6 +138,7 @@ class DistributedDataParallel(Module, GradSink):
         # busy for 230 us per 64 MB bucket; they do not fit beside a persistent GEMM CTA and stream half of the
         # optimizer state through the L2 the GEMMs live on (7.4 ms/step against 6.3 on one GPU).
         self._defer = True
+        self._update_in_backward = False  # two-kernel form with the update launched per bucket inside backward
         self._update_blocks = 444     # blocks of the update kernel: three per SM, it runs alone
         self._dev_epoch_up = None
         self._table = None
@@ -191,6 +192,15 @@ class DistributedDataParallel(Module, GradSink):
         """``True`` (default): reduce-scatter per bucket during backward, one optimizer + publish kernel after it.
         ``False``: all-reduce, optimizer and publish in one kernel per bucket, inside backward."""
         self._defer = bool(flag)
+        return self
+
+    def update_in_backward(self, flag: bool = True) -> "DistributedDataParallel":
+        """Two-kernel form with the update kernel launched per bucket right behind its reduce-scatter instead of
+        once after backward: both kernels are small enough to share an SM with a persistent GEMM CTA, so the
+        optimizer's memory traffic is spread over the backward pass."""
+        self._update_in_backward = bool(flag)
+        if flag:
+            self._defer = True
         return self
 
     def push_gradients(self, flag: bool = True) -> "DistributedDataParallel":
@@ -554,10 +564,13 @@ class DistributedDataParallel(Module, GradSink):
                 rc = lib.fb_dist_reduce_scatter_shard(a.ctx, use_mc, 2, e, dev_e, self._off_grad + bk.start * 4,
                                                       bk.length, 1.0 / world, self._comm_blocks, self._comm_threads,
                                                       self._comm_stream.cuda_stream)
+            _lib.check(rc, "fb_dist_reduce_scatter_shard")
+            if self._update_in_backward:
+                self._launch_update(None, bucket=b)
+            else:
+                self._deferred = True
             if prof is not None:
                 prof["buckets"][b][2].record(self._comm_stream)
-            _lib.check(rc, "fb_dist_reduce_scatter_shard")
-            self._deferred = True
             return
         if self._pushed[b]:  # consumed by the launch below: these ranges are already complete in local memory
             rng = self._pushed[b]
@@ -592,17 +605,19 @@ class DistributedDataParallel(Module, GradSink):
             prof["buckets"][b][2].record(self._comm_stream)
         _lib.check(rc, "fb_dist_allreduce")
 
-    def _launch_update(self, prof) -> None:
-        """Optimizer update of this rank's shards of every bucket + publication of the new weights, one kernel on
-        the communication stream behind everything the backward pass enqueued."""
+    def _launch_update(self, prof, bucket: int | None = None) -> None:
+        """Optimizer update of this rank's shards + publication of the new weights on the communication stream:
+        one kernel over every bucket behind everything the backward pass enqueued, or (``bucket`` given) the
+        kernel for that one bucket behind its reduce-scatter."""
         from ..optim.optimizers import Adam
 
-        self._deferred = False
         lib, a, opt = _lib.cuda(), self._arena, self._opt
         world = self._pg.world_size()
         cur = torch.cuda.current_stream()
-        self._ready_event.record(cur)              # the new weights must not land under a GEMM that still reads them
-        self._comm_stream.wait_event(self._ready_event)
+        if bucket is None:
+            self._deferred = False
+            self._ready_event.record(cur)          # the new weights must not land under a GEMM that still reads them
+            self._comm_stream.wait_event(self._ready_event)
         self._ensure_state()
         if self._table is None:
             rows = [[bk.start, bk.length, self._state_off[i],
@@ -622,16 +637,20 @@ class DistributedDataParallel(Module, GradSink):
                 self._dev_epoch_up = torch.tensor([e], dtype=torch.int32, device=self._flat_params.device)
             dev_e = self._dev_epoch_up.data_ptr()
             dyn = opt._dyn.data_ptr()
-            if adam:
+            if adam and not self._advanced:  # once per step, before the first update kernel
+                self._advanced = True
                 _lib.check(lib.fb_optim_advance(dyn, opt.config.beta1, opt.config.beta2, st), "fb_optim_advance")
         ev = None
         if prof is not None and "buckets" in prof:
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             ev[0].record(cur)
             ev[1].record(self._comm_stream)
+        first, count, blocks = (0, len(self.buckets), self._update_blocks) if bucket is None else (
+            bucket, 1, self._comm_blocks)
         rc = lib.fb_dist_shard_update(a.ctx, 2 if adam else 1, 1 if a.has_multicast() else 0, 4, e, dev_e,
-                                      self._off_grad, self._off_param, self._off_shadow, self._table.data_ptr(),
-                                      len(self.buckets), adam_h, sgd_h, m_ptr, v_ptr, self._update_blocks, 256, dyn, st)
+                                      self._off_grad, self._off_param, self._off_shadow,
+                                      self._table.data_ptr() + 32 * first, count, adam_h, sgd_h, m_ptr, v_ptr,
+                                      blocks, 256, dyn, st)
         if ev is not None:
             ev[2].record(self._comm_stream)
             prof["buckets"]["update"] = (ev[0], ev[1], ev[2], self._total * 4)

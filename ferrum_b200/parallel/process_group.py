@@ -52,6 +52,7 @@ class ProcessGroup:
         self._seq = 0  # collective sequence number, identical on all ranks of a correct program
         self._last_peer_check = 0.0
         self._left = False
+        self._symm = {}  # data_ptr -> (arena, offset, bytes) of tensors handed out by symmetric_empty
 
     # ------------------------------------------------------------------ accessors
     @classmethod
@@ -161,10 +162,46 @@ class ProcessGroup:
     def comm_arena(self) -> SymmetricArena:
         """The staging arena of this group (allocated collectively on first use)."""
         if self._arena is None:
-            need = self._chunk * (1 + self._world)
+            need = self._chunk * (1 + self._world) + 2 * self._ONESHOT_BYTES  # + the two one-shot slots
             self._arena = SymmetricArena.create(need, self._rank, self._world, self.exchange,
                                                 self._config.device_wait_ns())
         return self._arena
+
+    # ------------------------------------------------------------------ registered tensors
+    def symmetric_empty(self, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A tensor in peer-mapped symmetric memory (collective: every rank calls it with the same arguments, in
+        the same order).  ``all_reduce`` and ``broadcast`` on it, and ``all_gather`` from it, run directly on the
+        peers' mappings, without the pass that stages an ordinary tensor into the group's arena and back.  The
+        tensor stays valid until the group is closed.  With one rank (or off the NVLink backend) it is an
+        ordinary tensor."""
+        shape = tuple(int(d) for d in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)))
+        numel = 1
+        for d in shape:
+            numel *= d
+        if not (self._backend is Backend.Nvlink and self._world > 1 and torch.cuda.is_available()):
+            return torch.empty(shape, dtype=dtype, device="cuda" if torch.cuda.is_available() else "cpu")
+        esz = torch.empty((), dtype=dtype).element_size()
+        unit = 16 * self._world                                  # every rank's shard starts on a 16-byte boundary
+        nbytes = max(unit, (numel * esz + unit - 1) // unit * unit)
+        arena = SymmetricArena.create(nbytes, self._rank, self._world, self.exchange, self._config.device_wait_ns())
+        off = arena.data_offset()
+        arena.view(off, (nbytes,), torch.uint8).zero_()
+        t = arena.view(off, (numel,), dtype).view(shape)
+        self._symm[t.data_ptr()] = (arena, off, nbytes)
+        torch.cuda.current_stream().synchronize()
+        self.barrier()                                           # every rank's padding is zero before anyone reads it
+        return t
+
+    def _registered(self, t: torch.Tensor):
+        """(arena, byte offset, region bytes) when ``t`` is a whole tensor from ``symmetric_empty``."""
+        ent = self._symm.get(t.data_ptr()) if t.is_cuda and t.is_contiguous() else None
+        if ent is not None and t.numel() * t.element_size() <= ent[2]:
+            return ent
+        return None
+
+    # Messages up to this size are all-reduced by the one-shot kernel (one handshake, every rank reduces for
+    # itself); its two alternating slots sit behind the staging regions of the other collectives.
+    _ONESHOT_BYTES = 256 * 1024
 
     def _check_device_status(self, what: str) -> None:
         code, where, i0, i1 = _rt.read_status(clear=True)
@@ -202,8 +239,19 @@ class ProcessGroup:
 
         if not t.is_floating_point():
             raise TensorError("native all_reduce supports floating-point tensors")
-        arena = self.comm_arena()
         lib = _lib.cuda()
+        reg = self._registered(t) if t.dtype == torch.float32 else None
+        if reg is not None:
+            # in place on the peers' mappings: two-shot over the (zero-padded) region, no staging pass
+            arena, roff, rbytes = reg
+            e = arena.next_epoch(0)
+            scale = 1.0 / self._world if op is ReduceOp.Average else 1.0
+            use_mc = 1 if (arena.has_multicast() and op in (ReduceOp.Sum, ReduceOp.Average)) else 0
+            _lib.check(lib.fb_dist_allreduce(arena.ctx, 0, use_mc, 0, e, roff, 0, -1, rbytes // 4, _OP_CODE[op],
+                                             scale, None, None, None, None, 1, self._blocks(rbytes), 256,
+                                             self._stream()), "fb_dist_allreduce")
+            return
+        arena = self.comm_arena()
         flat = t.contiguous().view(-1)
         work = flat if flat.dtype == torch.float32 else F.raw_cast(flat, torch.float32) if flat.dtype == torch.bfloat16 \
             else flat.float()
@@ -211,6 +259,18 @@ class ProcessGroup:
         per = self._chunk // 4
         off = arena.data_offset()
         scale = 1.0 / self._world if op is ReduceOp.Average else 1.0
+        if n * 4 <= self._ONESHOT_BYTES and work.data_ptr() % 4 == 0:
+            self._oneshot_parity = 1 - getattr(self, "_oneshot_parity", 1)
+            slot = off + self._chunk * (1 + self._world) + self._oneshot_parity * self._ONESHOT_BYTES
+            e = arena.next_epoch(0)
+            _lib.check(lib.fb_dist_allreduce_oneshot(arena.ctx, 0, e, slot, n, _OP_CODE[op], scale, work.data_ptr(),
+                                                     work.data_ptr(), max(1, min(128, (n + 1023) // 1024)), 256,
+                                                     self._stream()), "fb_dist_allreduce_oneshot")
+            if work.data_ptr() != flat.data_ptr():
+                flat.copy_(work)
+            if flat.data_ptr() != t.data_ptr():
+                t.copy_(flat.view(t.shape))
+            return
         use_mc = 1 if (arena.has_multicast() and op in (ReduceOp.Sum, ReduceOp.Average)) else 0
         for lo in range(0, n, per):
             cnt = min(per, n - lo)
@@ -256,6 +316,13 @@ class ProcessGroup:
         if not 0 <= root < self._world:
             raise InvalidRank(root, self._world)
         if self._world == 1:
+            return tensor
+        reg = self._registered(t) if self._native(t) else None
+        if reg is not None:  # every rank pulls the root's region into its own, in place
+            arena, roff, rbytes = reg
+            e = arena.next_epoch(0)
+            _lib.check(_lib.cuda().fb_dist_collective(arena.ctx, 0, 0, e, root, roff, roff, rbytes, 0, 1.0,
+                                                      self._blocks(rbytes), self._stream()), "fb_dist_collective")
             return tensor
         if self._native(t):
             flat = t.contiguous().view(-1).view(torch.uint8)
@@ -315,6 +382,20 @@ class ProcessGroup:
             outs[0].copy_(x)
             return output
         nbytes = x.numel() * x.element_size()
+        reg = self._registered(x) if self._native(x) else None
+        if reg is not None and nbytes % 16 == 0:
+            # the peers read this tensor where it lies; the results go straight into the output tensors
+            arena, roff, _ = reg
+            one = self._as_one_buffer(outs, nbytes)
+            dst = one if one is not None else torch.empty(self._world * nbytes, dtype=torch.uint8, device=x.device)
+            e = arena.next_epoch(0)
+            _lib.check(_lib.cuda().fb_dist_collective_staged(arena.ctx, 1, 0, e, 0, roff, nbytes, 0, 1.0, None,
+                                                             dst.data_ptr(), self._blocks(nbytes), self._stream()),
+                       "fb_dist_collective_staged")
+            if one is None:
+                for r, o in enumerate(outs):
+                    o.copy_(dst[r * nbytes:(r + 1) * nbytes].view(o.dtype).view(o.shape))
+            return output
         if self._native(x) and nbytes <= self._chunk:
             self._gather_like(1, 0, x, outs, nbytes)
             return output
@@ -427,6 +508,9 @@ class ProcessGroup:
             raise CommunicationError(f"ranks disagree on the collective sequence number: {seqs}")
 
     def close(self) -> None:
+        for arena, _, _ in self._symm.values():
+            arena.close()
+        self._symm = {}
         for name in ("_arena", "_sync_arena"):
             a = getattr(self, name)
             if a is not None:

@@ -60,6 +60,37 @@ def main(out_dir):
         check("reduce", torch.allclose(r_, base[:, :100].sum(0), atol=1e-5))
     pg.barrier()
 
+    # ---- tensors registered in symmetric memory: collectives run on the peers' mappings, no staging pass
+    for n in (5, 4099, (1 << 21) + 3):
+        st = pg.symmetric_empty((n,))
+        for rep in range(2):
+            st.copy_(base[rank, :1].expand(n) * (rep + 1) + torch.arange(n, device=dev) % 7)
+            pg.all_reduce(st, d.ReduceOp.Sum)
+            want = base[:, 0].sum() * (rep + 1) + world * (torch.arange(n, device=dev) % 7)
+            check(f"registered all_reduce {n} rep {rep}", torch.allclose(st, want, atol=1e-4, rtol=1e-5))
+        st.fill_(float(rank + 1))
+        pg.all_reduce(st, d.ReduceOp.Average)
+        check(f"registered all_reduce avg {n}", torch.allclose(st, torch.full_like(st, (world + 1) / 2.0)))
+    sb = pg.symmetric_empty((3, 1001), torch.bfloat16)
+    sb.copy_(base[rank, :3003].view(3, 1001).to(torch.bfloat16))
+    pg.broadcast(sb, world - 1)
+    check("registered broadcast", torch.equal(sb, base[world - 1, :3003].view(3, 1001).to(torch.bfloat16)))
+    sg = pg.symmetric_empty((2048,))
+    sg.copy_(base[rank, :2048])
+    outs = list(torch.empty(world, 2048, device=dev).unbind(0))
+    pg.all_gather(outs, sg)
+    check("all_gather from a registered tensor", all(torch.equal(o, base[r, :2048]) for r, o in enumerate(outs)))
+    outs = [torch.empty(2048, device=dev) for _ in range(world)]
+    pg.all_gather(outs, sg)
+    check("all_gather from a registered tensor into separate outputs",
+          all(torch.equal(o, base[r, :2048]) for r, o in enumerate(outs)))
+    # small messages take the one-shot kernel: many in a row alternate between its two slots
+    for k in range(6):
+        t = torch.full((257,), float(rank + k), device=dev)
+        pg.all_reduce(t, d.ReduceOp.Max)
+        check(f"one-shot all_reduce call {k}", torch.equal(t, torch.full_like(t, float(world - 1 + k))))
+    pg.barrier()
+
     # ---- fused DDP (fp32 GEMMs): world ranks x batch 16 == one process x batch world*16
     def make_model(seed=5):
         torch.manual_seed(seed)

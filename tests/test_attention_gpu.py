@@ -220,3 +220,75 @@ def test_flash_attention_causal(B, H, Sq, Skv):
     s = s.masked_fill(j > i + (Skv - Sq), float("-inf"))
     ref = torch.softmax(s, -1) @ v.float()
     assert (out.float() - ref).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv,causal", [(1, 2, 128, 128, False), (2, 3, 256, 384, False), (1, 2, 200, 200, True),
+                                               (2, 2, 130, 333, False), (1, 4, 384, 512, True), (1, 1, 77, 77, True)])
+def test_blockwise_attention_backward_matches_fp32_reference(B, H, Sq, Skv, causal):
+    """dQ, dK, dV of the blockwise tcgen05 kernels (probabilities recomputed tile by tile from the saved row
+    log-sum-exp) against PyTorch autograd in fp32 on the same bf16 operands: ragged sequence lengths, more keys than
+    queries, causal masks with the diagonal inside a tile, head-interleaved (strided) operand views."""
+    from ferrum_b200.ops import functional as F
+    from ferrum_b200.utils.runtime import check_status
+
+    torch.manual_seed(B * 100 + Sq + Skv)
+    D = 64
+    # operands as MultiHeadAttention produces them: [B, S, H * D] projections viewed as [B, H, S, D]
+    q, k, v = (torch.randn(B, S, H * D, device="cuda").bfloat16().view(B, S, H, D).permute(0, 2, 1, 3)
+               .requires_grad_(True) for S in (Sq, Skv, Skv))
+    scale = 1.0 / math.sqrt(D)
+    out = F.attention_blockwise(q, k, v, scale, causal=causal)
+    go = torch.randn(B, H, Sq, D, device="cuda").bfloat16()
+    gq, gk, gv = torch.autograd.grad(out, (q, k, v), go)
+    check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    s = torch.matmul(qr, kr.transpose(-1, -2)) * scale
+    if causal:
+        i = torch.arange(Sq, device="cuda")[:, None]
+        j = torch.arange(Skv, device="cuda")[None, :]
+        s = s.masked_fill(j > i + (Skv - Sq), float("-inf"))
+    ref = torch.matmul(torch.softmax(s, -1), vr)
+    rq, rk, rv = torch.autograd.grad(ref, (qr, kr, vr), go.float())
+    assert _rel(out, ref) < 1e-2
+    assert gq.shape == q.shape and gk.shape == k.shape and gv.shape == v.shape
+    assert _rel(gq, rq) < 2e-2, _rel(gq, rq)
+    assert _rel(gk, rk) < 2e-2, _rel(gk, rk)
+    assert _rel(gv, rv) < 2e-2, _rel(gv, rv)
+
+
+def test_multi_head_attention_trains_through_the_blockwise_kernels():
+    """Under autocast with head dimension 64 the module's training step uses the blockwise forward and backward
+    (no S x S tensor is created); gradients of every projection agree with the fp32 reference module."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import _lib
+    from ferrum_b200.nn import MultiHeadAttention
+
+    torch.manual_seed(8)
+    B, S, E, H = 2, 256, 256, 4
+    mha = MultiHeadAttention(E, H, device=fb.Device.Cuda(0))
+    x = torch.randn(B, S, E, device="cuda", requires_grad=True)
+    calls = []
+    lib = _lib.cuda()
+    orig = lib.fb_attention_bwd
+    try:
+        lib.fb_attention_bwd = lambda *a: (calls.append(1), orig(*a))[1]
+        with fb.autocast():
+            y = mha.forward_attn(x, x, x, causal=True)
+        y.float().square().mean().backward()
+    finally:
+        lib.fb_attention_bwd = orig
+    assert calls, "the blockwise backward kernel was not used"
+    ref = torch.nn.MultiheadAttention(E, H, batch_first=True, device="cuda")
+    with torch.no_grad():
+        ref.in_proj_weight.copy_(torch.cat([mha.q_proj.weight, mha.k_proj.weight, mha.v_proj.weight]))
+        ref.in_proj_bias.copy_(torch.cat([mha.q_proj.bias, mha.k_proj.bias, mha.v_proj.bias]))
+        ref.out_proj.weight.copy_(mha.out_proj.weight)
+        ref.out_proj.bias.copy_(mha.out_proj.bias)
+    xr = x.detach().clone().requires_grad_(True)
+    cm = torch.triu(torch.ones(S, S, device="cuda", dtype=torch.bool), 1)
+    yr, _ = ref(xr, xr, xr, attn_mask=cm, need_weights=False)
+    yr.square().mean().backward()
+    assert _rel(y, yr) < 2e-2
+    assert _rel(x.grad, xr.grad) < 4e-2
+    gw = torch.cat([mha.q_proj.weight.grad, mha.k_proj.weight.grad, mha.v_proj.weight.grad])
+    assert _rel(gw, ref.in_proj_weight.grad) < 4e-2

@@ -47,6 +47,36 @@ def test_allreduce_average_emulated(world, n):
         a.close()
 
 
+@pytest.mark.parametrize("world,n,blocks", [(2, 1000, 1), (4, 4097, 5), (8, 65536, 16), (3, 1, 1)])
+@pytest.mark.parametrize("op", [0, 3, 4])
+def test_oneshot_allreduce_emulated(world, n, blocks, op):
+    """Latency form of the all-reduce: one handshake, every rank reads all regions and reduces for itself.  Four
+    calls in a row alternate between the two slots (no exit handshake protects a slot: its reuse is safe only
+    because a whole collective lies between two uses), sum / max / average, tensors that are their own output."""
+    from ferrum_b200.utils.runtime import check_status
+
+    slot_bytes = (n * 4 + 255) // 256 * 256
+    lib, arenas, ctxs = _setup(world, 2 * slot_bytes // 4 + 64)
+    off = arenas[0].data_offset()
+    torch.manual_seed(world * 7 + n + op)
+    epoch = 1
+    for call in range(4):
+        data = [torch.randn(n, device="cuda") for _ in range(world)]
+        stack = torch.stack([d.clone() for d in data])
+        ref = stack.max(0).values if op == 3 else stack.sum(0) / (world if op == 4 else 1)
+        ptrs = (ctypes.c_void_p * world)(*[d.data_ptr() for d in data])
+        rc = lib.fb_dist_allreduce_oneshot_emulated(ctxs, world, 0, epoch, off + (call % 2) * slot_bytes, n, op,
+                                                    1.0 / world if op == 4 else 1.0, ptrs, ptrs, blocks, 256,
+                                                    _stream())
+        assert rc == 0
+        epoch += 2
+        check_status()
+        for d in data:
+            assert torch.allclose(d, ref, atol=1e-5, rtol=1e-5)
+    for a in arenas:
+        a.close()
+
+
 @pytest.mark.parametrize("world,n_valid,offset", [(2, 8000, 0), (4, 4097, 0), (8, 333, 1), (3, 1, 3)])
 def test_staged_allreduce_emulated(world, n_valid, offset):
     """All-reduce of tensors that live outside the arena: the kernel stages them in and out itself (ragged
@@ -419,9 +449,11 @@ def test_sharded_master_weights_and_inplace_all_gather_emulated():
         a.close()
 
 
-def test_single_rank_engine_overlaps_optimizer_and_matches_plain_training():
-    """World size 1 with a fused optimizer: the per-bucket update kernels run behind each weight gradient on the
-    side stream; the trajectory must equal plain Adam / SGD on the same model."""
+@pytest.mark.parametrize("schedule", ["update after backward", "update in backward", "single kernel"])
+def test_single_rank_engine_overlaps_optimizer_and_matches_plain_training(schedule):
+    """World size 1 with a fused optimizer, in the engine's three schedules (one update kernel after backward,
+    an update kernel per bucket behind each weight gradient, the single all-reduce + update kernel per bucket);
+    the trajectory must equal plain Adam / SGD on the same model."""
     import copy
 
     import ferrum_b200 as fb
@@ -440,6 +472,10 @@ def test_single_rank_engine_overlaps_optimizer_and_matches_plain_training():
         pg = ProcessGroup(Backend.Nvlink, 0, 1)
         eng = DistributedDataParallel(eng_model, pg).bucket_size_mb(0.1)
         eng.fuse_optimizer(opt_eng)
+        if schedule == "update in backward":
+            eng.update_in_backward(True)
+        elif schedule == "single kernel":
+            eng.defer_update(False)
         x = torch.randn(96, 64, device="cuda")
         y = torch.randint(0, 10, (96,), device="cuda")
         for step in range(4):
