@@ -88,12 +88,15 @@ __device__ __forceinline__ void store_chunk(uint8_t* mat, int row, int c, const 
   }
 }
 
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row) {
+// One 64-column accumulator row from tensor memory to 64 bf16 in global memory.  The tensor-memory loads are
+// warp-wide (.sync.aligned): EVERY lane of the warp must call this, `valid` only predicates the stores.
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row, bool valid) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     uint32_t r[32];
     ptx::tmem_ld_32x32b_x32(tmem_row + c * 32, r);
     ptx::tmem_wait_ld();
+    if (!valid) continue;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t w[4];
@@ -270,12 +273,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const bool done = n_tiles > 0 ? ptx::mbar_wait(dq_full, 0, abort_flag, p.timeout_ns) : true;
       if (!__all_sync(0xffffffffu, done)) {
         if (lane == 0) report_status(p.status, kStatusGemmTimeout, 67, blockIdx.x, 0);
-      } else if (qrow < p.Sq) {
+      } else {
         ptx::tc_fence_after();
         __nv_bfloat16* dst = p.dq + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * kD;
-        if (n_tiles > 0) {
-          store_row_bf16(dst, t_dq + t_row);
-        } else {
+        if (n_tiles > 0) {  // uniform over the CTA
+          store_row_bf16(dst, t_dq + t_row, qrow < p.Sq);
+        } else if (qrow < p.Sq) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) reinterpret_cast<uint4*>(dst)[q] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -469,26 +472,25 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(pt_full);
     }
-    if (ok && krow < p.Skv) {
+    if (n_iter == 0 && krow < p.Skv) {  // no query sees these keys
       __nv_bfloat16* dv = p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
       __nv_bfloat16* dk = p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
-      if (n_iter == 0) {  // no query sees these keys
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          reinterpret_cast<uint4*>(dv)[q] = make_uint4(0u, 0u, 0u, 0u);
-          reinterpret_cast<uint4*>(dk)[q] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        ok = false;
+      for (int q = 0; q < 8; ++q) {
+        reinterpret_cast<uint4*>(dv)[q] = make_uint4(0u, 0u, 0u, 0u);
+        reinterpret_cast<uint4*>(dk)[q] = make_uint4(0u, 0u, 0u, 0u);
       }
     }
-    if (n_iter > 0 && ok) {
+    if (n_iter > 0 && ok) {  // both uniform over the warp
       const bool done = ptx::mbar_wait(acc_full, 0, abort_flag, p.timeout_ns);
       if (!__all_sync(0xffffffffu, done)) {
         if (lane == 0) report_status(p.status, kStatusGemmTimeout, 77, blockIdx.x, 0);
-      } else if (krow < p.Skv) {
+      } else {
         ptx::tc_fence_after();
-        store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dv + t_row);
-        store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dk + t_row);
+        store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dv + t_row,
+                       krow < p.Skv);
+        store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dk + t_row,
+                       krow < p.Skv);
       }
     }
   }
