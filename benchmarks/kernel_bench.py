@@ -160,6 +160,22 @@ def _cases(small: bool):
          "K16 (batched tcgen05 QK^T, row softmax, batched PV; bytes = score matrix written + read twice + q, k, v, o)")
     case("attention_flash_fwd_bf16_S1024_D64", lambda: F.flash_attention(qa, ka, va, Da ** -0.5),
          4 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 attention (bytes = q, k, v, o only)")
+    # backward alone: the forward runs once, each timed call differentiates the saved graph again
+    go = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)  # laid out like the outputs
+    import ferrum_b200 as fb
+
+    qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (qa, ka, va))
+    with fb.autocast():
+        out_mat = F.bmm_scaled(F.softmax(F.bmm_scaled(qg, kg.transpose(-1, -2), Da ** -0.5), -1), vg, 1.0,
+                               heads_inner=True)
+    out_blk = F.attention_blockwise(qg, kg, vg, Da ** -0.5)
+    case("attention_bwd_materialised_bf16_S1024_D64",
+         lambda: torch.autograd.grad(out_mat, (qg, kg, vg), go, retain_graph=True),
+         Ba * Ha * Sa * Sa * 2 * 6 + 8 * Ba * Ha * Sa * Da * 2,
+         "K16 backward through the stored S x S probabilities (batched GEMMs + softmax backward)")
+    case("attention_bwd_blockwise_bf16_S1024_D64",
+         lambda: torch.autograd.grad(out_blk, (qg, kg, vg), go, retain_graph=True),
+         8 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 backward (bytes = q, k, v, o, dO, dq, dk, dv only)")
     return cases
 
 
