@@ -11,6 +11,15 @@ embedding  vocab 50000, dim 1024, 256 token ids ~ Zipf(1.1) per sample, mean-poo
            cosine LR schedule, per-GPU batch 512.
 
 Prints one JSON line (rank 0): samples/s over K timed steps (CUDA events, max over ranks), synthetic seeded data.
+
+    python bench_configs.py --impl cpu_ref --config xor|mnist|wide_mlp [--steps K]
+
+``--impl cpu_ref`` times the reference's CPU arithmetic (no GPU needed): for ``xor`` the reference's own prebuilt
+``train_xor`` binary when it is present beside the sources, else the restated loop; for ``mnist`` and ``wide_mlp``
+the restated loops of ``csrc/host/cpu_ref.cpp`` (the naive triple-loop matmul of ferrum-core/src/tensor.rs:2487-2558
+for the forward, data-gradient and weight-gradient products of every Linear, the row-wise LayerNorm / softmax loops
+and the Adam loop of ferrum-optim/src/adam.rs:91-146), single thread, at a stated REDUCED size for ``wide_mlp``
+(the full 8 x 4096, batch 8192 step is 6.2 TFLOP: hours per step on these loops).
 """
 from __future__ import annotations
 
@@ -20,10 +29,110 @@ import os
 import sys
 
 
+def cpu_ref(a):
+    """Reference-CPU arm: see the module docstring.  Prints one JSON line."""
+    import ctypes
+    import subprocess
+    import time
+
+    import numpy as np
+
+    from ferrum_b200 import _lib
+
+    lib = _lib.host()
+    fp = ctypes.POINTER(ctypes.c_float)
+
+    def ptr(x):
+        return x.ctypes.data_as(ctypes.c_void_p)
+
+    if a.config == "xor":
+        exe = "/root/reference/target/release/examples/train_xor"
+        if os.path.exists(exe):
+            ts = []
+            for _ in range(10):
+                t0 = time.perf_counter()
+                subprocess.run([exe], capture_output=True, check=True)
+                ts.append(time.perf_counter() - t0)
+            ts.sort()
+            print(json.dumps({"config": "xor", "impl": "cpu_ref", "what": "the reference's prebuilt train_xor binary, "
+                              "whole process, 2000 full-batch epochs of 4 samples", "wall_ms_median": 1e3 * ts[5],
+                              "wall_ms_min": 1e3 * ts[0], "samples_per_s": 2000 * 4 / ts[5]}))
+            return 0
+        H, epochs = 8, 2000
+        rng = np.random.default_rng(0)
+        w1, b1 = rng.standard_normal((H, 2)).astype(np.float32), np.zeros(H, np.float32)
+        w2, b2 = rng.standard_normal((1, H)).astype(np.float32), np.zeros(1, np.float32)
+        losses = np.zeros(epochs, np.float32)
+        t0 = time.perf_counter()
+        lib.fb_ref_train_xor(ptr(w1), ptr(b1), ptr(w2), ptr(b2), H, 1.0, epochs, 0, ptr(losses))
+        dt = time.perf_counter() - t0
+        print(json.dumps({"config": "xor", "impl": "cpu_ref", "what": "restated train_xor loop (no reference binary "
+                          "on this machine)", "wall_ms": 1e3 * dt, "samples_per_s": epochs * 4 / dt,
+                          "final_loss": float(losses[-1])}))
+        return 0
+
+    # (in, width, depth, classes, batch): mnist is the real size, wide_mlp a reduced one
+    cfg = {"mnist": (784, 256, 1, 10, 128), "wide_mlp": (128, 512, 4, 100, 64)}[a.config]
+    d_in, width, depth, classes, batch = cfg
+    rng = np.random.default_rng(0)
+    dims = [d_in] + [width] * depth + [classes]
+    Ws = [rng.standard_normal((dims[i + 1], dims[i])).astype(np.float32) * 0.05 for i in range(len(dims) - 1)]
+    Bs = [np.zeros(dims[i + 1], np.float32) for i in range(len(dims) - 1)]
+    Ms = [np.zeros_like(w) for w in Ws]
+    Vs = [np.zeros_like(w) for w in Ws]
+    gam, bet = np.ones(width, np.float32), np.zeros(width, np.float32)
+    x = rng.standard_normal((batch, d_in)).astype(np.float32)
+    steps = max(1, min(a.steps, 5))
+    flops = 0
+
+    def step(t):
+        nonlocal flops
+        acts, h = [x], x
+        for i, (w, b) in enumerate(zip(Ws, Bs)):
+            y = np.empty((batch, w.shape[0]), np.float32)
+            lib.fb_ref_linear(ptr(h), ptr(w), ptr(b), ptr(y), batch, w.shape[1], w.shape[0])
+            flops += 2 * batch * w.size
+            if i < len(Ws) - 1:
+                y = np.maximum(y, 0.0, out=y)           # activation: elementwise, negligible beside the products
+                n = np.empty_like(y)
+                lib.fb_ref_layernorm_rows(ptr(y), ptr(gam), ptr(bet), ptr(n), batch, width, 1e-5)
+                y = n
+            acts.append(y)
+            h = y
+        p = np.empty_like(h)
+        lib.fb_ref_softmax_rows(ptr(h), ptr(p), batch, classes, 0)
+        g = p / batch                                   # gradient of the mean cross-entropy up to the one-hot term
+        for i in reversed(range(len(Ws))):
+            w = Ws[i]
+            gw = np.empty_like(w)
+            gt = np.ascontiguousarray(g.T)
+            lib.fb_ref_matmul(ptr(gt), ptr(acts[i]), ptr(gw), w.shape[0], batch, w.shape[1])      # weight gradient
+            flops += 2 * batch * w.size
+            if i > 0:
+                gx = np.empty((batch, w.shape[1]), np.float32)
+                lib.fb_ref_matmul(ptr(g), ptr(w), ptr(gx), batch, w.shape[0], w.shape[1])        # data gradient
+                flops += 2 * batch * w.size
+                g = gx
+            lib.fb_ref_adam_step(ptr(w), ptr(gw), ptr(Ms[i]), ptr(Vs[i]), w.size, 1e-3, 0.9, 0.999, 1e-8, 0.0, t)
+
+    step(1)
+    flops = 0
+    t0 = time.perf_counter()
+    for t in range(steps):
+        step(t + 2)
+    dt = time.perf_counter() - t0
+    print(json.dumps({"config": a.config, "impl": "cpu_ref", "what": "restated reference loops (naive matmul x3 per "
+                      "Linear, LayerNorm, softmax, Adam), one thread", "model": {"in": d_in, "width": width,
+                      "depth": depth, "classes": classes, "batch": batch}, "reduced_size": a.config == "wide_mlp",
+                      "steps": steps, "ms_per_step": 1e3 * dt / steps, "samples_per_s": steps * batch / dt,
+                      "gflops": flops / dt / 1e9}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True, choices=["mnist", "embedding"])
-    ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
+    ap.add_argument("--config", required=True, choices=["mnist", "embedding", "xor", "wide_mlp"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch", "cpu_ref"])
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--bf16", action="store_true", help="bf16 tensor-core GEMMs (default for embedding)")
@@ -31,6 +140,13 @@ def main():
                     help="ours (any config, any number of GPUs): record the step (zero_grad, forward, backward, Adam) in a CUDA graph and "
                          "replay it (the batch fetch and the LR schedule stay outside)")
     a = ap.parse_args()
+    if a.impl == "cpu_ref":
+        if a.config == "embedding":
+            raise SystemExit("--impl cpu_ref covers xor, mnist and wide_mlp")
+        return cpu_ref(a)
+    if a.config in ("xor", "wide_mlp"):
+        raise SystemExit(f"--config {a.config} is a --impl cpu_ref configuration (the GPU arms are mnist, embedding; "
+                         "the wide MLP is bench.py)")
 
     import torch
 

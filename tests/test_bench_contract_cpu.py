@@ -43,3 +43,15 @@ def test_flags_and_defaults():
         assert not a.no_baseline and a.dataset_batches >= 2 and a.loader_workers >= 1
     finally:
         sys.argv = argv
+
+
+def test_reference_cpu_arm_of_the_secondary_benchmarks():
+    """``bench_configs.py --impl cpu_ref`` needs no GPU: it times the restated reference loops (reduced size for the
+    wide MLP) and prints one JSON line per configuration."""
+    for cfg in ("wide_mlp", "mnist"):
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bench_configs.py"), "--impl", "cpu_ref", "--config",
+                            cfg, "--steps", "1"], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        rec = json.loads(r.stdout.strip().splitlines()[-1])
+        assert rec["impl"] == "cpu_ref" and rec["samples_per_s"] > 0 and rec["gflops"] > 0
+        assert rec["reduced_size"] == (cfg == "wide_mlp")
