@@ -22,6 +22,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=float, default=256.0)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--registered", action="store_true",
+                    help="also time all_reduce / broadcast / all_gather on tensors from ProcessGroup.symmetric_empty "
+                         "(in place on the peers' mappings, no staging pass; NCCL gets ordinary tensors)")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
 
@@ -78,6 +81,17 @@ def main():
         outs = [torch.empty(n, device="cuda") for _ in range(world)]
         report("all_gather", nbytes, timed(lambda: ours.all_gather(outs, x)), timed(lambda: nccl.all_gather(outs, x)),
                float((world - 1) * nbytes))
+        if args.registered:
+            xr = ours.symmetric_empty((n,))
+            xr.copy_(x)
+            report("all_reduce (registered)", nbytes, timed(lambda: ours.all_reduce(xr, d.ReduceOp.Sum)),
+                   timed(lambda: nccl.all_reduce(x, d.ReduceOp.Sum)), 2.0 * (world - 1) / world * nbytes)
+            report("broadcast (registered)", nbytes, timed(lambda: ours.broadcast(xr, 0)),
+                   timed(lambda: nccl.broadcast(x, 0)), float(nbytes))
+            one = torch.empty(world * n, device="cuda")
+            outs1 = list(one.view(world, n).unbind(0))
+            report("all_gather (registered input)", nbytes, timed(lambda: ours.all_gather(outs1, xr)),
+                   timed(lambda: nccl.all_gather(outs1, x)), float((world - 1) * nbytes))
         chunk = max(n // world, 1)
         ins = [torch.randn(chunk, device="cuda") for _ in range(world)]
         o = torch.empty(chunk, device="cuda")

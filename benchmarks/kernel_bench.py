@@ -160,22 +160,26 @@ def _cases(small: bool):
          "K16 (batched tcgen05 QK^T, row softmax, batched PV; bytes = score matrix written + read twice + q, k, v, o)")
     case("attention_flash_fwd_bf16_S1024_D64", lambda: F.flash_attention(qa, ka, va, Da ** -0.5),
          4 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 attention (bytes = q, k, v, o only)")
-    # backward alone: the forward runs once, each timed call differentiates the saved graph again
+    # training direction: forward + backward of the attention core, gradients with respect to q, k, v
     go = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)  # laid out like the outputs
     import ferrum_b200 as fb
 
     qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (qa, ka, va))
-    with fb.autocast():
-        out_mat = F.bmm_scaled(F.softmax(F.bmm_scaled(qg, kg.transpose(-1, -2), Da ** -0.5), -1), vg, 1.0,
-                               heads_inner=True)
-    out_blk = F.attention_blockwise(qg, kg, vg, Da ** -0.5)
-    case("attention_bwd_materialised_bf16_S1024_D64",
-         lambda: torch.autograd.grad(out_mat, (qg, kg, vg), go, retain_graph=True),
-         Ba * Ha * Sa * Sa * 2 * 6 + 8 * Ba * Ha * Sa * Da * 2,
-         "K16 backward through the stored S x S probabilities (batched GEMMs + softmax backward)")
-    case("attention_bwd_blockwise_bf16_S1024_D64",
-         lambda: torch.autograd.grad(out_blk, (qg, kg, vg), go, retain_graph=True),
-         8 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 backward (bytes = q, k, v, o, dO, dq, dk, dv only)")
+
+    def attn_train_materialised():
+        with fb.autocast():
+            p_ = F.softmax(F.bmm_scaled(qg, kg.transpose(-1, -2), Da ** -0.5), -1)
+            out = F.bmm_scaled(p_, vg, 1.0, heads_inner=True)
+            return torch.autograd.grad(out, (qg, kg, vg), go)
+
+    def attn_train_blockwise():
+        return torch.autograd.grad(F.attention_blockwise(qg, kg, vg, Da ** -0.5), (qg, kg, vg), go)
+
+    case("attention_fwd_bwd_materialised_bf16_S1024_D64", attn_train_materialised,
+         Ba * Ha * Sa * Sa * 2 * 10 + 12 * Ba * Ha * Sa * Da * 2,
+         "K16 forward + backward through the stored S x S probabilities (batched GEMMs, softmax and its backward)")
+    case("attention_fwd_bwd_blockwise_bf16_S1024_D64", attn_train_blockwise, 12 * Ba * Ha * Sa * Da * 2,
+         "K16 blockwise tcgen05 forward + backward (bytes = q, k, v, o, dO, dq, dk, dv and the re-read operands)")
     return cases
 
 
@@ -199,8 +203,12 @@ def main():
     for name, (fn, nbytes, note) in cases.items():
         if only and name not in only:
             continue
-        for _ in range(a.warmup):
-            fn()
+        try:
+            for _ in range(a.warmup):
+                fn()
+        except Exception as exc:  # noqa: BLE001 - report and go on with the other kernels
+            print(json.dumps({"kernel": name, "error": f"{type(exc).__name__}: {exc}"}), flush=True)
+            continue
         ts = []
         for _ in range(a.iters):
             flush.zero_()

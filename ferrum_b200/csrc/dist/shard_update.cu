@@ -130,9 +130,18 @@ struct EmuUp {
   int blocks_per_rank;
 };
 
+constexpr int kMaxUpBuckets = 256;  // rows of the bucket table one launch can take (kept in shared memory)
+
+// The shards of all buckets form ONE index space of float4 positions (bucket after bucket), walked with a grid
+// stride: a bucket whose shard is smaller than the grid (biases, normalisation parameters; every bucket once the
+// world is large) then costs no trip of its own, and no trip ends with most of the grid idle.
 template <int FUSE, bool MC, int U>
 __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, const UpArgs& a, float* m_base,
                             float* v_base, int* s_fail) {
+  __shared__ long long s_pre[kMaxUpBuckets + 1];  // first position of bucket k in the joint index space
+  __shared__ long long s_e4[kMaxUpBuckets];       // first float4 of the rank's shard inside a region
+  __shared__ long long s_so4[kMaxUpBuckets];      // first float4 of the shard inside m / v
+  __shared__ unsigned char s_pub[kMaxUpBuckets];  // 1: fp32 values go to every rank
   const uint32_t epoch = a.dev_epoch != nullptr ? *a.dev_epoch : a.epoch;
   fb_adam_hparams adam = a.adam;
   fb_sgd_hparams sgd = a.sgd;
@@ -142,67 +151,81 @@ __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, cons
     adam.bias_corr2 = a.dyn[2];
     sgd.lr = a.dyn[0];
   }
-  if (!block_handshake(c, a.channel, vblock, epoch, s_fail, 410)) return;
-  const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
-  unsigned char* self = c.arena[c.rank];
-  for (int k = 0; k < a.nbuckets; ++k) {
-    const long long start = a.table[4 * k], len = a.table[4 * k + 1], soff = a.table[4 * k + 2];
-    const bool publish_master = a.table[4 * k + 3] != 0;  // 0: peers only need the bf16 copy, the owner keeps fp32
+  for (int k = threadIdx.x; k < a.nbuckets; k += blockDim.x) {
+    const long long start = a.table[4 * k], len = a.table[4 * k + 1];
     long long lo, hi;
     shard_bounds(len, c.world, c.rank, lo, hi);
-    const long long n4 = (hi - lo) >> 2;
-    const long long e4 = (start + lo) >> 2;  // first float4 of the shard inside a region
-    const float4* gp = reinterpret_cast<const float4*>(self + a.grad_off) + e4;
-    float4* pp = reinterpret_cast<float4*>(self + a.param_off) + e4;
-    float4* mp = reinterpret_cast<float4*>(m_base + soff);
-    float4* vp = reinterpret_cast<float4*>(v_base + soff);
-    for (long long base = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; base < n4; base += stride * U) {
-      float4 g[U], p[U], m[U], v[U];
+    s_pre[k + 1] = (hi - lo) >> 2;  // lengths first, summed below
+    s_e4[k] = (start + lo) >> 2;
+    s_so4[k] = a.table[4 * k + 2] >> 2;
+    s_pub[k] = a.table[4 * k + 3] != 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_pre[0] = 0;
+    for (int k = 0; k < a.nbuckets; ++k) s_pre[k + 1] += s_pre[k];
+  }
+  if (!block_handshake(c, a.channel, vblock, epoch, s_fail, 410)) return;  // (its barriers publish the table)
+  const long long total4 = s_pre[a.nbuckets];
+  const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
+  unsigned char* self = c.arena[c.rank];
+  const float4* gp = reinterpret_cast<const float4*>(self + a.grad_off);
+  float4* pp = reinterpret_cast<float4*>(self + a.param_off);
+  float4* mp = reinterpret_cast<float4*>(m_base);
+  float4* vp = reinterpret_cast<float4*>(v_base);
+  int cur = 0;  // bucket of this thread's first position of the trip; positions only grow
+  for (long long base = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; base < total4; base += stride * U) {
+    float4 g[U], p[U], m[U], v[U];
+    long long ri[U], si[U];  // float4 index inside a region / inside the moments
+    bool pub[U];
+    int bk = cur;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long i4 = base + u * stride;
-        if (i4 < n4) {
-          g[u] = __ldcs(gp + i4);
-          p[u] = pp[i4];
-          m[u] = (FUSE == FB_FUSE_ADAM || m_base != nullptr) ? __ldcs(mp + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          if (FUSE == FB_FUSE_ADAM) v[u] = __ldcs(vp + i4);
-        }
+    for (int u = 0; u < U; ++u) {
+      const long long i4 = base + u * stride;
+      if (i4 < total4) {
+        while (i4 >= s_pre[bk + 1]) ++bk;
+        if (u == 0) cur = bk;
+        const long long j = i4 - s_pre[bk];
+        ri[u] = s_e4[bk] + j;
+        si[u] = s_so4[bk] + j;
+        pub[u] = s_pub[bk] != 0;
+        g[u] = __ldcs(gp + ri[u]);
+        p[u] = pp[ri[u]];
+        m[u] = (FUSE == FB_FUSE_ADAM || m_base != nullptr) ? __ldcs(mp + si[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (FUSE == FB_FUSE_ADAM) v[u] = __ldcs(vp + si[u]);
       }
+    }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long i4 = base + u * stride;
-        if (i4 >= n4) continue;
-        if (FUSE == FB_FUSE_ADAM) {
-          adam1(p[u].x, g[u].x, m[u].x, v[u].x, adam);
-          adam1(p[u].y, g[u].y, m[u].y, v[u].y, adam);
-          adam1(p[u].z, g[u].z, m[u].z, v[u].z, adam);
-          adam1(p[u].w, g[u].w, m[u].w, v[u].w, adam);
-          __stcs(mp + i4, m[u]);
-          __stcs(vp + i4, v[u]);
-        } else {
-          sgd1(p[u].x, g[u].x, m[u].x, sgd);
-          sgd1(p[u].y, g[u].y, m[u].y, sgd);
-          sgd1(p[u].z, g[u].z, m[u].z, sgd);
-          sgd1(p[u].w, g[u].w, m[u].w, sgd);
-          if (m_base != nullptr) __stcs(mp + i4, m[u]);
-        }
-        uint2 sh;
-        *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p[u].x, p[u].y);
-        *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p[u].z, p[u].w);
-        if (!publish_master) pp[i4] = p[u];
-        if (MC) {
-          if (publish_master)
-            ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + e4 + i4, p[u]);
+    for (int u = 0; u < U; ++u) {
+      if (base + u * stride >= total4) continue;
+      if (FUSE == FB_FUSE_ADAM) {
+        adam1(p[u].x, g[u].x, m[u].x, v[u].x, adam);
+        adam1(p[u].y, g[u].y, m[u].y, v[u].y, adam);
+        adam1(p[u].z, g[u].z, m[u].z, v[u].z, adam);
+        adam1(p[u].w, g[u].w, m[u].w, v[u].w, adam);
+        __stcs(mp + si[u], m[u]);
+        __stcs(vp + si[u], v[u]);
+      } else {
+        sgd1(p[u].x, g[u].x, m[u].x, sgd);
+        sgd1(p[u].y, g[u].y, m[u].y, sgd);
+        sgd1(p[u].z, g[u].z, m[u].z, sgd);
+        sgd1(p[u].w, g[u].w, m[u].w, sgd);
+        if (m_base != nullptr) __stcs(mp + si[u], m[u]);
+      }
+      uint2 sh;
+      *reinterpret_cast<__nv_bfloat162*>(&sh.x) = __floats2bfloat162_rn(p[u].x, p[u].y);
+      *reinterpret_cast<__nv_bfloat162*>(&sh.y) = __floats2bfloat162_rn(p[u].z, p[u].w);
+      if (!pub[u]) pp[ri[u]] = p[u];  // the owner keeps the fp32 master; peers only need the bf16 copy
+      if (MC) {
+        if (pub[u]) ptx::multimem_st_f4(reinterpret_cast<float4*>(c.mc_arena + a.param_off) + ri[u], p[u]);
+        if (a.shadow_off >= 0)
+          ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + ri[u],
+                              make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
+      } else {
+        for (int r = 0; r < c.world; ++r) {
+          if (pub[u]) ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + ri[u], p[u]);
           if (a.shadow_off >= 0)
-            ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + e4 + i4,
-                                make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
-        } else {
-          for (int r = 0; r < c.world; ++r) {
-            if (publish_master)
-              ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + e4 + i4, p[u]);
-            if (a.shadow_off >= 0)
-              ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + e4 + i4, sh);
-          }
+            ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + ri[u], sh);
         }
       }
     }
@@ -290,7 +313,8 @@ extern "C" int fb_dist_shard_update(const fb_dist_ctx* ctx, int fuse, int use_mc
                                     long long shadow_off, const long long* table, int nbuckets,
                                     const fb_adam_hparams* adam, const fb_sgd_hparams* sgd, float* m, float* v,
                                     int nblocks, int nthreads, const float* dyn, cudaStream_t stream) {
-  if (!launch_ok(ctx, channel, nblocks, nthreads) || table == nullptr || nbuckets < 1) return -1;
+  if (!launch_ok(ctx, channel, nblocks, nthreads) || table == nullptr || nbuckets < 1 || nbuckets > kMaxUpBuckets)
+    return -1;
   if ((grad_off & 15) || (param_off & 15) || (shadow_off >= 0 && (shadow_off & 7))) return -1;
   if (use_mc && ctx->mc_arena == nullptr) return -2;
   UpArgs a{};
@@ -349,8 +373,8 @@ extern "C" int fb_dist_shard_update_emulated(const fb_dist_ctx* ctxs, int world,
                                              const fb_adam_hparams* adam, const fb_sgd_hparams* sgd,
                                              float* const* m, float* const* v, int nblocks, int nthreads,
                                              cudaStream_t stream) {
-  if (world < 1 || world > FB_MAX_RANKS || table == nullptr || nbuckets < 1 || nblocks < 1 ||
-      nblocks > FB_FLAG_BLOCKS)
+  if (world < 1 || world > FB_MAX_RANKS || table == nullptr || nbuckets < 1 || nbuckets > kMaxUpBuckets ||
+      nblocks < 1 || nblocks > FB_FLAG_BLOCKS)
     return -1;
   EmuUp pk{};
   for (int r = 0; r < world; ++r) {
