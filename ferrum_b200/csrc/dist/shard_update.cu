@@ -222,10 +222,13 @@ __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, cons
           ptx::multimem_st_f2(reinterpret_cast<float2*>(c.mc_arena + a.shadow_off) + ri[u],
                               make_float2(__uint_as_float(sh.x), __uint_as_float(sh.y)));
       } else {
+        // Plain (weak) stores, to the peers' memory too: the exit handshake orders them.  Its barrier makes every
+        // store of the block happen before the flag writers' fence.sys, which is cumulative, and only then is
+        // the flag released; a reader that has seen all flags therefore sees all data.  (Measured level with
+        // st.relaxed.sys stores on one and two GPUs; the weak form leaves the hardware free to combine them.)
         for (int r = 0; r < c.world; ++r) {
-          if (pub[u]) ptx::st_relaxed_sys_f4(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + ri[u], p[u]);
-          if (a.shadow_off >= 0)
-            ptx::st_relaxed_sys_u2(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + ri[u], sh);
+          if (pub[u]) *(reinterpret_cast<float4*>(c.arena[r] + a.param_off) + ri[u]) = p[u];
+          if (a.shadow_off >= 0) *(reinterpret_cast<uint2*>(c.arena[r] + a.shadow_off) + ri[u]) = sh;
         }
       }
     }
