@@ -6,6 +6,10 @@
 // Two kernels, both shaped like the forward kernel (same operand layouts, same roles), so that neither needs an
 // atomic or a cross-CTA reduction:
 //
+// Roles of a CTA (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 the elementwise work — two
+// warps per tensor-memory lane quarter, each taking 64 of a tile's 128 columns, because that work (two
+// tensor-memory reads, an exponential and half a dozen multiply-adds per score) and not the MMAs bounds a tile.
+//
 //   attn_bwd_dq_kernel    a CTA owns 128 query rows and walks the key / value tiles:
 //                           S = Q K_j^T, dP = dO V_j^T            (tensor memory, 2 x 128 columns)
 //                           dS = P * (dP - delta) * scale          (thread = query row; bf16 into shared memory)
@@ -36,9 +40,10 @@ constexpr int kD = 64;
 constexpr int kT = 128;                     // rows of a query tile = rows of a key tile
 constexpr int kTile = kT * kD * 2;          // 16 KB: 128 rows of 64 bf16
 constexpr int kPBytes = 2 * kTile;          // a 128 x 128 bf16 matrix: two k-blocks of 128 rows x 128 bytes
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;            // TMA warp, MMA warp, eight softmax warps
+constexpr int kSoftmaxWarps = 8;            // two per tensor-memory lane quarter, 64 of the tile's 128 columns each
 constexpr int kSmemDq = 2 * kTile + 2 * kTile + 2 * kTile + kPBytes + 1024 + 256;           // Q dO | K x2 | V x2 | dS
-constexpr int kSmemDkv = 2 * kTile + 2 * kTile + 2 * kTile + 2 * kPBytes + 4096 + 1024 + 256;  // K V | Q x2 | dO x2 | P^T dS^T | lse, delta
+constexpr int kSmemDkv = 2 * kTile + 2 * kTile + 2 * kTile + 2 * kPBytes + 8192 + 1024 + 256;  // K V | Q x2 | dO x2 | P^T dS^T | lse, delta
 constexpr int kTmemBwd = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -90,9 +95,10 @@ __device__ __forceinline__ void store_chunk(uint8_t* mat, int row, int c, const 
 
 // One 64-column accumulator row from tensor memory to 64 bf16 in global memory.  The tensor-memory loads are
 // warp-wide (.sync.aligned): EVERY lane of the warp must call this, `valid` only predicates the stores.
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row, bool valid) {
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row, bool valid, int c_lo = 0,
+                                               int c_hi = 2) {
+#pragma unroll 1
+  for (int c = c_lo; c < c_hi; ++c) {
     uint32_t r[32];
     ptx::tmem_ld_32x32b_x32(tmem_row + c * 32, r);
     ptx::tmem_wait_ld();
@@ -149,7 +155,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       ptx::mbar_init(&kv_empty[s], 1);
     }
     ptx::mbar_init(sp_full, 1);
-    ptx::mbar_init(ds_full, 4);
+    ptx::mbar_init(ds_full, kSoftmaxWarps);
     ptx::mbar_init(ds_empty, 1);
     ptx::mbar_init(dq_full, 1);
     ptx::fence_mbar_init();
@@ -218,6 +224,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;      // which 64 columns of a tile this warp handles
     const int row = quarter * 32 + lane;
     const int qrow = q0 + row;
     const uint32_t t_row = (static_cast<uint32_t>(quarter * 32) << 16);
@@ -245,7 +252,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       int valid = min(kT, p.Skv - j * kT);
       if (p.causal) valid = max(0, min(valid, qrow + off + 1 - j * kT));
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t rs[32], rp[32];
         ptx::tmem_ld_32x32b_x32(t_s + t_row + c * 32, rs);
         ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
@@ -276,9 +283,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       } else {
         ptx::tc_fence_after();
         __nv_bfloat16* dst = p.dq + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * kD;
-        if (n_tiles > 0) {  // uniform over the CTA
-          store_row_bf16(dst, t_dq + t_row, qrow < p.Sq);
-        } else if (qrow < p.Sq) {
+        if (n_tiles > 0) {  // uniform over the CTA; each warp of a quarter stores 32 of the 64 columns
+          store_row_bf16(dst, t_dq + t_row, qrow < p.Sq, half, half + 1);
+        } else if (qrow < p.Sq && half == 0) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) reinterpret_cast<uint4*>(dst)[q] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -307,7 +314,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t* spt = sdo + 2 * kTile;  // P^T: 128 keys x 128 queries bf16
   uint8_t* sdst = spt + kPBytes;   // dS^T
   float* s_stat = reinterpret_cast<float*>(sdst + kPBytes);  // per softmax warp: [lse2 | delta][128]
-  uint8_t* bar_base = reinterpret_cast<uint8_t*>(s_stat) + 4096;
+  uint8_t* bar_base = reinterpret_cast<uint8_t*>(s_stat) + 8192;
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* qd_full = kv_full + 1;    // [2]
   uint64_t* qd_empty = qd_full + 2;   // [2]
@@ -335,7 +342,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       ptx::mbar_init(&qd_empty[s], 1);
     }
     ptx::mbar_init(sp_full, 1);
-    ptx::mbar_init(pt_full, 4);
+    ptx::mbar_init(pt_full, kSoftmaxWarps);
     ptx::mbar_init(pt_empty, 1);
     ptx::mbar_init(acc_full, 1);
     ptx::fence_mbar_init();
@@ -405,6 +412,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;      // which 64 query columns of a tile this warp handles
     const int row = quarter * 32 + lane;   // key row of this thread
     const int krow = k0 + row;
     const uint32_t t_row = (static_cast<uint32_t>(quarter * 32) << 16);
@@ -417,7 +425,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       float* slot = s_stat + (warp - 2) * 256;
       __syncwarp();  // the previous iteration's reads are done
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
+      for (int x = 2 * half; x < 2 * half + 2; ++x) {  // only the columns this warp handles
         const int ql = x * 32 + lane, q = i * kT + ql;
         slot[ql] = q < p.Sq ? p.lse[stat_base + q] * kLog2e : INFINITY;   // +inf: a query past the end sees nothing
         slot[128 + ql] = q < p.Sq ? p.delta[stat_base + q] : 0.f;
@@ -442,7 +450,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int q_first = p.causal ? max(0, krow - off - i * kT) : 0;  // first local query column that sees the key
       const bool key_ok = krow < p.Skv;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t rs[32], rp[32];
         ptx::tmem_ld_32x32b_x32(t_s + t_row + c * 32, rs);
         ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
@@ -472,7 +480,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(pt_full);
     }
-    if (n_iter == 0 && krow < p.Skv) {  // no query sees these keys
+    if (n_iter == 0 && krow < p.Skv && half == 0) {  // no query sees these keys
       __nv_bfloat16* dv = p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
       __nv_bfloat16* dk = p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
 #pragma unroll
@@ -487,10 +495,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (lane == 0) report_status(p.status, kStatusGemmTimeout, 77, blockIdx.x, 0);
       } else {
         ptx::tc_fence_after();
-        store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dv + t_row,
-                       krow < p.Skv);
-        store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dk + t_row,
-                       krow < p.Skv);
+        // the two warps of a lane quarter share the work: one stores the dV rows, the other the dK rows
+        if (half == 0)
+          store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dv + t_row,
+                         krow < p.Skv);
+        else
+          store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dk + t_row,
+                         krow < p.Skv);
       }
     }
   }

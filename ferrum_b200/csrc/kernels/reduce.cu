@@ -252,68 +252,67 @@ __global__ void arg_cols_kernel(const float* __restrict__ x, long long* __restri
   if (val) val[col] = best;
 }
 
-// Column sums of [rows, cols]: block = 128 columns x a chunk of rows, 8 warps
-// walk the rows, lanes own 4 adjacent columns; partials meet in shared memory
-// and leave with one atomicAdd per column per block.
+// Column sums of [rows, cols]: a block covers 32 x V adjacent columns (V = elements per 16 bytes: 4 fp32, 8 bf16)
+// and a chunk of rows; its 8 warps walk the rows, a lane owns V adjacent columns and keeps eight independent
+// 16-byte loads in flight; the partials meet in shared memory and leave with one atomicAdd per column per block.
+template <typename T>
+struct ColVec {
+  static constexpr int kV = 16 / sizeof(T);
+};
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, long long cols,
               long long rows_per_block) {
-  __shared__ float sm[8][128];
+  constexpr int kV = ColVec<T>::kV, kCols = 32 * kV, kU = 8;
+  __shared__ float sm[8][kCols];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long c0 = static_cast<long long>(blockIdx.x) * 128 + lane * 4;
+  const long long c0 = static_cast<long long>(blockIdx.x) * kCols + lane * kV;
   const long long r_lo = static_cast<long long>(blockIdx.y) * rows_per_block;
   const long long r_hi = min(rows, r_lo + rows_per_block);
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  const bool vec = (cols % 4 == 0) && (c0 + 3 < cols) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  float acc[kV];
+#pragma unroll
+  for (int i = 0; i < kV; ++i) acc[i] = 0.f;
+  const bool vec = (cols % kV == 0) && (c0 + kV - 1 < cols) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   if (vec) {
-    // four rows per trip: the loads are independent, so each thread keeps four of them in flight
-    for (long long r = r_lo + warp; r < r_hi; r += 32) {
-      if constexpr (sizeof(T) == 4) {
-        float4 v[4];
+    for (long long r = r_lo + warp; r < r_hi; r += 8 * kU) {
+      uint4 v[kU];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const long long rr = r + 8 * u;
-          v[u] = rr < r_hi ? *reinterpret_cast<const float4*>(x + rr * cols + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+      for (int u = 0; u < kU; ++u) {
+        const long long rr = r + 8 * u;
+        v[u] = rr < r_hi ? *reinterpret_cast<const uint4*>(x + rr * cols + c0) : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          a0 += v[u].x; a1 += v[u].y; a2 += v[u].z; a3 += v[u].w;
-        }
-      } else {
-        uint2 v[4];
+      for (int u = 0; u < kU; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        if constexpr (sizeof(T) == 4) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const long long rr = r + 8 * u;
-          v[u] = rr < r_hi ? *reinterpret_cast<const uint2*>(x + rr * cols + c0) : make_uint2(0u, 0u);
-        }
+          for (int i = 0; i < 4; ++i) acc[i] += __uint_as_float(w[i]);
+        } else {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].x));
-          const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[u].y));
-          a0 += f0.x; a1 += f0.y; a2 += f1.x; a3 += f1.y;
+          for (int i = 0; i < 4; ++i) {  // bf16 -> fp32 is a 16-bit shift
+            acc[2 * i] += __uint_as_float(w[i] << 16);
+            acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+          }
         }
       }
     }
   } else {
     for (long long r = r_lo + warp; r < r_hi; r += 8) {
       const T* p = x + r * cols + c0;
-      if (c0 < cols) a0 += static_cast<float>(p[0]);
-      if (c0 + 1 < cols) a1 += static_cast<float>(p[1]);
-      if (c0 + 2 < cols) a2 += static_cast<float>(p[2]);
-      if (c0 + 3 < cols) a3 += static_cast<float>(p[3]);
+#pragma unroll
+      for (int i = 0; i < kV; ++i)
+        if (c0 + i < cols) acc[i] += static_cast<float>(p[i]);
     }
   }
-  sm[warp][lane * 4 + 0] = a0;
-  sm[warp][lane * 4 + 1] = a1;
-  sm[warp][lane * 4 + 2] = a2;
-  sm[warp][lane * 4 + 3] = a3;
+#pragma unroll
+  for (int i = 0; i < kV; ++i) sm[warp][lane * kV + i] = acc[i];
   __syncthreads();
-  if (threadIdx.x < 128) {
+  for (int t = threadIdx.x; t < kCols; t += 256) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += sm[w][threadIdx.x];
-    const long long c = static_cast<long long>(blockIdx.x) * 128 + threadIdx.x;
+    for (int w = 0; w < 8; ++w) s += sm[w][t];
+    const long long c = static_cast<long long>(blockIdx.x) * kCols + t;
     if (c < cols) atomicAdd(out + c, s);
   }
 }
@@ -430,7 +429,8 @@ extern "C" int fb_colsum(const void* x, float* out, long long rows, long long co
     cudaError_t e = cudaMemsetAsync(out, 0, cols * sizeof(float), stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  const long long col_blocks = (cols + 127) / 128;
+  const long long per_block = dtype == FB_DT_BF16 ? 256 : 128;  // 32 lanes x 16 bytes
+  const long long col_blocks = (cols + per_block - 1) / per_block;
   long long row_blocks = (static_cast<long long>(sm_count()) * 4 + col_blocks - 1) / col_blocks;
   const long long max_rb = (rows + 63) / 64;
   if (row_blocks > max_rb) row_blocks = max_rb;
