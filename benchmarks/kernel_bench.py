@@ -143,6 +143,34 @@ def _cases(small: bool):
     img = torch.randn(16 if small else 64, 64, 56, 56, device=dev)
     case("im2col_3x3_f32", lambda: F.im2col(img, (3, 3), (1, 1), (1, 1), (1, 1)),
          img.numel() * 4 * (1 + 9), "K14 (input read once, 9x window matrix written)")
+    # 3 x 3 convolution, 64 -> 64 channels, padding 1, bf16 autocast: window matrix + GEMM against the implicit GEMM
+    import ferrum_b200 as fb_
+    wconv = (torch.randn(64, 64, 3, 3, device=dev) * 0.05).requires_grad_(True)
+    bconv = torch.zeros(64, device=dev, requires_grad=True)
+    imgg = img.detach().clone().requires_grad_(True)
+    gconv = torch.randn_like(img)
+    conv_bytes = img.numel() * 4 * 2   # NCHW fp32 input read, NCHW fp32 output written (64 -> 64 channels)
+
+    def conv_window(train):
+        with fb_.autocast():
+            cols = F.im2col(imgg if train else img, (3, 3), (1, 1), (1, 1), (1, 1))
+            y = F.linear(cols, wconv.reshape(64, -1), bconv).reshape(img.shape[0], 56 * 56, 64)
+            y = y.transpose(1, 2).reshape(img.shape[0], 64, 56, 56)
+        return torch.autograd.grad(y, (imgg, wconv, bconv), gconv) if train else y
+
+    def conv_implicit(train):
+        with fb_.autocast():
+            y = F.conv2d_igemm(imgg if train else img, wconv, bconv, (1, 1), (1, 1))
+        return torch.autograd.grad(y, (imgg, wconv, bconv), gconv) if train else y
+
+    case("conv2d_3x3_fwd_window_matrix_bf16", lambda: conv_window(False), conv_bytes,
+         "K14 im2col (9x matrix) + tcgen05 GEMM + transpose back")
+    case("conv2d_3x3_fwd_implicit_gemm_bf16", lambda: conv_implicit(False), conv_bytes,
+         "K14 NHWC bf16 copy + implicit GEMM (4-D TMA boxes per filter tap) + NCHW copy")
+    case("conv2d_3x3_fwd_bwd_window_matrix_bf16", lambda: conv_window(True), 3 * conv_bytes,
+         "K14 forward + backward through the stored window matrix (col2im for the data gradient)")
+    case("conv2d_3x3_fwd_bwd_implicit_gemm_bf16", lambda: conv_implicit(True), 3 * conv_bytes,
+         "K14 forward + data gradient + weight gradient as implicit GEMMs")
     case("maxpool2d_2x2_f32", lambda: F.pool2d(img, (2, 2), (2, 2), "max"), img.numel() * 4 * 1.25 + img.numel(),
          "K14 (input read, quarter-size output + int32 argmax written)")
     Ba, Ha, Sa, Da = (2 if small else 8), 16, 1024, 64

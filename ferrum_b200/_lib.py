@@ -119,6 +119,12 @@ _CUDA_SIGS = {
     "fb_gru_gates_fwd": (I, [P, P, P, P, P, LL, I, P]),
     "fb_gru_gates_bwd": (I, [P, P, P, P, P, P, LL, I, P]),
     "fb_im2col": (I, [P, P] + [I] * 14 + [LL, I, P]),
+    "fb_conv_igemm": (I, [P, P, P, P] + [I] * 11 + [LL, I, P, P]),
+    "fb_conv_wgrad_splits": (I, [I] * 6),
+    "fb_conv_wgrad": (I, [P, P, P] + [I] * 12 + [P, P]),
+    "fb_nchw_to_nhwc_bf16": (I, [P, P, I, I, LL, I, P]),
+    "fb_nhwc_to_nchw_f32": (I, [P, P, I, I, LL, LL, P]),
+    "fb_attention_bwd_map_error": (I, []),
     "fb_col2im": (I, [P, P] + [I] * 14 + [LL, P]),
     "fb_pool2d_fwd": (I, [P, P, P] + [I] * 10 + [I, P]),
     "fb_pool2d_bwd": (I, [P, P, P] + [I] * 10 + [I, P]),

@@ -6,10 +6,10 @@
 
 #define FB_MAX_RANKS 8
 #define FB_FLAG_CHANNELS 8
-#define FB_FLAG_BLOCKS 512
+#define FB_FLAG_BLOCKS 1024
 // flags[channel][block][source rank], one 32-bit epoch each
 #define FB_FLAG_WORDS (FB_FLAG_CHANNELS * FB_FLAG_BLOCKS * FB_MAX_RANKS)
-#define FB_FLAG_BYTES 131072  // flag words (8 x 512 x 8 x 4 B), so the data region stays 64 KiB aligned
+#define FB_FLAG_BYTES 262144  // flag words (8 x 1024 x 8 x 4 B), so the data region stays 64 KiB aligned
 
 typedef struct {
   int rank;

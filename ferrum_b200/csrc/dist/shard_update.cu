@@ -135,7 +135,7 @@ constexpr int kMaxUpBuckets = 256;  // rows of the bucket table one launch can t
 // The shards of all buckets form ONE index space of float4 positions (bucket after bucket), walked with a grid
 // stride: a bucket whose shard is smaller than the grid (biases, normalisation parameters; every bucket once the
 // world is large) then costs no trip of its own, and no trip ends with most of the grid idle.
-template <int FUSE, bool MC, int U>
+template <int FUSE, bool MC, int U, bool CS = true>
 __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, const UpArgs& a, float* m_base,
                             float* v_base, int* s_fail) {
   __shared__ long long s_pre[kMaxUpBuckets + 1];  // first position of bucket k in the joint index space
@@ -189,10 +189,10 @@ __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, cons
         ri[u] = s_e4[bk] + j;
         si[u] = s_so4[bk] + j;
         pub[u] = s_pub[bk] != 0;
-        g[u] = __ldcs(gp + ri[u]);
+        g[u] = CS ? __ldcs(gp + ri[u]) : gp[ri[u]];
         p[u] = pp[ri[u]];
-        m[u] = (FUSE == FB_FUSE_ADAM || m_base != nullptr) ? __ldcs(mp + si[u]) : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (FUSE == FB_FUSE_ADAM) v[u] = __ldcs(vp + si[u]);
+        m[u] = (FUSE == FB_FUSE_ADAM || m_base != nullptr) ? (CS ? __ldcs(mp + si[u]) : mp[si[u]]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (FUSE == FB_FUSE_ADAM) v[u] = CS ? __ldcs(vp + si[u]) : vp[si[u]];
       }
     }
 #pragma unroll
@@ -203,8 +203,13 @@ __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, cons
         adam1(p[u].y, g[u].y, m[u].y, v[u].y, adam);
         adam1(p[u].z, g[u].z, m[u].z, v[u].z, adam);
         adam1(p[u].w, g[u].w, m[u].w, v[u].w, adam);
-        __stcs(mp + si[u], m[u]);
-        __stcs(vp + si[u], v[u]);
+        if (CS) {
+          __stcs(mp + si[u], m[u]);
+          __stcs(vp + si[u], v[u]);
+        } else {
+          mp[si[u]] = m[u];
+          vp[si[u]] = v[u];
+        }
       } else {
         sgd1(p[u].x, g[u].x, m[u].x, sgd);
         sgd1(p[u].y, g[u].y, m[u].y, sgd);
@@ -236,13 +241,15 @@ __device__ void update_body(const fb_dist_ctx& c, int vblock, int nvblocks, cons
   block_handshake(c, a.channel, vblock, epoch + 1, s_fail, 411);
 }
 
-template <int FUSE, bool MC>
+// One 16-byte group of g, p, m, v per thread and trip with ordinary loads and stores: measured on one GPU (131 M
+// parameters, 592 blocks) 635 us against 646 us with two groups per trip and streaming hints.
+template <int FUSE, bool MC, int U = 1, bool CS = false>
 __global__ void __launch_bounds__(256)
 update_kernel(const fb_dist_ctx c, const UpArgs a) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
-  update_body<FUSE, MC, 2>(c, blockIdx.x, gridDim.x, a, a.m, a.v, &s_fail);
+  update_body<FUSE, MC, U, CS>(c, blockIdx.x, gridDim.x, a, a.m, a.v, &s_fail);
 }
 
 // All ranks in ONE cooperative launch on one GPU (virtual rank = blockIdx.x / blocks_per_rank): the protocol can

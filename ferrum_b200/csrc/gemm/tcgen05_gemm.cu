@@ -80,7 +80,30 @@ struct GemmArgs {
   int batch_inner, batch_total;
   long long sc_outer, sc_inner;
   float alpha;
+  // Convolution forms (kConv), stride 1, NHWC bf16 operands read through 4-D tensor maps {channel, x, y, image}:
+  //   cv_wgrad == 0 (forward / data gradient): a row tile is a cv_tw x cv_th patch of 128 output pixels of one
+  //     image, a k-block is 64 channels of one filter tap, and the A tile is the patch shifted by the tap
+  //     (out-of-range pixels read zeros: the padding).
+  //   cv_wgrad == 1 (weight gradient): rows = output channels, columns = input channels, and the REDUCTION runs
+  //     over output pixels in patches of 64 (one k-block); tile index = ((split * taps + tap) * num_m + m) ...
+  //     with the patches of a split summed into slice `split` of the output (sc_outer), tap at sc_inner * tap.
+  int cv_wgrad;
+  int cv_tw, cv_th, cv_tiles_w, cv_tiles_h, cv_nb;
+  int cv_Ho, cv_Wo;
+  int cv_kw, cv_taps, cv_cchunks, cv_cp;
+  int cv_ph, cv_pw, cv_dh, cv_dw;
+  int cv_splits, cv_kb_per_split, cv_total_kb;
 };
+
+// Patch index -> (image, first y, first x) of the patch.
+__device__ __forceinline__ void conv_patch(const GemmArgs& p, int idx, int& b, int& y0, int& x0) {
+  const int per_img = p.cv_tiles_h * p.cv_tiles_w;
+  b = idx / per_img;
+  const int r = idx - b * per_img;
+  const int ty = r / p.cv_tiles_w;
+  y0 = ty * p.cv_th;
+  x0 = (r - ty * p.cv_tiles_w) * p.cv_tw;
+}
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
   const int per_group = kGroupM * num_n;
@@ -92,7 +115,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gsize;
 }
 
-template <int BN, bool kBatched, bool kTf32>
+template <int BN, bool kBatched, bool kTf32, bool kConv = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const GemmArgs p) {
@@ -112,11 +135,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int num_m = (p.M + kBM - 1) / kBM;
+  const bool conv_rows = kConv && !p.cv_wgrad;   // rows are output pixels
+  const bool conv_red = kConv && p.cv_wgrad;     // the reduction runs over output pixels
+  const int num_m = conv_rows ? p.cv_nb * p.cv_tiles_h * p.cv_tiles_w : (p.M + kBM - 1) / kBM;
   const int num_n = (p.N + BN - 1) / BN;
   const int tiles_per_slice = num_m * num_n;
-  const int num_tiles = kBatched ? tiles_per_slice * p.batch_total : tiles_per_slice;
-  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int num_tiles = kBatched ? tiles_per_slice * p.batch_total
+                                 : (conv_red ? tiles_per_slice * p.cv_taps * p.cv_splits : tiles_per_slice);
+  const int num_kb = conv_rows ? p.cv_taps * p.cv_cchunks : (p.K + kBK - 1) / kBK;
+  // k-blocks [kb_lo, kb_hi) of tile t: everything, or (weight gradient) the pixel patches of the tile's split
+  auto kb_range = [&](int t, int& kb_lo, int& kb_hi) {
+    kb_lo = 0;
+    kb_hi = num_kb;
+    if (conv_red) {
+      const int split = (t / tiles_per_slice) / p.cv_taps;
+      kb_lo = split * p.cv_kb_per_split;
+      kb_hi = min(p.cv_total_kb, kb_lo + p.cv_kb_per_split);
+    }
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -150,11 +186,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        const int slice = kBatched ? t / tiles_per_slice : 0;
-        tile_coords(kBatched ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
+        const int slice = (kBatched || conv_red) ? t / tiles_per_slice : 0;
+        tile_coords((kBatched || conv_red) ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
         const int m0 = m_blk * kBM, n0 = n_blk * BN;
         const int bz = kBatched ? slice % p.batch_inner : 0, bw = kBatched ? slice / p.batch_inner : 0;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb_lo, kb_hi;
+        kb_range(t, kb_lo, kb_hi);
+        int cb = 0, cy0 = 0, cx0 = 0;              // conv, rows = pixels: this tile's patch
+        if (conv_rows) conv_patch(p, m_blk, cb, cy0, cx0);
+        const int ctap = conv_red ? slice % p.cv_taps : 0;   // conv, weight gradient: this tile's filter tap
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 1, blockIdx.x, stage);
             ok = false;
@@ -164,7 +205,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sb = sa + C::kABytes;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const int k0 = kb * kBK;
-          if constexpr (kBatched) {
+          if constexpr (kConv) {
+            if (!p.cv_wgrad) {
+              const int tap = kb / p.cv_cchunks, cc = kb - tap * p.cv_cchunks;
+              const int khi = tap / p.cv_kw, kwi = tap - khi * p.cv_kw;
+              ptx::tma_load_4d(sa, &tma_a, &full_bar[stage], cc * 64, cx0 - p.cv_pw + kwi * p.cv_dw,
+                               cy0 - p.cv_ph + khi * p.cv_dh, cb);
+              ptx::tma_load_2d(sb, &tma_b, &full_bar[stage], tap * p.cv_cp + cc * 64, n0);
+            } else {
+              int pb, py0, px0;
+              conv_patch(p, kb, pb, py0, px0);
+              const int khi = ctap / p.cv_kw, kwi = ctap - khi * p.cv_kw;
+#pragma unroll
+              for (int c = 0; c < kBM / 64; ++c)
+                ptx::tma_load_4d(sa + c * (64 * 128), &tma_a, &full_bar[stage], m0 + c * 64, px0, py0, pb);
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                ptx::tma_load_4d(sb + c * (64 * 128), &tma_b, &full_bar[stage], n0 + c * 64,
+                                 px0 - p.cv_pw + kwi * p.cv_dw, py0 - p.cv_ph + khi * p.cv_dh, pb);
+            }
+          } else if constexpr (kBatched) {
             if (p.a_mn_major) {
 #pragma unroll
               for (int c = 0; c < kBM / kMnChunk; ++c)
@@ -240,7 +300,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int kb_lo, kb_hi;
+        kb_range(t, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.timeout_ns)) {
             report_status(p.status, kStatusGemmTimeout, 3, blockIdx.x, stage);
             ok = false;
@@ -254,9 +316,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint64_t adesc = ptx::make_smem_desc_sw128(sa + k * a_kstep, a_lbo, a_sbo, a_layout);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(sb + k * b_kstep, b_lbo, b_sbo, b_layout);
             if constexpr (kTf32)
-              ptx::umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_tf32(d_tmem, adesc, bdesc, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
             else
-              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(&empty_bar[stage]);  // frees the smem slot when the MMAs retire
           if (++stage == C::kStages) {
@@ -277,15 +339,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase = 0;
     const int esz = p.out_bf16 ? 2 : 4;
     const bool vec_ok = ((p.ldc * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
-                        (!kBatched || ((p.sc_outer * esz) % 16 == 0 && (p.sc_inner * esz) % 16 == 0));
+                        (!(kBatched || kConv) || ((p.sc_outer * esz) % 16 == 0 && (p.sc_inner * esz) % 16 == 0));
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int m_blk, n_blk;
-      const int slice = kBatched ? t / tiles_per_slice : 0;
-      tile_coords(kBatched ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
-      const int row = m_blk * kBM + quarter * 32 + lane;
+      const int slice = (kBatched || conv_red) ? t / tiles_per_slice : 0;
+      tile_coords((kBatched || conv_red) ? t - slice * tiles_per_slice : t, num_m, num_n, m_blk, n_blk);
+      int row = m_blk * kBM + quarter * 32 + lane;
+      if (conv_rows) {  // accumulator row -> output pixel of the patch (rows outside the image are dropped)
+        int cb, cy0, cx0;
+        conv_patch(p, m_blk, cb, cy0, cx0);
+        const int ml = quarter * 32 + lane;
+        const int oy = cy0 + ml / p.cv_tw, ox = cx0 + ml % p.cv_tw;
+        row = (oy < p.cv_Ho && ox < p.cv_Wo) ? (cb * p.cv_Ho + oy) * p.cv_Wo + ox : p.M;
+      }
       const int n0 = n_blk * BN;
       const long long slice_off =
-          kBatched ? (slice / p.batch_inner) * p.sc_outer + (slice % p.batch_inner) * p.sc_inner : 0;
+          kBatched ? (slice / p.batch_inner) * p.sc_outer + (slice % p.batch_inner) * p.sc_inner
+                   : (conv_red ? (slice / p.cv_taps) * p.sc_outer + (slice % p.cv_taps) * p.sc_inner : 0);
       // The vote keeps the warp converged for the .sync.aligned TMEM loads below.
       const bool ready = ptx::mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.timeout_ns);
       if (!__all_sync(0xffffffffu, ready)) {
@@ -416,6 +486,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
+  // The driver's encoder wants a current context; a thread that has made no runtime call yet (an autograd
+  // worker entering its first backward) has none, and the encoder then fails with CUDA_ERROR_INVALID_CONTEXT.
+  static thread_local bool bound = false;
+  if (!bound) {  // cudaSetDevice binds the primary context to the thread and is legal during stream capture
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* sym = nullptr;
@@ -482,24 +560,79 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool kBatched, bool kTf32 = false>
+template <int BN, bool kBatched, bool kTf32 = false, bool kConv = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int max_ctas, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kBatched, kTf32>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, kBatched, kTf32, kConv>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const long long tiles = static_cast<long long>((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) *
-                          (kBatched ? args.batch_total : 1);
+  long long tiles = static_cast<long long>((args.M + kBM - 1) / kBM) * ((args.N + BN - 1) / BN) *
+                    (kBatched ? args.batch_total : 1);
+  if (kConv) {
+    const long long num_n = (args.N + BN - 1) / BN;
+    tiles = args.cv_wgrad ? static_cast<long long>((args.M + kBM - 1) / kBM) * num_n * args.cv_taps * args.cv_splits
+                          : static_cast<long long>(args.cv_nb) * args.cv_tiles_h * args.cv_tiles_w * num_n;
+  }
   if (tiles > 0x7fffffffll) return -1;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  gemm_bf16_kernel<BN, kBatched, kTf32><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
+  gemm_bf16_kernel<BN, kBatched, kTf32, kConv><<<grid, kThreads, C::kSmemBytes, stream>>>(ma, mb, args);
   return static_cast<int>(cudaGetLastError());
+}
+
+// 4-D map of an NHWC bf16 tensor [images, height, width, channels] (channels a multiple of 8): dims {channel, x, y,
+// image}, box = 64 channels x (bw x bh) pixels of one image, 128-byte swizzle; pixels and channels outside the
+// tensor read zeros, which is how a convolution's padding is applied.
+bool make_map_nhwc(CUtensorMap* map, const void* ptr, int images, int height, int width, int channels, int bw,
+                   int bh) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || channels % 8 != 0 || bw < 1 || bh < 1 || bw > 256 || bh > 256)
+    return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(channels), static_cast<cuuint64_t>(width),
+                        static_cast<cuuint64_t>(height), static_cast<cuuint64_t>(images)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(channels) * 2, static_cast<cuuint64_t>(width) * channels * 2,
+                           static_cast<cuuint64_t>(height) * width * channels * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Patch of `pixels` (a power of two) output pixels, bw x bh, that wastes the fewest positions on a wo x ho image.
+void pick_patch(int pixels, int wo, int ho, int& bw, int& bh) {
+  long long best = -1;
+  for (int w = 1; w <= pixels; w <<= 1) {
+    const int h = pixels / w;
+    if (w > 256 || h > 256) continue;
+    const long long cost = static_cast<long long>((wo + w - 1) / w) * w * ((ho + h - 1) / h) * h;
+    // ties: the wider patch (longer contiguous runs of pixels in memory)
+    if (best < 0 || cost < best || (cost == best && w > bw)) {
+      best = cost;
+      bw = w;
+      bh = h;
+    }
+  }
+}
+
+void default_args(GemmArgs& args) {
+  args.out2 = nullptr;
+  args.bias = nullptr;
+  args.act = FB_ACT_NONE;
+  args.beta = 0;
+  args.timeout_ns = 2000000000ull;
+  args.batch_inner = 1;
+  args.batch_total = 1;
+  args.sc_outer = args.sc_inner = 0;
+  args.alpha = 1.f;
+  args.cv_wgrad = 0;
+  args.cv_splits = 1;
 }
 
 }  // namespace
@@ -638,4 +771,125 @@ extern "C" int fb_gemm_tf32(const float* a, const float* b, float* out, const fl
   args.alpha = 1.f;
   return small_n ? launch<128, false, true>(ma, mb, args, max_ctas, stream)
                  : launch<256, false, true>(ma, mb, args, max_ctas, stream);
+}
+
+// Stride-1 convolution as an implicit GEMM on the tensor cores (no window matrix in memory):
+//   y[b, oy, ox, o] = bias[o] + sum over (ky, kx, c) of x[b, oy - ph + ky * dh, ox - pw + kx * dw, c] * w[o, ky, kx, c]
+// x: NHWC bf16 [B, H, W, Cp]; w: bf16 [O, kh * kw * Cp] (tap-major, channel innermost); Cp a multiple of 8 (pad the
+// channels with zeros).  y: NHWC [B, Ho, Wo, ldy] (fp32, or bf16 with out_bf16), Ho = H + 2 ph - dh (kh - 1), Wo alike.
+// The data gradient of a stride-1 convolution is the same call with the flipped, transposed filters and padding
+// dh (kh - 1) - ph.  Returns -2 when an operand cannot be described by a TMA map.
+extern "C" int fb_conv_igemm(const void* x, const void* w, void* y, const float* bias, int B, int H, int W, int Cp,
+                             int O, int kh, int kw, int ph, int pw, int dh, int dw, long long ldy, int out_bf16,
+                             int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  const int Ho = H + 2 * ph - dh * (kh - 1), Wo = W + 2 * pw - dw * (kw - 1);
+  if (B <= 0 || H <= 0 || W <= 0 || Cp <= 0 || (Cp & 7) || O <= 0 || kh <= 0 || kw <= 0 || Ho <= 0 || Wo <= 0 ||
+      dh <= 0 || dw <= 0 || ldy < O)
+    return -1;
+  if (static_cast<long long>(B) * Ho * Wo > 0x7fffffffll) return -1;
+  GemmArgs args;
+  default_args(args);
+  pick_patch(128, Wo, Ho, args.cv_tw, args.cv_th);
+  const bool small_n = O <= 128;
+  CUtensorMap ma, mb;
+  if (!make_map_nhwc(&ma, x, B, H, W, Cp, args.cv_tw, args.cv_th)) return -2;
+  const long long K = static_cast<long long>(kh) * kw * Cp;
+  if (!make_map(&mb, w, K, O, K, small_n ? 128 : 256)) return -2;
+  args.out = y;
+  args.bias = bias;
+  args.M = B * Ho * Wo;
+  args.N = O;
+  args.K = static_cast<int>(K);
+  args.ldc = ldy;
+  args.a_mn_major = 0;
+  args.b_mn_major = 0;
+  args.out_bf16 = out_bf16;
+  args.status = status;
+  args.cv_tiles_w = (Wo + args.cv_tw - 1) / args.cv_tw;
+  args.cv_tiles_h = (Ho + args.cv_th - 1) / args.cv_th;
+  args.cv_nb = B;
+  args.cv_Ho = Ho;
+  args.cv_Wo = Wo;
+  args.cv_kw = kw;
+  args.cv_taps = kh * kw;
+  args.cv_cchunks = (Cp + 63) / 64;
+  args.cv_cp = Cp;
+  args.cv_ph = ph;
+  args.cv_pw = pw;
+  args.cv_dh = dh;
+  args.cv_dw = dw;
+  args.cv_kb_per_split = args.cv_total_kb = 0;
+  return small_n ? launch<128, false, false, true>(ma, mb, args, 0, stream)
+                 : launch<256, false, false, true>(ma, mb, args, 0, stream);
+}
+
+// Number of partial results fb_conv_wgrad writes for this problem (the caller sums them; 1 = final result).
+extern "C" int fb_conv_wgrad_splits(int B, int Ho, int Wo, int O, int Cp, int taps) {
+  using namespace fb;
+  if (B <= 0 || Ho <= 0 || Wo <= 0 || O <= 0 || Cp <= 0 || taps <= 0) return 0;
+  int bw = 1, bh = 1;
+  pick_patch(64, Wo, Ho, bw, bh);
+  const long long total_kb = static_cast<long long>(B) * ((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh);
+  const long long tiles = static_cast<long long>((O + kBM - 1) / kBM) * ((Cp + (Cp <= 128 ? 127 : 255)) / (Cp <= 128 ? 128 : 256)) * taps;
+  long long splits = (2ll * sm_count() + tiles - 1) / tiles;
+  if (splits > 64) splits = 64;
+  if (splits > total_kb) splits = total_kb;
+  if (splits < 1) splits = 1;
+  const long long per = (total_kb + splits - 1) / splits;
+  return static_cast<int>((total_kb + per - 1) / per);
+}
+
+// Weight gradient of the convolution above:
+//   dw[s][o, (ky, kx), c] = sum over the output pixels of split s of dy[b, oy, ox, o] * x[b, oy - ph + ky * dh, ox - pw + kx * dw, c]
+// dy: NHWC bf16 [B, Ho, Wo, Op] (Op >= O, a multiple of 8), x: NHWC bf16 [B, H, W, Cp]; out: fp32
+// [fb_conv_wgrad_splits(...)][O][kh * kw * Cp]; the caller adds the splits.
+extern "C" int fb_conv_wgrad(const void* dy, const void* x, float* out, int B, int H, int W, int Cp, int O, int Op,
+                             int kh, int kw, int ph, int pw, int dh, int dw, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  const int Ho = H + 2 * ph - dh * (kh - 1), Wo = W + 2 * pw - dw * (kw - 1);
+  if (B <= 0 || H <= 0 || W <= 0 || Cp <= 0 || (Cp & 7) || O <= 0 || Op < O || (Op & 7) || kh <= 0 || kw <= 0 ||
+      Ho <= 0 || Wo <= 0 || dh <= 0 || dw <= 0)
+    return -1;
+  GemmArgs args;
+  default_args(args);
+  pick_patch(64, Wo, Ho, args.cv_tw, args.cv_th);
+  CUtensorMap ma, mb;
+  if (!make_map_nhwc(&ma, dy, B, Ho, Wo, Op, args.cv_tw, args.cv_th)) return -2;
+  if (!make_map_nhwc(&mb, x, B, H, W, Cp, args.cv_tw, args.cv_th)) return -2;
+  const int taps = kh * kw;
+  const bool small_n = Cp <= 128;
+  args.out = out;
+  args.M = O;
+  args.N = Cp;
+  args.K = 64;  // not used: the reduction is the list of pixel patches
+  args.ldc = static_cast<long long>(taps) * Cp;
+  args.a_mn_major = 1;
+  args.b_mn_major = 1;
+  args.out_bf16 = 0;
+  args.status = status;
+  args.cv_wgrad = 1;
+  args.cv_tiles_w = (Wo + args.cv_tw - 1) / args.cv_tw;
+  args.cv_tiles_h = (Ho + args.cv_th - 1) / args.cv_th;
+  args.cv_nb = B;
+  args.cv_Ho = Ho;
+  args.cv_Wo = Wo;
+  args.cv_kw = kw;
+  args.cv_taps = taps;
+  args.cv_cchunks = (Cp + 63) / 64;
+  args.cv_cp = Cp;
+  args.cv_ph = ph;
+  args.cv_pw = pw;
+  args.cv_dh = dh;
+  args.cv_dw = dw;
+  const long long total_kb = static_cast<long long>(B) * args.cv_tiles_w * args.cv_tiles_h;
+  if (total_kb > 0x7fffffffll) return -1;
+  const int splits = fb_conv_wgrad_splits(B, Ho, Wo, O, Cp, taps);
+  args.cv_total_kb = static_cast<int>(total_kb);
+  args.cv_kb_per_split = static_cast<int>((total_kb + splits - 1) / splits);
+  args.cv_splits = splits;
+  args.sc_outer = static_cast<long long>(O) * args.ldc;
+  args.sc_inner = Cp;
+  return small_n ? launch<128, false, false, true>(ma, mb, args, 0, stream)
+                 : launch<256, false, false, true>(ma, mb, args, 0, stream);
 }

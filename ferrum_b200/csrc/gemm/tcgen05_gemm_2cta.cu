@@ -535,6 +535,14 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn2 encode_fn2() {
+  // The driver's encoder wants a current context; a thread that has made no runtime call yet (an autograd
+  // worker entering its first backward) has none, and the encoder then fails with CUDA_ERROR_INVALID_CONTEXT.
+  static thread_local bool bound = false;
+  if (!bound) {  // cudaSetDevice binds the primary context to the thread and is legal during stream capture
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    bound = true;
+  }
   static EncodeTiledFn2 fn = nullptr;
   if (fn == nullptr) {
     void* sym = nullptr;

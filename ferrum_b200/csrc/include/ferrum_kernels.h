@@ -198,6 +198,17 @@ int fb_attention_bwd(const void* q, const void* k, const void* v, const void* ou
                      long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
                      long long v_sb, long long v_sh, long long v_ss, float scale, int causal, int32_t* status,
                      cudaStream_t stream);
+int fb_attention_bwd_map_error(void);
+// Stride-1 convolution as an implicit GEMM (gemm/tcgen05_gemm.cu) over NHWC bf16 operands with channel counts padded
+// to multiples of 8, its weight gradient, and the layout changes from / to NCHW fp32 (kernels/conv_layout.cu).
+int fb_conv_igemm(const void* x, const void* w, void* y, const float* bias, int B, int H, int W, int Cp, int O, int kh,
+                  int kw, int ph, int pw, int dh, int dw, long long ldy, int out_bf16, int32_t* status,
+                  cudaStream_t stream);
+int fb_conv_wgrad_splits(int B, int Ho, int Wo, int O, int Cp, int taps);
+int fb_conv_wgrad(const void* dy, const void* x, float* out, int B, int H, int W, int Cp, int O, int Op, int kh, int kw,
+                  int ph, int pw, int dh, int dw, int32_t* status, cudaStream_t stream);
+int fb_nchw_to_nhwc_bf16(const float* x, void* y, int B, int C, long long P, int Cp, cudaStream_t stream);
+int fb_nhwc_to_nchw_f32(const float* x, float* y, int B, int C, long long P, long long ld, cudaStream_t stream);
 int fb_gather_rows(const void* src, const long long* idx, void* dst, long long n_idx, long long row_bytes,
                    long long n_rows, int32_t* status, cudaStream_t stream);
 

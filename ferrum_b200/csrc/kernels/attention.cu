@@ -309,6 +309,14 @@ typedef CUresult (*EncodeTiledFnA)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFnA encode_fn_a() {
+  // The driver's encoder wants a current context; a thread that has made no runtime call yet (an autograd
+  // worker entering its first backward) has none, and the encoder then fails with CUDA_ERROR_INVALID_CONTEXT.
+  static thread_local bool bound = false;
+  if (!bound) {  // cudaSetDevice binds the primary context to the thread and is legal during stream capture
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    bound = true;
+  }
   static EncodeTiledFnA fn = nullptr;
   if (fn == nullptr) {
     void* sym = nullptr;

@@ -539,6 +539,14 @@ typedef CUresult (*EncodeTiledFnB)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFnB encode_fn_b() {
+  // The driver's encoder wants a current context; a thread that has made no runtime call yet (an autograd
+  // worker entering its first backward) has none, and the encoder then fails with CUDA_ERROR_INVALID_CONTEXT.
+  static thread_local bool bound = false;
+  if (!bound) {  // cudaSetDevice binds the primary context to the thread and is legal during stream capture
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    bound = true;
+  }
   static EncodeTiledFnB fn = nullptr;
   if (fn == nullptr) {
     void* sym = nullptr;
@@ -552,10 +560,15 @@ EncodeTiledFnB encode_fn_b() {
 }
 
 // [B, H, S, 64] bf16 view with element strides (sb, sh, ss): 4-D map, 64 x 128 x 1 x 1 box, rows past S read zeros.
+int g_map_error = 0;  // why the last map_bhsd failed: -1 no driver entry point, -2 / -3 alignment, > 0 the driver's code
+
 bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long sb, long long sh, long long ss) {
   EncodeTiledFnB enc = encode_fn_b();
+  g_map_error = -1;
   if (enc == nullptr) return false;
+  g_map_error = -2;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || ss % 8 || ss < kD) return false;
+  g_map_error = -3;
   if ((H > 1 && (sh % 8 || sh <= 0)) || (B > 1 && (sb % 8 || sb <= 0))) return false;
   const long long sh_ok = H > 1 ? sh : ss * S + ((8 - (ss * S) % 8) % 8);
   const long long sb_ok = B > 1 ? sb : sh_ok * H;
@@ -565,13 +578,17 @@ bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long 
                            static_cast<cuuint64_t>(sb_ok) * 2};
   cuuint32_t box[4] = {kD, 128, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  g_map_error = static_cast<int>(enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides,
+                                       box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return g_map_error == 0;
 }
 
 }  // namespace
 }  // namespace fb
+
+// Reason of the last -2 ... -5 of fb_attention_bwd (see g_map_error).
+extern "C" int fb_attention_bwd_map_error() { return fb::g_map_error; }
 
 // Gradients of out = softmax(scale q k^T) v (head dimension 64, bf16).  q, k, v: [B, H, S, 64] views with element
 // strides (last dimension contiguous, strides multiples of 8); out, d_out: [B, Sq, H, 64] contiguous (the forward
@@ -591,9 +608,11 @@ extern "C" int fb_attention_bwd(const void* q, const void* k, const void* v, con
     return -1;
   CUtensorMap mq, mk, mv, mdo;
   const long long o_sb = static_cast<long long>(Sq) * H * kD, o_sh = kD, o_ss = static_cast<long long>(H) * kD;
-  if (!map_bhsd(&mq, q, B, H, Sq, q_sb, q_sh, q_ss) || !map_bhsd(&mk, k, B, H, Skv, k_sb, k_sh, k_ss) ||
-      !map_bhsd(&mv, v, B, H, Skv, v_sb, v_sh, v_ss) || !map_bhsd(&mdo, d_out, B, H, Sq, o_sb, o_sh, o_ss))
-    return -2;
+  // -2: q, -3: k, -4: v, -5: d_out cannot be described by a TMA map (pointer / stride alignment)
+  if (!map_bhsd(&mq, q, B, H, Sq, q_sb, q_sh, q_ss)) return -2;
+  if (!map_bhsd(&mk, k, B, H, Skv, k_sb, k_sh, k_ss)) return -3;
+  if (!map_bhsd(&mv, v, B, H, Skv, v_sb, v_sh, v_ss)) return -4;
+  if (!map_bhsd(&mdo, d_out, B, H, Sq, o_sb, o_sh, o_ss)) return -5;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess ||

@@ -635,6 +635,11 @@ class _BlockwiseAttentionFn(Function):
                                           k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
                                           v.stride(2), float(ctx.scale), 1 if ctx.causal else 0, _rt.status_ptr(),
                                           _stream())
+        if -5 <= rc <= -2:  # an operand that no TMA map describes: name it
+            name, t = {-2: ("q", q), -3: ("k", k), -4: ("v", v), -5: ("grad_output", go)}[rc]
+            raise ValueError(f"fb_attention_bwd: {name} of shape {tuple(t.shape)}, strides {t.stride()}, address "
+                             f"{t.data_ptr():#x} cannot be a TMA operand (16-byte aligned pointer, strides multiples of 8; "
+                             f"reason {_lib.cuda().fb_attention_bwd_map_error()})")
         _lib.check(rc, "fb_attention_bwd")
         grads = [t.permute(0, 2, 1, 3) for t in (dq, dk, dv)]
         grads = [gr if gr.dtype == dt else gr.to(dt) for gr, dt in zip(grads, ctx.in_dtypes)]
@@ -1433,6 +1438,97 @@ class _Im2colFn(Function):
         dx = torch.empty((B, C, H, W), device=g.device, dtype=torch.float32)
         _lib.check(_lib.cuda().fb_col2im(g.data_ptr(), dx.data_ptr(), *ctx.geom, g.shape[1], _stream()), "fb_col2im")
         return dx, None, None, None, None
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def _to_nhwc_bf16(x: torch.Tensor) -> torch.Tensor:
+    """[B, C, H, W] fp32 -> [B, H, W, Cp] bf16 with the channels padded by zeros to a multiple of 8."""
+    x = _f32(x).contiguous()
+    B, C, H, W = x.shape
+    y = torch.empty((B, H, W, _pad8(C)), device=x.device, dtype=torch.bfloat16)
+    _lib.check(_lib.cuda().fb_nchw_to_nhwc_bf16(x.data_ptr(), y.data_ptr(), B, C, H * W, y.shape[3], _stream()),
+               "fb_nchw_to_nhwc_bf16")
+    return y
+
+
+def _to_nchw_f32(y: torch.Tensor, C: int) -> torch.Tensor:
+    """[B, H, W, ld] fp32 (first C channels) -> [B, C, H, W] fp32."""
+    B, H, W, ld = y.shape
+    out = torch.empty((B, C, H, W), device=y.device, dtype=torch.float32)
+    _lib.check(_lib.cuda().fb_nhwc_to_nchw_f32(y.data_ptr(), out.data_ptr(), B, C, H * W, ld, _stream()),
+               "fb_nhwc_to_nchw_f32")
+    return out
+
+
+def _conv_igemm(xh: torch.Tensor, wk: torch.Tensor, bias, O: int, kernel, padding, dilation) -> torch.Tensor:
+    """NHWC bf16 ``xh`` [B, H, W, Cp] * ``wk`` [O, kh * kw * Cp] -> NHWC fp32 [B, Ho, Wo, O] on the tensor cores."""
+    B, H, W, Cp = xh.shape
+    (kh, kw), (ph, pw), (dh, dw) = kernel, padding, dilation
+    Ho, Wo = H + 2 * ph - dh * (kh - 1), W + 2 * pw - dw * (kw - 1)
+    y = torch.empty((B, Ho, Wo, O), device=xh.device, dtype=torch.float32)
+    _lib.check(_lib.cuda().fb_conv_igemm(xh.data_ptr(), wk.data_ptr(), y.data_ptr(), _ptr(bias), B, H, W, Cp, O, kh,
+                                         kw, ph, pw, dh, dw, O, 0, _rt.status_ptr(), _stream()), "fb_conv_igemm")
+    return y
+
+
+class _ConvIgemmFn(Function):
+    """Stride-1, ungrouped 2-D convolution without a window matrix (csrc/gemm/tcgen05_gemm.cu, conv forms): all three
+    products — forward, data gradient, weight gradient — read NHWC bf16 activations through 4-D TMA boxes shifted by
+    the filter tap (zero fill = padding) and run on tcgen05.  Counterpart of the reference's direct loops
+    (ferrum-nn/src/conv.rs:209-330)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, padding, dilation):
+        B, C, H, W = x.shape
+        O, _, kh, kw = weight.shape
+        xh = _to_nhwc_bf16(x)                                              # [B, H, W, Cp]
+        wk = _to_nhwc_bf16(weight.detach()).reshape(O, -1)                 # [O, kh * kw * Cp]
+        b = _f32(bias.detach()).contiguous() if bias is not None else None
+        y = _conv_igemm(xh, wk, b, O, (kh, kw), padding, dilation)
+        ctx.save_for_backward(xh, weight)
+        ctx.geom = (C, tuple(padding), tuple(dilation), bias is not None)
+        return _to_nchw_f32(y, O)
+
+    @staticmethod
+    def backward(ctx, g):
+        xh, weight = ctx.saved_tensors
+        C, (ph, pw), (dh, dw), has_bias = ctx.geom
+        B, H, W, Cp = xh.shape
+        O, _, kh, kw = weight.shape
+        gh = _to_nhwc_bf16(g)                                              # [B, Ho, Wo, Op]
+        Op = gh.shape[3]
+        dx = dwt = db = None
+        if ctx.needs_input_grad[0]:
+            # dx = dy convolved with the filters flipped in both directions and input / output channels exchanged
+            wt = _to_nhwc_bf16(weight.detach().transpose(0, 1).flip(2, 3)).reshape(C, -1)   # [C, kh * kw * Op]
+            dxh = _conv_igemm(gh, wt, None, C, (kh, kw), (dh * (kh - 1) - ph, dw * (kw - 1) - pw), (dh, dw))
+            dx = _to_nchw_f32(dxh, C)
+        if ctx.needs_input_grad[1]:
+            lib = _lib.cuda()
+            Ho, Wo = gh.shape[1], gh.shape[2]
+            splits = lib.fb_conv_wgrad_splits(B, Ho, Wo, O, Cp, kh * kw)
+            part = torch.empty((splits, O, kh * kw * Cp), device=g.device, dtype=torch.float32)
+            _lib.check(lib.fb_conv_wgrad(gh.data_ptr(), xh.data_ptr(), part.data_ptr(), B, H, W, Cp, O, Op, kh, kw, ph,
+                                         pw, dh, dw, _rt.status_ptr(), _stream()), "fb_conv_wgrad")
+            full = raw_reduce(part, "sum", 0) if splits > 1 else part[0]
+            dwt = full.reshape(O, kh, kw, Cp)[..., :C].permute(0, 3, 1, 2).contiguous()
+        if has_bias and ctx.needs_input_grad[2]:
+            db = raw_colsum(gh.reshape(-1, Op))[:O]
+        return dx, dwt, db, None, None
+
+
+def conv_igemm_ok(x: torch.Tensor, stride, dilation, padding, kernel, groups: int) -> bool:
+    """True when ``conv2d`` can take the implicit-GEMM path: CUDA, bf16 autocast on, one group, stride 1 and a data
+    gradient whose padding ``dilation * (kernel - 1) - padding`` is not negative."""
+    return (_native(x) and x.dim() == 4 and config.low_precision_active() and groups == 1 and tuple(stride) == (1, 1)
+            and dilation[0] * (kernel[0] - 1) - padding[0] >= 0 and dilation[1] * (kernel[1] - 1) - padding[1] >= 0)
+
+
+def conv2d_igemm(x, weight, bias, padding=(0, 0), dilation=(1, 1)):
+    return _ConvIgemmFn.apply(x, weight, bias, tuple(padding), tuple(dilation))
 
 
 def im2col(x, kernel, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):

@@ -127,11 +127,12 @@ class DistributedDataParallel(Module, GradSink):
         self._push = os.environ.get("FERRUM_GEMM_PUSH", "0") == "1"
         self._pushed = []
         self._pushed_params = set()
-        # Blocks of a bucket kernel.  A rank updates 1 / world of every bucket, so two ranks want many blocks
-        # (measured: 6.9 ms/step with 128 vs 7.4 with 48) while at four and eight ranks more blocks only take
-        # issue slots and memory bandwidth from the GEMMs they run beside (7.1 with 48 vs 7.3 - 7.7 with 128).
+        # Blocks of a bucket kernel.  The per-bucket reduce-scatter kernel is light (at most 80 registers, it sits
+        # beside a persistent GEMM CTA), and 128 blocks measured best at 2 and at 8 ranks (8 ranks: a 64 MB bucket
+        # takes 128 us with 128 blocks and 216 - 308 us with 48, step 7.1 against 7.6 ms with eager launches).  The
+        # single-kernel form (defer_update(False)) carries the optimizer and wanted 48 at 4 and 8 ranks.
         env_blocks = os.environ.get("FERRUM_COMM_BLOCKS")
-        self._comm_blocks = int(env_blocks) if env_blocks else (128 if self._pg.world_size() <= 2 else 48)
+        self._comm_blocks = int(env_blocks) if env_blocks else 128
         self._comm_threads = int(os.environ.get("FERRUM_COMM_THREADS", "256"))
         # Deferred update (default): reduce-scatter per bucket inside backward, one optimizer + publish kernel after
         # it.  Measured at 2 GPUs on the 8 x 4096 MLP: the single-kernel form keeps 128 blocks of 200+ registers
@@ -139,7 +140,7 @@ class DistributedDataParallel(Module, GradSink):
         # optimizer state through the L2 the GEMMs live on (7.4 ms/step against 6.3 on one GPU).
         self._defer = True
         self._update_in_backward = False  # two-kernel form with the update launched per bucket inside backward
-        self._update_blocks = 444     # blocks of the update kernel: three per SM, it runs alone
+        self._update_blocks = 592     # blocks of the update kernel: four per SM, it runs alone (measured best of 444 / 592 / 888)
         self._dev_epoch_up = None
         self._table = None
         self._prof = None             # per-step timing events of the bucket kernels (comm_profile)
@@ -192,6 +193,8 @@ class DistributedDataParallel(Module, GradSink):
         """``True`` (default): reduce-scatter per bucket during backward, one optimizer + publish kernel after it.
         ``False``: all-reduce, optimizer and publish in one kernel per bucket, inside backward."""
         self._defer = bool(flag)
+        if not os.environ.get("FERRUM_COMM_BLOCKS"):
+            self._comm_blocks = 128 if (self._defer or self._pg.world_size() <= 2) else 48
         return self
 
     def update_in_backward(self, flag: bool = True) -> "DistributedDataParallel":

@@ -292,3 +292,22 @@ def test_multi_head_attention_trains_through_the_blockwise_kernels():
     assert _rel(x.grad, xr.grad) < 4e-2
     gw = torch.cat([mha.q_proj.weight.grad, mha.k_proj.weight.grad, mha.v_proj.weight.grad])
     assert _rel(gw, ref.in_proj_weight.grad) < 4e-2
+
+
+def test_backward_kernels_work_as_the_first_cuda_work_of_the_autograd_thread():
+    """The backward's TMA maps are encoded on the autograd worker thread; in a fresh process that thread has made no
+    CUDA runtime call before, and the driver's encoder refuses to work without a current context."""
+    import subprocess
+    import sys
+
+    code = ("import torch\n"
+            "from ferrum_b200.ops import functional as F\n"
+            "q, k, v = (torch.randn(2, 1024, 16, 64, device='cuda').bfloat16().permute(0, 2, 1, 3).requires_grad_(True)"
+            " for _ in range(3))\n"
+            "g = torch.randn(2, 1024, 16, 64, device='cuda').bfloat16().permute(0, 2, 1, 3)\n"
+            "dq, dk, dv = torch.autograd.grad(F.attention_blockwise(q, k, v, 0.125), (q, k, v), g)\n"
+            "torch.cuda.synchronize()\n"
+            "assert all(bool(torch.isfinite(t.float()).all()) for t in (dq, dk, dv))\n"
+            "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]

@@ -93,6 +93,42 @@ def test_conv2d_forward_backward_matches_torch(cfg):
     _close(x.grad, xr.grad, 1e-4), _close(conv.weight.grad, wr.grad, 1e-4), _close(conv.bias.grad, br.grad, 1e-4)
 
 
+@pytest.mark.parametrize("B,cin,cout,H,W,k,pad,dil", [
+    (2, 3, 5, 17, 19, (3, 3), (1, 1), (1, 1)),          # RGB-like input: channels padded to 8
+    (1, 64, 64, 56, 56, (3, 3), (1, 1), (1, 1)),        # the kernel benchmark's layer
+    (2, 16, 200, 20, 33, (3, 5), (1, 2), (2, 1)),       # 256-column tile, rectangular dilated filter
+    (2, 136, 72, 9, 70, (1, 1), (0, 0), (1, 1)),        # pointwise, three channel chunks, wide flat image
+    (3, 24, 40, 12, 12, (5, 5), (2, 2), (1, 1)),
+    (1, 8, 8, 5, 4, (3, 3), (0, 0), (1, 1)),            # output smaller than one patch
+])
+def test_conv2d_implicit_gemm_forward_backward_matches_fp32(B, cin, cout, H, W, k, pad, dil):
+    """Under bf16 autocast a stride-1 convolution takes the implicit-GEMM kernels in all three directions; the result
+    is compared with an fp32 PyTorch convolution of the bf16-rounded operands (products are exact in fp32, so only
+    the accumulation order and the bf16 rounding of the incoming gradient differ)."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(11)
+    conv = nn.Conv2d(cin, cout, k, 1, pad, dil, 1, device=fb.Device.Cuda(0))
+    x = torch.randn(B, cin, H, W, device="cuda", requires_grad=True)
+    with fb.autocast():
+        assert F.conv_igemm_ok(x, (1, 1), dil, pad, k, 1)
+        y = conv(x)
+    fb.utils.runtime.check_status()
+    r16 = lambda t: t.detach().bfloat16().float()
+    xr, wr = r16(x).requires_grad_(True), r16(conv.weight).requires_grad_(True)
+    br = conv.bias.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.conv2d(xr, wr, br, 1, pad, dil, 1)
+    assert y.dtype == torch.float32 and y.shape == yr.shape
+    _close(y, yr, 2e-4)
+    g = torch.randn_like(yr).bfloat16().float()         # a gradient that bf16 represents exactly
+    y.backward(g)
+    yr.backward(g)
+    fb.utils.runtime.check_status()
+    _close(x.grad, xr.grad, 2e-4), _close(conv.weight.grad, wr.grad, 2e-4), _close(conv.bias.grad, br.grad, 2e-4)
+
+
 def test_im2col_rows_are_gemm_ready():
     from ferrum_b200.ops import functional as F
 
