@@ -258,16 +258,31 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
         ptx::tmem_wait_ld();
         uint32_t packed[16];
+        // The warp takes the packed path (two scores per instruction: fused multiply-adds on fp32 pairs) whenever
+        // none of its rows is cut in this chunk by the causal diagonal or by the end of the keys.
+        if (__all_sync(0xffffffffu, c * 32 + 32 <= valid)) {
+          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
+          const float2 sc2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float d0 = 0.f, d1 = 0.f;
-          if (c * 32 + i < valid)
-            d0 = ex2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i]) - delta) * p.scale;
-          if (c * 32 + i + 1 < valid)
-            d1 = ex2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i + 1]) - delta) *
-                 p.scale;
-          const __nv_bfloat162 pk = __floats2bfloat162_rn(d0, d1);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+          for (int i = 0; i < 32; i += 2) {
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1])), sl2, nl2);
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(rp[i]), __uint_as_float(rp[i + 1])), sc2, nd2);
+            const float2 d = __fmul2_rn(make_float2(ex2f(e.x), ex2f(e.y)), t);
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(d.x, d.y);
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float d0 = 0.f, d1 = 0.f;
+            if (c * 32 + i < valid)
+              d0 = ex2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i]) - delta) * p.scale;
+            if (c * 32 + i + 1 < valid)
+              d1 = ex2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i + 1]) - delta) *
+                   p.scale;
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(d0, d1);
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
         }
         store_chunk(sds, row, c, packed);
       }
@@ -427,8 +442,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int x = 2 * half; x < 2 * half + 2; ++x) {  // only the columns this warp handles
         const int ql = x * 32 + lane, q = i * kT + ql;
-        slot[ql] = q < p.Sq ? p.lse[stat_base + q] * kLog2e : INFINITY;   // +inf: a query past the end sees nothing
-        slot[128 + ql] = q < p.Sq ? p.delta[stat_base + q] : 0.f;
+        // negated, so that one fused multiply-add forms the exponent; -inf: a query past the end sees nothing
+        slot[ql] = q < p.Sq ? -p.lse[stat_base + q] * kLog2e : -INFINITY;
+        slot[128 + ql] = q < p.Sq ? -p.delta[stat_base + q] * p.scale : 0.f;
       }
       __syncwarp();
       const bool ready = ptx::mbar_wait(sp_full, it & 1, abort_flag, p.timeout_ns);
@@ -448,7 +464,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       // queries of this tile that may see this key: all of them, or (causal) those with q + off >= key
       const int q_first = p.causal ? max(0, krow - off - i * kT) : 0;  // first local query column that sees the key
-      const bool key_ok = krow < p.Skv;
 #pragma unroll 1
       for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t rs[32], rp[32];
@@ -456,21 +471,49 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
         ptx::tmem_wait_ld();
         uint32_t pk_p[16], pk_d[16];
+        // Keys past the end need no mask (their rows of dK / dV are never stored and no other row depends on
+        // them); only the causal diagonal does.  Packed path: two scores per instruction.
+        if (__all_sync(0xffffffffu, q_first <= c * 32)) {
+          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), sc2 = make_float2(p.scale, p.scale);
 #pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          const int qa = c * 32 + x;
-          if (key_ok && qa >= q_first) {
-            p0 = ex2f(fmaf(__uint_as_float(rs[x]), p.scale_log2, -slot[qa]));
-            d0 = p0 * (__uint_as_float(rp[x]) - slot[128 + qa]) * p.scale;
+          for (int x = 0; x < 32; x += 4) {
+            const int qa = c * 32 + x;
+            const float4 nl = *reinterpret_cast<const float4*>(slot + qa);
+            const float4 nd = *reinterpret_cast<const float4*>(slot + 128 + qa);
+            const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(rs[x]), __uint_as_float(rs[x + 1])), sl2,
+                                         make_float2(nl.x, nl.y));
+            const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(rs[x + 2]), __uint_as_float(rs[x + 3])), sl2,
+                                         make_float2(nl.z, nl.w));
+            const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(rp[x]), __uint_as_float(rp[x + 1])), sc2,
+                                         make_float2(nd.x, nd.y));
+            const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(rp[x + 2]), __uint_as_float(rp[x + 3])), sc2,
+                                         make_float2(nd.z, nd.w));
+            const float2 p0 = make_float2(ex2f(e0.x), ex2f(e0.y)), p1 = make_float2(ex2f(e1.x), ex2f(e1.y));
+            const float2 d0 = __fmul2_rn(p0, t0), d1 = __fmul2_rn(p1, t1);
+            const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0.x, p0.y), a1 = __floats2bfloat162_rn(p1.x, p1.y);
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(d0.x, d0.y), b1 = __floats2bfloat162_rn(d1.x, d1.y);
+            pk_p[x >> 1] = *reinterpret_cast<const uint32_t*>(&a0);
+            pk_p[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&a1);
+            pk_d[x >> 1] = *reinterpret_cast<const uint32_t*>(&b0);
+            pk_d[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&b1);
           }
-          if (key_ok && qa + 1 >= q_first) {
-            p1 = ex2f(fmaf(__uint_as_float(rs[x + 1]), p.scale_log2, -slot[qa + 1]));
-            d1 = p1 * (__uint_as_float(rp[x + 1]) - slot[128 + qa + 1]) * p.scale;
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+            const int qa = c * 32 + x;
+            if (qa >= q_first) {
+              p0 = ex2f(fmaf(__uint_as_float(rs[x]), p.scale_log2, slot[qa]));
+              d0 = p0 * fmaf(__uint_as_float(rp[x]), p.scale, slot[128 + qa]);
+            }
+            if (qa + 1 >= q_first) {
+              p1 = ex2f(fmaf(__uint_as_float(rs[x + 1]), p.scale_log2, slot[qa + 1]));
+              d1 = p1 * fmaf(__uint_as_float(rp[x + 1]), p.scale, slot[128 + qa + 1]);
+            }
+            const __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), d = __floats2bfloat162_rn(d0, d1);
+            pk_p[x >> 1] = *reinterpret_cast<const uint32_t*>(&a);
+            pk_d[x >> 1] = *reinterpret_cast<const uint32_t*>(&d);
           }
-          const __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), d = __floats2bfloat162_rn(d0, d1);
-          pk_p[x >> 1] = *reinterpret_cast<const uint32_t*>(&a);
-          pk_d[x >> 1] = *reinterpret_cast<const uint32_t*>(&d);
         }
         store_chunk(spt, row, c, pk_p);
         store_chunk(sdst, row, c, pk_d);
