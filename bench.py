@@ -323,7 +323,10 @@ def run_ours(args):
     feed.close()
     loader.close()
     fb.utils.runtime.check_status()
+    multimem = None
     if engine is not None:
+        arena = getattr(engine, "_arena", None)
+        multimem = arena.has_multicast() if arena is not None else None
         engine.shutdown()
     if use_engine:
         # the torch.distributed rendezvous stays up for the baseline arm that follows in this process
@@ -331,6 +334,8 @@ def run_ours(args):
 
     if world > 1:
         par = "nvlink-fused-ddp" + ("-sharded-master" if shard else "")
+        if multimem is not None:
+            par += ", multimem through the NVSwitch" if multimem else ", peer loads"
     else:
         par = "single, optimizer overlapped with backward" if use_engine else "single"
     par += ", step replayed from a CUDA graph" if graph_box[0] is not None else ", eager launches"

@@ -82,15 +82,13 @@ __device__ __forceinline__ void mma_pv(uint32_t tmem, uint32_t a, uint32_t b, ui
                   ptx::make_smem_desc_sw128(b + k * 2048, 8192, 1024), idesc, (accumulate || k != 0) ? 1u : 0u);
 }
 
-// 32 bf16 pairs of one row -> four 16-byte chunks of the row's 128-byte line in k-block (c >> 1), swizzled.
-__device__ __forceinline__ void store_chunk(uint8_t* mat, int row, int c, const uint32_t (&packed)[16]) {
-  uint8_t* blk = mat + (c >> 1) * kTile + row * 128;
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int chunk = (c & 1) * 4 + q;
-    *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) =
-        make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
-  }
+// 16 columns (8 bf16 pairs) of one row, starting at column col (a multiple of 16): two 16-byte chunks of the row's
+// 128-byte line in k-block (col >> 6), swizzled.
+__device__ __forceinline__ void store_cols16(uint8_t* mat, int row, int col, const uint32_t (&w)[8]) {
+  uint8_t* blk = mat + (col >> 6) * kTile + row * 128;
+  const int chunk = (col & 63) >> 3;
+  *reinterpret_cast<uint4*>(blk + (((chunk) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(blk + (((chunk + 1) ^ (row & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 // One 64-column accumulator row from tensor memory to 64 bf16 in global memory.  The tensor-memory loads are
@@ -251,40 +249,57 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       int valid = min(kT, p.Skv - j * kT);
       if (p.causal) valid = max(0, min(valid, qrow + off + 1 - j * kT));
-#pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
-        uint32_t rs[32], rp[32];
-        ptx::tmem_ld_32x32b_x32(t_s + t_row + c * 32, rs);
-        ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
+      // The warp's 64 columns in four batches of 16: the tensor-memory loads of batch k + 1 are in flight while
+      // batch k is computed (tcgen05.wait::ld waits for every load issued before it, so the wait for a batch comes
+      // after the arithmetic of the previous one).
+      {
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
+        const float2 sc2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
+        auto batch = [&](int col, const uint32_t (&rs)[16], const uint32_t (&rp)[16]) {
+          uint32_t w[8];
+          // packed path (two scores per instruction) unless the causal diagonal or the end of the keys cuts a row
+          if (__all_sync(0xffffffffu, col + 16 <= valid)) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1])), sl2, nl2);
+              const float2 t = __ffma2_rn(make_float2(__uint_as_float(rp[i]), __uint_as_float(rp[i + 1])), sc2, nd2);
+              const float2 d = __fmul2_rn(make_float2(ex2f(e.x), ex2f(e.y)), t);
+              const __nv_bfloat162 pk = __floats2bfloat162_rn(d.x, d.y);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              float d0 = 0.f, d1 = 0.f;
+              if (col + i < valid)
+                d0 = ex2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i]) - delta) * p.scale;
+              if (col + i + 1 < valid)
+                d1 = ex2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2)) *
+                     (__uint_as_float(rp[i + 1]) - delta) * p.scale;
+              const __nv_bfloat162 pk = __floats2bfloat162_rn(d0, d1);
+              w[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+            }
+          }
+          store_cols16(sds, row, col, w);
+        };
+        const int c0 = half * 64;
+        uint32_t sa[16], pa[16], sb[16], pb[16];
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0, sa);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0, pa);
         ptx::tmem_wait_ld();
-        uint32_t packed[16];
-        // The warp takes the packed path (two scores per instruction: fused multiply-adds on fp32 pairs) whenever
-        // none of its rows is cut in this chunk by the causal diagonal or by the end of the keys.
-        if (__all_sync(0xffffffffu, c * 32 + 32 <= valid)) {
-          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
-          const float2 sc2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1])), sl2, nl2);
-            const float2 t = __ffma2_rn(make_float2(__uint_as_float(rp[i]), __uint_as_float(rp[i + 1])), sc2, nd2);
-            const float2 d = __fmul2_rn(make_float2(ex2f(e.x), ex2f(e.y)), t);
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(d.x, d.y);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float d0 = 0.f, d1 = 0.f;
-            if (c * 32 + i < valid)
-              d0 = ex2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i]) - delta) * p.scale;
-            if (c * 32 + i + 1 < valid)
-              d1 = ex2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2)) * (__uint_as_float(rp[i + 1]) - delta) *
-                   p.scale;
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(d0, d1);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-          }
-        }
-        store_chunk(sds, row, c, packed);
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 16, sb);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 16, pb);
+        batch(c0, sa, pa);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 32, sa);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 32, pa);
+        batch(c0 + 16, sb, pb);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 48, sb);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 48, pb);
+        batch(c0 + 32, sa, pa);
+        ptx::tmem_wait_ld();
+        batch(c0 + 48, sb, pb);
       }
       ptx::tc_fence_before();
       ptx::fence_proxy_async_smem();
@@ -464,59 +479,74 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       // queries of this tile that may see this key: all of them, or (causal) those with q + off >= key
       const int q_first = p.causal ? max(0, krow - off - i * kT) : 0;  // first local query column that sees the key
-#pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
-        uint32_t rs[32], rp[32];
-        ptx::tmem_ld_32x32b_x32(t_s + t_row + c * 32, rs);
-        ptx::tmem_ld_32x32b_x32(t_dp + t_row + c * 32, rp);
+      // Four batches of 16 query columns, tensor-memory loads of the next batch in flight during the arithmetic.
+      // Keys past the end need no mask (their rows of dK / dV are never stored and no other row depends on them);
+      // only the causal diagonal does.
+      {
+        const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), sc2 = make_float2(p.scale, p.scale);
+        auto batch = [&](int col, const uint32_t (&rs)[16], const uint32_t (&rp)[16]) {
+          uint32_t wp[8], wd[8];
+          if (__all_sync(0xffffffffu, q_first <= col)) {
+#pragma unroll
+            for (int x = 0; x < 16; x += 4) {
+              const float4 nl = *reinterpret_cast<const float4*>(slot + col + x);
+              const float4 nd = *reinterpret_cast<const float4*>(slot + 128 + col + x);
+              const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(rs[x]), __uint_as_float(rs[x + 1])), sl2,
+                                           make_float2(nl.x, nl.y));
+              const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(rs[x + 2]), __uint_as_float(rs[x + 3])), sl2,
+                                           make_float2(nl.z, nl.w));
+              const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(rp[x]), __uint_as_float(rp[x + 1])), sc2,
+                                           make_float2(nd.x, nd.y));
+              const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(rp[x + 2]), __uint_as_float(rp[x + 3])), sc2,
+                                           make_float2(nd.z, nd.w));
+              const float2 p0 = make_float2(ex2f(e0.x), ex2f(e0.y)), p1 = make_float2(ex2f(e1.x), ex2f(e1.y));
+              const float2 d0 = __fmul2_rn(p0, t0), d1 = __fmul2_rn(p1, t1);
+              const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0.x, p0.y), a1 = __floats2bfloat162_rn(p1.x, p1.y);
+              const __nv_bfloat162 b0 = __floats2bfloat162_rn(d0.x, d0.y), b1 = __floats2bfloat162_rn(d1.x, d1.y);
+              wp[x >> 1] = *reinterpret_cast<const uint32_t*>(&a0);
+              wp[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&a1);
+              wd[x >> 1] = *reinterpret_cast<const uint32_t*>(&b0);
+              wd[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&b1);
+            }
+          } else {
+#pragma unroll
+            for (int x = 0; x < 16; x += 2) {
+              float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+              const int qa = col + x;
+              if (qa >= q_first) {
+                p0 = ex2f(fmaf(__uint_as_float(rs[x]), p.scale_log2, slot[qa]));
+                d0 = p0 * fmaf(__uint_as_float(rp[x]), p.scale, slot[128 + qa]);
+              }
+              if (qa + 1 >= q_first) {
+                p1 = ex2f(fmaf(__uint_as_float(rs[x + 1]), p.scale_log2, slot[qa + 1]));
+                d1 = p1 * fmaf(__uint_as_float(rp[x + 1]), p.scale, slot[128 + qa + 1]);
+              }
+              const __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), d = __floats2bfloat162_rn(d0, d1);
+              wp[x >> 1] = *reinterpret_cast<const uint32_t*>(&a);
+              wd[x >> 1] = *reinterpret_cast<const uint32_t*>(&d);
+            }
+          }
+          store_cols16(spt, row, col, wp);
+          store_cols16(sdst, row, col, wd);
+        };
+        const int c0 = half * 64;
+        uint32_t sa[16], pa[16], sb[16], pb[16];
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0, sa);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0, pa);
         ptx::tmem_wait_ld();
-        uint32_t pk_p[16], pk_d[16];
-        // Keys past the end need no mask (their rows of dK / dV are never stored and no other row depends on
-        // them); only the causal diagonal does.  Packed path: two scores per instruction.
-        if (__all_sync(0xffffffffu, q_first <= c * 32)) {
-          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), sc2 = make_float2(p.scale, p.scale);
-#pragma unroll
-          for (int x = 0; x < 32; x += 4) {
-            const int qa = c * 32 + x;
-            const float4 nl = *reinterpret_cast<const float4*>(slot + qa);
-            const float4 nd = *reinterpret_cast<const float4*>(slot + 128 + qa);
-            const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(rs[x]), __uint_as_float(rs[x + 1])), sl2,
-                                         make_float2(nl.x, nl.y));
-            const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(rs[x + 2]), __uint_as_float(rs[x + 3])), sl2,
-                                         make_float2(nl.z, nl.w));
-            const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(rp[x]), __uint_as_float(rp[x + 1])), sc2,
-                                         make_float2(nd.x, nd.y));
-            const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(rp[x + 2]), __uint_as_float(rp[x + 3])), sc2,
-                                         make_float2(nd.z, nd.w));
-            const float2 p0 = make_float2(ex2f(e0.x), ex2f(e0.y)), p1 = make_float2(ex2f(e1.x), ex2f(e1.y));
-            const float2 d0 = __fmul2_rn(p0, t0), d1 = __fmul2_rn(p1, t1);
-            const __nv_bfloat162 a0 = __floats2bfloat162_rn(p0.x, p0.y), a1 = __floats2bfloat162_rn(p1.x, p1.y);
-            const __nv_bfloat162 b0 = __floats2bfloat162_rn(d0.x, d0.y), b1 = __floats2bfloat162_rn(d1.x, d1.y);
-            pk_p[x >> 1] = *reinterpret_cast<const uint32_t*>(&a0);
-            pk_p[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&a1);
-            pk_d[x >> 1] = *reinterpret_cast<const uint32_t*>(&b0);
-            pk_d[(x >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&b1);
-          }
-        } else {
-#pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-            const int qa = c * 32 + x;
-            if (qa >= q_first) {
-              p0 = ex2f(fmaf(__uint_as_float(rs[x]), p.scale_log2, slot[qa]));
-              d0 = p0 * fmaf(__uint_as_float(rp[x]), p.scale, slot[128 + qa]);
-            }
-            if (qa + 1 >= q_first) {
-              p1 = ex2f(fmaf(__uint_as_float(rs[x + 1]), p.scale_log2, slot[qa + 1]));
-              d1 = p1 * fmaf(__uint_as_float(rp[x + 1]), p.scale, slot[128 + qa + 1]);
-            }
-            const __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1), d = __floats2bfloat162_rn(d0, d1);
-            pk_p[x >> 1] = *reinterpret_cast<const uint32_t*>(&a);
-            pk_d[x >> 1] = *reinterpret_cast<const uint32_t*>(&d);
-          }
-        }
-        store_chunk(spt, row, c, pk_p);
-        store_chunk(sdst, row, c, pk_d);
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 16, sb);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 16, pb);
+        batch(c0, sa, pa);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 32, sa);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 32, pa);
+        batch(c0 + 16, sb, pb);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32b_x16(t_s + t_row + c0 + 48, sb);
+        ptx::tmem_ld_32x32b_x16(t_dp + t_row + c0 + 48, pb);
+        batch(c0 + 32, sa, pa);
+        ptx::tmem_wait_ld();
+        batch(c0 + 48, sb, pb);
       }
       ptx::tc_fence_before();
       ptx::fence_proxy_async_smem();

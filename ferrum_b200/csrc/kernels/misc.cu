@@ -350,18 +350,18 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, const long l
 // BatchNorm1d over [rows, cols] fp32.  Column statistics come from full-grid passes (a block = 128 columns x a
 // chunk of rows, lanes own 4 adjacent columns with 16-byte loads, warps walk the rows four at a time, partials
 // meet in shared memory and leave with one atomicAdd per column per block), so a 1024-feature layer uses the
-// whole GPU instead of 32 blocks.  Training forward = mean pass, centred second-moment pass (two-pass variance:
-// no cancellation), finalize, apply; backward = one two-statistic pass (d_beta, d_gamma) and one elementwise pass.
-//   MODE 0: a += x                          b unused
-//   MODE 1: a += (x - mean)^2               b unused
+// whole GPU instead of 32 blocks.  Training forward = ONE statistics pass (sums of x - k and (x - k)^2 with k = the
+// column's first row: shifted data, so the variance is not a difference of two large numbers), finalize, apply;
+// backward = one two-statistic pass (d_beta, d_gamma) and one elementwise pass.
 //   MODE 2: a += dy, b += dy * (x - mean) * rstd
+//   MODE 3: a += x - k, b += (x - k)^2      k = x[0, column] (read by the kernel; `mean` unused)
 template <int MODE>
 __global__ void __launch_bounds__(256)
 bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mean,
                    const float* __restrict__ rstd, float* __restrict__ out_a, float* __restrict__ out_b,
                    long long rows, int cols, long long rows_per_block) {
   __shared__ float sm_a[8][128];
-  __shared__ float sm_b[MODE == 2 ? 8 : 1][128];
+  __shared__ float sm_b[MODE >= 2 ? 8 : 1][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = blockIdx.x * 128 + lane * 4;
   const long long r_lo = static_cast<long long>(blockIdx.y) * rows_per_block;
@@ -369,25 +369,25 @@ bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, co
   const bool vec = (cols % 4 == 0) && (c0 + 3 < cols);
   float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
   float mu[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
-  if (MODE != 0) {
+  {
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       if (c0 + j < cols) {
-        mu[j] = mean[c0 + j];
+        mu[j] = MODE == 3 ? x[c0 + j] : mean[c0 + j];
         if (MODE == 2) rs[j] = rstd[c0 + j];
       }
   }
   auto accum = [&](const float (&xv)[4], const float (&gv)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (MODE == 0) a[j] += xv[j];
-      if (MODE == 1) {
-        const float d = xv[j] - mu[j];
-        a[j] = fmaf(d, d, a[j]);
-      }
       if (MODE == 2) {
         a[j] += gv[j];
         b[j] = fmaf(gv[j], (xv[j] - mu[j]) * rs[j], b[j]);
+      }
+      if (MODE == 3) {
+        const float d = xv[j] - mu[j];
+        a[j] += d;
+        b[j] = fmaf(d, d, b[j]);
       }
     }
   };
@@ -403,7 +403,7 @@ bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, co
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        if (MODE == 0 && r + 8 * u >= r_hi) continue;  // padded rows equal the mean: no effect in modes 1, 2
+        // padded rows equal the shift / the mean: no effect
         const float xa[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
         const float ga[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
         accum(xa, ga);
@@ -412,27 +412,19 @@ bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, co
   } else {
     for (long long r = r_lo + warp; r < r_hi; r += 8) {
       float xa[4] = {mu[0], mu[1], mu[2], mu[3]}, ga[4] = {0.f, 0.f, 0.f, 0.f};
-      bool any = false;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         if (c0 + j < cols) {
           xa[j] = x[r * cols + c0 + j];
           if (MODE == 2) ga[j] = dy[r * cols + c0 + j];
-          any = true;
         }
-      if (MODE == 0 && !any) continue;
-      if (MODE == 0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (c0 + j >= cols) xa[j] = 0.f;
-      }
       accum(xa, ga);
     }
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     sm_a[warp][lane * 4 + j] = a[j];
-    if (MODE == 2) sm_b[warp][lane * 4 + j] = b[j];
+    if (MODE >= 2) sm_b[warp][lane * 4 + j] = b[j];
   }
   __syncthreads();
   if (threadIdx.x < 128) {
@@ -441,26 +433,25 @@ bn_colstats_kernel(const float* __restrict__ x, const float* __restrict__ dy, co
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
       ta += sm_a[w][threadIdx.x];
-      if (MODE == 2) tb += sm_b[w][threadIdx.x];
+      if (MODE >= 2) tb += sm_b[w][threadIdx.x];
     }
     if (c < cols) {
       atomicAdd(out_a + c, ta);
-      if (MODE == 2) atomicAdd(out_b + c, tb);
+      if (MODE >= 2) atomicAdd(out_b + c, tb);
     }
   }
 }
 
-// stage 0: mean <- sum / rows.   stage 1: rstd <- rsqrt(m2 / rows + eps), running statistics.
+// mean holds sum(x - k), rstd holds sum((x - k)^2), k = x0[column] (the first row): both statistics and the
+// running buffers are finished here.
 __global__ void bn_finalize_kernel(float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ running_mean,
                                    float* __restrict__ running_var, long long rows, int cols, float eps,
-                                   float momentum, int stage) {
+                                   float momentum, const float* __restrict__ x0) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
-  if (stage == 0) {
-    mean[c] = mean[c] / static_cast<float>(rows);
-    return;
-  }
-  const float var = rstd[c] / static_cast<float>(rows);
+  const float m = mean[c] / static_cast<float>(rows);  // mean of the shifted data
+  const float var = fmaxf(rstd[c] / static_cast<float>(rows) - m * m, 0.f);
+  mean[c] = x0[c] + m;
   rstd[c] = rsqrtf(var + eps);
   if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean[c];
   if (running_var) {
@@ -747,11 +738,9 @@ extern "C" int fb_batchnorm_fwd(const float* x, const float* gamma, const float*
     long long rpb = 0;
     const dim3 grid = bn_stats_grid(rows, cols, &rpb);
     const int fgrid = (cols + 255) / 256;
-    bn_colstats_kernel<0><<<grid, 256, 0, stream>>>(x, nullptr, nullptr, nullptr, save_mean, nullptr, rows, cols, rpb);
-    bn_finalize_kernel<<<fgrid, 256, 0, stream>>>(save_mean, save_rstd, nullptr, nullptr, rows, cols, eps, momentum, 0);
-    bn_colstats_kernel<1><<<grid, 256, 0, stream>>>(x, nullptr, save_mean, nullptr, save_rstd, nullptr, rows, cols, rpb);
+    bn_colstats_kernel<3><<<grid, 256, 0, stream>>>(x, nullptr, nullptr, nullptr, save_mean, save_rstd, rows, cols, rpb);
     bn_finalize_kernel<<<fgrid, 256, 0, stream>>>(save_mean, save_rstd, running_mean, running_var, rows, cols, eps,
-                                                  momentum, 1);
+                                                  momentum, x);
     bn_apply_kernel<<<apply_grid, 256, 0, stream>>>(x, gamma, beta, save_mean, save_rstd, y, rows, cols, eps, 0);
   } else {
     bn_apply_kernel<<<apply_grid, 256, 0, stream>>>(x, gamma, beta, running_mean, running_var, y, rows, cols, eps, 1);

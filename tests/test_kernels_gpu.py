@@ -277,6 +277,22 @@ def test_batchnorm_train_and_eval():
     assert torch.allclose(ye, yer, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("rows,cols,offset", [(8192, 1024, 0.0), (4100, 130, 300.0), (33, 7, -50.0)])
+def test_batchnorm_one_pass_statistics_survive_a_large_mean(rows, cols, offset):
+    """The statistics come from one pass over the shifted data x - x[0]; a column mean far from zero must not cost
+    the variance its digits (sum of squares minus squared sum of the raw data would)."""
+    F = _F()
+    torch.manual_seed(9)
+    x = torch.randn(rows, cols, device="cuda") * 0.5 + offset
+    rm, rv = torch.zeros(cols, device="cuda"), torch.ones(cols, device="cuda")
+    y = F.batch_norm(x, None, None, rm, rv, True, 1.0, 1e-5)
+    xd = x.double()
+    ref = (xd - xd.mean(0)) / torch.sqrt(xd.var(0, unbiased=False) + 1e-5)
+    assert (y.double() - ref).abs().max().item() < 2e-3
+    assert torch.allclose(rm.double(), xd.mean(0), atol=1e-4 * max(1.0, abs(offset)))
+    assert torch.allclose(rv.double(), xd.var(0, unbiased=True), rtol=2e-3)
+
+
 def test_cast_transpose_gather_colsum():
     F = _F()
     x = torch.randn(130, 77, device="cuda")
