@@ -52,6 +52,23 @@ __device__ __forceinline__ void shard_bounds(long long n, int world, int rank, l
   hi = min(n, lo + per);
 }
 
+// One 16-byte group of the shard, all ranks summed (used for the ends that the 32-byte main loop leaves over).
+template <bool MC, int W>
+__device__ __forceinline__ float4 rs_group4(const fb_dist_ctx& c, long long grad_off, long long i4) {
+  if (MC) return ptx::multimem_ld_reduce_add_f4(reinterpret_cast<const float4*>(c.mc_arena + grad_off) + i4);
+  float4 g = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[0] + grad_off) + i4);
+#pragma unroll
+  for (int r = 1; r < W; ++r)
+    if (r < c.world) {
+      const float4 q = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + grad_off) + i4);
+      g.x += q.x; g.y += q.y; g.z += q.z; g.w += q.w;
+    }
+  return g;
+}
+
+// Peer-load form: 32 bytes per load instruction, marked evict-first in L2 and not allocated in L1 — the gradients
+// stream past once while the GEMMs that run beside this kernel live on operand tiles cached in L2.  Ranks are read
+// in groups of at most four so that U x 4 x 32 bytes are in flight per thread within the register budget.
 template <bool MC, int U, int W>
 __device__ void rs_body(const fb_dist_ctx& c, int vblock, int nvblocks, const RsArgs& a, int* s_fail) {
   const uint32_t epoch = a.dev_epoch != nullptr ? *a.dev_epoch : a.epoch;
@@ -61,41 +78,71 @@ __device__ void rs_body(const fb_dist_ctx& c, int vblock, int nvblocks, const Rs
   const long long n4 = (hi - lo) >> 2, lo4 = lo >> 2;
   const long long stride = static_cast<long long>(nvblocks) * blockDim.x;
   float4* mine = reinterpret_cast<float4*>(c.arena[c.rank] + a.grad_off) + lo4;
-  for (long long base = static_cast<long long>(vblock) * blockDim.x + threadIdx.x; base < n4; base += stride * U) {
-    float4 g[U];
-    if (MC) {
+  const long long tid = static_cast<long long>(vblock) * blockDim.x + threadIdx.x;
+  if (MC) {
+    for (long long base = tid; base < n4; base += stride * U) {
+      float4 g[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i4 = base + u * stride;
         if (i4 < n4)
           g[u] = ptx::multimem_ld_reduce_add_f4(reinterpret_cast<const float4*>(c.mc_arena + a.grad_off) + lo4 + i4);
       }
-    } else {
-      float4 part[U][W];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i4 = base + u * stride;
-        if (i4 < n4) {
+        if (i4 < n4) mine[i4] = make_float4(g[u].x * a.scale, g[u].y * a.scale, g[u].z * a.scale, g[u].w * a.scale);
+      }
+    }
+    return;
+  }
+  // 16-byte groups before the first 32-byte boundary (0 or 1; the arenas share their alignment) and after the last
+  const long long head = min(n4, static_cast<long long>((reinterpret_cast<uintptr_t>(mine) >> 4) & 1));
+  const long long n8 = (n4 - head) >> 1;
+  if (tid < head || (tid == 1 && head + 2 * n8 < n4)) {
+    const long long i4 = tid < head ? 0 : n4 - 1;
+    const float4 g = rs_group4<false, W>(c, a.grad_off, lo4 + i4);
+    mine[i4] = make_float4(g.x * a.scale, g.y * a.scale, g.z * a.scale, g.w * a.scale);
+  }
+  constexpr int kG = W < 4 ? W : 4;  // ranks per group of loads
+  const long long off8 = (lo4 + head) * 16;  // byte offset of the first 32-byte group inside the gradient region
+  for (long long base = tid; base < n8; base += stride * U) {
+    ptx::f8 acc[U];
 #pragma unroll
-          for (int r = 0; r < W; ++r)
-            if (r < c.world)
-              part[u][r] = ptx::ld_relaxed_sys_f4(reinterpret_cast<const float4*>(c.arena[r] + a.grad_off) + lo4 + i4);
+    for (int r0 = 0; r0 < W; r0 += kG) {
+      if (r0 >= c.world) break;
+      ptx::f8 part[U][kG];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i8 = base + u * stride;
+        if (i8 < n8) {
+#pragma unroll
+          for (int r = 0; r < kG; ++r)
+            if (r0 + r < c.world)
+              part[u][r] = ptx::ld_relaxed_sys_f8_stream(c.arena[r0 + r] + a.grad_off + off8 + i8 * 32);
         }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        g[u] = part[u][0];
 #pragma unroll
-        for (int r = 1; r < W; ++r)
-          if (r < c.world) {
-            g[u].x += part[u][r].x; g[u].y += part[u][r].y; g[u].z += part[u][r].z; g[u].w += part[u][r].w;
+        for (int r = 0; r < kG; ++r)
+          if (r0 + r < c.world) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              if (r0 + r == 0) acc[u].v[e] = part[u][r].v[e];
+              else acc[u].v[e] += part[u][r].v[e];
+            }
           }
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long i4 = base + u * stride;
-      if (i4 < n4) mine[i4] = make_float4(g[u].x * a.scale, g[u].y * a.scale, g[u].z * a.scale, g[u].w * a.scale);
+      const long long i8 = base + u * stride;
+      if (i8 < n8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u].v[e] *= a.scale;
+        ptx::st_f8_stream(c.arena[c.rank] + a.grad_off + off8 + i8 * 32, acc[u]);
+      }
     }
   }
 }
@@ -302,8 +349,8 @@ extern "C" int fb_dist_reduce_scatter_shard(const fb_dist_ctx* ctx, int use_mc, 
   RsArgs a{channel, epoch, dev_epoch, grad_off, n, scale};
   // bytes in flight per thread = U x world x 16 (peer loads): deeper unrolling for small worlds
   if (use_mc) rs_kernel<true, 4, 1><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
-  else if (ctx->world <= 2) rs_kernel<false, 4, 2><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
-  else if (ctx->world <= 4) rs_kernel<false, 2, 4><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
+  else if (ctx->world <= 2) rs_kernel<false, 2, 2><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
+  else if (ctx->world <= 4) rs_kernel<false, 1, 4><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
   else rs_kernel<false, 1, FB_MAX_RANKS><<<nblocks, nthreads, 0, stream>>>(*ctx, a);
   int rc = static_cast<int>(cudaGetLastError());
   if (rc == 0 && dev_epoch != nullptr) {

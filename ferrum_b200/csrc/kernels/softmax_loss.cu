@@ -280,7 +280,7 @@ ce_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, fl
 // elements in registers (K vectors of 8), so the row is read once, exp is evaluated once per element and the
 // three reductions are warp shuffles without a block barrier.
 template <int K>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, K <= 4 ? 4 : (K <= 8 ? 2 : 1))
 ce_warp_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                float* __restrict__ row_loss, __nv_bfloat16* __restrict__ dlogits, long long rows, int cols,
                float grad_scale, int32_t* bstatus) {
