@@ -100,7 +100,7 @@ def _cases(small: bool):
     bx = torch.randn(R, 1024, device=dev)
     bg_, bb_ = torch.ones(1024, device=dev), torch.zeros(1024, device=dev)
     rm, rv = torch.zeros(1024, device=dev), torch.ones(1024, device=dev)
-    case("batchnorm_fwd_f32", lambda: F.batch_norm(bx, bg_, bb_, rm, rv, True), R * 1024 * 4 * 4, "K8 (3 reads + 1 write)")
+    case("batchnorm_fwd_f32", lambda: F.batch_norm(bx, bg_, bb_, rm, rv, True), R * 1024 * 4 * 3, "K8 (one statistics pass + apply: 2 reads + 1 write)")
     case("dropout_fwd_bf16", lambda: F.dropout(xb, 0.1, True, seed=1), n * 5, "K9 (+1 B mask)")
 
     V, D, S, Bt = 50000, 1024, 256, 128 if small else 512
