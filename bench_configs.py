@@ -46,7 +46,10 @@ def cpu_ref(a):
         return x.ctypes.data_as(ctypes.c_void_p)
 
     if a.config == "xor":
-        exe = "/root/reference/target/release/examples/train_xor"
+        # the reference checkout: FERRUM_REFERENCE_ROOT, else a directory named "reference" beside this repository
+        ref_root = os.environ.get("FERRUM_REFERENCE_ROOT") or os.path.join(
+            os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "reference")
+        exe = os.path.join(ref_root, "target", "release", "examples", "train_xor")
         if os.path.exists(exe):
             ts = []
             for _ in range(10):

@@ -68,6 +68,22 @@ def test_dataloader_batches_drop_last_shuffle():
     assert list(col) == [5, 5]
 
 
+@pytest.mark.parametrize("width", [1024, 68, 65, 130])
+def test_dataloader_native_rows_of_every_width_arrive_intact(width):
+    """Rows of 256 bytes and more leave the worker threads with non-temporal stores in 64-byte pieces (plus an
+    ordinary tail); narrower rows and rows that start off a 16-byte boundary take the plain copy.  4096, 272, 260 and
+    520 bytes per row cover the four cases."""
+    x = torch.arange(300 * width, dtype=torch.float32).view(300, width)
+    ds = data.TensorDataset.from_tensors(x, torch.arange(300))
+    loader = data.DataLoader(ds).batch_size(32).shuffle(True).seed(3).num_workers(4)
+    seen = 0
+    for a, b in loader:
+        assert torch.equal(a._t, x[b._t])
+        seen += b._t.numel()
+    assert seen == 300
+    loader.close()
+
+
 def test_dataloader_native_worker_path_matches_the_plain_path():
     """Stacked host tensors + ``num_workers > 0``: rows are gathered by the host library's worker threads into a
     ring of staging slots.  Same batches as the single-threaded path for the same seed, ragged last batch,
