@@ -188,6 +188,18 @@ def _cases(small: bool):
          "K16 (batched tcgen05 QK^T, row softmax, batched PV; bytes = score matrix written + read twice + q, k, v, o)")
     case("attention_flash_fwd_bf16_S1024_D64", lambda: F.flash_attention(qa, ka, va, Da ** -0.5),
          4 * Ba * Ha * Sa * Da * 2, "K16 blockwise tcgen05 attention (bytes = q, k, v, o only)")
+    q128, k128, v128 = (torch.randn(Ba, Sa, Ha // 2, 128, device=dev).to(bf).permute(0, 2, 1, 3) for _ in range(3))
+
+    def attn128():
+        import ferrum_b200 as fb
+        with fb.autocast():
+            p_ = F.softmax(F.bmm_scaled(q128, k128.transpose(-1, -2), 128 ** -0.5), -1)
+            return F.bmm_scaled(p_, v128, 1.0, heads_inner=True)
+
+    case("attention_fwd_bf16_S1024_D128", attn128, Ba * (Ha // 2) * Sa * Sa * 2 * 4 + 4 * Ba * (Ha // 2) * Sa * 128 * 2,
+         "K16 head dimension 128, 8 heads (batched tcgen05 QK^T, row softmax, batched PV)")
+    case("attention_flash_fwd_bf16_S1024_D128", lambda: F.flash_attention(q128, k128, v128, 128 ** -0.5),
+         4 * Ba * (Ha // 2) * Sa * 128 * 2, "K16 blockwise tcgen05 attention, head dimension 128 (bytes = q, k, v, o only)")
     # training direction: forward + backward of the attention core, gradients with respect to q, k, v
     go = torch.randn(Ba, Sa, Ha, Da, device=dev).to(bf).permute(0, 2, 1, 3)  # laid out like the outputs
     import ferrum_b200 as fb

@@ -188,9 +188,9 @@ int fb_embedding_bwd_sorted(const void* dout, const long long* sorted_idx, const
 // Blockwise attention forward (tcgen05, head dimension 64, bf16): out[B, Sq, H, 64] = softmax(scale q k^T) v for
 // [B, H, S, 64] views given by element strides; lse (optional) [B, H, Sq].  -2: operand not describable by TMA.
 int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int Sq, int Skv,
-                     long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
-                     long long v_sb, long long v_sh, long long v_ss, float scale, int causal, int32_t* status,
-                     cudaStream_t stream);
+                     int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh,
+                     long long k_ss, long long v_sb, long long v_sh, long long v_ss, float scale, int causal,
+                     int32_t* status, cudaStream_t stream);
 // Gradients of the blockwise attention (attention_bwd.cu): out / d_out [B, Sq, H, 64] contiguous bf16, lse as written
 // by fb_attention_fwd, delta = [B, H, Sq] fp32 scratch filled by the call; dq [B, Sq, H, 64], dk / dv [B, Skv, H, 64].
 int fb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out,

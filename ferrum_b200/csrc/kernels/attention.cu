@@ -1,12 +1,13 @@
-// Blockwise (flash-style) attention forward on the tcgen05 tensor cores, head dimension 64, bf16.
+// Blockwise (flash-style) attention forward on the tcgen05 tensor cores, head dimension 64 or 128, bf16.
 //
 // The reference materialises the [S, S] score matrix per head on the host (ferrum-nn/src/transformer.rs:127-220).
 // This kernel never writes scores to memory: one CTA owns 128 query rows of one (batch, head) and walks the keys /
 // values in tiles of 128:
 //
 //   warp 0      TMA producer: Q once, then K_j into a two-stage shared-memory ring and V_j into a single buffer
-//               (128-byte swizzle); 97 KB of shared memory and 256 tensor-memory columns, so two CTAs share an SM
-//               and one CTA's softmax runs while the other's MMAs and loads are in flight
+//               (128-byte swizzle; a 128-wide head is two 64-column blocks per tile).  Head dimension 64: 97 KB of
+//               shared memory and 256 tensor-memory columns, so two CTAs share an SM and one CTA's softmax runs
+//               while the other's MMAs and loads are in flight; head dimension 128: 161 KB, one CTA per SM
 //   warp 1      one thread issues the MMAs: S = Q K_j^T (128 x 128 x 64) into tensor memory, later
 //               O_j = P_j V_j (128 x 64 x 128) into a second tensor-memory region
 //   warps 2-5   softmax: thread = query row.  Reads its row of S from tensor memory (tcgen05.ld), keeps the running
@@ -30,16 +31,23 @@
 namespace fb {
 namespace {
 
-constexpr int kD = 64;            // head dimension
 constexpr int kBQ = 128;          // query rows per CTA
 constexpr int kBKV = 128;         // keys per tile
-constexpr int kTileBytes = 128 * kD * 2;  // 16 KB: 128 rows of 64 bf16 = 128-byte rows
+constexpr int kBlk = 128 * 128;   // 16 KB: 128 rows of 64 bf16 = one 128-byte-swizzled block
 constexpr int kAttnThreads = 192;
-constexpr int kAttnSmem = kTileBytes * (1 + 2 + 1) + 2 * kTileBytes + 1024 + 256;  // Q, K x2, V, P (two k-blocks)
-constexpr int kTmemColsAttn = 256;  // S: columns 0..127, O_j: columns 128..191
+constexpr int kTmemColsAttn = 256;  // S: columns 0..127, O_j: columns 128..(128 + D - 1)
+// D = head dimension (64 or 128): an operand tile is D / 64 blocks side by side in the reduction (Q, K) or output (V)
+// dimension; P is always 128 x 128 = two blocks.
+template <int D>
+struct AttnCfg {
+  static constexpr int kNB = D / 64;
+  static constexpr int kTile = kNB * kBlk;
+  static constexpr int kSmem = kTile * (1 + 2 + 1) + 2 * kBlk + 1024 + 256;  // Q, K x2, V, P
+  static constexpr int kCtasPerSm = D == 64 ? 2 : 1;
+};
 
 struct AttnArgs {
-  __nv_bfloat16* out;   // [B, Sq, H, 64]
+  __nv_bfloat16* out;   // [B, Sq, H, D]
   float* lse;           // [B, H, Sq] or NULL
   int B, H, Sq, Skv;
   float scale_log2;     // softmax scale * log2(e)
@@ -54,16 +62,18 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, AttnCfg<D>::kCtasPerSm)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kNB = AttnCfg<D>::kNB, kTileBytes = AttnCfg<D>::kTile;
   uint8_t* sq = smem;
   uint8_t* sk = sq + kTileBytes;            // two stages
   uint8_t* sv = sk + 2 * kTileBytes;        // one buffer
   uint8_t* sp = sv + kTileBytes;            // P: two k-blocks of 128 rows x 128 bytes
-  uint8_t* bar_base = sp + 2 * kTileBytes;
+  uint8_t* bar_base = sp + 2 * kBlk;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* k_full = q_full + 1;    // [2]
   uint64_t* k_empty = k_full + 2;   // [2]
@@ -112,7 +122,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       ptx::mbar_arrive_expect_tx(q_full, kTileBytes);
-      ptx::tma_load_4d(sq, &map_q, q_full, 0, q0, h, b);
+#pragma unroll
+      for (int nb = 0; nb < kNB; ++nb) ptx::tma_load_4d(sq + nb * kBlk, &map_q, q_full, nb * 64, q0, h, b);
       uint32_t phase = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
@@ -121,13 +132,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           break;
         }
         ptx::mbar_arrive_expect_tx(&k_full[st], kTileBytes);
-        ptx::tma_load_4d(sk + st * kTileBytes, &map_k, &k_full[st], 0, j * kBKV, h, b);
+#pragma unroll
+        for (int nb = 0; nb < kNB; ++nb)
+          ptx::tma_load_4d(sk + st * kTileBytes + nb * kBlk, &map_k, &k_full[st], nb * 64, j * kBKV, h, b);
         if (!ptx::mbar_wait(v_empty, (j & 1) ^ 1u, abort_flag, p.timeout_ns)) {        // P_(j-1) V_(j-1) is done
           report_status(p.status, kStatusGemmTimeout, 57, blockIdx.x, j);
           break;
         }
         ptx::mbar_arrive_expect_tx(v_full, kTileBytes);
-        ptx::tma_load_4d(sv, &map_v, v_full, 0, j * kBKV, h, b);
+#pragma unroll
+        for (int nb = 0; nb < kNB; ++nb) ptx::tma_load_4d(sv + nb * kBlk, &map_v, v_full, nb * 64, j * kBKV, h, b);
         if (st == 1) phase ^= 1u;
       }
     }
@@ -135,15 +149,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = ptx::make_idesc(1u, kBQ, kBKV, 0, 0);   // Q, K both K-major
-      const uint32_t idesc_o = ptx::make_idesc(1u, kBQ, kD, 0, 1);     // P K-major, V with d contiguous (MN-major)
+      const uint32_t idesc_o = ptx::make_idesc(1u, kBQ, D, 0, 1);      // P K-major, V with d contiguous (MN-major)
       const uint32_t t_s = tmem_base, t_o = tmem_base + 128;
       const uint32_t sq_a = ptx::smem_u32(sq), sp_a = ptx::smem_u32(sp);
       auto issue_s = [&](int st) {
         const uint32_t sk_a = ptx::smem_u32(sk + st * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k)
-          ptx::umma_f16(t_s, ptx::make_smem_desc_sw128(sq_a + k * 32, 16, 1024),
-                        ptx::make_smem_desc_sw128(sk_a + k * 32, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        for (int k = 0; k < D / 16; ++k)
+          ptx::umma_f16(t_s, ptx::make_smem_desc_sw128(sq_a + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024),
+                        ptx::make_smem_desc_sw128(sk_a + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), idesc_s,
+                        k != 0 ? 1u : 0u);
         ptx::umma_commit(s_full);
         ptx::umma_commit(&k_empty[st]);  // the K slot is free once these MMAs have read it
       };
@@ -164,8 +179,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t sv_a = ptx::smem_u32(sv);
 #pragma unroll
         for (int k = 0; k < kBKV / 16; ++k)
-          ptx::umma_f16(t_o, ptx::make_smem_desc_sw128(sp_a + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024),
-                        ptx::make_smem_desc_sw128(sv_a + k * 2048, 8192, 1024), idesc_o, k != 0 ? 1u : 0u);
+          // V: 16 keys (rows of 128 bytes) per MMA; its 64-column blocks lie kBlk apart (the leading-dimension offset)
+          ptx::umma_f16(t_o, ptx::make_smem_desc_sw128(sp_a + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024),
+                        ptx::make_smem_desc_sw128(sv_a + k * 2048, kBlk, 1024), idesc_o, k != 0 ? 1u : 0u);
         ptx::umma_commit(o_full);
         ptx::umma_commit(v_empty);
         if (j + 1 < n_tiles) {
@@ -185,9 +201,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int row = quarter * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     float m = -INFINITY, l = 0.f;
-    float o[kD];
+    float o[D];
 #pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const bool ready = ptx::mbar_wait(s_full, j & 1, abort_flag, p.timeout_ns);
@@ -222,7 +238,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float alpha = ex2(m - m_new);  // 0 for the first tile (m = -inf)
       l *= alpha;
 #pragma unroll
-      for (int i = 0; i < kD; ++i) o[i] *= alpha;
+      for (int i = 0; i < D; ++i) o[i] *= alpha;
       // pass 2: p = 2^(s * scale - m_new), row sum, bf16 P into shared memory (K-major, 128-byte swizzle)
       const float neg_m = -m_new;
 #pragma unroll 1
@@ -246,7 +262,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         l += part;
         // 32 columns = four 16-byte chunks; chunk index inside the 64-column k-block: (c & 1) * 4 + q
-        uint8_t* blk = sp + (c >> 1) * kTileBytes + row * 128;
+        uint8_t* blk = sp + (c >> 1) * kBlk + row * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int chunk = (c & 1) * 4 + q;
@@ -268,7 +284,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       ptx::tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32b_x32(t_row + 128 + c * 32, r);
         ptx::tmem_wait_ld();
@@ -280,9 +296,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int qrow = q0 + row;
     if (ok && qrow < p.Sq) {
       const float inv = 1.f / l;
-      __nv_bfloat16* dst = p.out + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * kD;
+      __nv_bfloat16* dst = p.out + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * D;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
+      for (int q = 0; q < D / 8; ++q) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -329,9 +345,10 @@ EncodeTiledFnA encode_fn_a() {
   return fn;
 }
 
-// [B, H, S, 64] bf16 view with element strides (sb, sh, ss), last dimension contiguous: a 4-D map with a
-// 64 x 128 x 1 x 1 box; rows past S read zeros.
-bool make_map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long sb, long long sh, long long ss) {
+// [B, H, S, D] bf16 view with element strides (sb, sh, ss), last dimension contiguous: a 4-D map with a
+// 64 x 128 x 1 x 1 box (one 64-column block of 128 rows); rows past S read zeros.
+bool make_map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, int kD, long long sb, long long sh,
+                   long long ss) {
   EncodeTiledFnA enc = encode_fn_a();
   if (enc == nullptr) return false;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || ss % 8 || ss < kD) return false;
@@ -343,37 +360,46 @@ bool make_map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long 
                         static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh_ok) * 2,
                            static_cast<cuuint64_t>(sb_ok) * 2};
-  cuuint32_t box[4] = {kD, 128, 1, 1};
+  cuuint32_t box[4] = {64, 128, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-}  // namespace
-}  // namespace fb
-
-// out[b, s, h, :] = softmax(scale * q[b,h,s,:] . k[b,h,:,:]^T) v[b,h,:,:]  for head dimension 64, bf16 operands given
-// as [B, H, S, 64] views with element strides (last dimension contiguous, strides multiples of 8).  out is
-// [B, Sq, H, 64] contiguous; lse (optional) [B, H, Sq] fp32.  Returns -2 when an operand cannot be described by a
-// TMA map.  causal: query i sees keys j <= i + (Skv - Sq); key tiles past the diagonal are skipped.
-extern "C" int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H,
-                                int Sq, int Skv, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
-                                long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss,
-                                float scale, int causal, int32_t* status, cudaStream_t stream) {
-  using namespace fb;
-  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || (causal && Skv < Sq)) return -1;
-  if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
-  CUtensorMap mq, mk, mv;
-  if (!make_map_bhsd(&mq, q, B, H, Sq, q_sb, q_sh, q_ss) || !make_map_bhsd(&mk, k, B, H, Skv, k_sb, k_sh, k_ss) ||
-      !make_map_bhsd(&mv, v, B, H, Skv, v_sb, v_sh, v_ss))
-    return -2;
+template <int D>
+int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a,
+                cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnCfg<D>::kSmem) !=
+        cudaSuccess)
       return static_cast<int>(cudaGetLastError());
     attr_set = true;
   }
+  const dim3 grid((a.Sq + kBQ - 1) / kBQ, a.B * a.H);
+  attn_fwd_kernel<D><<<grid, kAttnThreads, AttnCfg<D>::kSmem, stream>>>(mq, mk, mv, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace fb
+
+// out[b, s, h, :] = softmax(scale * q[b,h,s,:] . k[b,h,:,:]^T) v[b,h,:,:]  for head dimension D = 64 or 128, bf16
+// operands given as [B, H, S, D] views with element strides (last dimension contiguous, strides multiples of 8).
+// out is [B, Sq, H, D] contiguous; lse (optional) [B, H, Sq] fp32.  Returns -2 when an operand cannot be described
+// by a TMA map.  causal: query i sees keys j <= i + (Skv - Sq); key tiles past the diagonal are skipped.
+extern "C" int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H,
+                                int Sq, int Skv, int D, long long q_sb, long long q_sh, long long q_ss,
+                                long long k_sb, long long k_sh, long long k_ss, long long v_sb, long long v_sh,
+                                long long v_ss, float scale, int causal, int32_t* status, cudaStream_t stream) {
+  using namespace fb;
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || (causal && Skv < Sq) || (D != 64 && D != 128)) return -1;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
+  CUtensorMap mq, mk, mv;
+  if (!make_map_bhsd(&mq, q, B, H, Sq, D, q_sb, q_sh, q_ss) || !make_map_bhsd(&mk, k, B, H, Skv, D, k_sb, k_sh, k_ss) ||
+      !make_map_bhsd(&mv, v, B, H, Skv, D, v_sb, v_sh, v_ss))
+    return -2;
   AttnArgs a;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.lse = lse;
@@ -385,7 +411,5 @@ extern "C" int fb_attention_fwd(const void* q, const void* k, const void* v, voi
   a.causal = causal ? 1 : 0;
   a.status = status;
   a.timeout_ns = 2000000000ull;
-  const dim3 grid((Sq + kBQ - 1) / kBQ, B * H);
-  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, a);
-  return static_cast<int>(cudaGetLastError());
+  return D == 64 ? launch_attn<64>(mq, mk, mv, a, stream) : launch_attn<128>(mq, mk, mv, a, stream);
 }

@@ -563,35 +563,38 @@ def bmm_scaled(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, heads_inner
     return scalar_op(out, "mul", float(alpha)) if alpha != 1.0 else out
 
 
-def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_no_grad: bool = True) -> bool:
-    """True when ``flash_attention`` can take these ``[B, H, S, 64]`` operands: CUDA, head dimension 64 contiguous,
-    other strides multiples of 8 elements and (``need_no_grad``) no gradient needed — the kernel is forward-only."""
-    if not (q.is_cuda and q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and q.shape[-1] == 64):
+def flash_attention_ok(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_no_grad: bool = True,
+                       head_dims=(64, 128)) -> bool:
+    """True when ``flash_attention`` can take these ``[B, H, S, D]`` operands: CUDA, head dimension 64 or 128
+    (``head_dims``) contiguous, other strides multiples of 8 elements and (``need_no_grad``) no gradient needed —
+    the kernel records no autograd node."""
+    if not (q.is_cuda and q.dim() == 4 and k.dim() == 4 and v.dim() == 4 and q.shape[-1] in head_dims):
         return False
+    D = q.shape[-1]
     if need_no_grad and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
         return False
-    if k.shape != v.shape or q.shape[:2] != k.shape[:2] or k.shape[-1] != 64:
+    if k.shape != v.shape or q.shape[:2] != k.shape[:2] or k.shape[-1] != D:
         return False
     for t in (q, k, v):
-        if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.stride(2) < 64:
+        if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.stride(2) < D:
             return False
     return True
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                     return_lse: bool = False, causal: bool = False):
-    """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, 64]`` operands without materialising the score matrix:
-    one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  No autograd node is recorded here
-    (:func:`attention_blockwise` is the differentiable form).  ``causal``: query ``i`` sees
+    """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, D]`` operands (D = 64 or 128) without materialising the
+    score matrix: one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  No autograd node is recorded
+    here (:func:`attention_blockwise` is the differentiable form for D = 64).  ``causal``: query ``i`` sees
     keys ``j <= i + (Skv - Sq)`` and key tiles past the diagonal are skipped.  The result is stored as
-    ``[B, Sq, H, 64]`` and returned as the ``[B, H, Sq, 64]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
-    B, H, Sq, _ = q.shape
+    ``[B, Sq, H, D]`` and returned as the ``[B, H, Sq, D]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
+    B, H, Sq, D = q.shape
     Skv = k.shape[2]
     qb, kb, vb = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (q.detach(), k.detach(), v.detach()))
-    out = torch.empty((B, Sq, H, 64), device=q.device, dtype=torch.bfloat16)
+    out = torch.empty((B, Sq, H, D), device=q.device, dtype=torch.bfloat16)
     lse = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32) if return_lse else None
     rc = _lib.cuda().fb_attention_fwd(qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), out.data_ptr(),
-                                      lse.data_ptr() if lse is not None else None, B, H, Sq, Skv,
+                                      lse.data_ptr() if lse is not None else None, B, H, Sq, Skv, D,
                                       qb.stride(0), qb.stride(1), qb.stride(2), kb.stride(0), kb.stride(1),
                                       kb.stride(2), vb.stride(0), vb.stride(1), vb.stride(2), float(scale),
                                       1 if causal else 0, _rt.status_ptr(), _stream())

@@ -133,16 +133,16 @@ def test_transformer_encoder_layer_trains_under_autocast():
     assert losses[-1] < 0.5 * losses[0]
 
 
-@pytest.mark.parametrize("B,H,Sq,Skv", [(2, 3, 128, 128), (1, 2, 256, 384), (2, 2, 200, 200), (1, 4, 64, 1000),
-                                        (1, 16, 1024, 1024)])
-def test_flash_attention_forward_matches_softmax_attention(B, H, Sq, Skv):
+@pytest.mark.parametrize("B,H,Sq,Skv,D", [(2, 3, 128, 128, 64), (1, 2, 256, 384, 64), (2, 2, 200, 200, 64),
+                                          (1, 4, 64, 1000, 64), (1, 16, 1024, 1024, 64), (2, 3, 128, 128, 128),
+                                          (1, 2, 200, 333, 128), (1, 8, 1024, 1024, 128)])
+def test_flash_attention_forward_matches_softmax_attention(B, H, Sq, Skv, D):
     """Blockwise tcgen05 attention (online softmax, scores never materialised) against fp32 softmax(QK^T)V, with
-    head-interleaved [B, S, H, D] storage, ragged sequence lengths and several key tiles."""
+    head-interleaved [B, S, H, D] storage, ragged sequence lengths, several key tiles and both head dimensions."""
     from ferrum_b200.ops import functional as F
     from ferrum_b200.utils.runtime import check_status
 
     torch.manual_seed(B * 7 + Sq + Skv)
-    D = 64
     q = (torch.randn(B, Sq, H, D, device="cuda") * 0.8).bfloat16().permute(0, 2, 1, 3)
     k = (torch.randn(B, Skv, H, D, device="cuda") * 0.8).bfloat16().permute(0, 2, 1, 3)
     v = torch.randn(B, Skv, H, D, device="cuda").bfloat16().permute(0, 2, 1, 3)
@@ -200,15 +200,15 @@ def test_memory_efficient_attention_gradients_match_the_materialising_path():
         assert _rel(a, b) < 3e-2, _rel(a, b)
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("B,H,Sq,Skv", [(1, 2, 256, 256), (2, 2, 200, 300), (1, 3, 128, 640), (1, 1, 384, 384)])
-def test_flash_attention_causal(B, H, Sq, Skv):
+def test_flash_attention_causal(B, H, Sq, Skv, D):
     """Causal (bottom-right aligned) masking inside the blockwise kernel: key tiles past the diagonal are skipped,
     the diagonal tiles masked per row, also when the offset Skv - Sq is not a multiple of the tile."""
     from ferrum_b200.ops import functional as F
     from ferrum_b200.utils.runtime import check_status
 
     torch.manual_seed(Sq + Skv)
-    D = 64
     q = torch.randn(B, H, Sq, D, device="cuda").bfloat16()
     k = torch.randn(B, H, Skv, D, device="cuda").bfloat16()
     v = torch.randn(B, H, Skv, D, device="cuda").bfloat16()
@@ -311,3 +311,32 @@ def test_backward_kernels_work_as_the_first_cuda_work_of_the_autograd_thread():
             "print('ok')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+def test_multihead_attention_head_dimension_128_uses_the_blockwise_forward():
+    """Head dimension 128: inference under autocast runs the blockwise kernel, training with memory_efficient=True
+    recomputes the scores in the backward pass; both agree with the batched-GEMM path."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    torch.manual_seed(5)
+    ref = nn.MultiHeadAttention(256, 2, device=fb.Device.Cuda(0))
+    eff = copy.deepcopy(ref)
+    eff.memory_efficient = True
+    x = torch.randn(2, 160, 256, device="cuda")
+    with fb.autocast(), torch.no_grad():
+        y_fast = eff(x).float()           # no gradient needed: the blockwise kernel
+    outs, grads = [], []
+    for m in (ref, eff):
+        xi = x.clone().requires_grad_(True)
+        with fb.autocast():
+            y = m(xi)
+        (y.float() * torch.linspace(-1, 1, y.numel(), device="cuda").reshape(y.shape)).sum().backward()
+        outs.append(y.float().detach())
+        grads.append([xi.grad] + [p.grad for p in m.torch_parameters()])
+    fb.utils.runtime.check_status()
+    assert _rel(y_fast, outs[0]) < 2e-2 and _rel(outs[1], outs[0]) < 2e-2
+    for a, b in zip(grads[1], grads[0]):
+        assert _rel(a, b) < 3e-2, _rel(a, b)
