@@ -129,6 +129,28 @@ def test_conv2d_implicit_gemm_forward_backward_matches_fp32(B, cin, cout, H, W, 
     _close(x.grad, xr.grad, 2e-4), _close(conv.weight.grad, wr.grad, 2e-4), _close(conv.bias.grad, br.grad, 2e-4)
 
 
+def test_conv1d_under_autocast_takes_the_implicit_gemm():
+    """Conv1d is a one-row Conv2d: under autocast with stride 1 it runs on the implicit-GEMM kernels (patch 128 x 1)."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+
+    torch.manual_seed(12)
+    conv = nn.Conv1d(24, 40, 5, 1, 2, 1, 1, device=fb.Device.Cuda(0))
+    x = torch.randn(3, 24, 301, device="cuda", requires_grad=True)
+    with fb.autocast():
+        y = conv(x)
+    r16 = lambda t: t.detach().bfloat16().float()
+    xr, wr = r16(x).requires_grad_(True), r16(conv.weight).requires_grad_(True)
+    br = conv.bias.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.conv1d(xr, wr, br, 1, 2, 1, 1)
+    _close(y, yr, 2e-4)
+    g = torch.randn_like(yr).bfloat16().float()
+    y.backward(g)
+    yr.backward(g)
+    fb.utils.runtime.check_status()
+    _close(x.grad, xr.grad, 2e-4), _close(conv.weight.grad, wr.grad, 2e-4), _close(conv.bias.grad, br.grad, 2e-4)
+
+
 def test_im2col_rows_are_gemm_ready():
     from ferrum_b200.ops import functional as F
 
