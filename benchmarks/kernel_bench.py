@@ -215,6 +215,22 @@ def _cases(small: bool):
     def attn_train_blockwise():
         return torch.autograd.grad(F.attention_blockwise(qg, kg, vg, Da ** -0.5), (qg, kg, vg), go)
 
+    q128g, k128g, v128g = (t.detach().clone().requires_grad_(True) for t in (q128, k128, v128))
+    go128 = torch.randn(Ba, Sa, Ha // 2, 128, device=dev).to(bf).permute(0, 2, 1, 3)
+
+    def attn128_train_materialised():
+        with fb.autocast():
+            p_ = F.softmax(F.bmm_scaled(q128g, k128g.transpose(-1, -2), 128 ** -0.5), -1)
+            out = F.bmm_scaled(p_, v128g, 1.0, heads_inner=True)
+            return torch.autograd.grad(out, (q128g, k128g, v128g), go128)
+
+    case("attention_fwd_bwd_materialised_bf16_S1024_D128", attn128_train_materialised,
+         Ba * (Ha // 2) * Sa * Sa * 2 * 10 + 12 * Ba * (Ha // 2) * Sa * 128 * 2,
+         "K16 head dimension 128: forward + backward through the stored S x S probabilities")
+    case("attention_fwd_bwd_blockwise_bf16_S1024_D128",
+         lambda: torch.autograd.grad(F.attention_blockwise(q128g, k128g, v128g, 128 ** -0.5), (q128g, k128g, v128g),
+                                     go128),
+         12 * Ba * (Ha // 2) * Sa * 128 * 2, "K16 head dimension 128: blockwise tcgen05 forward + backward")
     case("attention_fwd_bwd_materialised_bf16_S1024_D64", attn_train_materialised,
          Ba * Ha * Sa * Sa * 2 * 10 + 12 * Ba * Ha * Sa * Da * 2,
          "K16 forward + backward through the stored S x S probabilities (batched GEMMs, softmax and its backward)")

@@ -162,7 +162,7 @@ _CUDA_SIGS = {
     "fb_embedding_bwd_sorted": (I, [P, P, P, P, LL, I, I, F, LL, LL, I, P]),
     "fb_gather_rows": (I, [P, P, P, LL, LL, LL, P, P]),
     "fb_attention_fwd": (I, [P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL, F, I, P, P]),
-    "fb_attention_bwd": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL, F, I, P, P]),
+    "fb_attention_bwd": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL, F, I, P, P]),
     # optimizers
     "fb_adam_flat": (I, [P, P, P, P, P, LL, AdamH, P]),
     "fb_sgd_flat": (I, [P, P, P, P, LL, SgdH, P]),

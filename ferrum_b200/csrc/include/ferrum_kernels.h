@@ -191,11 +191,11 @@ int fb_attention_fwd(const void* q, const void* k, const void* v, void* out, flo
                      int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh,
                      long long k_ss, long long v_sb, long long v_sh, long long v_ss, float scale, int causal,
                      int32_t* status, cudaStream_t stream);
-// Gradients of the blockwise attention (attention_bwd.cu): out / d_out [B, Sq, H, 64] contiguous bf16, lse as written
-// by fb_attention_fwd, delta = [B, H, Sq] fp32 scratch filled by the call; dq [B, Sq, H, 64], dk / dv [B, Skv, H, 64].
+// Gradients of the blockwise attention (attention_bwd.cu), D = 64 or 128: out / d_out [B, Sq, H, D] contiguous bf16, lse as
+// written by fb_attention_fwd, delta = [B, H, Sq] fp32 scratch filled by the call; dq [B, Sq, H, D], dk / dv [B, Skv, H, D].
 int fb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out,
                      const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Sq, int Skv,
-                     long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
+                     int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
                      long long v_sb, long long v_sh, long long v_ss, float scale, int causal, int32_t* status,
                      cudaStream_t stream);
 int fb_attention_bwd_map_error(void);

@@ -36,21 +36,36 @@
 namespace fb {
 namespace {
 
-constexpr int kD = 64;
 constexpr int kT = 128;                     // rows of a query tile = rows of a key tile
-constexpr int kTile = kT * kD * 2;          // 16 KB: 128 rows of 64 bf16
-constexpr int kPBytes = 2 * kTile;          // a 128 x 128 bf16 matrix: two k-blocks of 128 rows x 128 bytes
+constexpr int kBlk = kT * 128;              // 16 KB: 128 rows of 64 bf16 = one 128-byte-swizzled block
+constexpr int kPBytes = 2 * kBlk;           // a 128 x 128 bf16 matrix: two k-blocks of 128 rows x 128 bytes
 constexpr int kBwdThreads = 320;            // TMA warp, MMA warp, eight softmax warps
 constexpr int kSoftmaxWarps = 8;            // two per tensor-memory lane quarter, 64 of the tile's 128 columns each
-constexpr int kSmemDq = 2 * kTile + 2 * kTile + 2 * kTile + kPBytes + 1024 + 256;           // Q dO | K x2 | V x2 | dS
-constexpr int kSmemDkv = 2 * kTile + 2 * kTile + 2 * kTile + 2 * kPBytes + 8192 + 1024 + 256;  // K V | Q x2 | dO x2 | P^T dS^T | lse, delta
 constexpr int kTmemBwd = 512;
+// D = head dimension (64 or 128).  An operand tile (128 rows x D) is D / 64 blocks side by side.  With D = 64 the
+// tiles that change per iteration sit in a two-stage ring; with D = 128 shared memory (160 KB / 206 KB) and tensor
+// memory (dK/dV: all 512 columns) leave room for one stage only.
+template <int D>
+struct BwdCfg {
+  static constexpr int kNB = D / 64;
+  static constexpr int kTile = kNB * kBlk;
+  static constexpr int kStages = D == 64 ? 2 : 1;
+  static constexpr int kSmemDq = 2 * kTile + 2 * kStages * kTile + kPBytes + 1024 + 256;  // Q dO | K | V | dS
+  static constexpr int kSmemDkv = 2 * kTile + 2 * kStages * kTile + 2 * kPBytes + 8192 + 1024 + 256;  // K V | Q | dO | P^T dS^T | lse, delta
+};
+
+// One operand tile: D / 64 boxes of 64 columns x 128 rows.
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int b) {
+#pragma unroll
+  for (int nb = 0; nb < D / 64; ++nb) ptx::tma_load_4d(dst + nb * kBlk, map, bar, nb * 64, row0, h, b);
+}
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdArgs {
-  __nv_bfloat16* dq;   // [B, Sq, H, 64]
-  __nv_bfloat16* dk;   // [B, Skv, H, 64]
-  __nv_bfloat16* dv;   // [B, Skv, H, 64]
+  __nv_bfloat16* dq;   // [B, Sq, H, D]
+  __nv_bfloat16* dk;   // [B, Skv, H, D]
+  __nv_bfloat16* dv;   // [B, Skv, H, D]
   const float* lse;    // [B, H, Sq] natural log
   const float* delta;  // [B, H, Sq]
   int B, H, Sq, Skv;
@@ -66,35 +81,36 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-// 128 x 128 x 64 product of two K-major tiles (rows x 64 d): the score shape.
+// 128 x 128 x D product of two K-major tiles (rows x D): the score shape.
+template <int D>
 __device__ __forceinline__ void mma_scores(uint32_t tmem, uint32_t a, uint32_t b, uint32_t idesc) {
 #pragma unroll
-  for (int k = 0; k < kD / 16; ++k)
-    ptx::umma_f16(tmem, ptx::make_smem_desc_sw128(a + k * 32, 16, 1024), ptx::make_smem_desc_sw128(b + k * 32, 16, 1024),
-                  idesc, k != 0 ? 1u : 0u);
+  for (int k = 0; k < D / 16; ++k)
+    ptx::umma_f16(tmem, ptx::make_smem_desc_sw128(a + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024),
+                  ptx::make_smem_desc_sw128(b + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), idesc, k != 0 ? 1u : 0u);
 }
-// 128 x 64 x 128 product: A = a 128 x 128 matrix in two K-major k-blocks, B = a 128 x 64 tile whose 64 columns are
-// contiguous (MN-major): the P V shape of the forward kernel.
+// 128 x D x 128 product: A = a 128 x 128 matrix in two K-major k-blocks, B = a 128 x D tile whose D columns are
+// contiguous (MN-major; its 64-column blocks lie kBlk apart): the P V shape of the forward kernel.
 __device__ __forceinline__ void mma_pv(uint32_t tmem, uint32_t a, uint32_t b, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int k = 0; k < kT / 16; ++k)
-    ptx::umma_f16(tmem, ptx::make_smem_desc_sw128(a + (k >> 2) * kTile + (k & 3) * 32, 16, 1024),
-                  ptx::make_smem_desc_sw128(b + k * 2048, 8192, 1024), idesc, (accumulate || k != 0) ? 1u : 0u);
+    ptx::umma_f16(tmem, ptx::make_smem_desc_sw128(a + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024),
+                  ptx::make_smem_desc_sw128(b + k * 2048, kBlk, 1024), idesc, (accumulate || k != 0) ? 1u : 0u);
 }
 
 // 16 columns (8 bf16 pairs) of one row, starting at column col (a multiple of 16): two 16-byte chunks of the row's
 // 128-byte line in k-block (col >> 6), swizzled.
 __device__ __forceinline__ void store_cols16(uint8_t* mat, int row, int col, const uint32_t (&w)[8]) {
-  uint8_t* blk = mat + (col >> 6) * kTile + row * 128;
+  uint8_t* blk = mat + (col >> 6) * kBlk + row * 128;
   const int chunk = (col & 63) >> 3;
   *reinterpret_cast<uint4*>(blk + (((chunk) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
   *reinterpret_cast<uint4*>(blk + (((chunk + 1) ^ (row & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-// One 64-column accumulator row from tensor memory to 64 bf16 in global memory.  The tensor-memory loads are
+// Chunks c_lo .. c_hi - 1 (32 columns each) of an accumulator row from tensor memory to bf16 in global memory.  The tensor-memory loads are
 // warp-wide (.sync.aligned): EVERY lane of the warp must call this, `valid` only predicates the stores.
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row, bool valid, int c_lo = 0,
-                                               int c_hi = 2) {
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem_row, bool valid, int c_lo,
+                                               int c_hi) {
 #pragma unroll 1
   for (int c = c_lo; c < c_hi; ++c) {
     uint32_t r[32];
@@ -116,17 +132,19 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, uint32_t tmem
 }
 
 // ------------------------------------------------------------------------------------------------ dQ
+template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                    const BwdArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kTile = BwdCfg<D>::kTile, kStages = BwdCfg<D>::kStages;
   uint8_t* sq = smem;
   uint8_t* sdo = sq + kTile;
-  uint8_t* sk = sdo + kTile;       // two stages
-  uint8_t* sv = sk + 2 * kTile;    // two stages
-  uint8_t* sds = sv + 2 * kTile;   // dS: 128 x 128 bf16
+  uint8_t* sk = sdo + kTile;             // kStages stages
+  uint8_t* sv = sk + kStages * kTile;    // kStages stages
+  uint8_t* sds = sv + kStages * kTile;   // dS: 128 x 128 bf16
   uint8_t* bar_base = sds + kPBytes;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* kv_full = q_full + 1;    // [2]
@@ -175,39 +193,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       ptx::mbar_arrive_expect_tx(q_full, 2 * kTile);
-      ptx::tma_load_4d(sq, &map_q, q_full, 0, q0, h, b);
-      ptx::tma_load_4d(sdo, &map_do, q_full, 0, q0, h, b);
-      uint32_t phase = 0;
+      load_tile<D>(sq, &map_q, q_full, q0, h, b);
+      load_tile<D>(sdo, &map_do, q_full, q0, h, b);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        if (!ptx::mbar_wait(&kv_empty[st], phase ^ 1u, abort_flag, p.timeout_ns)) {
+        const int st = j % kStages;
+        const uint32_t round = static_cast<uint32_t>(j / kStages) & 1u;
+        if (!ptx::mbar_wait(&kv_empty[st], round ^ 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 61, blockIdx.x, j);
           break;
         }
         ptx::mbar_arrive_expect_tx(&kv_full[st], 2 * kTile);
-        ptx::tma_load_4d(sk + st * kTile, &map_k, &kv_full[st], 0, j * kT, h, b);
-        ptx::tma_load_4d(sv + st * kTile, &map_v, &kv_full[st], 0, j * kT, h, b);
-        if (st == 1) phase ^= 1u;
+        load_tile<D>(sk + st * kTile, &map_k, &kv_full[st], j * kT, h, b);
+        load_tile<D>(sv + st * kTile, &map_v, &kv_full[st], j * kT, h, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = ptx::make_idesc(1u, kT, kT, 0, 0);
-      const uint32_t idesc_o = ptx::make_idesc(1u, kT, kD, 0, 1);
+      const uint32_t idesc_o = ptx::make_idesc(1u, kT, D, 0, 1);
       const uint32_t sq_a = ptx::smem_u32(sq), sdo_a = ptx::smem_u32(sdo), sds_a = ptx::smem_u32(sds);
       bool ok = ptx::mbar_wait(q_full, 0, abort_flag, p.timeout_ns);
       if (!ok) report_status(p.status, kStatusGemmTimeout, 62, blockIdx.x, 0);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int st = j & 1;
+        const int st = j % kStages;
         const uint32_t sk_a = ptx::smem_u32(sk + st * kTile), sv_a = ptx::smem_u32(sv + st * kTile);
-        if (!ptx::mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, p.timeout_ns)) {
+        if (!ptx::mbar_wait(&kv_full[st], static_cast<uint32_t>(j / kStages) & 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 63, blockIdx.x, j);
           break;
         }
         ptx::tc_fence_after();
         // (S and dP of the previous tile were read before its ds_full, which the previous iteration waited for)
-        mma_scores(t_s, sq_a, sk_a, idesc_s);
-        mma_scores(t_dp, sdo_a, sv_a, idesc_s);
+        mma_scores<D>(t_s, sq_a, sk_a, idesc_s);
+        mma_scores<D>(t_dp, sdo_a, sv_a, idesc_s);
         ptx::umma_commit(sp_full);
         if (!ptx::mbar_wait(ds_full, j & 1, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 64, blockIdx.x, j);
@@ -312,12 +329,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) report_status(p.status, kStatusGemmTimeout, 67, blockIdx.x, 0);
       } else {
         ptx::tc_fence_after();
-        __nv_bfloat16* dst = p.dq + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * kD;
-        if (n_tiles > 0) {  // uniform over the CTA; each warp of a quarter stores 32 of the 64 columns
-          store_row_bf16(dst, t_dq + t_row, qrow < p.Sq, half, half + 1);
+        __nv_bfloat16* dst = p.dq + ((static_cast<long long>(b) * p.Sq + qrow) * p.H + h) * D;
+        if (n_tiles > 0) {  // uniform over the CTA; each warp of a quarter stores half of the D columns
+          store_row_bf16(dst, t_dq + t_row, qrow < p.Sq, half * (D / 64), (half + 1) * (D / 64));
         } else if (qrow < p.Sq && half == 0) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) reinterpret_cast<uint4*>(dst)[q] = make_uint4(0u, 0u, 0u, 0u);
+          for (int q = 0; q < D / 8; ++q) reinterpret_cast<uint4*>(dst)[q] = make_uint4(0u, 0u, 0u, 0u);
         }
       }
     }
@@ -331,17 +348,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------------ dK, dV
+template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const BwdArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kTile = BwdCfg<D>::kTile, kStages = BwdCfg<D>::kStages;
   uint8_t* sk = smem;
   uint8_t* sv = sk + kTile;
-  uint8_t* sq = sv + kTile;        // two stages
-  uint8_t* sdo = sq + 2 * kTile;   // two stages
-  uint8_t* spt = sdo + 2 * kTile;  // P^T: 128 keys x 128 queries bf16
+  uint8_t* sq = sv + kTile;              // kStages stages
+  uint8_t* sdo = sq + kStages * kTile;   // kStages stages
+  uint8_t* spt = sdo + kStages * kTile;  // P^T: 128 keys x 128 queries bf16
   uint8_t* sdst = spt + kPBytes;   // dS^T
   float* s_stat = reinterpret_cast<float*>(sdst + kPBytes);  // per softmax warp: [lse2 | delta][128]
   uint8_t* bar_base = reinterpret_cast<uint8_t*>(s_stat) + 8192;
@@ -389,44 +408,43 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 320;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + D;
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
       ptx::mbar_arrive_expect_tx(kv_full, 2 * kTile);
-      ptx::tma_load_4d(sk, &map_k, kv_full, 0, k0, h, b);
-      ptx::tma_load_4d(sv, &map_v, kv_full, 0, k0, h, b);
-      uint32_t phase = 0;
+      load_tile<D>(sk, &map_k, kv_full, k0, h, b);
+      load_tile<D>(sv, &map_v, kv_full, k0, h, b);
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1, i = i_begin + it;
-        if (!ptx::mbar_wait(&qd_empty[st], phase ^ 1u, abort_flag, p.timeout_ns)) {
+        const int st = it % kStages, i = i_begin + it;
+        const uint32_t round = static_cast<uint32_t>(it / kStages) & 1u;
+        if (!ptx::mbar_wait(&qd_empty[st], round ^ 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 71, blockIdx.x, it);
           break;
         }
         ptx::mbar_arrive_expect_tx(&qd_full[st], 2 * kTile);
-        ptx::tma_load_4d(sq + st * kTile, &map_q, &qd_full[st], 0, i * kT, h, b);
-        ptx::tma_load_4d(sdo + st * kTile, &map_do, &qd_full[st], 0, i * kT, h, b);
-        if (st == 1) phase ^= 1u;
+        load_tile<D>(sq + st * kTile, &map_q, &qd_full[st], i * kT, h, b);
+        load_tile<D>(sdo + st * kTile, &map_do, &qd_full[st], i * kT, h, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_s = ptx::make_idesc(1u, kT, kT, 0, 0);
-      const uint32_t idesc_o = ptx::make_idesc(1u, kT, kD, 0, 1);
+      const uint32_t idesc_o = ptx::make_idesc(1u, kT, D, 0, 1);
       const uint32_t sk_a = ptx::smem_u32(sk), sv_a = ptx::smem_u32(sv);
       const uint32_t spt_a = ptx::smem_u32(spt), sdst_a = ptx::smem_u32(sdst);
       bool ok = ptx::mbar_wait(kv_full, 0, abort_flag, p.timeout_ns);
       if (!ok) report_status(p.status, kStatusGemmTimeout, 72, blockIdx.x, 0);
       for (int it = 0; ok && it < n_iter; ++it) {
-        const int st = it & 1;
+        const int st = it % kStages;
         const uint32_t sq_a = ptx::smem_u32(sq + st * kTile), sdo_a = ptx::smem_u32(sdo + st * kTile);
-        if (!ptx::mbar_wait(&qd_full[st], (it >> 1) & 1, abort_flag, p.timeout_ns)) {
+        if (!ptx::mbar_wait(&qd_full[st], static_cast<uint32_t>(it / kStages) & 1u, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 73, blockIdx.x, it);
           break;
         }
         ptx::tc_fence_after();
-        mma_scores(t_s, sk_a, sq_a, idesc_s);     // S^T  = K Q_i^T
-        mma_scores(t_dp, sv_a, sdo_a, idesc_s);   // dP^T = V dO_i^T
+        mma_scores<D>(t_s, sk_a, sq_a, idesc_s);     // S^T  = K Q_i^T
+        mma_scores<D>(t_dp, sv_a, sdo_a, idesc_s);   // dP^T = V dO_i^T
         ptx::umma_commit(sp_full);
         if (!ptx::mbar_wait(pt_full, it & 1, abort_flag, p.timeout_ns)) {
           report_status(p.status, kStatusGemmTimeout, 74, blockIdx.x, it);
@@ -554,10 +572,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (lane == 0) ptx::mbar_arrive(pt_full);
     }
     if (n_iter == 0 && krow < p.Skv && half == 0) {  // no query sees these keys
-      __nv_bfloat16* dv = p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
-      __nv_bfloat16* dk = p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD;
+      __nv_bfloat16* dv = p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * D;
+      __nv_bfloat16* dk = p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * D;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
+      for (int q = 0; q < D / 8; ++q) {
         reinterpret_cast<uint4*>(dv)[q] = make_uint4(0u, 0u, 0u, 0u);
         reinterpret_cast<uint4*>(dk)[q] = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -570,11 +588,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ptx::tc_fence_after();
         // the two warps of a lane quarter share the work: one stores the dV rows, the other the dK rows
         if (half == 0)
-          store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dv + t_row,
-                         krow < p.Skv);
+          store_row_bf16(p.dv + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * D, t_dv + t_row,
+                         krow < p.Skv, 0, D / 32);
         else
-          store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * kD, t_dk + t_row,
-                         krow < p.Skv);
+          store_row_bf16(p.dk + ((static_cast<long long>(b) * p.Skv + krow) * p.H + h) * D, t_dk + t_row,
+                         krow < p.Skv, 0, D / 32);
       }
     }
   }
@@ -586,16 +604,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   }
 }
 
-// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]  (both [B, S, H, 64] contiguous bf16); warp per row.
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]  (both [B, S, H, D] contiguous bf16); warp per row.
+template <int D>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   float* __restrict__ delta, int B, int H, int S) {
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;  // over B * S * H
   const int lane = threadIdx.x & 31;
   const long long rows = static_cast<long long>(B) * S * H;
   if (row >= rows) return;
-  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + row * kD)[lane];
-  const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + row * kD)[lane];
-  float acc = __bfloat162float(a.x) * __bfloat162float(g.x) + __bfloat162float(a.y) * __bfloat162float(g.y);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 64; ++i) {
+    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + row * D)[lane + 32 * i];
+    const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(d_o + row * D)[lane + 32 * i];
+    acc += __bfloat162float(a.x) * __bfloat162float(g.x) + __bfloat162float(a.y) * __bfloat162float(g.y);
+  }
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
   if (lane == 0) {
@@ -632,10 +655,11 @@ EncodeTiledFnB encode_fn_b() {
   return fn;
 }
 
-// [B, H, S, 64] bf16 view with element strides (sb, sh, ss): 4-D map, 64 x 128 x 1 x 1 box, rows past S read zeros.
+// [B, H, S, D] bf16 view with element strides (sb, sh, ss): 4-D map, 64 x 128 x 1 x 1 box, rows past S read zeros.
 int g_map_error = 0;  // why the last map_bhsd failed: -1 no driver entry point, -2 / -3 alignment, > 0 the driver's code
 
-bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long sb, long long sh, long long ss) {
+bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, int kD, long long sb, long long sh,
+              long long ss) {
   EncodeTiledFnB enc = encode_fn_b();
   g_map_error = -1;
   if (enc == nullptr) return false;
@@ -649,7 +673,7 @@ bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long 
                         static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh_ok) * 2,
                            static_cast<cuuint64_t>(sb_ok) * 2};
-  cuuint32_t box[4] = {kD, 128, 1, 1};
+  cuuint32_t box[4] = {64, 128, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   g_map_error = static_cast<int>(enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides,
                                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -663,39 +687,55 @@ bool map_bhsd(CUtensorMap* map, const void* ptr, int B, int H, int S, long long 
 // Reason of the last -2 ... -5 of fb_attention_bwd (see g_map_error).
 extern "C" int fb_attention_bwd_map_error() { return fb::g_map_error; }
 
-// Gradients of out = softmax(scale q k^T) v (head dimension 64, bf16).  q, k, v: [B, H, S, 64] views with element
-// strides (last dimension contiguous, strides multiples of 8); out, d_out: [B, Sq, H, 64] contiguous (the forward
-// kernel's output layout); lse: [B, H, Sq] fp32 as written by fb_attention_fwd; delta: [B, H, Sq] fp32 scratch that
-// this call fills.  dq: [B, Sq, H, 64], dk, dv: [B, Skv, H, 64], contiguous bf16.  Returns -2 when an operand
-// cannot be described by a TMA map.
+namespace fb {
+namespace {
+template <int D>
+int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+               const void* out, const void* d_out, const BwdArgs& a, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             BwdCfg<D>::kSmemDq) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             BwdCfg<D>::kSmemDkv) != cudaSuccess)
+      return static_cast<int>(cudaGetLastError());
+    attr_set = true;
+  }
+  const long long rows = static_cast<long long>(a.B) * a.Sq * a.H;
+  attn_delta_kernel<D><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out),
+      const_cast<float*>(a.delta), a.B, a.H, a.Sq);
+  attn_bwd_dq_kernel<D><<<dim3((a.Sq + kT - 1) / kT, a.B * a.H), kBwdThreads, BwdCfg<D>::kSmemDq, stream>>>(
+      mq, mk, mv, mdo, a);
+  attn_bwd_dkv_kernel<D><<<dim3((a.Skv + kT - 1) / kT, a.B * a.H), kBwdThreads, BwdCfg<D>::kSmemDkv, stream>>>(
+      mq, mk, mv, mdo, a);
+  return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+}  // namespace fb
+
+// Gradients of out = softmax(scale q k^T) v (head dimension D = 64 or 128, bf16).  q, k, v: [B, H, S, D] views with
+// element strides (last dimension contiguous, strides multiples of 8); out, d_out: [B, Sq, H, D] contiguous (the
+// forward kernel's output layout); lse: [B, H, Sq] fp32 as written by fb_attention_fwd; delta: [B, H, Sq] fp32
+// scratch that this call fills.  dq: [B, Sq, H, D], dk, dv: [B, Skv, H, D], contiguous bf16.  Returns -2 ... -5
+// when q / k / v / d_out cannot be described by a TMA map.
 extern "C" int fb_attention_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out,
                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Sq,
-                                int Skv, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                                int Skv, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                                 long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss,
                                 float scale, int causal, int32_t* status, cudaStream_t stream) {
   using namespace fb;
-  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || (causal && Skv < Sq)) return -1;
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0 || (causal && Skv < Sq) || (D != 64 && D != 128)) return -1;
   if (lse == nullptr || delta == nullptr || out == nullptr || d_out == nullptr) return -1;
   if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv) |
        reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(d_out)) & 15)
     return -1;
   CUtensorMap mq, mk, mv, mdo;
-  const long long o_sb = static_cast<long long>(Sq) * H * kD, o_sh = kD, o_ss = static_cast<long long>(H) * kD;
-  // -2: q, -3: k, -4: v, -5: d_out cannot be described by a TMA map (pointer / stride alignment)
-  if (!map_bhsd(&mq, q, B, H, Sq, q_sb, q_sh, q_ss)) return -2;
-  if (!map_bhsd(&mk, k, B, H, Skv, k_sb, k_sh, k_ss)) return -3;
-  if (!map_bhsd(&mv, v, B, H, Skv, v_sb, v_sh, v_ss)) return -4;
-  if (!map_bhsd(&mdo, d_out, B, H, Sq, o_sb, o_sh, o_ss)) return -5;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess)
-      return static_cast<int>(cudaGetLastError());
-    attr_set = true;
-  }
-  const long long rows = static_cast<long long>(B) * Sq * H;
-  attn_delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, B, H, Sq);
+  const long long o_sb = static_cast<long long>(Sq) * H * D, o_sh = D, o_ss = static_cast<long long>(H) * D;
+  if (!map_bhsd(&mq, q, B, H, Sq, D, q_sb, q_sh, q_ss)) return -2;
+  if (!map_bhsd(&mk, k, B, H, Skv, D, k_sb, k_sh, k_ss)) return -3;
+  if (!map_bhsd(&mv, v, B, H, Skv, D, v_sb, v_sh, v_ss)) return -4;
+  if (!map_bhsd(&mdo, d_out, B, H, Sq, D, o_sb, o_sh, o_ss)) return -5;
   BwdArgs a;
   a.dq = static_cast<__nv_bfloat16*>(dq);
   a.dk = static_cast<__nv_bfloat16*>(dk);
@@ -711,7 +751,6 @@ extern "C" int fb_attention_bwd(const void* q, const void* k, const void* v, con
   a.causal = causal ? 1 : 0;
   a.status = status;
   a.timeout_ns = 2000000000ull;
-  attn_bwd_dq_kernel<<<dim3((Sq + kT - 1) / kT, B * H), kBwdThreads, kSmemDq, stream>>>(mq, mk, mv, mdo, a);
-  attn_bwd_dkv_kernel<<<dim3((Skv + kT - 1) / kT, B * H), kBwdThreads, kSmemDkv, stream>>>(mq, mk, mv, mdo, a);
-  return static_cast<int>(cudaGetLastError());
+  return D == 64 ? launch_bwd<64>(mq, mk, mv, mdo, out, d_out, a, stream)
+                 : launch_bwd<128>(mq, mk, mv, mdo, out, d_out, a, stream);
 }

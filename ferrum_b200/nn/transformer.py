@@ -20,12 +20,11 @@ from .modules import LayerNorm, Linear, Module, tensor_io
 
 
 class MultiHeadAttention(Module):
-    """Under autocast with head dimension 64 and no explicit mask (``causal=True`` is fine) the attention core runs
-    on the blockwise tcgen05 kernels in both directions: no S x S matrix is stored for the backward pass, the
-    probabilities are recomputed tile by tile from one log-sum-exp per row.  Head dimension 128 has the blockwise
-    forward kernel (inference, and training with ``memory_efficient=True``, which recomputes the scores in the
-    backward pass); other head dimensions, explicit masks and fp32 precision take the batched-GEMM + softmax
-    path."""
+    """Under autocast with head dimension 64 or 128 and no explicit mask (``causal=True`` is fine) the attention core
+    runs on the blockwise tcgen05 kernels in both directions: no S x S matrix is stored for the backward pass, the
+    probabilities are recomputed tile by tile from one log-sum-exp per row.  Other head dimensions, explicit
+    masks and fp32 precision take the batched-GEMM + softmax path (``memory_efficient=True`` then recomputes the
+    scores in the backward pass where the blockwise forward applies)."""
 
     def __init__(self, embed_dim: int, num_heads: int, device=None, memory_efficient: bool = False):
         super().__init__()
@@ -61,8 +60,8 @@ class MultiHeadAttention(Module):
             # inference (no gradient needed), bf16: blockwise attention, the score matrix is never materialised
             ctx = F.flash_attention(q, k, v, 1.0 / math.sqrt(self.head_dim), causal=causal)
             return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))
-        if (mask is None and self.head_dim == 64 and config.low_precision_active()
-                and F.flash_attention_ok(q, k, v, need_no_grad=False, head_dims=(64,))):
+        if (mask is None and self.head_dim in (64, 128) and config.low_precision_active()
+                and F.flash_attention_ok(q, k, v, need_no_grad=False)):
             # training, bf16: blockwise forward AND backward, nothing of size S x S in memory
             ctx = F.attention_blockwise(q, k, v, 1.0 / math.sqrt(self.head_dim), causal=causal)
             return self.out_proj(ctx.transpose(1, 2).reshape(B, Sq, self.embed_dim))

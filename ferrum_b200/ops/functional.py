@@ -585,7 +585,7 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: fl
                     return_lse: bool = False, causal: bool = False):
     """``softmax(scale * q @ k^T) @ v`` for ``[B, H, S, D]`` operands (D = 64 or 128) without materialising the
     score matrix: one tcgen05 kernel with online softmax (csrc/kernels/attention.cu).  No autograd node is recorded
-    here (:func:`attention_blockwise` is the differentiable form for D = 64).  ``causal``: query ``i`` sees
+    here (:func:`attention_blockwise` is the differentiable form).  ``causal``: query ``i`` sees
     keys ``j <= i + (Skv - Sq)`` and key tiles past the diagonal are skipped.  The result is stored as
     ``[B, Sq, H, D]`` and returned as the ``[B, H, Sq, D]`` view (like ``bmm_scaled(..., heads_inner=True)``)."""
     B, H, Sq, D = q.shape
@@ -620,21 +620,21 @@ class _BlockwiseAttentionFn(Function):
     @staticmethod
     def backward(ctx, g):
         q, k, v, out, lse = ctx.saved_tensors
-        B, H, Sq, _ = q.shape
+        B, H, Sq, D = q.shape
         Skv = k.shape[2]
-        o = out.permute(0, 2, 1, 3)                      # the kernel's own [B, Sq, H, 64] storage
+        o = out.permute(0, 2, 1, 3)                      # the kernel's own [B, Sq, H, D] storage
         if not o.is_contiguous():
             o = o.contiguous()
         go = g.permute(0, 2, 1, 3)
         if go.dtype != torch.bfloat16 or not go.is_contiguous():
             go = go.to(torch.bfloat16).contiguous()
-        dq = torch.empty((B, Sq, H, 64), device=q.device, dtype=torch.bfloat16)
-        dk = torch.empty((B, Skv, H, 64), device=q.device, dtype=torch.bfloat16)
-        dv = torch.empty((B, Skv, H, 64), device=q.device, dtype=torch.bfloat16)
+        dq = torch.empty((B, Sq, H, D), device=q.device, dtype=torch.bfloat16)
+        dk = torch.empty((B, Skv, H, D), device=q.device, dtype=torch.bfloat16)
+        dv = torch.empty((B, Skv, H, D), device=q.device, dtype=torch.bfloat16)
         delta = torch.empty((B, H, Sq), device=q.device, dtype=torch.float32)
         rc = _lib.cuda().fb_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), go.data_ptr(),
                                           lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(),
-                                          dv.data_ptr(), B, H, Sq, Skv, q.stride(0), q.stride(1), q.stride(2),
+                                          dv.data_ptr(), B, H, Sq, Skv, D, q.stride(0), q.stride(1), q.stride(2),
                                           k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
                                           v.stride(2), float(ctx.scale), 1 if ctx.causal else 0, _rt.status_ptr(),
                                           _stream())
@@ -651,8 +651,8 @@ class _BlockwiseAttentionFn(Function):
 
 def attention_blockwise(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                         causal: bool = False) -> torch.Tensor:
-    """Differentiable blockwise attention for ``[B, H, S, 64]`` operands (see ``flash_attention_ok``): forward and
-    backward on the tcgen05 kernels, no S x S matrix in memory in either direction."""
+    """Differentiable blockwise attention for ``[B, H, S, D]`` operands, D = 64 or 128 (see ``flash_attention_ok``):
+    forward and backward on the tcgen05 kernels, no S x S matrix in memory in either direction."""
     return _BlockwiseAttentionFn.apply(q, k, v, float(scale), bool(causal))
 
 

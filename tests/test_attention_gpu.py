@@ -222,9 +222,10 @@ def test_flash_attention_causal(B, H, Sq, Skv, D):
     assert (out.float() - ref).abs().max().item() < 3e-2
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("B,H,Sq,Skv,causal", [(1, 2, 128, 128, False), (2, 3, 256, 384, False), (1, 2, 200, 200, True),
                                                (2, 2, 130, 333, False), (1, 4, 384, 512, True), (1, 1, 77, 77, True)])
-def test_blockwise_attention_backward_matches_fp32_reference(B, H, Sq, Skv, causal):
+def test_blockwise_attention_backward_matches_fp32_reference(B, H, Sq, Skv, causal, D):
     """dQ, dK, dV of the blockwise tcgen05 kernels (probabilities recomputed tile by tile from the saved row
     log-sum-exp) against PyTorch autograd in fp32 on the same bf16 operands: ragged sequence lengths, more keys than
     queries, causal masks with the diagonal inside a tile, head-interleaved (strided) operand views."""
@@ -232,7 +233,6 @@ def test_blockwise_attention_backward_matches_fp32_reference(B, H, Sq, Skv, caus
     from ferrum_b200.utils.runtime import check_status
 
     torch.manual_seed(B * 100 + Sq + Skv)
-    D = 64
     # operands as MultiHeadAttention produces them: [B, S, H * D] projections viewed as [B, H, S, D]
     q, k, v = (torch.randn(B, S, H * D, device="cuda").bfloat16().view(B, S, H, D).permute(0, 2, 1, 3)
                .requires_grad_(True) for S in (Sq, Skv, Skv))
@@ -314,8 +314,9 @@ def test_backward_kernels_work_as_the_first_cuda_work_of_the_autograd_thread():
 
 
 def test_multihead_attention_head_dimension_128_uses_the_blockwise_forward():
-    """Head dimension 128: inference under autocast runs the blockwise kernel, training with memory_efficient=True
-    recomputes the scores in the backward pass; both agree with the batched-GEMM path."""
+    """Head dimension 128 under autocast: the blockwise kernels in inference and in training (``eff``: with
+    ``memory_efficient`` set, which changes nothing where the blockwise backward applies) agree with the same module
+    run through an explicit all-true mask, i.e. the batched-GEMM path."""
     import copy
 
     import ferrum_b200 as fb
@@ -329,14 +330,18 @@ def test_multihead_attention_head_dimension_128_uses_the_blockwise_forward():
     with fb.autocast(), torch.no_grad():
         y_fast = eff(x).float()           # no gradient needed: the blockwise kernel
     outs, grads = [], []
+    everything = torch.ones(160, 160, dtype=torch.bool, device="cuda")
     for m in (ref, eff):
         xi = x.clone().requires_grad_(True)
         with fb.autocast():
-            y = m(xi)
+            y = m.forward_attn(xi, xi, xi, mask=everything) if m is ref else m(xi)
         (y.float() * torch.linspace(-1, 1, y.numel(), device="cuda").reshape(y.shape)).sum().backward()
         outs.append(y.float().detach())
         grads.append([xi.grad] + [p.grad for p in m.torch_parameters()])
     fb.utils.runtime.check_status()
     assert _rel(y_fast, outs[0]) < 2e-2 and _rel(outs[1], outs[0]) < 2e-2
+    # (the key projection's bias has a zero gradient in exact arithmetic — a constant added to every key shifts all
+    # scores of a row alike — so what both paths hold there is rounding noise: compare on the scale of all gradients)
+    top = max(g.abs().max().item() for g in grads[0])
     for a, b in zip(grads[1], grads[0]):
-        assert _rel(a, b) < 3e-2, _rel(a, b)
+        assert _rel(a, b) < 3e-2 or (a - b).abs().max().item() < 2e-3 * top, _rel(a, b)
