@@ -124,6 +124,8 @@ _CUDA_SIGS = {
     "fb_conv_wgrad": (I, [P, P, P] + [I] * 12 + [P, P]),
     "fb_nchw_to_nhwc_bf16": (I, [P, P, I, I, LL, I, P]),
     "fb_nhwc_to_nchw_f32": (I, [P, P, I, I, LL, LL, P]),
+    "fb_nchw_to_s2d_nhwc_bf16": (I, [P, P] + [I] * 10 + [LL, P]),
+    "fb_s2d_nhwc_to_nchw_f32": (I, [P, P] + [I] * 10 + [LL, P]),
     "fb_attention_bwd_map_error": (I, []),
     "fb_col2im": (I, [P, P] + [I] * 14 + [LL, P]),
     "fb_pool2d_fwd": (I, [P, P, P] + [I] * 10 + [I, P]),

@@ -209,6 +209,11 @@ int fb_conv_wgrad(const void* dy, const void* x, float* out, int B, int H, int W
                   int ph, int pw, int dh, int dw, int32_t* status, cudaStream_t stream);
 int fb_nchw_to_nhwc_bf16(const float* x, void* y, int B, int C, long long P, int Cp, cudaStream_t stream);
 int fb_nhwc_to_nchw_f32(const float* x, float* y, int B, int C, long long P, long long ld, cudaStream_t stream);
+// Space-to-depth layouts that turn a strided convolution into the stride-1 case of fb_conv_igemm (conv_layout.cu).
+int fb_nchw_to_s2d_nhwc_bf16(const float* x, void* z, int B, int C, int H, int W, int sh, int sw, int ph, int pw,
+                             int Hz, int Wz, long long ld, cudaStream_t stream);
+int fb_s2d_nhwc_to_nchw_f32(const float* z, float* x, int B, int C, int H, int W, int sh, int sw, int ph, int pw,
+                            int Hz, int Wz, long long ld, cudaStream_t stream);
 int fb_gather_rows(const void* src, const long long* idx, void* dst, long long n_idx, long long row_bytes,
                    long long n_rows, int32_t* status, cudaStream_t stream);
 

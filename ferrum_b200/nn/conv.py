@@ -1,8 +1,9 @@
 """Convolutions and pooling (ferrum-nn/src/conv.rs:9-497; forward-only host loops there).
 
-Under bf16 autocast a stride-1, ungrouped convolution runs as an implicit GEMM on the tensor cores in all three
-directions (``ops.functional._ConvIgemmFn``: NHWC bf16 activations read through 4-D TMA boxes shifted by the filter
-tap, no window matrix in memory).  Otherwise convolution is lowered to GEMM explicitly: an im2col kernel writes the input windows as a K-major matrix (one row per output
+Under bf16 autocast an ungrouped convolution runs as an implicit GEMM on the tensor cores in all three directions
+(``ops.functional._ConvIgemmFn``: NHWC bf16 activations read through 4-D TMA boxes shifted by the filter tap, no
+window matrix in memory; strided convolutions reach the same kernels through a space-to-depth layout,
+``_ConvS2dFn``; stride together with dilation takes the explicit path).  Otherwise convolution is lowered to GEMM explicitly: an im2col kernel writes the input windows as a K-major matrix (one row per output
 position) and the product with the flattened filters runs on this package's GEMM kernels (tcgen05 under bf16
 autocast, fp32 SIMT otherwise); the backward is the dgrad / wgrad GEMMs plus a gather-form col2im kernel.  Groups,
 dilation, stride and padding follow the reference; weights ~ U(+-1/sqrt(fan_in)).  Max / average pooling are
@@ -38,7 +39,7 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
         raise ShapeMismatch("conv2d", f"{Cg * groups} input channels", C)
     Ho, Wo = _out_hw(x, (kh, kw), stride, padding, dilation)
     if F.conv_igemm_ok(x, stride, dilation, padding, (kh, kw), groups):
-        return F.conv2d_igemm(x, weight, bias, padding, dilation)        # no window matrix: implicit GEMM
+        return F.conv2d_igemm(x, weight, bias, padding, dilation, stride)  # no window matrix: implicit GEMM
     cols = F.im2col(x, (kh, kw), stride, padding, dilation)              # [B*L, C*kh*kw], K contiguous
     L = Ho * Wo
     outs = []

@@ -1523,14 +1523,97 @@ class _ConvIgemmFn(Function):
         return dx, dwt, db, None, None
 
 
+class _ConvS2dFn(Function):
+    """Strided, undilated, ungrouped 2-D convolution on the implicit-GEMM kernels: the input goes through a
+    space-to-depth layout change (``z[b, I, J, (rh, rw, c)] = x[b, c, I * sh + rh - ph, J * sw + rw - pw]``), after
+    which the stride-(sh, sw) convolution with a kh x kw filter IS a stride-1 convolution with a
+    ceil(kh / sh) x ceil(kw / sw) filter over sh * sw * C channels (filter taps that do not exist are zero).  A
+    patch embedding (kernel = stride) becomes one plain GEMM."""
+
+    @staticmethod
+    def _geometry(x_shape, w_shape, stride, padding):
+        B, C, H, W = x_shape
+        O, _, kh, kw = w_shape
+        (sh, sw), (ph, pw) = stride, padding
+        Ho, Wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        k2h, k2w = -(-kh // sh), -(-kw // sw)
+        return Ho, Wo, k2h, k2w, Ho + k2h - 1, Wo + k2w - 1, _pad8(sh * sw * C)
+
+    @staticmethod
+    def _filters(weight, stride, k2h, k2w, Cz):
+        """[O, C, kh, kw] -> [O, k2h, k2w, Cz] fp32 in the channel order (rh, rw, c) of the space-to-depth input."""
+        O, C, kh, kw = weight.shape
+        sh, sw = stride
+        w = torch.zeros((O, C, k2h * sh, k2w * sw), device=weight.device, dtype=torch.float32)
+        w[:, :, :kh, :kw] = weight.detach().float()
+        w = w.view(O, C, k2h, sh, k2w, sw).permute(0, 2, 4, 3, 5, 1).reshape(O, k2h, k2w, sh * sw * C)
+        out = torch.zeros((O, k2h, k2w, Cz), device=weight.device, dtype=torch.float32)
+        out[..., :sh * sw * C] = w
+        return out
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding):
+        x = _f32(x).contiguous()
+        B, C, H, W = x.shape
+        O = weight.shape[0]
+        (sh, sw), (ph, pw) = stride, padding
+        Ho, Wo, k2h, k2w, Hz, Wz, Cz = _ConvS2dFn._geometry(x.shape, weight.shape, stride, padding)
+        z = torch.empty((B, Hz, Wz, Cz), device=x.device, dtype=torch.bfloat16)
+        _lib.check(_lib.cuda().fb_nchw_to_s2d_nhwc_bf16(x.data_ptr(), z.data_ptr(), B, C, H, W, sh, sw, ph, pw, Hz, Wz,
+                                                        Cz, _stream()), "fb_nchw_to_s2d_nhwc_bf16")
+        w2 = _ConvS2dFn._filters(weight, stride, k2h, k2w, Cz)
+        b = _f32(bias.detach()).contiguous() if bias is not None else None
+        y = _conv_igemm(z, w2.reshape(O, -1).to(torch.bfloat16), b, O, (k2h, k2w), (0, 0), (1, 1))
+        ctx.save_for_backward(z, weight)
+        ctx.geom = (x.shape, tuple(stride), tuple(padding), bias is not None)
+        return _to_nchw_f32(y, O)
+
+    @staticmethod
+    def backward(ctx, g):
+        z, weight = ctx.saved_tensors
+        x_shape, (sh, sw), (ph, pw), has_bias = ctx.geom
+        B, C, H, W = x_shape
+        O, _, kh, kw = weight.shape
+        Ho, Wo, k2h, k2w, Hz, Wz, Cz = _ConvS2dFn._geometry(x_shape, weight.shape, (sh, sw), (ph, pw))
+        gh = _to_nhwc_bf16(g)                                              # [B, Ho, Wo, Op]
+        Op = gh.shape[3]
+        lib = _lib.cuda()
+        dx = dwt = db = None
+        if ctx.needs_input_grad[0]:
+            w2 = _ConvS2dFn._filters(weight, (sh, sw), k2h, k2w, Cz)       # [O, k2h, k2w, Cz]
+            wt = torch.zeros((Cz, k2h, k2w, Op), device=g.device, dtype=torch.float32)
+            wt[..., :O] = w2.permute(3, 1, 2, 0).flip(1, 2)
+            dz = _conv_igemm(gh, wt.reshape(Cz, -1).to(torch.bfloat16), None, Cz, (k2h, k2w), (k2h - 1, k2w - 1), (1, 1))
+            dx = torch.empty(x_shape, device=g.device, dtype=torch.float32)
+            _lib.check(lib.fb_s2d_nhwc_to_nchw_f32(dz.data_ptr(), dx.data_ptr(), B, C, H, W, sh, sw, ph, pw, Hz, Wz, Cz,
+                                                   _stream()), "fb_s2d_nhwc_to_nchw_f32")
+        if ctx.needs_input_grad[1]:
+            splits = lib.fb_conv_wgrad_splits(B, Ho, Wo, O, Cz, k2h * k2w)
+            part = torch.empty((splits, O, k2h * k2w * Cz), device=g.device, dtype=torch.float32)
+            _lib.check(lib.fb_conv_wgrad(gh.data_ptr(), z.data_ptr(), part.data_ptr(), B, Hz, Wz, Cz, O, Op, k2h, k2w, 0, 0,
+                                         1, 1, _rt.status_ptr(), _stream()), "fb_conv_wgrad")
+            full = raw_reduce(part, "sum", 0) if splits > 1 else part[0]
+            d2 = full.reshape(O, k2h, k2w, Cz)[..., :sh * sw * C].reshape(O, k2h, k2w, sh, sw, C)
+            dwt = d2.permute(0, 5, 1, 3, 2, 4).reshape(O, C, k2h * sh, k2w * sw)[:, :, :kh, :kw].contiguous()
+        if has_bias and ctx.needs_input_grad[2]:
+            db = raw_colsum(gh.reshape(-1, Op))[:O]
+        return dx, dwt, db, None, None
+
+
 def conv_igemm_ok(x: torch.Tensor, stride, dilation, padding, kernel, groups: int) -> bool:
-    """True when ``conv2d`` can take the implicit-GEMM path: CUDA, bf16 autocast on, one group, stride 1 and a data
-    gradient whose padding ``dilation * (kernel - 1) - padding`` is not negative."""
-    return (_native(x) and x.dim() == 4 and config.low_precision_active() and groups == 1 and tuple(stride) == (1, 1)
-            and dilation[0] * (kernel[0] - 1) - padding[0] >= 0 and dilation[1] * (kernel[1] - 1) - padding[1] >= 0)
+    """True when ``conv2d`` can take the implicit-GEMM path: CUDA, bf16 autocast on, one group, and either stride 1
+    with a data gradient whose padding ``dilation * (kernel - 1) - padding`` is not negative, or any stride without
+    dilation (space-to-depth form)."""
+    if not (_native(x) and x.dim() == 4 and config.low_precision_active() and groups == 1):
+        return False
+    if tuple(stride) == (1, 1):
+        return (dilation[0] * (kernel[0] - 1) - padding[0] >= 0 and dilation[1] * (kernel[1] - 1) - padding[1] >= 0)
+    return tuple(dilation) == (1, 1) and padding[0] >= 0 and padding[1] >= 0
 
 
-def conv2d_igemm(x, weight, bias, padding=(0, 0), dilation=(1, 1)):
+def conv2d_igemm(x, weight, bias, padding=(0, 0), dilation=(1, 1), stride=(1, 1)):
+    if tuple(stride) != (1, 1):
+        return _ConvS2dFn.apply(x, weight, bias, tuple(stride), tuple(padding))
     return _ConvIgemmFn.apply(x, weight, bias, tuple(padding), tuple(dilation))
 
 

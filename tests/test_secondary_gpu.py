@@ -129,6 +129,40 @@ def test_conv2d_implicit_gemm_forward_backward_matches_fp32(B, cin, cout, H, W, 
     _close(x.grad, xr.grad, 2e-4), _close(conv.weight.grad, wr.grad, 2e-4), _close(conv.bias.grad, br.grad, 2e-4)
 
 
+@pytest.mark.parametrize("B,cin,cout,H,W,k,stride,pad", [
+    (2, 3, 5, 17, 19, (3, 3), (2, 2), (1, 1)),
+    (1, 4, 6, 16, 16, (4, 4), (4, 4), (0, 0)),          # patch embedding: kernel = stride, one plain GEMM
+    (2, 5, 7, 15, 20, (5, 3), (2, 3), (2, 1)),          # different strides per axis, kernel not a multiple of them
+    (1, 3, 64, 56, 56, (7, 7), (2, 2), (3, 3)),         # a ResNet stem
+    (2, 64, 128, 28, 28, (3, 3), (2, 2), (1, 1)),       # a down-sampling layer: 256 space-to-depth channels
+])
+def test_strided_conv2d_under_autocast_runs_through_space_to_depth(B, cin, cout, H, W, k, stride, pad):
+    """Strided convolutions reach the implicit-GEMM kernels through the space-to-depth layout: forward, data gradient
+    and weight gradient against an fp32 PyTorch convolution of the bf16-rounded operands."""
+    import ferrum_b200 as fb
+    from ferrum_b200 import nn
+    from ferrum_b200.ops import functional as F
+
+    torch.manual_seed(13)
+    conv = nn.Conv2d(cin, cout, k, stride, pad, 1, 1, device=fb.Device.Cuda(0))
+    x = torch.randn(B, cin, H, W, device="cuda", requires_grad=True)
+    with fb.autocast():
+        assert F.conv_igemm_ok(x, stride, (1, 1), pad, k, 1)
+        y = conv(x)
+    fb.utils.runtime.check_status()
+    r16 = lambda t: t.detach().bfloat16().float()
+    xr, wr = r16(x).requires_grad_(True), r16(conv.weight).requires_grad_(True)
+    br = conv.bias.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.conv2d(xr, wr, br, stride, pad, 1, 1)
+    assert y.shape == yr.shape
+    _close(y, yr, 2e-4)
+    g = torch.randn_like(yr).bfloat16().float()
+    y.backward(g)
+    yr.backward(g)
+    fb.utils.runtime.check_status()
+    _close(x.grad, xr.grad, 2e-4), _close(conv.weight.grad, wr.grad, 2e-4), _close(conv.bias.grad, br.grad, 2e-4)
+
+
 def test_conv1d_under_autocast_takes_the_implicit_gemm():
     """Conv1d is a one-row Conv2d: under autocast with stride 1 it runs on the implicit-GEMM kernels (patch 128 x 1)."""
     import ferrum_b200 as fb
