@@ -148,3 +148,30 @@ def test_new_switches_are_inert_without_a_gpu():
     mha = fb.nn.MultiHeadAttention(128, 2, memory_efficient=True)
     y = mha(torch.randn(2, 5, 128))
     assert tuple(y.shape) == (2, 5, 128)
+
+
+def test_space_to_depth_filters_reproduce_a_strided_convolution():
+    """The host-side half of the strided implicit-GEMM convolution, on the CPU: with the input rearranged as
+    z[b, I, J, (rh, rw, c)] = x_padded[b, c, I * sh + rh, J * sw + rw] and the filters rearranged by
+    ``_ConvS2dFn._filters``, a stride-1 convolution of z equals the strided convolution of x; the weight-gradient
+    mapping back is the exact inverse."""
+    import torch.nn.functional as TF
+
+    from ferrum_b200.ops.functional import _ConvS2dFn, conv_igemm_ok
+
+    torch.manual_seed(0)
+    for (B, C, O, H, W, k, s, p) in [(2, 3, 5, 17, 19, (3, 3), (2, 2), (1, 1)), (1, 4, 6, 16, 16, (4, 4), (4, 4), (0, 0)),
+                                     (2, 5, 7, 15, 20, (5, 3), (2, 3), (2, 1)), (1, 3, 4, 14, 14, (7, 7), (2, 2), (3, 3))]:
+        x, w = torch.randn(B, C, H, W), torch.randn(O, C, *k)
+        (sh, sw), (ph, pw) = s, p
+        Ho, Wo, k2h, k2w, Hz, Wz, Cz = _ConvS2dFn._geometry(x.shape, w.shape, s, p)
+        assert (Ho, Wo) == tuple(TF.conv2d(x, w, None, s, p).shape[2:]) and Cz % 8 == 0 and Cz >= sh * sw * C
+        xp = TF.pad(x, (pw, Wz * sw, ph, Hz * sh))[:, :, :Hz * sh, :Wz * sw]       # zero outside the image
+        z = xp.reshape(B, C, Hz, sh, Wz, sw).permute(0, 2, 4, 3, 5, 1).reshape(B, Hz, Wz, sh * sw * C)
+        w2 = _ConvS2dFn._filters(w, s, k2h, k2w, Cz)
+        assert w2.shape == (O, k2h, k2w, Cz) and not w2[..., sh * sw * C:].any()
+        y = TF.conv2d(z.permute(0, 3, 1, 2), w2[..., :sh * sw * C].permute(0, 3, 1, 2))
+        assert torch.allclose(y, TF.conv2d(x, w, None, s, p), atol=1e-4)
+        back = w2[..., :sh * sw * C].reshape(O, k2h, k2w, sh, sw, C).permute(0, 5, 1, 3, 2, 4)
+        assert torch.equal(back.reshape(O, C, k2h * sh, k2w * sw)[:, :, :k[0], :k[1]], w)
+        assert not conv_igemm_ok(x, s, (1, 1), p, k, 1)      # host tensors never take the tensor-core path
