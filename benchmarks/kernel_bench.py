@@ -163,6 +163,28 @@ def _cases(small: bool):
             y = F.conv2d_igemm(imgg if train else img, wconv, bconv, (1, 1), (1, 1))
         return torch.autograd.grad(y, (imgg, wconv, bconv), gconv) if train else y
 
+    # the same input through a stride-2 3 x 3 convolution, 64 -> 128 channels (a down-sampling layer)
+    wdown = (torch.randn(128, 64, 3, 3, device=dev) * 0.05).requires_grad_(True)
+    bdown = torch.zeros(128, device=dev, requires_grad=True)
+    gdown = torch.randn(img.shape[0], 128, 28, 28, device=dev)
+    down_bytes = img.numel() * 4 + gdown.numel() * 4
+
+    def down_window(train):
+        with fb_.autocast():
+            cols = F.im2col(imgg if train else img, (3, 3), (2, 2), (1, 1), (1, 1))
+            y = F.linear(cols, wdown.reshape(128, -1), bdown).reshape(img.shape[0], 28 * 28, 128)
+            y = y.transpose(1, 2).reshape(img.shape[0], 128, 28, 28)
+        return torch.autograd.grad(y, (imgg, wdown, bdown), gdown) if train else y
+
+    def down_implicit(train):
+        with fb_.autocast():
+            y = F.conv2d_igemm(imgg if train else img, wdown, bdown, (1, 1), (1, 1), (2, 2))
+        return torch.autograd.grad(y, (imgg, wdown, bdown), gdown) if train else y
+
+    case("conv2d_3x3_s2_fwd_bwd_window_matrix_bf16", lambda: down_window(True), 3 * down_bytes,
+         "K14 stride 2, 64 -> 128 channels: im2col + GEMMs + col2im")
+    case("conv2d_3x3_s2_fwd_bwd_implicit_gemm_bf16", lambda: down_implicit(True), 3 * down_bytes,
+         "K14 stride 2, 64 -> 128 channels: space-to-depth layout + implicit GEMMs in all three directions")
     case("conv2d_3x3_fwd_window_matrix_bf16", lambda: conv_window(False), conv_bytes,
          "K14 im2col (9x matrix) + tcgen05 GEMM + transpose back")
     case("conv2d_3x3_fwd_implicit_gemm_bf16", lambda: conv_implicit(False), conv_bytes,
