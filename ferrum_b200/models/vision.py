@@ -1,5 +1,7 @@
 """ResNet-18/34 and VGG-16/19 as laid out in ferrum-nn/src/models.rs:13-244 (no batch norm in the reference's
-blocks; convolutions run as im2col + GEMM kernels)."""
+blocks).  Under bf16 autocast every convolution here — the 7 x 7 stride-2 stem, the 3 x 3 layers, the stride-2
+layers and the 1 x 1 stride-2 shortcuts — runs on the implicit-GEMM tensor-core kernels; in fp32 they run as
+im2col + GEMM kernels."""
 from __future__ import annotations
 
 import torch

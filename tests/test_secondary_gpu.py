@@ -251,3 +251,36 @@ def test_small_cnn_trains():
         opt.step()
         losses.append(float(loss))
     assert losses[-1] < 0.5 * losses[0]
+
+
+def test_resnet18_under_autocast_matches_the_fp32_path():
+    """Every convolution of the model zoo's ResNet-18 on the implicit-GEMM kernels (7 x 7 stride-2 stem on three
+    channels, 3 x 3 stride-1 and stride-2 layers, 1 x 1 stride-2 shortcuts, no biases, feature maps down to 2 x 2):
+    logits agree with the fp32 im2col path within bf16 accuracy, weight gradients in direction."""
+    import copy
+
+    import ferrum_b200 as fb
+    from ferrum_b200.models.vision import ResNet
+
+    torch.manual_seed(21)
+    net = ResNet.resnet18(10, device=fb.Device.Cuda(0))
+    ref = copy.deepcopy(net)
+    x = torch.randn(4, 3, 64, 64, device="cuda")
+    with fb.autocast():
+        y = net(x)
+    yr = ref(x)
+    fb.utils.runtime.check_status()
+    assert y.shape == yr.shape == (4, 10)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+    assert rel(y, yr) < 5e-2, rel(y, yr)
+    g = torch.randn_like(yr)
+    y.float().backward(g)
+    yr.backward(g)
+    fb.utils.runtime.check_status()
+    # seventeen bf16 layers with ReLU and max-pool switches between the loss and the stem: the gradients agree in
+    # direction, not digit by digit
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten().float(), b.flatten().float(), dim=0).item()
+    for a, b in ((net.conv1.weight.grad, ref.conv1.weight.grad),
+                 (net.blocks[2].downsample.weight.grad, ref.blocks[2].downsample.weight.grad),
+                 (net.fc.weight.grad, ref.fc.weight.grad)):
+        assert torch.isfinite(a).all() and cos(a, b) > 0.8, cos(a, b)
