@@ -67,6 +67,27 @@ def test_ops_namespace_and_prelude():
                  "SGD", "StepLR", "OneCycleLR", "DataLoader", "DistributedSampler", "save", "load", "GradientTape",
                  "no_grad", "DistributedDataParallel", "ReduceOp", "mse_loss", "nll_loss", "init_process_group"):
         assert name in ns, name
+    # the whole public checklist of the reference's facade: prelude names and the per-crate extras
+    import ferrum_b200 as fb
+
+    prelude_names = ("DType Device FerrumError Shape Tensor backward GradientTape AutogradTensor NoGradGuard no_grad "
+                     "Linear Module ReLU Sequential Sigmoid Tanh GELU SiLU Softmax LogSoftmax LeakyReLU ELU LayerNorm "
+                     "BatchNorm1d Dropout Embedding bce_loss cross_entropy_loss l1_loss log_softmax mse_loss nll_loss "
+                     "smooth_l1_loss softmax Adam AdamConfig Optimizer SGDConfig SGD LRScheduler StepLR MultiStepLR "
+                     "ExponentialLR CosineAnnealingLR CosineAnnealingWarmRestarts LinearWarmupLR OneCycleLR "
+                     "ReduceLROnPlateau PlateauMode load save DataLoader Dataset TensorDataset Subset train_test_split "
+                     "RandomSampler SequentialSampler DistributedSampler init_process_group get_rank get_world_size "
+                     "is_main_process barrier Backend ProcessGroup DistributedDataParallel ReduceOp").split()
+    assert [n for n in prelude_names if n not in ns] == []
+    extras = {"nn": "Conv2d LSTM MultiHeadAttention ResNet MLP VGG BasicBlock init",
+              "optim": "GradScaler Autocast clip_grad_norm",
+              "data": "BatchSampler WeightedRandomSampler SubsetRandomSampler MapDataset ConcatDataset Compose Normalize",
+              "distributed": "init_process_group_from_env destroy_process_group get_world is_initialized BackendConfig "
+                             "new_group GradientBucket"}
+    for mod, names in extras.items():
+        assert [n for n in names.split() if not hasattr(getattr(fb, mod), n)] == [], mod
+    assert callable(fb.banner) and hasattr(fb, "cuda")
+    assert fb.nn.MLP.new([4, 8, 2])(Tensor.ones([3, 4])).shape == (3, 2)
 
 
 def test_conv_pool_rnn_transformer_shapes_and_values():
