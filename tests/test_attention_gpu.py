@@ -309,7 +309,10 @@ def test_backward_kernels_work_as_the_first_cuda_work_of_the_autograd_thread():
             "torch.cuda.synchronize()\n"
             "assert all(bool(torch.isfinite(t.float()).all()) for t in (dq, dk, dv))\n"
             "print('ok')\n")
-    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))     # the package lives beside tests/
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=root)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
 
 
